@@ -1,0 +1,817 @@
+"""Training / model configuration.
+
+Two dataclasses live here:
+
+* :class:`ModelConfig` (alias ``DeepSeekConfig``) -- the architecture of the
+  decoder (dense, MoE, MoD or hybrid).  Field names follow the reference model
+  config (reference ``core/model.py:2271-2401``) so checkpoints and user code
+  carry over.
+* :class:`Config` -- the full run configuration (architecture + optimisation +
+  data + parallelism + monitoring), field-compatible with the reference
+  ``config/config_manager.py:14-158``, plus the knobs this framework adds
+  (fp8 mode, ZeRO/EP/PP degrees, fused-communication switches).
+
+Differences from the reference that are deliberate:
+
+* ``validate`` accepts any ``num_experts >= 2`` and ``fp8`` precisions (the
+  reference rejects 4 experts and fp8 although its docs advertise both,
+  ``config_manager.py:521-570``).
+* auto-configuration is a pure function of the fields and the visible
+  hardware and never mutates on attribute access.
+* unknown attributes set with ``setattr`` are kept in ``extras`` on
+  serialisation, so the "edit the dict" launch style keeps working.
+"""
+from __future__ import annotations
+
+import copy
+import dataclasses
+import json
+import math
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+try:  # yaml is optional; JSON is always available
+    import yaml  # type: ignore
+except Exception:  # pragma: no cover
+    yaml = None
+
+PRECISIONS = (
+    "auto", "fp32", "fp16", "bf16", "mixed_fp16", "mixed_bf16", "tf32", "fp64",
+    "fp8", "fp8_e4m3", "fp8_e5m2", "mixed_fp8", "int8", "int4",
+)
+MOE_PATTERNS = ("all", "every_2nd", "every_3rd", "every_4th", "sandwich", "none", "odd")
+SCHEDULERS = ("cosine", "onecycle", "constant", "linear", "warmup_decay")
+
+
+def _round_up(x: int, m: int) -> int:
+    return ((int(x) + m - 1) // m) * m
+
+
+# --------------------------------------------------------------------------- #
+# Model architecture
+# --------------------------------------------------------------------------- #
+@dataclass
+class ModelConfig:
+    vocab_size: int = 50257
+    hidden_size: int = 768
+    num_layers: int = 12
+    num_heads: int = 12
+    num_kv_heads: Optional[int] = None
+    intermediate_size: Optional[int] = None
+    seq_length: int = 2048
+    dropout: float = 0.0
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    rope_scaling_factor: float = 1.0
+    init_std: float = 0.02
+    use_stable_embedding: bool = True
+    tie_word_embeddings: bool = True
+    gradient_checkpointing: bool = False
+    use_flash_attention: bool = True
+    # MoE
+    use_moe: bool = False
+    num_experts: int = 8
+    moe_top_k: int = 2
+    capacity_factor: float = 1.25
+    load_balancing_weight: float = 0.01
+    routing_temperature: float = 1.0
+    routing_noise_std: float = 0.0
+    moe_pattern: str = "all"
+    moe_layers: Optional[List[int]] = None  # explicit layer list wins over moe_pattern
+    dense_start_layers: int = 2
+    dense_end_layers: int = 2
+    expert_output_scaling: float = 1.0
+    drop_tokens: bool = True  # apply capacity_factor (False = dropless)
+    # MoD
+    use_mod: bool = False
+    mod_capacity_factor: float = 0.5
+    mod_routing_temperature: float = 1.0
+    mod_layers: Optional[List[int]] = None
+    mod_per_sequence: bool = True
+    mod_aux_weight: float = 0.01
+    # misc
+    scale_lm_head_output: bool = False
+    use_cuda_moe: bool = True
+    fp8: bool = False
+    init_mode: str = "normal"  # "normal" = every weight N(0, init_std); "scaled" = depth-scaled
+
+    def __post_init__(self):
+        if self.num_kv_heads is None:
+            self.num_kv_heads = self.num_heads
+        if self.intermediate_size is None:
+            self.intermediate_size = 4 * self.hidden_size
+        self.validate()
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_heads
+
+    def validate(self) -> None:
+        if self.hidden_size % self.num_heads:
+            raise ValueError(f"hidden_size {self.hidden_size} not divisible by num_heads {self.num_heads}")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"num_heads {self.num_heads} not divisible by num_kv_heads {self.num_kv_heads}")
+        if self.head_dim % 2:
+            raise ValueError("head_dim must be even for rotary embeddings")
+        if self.use_moe:
+            if self.num_experts < 2:
+                raise ValueError("num_experts must be >= 2")
+            if not 1 <= self.moe_top_k <= self.num_experts:
+                raise ValueError("moe_top_k must be in [1, num_experts]")
+            if self.capacity_factor <= 0:
+                raise ValueError("capacity_factor must be positive")
+        if self.moe_pattern not in MOE_PATTERNS:
+            raise ValueError(f"moe_pattern must be one of {MOE_PATTERNS}")
+        if self.use_mod and not 0.0 < self.mod_capacity_factor <= 1.0:
+            raise ValueError("mod_capacity_factor must be in (0, 1]")
+
+    # -- layer typing -------------------------------------------------------
+    def is_moe_layer(self, idx: int) -> bool:
+        if not self.use_moe:
+            return False
+        if self.moe_layers is not None:
+            return idx in self.moe_layers
+        p, n = self.moe_pattern, self.num_layers
+        if p == "all":
+            return True
+        if p == "none":
+            return False
+        if p == "odd":
+            return idx % 2 == 1
+        if p == "every_2nd":
+            return (idx + 1) % 2 == 0
+        if p == "every_3rd":
+            return (idx + 1) % 3 == 0
+        if p == "every_4th":
+            return (idx + 1) % 4 == 0
+        if p == "sandwich":
+            return self.dense_start_layers <= idx < n - self.dense_end_layers
+        return False
+
+    def is_mod_layer(self, idx: int) -> bool:
+        if not self.use_mod:
+            return False
+        if self.mod_layers is not None:
+            return idx in self.mod_layers
+        # hybrid: Mixture-of-Depths on the layers that are not MoE
+        return not self.is_moe_layer(idx)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return dataclasses.asdict(self)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "ModelConfig":
+        names = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in names})
+
+    # presets mirroring reference model.py classmethods
+    @classmethod
+    def standard_moe(cls, **kw) -> "ModelConfig":
+        return cls(use_moe=True, use_mod=False, moe_pattern="all", **kw)
+
+    @classmethod
+    def hybrid_moe_mod(cls, **kw) -> "ModelConfig":
+        return cls(use_moe=True, use_mod=True, moe_pattern=kw.pop("moe_pattern", "every_2nd"), **kw)
+
+    @classmethod
+    def standard_dense_with_mod(cls, **kw) -> "ModelConfig":
+        return cls(use_moe=False, use_mod=True, **kw)
+
+    def num_parameters(self, active_only: bool = False) -> int:
+        h, i, v = self.hidden_size, self.intermediate_size, self.vocab_size
+        kvd = self.num_kv_heads * self.head_dim
+        attn = 2 * h * h + 2 * h * kvd
+        ffn = 3 * h * i
+        total = v * h * (1 if self.tie_word_embeddings else 2) + h
+        for l in range(self.num_layers):
+            total += attn + 2 * h
+            if self.is_moe_layer(l):
+                e = self.moe_top_k if active_only else self.num_experts
+                total += e * ffn + h * self.num_experts
+            else:
+                total += ffn + ((h + 1) if self.is_mod_layer(l) else 0)
+        return total
+
+
+DeepSeekConfig = ModelConfig  # reference name
+
+
+# --------------------------------------------------------------------------- #
+# Run configuration
+# --------------------------------------------------------------------------- #
+@dataclass
+class Config:
+    # -- architecture --------------------------------------------------------
+    vocab_size: int = 50304
+    hidden_size: int = 512
+    num_layers: int = 8
+    num_heads: int = 8
+    num_kv_heads: int = 4
+    seq_length: int = 1024
+    intermediate_size: Optional[int] = None
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    dropout: float = 0.0
+    # -- optimisation --------------------------------------------------------
+    batch_size: int = 2
+    micro_batch_size: Optional[int] = None
+    gradient_accumulation_steps: int = 8
+    learning_rate: float = 1e-4
+    weight_decay: float = 0.01
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_eps: float = 1e-8
+    max_grad_norm: float = 1.0
+    num_epochs: int = 3
+    warmup_ratio: float = 0.15
+    eval_every_n_batches: int = 500
+    save_every_n_batches: int = 1000
+    precision: str = "auto"
+    inference_precision: str = "auto"
+    compile: bool = False  # no tracing compiler on the hot path; kept for API parity
+    # -- data ----------------------------------------------------------------
+    train_data_path: str = "data/train.jsonl"
+    eval_data_path: str = "data/eval.jsonl"
+    training_mode: str = "finetuning_only"
+    base_training_paths: Optional[List[str]] = None
+    finetuning_paths: Optional[List[str]] = None
+    base_eval_paths: Optional[List[str]] = None
+    finetuning_eval_paths: Optional[List[str]] = None
+    base_finetuning_ratio: float = 0.5
+    num_workers: int = 2
+    assistant_loss_weight: float = 1.5
+    max_conversations_per_file: int = 10000
+    streaming_threshold_gb: float = 10.0
+    prefetch_factor: int = 4
+    pin_memory: bool = True
+    # -- generation ----------------------------------------------------------
+    max_new_tokens: int = 512
+    temperature: float = 0.8
+    top_p: float = 0.9
+    top_k: int = 50
+    repetition_penalty: float = 1.1
+    use_kv_cache: bool = True
+    kv_cache_dtype: str = "bf16"
+    # -- stability -----------------------------------------------------------
+    init_std: float = 0.02
+    layer_norm_eps: float = 1e-5
+    use_stable_embedding: bool = True
+    gradient_checkpointing: bool = True
+    tie_word_embeddings: bool = True
+    use_flash_attention: bool = True
+    # -- MoE / MoD -----------------------------------------------------------
+    use_moe: bool = True
+    use_mod: bool = False
+    num_experts: int = 8
+    moe_top_k: int = 2
+    capacity_factor: float = 1.25
+    load_balancing_weight: float = 0.01
+    routing_temperature: float = 1.0
+    routing_noise_std: float = 0.0
+    moe_pattern: str = "all"
+    mod_capacity_factor: float = 0.5
+    mod_routing_temperature: float = 1.0
+    expert_parallel_size: Optional[int] = None
+    # -- sharding (DeepSpeed-compatible names) -----------------------------
+    use_deepspeed: bool = False
+    zero_stage: int = 0
+    cpu_offload: bool = False
+    cpu_offload_optimizer: bool = False
+    cpu_offload_parameters: bool = False
+    aggressive_cpu_offload: bool = False
+    nvme_path: Optional[str] = None
+    nvme_offload_optimizer: bool = False
+    nvme_offload_parameters: bool = False
+    gradient_compression: bool = False
+    communication_backend: str = "nccl"
+    overlap_comm: bool = True
+    contiguous_gradients: bool = True
+    allgather_bucket_size: int = 500_000_000
+    reduce_bucket_size: int = 500_000_000
+    # framework-native parallel layout
+    backend: str = "native"  # native | fsdp | deepspeed | colossalai  (all map onto the native engine)
+    fsdp_sharding_strategy: str = "FULL_SHARD"
+    fsdp_auto_wrap_threshold: int = 100_000_000
+    pipeline_parallel_size: int = 1
+    tensor_parallel_size: int = 1
+    sequence_parallel_size: int = 1
+    num_microbatches: int = 1
+    fused_comm: bool = True  # peer-memory kernels; False = NCCL-only baseline path
+    use_nvls: bool = False
+    # -- production ----------------------------------------------------------
+    experiment_name: Optional[str] = None
+    output_dir: str = "experiments"
+    seed: int = 42
+    log_level: str = "INFO"
+    log_every_n_steps: int = 50
+    save_total_limit: int = 5
+    early_stopping_patience: Optional[int] = None
+    min_lr: float = 1e-6
+    lr_scheduler: str = "cosine"
+    use_lr_scheduler: bool = True
+    # -- monitoring / fault tolerance -----------------------------------------
+    health_check_interval: int = 100
+    auto_resume: bool = True
+    backup_every_n_hours: int = 6
+    max_retries: int = 3
+    enable_wandb: bool = False
+    wandb_project: Optional[str] = None
+    wandb_entity: Optional[str] = None
+    comm_timeout_s: float = 1.0
+    heartbeat_interval_s: float = 0.5
+    # -- adaptive LR ------------------------------------------------------------
+    enable_adaptive_lr: bool = True
+    allow_scheduler_override: bool = True
+    min_override_threshold: float = 0.2
+    emergency_override_enabled: bool = True
+    log_lr_decisions: bool = True
+    adaptive_log_frequency: int = 100
+    # -- precision ---------------------------------------------------------------
+    auto_tune_precision: bool = True
+    precision_target: str = "balanced"
+    dynamic_precision: bool = False
+    tf32_enabled: Optional[bool] = None
+    fp16_loss_scale: float = 65536.0
+    bf16_enabled: bool = True
+    quantization_method: Optional[str] = None
+    quantization_bits: Optional[int] = None
+    # -- memory -------------------------------------------------------------------
+    max_memory_usage: float = 0.9
+    memory_cleanup_interval: int = 1000
+    enable_cpu_adam: bool = False
+    partition_activations: bool = False
+    # -- multi-node ----------------------------------------------------------------
+    master_addr: Optional[str] = None
+    master_port: int = 29500
+    world_size: Optional[int] = None
+    rank: Optional[int] = None
+    local_rank: Optional[int] = None
+    # -- data processing -------------------------------------------------------------
+    data_cache_dir: str = "data/cache"
+    tokenizer_cache_dir: str = "tokenizers/cache"
+    max_seq_length_percentile: float = 0.95
+    # -- checkpointing ---------------------------------------------------------------
+    save_optimizer_states: bool = True
+    checkpoint_compression: bool = True
+    async_save: bool = True
+    universal_checkpoint: bool = True
+    # -- profiling -------------------------------------------------------------------
+    profile_memory: bool = False
+    profile_communication: bool = False
+    log_throughput: bool = True
+    enable_profiling: bool = False
+    # -- Chinchilla planner ------------------------------------------------------------
+    auto_epoch_scaling: bool = True
+    chinchilla_multiplier: float = 20.0
+    min_auto_epochs: int = 1
+    max_auto_epochs: int = 50
+    enable_loss_landscape: bool = True
+    enable_compute_efficiency: bool = True
+    enable_adaptive_curriculum: bool = True
+    enable_early_stopping: bool = True
+    plateau_patience: int = 5
+    efficiency_decline_threshold: float = 0.3
+    convergence_threshold: float = 0.85
+
+    _batch_size_set: bool = field(default=False, init=False, repr=False)
+    _device_optimizations_applied: bool = field(default=False, init=False, repr=False)
+
+    # ----------------------------------------------------------------------- #
+    def __post_init__(self):
+        self.validate()
+        self._auto_configure()
+
+    # -- validation ----------------------------------------------------------
+    def validate(self) -> None:
+        errs: List[str] = []
+        if self.hidden_size <= 0 or self.num_layers <= 0:
+            errs.append("hidden_size and num_layers must be positive")
+        if self.num_heads <= 0 or self.hidden_size % self.num_heads:
+            errs.append(f"hidden_size ({self.hidden_size}) must be divisible by num_heads ({self.num_heads})")
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads:
+            errs.append(f"num_heads ({self.num_heads}) must be divisible by num_kv_heads ({self.num_kv_heads})")
+        if self.precision not in PRECISIONS:
+            errs.append(f"precision must be one of {PRECISIONS}")
+        if self.inference_precision not in PRECISIONS:
+            errs.append(f"inference_precision must be one of {PRECISIONS}")
+        if self.use_moe:
+            if self.num_experts < 2:
+                errs.append("num_experts must be >= 2")
+            if not 1 <= self.moe_top_k <= max(self.num_experts, 1):
+                errs.append("moe_top_k must be in [1, num_experts]")
+            if self.capacity_factor < 1.0:
+                errs.append("capacity_factor must be >= 1.0")
+        if not 0 <= self.zero_stage <= 3:
+            errs.append("zero_stage must be 0..3")
+        if self.batch_size <= 0 or self.gradient_accumulation_steps <= 0:
+            errs.append("batch_size and gradient_accumulation_steps must be positive")
+        if not 0.0 <= self.warmup_ratio <= 1.0:
+            errs.append("warmup_ratio must be in [0, 1]")
+        if self.learning_rate <= 0:
+            errs.append("learning_rate must be positive")
+        if self.weight_decay < 0:
+            errs.append("weight_decay must be non-negative")
+        if self.lr_scheduler not in SCHEDULERS:
+            errs.append(f"lr_scheduler must be one of {SCHEDULERS}")
+        if not 0 < self.max_memory_usage <= 1:
+            errs.append("max_memory_usage must be in (0, 1]")
+        if errs:
+            raise ValueError("invalid configuration: " + "; ".join(errs))
+
+    # -- derived values ------------------------------------------------------
+    def _auto_configure(self) -> None:
+        if self.experiment_name is None:
+            self.experiment_name = time.strftime("experiment_%Y%m%d_%H%M%S")
+        self.vocab_size = _round_up(self.vocab_size, 64)
+        if self.intermediate_size is None:
+            self.intermediate_size = _round_up(math.ceil(8 * self.hidden_size / 3), 64)
+        if self.micro_batch_size is None:
+            self.micro_batch_size = self.batch_size
+        n_dev = self._visible_devices()
+        if self.expert_parallel_size is None:
+            ep = 1
+            if self.use_moe:
+                ep = math.gcd(self.num_experts, max(n_dev, 1))
+            self.expert_parallel_size = max(ep, 1)
+        if self.precision == "auto":
+            self.precision = self._auto_precision()
+        if self.inference_precision == "auto":
+            self.inference_precision = "bf16" if "bf16" in self.precision or "fp8" in self.precision else (
+                "fp16" if "fp16" in self.precision else "fp32")
+        if self.tf32_enabled is None:
+            self.tf32_enabled = self.precision in ("tf32", "mixed_bf16", "mixed_fp16", "bf16", "fp16")
+
+    @staticmethod
+    def _visible_devices() -> int:
+        try:
+            import torch
+            return torch.cuda.device_count() if torch.cuda.is_available() else 0
+        except Exception:
+            return 0
+
+    @staticmethod
+    def _auto_precision() -> str:
+        try:
+            import torch
+            if torch.cuda.is_available():
+                major, _ = torch.cuda.get_device_capability()
+                return "mixed_bf16" if major >= 8 else "mixed_fp16"
+        except Exception:
+            pass
+        return "fp32"
+
+    @property
+    def effective_batch_size(self) -> int:
+        ws = self.world_size or 1
+        return self.micro_batch_size * self.gradient_accumulation_steps * ws
+
+    # -- conversions ---------------------------------------------------------
+    def to_model_config(self) -> ModelConfig:
+        """Every architecture field is forwarded (the reference forwards only 19 and
+        silently loses use_mod / moe_pattern / temperatures, ``Main.py:572-602``)."""
+        return ModelConfig(
+            vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_layers=self.num_layers,
+            num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+            intermediate_size=self.intermediate_size, seq_length=self.seq_length, dropout=self.dropout,
+            rms_norm_eps=self.rms_norm_eps, rope_theta=self.rope_theta, init_std=self.init_std,
+            use_stable_embedding=self.use_stable_embedding, tie_word_embeddings=self.tie_word_embeddings,
+            gradient_checkpointing=self.gradient_checkpointing, use_flash_attention=self.use_flash_attention,
+            use_moe=self.use_moe, num_experts=self.num_experts, moe_top_k=self.moe_top_k,
+            capacity_factor=self.capacity_factor, load_balancing_weight=self.load_balancing_weight,
+            routing_temperature=self.routing_temperature, routing_noise_std=self.routing_noise_std,
+            moe_pattern=self.moe_pattern, use_mod=self.use_mod, mod_capacity_factor=self.mod_capacity_factor,
+            mod_routing_temperature=self.mod_routing_temperature,
+            fp8=self.precision in ("fp8", "fp8_e4m3", "mixed_fp8"),
+        )
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = {f.name: getattr(self, f.name) for f in dataclasses.fields(self) if not f.name.startswith("_")}
+        extras = {k: v for k, v in self.__dict__.items()
+                  if k not in d and not k.startswith("_") and _jsonable(v)}
+        if extras:
+            d["extras"] = extras
+        return d
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "Config":
+        d = dict(d)
+        d.pop("_metadata", None)
+        extras = d.pop("extras", {}) or {}
+        names = {f.name for f in dataclasses.fields(cls) if f.init}
+        known = {k: v for k, v in d.items() if k in names}
+        cfg = cls(**known)
+        for k, v in {**{k: v for k, v in d.items() if k not in names}, **extras}.items():
+            setattr(cfg, k, v)
+        return cfg
+
+    def save(self, path: str) -> None:
+        payload = self.to_dict()
+        payload["_metadata"] = {"saved_at": time.strftime("%Y-%m-%dT%H:%M:%S"), "format": 1}
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(path, "w") as f:
+            if path.endswith((".yaml", ".yml")) and yaml is not None:
+                yaml.safe_dump(payload, f, sort_keys=False)
+            else:
+                json.dump(payload, f, indent=2)
+
+    @classmethod
+    def load(cls, path: str) -> "Config":
+        with open(path) as f:
+            if path.endswith((".yaml", ".yml")) and yaml is not None:
+                payload = yaml.safe_load(f)
+            else:
+                payload = json.load(f)
+        return cls.from_dict(payload)
+
+    def copy(self, **overrides) -> "Config":
+        c = copy.deepcopy(self)
+        for k, v in overrides.items():
+            setattr(c, k, v)
+        return c
+
+    # -- estimates -----------------------------------------------------------
+    def num_parameters(self, active_only: bool = False) -> int:
+        return self.to_model_config().num_parameters(active_only)
+
+    def get_memory_estimate_gb(self, world_size: int = 1) -> Dict[str, float]:
+        """bf16 params + bf16 grads + fp32 master/m/v, sharded per the ZeRO stage, plus a
+        per-layer-recompute activation estimate (reference ``config_manager.py:572-614``)."""
+        n = self.num_parameters()
+        w = max(world_size, 1)
+        params = 2 * n / (w if self.zero_stage >= 3 else 1)
+        grads = 2 * n / (w if self.zero_stage >= 2 else 1)
+        optim = 12 * n / (w if self.zero_stage >= 1 else 1)
+        tokens = self.micro_batch_size * self.seq_length
+        act_per_layer = tokens * self.hidden_size * 2 * (2 if self.gradient_checkpointing else 18)
+        acts = act_per_layer * self.num_layers + tokens * self.vocab_size * 2 * 0.25
+        gb = 1024 ** 3
+        out = {"parameters": params / gb, "gradients": grads / gb, "optimizer": optim / gb,
+               "activations": acts / gb}
+        out["total"] = sum(out.values())
+        return out
+
+    def to_deepspeed_config(self) -> Dict[str, Any]:
+        """DeepSpeed-style JSON view of the sharding knobs.  The native engine consumes the
+        same dictionary (bucket sizes, overlap, stage) so reference launch scripts that
+        inspect or dump this JSON keep working (reference ``config_manager.py:649-756``)."""
+        ds: Dict[str, Any] = {
+            "train_batch_size": self.effective_batch_size,
+            "train_micro_batch_size_per_gpu": self.micro_batch_size,
+            "gradient_accumulation_steps": self.gradient_accumulation_steps,
+            "gradient_clipping": self.max_grad_norm,
+            "steps_per_print": self.log_every_n_steps,
+            "zero_optimization": {
+                "stage": self.zero_stage,
+                "overlap_comm": self.overlap_comm,
+                "contiguous_gradients": self.contiguous_gradients,
+                "reduce_scatter": True,
+                "reduce_bucket_size": self.reduce_bucket_size,
+                "allgather_bucket_size": self.allgather_bucket_size,
+            },
+            "optimizer": {"type": "AdamW", "params": {
+                "lr": self.learning_rate, "betas": [self.adam_beta1, self.adam_beta2],
+                "eps": self.adam_eps, "weight_decay": self.weight_decay}},
+            "bf16": {"enabled": "bf16" in self.precision or "fp8" in self.precision},
+            "fp16": {"enabled": "fp16" in self.precision, "initial_scale_power": 16,
+                     "loss_scale_window": 1000, "hysteresis": 2, "min_loss_scale": 1},
+        }
+        if self.zero_stage >= 3:
+            ds["zero_optimization"].update({
+                "stage3_prefetch_bucket_size": 50_000_000,
+                "stage3_param_persistence_threshold": 100_000,
+                "stage3_max_live_parameters": 1_000_000_000,
+                "stage3_max_reuse_distance": 1_000_000_000,
+            })
+        if self.cpu_offload or self.cpu_offload_optimizer:
+            ds["zero_optimization"]["offload_optimizer"] = {"device": "cpu", "pin_memory": True}
+        if self.cpu_offload_parameters:
+            ds["zero_optimization"]["offload_param"] = {"device": "cpu", "pin_memory": True}
+        if self.nvme_path:
+            ds["zero_optimization"].setdefault("offload_optimizer", {})
+            ds["zero_optimization"]["offload_optimizer"].update({"device": "nvme", "nvme_path": self.nvme_path})
+        if self.gradient_compression:
+            ds["compression_training"] = {"enabled": True}
+        if self.use_moe:
+            ds["moe"] = {"enabled": True, "num_experts": self.num_experts, "top_k": self.moe_top_k,
+                         "capacity_factor": self.capacity_factor,
+                         "expert_parallel_size": self.expert_parallel_size}
+        if self.gradient_checkpointing:
+            ds["activation_checkpointing"] = {"partition_activations": self.partition_activations,
+                                              "contiguous_memory_optimization": False}
+        if self.lr_scheduler in ("warmup_decay", "linear"):
+            ds["scheduler"] = {"type": "WarmupDecayLR", "params": {"warmup_min_lr": self.min_lr,
+                                                                    "warmup_max_lr": self.learning_rate}}
+        return ds
+
+
+def _jsonable(v: Any) -> bool:
+    try:
+        json.dumps(v)
+        return True
+    except Exception:
+        return False
+
+
+# --------------------------------------------------------------------------- #
+# Presets
+# --------------------------------------------------------------------------- #
+class ConfigPresets:
+    """Named configurations.  ``debug … b300`` follow the reference preset ladder
+    (reference ``config_manager.py:759-1667``; README table ``Readme.md:198-209``);
+    dimensions are chosen tensor-core friendly (head_dim 64/128, sizes multiples
+    of 128).  ``tiny_cpu``, ``dense_1b``, ``mixtral_8x7b``, ``hybrid_fp8`` and
+    ``b1_moe`` are the benchmark shapes."""
+
+    _LADDER = {
+        # name: hidden, layers, heads, kv, seq, experts, lr
+        "debug":      (128, 2, 2, 1, 256, 8, 1e-3),
+        "debug_200m": (768, 12, 12, 4, 1024, 8, 5e-4),
+        "debug_300m": (1024, 12, 16, 4, 1024, 8, 5e-4),
+        "moe_stress_test": (512, 4, 8, 2, 512, 16, 5e-4),
+        "b1":   (2048, 22, 32, 4, 2048, 8, 3e-4),
+        "b7":   (4096, 32, 32, 8, 4096, 8, 1e-4),
+        "b14":  (5120, 40, 40, 10, 4096, 8, 8e-5),
+        "b30":  (6656, 60, 52, 4, 4096, 8, 6e-5),
+        "b50":  (8192, 64, 64, 8, 4096, 8, 5e-5),
+        "b75":  (8192, 96, 64, 8, 4096, 8, 4e-5),
+        "b100": (10240, 80, 80, 8, 4096, 8, 3e-5),
+        "b200": (12288, 96, 96, 8, 4096, 8, 2e-5),
+        "b300": (14336, 104, 112, 8, 4096, 8, 1.5e-5),
+    }
+
+    @classmethod
+    def names(cls) -> List[str]:
+        return list(cls._LADDER) + ["tiny_cpu", "dense_1b", "b1_moe", "mixtral_8x7b", "hybrid_fp8"]
+
+    @classmethod
+    def get(cls, name: str, **overrides) -> Config:
+        if name in cls._LADDER:
+            h, l, nh, kv, s, e, lr = cls._LADDER[name]
+            base = dict(hidden_size=h, num_layers=l, num_heads=nh, num_kv_heads=kv, seq_length=s,
+                        num_experts=e, learning_rate=lr, use_moe=True, moe_top_k=2,
+                        experiment_name=name, batch_size=2 if h >= 2048 else 8,
+                        gradient_accumulation_steps=4, vocab_size=50304,
+                        zero_stage=0 if h < 4096 else (2 if h < 8192 else 3),
+                        gradient_checkpointing=h >= 2048)
+        elif hasattr(cls, "_" + name):
+            base = getattr(cls, "_" + name)()
+        else:
+            raise KeyError(f"unknown preset {name!r}; available: {cls.names()}")
+        base.update(overrides)
+        return Config(**base)
+
+    # benchmark shapes -------------------------------------------------------
+    @staticmethod
+    def _tiny_cpu() -> Dict[str, Any]:
+        return dict(vocab_size=8192, hidden_size=256, num_layers=4, num_heads=8, num_kv_heads=2,
+                    intermediate_size=688, seq_length=256, batch_size=4, micro_batch_size=4,
+                    gradient_accumulation_steps=1, use_moe=True, num_experts=4, moe_top_k=2,
+                    capacity_factor=1.25, load_balancing_weight=0.01, moe_pattern="odd",
+                    learning_rate=3e-4, precision="fp32", tie_word_embeddings=False,
+                    gradient_checkpointing=False, experiment_name="tiny_cpu")
+
+    @staticmethod
+    def _dense_1b() -> Dict[str, Any]:
+        return dict(vocab_size=32000, hidden_size=2048, num_layers=22, num_heads=32, num_kv_heads=4,
+                    intermediate_size=5632, seq_length=2048, batch_size=8, micro_batch_size=8,
+                    gradient_accumulation_steps=1, use_moe=False, precision="mixed_bf16",
+                    tie_word_embeddings=False, zero_stage=3, max_grad_norm=1.0,
+                    experiment_name="dense_1b")
+
+    @staticmethod
+    def _b1_moe() -> Dict[str, Any]:
+        d = ConfigPresets._dense_1b()
+        d.update(use_moe=True, num_experts=8, moe_top_k=2, capacity_factor=1.25,
+                 load_balancing_weight=0.01, moe_pattern="all", zero_stage=1,
+                 batch_size=4, micro_batch_size=4, experiment_name="b1_moe")
+        return d
+
+    @staticmethod
+    def _mixtral_8x7b() -> Dict[str, Any]:
+        return dict(vocab_size=32000, hidden_size=4096, num_layers=32, num_heads=32, num_kv_heads=8,
+                    intermediate_size=14336, seq_length=4096, batch_size=1, micro_batch_size=1,
+                    gradient_accumulation_steps=1, use_moe=True, num_experts=8, moe_top_k=2,
+                    capacity_factor=1.25, load_balancing_weight=0.01, moe_pattern="all",
+                    precision="mixed_bf16", tie_word_embeddings=False, zero_stage=1,
+                    expert_parallel_size=8, experiment_name="mixtral_8x7b")
+
+    @staticmethod
+    def _hybrid_fp8() -> Dict[str, Any]:
+        return dict(vocab_size=32000, hidden_size=2048, num_layers=24, num_heads=16, num_kv_heads=4,
+                    intermediate_size=1408, seq_length=4096, batch_size=4, micro_batch_size=4,
+                    gradient_accumulation_steps=1, use_moe=True, use_mod=True, num_experts=16,
+                    moe_top_k=2, capacity_factor=1.25, moe_pattern="every_2nd",
+                    mod_capacity_factor=0.125, precision="mixed_fp8", tie_word_embeddings=False,
+                    zero_stage=1, expert_parallel_size=8, experiment_name="hybrid_fp8")
+
+    @classmethod
+    def get_preset_info(cls) -> Dict[str, Dict[str, Any]]:
+        info = {}
+        for n in cls.names():
+            c = cls.get(n)
+            info[n] = {"hidden_size": c.hidden_size, "num_layers": c.num_layers, "num_heads": c.num_heads,
+                       "seq_length": c.seq_length, "num_experts": c.num_experts if c.use_moe else 0,
+                       "total_params": c.num_parameters(), "active_params": c.num_parameters(True),
+                       "memory_gb": round(c.get_memory_estimate_gb()["total"], 1)}
+        return info
+
+    @classmethod
+    def compare_presets(cls, names: Optional[List[str]] = None) -> str:
+        info = cls.get_preset_info()
+        rows = ["preset        hidden layers heads  seq  experts  total(B) active(B) mem(GB)"]
+        for n in (names or cls.names()):
+            i = info[n]
+            rows.append(f"{n:<13}{i['hidden_size']:>6}{i['num_layers']:>7}{i['num_heads']:>6}{i['seq_length']:>6}"
+                        f"{i['num_experts']:>8}{i['total_params'] / 1e9:>10.2f}{i['active_params'] / 1e9:>10.2f}"
+                        f"{i['memory_gb']:>8.1f}")
+        return "\n".join(rows)
+
+
+for _n in ConfigPresets._LADDER:  # ConfigPresets.b7() style accessors
+    setattr(ConfigPresets, _n, staticmethod(lambda _n=_n, **kw: ConfigPresets.get(_n, **kw)))
+for _n in ("tiny_cpu", "dense_1b", "b1_moe", "mixtral_8x7b", "hybrid_fp8"):
+    setattr(ConfigPresets, _n, staticmethod(lambda _n=_n, **kw: ConfigPresets.get(_n, **kw)))
+
+
+# --------------------------------------------------------------------------- #
+# Manager
+# --------------------------------------------------------------------------- #
+class ConfigManager:
+    """Factory + hardware fitting + lint (reference ``config_manager.py:1871-2099``)."""
+
+    @staticmethod
+    def create_config(preset: str = "debug", overrides: Optional[Dict[str, Any]] = None,
+                      optimize_for_hardware: bool = False, target_memory_usage: float = 0.85) -> Config:
+        cfg = ConfigPresets.get(preset, **(overrides or {}))
+        if optimize_for_hardware:
+            cfg = ConfigManager.optimize_for_hardware(cfg, target_memory_usage)
+        return cfg
+
+    @staticmethod
+    def optimize_for_hardware(cfg: Config, target_memory_usage: float = 0.85,
+                              device_memory_gb: Optional[float] = None,
+                              world_size: Optional[int] = None) -> Config:
+        """Pick the ZeRO stage, micro-batch and EP degree that fit the device memory.
+        B200 default is 180 GB of HBM3e per GPU."""
+        cfg = cfg.copy()
+        if device_memory_gb is None:
+            device_memory_gb = 180.0
+            try:
+                import torch
+                if torch.cuda.is_available():
+                    device_memory_gb = torch.cuda.get_device_properties(0).total_memory / 1024 ** 3
+            except Exception:
+                pass
+        ws = world_size or cfg.world_size or max(Config._visible_devices(), 1)
+        budget = device_memory_gb * target_memory_usage
+        for stage in range(cfg.zero_stage, 4):
+            cfg.zero_stage = stage
+            if cfg.get_memory_estimate_gb(ws)["total"] <= budget or ws == 1:
+                break
+        while cfg.micro_batch_size > 1 and cfg.get_memory_estimate_gb(ws)["total"] > budget:
+            cfg.micro_batch_size //= 2
+            cfg.gradient_accumulation_steps *= 2
+        if cfg.use_moe:
+            cfg.expert_parallel_size = math.gcd(cfg.num_experts, ws)
+        cfg.gradient_compression = False
+        cfg.world_size = ws
+        return cfg
+
+    @staticmethod
+    def validate_config(cfg: Config) -> List[str]:
+        warnings: List[str] = []
+        if cfg.learning_rate > 1e-2:
+            warnings.append("learning_rate above 1e-2 usually diverges for transformers")
+        if cfg.use_moe and cfg.load_balancing_weight == 0:
+            warnings.append("MoE without a load-balancing loss tends to collapse onto few experts")
+        if cfg.use_moe and cfg.capacity_factor > 2.0:
+            warnings.append("capacity_factor above 2 wastes expert compute on padding")
+        if cfg.seq_length > 8192 and cfg.sequence_parallel_size == 1:
+            warnings.append("seq_length above 8192 without sequence parallelism may not fit")
+        if cfg.zero_stage == 3 and (cfg.world_size or 1) == 1:
+            warnings.append("zero_stage 3 on one device only adds gather traffic")
+        if cfg.precision in ("fp16", "mixed_fp16"):
+            warnings.append("fp16 needs dynamic loss scaling; bf16 is preferred on Blackwell")
+        if cfg.head_dim_check() not in (64, 128):
+            warnings.append("head_dim other than 64/128 falls back to the generic attention kernel")
+        est = cfg.get_memory_estimate_gb(cfg.world_size or 1)["total"]
+        if est > 180 * cfg.max_memory_usage:
+            warnings.append(f"estimated {est:.0f} GB per GPU exceeds the 180 GB HBM3e budget")
+        return warnings
+
+    @staticmethod
+    def save_config(cfg: Config, path: str) -> None:
+        cfg.save(path)
+
+    @staticmethod
+    def load_config(path: str) -> Config:
+        return Config.load(path)
+
+
+def _head_dim_check(self: Config) -> int:
+    return self.hidden_size // self.num_heads
+
+
+Config.head_dim_check = _head_dim_check  # small helper used by validate_config

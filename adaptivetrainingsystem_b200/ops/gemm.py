@@ -1,0 +1,241 @@
+"""bf16 GEMMs on the tcgen05 kernel (``csrc/gemm_tcgen05.cu``) and their PyTorch definitions.
+
+Naming: ``nt`` = A[M,K] · B[N,K]ᵀ, ``nn`` = A[M,K] · B[K,N], ``tn`` = A[K,M]ᵀ · B[K,N]; all row-major.
+These are the three products of a linear layer (forward, input gradient, weight gradient); none needs a
+transposed copy because the kernel reads either operand K-major or MN-major.
+
+Grouped forms work on the expert capacity layout ``[E, C, *]`` with a device-side ``counts[E]`` (rows of
+group ``e`` actually used; pad rows up to the next multiple of 128 must be zero).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+EPI_STORE, EPI_ADDC, EPI_F32, EPI_SWIGLU = 0, 1, 2, 3
+
+_c_int, _c_ll, _c_f, _vp = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+_configured = False
+
+
+def _fn():
+    global _configured
+    lib = _lib.cuda_lib()
+    if not _configured:
+        lib.ats_gemm_bf16.restype = _c_int
+        lib.ats_gemm_bf16.argtypes = [
+            _vp, _c_ll, _c_ll, _c_ll, _c_int,  # A
+            _vp, _c_ll, _c_ll, _c_ll, _c_int,  # B
+            _vp, _c_int, _vp, _c_int, _vp, _c_int,  # D, C, aux
+            _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int,  # M N K alpha beta epilogue up_offset
+            _c_int, _c_int, _vp,  # groups ragged counts
+            _c_int, _c_int, _c_int, _c_int,  # group coordinate shifts
+            _c_ll, _c_ll, _c_ll,  # d_gs c_gs aux_gs
+            _vp, _c_int, _vp]  # status, max_ctas, stream
+        _configured = True
+    return lib.ats_gemm_bf16
+
+
+def _raw(a, a_rows, a_cols, lda, a_mn, b, b_rows, b_cols, ldb, b_mn, d, ldd, c, ldc, aux, ldaux,
+         M, N, K, alpha=1.0, beta=0, epilogue=EPI_STORE, up_offset=0, groups=1, ragged=0, counts=None,
+         a_gs_mn=0, a_gs_k=0, b_gs_mn=0, b_gs_k=0, d_gs=0, c_gs=0, aux_gs=0, max_ctas=0):
+    st = _lib.status_tensor(a.device)
+    err = _fn()(_lib.ptr(a), a_rows, a_cols, lda, a_mn, _lib.ptr(b), b_rows, b_cols, ldb, b_mn,
+                _lib.ptr(d), ldd, _lib.ptr(c), ldc, _lib.ptr(aux), ldaux,
+                M, N, K, alpha, beta, epilogue, up_offset, groups, ragged, _lib.ptr(counts),
+                a_gs_mn, a_gs_k, b_gs_mn, b_gs_k, d_gs, c_gs, aux_gs,
+                _lib.ptr(st), max_ctas, _lib.stream_ptr(a.device))
+    _lib.check(err, "ats_gemm_bf16")
+
+
+def _check2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise ValueError("expected a 2-D tensor")
+    if t.stride(1) != 1 or (t.stride(0) % 8) or (t.data_ptr() % 16):
+        t = t.contiguous()
+    return t
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+            add: Optional[torch.Tensor] = None, alpha: float = 1.0, out_fp32: bool = False,
+            accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    """a[M,K] @ b[N,K]^T (+ add).  ``out_fp32`` writes (or accumulates into) an fp32 matrix."""
+    if not _lib.use_cuda_kernels(a):
+        r = (a.float() @ b.float().t()) * alpha
+        if add is not None:
+            r = r + add.float()
+        if out_fp32:
+            if out is not None:
+                out.copy_(out + r if accumulate else r)
+                return out
+            return r
+        r = r.to(a.dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    a, b = _check2d(a), _check2d(b)
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else a.dtype, device=a.device)
+    epi = EPI_F32 if out_fp32 else (EPI_ADDC if add is not None else EPI_STORE)
+    _raw(a, M, K, a.stride(0), 0, b, N, K, b.stride(0), 0, out, out.stride(0), add, add.stride(0) if add is not None else 0,
+         None, 0, M, N, K, alpha=alpha, beta=int(accumulate), epilogue=epi, max_ctas=max_ctas)
+    return out
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+            add: Optional[torch.Tensor] = None, alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+    """a[M,K] @ b[K,N] (+ add)."""
+    if not _lib.use_cuda_kernels(a):
+        r = (a.float() @ b.float()) * alpha
+        if add is not None:
+            r = r + add.float()
+        r = r.to(a.dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    a, b = _check2d(a), _check2d(b)
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    _raw(a, M, K, a.stride(0), 0, b, K, N, b.stride(0), 1, out, out.stride(0), add, add.stride(0) if add is not None else 0,
+         None, 0, M, N, K, alpha=alpha, epilogue=EPI_ADDC if add is not None else EPI_STORE, max_ctas=max_ctas)
+    return out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+            alpha: float = 1.0, out_fp32: bool = False, max_ctas: int = 0) -> torch.Tensor:
+    """a[K,M]^T @ b[K,N]; ``accumulate`` adds into ``out``."""
+    if not _lib.use_cuda_kernels(a):
+        r = (a.float().t() @ b.float()) * alpha
+        if out is not None:
+            if accumulate:
+                r = r + out.float()
+            out.copy_(r.to(out.dtype))
+            return out
+        return r if out_fp32 else r.to(a.dtype)
+    a, b = _check2d(a), _check2d(b)
+    K, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else a.dtype, device=a.device)
+        accumulate = False
+    fp32 = out.dtype == torch.float32
+    epi = EPI_F32 if fp32 else (EPI_ADDC if accumulate else EPI_STORE)
+    _raw(a, K, M, a.stride(0), 1, b, K, N, b.stride(0), 1, out, out.stride(0),
+         out if (accumulate and not fp32) else None, out.stride(0), None, 0, M, N, K, alpha=alpha,
+         beta=int(accumulate), epilogue=epi, max_ctas=max_ctas)
+    return out
+
+
+def gemm_nt_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None,
+                   pre_act: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
+    """h = silu(a @ Wg^T) * (a @ Wu^T) with ``w_gate_up = [Wg; Wu]`` of shape [2I, K].  ``pre_act`` ([M, 2I])
+    receives the gate/up pre-activations when the backward pass needs them."""
+    inter = w_gate_up.shape[0] // 2
+    if not _lib.use_cuda_kernels(a):
+        gu = (a.float() @ w_gate_up.float().t()).to(a.dtype)
+        if pre_act is not None:
+            pre_act.copy_(gu)
+        g, u = gu.float().chunk(2, dim=-1)
+        r = (torch.nn.functional.silu(g) * u).to(a.dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    a, w = _check2d(a), _check2d(w_gate_up)
+    M, K = a.shape
+    if out is None:
+        out = torch.empty(M, inter, dtype=a.dtype, device=a.device)
+    _raw(a, M, K, a.stride(0), 0, w, 2 * inter, K, w.stride(0), 0, out, out.stride(0), None, 0,
+         pre_act, pre_act.stride(0) if pre_act is not None else 0, M, inter, K, epilogue=EPI_SWIGLU,
+         up_offset=inter, max_ctas=max_ctas)
+    return out
+
+
+# ----------------------------------------------------------------------------------------------------------
+# grouped (expert) products on the capacity layout
+# ----------------------------------------------------------------------------------------------------------
+def _ref_mask(counts: torch.Tensor, cap: int) -> torch.Tensor:
+    return (torch.arange(cap, device=counts.device)[None, :] < counts[:, None].long())
+
+
+def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: bool = False,
+               pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[E,C,K] · w[E,N,K]^T -> [E,C,N] (or [E,C,N/2] through SwiGLU) for the first counts[e] rows of every
+    expert; rows beyond the padded count are left untouched."""
+    E, C, K = x.shape
+    N = w.shape[1]
+    if not _lib.use_cuda_kernels(x):
+        y = torch.einsum("eck,enk->ecn", x.float(), w.float()).to(x.dtype)
+        mask = _ref_mask(counts, C)[..., None]
+        y = torch.where(mask, y, torch.zeros_like(y))
+        if swiglu:
+            if pre_act is not None:
+                pre_act.copy_(y)
+            g, u = y.float().chunk(2, dim=-1)
+            y = (torch.nn.functional.silu(g) * u).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.is_contiguous() and w.is_contiguous() and C % 128 == 0
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(E, C, n_out, dtype=x.dtype, device=x.device)
+    _raw(x, E * C, K, K, 0, w, E * N, K, K, 0, out, n_out, None, 0, pre_act, N if pre_act is not None else 0,
+         C, n_out, K, epilogue=EPI_SWIGLU if swiglu else EPI_STORE, up_offset=N // 2 if swiglu else 0,
+         groups=E, ragged=1, counts=counts, a_gs_mn=C, b_gs_mn=N, d_gs=C * n_out,
+         aux_gs=C * N if pre_act is not None else 0)
+    return out
+
+
+def grouped_nn(dy: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dy[E,C,N] · w[E,N,K] -> [E,C,K] (input gradient of grouped_nt)."""
+    E, C, N = dy.shape
+    K = w.shape[2]
+    if not _lib.use_cuda_kernels(dy):
+        y = torch.einsum("ecn,enk->eck", dy.float(), w.float()).to(dy.dtype)
+        y = torch.where(_ref_mask(counts, C)[..., None], y, torch.zeros_like(y))
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert dy.is_contiguous() and w.is_contiguous() and C % 128 == 0
+    if out is None:
+        out = torch.empty(E, C, K, dtype=dy.dtype, device=dy.device)
+    _raw(dy, E * C, N, N, 0, w, E * N, K, K, 1, out, K, None, 0, None, 0, C, K, N,
+         groups=E, ragged=1, counts=counts, a_gs_mn=C, b_gs_k=N, d_gs=C * K)
+    return out
+
+
+def grouped_tn(dy: torch.Tensor, x: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None,
+               accumulate: bool = False) -> torch.Tensor:
+    """dy[E,C,N]^T · x[E,C,K] -> [E,N,K] (weight gradient of grouped_nt), reducing over the used rows."""
+    E, C, N = dy.shape
+    K = x.shape[2]
+    if not _lib.use_cuda_kernels(dy):
+        mask = _ref_mask(counts, C)[..., None].float()
+        r = torch.einsum("ecn,eck->enk", dy.float() * mask, x.float() * mask)
+        if out is not None:
+            if accumulate:
+                r = r + out.float()
+            out.copy_(r.to(out.dtype))
+            return out
+        return r.to(dy.dtype)
+    assert dy.is_contiguous() and x.is_contiguous() and C % 128 == 0
+    if out is None:
+        out = torch.empty(E, N, K, dtype=dy.dtype, device=dy.device)
+        accumulate = False
+    _raw(dy, E * C, N, N, 1, x, E * C, K, K, 1, out, K, out if accumulate else None, K, None, 0, N, K, C,
+         epilogue=EPI_ADDC if accumulate else EPI_STORE, groups=E, ragged=2, counts=counts,
+         a_gs_k=C, b_gs_k=C, d_gs=N * K, c_gs=N * K)
+    return out

@@ -1,0 +1,280 @@
+"""Mixture-of-Experts operators: gate projection, routing, and the dispatch -> grouped SwiGLU FFN -> combine
+block as one autograd function.
+
+Routing semantics (documented behaviour of the reference, ``core/model.py:1169-1263``): gate logits (+ optional
+Gaussian noise while training) / temperature -> softmax over ALL experts -> top-k -> the kept probabilities are
+renormalised to sum to one.  Auxiliary loss ``E * sum_e f_e * P_e * weight`` with ``f_e`` the fraction of
+(token, k) slots routed to expert ``e`` and ``P_e`` the mean softmax probability of the clean logits.
+
+Capacity: every expert accepts at most ``C = ceil(capacity_factor * k * T / E)`` slots (rounded up to a
+multiple of 128 rows so GEMM tiles are whole); slots are ranked in token order, later ones are dropped.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from . import gemm as G
+from .functional import _L, _P, _S, _CK, _deliver_grad
+
+
+def expert_capacity(tokens: int, num_experts: int, top_k: int, capacity_factor: float, drop_tokens: bool = True,
+                    multiple: int = 128) -> int:
+    if drop_tokens:
+        c = int(math.ceil(capacity_factor * top_k * tokens / num_experts))
+    else:
+        c = tokens  # dropless: an expert can receive every token once
+    c = max(c, 1)
+    return ((c + multiple - 1) // multiple) * multiple
+
+
+# ----------------------------------------------------------------------------------------------------------
+# gate projection
+# ----------------------------------------------------------------------------------------------------------
+class _GateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, wg):
+        T, H = x.shape
+        E = wg.shape[0]
+        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+        _CK(_L().ats_gate_fwd(_P(x), _P(wg), _P(logits), T, H, E, _S(x.device)), "gate_fwd")
+        ctx.save_for_backward(x, wg)
+        return logits
+
+    @staticmethod
+    def backward(ctx, dlogits):
+        x, wg = ctx.saved_tensors
+        T, H = x.shape
+        E = wg.shape[0]
+        dl = dlogits.contiguous().float()
+        dx = torch.empty_like(x)
+        _CK(_L().ats_gate_bwd_dx(_P(dl), _P(wg), _P(dx), T, H, E, 0, _S(x.device)), "gate_bwd_dx")
+        nb = max(1, min(296, T // 16))
+        partial = torch.empty(nb, E * H, dtype=torch.float32, device=x.device)
+        _CK(_L().ats_gate_bwd_dw(_P(dl), _P(x), _P(partial), nb, T, H, E, _S(x.device)), "gate_bwd_dw")
+
+        def compute(out, acc):
+            if out is None:
+                out = torch.empty_like(wg)
+            _CK(_L().ats_colsum_partial(_P(partial), nb, E * H, _P(out), None, 1 if acc else 0, _S(x.device)), "gate_dw_reduce")
+            return out
+        return dx, _deliver_grad(wg, compute)
+
+
+def gate_logits(x: torch.Tensor, wg: torch.Tensor) -> torch.Tensor:
+    """fp32 router logits x[T,H] @ wg[E,H]^T."""
+    if _lib.use_cuda_kernels(x) and wg.shape[0] <= 64 and x.shape[1] % 8 == 0:
+        return _GateFn.apply(x.contiguous(), wg)
+    return F.linear(x.float(), wg.float())
+
+
+def route(logits: torch.Tensor, top_k: int, temperature: float = 1.0, noise_std: float = 0.0,
+          training: bool = False, generator: Optional[torch.Generator] = None):
+    """-> (topk_idx int32 [T,k], topk_w fp32 [T,k], clean_probs fp32 [T,E])."""
+    clean_probs = torch.softmax(logits, dim=-1)
+    z = logits
+    if training and noise_std > 0:
+        z = z + torch.randn(z.shape, device=z.device, dtype=z.dtype, generator=generator) * noise_std
+    if not torch.is_grad_enabled() and logits.is_cuda and not (training and noise_std > 0) and logits.shape[1] <= 64 and top_k <= 8:
+        T, E = logits.shape
+        probs = torch.empty_like(logits)
+        idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        _CK(_L().ats_topk_softmax(_P(logits.contiguous()), _P(probs), _P(idx), _P(w), T, E, top_k, float(temperature),
+                                  _S(logits.device)), "topk_softmax")
+        return idx, w, clean_probs
+    probs = torch.softmax(z / temperature, dim=-1)
+    w, idx = torch.topk(probs, top_k, dim=-1)
+    w = w / w.sum(-1, keepdim=True).clamp(min=1e-20)
+    return idx.to(torch.int32), w, clean_probs
+
+
+def load_balancing_loss(clean_probs: torch.Tensor, topk_idx: torch.Tensor, num_experts: int, weight: float,
+                        token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """E * sum_e f_e * P_e * weight, clamped to <= 1 (reference ``core/model.py:1244-1263``)."""
+    flat = topk_idx.reshape(-1).long()
+    counts = torch.bincount(flat, minlength=num_experts).float()
+    f = counts / max(flat.numel(), 1)
+    p = clean_probs.mean(0)
+    return (num_experts * (f * p).sum() * weight).clamp(max=1.0)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# slot planning (deterministic) -- shared by the CUDA and the PyTorch bodies
+# ----------------------------------------------------------------------------------------------------------
+def plan_slots(topk_idx: torch.Tensor, num_experts: int, capacity: int):
+    """-> slot_pos int32 [T*k] (row inside the expert region or -1), counts int32 [E] (clamped), totals int32 [E]."""
+    flat = topk_idx.reshape(-1).contiguous()
+    if flat.is_cuda and num_experts <= 64:
+        slot_pos = torch.empty(flat.numel(), dtype=torch.int32, device=flat.device)
+        counts = torch.empty(num_experts, dtype=torch.int32, device=flat.device)
+        totals = torch.empty(num_experts, dtype=torch.int32, device=flat.device)
+        _CK(_L().ats_plan_slots(_P(flat), _P(slot_pos), _P(counts), _P(totals), flat.numel(), num_experts, capacity,
+                                _S(flat.device)), "plan_slots")
+        return slot_pos, counts, totals
+    oh = F.one_hot(flat.long(), num_experts)
+    rank = (oh.cumsum(0) - oh).gather(1, flat.long()[:, None]).squeeze(1)
+    totals = oh.sum(0).to(torch.int32)
+    slot_pos = torch.where(rank < capacity, rank, torch.full_like(rank, -1)).to(torch.int32)
+    return slot_pos, totals.clamp(max=capacity), totals
+
+
+def _ptr_table(t: torch.Tensor) -> torch.Tensor:
+    """int64 device table with the base address of every expert region of t[E, C, H]."""
+    E = t.shape[0]
+    step = t.stride(0) * t.element_size()
+    return torch.arange(E, dtype=torch.int64, device=t.device) * step + t.data_ptr()
+
+
+def dispatch(x: torch.Tensor, topk_idx: torch.Tensor, slot_pos: torch.Tensor, counts: torch.Tensor,
+             num_experts: int, capacity: int, slot_scale: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[T,H] -> buf[E, C, H] with row ``slot_pos`` of expert ``topk_idx`` holding (scaled) x[t]."""
+    T, H = x.shape
+    k = topk_idx.shape[1]
+    if out is None:
+        out = torch.empty(num_experts, capacity, H, dtype=x.dtype, device=x.device)
+    if _lib.use_cuda_kernels(x):
+        if table is None:
+            table = _ptr_table(out)
+        _CK(_L().ats_dispatch_rows(_P(x), _P(topk_idx), _P(slot_pos), _P(slot_scale), _P(table), _P(counts), T * k, k, H,
+                                   num_experts, capacity, 1, _S(x.device)), "dispatch_rows")
+        return out
+    out.zero_()
+    flat_e = topk_idx.reshape(-1).long()
+    pos = slot_pos.long()
+    keep = pos >= 0
+    tok = torch.arange(T * k, device=x.device) // k
+    rows = x[tok[keep]]
+    if slot_scale is not None:
+        rows = (rows.float() * slot_scale.reshape(-1)[keep][:, None]).to(x.dtype)
+    out[flat_e[keep], pos[keep]] = rows
+    return out
+
+
+def combine(buf: torch.Tensor, topk_idx: torch.Tensor, slot_pos: torch.Tensor, topk_w: Optional[torch.Tensor],
+            tokens: int, residual: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = residual[t] + sum_j w[t,j] * buf[e_j, pos_j] over kept slots."""
+    E, C, H = buf.shape
+    k = topk_idx.shape[1]
+    if _lib.use_cuda_kernels(buf):
+        out = torch.empty(tokens, H, dtype=buf.dtype, device=buf.device)
+        if table is None:
+            table = _ptr_table(buf)
+        w = topk_w.contiguous().float() if topk_w is not None else None
+        _CK(_L().ats_combine_rows(_P(table), _P(topk_idx), _P(slot_pos), _P(w), _P(residual), _P(out), tokens, k, H,
+                                  _S(buf.device)), "combine_rows")
+        return out
+    flat_e = topk_idx.reshape(-1).long()
+    pos = slot_pos.long()
+    keep = pos >= 0
+    rows = torch.zeros(tokens * k, H, dtype=torch.float32, device=buf.device)
+    rows[keep] = buf[flat_e[keep], pos[keep]].float()
+    if topk_w is not None:
+        rows = rows * topk_w.reshape(-1, 1).float()
+    out = rows.view(tokens, k, H).sum(1)
+    if residual is not None:
+        out = out + residual.float()
+    return out.to(buf.dtype)
+
+
+def slot_dot(buf: torch.Tensor, topk_idx: torch.Tensor, slot_pos: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
+    """<dout[t], buf[e_j, pos_j]> for every slot -> [T, k] fp32 (gradient of the combine weights)."""
+    T, H = dout.shape
+    k = topk_idx.shape[1]
+    if _lib.use_cuda_kernels(buf):
+        dw = torch.empty(T, k, dtype=torch.float32, device=buf.device)
+        _CK(_L().ats_slot_dot(_P(_ptr_table(buf)), _P(topk_idx), _P(slot_pos), _P(dout.contiguous()), _P(dw), T * k, k, H,
+                              _S(buf.device)), "slot_dot")
+        return dw
+    flat_e = topk_idx.reshape(-1).long()
+    pos = slot_pos.long()
+    keep = pos >= 0
+    rows = torch.zeros(T * k, H, dtype=torch.float32, device=buf.device)
+    rows[keep] = buf[flat_e[keep], pos[keep]].float()
+    return (rows.view(T, k, H) * dout.float()[:, None, :]).sum(-1)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# dispatch -> experts -> combine
+# ----------------------------------------------------------------------------------------------------------
+class _MoEFFNFn(torch.autograd.Function):
+    """y[t] = residual[t] + sum_j w[t,j] * FFN_{e_j}(x[t]) under a capacity limit.
+
+    ``w1``: [E, 2I, H] (gate rows then up rows), ``w2``: [E, H, I].  Saved for backward: the dispatched inputs,
+    the SwiGLU pre-activations and the expert outputs (needed for the combine-weight gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, topk_idx, topk_w, w1, w2, capacity, residual):
+        T, H = x.shape
+        E = w1.shape[0]
+        slot_pos, counts, totals = plan_slots(topk_idx, E, capacity)
+        xe = dispatch(x, topk_idx, slot_pos, counts, E, capacity)
+        need_bwd = any(ctx.needs_input_grad)
+        pre = torch.empty(E, capacity, w1.shape[1], dtype=x.dtype, device=x.device) if need_bwd else None
+        h = G.grouped_nt(xe, w1, counts, swiglu=True, pre_act=pre)
+        ye = G.grouped_nt(h, w2, counts)
+        out = combine(ye, topk_idx, slot_pos, topk_w, T, residual)
+        ctx.save_for_backward(topk_idx, slot_pos, counts, topk_w, w1, w2, xe, pre, ye)
+        ctx.capacity = capacity
+        ctx.has_res = residual is not None
+        ctx.mark_non_differentiable(totals)
+        return out, totals
+
+    @staticmethod
+    def backward(ctx, dout, _dtotals=None):
+        topk_idx, slot_pos, counts, topk_w, w1, w2, xe, pre, ye = ctx.saved_tensors
+        E, C, H = xe.shape
+        inter = w2.shape[2]
+        T = dout.shape[0]
+        dout = dout.contiguous()
+        dw_topk = slot_dot(ye, topk_idx, slot_pos, dout) if ctx.needs_input_grad[2] else None
+        dye = dispatch(dout, topk_idx, slot_pos, counts, E, C, slot_scale=topk_w.contiguous().float())
+        dh = G.grouped_nn(dye, w2, counts)
+        if _lib.use_cuda_kernels(pre):
+            dgu = torch.empty_like(pre)
+            h = torch.empty(E, C, inter, dtype=pre.dtype, device=pre.device)
+            _CK(_L().ats_swiglu_bwd(_P(pre), _P(dh), _P(dgu), _P(h), E * C, inter, _S(pre.device)), "swiglu_bwd")
+        else:
+            g, u = pre.float().chunk(2, dim=-1)
+            s = torch.sigmoid(g)
+            dhf = dh.float()
+            dgu = torch.cat([dhf * u * (s + g * s * (1 - s)), dhf * g * s], dim=-1).to(pre.dtype)
+            h = (g * s * u).to(pre.dtype)
+        dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(dye, h, counts, out=out, accumulate=acc))
+        dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, xe, counts, out=out, accumulate=acc))
+        dxe = G.grouped_nn(dgu, w1, counts)
+        dx = combine(dxe, topk_idx, slot_pos, None, T, None)
+        return dx, None, dw_topk, dw1, dw2, None, (dout if ctx.has_res else None)
+
+
+def moe_ffn(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+            capacity: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """-> (output [T,H], demand per expert int32 [E])."""
+    return _MoEFFNFn.apply(x, topk_idx, topk_w, w1, w2, capacity, None)
+
+
+def moe_ffn_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w1: torch.Tensor,
+                      w2: torch.Tensor, capacity: int) -> torch.Tensor:
+    """Per-expert loop in fp32 with the same capacity rule; the oracle for tests."""
+    T, H = x.shape
+    E = w1.shape[0]
+    k = topk_idx.shape[1]
+    slot_pos, _, _ = plan_slots(topk_idx, E, capacity)
+    keep = (slot_pos >= 0).view(T, k)
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for e in range(E):
+        sel = (topk_idx.long() == e) & keep
+        tok, kk = sel.nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok].float()
+        gu = xe @ w1[e].float().t()
+        g, u = gu.chunk(2, dim=-1)
+        ye = (F.silu(g) * u) @ w2[e].float().t()
+        out.index_add_(0, tok, ye * topk_w[tok, kk].float()[:, None])
+    return out.to(x.dtype)

@@ -1,0 +1,435 @@
+// Memory-bound kernels: RMSNorm / LayerNorm (fwd, bwd), half-split RoPE, SwiGLU (fwd, bwd), embedding
+// (gather * scale, sorted-segment gradient), casts.  bf16 in/out, fp32 math, 16-byte vector accesses.
+//
+// Counterparts in the reference: core/transformer_ops.cu:61-315 (fp32 CUDA-core RMSNorm / RoPE / SwiGLU) and
+// the eager PyTorch paths in core/model.py:228-304, 470-524, 1082-1088, 1924-1931.
+#include "common.cuh"
+
+namespace ats {
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm forward:  y = (x [+ res]) * rsqrt(mean((x+res)^2) + eps) * w ; optionally writes x+res.
+// One CTA per row; cols % 8 == 0.
+// ------------------------------------------------------------------------------------------------
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd, int cols, float eps) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + row * cols) : nullptr;
+  const int nvec = cols >> 3;
+  constexpr int MAXV = 4;  // up to 4 vectors per thread are cached in registers (cols <= THREADS*32)
+  float cache[MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      uint4 a = xr[v];
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      float f[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+      if (rr) {
+        uint4 b = rr[v];
+        float2 g0 = unpack_bf16x2(b.x), g1 = unpack_bf16x2(b.y), g2 = unpack_bf16x2(b.z), g3 = unpack_bf16x2(b.w);
+        f[0] += g0.x; f[1] += g0.y; f[2] += g1.x; f[3] += g1.y; f[4] += g2.x; f[5] += g2.y; f[6] += g3.x; f[7] += g3.y;
+        if (sum_out) {
+          uint4 o = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          reinterpret_cast<uint4*>(sum_out + row * cols)[v] = o;
+          // keep the bf16-rounded residual stream so forward and recompute agree
+          float2 q0 = unpack_bf16x2(o.x), q1 = unpack_bf16x2(o.y), q2 = unpack_bf16x2(o.z), q3 = unpack_bf16x2(o.w);
+          f[0] = q0.x; f[1] = q0.y; f[2] = q1.x; f[3] = q1.y; f[4] = q2.x; f[5] = q2.y; f[6] = q3.x; f[7] = q3.y;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        cache[i][e] = f[e];
+        ss += f[e] * f[e];
+      }
+    }
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / cols + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * cols);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      uint4 a = wr[v];
+      float2 w0 = unpack_bf16x2(a.x), w1 = unpack_bf16x2(a.y), w2 = unpack_bf16x2(a.z), w3 = unpack_bf16x2(a.w);
+      const float* f = cache[i];
+      yr[v] = make_uint4(pack_bf16x2(f[0] * r * w0.x, f[1] * r * w0.y), pack_bf16x2(f[2] * r * w1.x, f[3] * r * w1.y),
+                         pack_bf16x2(f[4] * r * w2.x, f[5] * r * w2.y), pack_bf16x2(f[6] * r * w3.x, f[7] * r * w3.y));
+    }
+  }
+}
+
+// RMSNorm backward. Each CTA walks rows blockIdx.x, +gridDim.x, ...; dx per row, dw partial per CTA (fp32),
+// reduced by rmsnorm_dw_reduce_kernel.  dx = rstd * (dy*w - xhat * mean(dy*w*xhat)), xhat = x * rstd.
+// If dres_in is given it is added to dx (gradient arriving through the residual branch).
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int cols) {
+  __shared__ float red[33];
+  constexpr int MAXV = 4;
+  const int nvec = cols >> 3;
+  float dwacc[MAXV][8];
+  float wreg[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+    if (v < nvec) {
+      uint4 a = reinterpret_cast<const uint4*>(w)[v];
+      float2 w0 = unpack_bf16x2(a.x), w1 = unpack_bf16x2(a.y), w2 = unpack_bf16x2(a.z), w3 = unpack_bf16x2(a.w);
+      wreg[i][0] = w0.x; wreg[i][1] = w0.y; wreg[i][2] = w1.x; wreg[i][3] = w1.y;
+      wreg[i][4] = w2.x; wreg[i][5] = w2.y; wreg[i][6] = w3.x; wreg[i][7] = w3.y;
+    }
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float r = rstd[row];
+    float xh[MAXV][8], g[MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) {
+        uint4 a = reinterpret_cast<const uint4*>(x + row * cols)[v];
+        uint4 b = reinterpret_cast<const uint4*>(dy + row * cols)[v];
+        float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+        float2 d0 = unpack_bf16x2(b.x), d1 = unpack_bf16x2(b.y), d2 = unpack_bf16x2(b.z), d3 = unpack_bf16x2(b.w);
+        float xv[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+        float dv[8] = {d0.x, d0.y, d1.x, d1.y, d2.x, d2.y, d3.x, d3.y};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[i][e] = xv[e] * r;
+          g[i][e] = dv[e] * wreg[i][e];
+          dot += g[i][e] * xh[i][e];
+          dwacc[i][e] += dv[e] * xh[i][e];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / cols;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = r * (g[i][e] - xh[i][e] * dot);
+        if (dres_in) {
+          uint4 c = reinterpret_cast<const uint4*>(dres_in + row * cols)[v];
+          float2 c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y), c2 = unpack_bf16x2(c.z), c3 = unpack_bf16x2(c.w);
+          o[0] += c0.x; o[1] += c0.y; o[2] += c1.x; o[3] += c1.y; o[4] += c2.x; o[5] += c2.y; o[6] += c3.x; o[7] += c3.y;
+        }
+        reinterpret_cast<uint4*>(dx + row * cols)[v] =
+            make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+      }
+    }
+  }
+  float* out = dw_partial + (long long)blockIdx.x * cols;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      reinterpret_cast<float4*>(out)[2 * v] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      reinterpret_cast<float4*>(out)[2 * v + 1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+}
+
+// dw[c] (+)= sum_b partial[b][c]; output bf16 or fp32.
+__global__ void colsum_partial_kernel(const float* __restrict__ partial, int nblocks, int cols,
+                                      __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * cols + c];
+  if (out_f32) out_f32[c] = accumulate ? out_f32[c] + s : s;
+  if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + s : s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// RoPE, half-split layout, in place on a packed projection buffer [tokens, row_stride] whose first
+// (n_heads * d) columns starting at col_offset are heads of width d.  cos/sin: [max_pos, d/2] fp32.
+// position of token t = pos[t] if pos != nullptr else pos_offset + (t % seq_len).  sign = -1 -> inverse (backward).
+// ------------------------------------------------------------------------------------------------
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, const int* __restrict__ pos, int tokens, int seq_len,
+                            int pos_offset, int row_stride, int col_offset, int n_heads, int d, float sign) {
+  const int half = d >> 1;
+  const int vec_per_head = half >> 3;  // 8 pairs per 16-byte vector
+  const long long total = (long long)tokens * n_heads * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = int(i % vec_per_head);
+    const int h = int((i / vec_per_head) % n_heads);
+    const long long t = i / ((long long)vec_per_head * n_heads);
+    const int p = pos ? pos[t] : pos_offset + int(t % seq_len);
+    __nv_bfloat16* base = buf + t * row_stride + col_offset + h * d + v * 8;
+    uint4 a = *reinterpret_cast<uint4*>(base);
+    uint4 b = *reinterpret_cast<uint4*>(base + half);
+    const float4* c4 = reinterpret_cast<const float4*>(cos_t + (long long)p * half + v * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_t + (long long)p * half + v * 8);
+    float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    float c[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+    float s[8] = {sa.x * sign, sa.y * sign, sa.z * sign, sa.w * sign, sb.x * sign, sb.y * sign, sb.z * sign, sb.w * sign};
+    uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 x1 = unpack_bf16x2(au[e]), x2 = unpack_bf16x2(bu[e]);
+      o1[e] = pack_bf16x2(x1.x * c[2 * e] - x2.x * s[2 * e], x1.y * c[2 * e + 1] - x2.y * s[2 * e + 1]);
+      o2[e] = pack_bf16x2(x1.x * s[2 * e] + x2.x * c[2 * e], x1.y * s[2 * e + 1] + x2.y * c[2 * e + 1]);
+    }
+    *reinterpret_cast<uint4*>(base) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4*>(base + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU on a fused projection gu[rows, 2I] (gate = first I columns): h = silu(g) * u.
+// Backward: given dh, writes dgu in the same [rows, 2I] layout and (optionally) recomputes h.
+// ------------------------------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h, long long rows,
+                                  int inter) {
+  const int vpr = inter >> 3;
+  const long long total = rows * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vpr;
+    const int v = int(i - r * vpr);
+    const __nv_bfloat16* row = gu + r * 2 * inter;
+    uint4 g = reinterpret_cast<const uint4*>(row)[v];
+    uint4 u = reinterpret_cast<const uint4*>(row + inter)[v];
+    uint32_t gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w}, o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]);
+      o[e] = pack_bf16x2(silu_f(a.x) * b.x, silu_f(a.y) * b.y);
+    }
+    reinterpret_cast<uint4*>(h + r * inter)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh,
+                                  __nv_bfloat16* __restrict__ dgu, __nv_bfloat16* __restrict__ h_out, long long rows,
+                                  int inter) {
+  const int vpr = inter >> 3;
+  const long long total = rows * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vpr;
+    const int v = int(i - r * vpr);
+    const __nv_bfloat16* row = gu + r * 2 * inter;
+    uint4 g = reinterpret_cast<const uint4*>(row)[v];
+    uint4 u = reinterpret_cast<const uint4*>(row + inter)[v];
+    uint4 d = reinterpret_cast<const uint4*>(dh + r * inter)[v];
+    uint32_t gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w}, dd[4] = {d.x, d.y, d.z, d.w};
+    uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]), c = unpack_bf16x2(dd[e]);
+      float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
+      float si0 = a.x * s0, si1 = a.y * s1;
+      // d silu(x)/dx = s + x*s*(1-s)
+      og[e] = pack_bf16x2(c.x * b.x * (s0 + si0 * (1.f - s0)), c.y * b.y * (s1 + si1 * (1.f - s1)));
+      ou[e] = pack_bf16x2(c.x * si0, c.y * si1);
+      oh[e] = pack_bf16x2(si0 * b.x, si1 * b.y);
+    }
+    __nv_bfloat16* orow = dgu + r * 2 * inter;
+    reinterpret_cast<uint4*>(orow)[v] = make_uint4(og[0], og[1], og[2], og[3]);
+    reinterpret_cast<uint4*>(orow + inter)[v] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+    if (h_out) reinterpret_cast<uint4*>(h_out + r * inter)[v] = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Embedding: out[t] = table[clamp(ids[t])] * scale.  Gradient: ids sorted on the host side of the op
+// (sorted_ids, order); one warp per run of equal ids sums its rows in fp32 -> deterministic, no atomics.
+// ------------------------------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                     __nv_bfloat16* __restrict__ out, long long tokens, int hidden, int vocab, float scale) {
+  const int vpr = hidden >> 3;
+  const long long total = tokens * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vpr;
+    const int v = int(i - t * vpr);
+    long long id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    uint4 a = reinterpret_cast<const uint4*>(table + id * hidden)[v];
+    if (scale != 1.f) {
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      a = make_uint4(pack_bf16x2(f0.x * scale, f0.y * scale), pack_bf16x2(f1.x * scale, f1.y * scale),
+                     pack_bf16x2(f2.x * scale, f2.y * scale), pack_bf16x2(f3.x * scale, f3.y * scale));
+    }
+    reinterpret_cast<uint4*>(out + t * hidden)[v] = a;
+  }
+}
+
+__global__ void embedding_bwd_kernel(const long long* __restrict__ sorted_ids, const long long* __restrict__ order,
+                                     const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dtable,
+                                     long long tokens, int hidden, int vocab, float scale, int accumulate) {
+  const long long warp_global = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= tokens) return;
+  long long id = sorted_ids[warp_global];
+  if (warp_global > 0 && sorted_ids[warp_global - 1] == id) return;  // not the start of a run
+  long long cid = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const int vpr = hidden >> 3;
+  for (int v = lane; v < vpr; v += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long j = warp_global; j < tokens && sorted_ids[j] == id; ++j) {
+      uint4 a = reinterpret_cast<const uint4*>(dout + order[j] * hidden)[v];
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(dtable + cid * hidden) + v;
+    if (accumulate) {
+      uint4 o = *dst;
+      float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
+      *dst = make_uint4(pack_bf16x2(f0.x + acc[0] * scale, f0.y + acc[1] * scale), pack_bf16x2(f1.x + acc[2] * scale, f1.y + acc[3] * scale),
+                        pack_bf16x2(f2.x + acc[4] * scale, f2.y + acc[5] * scale), pack_bf16x2(f3.x + acc[6] * scale, f3.y + acc[7] * scale));
+    } else {
+      *dst = make_uint4(pack_bf16x2(acc[0] * scale, acc[1] * scale), pack_bf16x2(acc[2] * scale, acc[3] * scale),
+                        pack_bf16x2(acc[4] * scale, acc[5] * scale), pack_bf16x2(acc[6] * scale, acc[7] * scale));
+    }
+  }
+}
+
+// fp32 -> bf16 cast (optionally accumulating into the destination)
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n,
+                                     int accumulate, float scale) {
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    if (i + 3 < n) {
+      float4 a = *reinterpret_cast<const float4*>(in + i);
+      float o[4] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale};
+      if (accumulate) {
+        uint2 p = *reinterpret_cast<uint2*>(out + i);
+        float2 p0 = unpack_bf16x2(p.x), p1 = unpack_bf16x2(p.y);
+        o[0] += p0.x; o[1] += p0.y; o[2] += p1.x; o[3] += p1.y;
+      }
+      *reinterpret_cast<uint2*>(out + i) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+    } else {
+      for (long long j = i; j < n; ++j) {
+        float o = in[j] * scale + (accumulate ? __bfloat162float(out[j]) : 0.f);
+        out[j] = __float2bfloat16(o);
+      }
+    }
+  }
+}
+
+static inline int grid_for(long long work_items, int threads, int cap = 148 * 16) {
+  long long b = (work_items + threads - 1) / threads;
+  if (b < 1) b = 1;
+  return int(b < cap ? b : cap);
+}
+
+}  // namespace ats
+
+using namespace ats;
+
+ATS_API int ats_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd,
+                            long long rows, int cols, float eps, void* stream) {
+  if (cols & 7) return 1003;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto R = static_cast<const __nv_bfloat16*>(res);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto Y = static_cast<__nv_bfloat16*>(y);
+  auto S = static_cast<__nv_bfloat16*>(sum_out);
+  if (rows == 0) return 0;
+  if (cols <= 128 * 32) rmsnorm_fwd_kernel<128><<<(unsigned)rows, 128, 0, s>>>(X, R, W, Y, S, rstd, cols, eps);
+  else if (cols <= 256 * 32) rmsnorm_fwd_kernel<256><<<(unsigned)rows, 256, 0, s>>>(X, R, W, Y, S, rstd, cols, eps);
+  else if (cols <= 512 * 32) rmsnorm_fwd_kernel<512><<<(unsigned)rows, 512, 0, s>>>(X, R, W, Y, S, rstd, cols, eps);
+  else return 1003;
+  return int(cudaGetLastError());
+}
+
+// dw_partial: fp32 scratch of nblocks*cols; dw written as bf16 (dw_bf16) and/or fp32 (dw_f32).
+ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres_in, void* dx,
+                            float* dw_partial, int nblocks, void* dw_bf16, float* dw_f32, int accumulate, long long rows,
+                            int cols, void* stream) {
+  if (cols & 7) return 1003;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto DR = static_cast<const __nv_bfloat16*>(dres_in);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+  if (cols <= 128 * 32) rmsnorm_bwd_kernel<128><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+  else if (cols <= 256 * 32) rmsnorm_bwd_kernel<256><<<nblocks, 256, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+  else if (cols <= 512 * 32) rmsnorm_bwd_kernel<512><<<nblocks, 512, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+  else return 1003;
+  colsum_partial_kernel<<<(cols + 255) / 256, 256, 0, s>>>(dw_partial, nblocks, cols, static_cast<__nv_bfloat16*>(dw_bf16),
+                                                          dw_f32, accumulate);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_colsum_partial(const float* partial, int nblocks, int cols, void* out_bf16, float* out_f32, int accumulate,
+                               void* stream) {
+  colsum_partial_kernel<<<(cols + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      partial, nblocks, cols, static_cast<__nv_bfloat16*>(out_bf16), out_f32, accumulate);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_rope(void* buf, const float* cos_t, const float* sin_t, const int* pos, long long tokens, int seq_len,
+                     int pos_offset, int row_stride, int col_offset, int n_heads, int d, int inverse, void* stream) {
+  if ((d & 15) || (row_stride & 7) || (col_offset & 7)) return 1003;
+  const long long work = tokens * n_heads * (d >> 4);
+  if (work == 0) return 0;
+  rope_kernel<<<grid_for(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(buf), cos_t, sin_t, pos, (int)tokens, seq_len, pos_offset, row_stride, col_offset, n_heads, d,
+      inverse ? -1.f : 1.f);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_swiglu_fwd(const void* gu, void* h, long long rows, int inter, void* stream) {
+  if (inter & 7) return 1003;
+  if (rows == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(rows * (inter >> 3), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), rows, inter);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_swiglu_bwd(const void* gu, const void* dh, void* dgu, void* h_out, long long rows, int inter, void* stream) {
+  if (inter & 7) return 1003;
+  if (rows == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(rows * (inter >> 3), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh), static_cast<__nv_bfloat16*>(dgu),
+      static_cast<__nv_bfloat16*>(h_out), rows, inter);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int hidden, int vocab,
+                              float scale, void* stream) {
+  if (hidden & 7) return 1003;
+  if (tokens == 0) return 0;
+  embedding_fwd_kernel<<<grid_for(tokens * (hidden >> 3), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), tokens, hidden, vocab, scale);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_embedding_bwd(const long long* sorted_ids, const long long* order, const void* dout, void* dtable,
+                              long long tokens, int hidden, int vocab, float scale, int accumulate, void* stream) {
+  if (hidden & 7) return 1003;
+  if (tokens == 0) return 0;
+  const int threads = 256;
+  const long long blocks = (tokens * 32 + threads - 1) / threads;
+  embedding_bwd_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      sorted_ids, order, static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dtable), tokens, hidden, vocab,
+      scale, accumulate);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_cast_f32_bf16(const float* in, void* out, long long n, int accumulate, float scale, void* stream) {
+  if (n == 0) return 0;
+  cast_f32_bf16_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      in, static_cast<__nv_bfloat16*>(out), n, accumulate, scale);
+  return int(cudaGetLastError());
+}

@@ -1,0 +1,449 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory (128-byte swizzle) ->
+// tcgen05.mma with fp32 accumulators in TMEM -> epilogue from TMEM.
+//
+//   D[g] (M x N) = alpha * A[g] (M x K) * B[g]^T (N x K)      for every group g
+//
+// * Either operand may be K-major (reduction index contiguous in global memory) or MN-major (output index
+//   contiguous).  Forward linear is K/K, dgrad is K/MN, wgrad is MN/MN, so no transposed copy of an
+//   activation or weight is ever materialised.
+// * Grouped mode walks `groups` problems that share one pair of tensor maps; per-group coordinate shifts
+//   select the expert.  `ragged == 1`: the row count of group g is counts[g] rounded up to 128 (capacity
+//   layout [E, C, *], pad rows are zero).  `ragged == 2`: the reduction length is counts[g] rounded up to 128
+//   (expert weight gradients).
+// * Epilogues: store bf16 | add bf16 C | fp32 store/accumulate | SwiGLU (gate and up halves of the accumulator
+//   are combined, optionally also writing the pre-activations for backward).
+//
+// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue
+// (one TMEM lane quadrant each).  Two 256-column accumulators ping-pong so the epilogue of tile i overlaps
+// the main loop of tile i+1.  No load in this file uses cluster multicast.
+//
+// Replaces the cuBLAS calls behind every nn.Linear of the reference (reference core/model.py:686-718,
+// 1082-1088, 1229-1240, 1957-1973).
+#include "common.cuh"
+#include <stdio.h>
+
+namespace ats {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;   // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UK = 16;   // K per tcgen05.mma for 16-bit inputs
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int MAX_GROUPS = 256;
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + (MAX_GROUPS + 1) * 4;
+
+enum Epilogue : int { kStore = 0, kAddC = 1, kF32 = 2, kSwiGLU = 3 };
+
+struct GemmArgs {
+  int M, N, K;
+  int groups, ragged;
+  const int* counts;
+  int a_gs_mn, a_gs_k, b_gs_mn, b_gs_k;  // per-group coordinate shifts (elements)
+  long long d_gs, c_gs, aux_gs;          // per-group element offsets of D / C / aux
+  __nv_bfloat16* D;
+  const __nv_bfloat16* C;
+  __nv_bfloat16* aux;
+  float* Df32;
+  int ldd, ldc, ldaux;
+  int a_mn, b_mn;        // operand majors: 0 = K-major, 1 = MN-major
+  int epilogue;
+  int up_offset;         // SwiGLU: row offset of the "up" half inside B (= intermediate size)
+  float alpha;
+  int beta;              // kF32: accumulate into Df32
+  int* status;
+};
+
+struct TileCoord {
+  int g, m0, n0, k_iters, valid;
+};
+
+__device__ __forceinline__ int round_up_128(int v) { return (v + 127) & ~127; }
+
+// Rows of D and reduction length of group g.
+__device__ __forceinline__ void group_extents(const GemmArgs& p, int g, int& mg, int& kg) {
+  mg = p.M;
+  kg = p.K;
+  if (p.ragged == 1) mg = min(round_up_128(p.counts[g]), p.M);
+  if (p.ragged == 2) kg = min(round_up_128(p.counts[g]), p.K);
+}
+
+__device__ __forceinline__ int tiles_n_of(const GemmArgs& p) {
+  return p.epilogue == kSwiGLU ? (p.N + 127) / 128 : (p.N + BN - 1) / BN;
+}
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* prefix, int tile, int& g_hint) {
+  TileCoord t;
+  int g = g_hint;
+  while (g + 1 < p.groups && tile >= prefix[g + 1]) ++g;
+  g_hint = g;
+  int local = tile - prefix[g];
+  int tn = tiles_n_of(p);
+  int mt = local / tn, nt = local - mt * tn;
+  int mg, kg;
+  group_extents(p, g, mg, kg);
+  t.g = g;
+  t.m0 = mt * BM;
+  t.n0 = nt * (p.epilogue == kSwiGLU ? 128 : BN);
+  t.k_iters = (kg + BK - 1) / BK;
+  t.valid = mg;
+  return t;
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]
+  uint64_t* empty = bars + STAGES;          // [STAGES]
+  uint64_t* tfull = bars + 2 * STAGES;      // [2]
+  uint64_t* tempty = bars + 2 * STAGES + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* prefix = reinterpret_cast<int*>(smem + STAGES * STAGE_BYTES + 256);  // [groups + 1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    // tile prefix sums (groups is small)
+    int acc = 0;
+    int tn = tiles_n_of(p);
+    for (int g = 0; g < p.groups; ++g) {
+      prefix[g] = acc;
+      int mg, kg;
+      group_extents(p, g, mg, kg);
+      acc += ((mg + BM - 1) / BM) * tn;
+    }
+    prefix[p.groups] = acc;
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = prefix[p.groups];
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0, phase = 0, g_hint = 0;
+      uint32_t armed = 0, armed_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        TileCoord t = decode_tile(p, prefix, tile, g_hint);
+        const int a_mn_c = t.m0 + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
+        const int b_mn_c = t.n0 + p.b_gs_mn * t.g, b_k_c = p.b_gs_k * t.g;
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          if (!mbar_wait_bounded(&empty[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          armed |= 1u << stage;
+          armed_phase = (armed_phase & ~(1u << stage)) | (uint32_t(phase) << stage);
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(a_dst, &map_a, &full[stage], a_k_c + k0, a_mn_c);  // box 64 x 128
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)  // box 64 (MN) x 64 (K rows)
+              tma_load_2d(a_dst + j * (BK * 128), &map_a, &full[stage], a_mn_c + 64 * j, a_k_c + k0);
+          }
+          if (!p.b_mn) {
+            // two boxes of 64 x 128 rows; SwiGLU takes the second from the "up" half
+            const int second = p.epilogue == kSwiGLU ? b_mn_c + p.up_offset : b_mn_c + 128;
+            tma_load_2d(b_dst, &map_b, &full[stage], b_k_c + k0, b_mn_c);
+            tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], b_k_c + k0, second);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * (BK * 128), &map_b, &full[stage], b_mn_c + 64 * j, b_k_c + k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // let copies that were already issued land before the CTA gives its shared memory back
+        for (int s = 0; s < STAGES; ++s) {
+          if (!(armed >> s & 1)) continue;
+          uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full[s], (armed_phase >> s) & 1) && globaltimer_ns() - t0 < 10000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
+      int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        TileCoord t = decode_tile(p, prefix, tile, g_hint);
+        if (!mbar_wait_bounded(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          if (!mbar_wait_bounded(&full[stage], phase, abort_flag, p.status, kTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(a_addr + k * (UK * 128), BK * 128, 1024)
+                                          : make_smem_desc_sw128(a_addr + k * (UK * 2), 16, 1024);
+            const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_addr + k * (UK * 128), BK * 128, 1024)
+                                          : make_smem_desc_sw128(b_addr + k * (UK * 2), 16, 1024);
+            tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          tc_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (t.k_iters > 0) tc_commit(&tfull[acc]);
+        else mbar_arrive(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0, acc_phase = 0, g_hint = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      TileCoord t = decode_tile(p, prefix, tile, g_hint);
+      if (!mbar_wait_bounded(&tfull[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
+      const int row = t.m0 + row_in_tile;
+      const bool row_ok = row < t.valid;
+      const bool have_acc = t.k_iters > 0;
+      if (p.epilogue == kSwiGLU) {
+        __nv_bfloat16* drow = p.D + p.d_gs * t.g + (long long)row * p.ldd;
+        __nv_bfloat16* arow = p.aux ? p.aux + p.aux_gs * t.g + (long long)row * p.ldaux : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t gr[32], ur[32];
+          tmem_ld_32x32(taddr + c * 32, gr);
+          tmem_ld_32x32(taddr + 128 + c * 32, ur);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c * 32 + v * 8;
+              if (col < p.N) {
+                uint32_t h[4], gg[4], uu[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * p.alpha, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * p.alpha;
+                  float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * p.alpha, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * p.alpha;
+                  gg[e] = pack_bf16x2(g0, g1);
+                  uu[e] = pack_bf16x2(u0, u1);
+                  // activation on the bf16-rounded values so a separate SwiGLU pass gives identical bits
+                  float2 gq = unpack_bf16x2(gg[e]), uq = unpack_bf16x2(uu[e]);
+                  h[e] = pack_bf16x2(silu_f(gq.x) * uq.x, silu_f(gq.y) * uq.y);
+                }
+                *reinterpret_cast<uint4*>(drow + col) = make_uint4(h[0], h[1], h[2], h[3]);
+                if (arow) {
+                  *reinterpret_cast<uint4*>(arow + col) = make_uint4(gg[0], gg[1], gg[2], gg[3]);
+                  *reinterpret_cast<uint4*>(arow + p.up_offset + col) = make_uint4(uu[0], uu[1], uu[2], uu[3]);
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0;
+          }
+          if (!row_ok) continue;
+          const int colbase = t.n0 + c * 32;
+          if (p.epilogue == kF32) {
+            float* drow = p.Df32 + p.d_gs * t.g + (long long)row * p.ldd;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              const int col = colbase + v * 4;
+              if (col < p.N) {
+                float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
+                                       __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
+                if (p.beta) {
+                  float4 old = *reinterpret_cast<float4*>(drow + col);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(drow + col) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* drow = p.D + p.d_gs * t.g + (long long)row * p.ldd;
+            const __nv_bfloat16* crow =
+                p.epilogue == kAddC ? p.C + p.c_gs * t.g + (long long)row * p.ldc : nullptr;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = colbase + v * 8;
+              if (col < p.N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+                if (crow) {
+                  uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
+                  float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
+                  f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
+                  f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
+                }
+                *reinterpret_cast<uint4*>(drow + col) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                                   pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host
+// ------------------------------------------------------------------------------------------------
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int elem_bytes,
+                 uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return 1000;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * elem_bytes) & 15)) return 1001;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1100 + int(r);
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+}  // namespace ats
+
+using namespace ats;
+
+// Generic entry point. The global 2-D extents of both operands are given explicitly (rows x cols, cols contiguous,
+// pitch ld elements); for a K-major operand cols is the reduction dimension, for an MN-major operand rows is.
+// Returns 0 or an error code (>= 1000: tensor-map encode, otherwise cudaError_t of the launch).
+ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, long long lda, int a_mn,
+                          const void* B, long long b_rows, long long b_cols, long long ldb, int b_mn,
+                          void* D, int ldd, const void* C, int ldc, void* aux, int ldaux,
+                          int M, int N, int K, float alpha, int beta, int epilogue, int up_offset,
+                          int groups, int ragged, const int* counts,
+                          int a_gs_mn, int a_gs_k, int b_gs_mn, int b_gs_k,
+                          long long d_gs, long long c_gs, long long aux_gs,
+                          int* status, int max_ctas, void* stream) {
+  if (groups < 1 || groups > MAX_GROUPS) return 1002;
+  if ((N & 7) || (a_gs_mn & 7) || (a_gs_k & 7) || (b_gs_mn & 7) || (b_gs_k & 7) || (ldd & 7) || (d_gs & 7)) return 1003;
+  if (epilogue == kSwiGLU && (b_mn || (up_offset & 7))) return 1004;
+  if (ragged && !counts) return 1005;
+  CUtensorMap ma, mb;
+  int e;
+  if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 2, 64, a_mn ? 64 : 128))) return e;
+  if ((e = make_tmap_2d(&mb, B, b_rows, b_cols, ldb, 2, 64, b_mn ? 64 : 128))) return e;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K; p.groups = groups; p.ragged = ragged; p.counts = counts;
+  p.a_gs_mn = a_gs_mn; p.a_gs_k = a_gs_k; p.b_gs_mn = b_gs_mn; p.b_gs_k = b_gs_k;
+  p.d_gs = d_gs; p.c_gs = c_gs; p.aux_gs = aux_gs;
+  p.D = static_cast<__nv_bfloat16*>(D); p.C = static_cast<const __nv_bfloat16*>(C);
+  p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = static_cast<float*>(D);
+  p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = a_mn; p.b_mn = b_mn; p.epilogue = epilogue;
+  p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t ce = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    if (ce != cudaSuccess) return int(ce);
+    attr_set = true;
+  }
+  const int tn = epilogue == kSwiGLU ? (N + 127) / 128 : (N + BN - 1) / BN;
+  long long upper = (long long)groups * ((M + BM - 1) / BM) * tn;
+  int grid = num_sms();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (upper < grid) grid = int(upper);
+  if (grid < 1) return 0;
+  gemm_bf16_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  return int(cudaGetLastError());
+}

@@ -1,0 +1,448 @@
+// Mixture-of-Experts routing kernels: gate projection (small-N GEMM) with its two gradients, fused
+// softmax / top-k / renormalise, deterministic capacity-limited slot planning, row dispatch into per-expert
+// buffers (local or on a peer GPU through a pointer table), weighted combine, and the per-slot dot product that
+// gives the combine-weight gradient.
+//
+// Counterparts in the reference: core/moe_cuda_ops.cu:47-310 (atomics-ordered top-k / dispatch / combine) and the
+// eager routing in core/model.py:1169-1263.  Differences: softmax runs over all experts before the top-k and the
+// kept probabilities are renormalised (the documented semantics), slot order is token order (deterministic), and
+// capacity is enforced.
+#include "common.cuh"
+
+namespace ats {
+
+// ------------------------------------------------------------------------------------------------
+// gate projection: logits[t, e] = sum_h x[t, h] * wg[e, h]       (fp32 out), one warp per token
+// ------------------------------------------------------------------------------------------------
+template <int EMAX>
+__global__ void __launch_bounds__(256)
+gate_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, float* __restrict__ logits,
+                long long tokens, int hidden, int experts) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  float acc[EMAX];
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) acc[e] = 0.f;
+  const int nvec = hidden >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + t * hidden);
+  for (int v = lane; v < nvec; v += 32) {
+    uint4 a = xr[v];
+    float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      if (e < experts) {
+        uint4 b = reinterpret_cast<const uint4*>(wg + (long long)e * hidden)[v];
+        float2 w0 = unpack_bf16x2(b.x), w1 = unpack_bf16x2(b.y), w2 = unpack_bf16x2(b.z), w3 = unpack_bf16x2(b.w);
+        acc[e] += x0.x * w0.x + x0.y * w0.y + x1.x * w1.x + x1.y * w1.y + x2.x * w2.x + x2.y * w2.y + x3.x * w3.x + x3.y * w3.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) {
+    if (e < experts) {
+      float s = warp_sum(acc[e]);
+      if (lane == 0) logits[t * experts + e] = s;
+    }
+  }
+}
+
+// dx[t, h] (+)= sum_e dlogits[t, e] * wg[e, h]
+__global__ void __launch_bounds__(256)
+gate_bwd_dx_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ wg, __nv_bfloat16* __restrict__ dx,
+                   long long tokens, int hidden, int experts, int accumulate) {
+  const int vpr = hidden >> 3;
+  const long long total = tokens * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vpr;
+    const int v = int(i - t * vpr);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int e = 0; e < experts; ++e) {
+      const float d = dlogits[t * experts + e];
+      uint4 b = reinterpret_cast<const uint4*>(wg + (long long)e * hidden)[v];
+      float2 w0 = unpack_bf16x2(b.x), w1 = unpack_bf16x2(b.y), w2 = unpack_bf16x2(b.z), w3 = unpack_bf16x2(b.w);
+      acc[0] += d * w0.x; acc[1] += d * w0.y; acc[2] += d * w1.x; acc[3] += d * w1.y;
+      acc[4] += d * w2.x; acc[5] += d * w2.y; acc[6] += d * w3.x; acc[7] += d * w3.y;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(dx + t * hidden) + v;
+    if (accumulate) {
+      uint4 o = *dst;
+      float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+    *dst = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+// dwg partial: block b sums tokens [b*chunk, (b+1)*chunk): partial[b][e][h] = sum_t dlogits[t,e] * x[t,h]
+__global__ void __launch_bounds__(256)
+gate_bwd_dw_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ x, float* __restrict__ partial,
+                   long long tokens, int hidden, int experts, int chunk) {
+  const long long t0 = (long long)blockIdx.x * chunk;
+  const long long t1 = min(t0 + chunk, tokens);
+  for (int e0 = 0; e0 < experts; e0 += 8) {
+    for (int v = threadIdx.x; v < (hidden >> 3); v += blockDim.x) {
+      float acc[8][8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.f;
+      for (long long t = t0; t < t1; ++t) {
+        uint4 q = reinterpret_cast<const uint4*>(x + t * hidden)[v];
+        float2 x0 = unpack_bf16x2(q.x), x1 = unpack_bf16x2(q.y), x2 = unpack_bf16x2(q.z), x3 = unpack_bf16x2(q.w);
+        float xs[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+          if (e0 + a < experts) {
+            const float d = dlogits[t * experts + e0 + a];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) acc[a][b] += d * xs[b];
+          }
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 8; ++a) {
+        if (e0 + a < experts) {
+          float* dst = partial + ((long long)blockIdx.x * experts + e0 + a) * hidden + v * 8;
+          reinterpret_cast<float4*>(dst)[0] = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+          reinterpret_cast<float4*>(dst)[1] = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// softmax over all experts (after temperature), top-k, renormalise.  One thread per token, experts <= 64.
+//   probs[t, e]   : softmax(logits / temperature)                         (kept for backward)
+//   topk_idx[t,k] : expert ids, descending probability, ties -> lower id
+//   topk_w[t, k]  : probs of the kept experts / their sum
+// ------------------------------------------------------------------------------------------------
+__global__ void topk_softmax_kernel(const float* __restrict__ logits, float* __restrict__ probs, int* __restrict__ topk_idx,
+                                    float* __restrict__ topk_w, long long tokens, int experts, int k, float inv_temp) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  float p[64];
+  float m = -INFINITY;
+  for (int e = 0; e < experts; ++e) {
+    p[e] = logits[t * experts + e] * inv_temp;
+    m = fmaxf(m, p[e]);
+  }
+  float s = 0.f;
+  for (int e = 0; e < experts; ++e) {
+    p[e] = __expf(p[e] - m);
+    s += p[e];
+  }
+  const float inv = 1.f / s;
+  for (int e = 0; e < experts; ++e) {
+    p[e] *= inv;
+    probs[t * experts + e] = p[e];
+  }
+  unsigned long long taken = 0ull;
+  float wsum = 0.f;
+  float wk[8];
+  int ik[8];
+  for (int j = 0; j < k; ++j) {
+    float best = -1.f;
+    int bi = 0;
+    for (int e = 0; e < experts; ++e)
+      if (!((taken >> e) & 1ull) && p[e] > best) {
+        best = p[e];
+        bi = e;
+      }
+    taken |= 1ull << bi;
+    wk[j] = best;
+    ik[j] = bi;
+    wsum += best;
+  }
+  const float wi = 1.f / fmaxf(wsum, 1e-20f);
+  for (int j = 0; j < k; ++j) {
+    topk_idx[t * k + j] = ik[j];
+    topk_w[t * k + j] = wk[j] * wi;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Slot planning (single CTA, deterministic): slot s = t*k + j goes to expert e = topk_idx[s]; its rank is the
+// number of earlier slots with the same expert.  rank >= capacity -> dropped (pos = -1).
+//   slot_pos[s] = rank (row inside the expert's region)   counts[e] = min(total_e, capacity)
+//   totals[e]   = un-clamped demand (for statistics / aux loss)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+plan_slots_kernel(const int* __restrict__ topk_idx, int* __restrict__ slot_pos, int* __restrict__ counts,
+                  int* __restrict__ totals, long long slots, int experts, int capacity) {
+  __shared__ int running[64];
+  __shared__ int warp_cnt[32][64 + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x < 64) running[threadIdx.x] = 0;
+  __syncthreads();
+  for (long long base = 0; base < slots; base += blockDim.x) {
+    const long long s = base + threadIdx.x;
+    const int e = s < slots ? topk_idx[s] : -1;
+    int my_rank_in_warp = 0;
+    for (int x = 0; x < experts; ++x) {
+      const unsigned mask = __ballot_sync(0xffffffffu, e == x);
+      if (e == x) my_rank_in_warp = __popc(mask & ((1u << lane) - 1u));
+      if (lane == 0) warp_cnt[warp][x] = __popc(mask);
+    }
+    __syncthreads();
+    int before = 0;
+    if (e >= 0) {
+      for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+      const int rank = running[e] + before + my_rank_in_warp;
+      slot_pos[s] = rank < capacity ? rank : -1;
+    }
+    __syncthreads();
+    if (threadIdx.x < experts) {
+      int tot = 0;
+      for (int w = 0; w < nwarps; ++w) tot += warp_cnt[w][threadIdx.x];
+      running[threadIdx.x] += tot;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x < experts) {
+    const int tot = running[threadIdx.x];
+    counts[threadIdx.x] = tot < capacity ? tot : capacity;
+    if (totals) totals[threadIdx.x] = tot;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Dispatch: for every kept slot copy (optionally scaled) row src[t] into dst_base[e] + pos * hidden, where
+// dst_base is a table of per-expert base pointers (a peer GPU's receive buffer under expert parallelism).
+// The last blocks zero the pad rows [count_e, round_up_128(count_e)) so that whole 128-row tiles are defined.
+// One warp per slot.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+dispatch_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ topk_idx,
+                     const int* __restrict__ slot_pos, const float* __restrict__ slot_scale,
+                     __nv_bfloat16* const* __restrict__ dst_base, const int* __restrict__ counts, long long slots, int k,
+                     int hidden, int experts, int capacity) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int vpr = hidden >> 3;
+  if (w < slots) {
+    const int pos = slot_pos[w];
+    if (pos < 0) return;
+    const int e = topk_idx[w];
+    const long long t = w / k;
+    const uint4* s = reinterpret_cast<const uint4*>(src + t * hidden);
+    uint4* d = reinterpret_cast<uint4*>(dst_base[e] + (long long)pos * hidden);
+    if (slot_scale) {
+      const float sc = slot_scale[w];
+      for (int v = lane; v < vpr; v += 32) {
+        uint4 a = s[v];
+        float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+        d[v] = make_uint4(pack_bf16x2(f0.x * sc, f0.y * sc), pack_bf16x2(f1.x * sc, f1.y * sc),
+                          pack_bf16x2(f2.x * sc, f2.y * sc), pack_bf16x2(f3.x * sc, f3.y * sc));
+      }
+    } else {
+      for (int v = lane; v < vpr; v += 32) d[v] = s[v];
+    }
+    return;
+  }
+  // pad rows: warp index beyond the slots enumerates (expert, pad row) pairs, at most 127 per expert
+  const long long pw = w - slots;
+  const int e = int(pw / 128);
+  if (e >= experts) return;
+  const int c = counts[e];
+  const int padded = min((c + 127) & ~127, capacity);
+  const int row = c + int(pw % 128);
+  if (row >= padded) return;
+  uint4* d = reinterpret_cast<uint4*>(dst_base[e] + (long long)row * hidden);
+  for (int v = lane; v < vpr; v += 32) d[v] = make_uint4(0, 0, 0, 0);
+}
+
+// Combine: out[t] = (res[t]) + sum_j w[t,j] * rows[e_j][pos_j]   over kept slots; one warp per token.
+__global__ void __launch_bounds__(256)
+combine_rows_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restrict__ topk_idx,
+                    const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
+                    const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, long long tokens, int k, int hidden) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const int vpr = hidden >> 3;
+  for (int v = lane; v < vpr; v += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (res) {
+      uint4 a = reinterpret_cast<const uint4*>(res + t * hidden)[v];
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+    }
+    for (int j = 0; j < k; ++j) {
+      const int pos = slot_pos[t * k + j];
+      if (pos < 0) continue;
+      const float wt = topk_w ? topk_w[t * k + j] : 1.f;
+      uint4 a = reinterpret_cast<const uint4*>(src_base[topk_idx[t * k + j]] + (long long)pos * hidden)[v];
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
+      acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
+    }
+    reinterpret_cast<uint4*>(out + t * hidden)[v] =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+// dw[t, j] = < dout[t], rows[e_j][pos_j] >  (0 for dropped slots); one warp per slot.
+__global__ void __launch_bounds__(256)
+slot_dot_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restrict__ topk_idx,
+                const int* __restrict__ slot_pos, const __nv_bfloat16* __restrict__ dout, float* __restrict__ dw,
+                long long slots, int k, int hidden) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= slots) return;
+  const int pos = slot_pos[w];
+  float acc = 0.f;
+  if (pos >= 0) {
+    const long long t = w / k;
+    const uint4* a = reinterpret_cast<const uint4*>(dout + t * hidden);
+    const uint4* b = reinterpret_cast<const uint4*>(src_base[topk_idx[w]] + (long long)pos * hidden);
+    for (int v = lane; v < (hidden >> 3); v += 32) {
+      uint4 p = a[v], q = b[v];
+      float2 p0 = unpack_bf16x2(p.x), p1 = unpack_bf16x2(p.y), p2 = unpack_bf16x2(p.z), p3 = unpack_bf16x2(p.w);
+      float2 q0 = unpack_bf16x2(q.x), q1 = unpack_bf16x2(q.y), q2 = unpack_bf16x2(q.z), q3 = unpack_bf16x2(q.w);
+      acc += p0.x * q0.x + p0.y * q0.y + p1.x * q1.x + p1.y * q1.y + p2.x * q2.x + p2.y * q2.y + p3.x * q3.x + p3.y * q3.y;
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dw[w] = acc;
+}
+
+// Per-sequence top-k token selection for Mixture-of-Depths: scores[b, l] -> the `keep` largest per sequence,
+// emitted in ascending position order (so causal attention / RoPE positions stay ordered).  One CTA per
+// sequence, rank by counting (L <= 8192).  sel[b, i] = position, i < keep.
+__global__ void __launch_bounds__(1024)
+mod_select_kernel(const float* __restrict__ scores, int* __restrict__ sel, int seq_len, int keep) {
+  extern __shared__ float s_sc[];
+  int* s_flag = reinterpret_cast<int*>(s_sc + seq_len);
+  const float* sc = scores + (long long)blockIdx.x * seq_len;
+  for (int i = threadIdx.x; i < seq_len; i += blockDim.x) s_sc[i] = sc[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < seq_len; i += blockDim.x) {
+    const float v = s_sc[i];
+    int rank = 0;
+    for (int j = 0; j < seq_len; ++j) {
+      const float o = s_sc[j];
+      rank += (o > v) || (o == v && j < i);
+    }
+    s_flag[i] = rank < keep;
+  }
+  __syncthreads();
+  // ordered compaction: thread 0 of each warp-sized segment would be slow; use a simple block scan over chunks
+  __shared__ int s_base;
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (int base = 0; base < seq_len; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int f = i < seq_len ? s_flag[i] : 0;
+    const unsigned mask = __ballot_sync(0xffffffffu, f);
+    __shared__ int wsum[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) wsum[warp] = __popc(mask);
+    __syncthreads();
+    int before = s_base;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
+    if (f) sel[(long long)blockIdx.x * keep + before + __popc(mask & ((1u << lane) - 1u))] = i;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < (blockDim.x >> 5); ++w) tot += wsum[w];
+      s_base += tot;
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace ats
+
+using namespace ats;
+
+ATS_API int ats_gate_fwd(const void* x, const void* wg, float* logits, long long tokens, int hidden, int experts, void* stream) {
+  if ((hidden & 7) || experts > 64) return 1003;
+  if (tokens == 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = unsigned((tokens * 32 + 255) / 256);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(wg);
+  if (experts <= 8) gate_fwd_kernel<8><<<blocks, 256, 0, s>>>(X, W, logits, tokens, hidden, experts);
+  else if (experts <= 16) gate_fwd_kernel<16><<<blocks, 256, 0, s>>>(X, W, logits, tokens, hidden, experts);
+  else gate_fwd_kernel<64><<<blocks, 256, 0, s>>>(X, W, logits, tokens, hidden, experts);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_gate_bwd_dx(const float* dlogits, const void* wg, void* dx, long long tokens, int hidden, int experts,
+                            int accumulate, void* stream) {
+  if (hidden & 7) return 1003;
+  if (tokens == 0) return 0;
+  long long work = tokens * (hidden >> 3);
+  long long blocks = (work + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  gate_bwd_dx_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      dlogits, static_cast<const __nv_bfloat16*>(wg), static_cast<__nv_bfloat16*>(dx), tokens, hidden, experts, accumulate);
+  return int(cudaGetLastError());
+}
+
+// partial: fp32 scratch [nblocks, experts, hidden]; reduce with ats_colsum_partial(partial, nblocks, experts*hidden, ...).
+ATS_API int ats_gate_bwd_dw(const float* dlogits, const void* x, float* partial, int nblocks, long long tokens, int hidden,
+                            int experts, void* stream) {
+  if (hidden & 7) return 1003;
+  const int chunk = int((tokens + nblocks - 1) / nblocks);
+  gate_bwd_dw_kernel<<<nblocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(dlogits, static_cast<const __nv_bfloat16*>(x),
+                                                                           partial, tokens, hidden, experts, chunk > 0 ? chunk : 1);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_topk_softmax(const float* logits, float* probs, int* topk_idx, float* topk_w, long long tokens, int experts,
+                             int k, float temperature, void* stream) {
+  if (experts > 64 || k > 8 || k > experts) return 1003;
+  if (tokens == 0) return 0;
+  topk_softmax_kernel<<<unsigned((tokens + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, probs, topk_idx, topk_w, tokens, experts, k, 1.f / temperature);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_plan_slots(const int* topk_idx, int* slot_pos, int* counts, int* totals, long long slots, int experts,
+                           int capacity, void* stream) {
+  if (experts > 64) return 1003;
+  plan_slots_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(topk_idx, slot_pos, counts, totals, slots, experts, capacity);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_dispatch_rows(const void* src, const int* topk_idx, const int* slot_pos, const float* slot_scale,
+                              void* const* dst_base, const int* counts, long long slots, int k, int hidden, int experts,
+                              int capacity, int zero_pad, void* stream) {
+  if (hidden & 7) return 1003;
+  const long long warps = slots + (zero_pad ? (long long)experts * 128 : 0);
+  if (warps == 0) return 0;
+  dispatch_rows_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), topk_idx, slot_pos, slot_scale,
+      reinterpret_cast<__nv_bfloat16* const*>(dst_base), counts, slots, k, hidden, experts, capacity);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_combine_rows(void* const* src_base, const int* topk_idx, const int* slot_pos, const float* topk_w,
+                             const void* res, void* out, long long tokens, int k, int hidden, void* stream) {
+  if (hidden & 7) return 1003;
+  if (tokens == 0) return 0;
+  combine_rows_kernel<<<unsigned((tokens * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16* const*>(src_base), topk_idx, slot_pos, topk_w, static_cast<const __nv_bfloat16*>(res),
+      static_cast<__nv_bfloat16*>(out), tokens, k, hidden);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_slot_dot(void* const* src_base, const int* topk_idx, const int* slot_pos, const void* dout, float* dw,
+                         long long slots, int k, int hidden, void* stream) {
+  if (hidden & 7) return 1003;
+  if (slots == 0) return 0;
+  slot_dot_kernel<<<unsigned((slots * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16* const*>(src_base), topk_idx, slot_pos, static_cast<const __nv_bfloat16*>(dout), dw, slots, k,
+      hidden);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_mod_select(const float* scores, int* sel, int batch, int seq_len, int keep, void* stream) {
+  if (seq_len > 8192 || keep > seq_len) return 1003;
+  if (batch == 0) return 0;
+  mod_select_kernel<<<batch, 1024, seq_len * 8, static_cast<cudaStream_t>(stream)>>>(scores, sel, seq_len, keep);
+  return int(cudaGetLastError());
+}
