@@ -378,7 +378,8 @@ class DeepSeekTransformer(nn.Module):
         n_layers = cfg.num_layers
 
         def normal_(t, s):
-            t.copy_(torch.randn(t.shape, generator=generator, dtype=torch.float32).mul_(s).to(t.dtype))
+            t.copy_(torch.randn(t.shape, generator=generator, dtype=torch.float32,
+                                device=t.device if generator is None else None).mul_(s).to(t.dtype))
         normal_(self.embed_tokens.weight, std)
         if self.lm_head_weight is not None:
             normal_(self.lm_head_weight, std)
@@ -525,7 +526,7 @@ def _import_reference_names(module: DeepSeekTransformer, state: Dict[str, torch.
         if blk.ffn_kind == "moe":
             e_local = blk.ffn.experts_w1.shape[0]
             first = blk.ffn.ep_rank * e_local
-            if f"{base}ffn.experts.{first}.gate_up_proj.weight" in state:
+            if all(f"{base}ffn.experts.{first + j}.gate_up_proj.weight" in state for j in range(e_local)):
                 state[base + "ffn.experts_w1"] = torch.stack(
                     [state[f"{base}ffn.experts.{first + j}.gate_up_proj.weight"] for j in range(e_local)])
                 state[base + "ffn.experts_w2"] = torch.stack(

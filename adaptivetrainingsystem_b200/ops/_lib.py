@@ -145,7 +145,17 @@ def check_status(device=None) -> None:
             raise KernelError(f"device {key}: kernel wait timed out: {_STATUS_NAMES.get(v, v)}")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native entry points called so far (each launches at least one kernel)."""
+    return _launches
+
+
 def check(err: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if err != 0:
         if err >= 1000:
             raise KernelError(f"{what}: argument/tensor-map error {err}")

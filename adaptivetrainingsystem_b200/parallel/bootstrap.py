@@ -1,0 +1,162 @@
+"""Process-group bootstrap and the rank mesh.
+
+One process per GPU; ``torch.distributed`` (NCCL on CUDA, Gloo on CPU) provides rendezvous, barriers and the
+baseline collectives.  The mesh factors the world into pipeline x data x expert axes and hands out cached
+process groups per axis (the role of ``ProcessGroupMesh`` / ``DistCoordinator`` in the reference's vendored
+tree, ``colossalai/cluster/process_group_mesh.py:24-260``, ``dist_coordinator.py:40-201``; first-party bootstrap
+``backend/backend_fsdp.py:102-116``).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def env_rank_info() -> Tuple[int, int, int]:
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+            int(os.environ.get("WORLD_SIZE", "1")))
+
+
+def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) -> Tuple[int, int, int]:
+    """Initialise the default process group from the launcher's environment (``env://``).  Returns
+    ``(rank, local_rank, world_size)``; a single process without launcher variables needs no group."""
+    rank, local_rank, world = env_rank_info()
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local_rank % max(torch.cuda.device_count(), 1))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        backend = backend or ("nccl" if use_cuda else "gloo")
+        kwargs = {}
+        if backend == "nccl":
+            kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+        dist.init_process_group(backend=backend, init_method="env://", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    return rank, local_rank, world
+
+
+def shutdown() -> None:
+    if dist.is_initialized():
+        try:
+            dist.barrier()
+        except Exception:
+            pass
+        dist.destroy_process_group()
+
+
+def world_size(group=None) -> int:
+    return dist.get_world_size(group) if dist.is_initialized() else 1
+
+
+def get_rank(group=None) -> int:
+    return dist.get_rank(group) if dist.is_initialized() else 0
+
+
+def is_main_process() -> bool:
+    return get_rank() == 0
+
+
+def barrier(group=None) -> None:
+    if dist.is_initialized():
+        dist.barrier(group)
+
+
+@dataclass
+class MeshCoord:
+    pp: int
+    dp: int
+    ep: int
+
+
+class ProcessMesh:
+    """World = pp x dp_outer x ep.  Expert parallelism lives inside data parallelism: the ``ep`` ranks of one
+    group hold different experts and the same dense weights; the data-parallel group for dense parameters is
+    ``dp_outer x ep`` and for expert parameters ``dp_outer`` ("expert data parallel")."""
+
+    def __init__(self, world: Optional[int] = None, rank: Optional[int] = None, pp_size: int = 1, ep_size: int = 1,
+                 create_groups: bool = True):
+        self.world = world if world is not None else world_size()
+        self.rank = rank if rank is not None else get_rank()
+        if self.world % (pp_size * ep_size):
+            raise ValueError(f"world size {self.world} not divisible by pp*ep = {pp_size * ep_size}")
+        self.pp_size, self.ep_size = pp_size, ep_size
+        self.dp_outer = self.world // (pp_size * ep_size)
+        self.dp_size = self.dp_outer * ep_size
+        self.coord = self.coord_of(self.rank)
+        self._groups: Dict[str, Optional[dist.ProcessGroup]] = {"dp": None, "ep": None, "edp": None, "pp": None}
+        self._ranks: Dict[str, List[int]] = {}
+        if create_groups:
+            self._build_groups()
+
+    def coord_of(self, rank: int) -> MeshCoord:
+        ep = rank % self.ep_size
+        dp = (rank // self.ep_size) % self.dp_outer
+        pp = rank // (self.ep_size * self.dp_outer)
+        return MeshCoord(pp, dp, ep)
+
+    def rank_of(self, pp: int, dp: int, ep: int) -> int:
+        return (pp * self.dp_outer + dp) * self.ep_size + ep
+
+    def ranks_along(self, axis: str, rank: Optional[int] = None) -> List[int]:
+        c = self.coord_of(self.rank if rank is None else rank)
+        if axis == "ep":
+            return [self.rank_of(c.pp, c.dp, e) for e in range(self.ep_size)]
+        if axis == "edp":
+            return [self.rank_of(c.pp, d, c.ep) for d in range(self.dp_outer)]
+        if axis == "dp":
+            return [self.rank_of(c.pp, d, e) for d in range(self.dp_outer) for e in range(self.ep_size)]
+        if axis == "pp":
+            return [self.rank_of(p, c.dp, c.ep) for p in range(self.pp_size)]
+        raise KeyError(axis)
+
+    def _build_groups(self) -> None:
+        for axis in ("dp", "ep", "edp", "pp"):
+            self._ranks[axis] = self.ranks_along(axis)
+            if not dist.is_initialized() or self.world == 1:
+                continue
+            seen = set()
+            for r in range(self.world):  # every rank must create every group, in the same order
+                ranks = tuple(self.ranks_along(axis, r))
+                if ranks in seen:
+                    continue
+                seen.add(ranks)
+                if len(ranks) == self.world:
+                    g = dist.group.WORLD
+                elif len(ranks) == 1:
+                    g = None
+                else:
+                    g = dist.new_group(list(ranks))
+                if self.rank in ranks:
+                    self._groups[axis] = g
+
+    def group(self, axis: str):
+        return self._groups[axis]
+
+    def size(self, axis: str) -> int:
+        return {"dp": self.dp_size, "ep": self.ep_size, "edp": self.dp_outer, "pp": self.pp_size}[axis]
+
+    def index(self, axis: str) -> int:
+        return self.ranks_along(axis).index(self.rank)
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.coord.pp == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.coord.pp == self.pp_size - 1
+
+    def describe(self) -> str:
+        parts = []
+        if self.pp_size > 1:
+            parts.append(f"pp{self.pp_size}")
+        if self.ep_size > 1:
+            parts.append(f"ep{self.ep_size}")
+        parts.append(f"dp{self.dp_size}")
+        return "+".join(parts)

@@ -1,0 +1,108 @@
+"""Precision and quantisation registries (reference ``training/trainer.py:157-801``).
+
+On this framework parameters live in the compute dtype (bf16 on B200) with fp32 master weights inside the sharded
+optimiser, so "mixed_bf16" needs no autocast; autocast contexts are only produced for fp32-parameter CPU / fp16 runs.
+fp8 precisions select the block-scaled e4m3 linear path of the model instead of wrapping ``torch.autocast``."""
+from __future__ import annotations
+
+from contextlib import nullcontext
+from typing import Any, Dict, Optional
+
+import torch
+
+PRECISION_TABLE: Dict[str, Dict[str, Any]] = {
+    "fp64": dict(dtype=torch.float64, bits=64, autocast=False), "fp32": dict(dtype=torch.float32, bits=32, autocast=False),
+    "tf32": dict(dtype=torch.float32, bits=19, autocast=False, tf32=True),
+    "fp16": dict(dtype=torch.float16, bits=16, autocast=False, loss_scale=True),
+    "bf16": dict(dtype=torch.bfloat16, bits=16, autocast=False),
+    "mixed_fp16": dict(dtype=torch.float16, bits=16, autocast=True, loss_scale=True),
+    "mixed_bf16": dict(dtype=torch.bfloat16, bits=16, autocast=True),
+    "fp8": dict(dtype=torch.bfloat16, bits=8, fp8="e4m3"), "fp8_e4m3": dict(dtype=torch.bfloat16, bits=8, fp8="e4m3"),
+    "fp8_e5m2": dict(dtype=torch.bfloat16, bits=8, fp8="e5m2"), "mixed_fp8": dict(dtype=torch.bfloat16, bits=8, fp8="e4m3"),
+    "int8": dict(dtype=torch.bfloat16, bits=8, quant=True), "int4": dict(dtype=torch.bfloat16, bits=4, quant=True),
+}
+
+
+class DynamicLossScaler:
+    """x2 after ``growth_interval`` clean steps, x0.5 after ``hysteresis`` overflows (fp16 only)."""
+
+    def __init__(self, init_scale: float = 65536.0, growth_interval: int = 1000, hysteresis: int = 2,
+                 min_scale: float = 1.0, max_scale: float = 2.0 ** 32):
+        self.scale, self.growth_interval, self.hysteresis = init_scale, growth_interval, hysteresis
+        self.min_scale, self.max_scale = min_scale, max_scale
+        self._good, self._bad = 0, 0
+
+    def update(self, overflow: bool) -> None:
+        if overflow:
+            self._bad += 1
+            self._good = 0
+            if self._bad >= self.hysteresis:
+                self.scale = max(self.scale / 2, self.min_scale)
+                self._bad = 0
+        else:
+            self._good += 1
+            if self._good >= self.growth_interval:
+                self.scale = min(self.scale * 2, self.max_scale)
+                self._good = 0
+
+
+class PrecisionManager:
+    def __init__(self, config, device: torch.device):
+        self.config, self.device = config, device
+        name = config.precision if config.precision != "auto" else "fp32"
+        if name not in PRECISION_TABLE:
+            raise ValueError(f"unknown precision {name}")
+        self.name = name
+        self.info = PRECISION_TABLE[name]
+        self.loss_scaler: Optional[DynamicLossScaler] = DynamicLossScaler(config.fp16_loss_scale) if self.info.get("loss_scale") else None
+        if self.info.get("tf32") or getattr(config, "tf32_enabled", False):
+            torch.backends.cuda.matmul.allow_tf32 = True
+
+    @property
+    def compute_dtype(self) -> torch.dtype:
+        return self.info["dtype"]
+
+    @property
+    def uses_fp8(self) -> bool:
+        return "fp8" in self.info
+
+    def autocast(self):
+        # Parameters already live in the compute dtype; autocast only for fp32-parameter models on request.
+        if self.info.get("autocast") and getattr(self.config, "autocast_fp32_params", False):
+            return torch.autocast(self.device.type, dtype=self.info["dtype"])
+        return nullcontext()
+
+    def supported_precisions(self):
+        return list(PRECISION_TABLE)
+
+    def get_precision_info(self) -> Dict[str, Any]:
+        return {"name": self.name, "bits": self.info["bits"], "dtype": str(self.info["dtype"]),
+                "loss_scaling": self.loss_scaler is not None, "fp8": self.info.get("fp8")}
+
+
+class QuantizationManager:
+    """Weight-only quantisation for inference is optional and needs external packages (bitsandbytes / GPTQ /
+    quanto), none of which is a dependency; the manager reports availability and refuses politely."""
+
+    def __init__(self, config):
+        self.method = getattr(config, "quantization_method", None)
+        self.bits = getattr(config, "quantization_bits", None)
+        self.applied = False
+
+    def available_backends(self) -> Dict[str, bool]:
+        out = {}
+        for mod in ("bitsandbytes", "auto_gptq", "optimum.quanto"):
+            try:
+                __import__(mod)
+                out[mod] = True
+            except Exception:
+                out[mod] = False
+        return out
+
+    def quantize_model(self, model):
+        if not self.method:
+            return model
+        raise RuntimeError(f"quantization backend for {self.method!r} is not installed; available: {self.available_backends()}")
+
+    def status(self) -> Dict[str, Any]:
+        return {"method": self.method, "bits": self.bits, "applied": self.applied, "backends": self.available_backends()}

@@ -1,0 +1,243 @@
+#!/usr/bin/env python
+"""Headline benchmark: MoE training throughput (tokens/s, whole job) on N B200s of one node.
+
+    python bench.py --gpus N --steps K --warmup W [--config b1_moe] [--impl ours|reference]
+
+For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1
+--master-port P bench.py --gpus N ...`` (one rank per GPU).  Rank 0 prints ONE JSON line.
+
+* ``value``: K optimiser steps (forward + backward + gradient reduction + clipped AdamW) timed on the device with CUDA
+  events between a barrier + synchronize on both sides, max over ranks; inputs already on the device.
+* ``e2e``: the same K steps through the public trainer API (``train_step`` + ``optimizer_step``) with each step's batch
+  copied from pinned host memory and the loss read back to the host every step.
+* weak scaling: the per-GPU micro-batch is fixed, experts are spread over the N ranks (EP = gcd(E, N)), dense weights are
+  replicated with ZeRO-1 optimiser sharding.
+
+Synthetic uniform token ids, random-init N(0, 0.02) weights, bf16 compute with fp32 master weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PUBLISHED_TOKENS_PER_S = {  # reference BENCHMARKS.md rows used for vs_baseline
+    "b1_moe": 73000.0,        # "B1 MoE 8x top-2 ~73,000 tok/s" (A100-40GB), BENCHMARKS.md:112-120
+    "mixtral_8x7b": 54000.0,  # "B7 MoE 8x top-2 ~54,000 tok/s" (2x A100-80GB), BENCHMARKS.md:168-176
+    "dense_1b": 96000.0,      # "B1 dense ~96,000 tok/s" (RTX 4090), BENCHMARKS.md:98-107
+    "hybrid_fp8": 91000.0,    # "B1 hybrid ~91,000 tok/s" (A100-40GB), BENCHMARKS.md:137-143
+}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([s.strip() for s in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200 import ops
+    from adaptivetrainingsystem_b200.config import ConfigPresets
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.ops import _lib
+    from adaptivetrainingsystem_b200.parallel import ProcessMesh, init_distributed
+    from adaptivetrainingsystem_b200.parallel.expert_parallel import attach_expert_parallel
+    from adaptivetrainingsystem_b200.training import EnhancedConversationTrainer
+
+    rank, local_rank, world = init_distributed()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    over = {}
+    if args.micro_batch:
+        over.update(batch_size=args.micro_batch, micro_batch_size=args.micro_batch)
+    if args.layers:
+        over["num_layers"] = args.layers
+    if args.seq:
+        over["seq_length"] = args.seq
+    cfg = ConfigPresets.get(args.config, num_workers=0, gradient_checkpointing=bool(args.checkpoint), **over)
+    cfg.fused_comm = not args.nccl_only
+    ep = math.gcd(cfg.num_experts, world) if cfg.use_moe else 1
+    mesh = ProcessMesh(world, rank, ep_size=ep)
+    cfg.world_size, cfg.expert_parallel_size = world, ep
+    torch.manual_seed(1234)
+    mc = cfg.to_model_config()
+    with torch.device(dev):
+        torch.set_default_dtype(torch.bfloat16)
+        model = DeepSeekTransformer(mc, ep_size=ep, ep_rank=mesh.coord.ep)
+        torch.set_default_dtype(torch.float32)
+    model.rope.cos, model.rope.sin = model.rope.cos.float(), model.rope.sin.float()
+    fused = attach_expert_parallel(model, mesh, cfg, use_fused=cfg.fused_comm) if world > 1 else None
+    trainer = EnhancedConversationTrainer(model, None, cfg, mesh=mesh, fused_comm=fused)
+    trainer._setup_scheduler(10 ** 6)
+
+    mb, L, V = cfg.micro_batch_size, cfg.seq_length, cfg.vocab_size
+    g = torch.Generator().manual_seed(99 + rank)
+    n_batches = 4
+    host = []
+    for _ in range(n_batches):
+        ids = torch.randint(0, V, (mb, L + 1), generator=g)
+        host.append({"input_ids": ids[:, :-1].contiguous().pin_memory(), "labels": ids[:, 1:].contiguous().pin_memory()})
+    devb = [{k: v.to(dev) for k, v in b.items()} for b in host]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device(i):
+        trainer.train_step(devb[i % n_batches])
+        trainer.optimizer_step()
+        trainer._pending_device.clear()
+
+    def step_e2e(i):
+        b = host[i % n_batches]
+        batch = {k: v.to(dev, non_blocking=True) for k, v in b.items()}
+        out = trainer.train_step(batch)
+        trainer.optimizer_step()
+        trainer._pending_device.clear()
+        return float(out["loss"])  # device -> host read every step
+
+    for i in range(args.warmup):
+        step_device(i)
+    ops.check_status()
+    barrier()
+    launches0 = _lib.launch_count()
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step_device(i)
+        e1.record()
+        barrier()
+    launches = _lib.launch_count() - launches0
+    ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    ops.check_status()
+
+    # end to end through the public API
+    step_e2e(0)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    f0.record()
+    last = 0.0
+    for i in range(args.steps):
+        last = step_e2e(i)
+    f1.record()
+    barrier()
+    e2e_ms = max(f0.elapsed_time(f1), (time.perf_counter() - w0) * 1e3) / args.steps
+    t = torch.tensor([e2e_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t)
+
+    tokens = mb * L * world
+    value = tokens / (ms / 1e3)
+    pub = PUBLISHED_TOKENS_PER_S.get(args.config)
+    h2d = sum(v.numel() * v.element_size() for v in host[0].values())
+    res = {
+        "metric": "moe_train_tokens_per_sec" if cfg.use_moe else "train_tokens_per_sec", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": (value / pub) if pub else None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": args.config, "global_batch": mb * world, "seq_len": L, "parallelism": mesh.describe() + f"+zero{cfg.zero_stage}",
+                   "hidden": cfg.hidden_size, "layers": cfg.num_layers, "experts": cfg.num_experts if cfg.use_moe else 0,
+                   "top_k": cfg.moe_top_k if cfg.use_moe else 0, "params_total": mc.num_parameters(),
+                   "params_active": mc.num_parameters(True), "l2": "working set per step (weights + activations) far exceeds the 126 MB L2",
+                   "fused_comm": bool(cfg.fused_comm), "attention_backend": os.environ.get("ATS_ATTN", "native"),
+                   "loss_last": last},
+        "clocks": clk.summary(),
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+    }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return res if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        from reference_arm import run as run_ref
+    except Exception as e:
+        return {"impl": "reference", "unavailable": f"reference arm not importable: {e!r}"[:300]}
+    return run_ref(args, PUBLISHED_TOKENS_PER_S)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="b1_moe")
+    ap.add_argument("--micro-batch", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: a run with fewer layers is not a benchmark number")
+    ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--checkpoint", type=int, default=0)
+    ap.add_argument("--nccl-only", action="store_true", help="baseline path: NCCL collectives instead of the fused peer-memory kernels")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    res = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if res:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,123 @@
+"""tcgen05 GEMM against a PyTorch fp32 reference of the same product."""
+import pytest
+import torch
+
+from adaptivetrainingsystem_b200 import ops
+from adaptivetrainingsystem_b200.ops import gemm as G
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, tol=2e-2):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"max err {err} vs scale {denom}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (200, 264, 136), (1024, 2560, 2048), (64, 8, 72)])
+def test_gemm_nt(M, N, K):
+    torch.manual_seed(0)
+    a, b = _rand(M, K), _rand(N, K)
+    _close(G.gemm_nt(a, b), a.float() @ b.float().t())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (200, 264, 136), (1024, 2048, 2560)])
+def test_gemm_nn(M, N, K):
+    torch.manual_seed(1)
+    a, b = _rand(M, K), _rand(K, N)
+    _close(G.gemm_nn(a, b), a.float() @ b.float())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (264, 200, 136), (2560, 2048, 1024)])
+def test_gemm_tn(M, N, K):
+    torch.manual_seed(2)
+    a, b = _rand(K, M), _rand(K, N)
+    _close(G.gemm_tn(a, b), a.float().t() @ b.float())
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(3)
+    M, N, K = 256, 512, 256
+    a, b, c = _rand(M, K), _rand(N, K), _rand(M, N)
+    ref = a.float() @ b.float().t()
+    _close(G.gemm_nt(a, b, add=c), ref + c.float())
+    out32 = torch.full((M, N), 1.0, device=DEV)
+    G.gemm_nt(a, b, out=out32, out_fp32=True, accumulate=True)
+    _close(out32, ref + 1.0, tol=1e-2)
+    acc = _rand(K, N)
+    x, dy = _rand(M, K), _rand(M, N)
+    expect = acc.float() + x.float().t() @ dy.float()
+    G.gemm_tn(x, dy, out=acc, accumulate=True)
+    _close(acc, expect)
+
+
+def test_gemm_swiglu_epilogue():
+    torch.manual_seed(4)
+    M, K, I = 256, 256, 384
+    a, w = _rand(M, K), _rand(2 * I, K, scale=0.1)
+    pre = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    h = G.gemm_nt_swiglu(a, w, pre_act=pre)
+    gu = a.float() @ w.float().t()
+    _close(pre, gu)
+    g, u = gu.chunk(2, dim=-1)
+    _close(h, torch.nn.functional.silu(g) * u, tol=3e-2)
+
+
+def test_grouped_products():
+    torch.manual_seed(5)
+    E, C, K, N = 4, 256, 128, 256
+    counts = torch.tensor([256, 100, 0, 129], dtype=torch.int32, device=DEV)
+    x = _rand(E, C, K)
+    dy = _rand(E, C, N)
+    mask = (torch.arange(C, device=DEV)[None, :] < counts[:, None]).unsqueeze(-1)
+    x = x * mask
+    dy = dy * mask
+    w = _rand(E, N, K, scale=0.2)
+    y = G.grouped_nt(x, w, counts)
+    ref = torch.einsum("eck,enk->ecn", x.float(), w.float())
+    for e in range(E):
+        n = int(counts[e])
+        if n:
+            _close(y[e, :n], ref[e, :n])
+    dx = G.grouped_nn(dy, w, counts)
+    refdx = torch.einsum("ecn,enk->eck", dy.float(), w.float())
+    for e in range(E):
+        n = int(counts[e])
+        if n:
+            _close(dx[e, :n], refdx[e, :n])
+    dw = G.grouped_tn(dy, x, counts)
+    refdw = torch.einsum("ecn,eck->enk", dy.float(), x.float())
+    _close(dw, refdw)
+    assert dw[2].abs().max().item() == 0.0  # an expert without tokens gets a zero gradient
+    pre = torch.zeros(E, C, N, dtype=torch.bfloat16, device=DEV)
+    h = G.grouped_nt(x, w, counts, swiglu=True, pre_act=pre)
+    g, u = ref.chunk(2, dim=-1)
+    refh = torch.nn.functional.silu(g) * u
+    for e in range(E):
+        n = int(counts[e])
+        if n:
+            _close(h[e, :n], refh[e, :n], tol=3e-2)
+            _close(pre[e, :n], ref[e, :n])
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(6)
+    x = _rand(4, 64, 256).requires_grad_()
+    w = _rand(512, 256, scale=0.05).requires_grad_()
+    r = _rand(4, 64, 512).requires_grad_()
+    y = ops.linear(x, w, residual=r)
+    gy = _rand(4, 64, 512)
+    y.backward(gy)
+    xf, wf, rf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), r.detach().float().requires_grad_()
+    yf = torch.nn.functional.linear(xf, wf) + rf
+    yf.backward(gy.float())
+    _close(y, yf)
+    _close(x.grad, xf.grad)
+    _close(w.grad, wf.grad)
+    _close(r.grad, rf.grad)

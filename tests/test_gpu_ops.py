@@ -1,0 +1,263 @@
+"""Element-wise, loss, optimiser and MoE kernels against the PyTorch fp32 definitions."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from adaptivetrainingsystem_b200 import ops
+from adaptivetrainingsystem_b200.ops import moe as M
+from adaptivetrainingsystem_b200.ops import functional as FN
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, tol=2e-2, what=""):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"{what}: max err {err} vs scale {denom}"
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (37, 4096), (16, 8192)])
+def test_rmsnorm_fwd_bwd(rows, cols):
+    torch.manual_seed(0)
+    x = _rand(rows, cols).requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-6)
+    gy = _rand(rows, cols)
+    y.backward(gy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = ops.rms_norm_reference(xf, wf, 1e-6)
+    yf.backward(gy.float())
+    _close(y, yf, what="y")
+    _close(x.grad, xf.grad, what="dx")
+    _close(w.grad, wf.grad, tol=3e-2, what="dw")
+
+
+def test_rmsnorm_residual():
+    torch.manual_seed(1)
+    x, r = _rand(128, 1024), _rand(128, 1024)
+    w = torch.ones(1024, device=DEV, dtype=torch.bfloat16)
+    y, s = ops.rms_norm(x, w, 1e-6, residual=r)
+    sf = (x.float() + r.float()).to(torch.bfloat16)
+    _close(s, sf, tol=1e-2)
+    _close(y, ops.rms_norm_reference(sf.float(), w.float(), 1e-6))
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_rope_packed(d):
+    torch.manual_seed(2)
+    B, L, nq, nkv = 2, 96, 4, 2
+    cos, sin = ops.rope_tables(256, d, device=DEV)
+    qkv = _rand(B, L, (nq + 2 * nkv) * d)
+    ref = ops.rope_packed(qkv.float(), cos, sin, nq, nkv, d, pos_offset=5)
+    leaf = qkv.clone().requires_grad_()
+    out = ops.rope_packed(leaf * 1.0, cos, sin, nq, nkv, d, pos_offset=5)
+    _close(out, ref)
+    g = _rand(*out.shape)
+    out.backward(g)
+    leaf_f = qkv.float().clone().requires_grad_()
+    ops.rope_packed(leaf_f * 1.0, cos, sin, nq, nkv, d, pos_offset=5).backward(g.float())
+    _close(leaf.grad, leaf_f.grad)
+
+
+def test_swiglu_fwd_bwd():
+    torch.manual_seed(3)
+    gu = _rand(300, 2 * 704).requires_grad_()
+    h = ops.swiglu(gu)
+    g = _rand(300, 704)
+    h.backward(g)
+    guf = gu.detach().float().requires_grad_()
+    hf = ops.swiglu_reference(guf)
+    hf.backward(g.float())
+    _close(h, hf)
+    _close(gu.grad, guf.grad)
+
+
+def test_swiglu_mlp_autograd():
+    torch.manual_seed(4)
+    x = _rand(256, 256).requires_grad_()
+    w1 = _rand(2 * 384, 256, scale=0.05).requires_grad_()
+    w2 = _rand(256, 384, scale=0.05).requires_grad_()
+    y = ops.swiglu_mlp(x, w1, w2)
+    g = _rand(256, 256)
+    y.backward(g)
+    xf, w1f, w2f = [t.detach().float().requires_grad_() for t in (x, w1, w2)]
+    yf = ops.swiglu_mlp(xf, w1f, w2f)
+    yf.backward(g.float())
+    _close(y, yf, tol=3e-2)
+    _close(x.grad, xf.grad, tol=3e-2)
+    _close(w1.grad, w1f.grad, tol=3e-2)
+    _close(w2.grad, w2f.grad, tol=3e-2)
+
+
+def test_embedding_fwd_bwd():
+    torch.manual_seed(5)
+    table = _rand(500, 256).requires_grad_()
+    ids = torch.randint(-3, 510, (4, 64), device=DEV)
+    out = ops.embedding(ids, table, 2.0)
+    g = _rand(4, 64, 256)
+    out.backward(g)
+    tf = table.detach().float().requires_grad_()
+    of = ops.embedding(ids, tf, 2.0)
+    of.backward(g.float())
+    _close(out, of)
+    _close(table.grad, tf.grad)
+
+
+@pytest.mark.parametrize("V", [1000, 32000, 8192 + 8])
+def test_cross_entropy(V):
+    torch.manual_seed(6)
+    T = 200
+    logits = _rand(T, V, scale=2.0).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::7] = -100
+    wts = torch.rand(T, device=DEV) + 0.5
+    loss, raw, nv, acc = ops.cross_entropy(logits, labels, wts)
+    loss.backward()
+    lf = logits.detach().float().requires_grad_()
+    lossf, rawf, nvf, accf = ops.cross_entropy_reference(lf, labels, wts)
+    lossf.backward()
+    assert abs(loss.item() - lossf.item()) < 2e-2 * abs(lossf.item())
+    assert abs(raw.item() - rawf.item()) < 2e-2 * abs(rawf.item())
+    assert int(nv) == int(nvf)
+    assert abs(acc.item() - accf.item()) < 1e-6
+    _close(logits.grad, lf.grad, tol=3e-2)
+
+
+def test_linear_cross_entropy():
+    torch.manual_seed(7)
+    T, H, V = 300, 256, 2048
+    h = _rand(T, H).requires_grad_()
+    w = _rand(V, H, scale=0.05).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[:10] = -100
+    loss, raw, nv, acc = ops.linear_cross_entropy(h, w, labels, None, -100, chunk_rows=128)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lossf, *_ = ops.cross_entropy_reference(F.linear(hf, wf), labels, None)
+    lossf.backward()
+    assert abs(loss.item() - lossf.item()) < 1e-2 * abs(lossf.item())
+    _close(h.grad, hf.grad, tol=3e-2)
+    _close(w.grad, wf.grad, tol=3e-2)
+
+
+def test_adamw_and_clip():
+    torch.manual_seed(8)
+    n = 10007 * 8
+    p = _rand(n)
+    master = p.float().clone()
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    g = _rand(n, scale=3.0)
+    hyper = torch.tensor([1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0], device=DEV)
+    ss = torch.zeros(1, device=DEV)
+    ops.sumsq(g, ss)
+    assert abs(ss.item() - g.float().pow(2).sum().item()) < 1e-3 * ss.item()
+    state = torch.zeros(4, device=DEV)
+    ops.clip_coef(ss, state, 0.5, 1.0)
+    norm = g.float().norm().item() * 0.5
+    assert abs(state[1].item() - norm) < 1e-3 * norm
+    coef = min(1.0, 1.0 / (norm + 1e-6)) * 0.5
+    assert abs(state[0].item() - coef) < 1e-4 * coef
+    mref, m2, v2 = master.clone(), m.clone(), v.clone()
+    pref = p.clone()
+    ops.adamw_step(master, m, v, g, p, hyper, state, 1.0)
+    # reference on CPU tensors goes through the PyTorch body
+    mc, m2c, v2c, gc, pc = mref.cpu(), m2.cpu(), v2.cpu(), g.cpu().float(), pref.cpu().float()
+    ops.adamw_step(mc, m2c, v2c, gc, pc, hyper.cpu(), state.cpu(), 1.0)
+    _close(master, mc.to(DEV), tol=1e-4)
+    _close(m, m2c.to(DEV), tol=1e-4)
+    _close(v, v2c.to(DEV), tol=1e-4)
+    _close(p, mc.to(DEV), tol=1e-2)
+
+
+def test_gate_topk_plan():
+    torch.manual_seed(9)
+    T, H, E, k = 1000, 512, 8, 2
+    x = _rand(T, H).requires_grad_()
+    wg = _rand(E, H, scale=0.05).requires_grad_()
+    logits = M.gate_logits(x, wg)
+    ref = F.linear(x.detach().float(), wg.detach().float())
+    _close(logits, ref, tol=1e-2)
+    gl = torch.randn(T, E, device=DEV)
+    logits.backward(gl)
+    xf, wf = x.detach().float().requires_grad_(), wg.detach().float().requires_grad_()
+    F.linear(xf, wf).backward(gl)
+    _close(x.grad, xf.grad)
+    _close(wg.grad, wf.grad)
+    with torch.no_grad():
+        idx, w, _ = M.route(ref, k, temperature=0.7)
+        probs = torch.softmax(ref / 0.7, -1)
+        wr, ir = torch.topk(probs, k, -1)
+        wr = wr / wr.sum(-1, keepdim=True)
+        assert torch.equal(idx.long(), ir)
+        _close(w, wr, tol=1e-4)
+    cap = 256
+    pos, counts, totals = M.plan_slots(idx, E, cap)
+    pos_r, counts_r, totals_r = M.plan_slots(idx.cpu(), E, cap)
+    assert torch.equal(pos.cpu(), pos_r) and torch.equal(counts.cpu(), counts_r) and torch.equal(totals.cpu(), totals_r)
+
+
+def test_moe_ffn_fwd_bwd():
+    torch.manual_seed(10)
+    T, H, I, E, k = 700, 256, 384, 4, 2
+    x = _rand(T, H).requires_grad_()
+    w1 = _rand(E, 2 * I, H, scale=0.05).requires_grad_()
+    w2 = _rand(E, H, I, scale=0.05).requires_grad_()
+    logits = torch.randn(T, E, device=DEV)
+    probs = torch.softmax(logits, -1)
+    wv, idx = torch.topk(probs, k, -1)
+    wv = (wv / wv.sum(-1, keepdim=True)).requires_grad_()
+    idx = idx.to(torch.int32)
+    cap = M.expert_capacity(T, E, k, 1.0)  # tight capacity: some slots are dropped
+    out, totals = M.moe_ffn(x, idx, wv, w1, w2, cap)
+    g = _rand(T, H)
+    out.backward(g)
+    xf, w1f, w2f, wvf = [t.detach().float().requires_grad_() for t in (x, w1, w2, wv)]
+    outf, _ = M.moe_ffn(xf, idx, wvf, w1f, w2f, cap)
+    outf.backward(g.float())
+    ref2 = M.moe_ffn_reference(x.detach().float(), idx, wv.detach(), w1.detach().float(), w2.detach().float(), cap)
+    _close(outf, ref2, tol=1e-3, what="oracle")
+    _close(out, outf, tol=3e-2, what="out")
+    _close(x.grad, xf.grad, tol=3e-2, what="dx")
+    _close(w1.grad, w1f.grad, tol=3e-2, what="dw1")
+    _close(w2.grad, w2f.grad, tol=3e-2, what="dw2")
+    _close(wv.grad, wvf.grad, tol=3e-2, what="dwv")
+    assert int(totals.sum()) == T * k
+
+
+def test_mod_select():
+    from adaptivetrainingsystem_b200.models.transformer import _mod_select_cuda
+    torch.manual_seed(11)
+    s = torch.randn(3, 512, device=DEV)
+    sel = _mod_select_cuda(s, 64)
+    ref = torch.topk(s, 64, dim=1).indices.sort(dim=1).values
+    assert torch.equal(sel.long(), ref)
+
+
+def test_model_bf16_matches_fp32_oracle():
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    torch.manual_seed(12)
+    cfg = ModelConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=512,
+                      seq_length=128, use_moe=True, num_experts=4, moe_top_k=2, tie_word_embeddings=False, capacity_factor=4.0)
+    m32 = DeepSeekTransformer(cfg).to(DEV)
+    m16 = DeepSeekTransformer(cfg).to(DEV, torch.bfloat16)
+    m16.load_state_dict(m32.state_dict())
+    m32.load_state_dict(m16.state_dict())  # identical (bf16-rounded) weights on both sides
+    ids = torch.randint(0, 1024, (2, 128), device=DEV)
+    labels = torch.roll(ids, -1, 1)
+    o16 = m16.forward_loss(ids, labels)
+    o32 = m32.forward_loss(ids, labels)
+    assert abs(o16["loss"].item() - o32["loss"].item()) < 3e-2 * abs(o32["loss"].item())
+    o16["loss"].backward()
+    o32["loss"].backward()
+    g16 = m16.layers[0].self_attn.qkv_proj.grad
+    g32 = m32.layers[0].self_attn.qkv_proj.grad
+    _close(g16, g32, tol=0.15, what="qkv grad")
