@@ -79,7 +79,9 @@ class _RMSNormFn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         rows, cols = x2.shape
-        y = torch.empty_like(x2)
+        # outputs are allocated in their final shape: returning a view made inside a Function would forbid
+        # in-place consumers downstream
+        y = torch.empty(shape, dtype=x.dtype, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         summed = None
         r2 = None
@@ -87,15 +89,15 @@ class _RMSNormFn(torch.autograd.Function):
             r2 = residual.reshape(-1, cols)
             if not r2.is_contiguous():
                 r2 = r2.contiguous()
-            summed = torch.empty_like(x2)
+            summed = torch.empty(shape, dtype=x.dtype, device=x.device)
         _CK(_L().ats_rmsnorm_fwd(_P(x2), _P(r2), _P(w), _P(y), _P(summed), _P(rstd), rows, cols, eps, _S(x.device)),
             "rmsnorm_fwd")
-        ctx.save_for_backward(summed if summed is not None else x2, w, rstd)
+        ctx.save_for_backward(summed.view(rows, cols) if summed is not None else x2, w, rstd)
         ctx.has_res = residual is not None
         ctx.shape = shape
         if residual is not None:
-            return y.view(shape), summed.view(shape)
-        return y.view(shape)
+            return y, summed
+        return y
 
     @staticmethod
     def backward(ctx, dy, dsum=None):
@@ -163,11 +165,12 @@ class _LinearFn(torch.autograd.Function):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         r2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
-        y = G.gemm_nt(x2, w, add=r2)
+        y = torch.empty(*shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+        G.gemm_nt(x2, w, out=y.view(-1, w.shape[0]), add=r2)
         ctx.save_for_backward(x2, w)
         ctx.has_res = residual is not None
         ctx.shape = shape
-        return y.view(*shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -204,11 +207,11 @@ class _SwiGLUFn(torch.autograd.Function):
         shape = gu.shape
         g2 = gu.reshape(-1, shape[-1])
         inter = shape[-1] // 2
-        h = torch.empty(g2.shape[0], inter, dtype=gu.dtype, device=gu.device)
+        h = torch.empty(*shape[:-1], inter, dtype=gu.dtype, device=gu.device)
         _CK(_L().ats_swiglu_fwd(_P(g2), _P(h), g2.shape[0], inter, _S(gu.device)), "swiglu_fwd")
         ctx.save_for_backward(g2)
         ctx.shape = shape
-        return h.view(*shape[:-1], inter)
+        return h
 
     @staticmethod
     def backward(ctx, dh):
@@ -239,11 +242,12 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         pre = torch.empty(x2.shape[0], w1.shape[0], dtype=x.dtype, device=x.device) if need_bwd else None
         h = G.gemm_nt_swiglu(x2, w1, pre_act=pre)
         r2 = residual.reshape(-1, w2.shape[0]) if residual is not None else None
-        y = G.gemm_nt(h, w2, add=r2)
+        y = torch.empty(*shape[:-1], w2.shape[0], dtype=x.dtype, device=x.device)
+        G.gemm_nt(h, w2, out=y.view(-1, w2.shape[0]), add=r2)
         ctx.save_for_backward(x2, w1, w2, pre)
         ctx.shape = shape
         ctx.has_res = residual is not None
-        return y.view(*shape[:-1], w2.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -338,12 +342,12 @@ class _EmbeddingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ids, table, scale):
         flat = ids.reshape(-1).contiguous()
-        out = torch.empty(flat.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+        out = torch.empty(*ids.shape, table.shape[1], dtype=table.dtype, device=table.device)
         _CK(_L().ats_embedding_fwd(_P(flat), _P(table), _P(out), flat.numel(), table.shape[1], table.shape[0], scale,
                                    _S(table.device)), "embedding_fwd")
         ctx.save_for_backward(flat, table)
         ctx.scale = scale
-        return out.view(*ids.shape, table.shape[1])
+        return out
 
     @staticmethod
     def backward(ctx, dout):
@@ -526,7 +530,7 @@ def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causa
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True, q_offset: int = 0,
               key_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-    from . import attention as A
+    from . import attn as A
     if _lib.use_cuda_kernels(q) and key_mask is None and A.supported(q, k, v, causal, q_offset):
         return A.flash_attention(q, k, v, causal, q_offset)
     return attention_reference(q, k, v, causal, q_offset, key_mask)

@@ -35,6 +35,7 @@ def _fn():
             _c_int, _c_int, _vp,  # groups ragged counts
             _c_int, _c_int, _c_int, _c_int,  # group coordinate shifts
             _c_ll, _c_ll, _c_ll,  # d_gs c_gs aux_gs
+            _c_int, _c_int, _c_int, _vp,  # b_div k_segs seg_stride d_table
             _vp, _c_int, _vp]  # status, max_ctas, stream
         _configured = True
     return lib.ats_gemm_bf16
@@ -42,12 +43,14 @@ def _fn():
 
 def _raw(a, a_rows, a_cols, lda, a_mn, b, b_rows, b_cols, ldb, b_mn, d, ldd, c, ldc, aux, ldaux,
          M, N, K, alpha=1.0, beta=0, epilogue=EPI_STORE, up_offset=0, groups=1, ragged=0, counts=None,
-         a_gs_mn=0, a_gs_k=0, b_gs_mn=0, b_gs_k=0, d_gs=0, c_gs=0, aux_gs=0, max_ctas=0):
+         a_gs_mn=0, a_gs_k=0, b_gs_mn=0, b_gs_k=0, d_gs=0, c_gs=0, aux_gs=0, max_ctas=0,
+         b_div=1, k_segs=1, seg_stride=0, d_table=None):
     st = _lib.status_tensor(a.device)
     err = _fn()(_lib.ptr(a), a_rows, a_cols, lda, a_mn, _lib.ptr(b), b_rows, b_cols, ldb, b_mn,
                 _lib.ptr(d), ldd, _lib.ptr(c), ldc, _lib.ptr(aux), ldaux,
                 M, N, K, alpha, beta, epilogue, up_offset, groups, ragged, _lib.ptr(counts),
                 a_gs_mn, a_gs_k, b_gs_mn, b_gs_k, d_gs, c_gs, aux_gs,
+                b_div, k_segs, seg_stride, _lib.ptr(d_table),
                 _lib.ptr(st), max_ctas, _lib.stream_ptr(a.device))
     _lib.check(err, "ats_gemm_bf16")
 
@@ -169,13 +172,17 @@ def _ref_mask(counts: torch.Tensor, cap: int) -> torch.Tensor:
 
 
 def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: bool = False,
-               pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x[E,C,K] · w[E,N,K]^T -> [E,C,N] (or [E,C,N/2] through SwiGLU) for the first counts[e] rows of every
-    expert; rows beyond the padded count are left untouched."""
-    E, C, K = x.shape
+               pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, b_div: int = 1,
+               d_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[G,C,K] · w[E,N,K]^T -> [G,C,N] (or [G,C,N/2] through SwiGLU) for the first counts[g] rows of every
+    group; group g uses weight g // b_div (G = E * b_div: several token blocks per expert, one per source rank).
+    Rows beyond the padded count are left untouched.  ``d_table`` (int64 [G]) redirects the output of group g to
+    an arbitrary base address (a buffer on a peer GPU)."""
+    Gn, C, K = x.shape
     N = w.shape[1]
     if not _lib.use_cuda_kernels(x):
-        y = torch.einsum("eck,enk->ecn", x.float(), w.float()).to(x.dtype)
+        wx = w.repeat_interleave(b_div, dim=0) if b_div > 1 else w
+        y = torch.einsum("eck,enk->ecn", x.float(), wx.float()).to(x.dtype)
         mask = _ref_mask(counts, C)[..., None]
         y = torch.where(mask, y, torch.zeros_like(y))
         if swiglu:
@@ -189,42 +196,46 @@ def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: b
         return y
     assert x.is_contiguous() and w.is_contiguous() and C % 128 == 0
     n_out = N // 2 if swiglu else N
-    if out is None:
-        out = torch.empty(E, C, n_out, dtype=x.dtype, device=x.device)
-    _raw(x, E * C, K, K, 0, w, E * N, K, K, 0, out, n_out, None, 0, pre_act, N if pre_act is not None else 0,
+    if out is None and d_table is None:
+        out = torch.empty(Gn, C, n_out, dtype=x.dtype, device=x.device)
+    _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 0, out, n_out, None, 0, pre_act, N if pre_act is not None else 0,
          C, n_out, K, epilogue=EPI_SWIGLU if swiglu else EPI_STORE, up_offset=N // 2 if swiglu else 0,
-         groups=E, ragged=1, counts=counts, a_gs_mn=C, b_gs_mn=N, d_gs=C * n_out,
-         aux_gs=C * N if pre_act is not None else 0)
+         groups=Gn, ragged=1, counts=counts, a_gs_mn=C, b_gs_mn=N, d_gs=C * n_out,
+         aux_gs=C * N if pre_act is not None else 0, b_div=b_div, d_table=d_table)
     return out
 
 
-def grouped_nn(dy: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """dy[E,C,N] · w[E,N,K] -> [E,C,K] (input gradient of grouped_nt)."""
-    E, C, N = dy.shape
+def grouped_nn(dy: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None,
+               b_div: int = 1, d_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dy[G,C,N] · w[E,N,K] -> [G,C,K] (input gradient of grouped_nt)."""
+    Gn, C, N = dy.shape
     K = w.shape[2]
     if not _lib.use_cuda_kernels(dy):
-        y = torch.einsum("ecn,enk->eck", dy.float(), w.float()).to(dy.dtype)
+        wx = w.repeat_interleave(b_div, dim=0) if b_div > 1 else w
+        y = torch.einsum("ecn,enk->eck", dy.float(), wx.float()).to(dy.dtype)
         y = torch.where(_ref_mask(counts, C)[..., None], y, torch.zeros_like(y))
         if out is not None:
             out.copy_(y)
             return out
         return y
     assert dy.is_contiguous() and w.is_contiguous() and C % 128 == 0
-    if out is None:
-        out = torch.empty(E, C, K, dtype=dy.dtype, device=dy.device)
-    _raw(dy, E * C, N, N, 0, w, E * N, K, K, 1, out, K, None, 0, None, 0, C, K, N,
-         groups=E, ragged=1, counts=counts, a_gs_mn=C, b_gs_k=N, d_gs=C * K)
+    if out is None and d_table is None:
+        out = torch.empty(Gn, C, K, dtype=dy.dtype, device=dy.device)
+    _raw(dy, Gn * C, N, N, 0, w, w.shape[0] * N, K, K, 1, out, K, None, 0, None, 0, C, K, N,
+         groups=Gn, ragged=1, counts=counts, a_gs_mn=C, b_gs_k=N, d_gs=C * K, b_div=b_div, d_table=d_table)
     return out
 
 
 def grouped_tn(dy: torch.Tensor, x: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None,
-               accumulate: bool = False) -> torch.Tensor:
-    """dy[E,C,N]^T · x[E,C,K] -> [E,N,K] (weight gradient of grouped_nt), reducing over the used rows."""
-    E, C, N = dy.shape
+               accumulate: bool = False, k_segs: int = 1) -> torch.Tensor:
+    """dy[G,C,N]^T · x[G,C,K] -> [G / k_segs, N, K] (weight gradient of grouped_nt): expert e reduces over the used
+    rows of its k_segs consecutive token blocks."""
+    Gn, C, N = dy.shape
     K = x.shape[2]
+    E = Gn // k_segs
     if not _lib.use_cuda_kernels(dy):
         mask = _ref_mask(counts, C)[..., None].float()
-        r = torch.einsum("ecn,eck->enk", dy.float() * mask, x.float() * mask)
+        r = torch.einsum("ecn,eck->enk", (dy.float() * mask).reshape(E, k_segs * C, N), (x.float() * mask).reshape(E, k_segs * C, K))
         if out is not None:
             if accumulate:
                 r = r + out.float()
@@ -235,7 +246,7 @@ def grouped_tn(dy: torch.Tensor, x: torch.Tensor, counts: torch.Tensor, out: Opt
     if out is None:
         out = torch.empty(E, N, K, dtype=dy.dtype, device=dy.device)
         accumulate = False
-    _raw(dy, E * C, N, N, 1, x, E * C, K, K, 1, out, K, out if accumulate else None, K, None, 0, N, K, C,
+    _raw(dy, Gn * C, N, N, 1, x, Gn * C, K, K, 1, out, K, out if accumulate else None, K, None, 0, N, K, C,
          epilogue=EPI_ADDC if accumulate else EPI_STORE, groups=E, ragged=2, counts=counts,
-         a_gs_k=C, b_gs_k=C, d_gs=N * K, c_gs=N * K)
+         a_gs_k=k_segs * C, b_gs_k=k_segs * C, d_gs=N * K, c_gs=N * K, k_segs=k_segs, seg_stride=C)
     return out

@@ -1,0 +1,148 @@
+"""Symmetric peer memory and the device-side flag barrier.
+
+Every rank allocates the same buffer with ``cudaMalloc`` inside the native library, publishes its CUDA IPC handle
+through ``torch.distributed`` (the plumbing), and opens the handles of its peers; kernels then receive the table of
+peer pointers and move data over NVLink / NVSwitch with plain loads and stores.  No collective library call is
+involved after set-up, and no cluster-multicast load is ever issued on peer memory.
+
+Failure handling: the barrier kernel spins on flags for at most a second; when a peer never arrives it sets the
+library status word, and :func:`adaptivetrainingsystem_b200.ops.check_status` turns that into a ``KernelError``
+on the host -- the GPU context stays usable.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+_vp, _c_int, _c_ll, _c_f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+_sig = False
+
+
+def _L():
+    global _sig
+    lib = _lib.cuda_lib()
+    if not _sig:
+        def sig(name, *args):
+            f = getattr(lib, name)
+            f.restype = _c_int
+            f.argtypes = list(args)
+        sig("ats_ipc_alloc", ctypes.c_ulonglong, ctypes.POINTER(_vp), ctypes.c_char_p)
+        sig("ats_ipc_open", ctypes.c_char_p, ctypes.POINTER(_vp))
+        sig("ats_ipc_close", _vp)
+        sig("ats_ipc_free", _vp)
+        sig("ats_peer_barrier", ctypes.POINTER(_vp), ctypes.POINTER(_vp), _vp, _c_int, _c_int, _c_int, _vp, _vp)
+        sig("ats_peer_reduce_shard", ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _vp, _c_int, _vp)
+        sig("ats_clip_coef_slots", _vp, _c_int, _c_f, _c_f, _vp, _vp)
+        sig("ats_adamw_push", _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _c_f, _vp)
+        sig("ats_peer_copy", _vp, _vp, _c_ll, _c_int, _vp)
+        _sig = True
+    return lib
+
+
+class _RawCuda:
+    """Minimal ``__cuda_array_interface__`` carrier so torch can wrap a raw device pointer without copying."""
+
+    def __init__(self, ptr: int, nbytes: int, owner=None):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+def wrap_pointer(ptr: int, nbytes: int, device: torch.device, owner=None) -> torch.Tensor:
+    return torch.as_tensor(_RawCuda(ptr, nbytes, owner), device=device)
+
+
+class SymmetricBuffer:
+    """Same-sized buffer on every rank of ``group``.  ``ptrs[i]`` is the address of rank i's copy in THIS process."""
+
+    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        lib = _L()
+        local = _vp()
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.ats_ipc_alloc(self.nbytes, ctypes.byref(local), handle), "ipc_alloc")
+        self.local_ptr = int(local.value)
+        self.ptrs: List[int] = [0] * self.world
+        self.ptrs[self.rank] = self.local_ptr
+        self._opened: List[int] = []
+        if self.world > 1:
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            for i, h in enumerate(handles):
+                if i == self.rank:
+                    continue
+                p = _vp()
+                _lib.check(lib.ats_ipc_open(h, ctypes.byref(p)), f"ipc_open(rank {i})")
+                self.ptrs[i] = int(p.value)
+                self._opened.append(int(p.value))
+        self._table = (_vp * self.world)(*[_vp(p) for p in self.ptrs])
+        self.bytes_view = wrap_pointer(self.local_ptr, self.nbytes, self.device, owner=self)
+
+    def table(self, offset_bytes: int = 0):
+        """ctypes array of the peers' base addresses (+ offset), for kernel launches."""
+        if offset_bytes == 0:
+            return self._table
+        return (_vp * self.world)(*[_vp(p + offset_bytes) for p in self.ptrs])
+
+    def tensor(self, dtype: torch.dtype, numel: Optional[int] = None, offset_bytes: int = 0) -> torch.Tensor:
+        es = torch.empty((), dtype=dtype).element_size()
+        n = (self.nbytes - offset_bytes) // es if numel is None else numel
+        return self.bytes_view[offset_bytes:offset_bytes + n * es].view(dtype)
+
+    def peer_tensor(self, rank: int, dtype: torch.dtype, numel: int, offset_bytes: int = 0) -> torch.Tensor:
+        """View of a peer's copy (debug / tests only; hot paths hand raw pointers to kernels)."""
+        es = torch.empty((), dtype=dtype).element_size()
+        return wrap_pointer(self.ptrs[rank] + offset_bytes, numel * es, self.device, owner=self).view(dtype)
+
+    def close(self) -> None:
+        lib = _L()
+        for p in self._opened:
+            lib.ats_ipc_close(_vp(p))
+        self._opened = []
+        if self.local_ptr:
+            lib.ats_ipc_free(_vp(self.local_ptr))
+            self.local_ptr = 0
+
+
+class PeerBarrier:
+    """Flag barrier across the ranks of a group, executed by a one-warp kernel on the caller's stream.  Optionally
+    carries one float from every rank to every rank (``slots`` then holds the ``world`` values)."""
+
+    def __init__(self, group=None, device: Optional[torch.device] = None):
+        self.group = group
+        self.buf = SymmetricBuffer(1024, group, device)  # [0:256) flags (int32[<=64]), [256:512) payload slots (float[<=64])
+        self.world, self.rank = self.buf.world, self.buf.rank
+        self.epoch = 0
+        self.flags = self.buf.tensor(torch.int32, 64, 0)
+        self.slots = self.buf.tensor(torch.float32, 64, 256)
+        self._flag_table = self.buf.table(0)
+        self._slot_table = self.buf.table(256)
+        if self.world > 1:
+            dist.barrier(group)  # every rank's flags are zeroed and mapped before the first device barrier
+
+    def __call__(self, payload: Optional[torch.Tensor] = None) -> None:
+        self.epoch += 1
+        st = _lib.status_tensor(self.buf.device)
+        _lib.check(_L().ats_peer_barrier(self._flag_table, self._slot_table if payload is not None else None,
+                                         _lib.ptr(payload), self.rank, self.world, self.epoch, _lib.ptr(st),
+                                         _lib.stream_ptr(self.buf.device)), "peer_barrier")
+
+
+def peers_available(group=None) -> bool:
+    """True when every pair of GPUs in the group can map each other's memory."""
+    if not torch.cuda.is_available() or not dist.is_initialized():
+        return False
+    n = torch.cuda.device_count()
+    me = torch.cuda.current_device()
+    ok = all(torch.cuda.can_device_access_peer(me, j) for j in range(n) if j != me)
+    t = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    return bool(t.item())

@@ -1,0 +1,238 @@
+// Peer-memory communication over NVLink / NVSwitch from inside kernels.
+//
+// * symmetric buffers: cudaMalloc + CUDA IPC handles, exchanged by the host through torch.distributed;
+// * a flag barrier kernel (release/acquire at system scope, bounded spin, optional one-float payload to every
+//   peer) -- all ranks launch it on their own GPU, it never waits on a kernel of the same GPU;
+// * fused gradient path: every rank pulls its shard of the gradient bucket from all peers with plain 16-byte
+//   loads, sums in fp32, keeps the reduced shard and its squared norm (reduce-scatter without a library call);
+// * fused update path: AdamW on the owned fp32 shard whose bf16 result is pushed with 16-byte stores into the
+//   parameter bucket of every peer (the all-gather happens inside the optimiser kernel).
+//
+// These replace the NCCL reduce-scatter / all-gather that DeepSpeed ZeRO, FSDP and the vendored LowLevelZero /
+// Gemini engines issue around their optimiser step (reference training/trainer.py:2125-2183,
+// backend/backend_fsdp.py:151-198, colossalai/zero/low_level/low_level_optim.py:370-449, 670-697).
+// No load or store here uses cluster multicast; all peer traffic is ld.global / st.global on mapped peer memory.
+#include "common.cuh"
+
+namespace ats {
+
+constexpr int MAX_PEERS = 16;
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// flags.p[r] = base of rank r's flag array (int[world]).  Thread t: optionally stores the payload into peer t's
+// payload slot [rank], releases epoch into peer t's flags[rank], then waits for flags[t] of its own array.
+__global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const float* payload_src, int rank, int world,
+                                    int epoch, int* status) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  if (payload_src) {
+    float v = *payload_src;
+    reinterpret_cast<float*>(payload_dst.p[t])[rank] = v;
+  }
+  __threadfence_system();
+  st_release_sys(reinterpret_cast<int*>(flags.p[t]) + rank, epoch);
+  const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + t;
+  const uint64_t t0 = globaltimer_ns();
+  while (ld_acquire_sys(mine) < epoch) {
+    if (globaltimer_ns() - t0 > ATS_WAIT_BUDGET_NS) {
+      if (status) atomicCAS(status, 0, kTimeoutPeerFlag);
+      return;
+    }
+    __nanosleep(64);
+  }
+  __threadfence_system();
+}
+
+// out32[i] = sum_p grads_p[offset + i]  (i < n, n % 8 == 0); partial[block] = sum of squares of this block's part.
+__global__ void __launch_bounds__(256)
+peer_reduce_shard_kernel(PeerPtrs grads, int world, int rank, long long offset, long long n, float* __restrict__ out32,
+                         float* __restrict__ partial) {
+  __shared__ float red[33];
+  float ss = 0.f;
+  const long long nvec = n >> 3;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
+    for (int q = 0; q < world; ++q) {
+      const int p = (rank + q) % world;  // start with the local copy, spread the remote reads over the peers
+      const uint4 a = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[p]) + offset)[v];
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+    reinterpret_cast<float4*>(out32)[2 * v] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    reinterpret_cast<float4*>(out32)[2 * v + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += acc[e] * acc[e];
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = ss;
+}
+
+__global__ void __launch_bounds__(256) sum_partials_kernel(const float* __restrict__ partial, int n, float* out, int accumulate) {
+  __shared__ float red[33];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) acc += partial[i];
+  acc = block_sum(acc, red);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + acc : acc;
+}
+
+// clip state from `world` per-rank squared sums (slots written by the peers through the barrier payload)
+__global__ void clip_coef_slots_kernel(const float* slots, int world, float pre_scale, float max_norm, float* state) {
+  float s = 0.f;
+  for (int i = 0; i < world; ++i) s += slots[i];
+  const float norm = sqrtf(s) * pre_scale;
+  const bool finite = isfinite(norm);
+  float coef = 1.f;
+  if (max_norm > 0.f && finite) coef = fminf(1.f, max_norm / (norm + 1e-6f));
+  state[0] = finite ? pre_scale * coef : 0.f;
+  state[1] = norm;
+  state[2] = finite ? 0.f : 1.f;
+}
+
+// AdamW on the owned shard with fp32 gradients; the bf16 result goes to params.p[q] + offset for every rank q.
+__global__ void __launch_bounds__(256)
+adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, const float* __restrict__ g32,
+                  PeerPtrs params, int world, int rank, long long offset, long long n, const float* __restrict__ hyper,
+                  const float* __restrict__ clip_state, float wd_mult) {
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4] * wd_mult, step = hyper[5];
+  float gscale = 1.f;
+  if (clip_state) {
+    if (clip_state[2] != 0.f) return;
+    gscale = clip_state[0];
+  }
+  const float bc1 = 1.f - __powf(b1, step), bc2 = 1.f - __powf(b2, step);
+  const float step_size = lr / bc1, inv_bc2_sqrt = rsqrtf(bc2);
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float pp[8], pm[8], pv[8], g[8];
+    *reinterpret_cast<float4*>(pp) = reinterpret_cast<float4*>(master)[2 * i];
+    *reinterpret_cast<float4*>(pp + 4) = reinterpret_cast<float4*>(master)[2 * i + 1];
+    *reinterpret_cast<float4*>(pm) = reinterpret_cast<float4*>(m)[2 * i];
+    *reinterpret_cast<float4*>(pm + 4) = reinterpret_cast<float4*>(m)[2 * i + 1];
+    *reinterpret_cast<float4*>(pv) = reinterpret_cast<float4*>(v)[2 * i];
+    *reinterpret_cast<float4*>(pv + 4) = reinterpret_cast<float4*>(v)[2 * i + 1];
+    *reinterpret_cast<float4*>(g) = reinterpret_cast<const float4*>(g32)[2 * i];
+    *reinterpret_cast<float4*>(g + 4) = reinterpret_cast<const float4*>(g32)[2 * i + 1];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ge = g[e] * gscale;
+      pm[e] = b1 * pm[e] + (1.f - b1) * ge;
+      pv[e] = b2 * pv[e] + (1.f - b2) * ge * ge;
+      const float denom = sqrtf(pv[e]) * inv_bc2_sqrt + eps;
+      pp[e] = pp[e] * (1.f - lr * wd) - step_size * pm[e] / denom;
+    }
+    reinterpret_cast<float4*>(master)[2 * i] = *reinterpret_cast<float4*>(pp);
+    reinterpret_cast<float4*>(master)[2 * i + 1] = *reinterpret_cast<float4*>(pp + 4);
+    reinterpret_cast<float4*>(m)[2 * i] = *reinterpret_cast<float4*>(pm);
+    reinterpret_cast<float4*>(m)[2 * i + 1] = *reinterpret_cast<float4*>(pm + 4);
+    reinterpret_cast<float4*>(v)[2 * i] = *reinterpret_cast<float4*>(pv);
+    reinterpret_cast<float4*>(v)[2 * i + 1] = *reinterpret_cast<float4*>(pv + 4);
+    const uint4 o = make_uint4(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]), pack_bf16x2(pp[4], pp[5]), pack_bf16x2(pp[6], pp[7]));
+    for (int q = 0; q < world; ++q) {
+      const int p = (rank + q) % world;
+      reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[p]) + offset)[i] = o;
+    }
+  }
+}
+
+// Plain peer copy (pull): dst[i] = src_peer[i], 16-byte vectors.  Used to stage a remote parameter shard locally.
+__global__ void __launch_bounds__(256) peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nvec) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+static PeerPtrs to_peers(void* const* host_ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? host_ptrs[i] : nullptr;
+  return pp;
+}
+
+}  // namespace ats
+
+using namespace ats;
+
+// ---- symmetric memory ----------------------------------------------------------------------------------
+ATS_API int ats_ipc_alloc(unsigned long long bytes, void** ptr, unsigned char* handle64) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return int(e);
+  e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) return int(e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e != cudaSuccess) return int(e);
+  static_assert(sizeof(h) == 64, "unexpected IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+ATS_API int ats_ipc_open(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return int(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+ATS_API int ats_ipc_close(void* ptr) { return int(cudaIpcCloseMemHandle(ptr)); }
+ATS_API int ats_ipc_free(void* ptr) { return int(cudaFree(ptr)); }
+
+// ---- kernels ------------------------------------------------------------------------------------------------
+// flags / payload_dst: host arrays of `world` device pointers (one per rank, peer-mapped).
+ATS_API int ats_peer_barrier(void* const* flags, void* const* payload_dst, const float* payload_src, int rank, int world,
+                             int epoch, int* status, void* stream) {
+  if (world > MAX_PEERS) return 1003;
+  PeerPtrs none = {};
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(flags, world),
+                                                                      payload_dst ? to_peers(payload_dst, world) : none,
+                                                                      payload_src, rank, world, epoch, status);
+  return int(cudaGetLastError());
+}
+
+// Reduce this rank's shard [offset, offset + n) of the gradient buckets of all ranks into out32 and its squared sum
+// into sumsq[0] (added when accumulate).  partial: >= 1184 floats of scratch.
+ATS_API int ats_peer_reduce_shard(void* const* grads, int world, int rank, long long offset, long long n, float* out32,
+                                  float* partial, float* sumsq, int accumulate, void* stream) {
+  if (world > MAX_PEERS || (n & 7) || (offset & 7)) return 1003;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  peer_reduce_shard_kernel<<<(unsigned)blocks, 256, 0, s>>>(to_peers(grads, world), world, rank, offset, n, out32, partial);
+  sum_partials_kernel<<<1, 256, 0, s>>>(partial, (int)blocks, sumsq, accumulate);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_clip_coef_slots(const float* slots, int world, float pre_scale, float max_norm, float* state, void* stream) {
+  clip_coef_slots_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(slots, world, pre_scale, max_norm, state);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_adamw_push(float* master, float* m, float* v, const float* g32, void* const* params, int world, int rank,
+                           long long offset, long long n, const float* hyper, const float* clip_state, float wd_mult,
+                           void* stream) {
+  if (world > MAX_PEERS || (n & 7) || (offset & 7)) return 1003;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  adamw_push_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(master, m, v, g32, to_peers(params, world),
+                                                                                   world, rank, offset, n, hyper, clip_state, wd_mult);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_peer_copy(const void* src, void* dst, long long bytes, int max_blocks, void* stream) {
+  if (bytes & 15) return 1003;
+  long long nvec = bytes >> 4;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  const long long cap = max_blocks > 0 ? max_blocks : 148 * 4;
+  if (blocks > cap) blocks = cap;
+  peer_copy_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src),
+                                                                                  static_cast<uint4*>(dst), nvec);
+  return int(cudaGetLastError());
+}

@@ -54,6 +54,10 @@ struct GemmArgs {
   int up_offset;         // SwiGLU: row offset of the "up" half inside B (= intermediate size)
   float alpha;
   int beta;              // kF32: accumulate into Df32
+  int b_div;             // B operand of group g belongs to weight g / b_div (several token blocks per expert)
+  int k_segs;            // ragged == 2: the reduction of group g runs over k_segs blocks of rows, seg_stride apart,
+  int seg_stride;        //              block s holding counts[g * k_segs + s] rows
+  void* const* d_table;  // optional per-group output base pointers (e.g. buffers on peer GPUs)
   int* status;
 };
 
@@ -68,7 +72,14 @@ __device__ __forceinline__ void group_extents(const GemmArgs& p, int g, int& mg,
   mg = p.M;
   kg = p.K;
   if (p.ragged == 1) mg = min(round_up_128(p.counts[g]), p.M);
-  if (p.ragged == 2) kg = min(round_up_128(p.counts[g]), p.K);
+  if (p.ragged == 2) {
+    kg = 0;
+    for (int s = 0; s < p.k_segs; ++s) kg += min(round_up_128(p.counts[g * p.k_segs + s]), p.K);
+  }
+}
+__device__ __forceinline__ int seg_iters_of(const GemmArgs& p, int g, int s, int k_iters) {
+  if (p.ragged != 2) return k_iters;
+  return min(round_up_128(p.counts[g * p.k_segs + s]), p.K) / BK;
 }
 
 __device__ __forceinline__ int tiles_n_of(const GemmArgs& p) {
@@ -82,9 +93,16 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   g_hint = g;
   int local = tile - prefix[g];
   int tn = tiles_n_of(p);
-  int mt = local / tn, nt = local - mt * tn;
   int mg, kg;
   group_extents(p, g, mg, kg);
+  // Rasterisation: panels of PANEL_N tile columns, rows fastest-varying across panels' columns, so that the ~148
+  // tiles in flight touch about as many rows of A as of B (keeps both operands L2-resident per wave).
+  constexpr int PANEL_N = 8;
+  const int tm = (mg + BM - 1) / BM;
+  const int panel = local / (PANEL_N * tm);
+  const int within = local - panel * PANEL_N * tm;
+  const int width = min(PANEL_N, tn - panel * PANEL_N);
+  const int mt = within / width, nt = panel * PANEL_N + (within - mt * width);
   t.g = g;
   t.m0 = mt * BM;
   t.n0 = nt * (p.epilogue == kSwiGLU ? 128 : BN);
@@ -155,8 +173,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint);
         const int a_mn_c = t.m0 + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
-        const int b_mn_c = t.n0 + p.b_gs_mn * t.g, b_k_c = p.b_gs_k * t.g;
+        const int gb = t.g / p.b_div;
+        const int b_mn_c = t.n0 + p.b_gs_mn * gb, b_k_c = p.b_gs_k * gb;
+        int seg = 0, seg_left = seg_iters_of(p, t.g, 0, t.k_iters), kpos = 0;
         for (int kb = 0; kb < t.k_iters; ++kb) {
+          while (seg_left == 0) {
+            ++seg;
+            seg_left = seg_iters_of(p, t.g, seg, t.k_iters);
+            kpos = 0;
+          }
           if (!mbar_wait_bounded(&empty[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmpty)) {
             ok = false;
             break;
@@ -166,7 +191,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           armed_phase = (armed_phase & ~(1u << stage)) | (uint32_t(phase) << stage);
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
-          const int k0 = kb * BK;
+          const int k0 = seg * p.seg_stride + kpos * BK;
+          ++kpos;
+          --seg_left;
           if (!p.a_mn) {
             tma_load_2d(a_dst, &map_a, &full[stage], a_k_c + k0, a_mn_c);  // box 64 x 128
           } else {
@@ -256,7 +283,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const bool row_ok = row < t.valid;
       const bool have_acc = t.k_iters > 0;
       if (p.epilogue == kSwiGLU) {
-        __nv_bfloat16* drow = p.D + p.d_gs * t.g + (long long)row * p.ldd;
+        __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
+        __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
         __nv_bfloat16* arow = p.aux ? p.aux + p.aux_gs * t.g + (long long)row * p.ldaux : nullptr;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -318,7 +346,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               }
             }
           } else {
-            __nv_bfloat16* drow = p.D + p.d_gs * t.g + (long long)row * p.ldd;
+            __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
+            __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
             const __nv_bfloat16* crow =
                 p.epilogue == kAddC ? p.C + p.c_gs * t.g + (long long)row * p.ldc : nullptr;
 #pragma unroll
@@ -414,11 +443,20 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
                           int groups, int ragged, const int* counts,
                           int a_gs_mn, int a_gs_k, int b_gs_mn, int b_gs_k,
                           long long d_gs, long long c_gs, long long aux_gs,
+                          int b_div, int k_segs, int seg_stride, void* const* d_table,
                           int* status, int max_ctas, void* stream) {
+  // The tensor-map encoder is a driver call: make sure this thread (autograd runs backward on its own threads)
+  // has the primary context bound before the first use.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
   if (groups < 1 || groups > MAX_GROUPS) return 1002;
   if ((N & 7) || (a_gs_mn & 7) || (a_gs_k & 7) || (b_gs_mn & 7) || (b_gs_k & 7) || (ldd & 7) || (d_gs & 7)) return 1003;
   if (epilogue == kSwiGLU && (b_mn || (up_offset & 7))) return 1004;
   if (ragged && !counts) return 1005;
+  if (b_div < 1 || k_segs < 1 || (seg_stride & 7) || (k_segs > 1 && ragged != 2)) return 1006;
   CUtensorMap ma, mb;
   int e;
   if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 2, 64, a_mn ? 64 : 128))) return e;
@@ -431,6 +469,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = static_cast<float*>(D);
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = a_mn; p.b_mn = b_mn; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
+  p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table;
 
   static bool attr_set = false;
   if (!attr_set) {

@@ -121,3 +121,40 @@ def test_linear_autograd_matches_reference():
     _close(x.grad, xf.grad)
     _close(w.grad, wf.grad)
     _close(r.grad, rf.grad)
+
+
+def test_grouped_expert_parallel_layout():
+    """Several token blocks per expert (one per source rank), K-segmented weight gradient, output pointer table."""
+    torch.manual_seed(7)
+    E, W, C, K, N = 2, 3, 128, 128, 256
+    Gn = E * W
+    counts = torch.tensor([128, 5, 0, 77, 128, 1], dtype=torch.int32, device=DEV)
+    mask = (torch.arange(C, device=DEV)[None, :] < counts[:, None]).unsqueeze(-1)
+    x = _rand(Gn, C, K) * mask
+    dy = _rand(Gn, C, N) * mask
+    w = _rand(E, N, K, scale=0.2)
+    wx = w.repeat_interleave(W, dim=0)
+    y = G.grouped_nt(x, w, counts, b_div=W)
+    ref = torch.einsum("eck,enk->ecn", x.float(), wx.float())
+    for g in range(Gn):
+        n = int(counts[g])
+        if n:
+            _close(y[g, :n], ref[g, :n])
+    dx = G.grouped_nn(dy, w, counts, b_div=W)
+    refdx = torch.einsum("ecn,enk->eck", dy.float(), wx.float())
+    for g in range(Gn):
+        n = int(counts[g])
+        if n:
+            _close(dx[g, :n], refdx[g, :n])
+    dw = G.grouped_tn(dy, x, counts, k_segs=W)
+    refdw = torch.einsum("ecn,eck->enk", dy.float().reshape(E, W * C, N), x.float().reshape(E, W * C, K))
+    _close(dw, refdw)
+    # pointer table: scatter the groups' outputs into a permuted buffer
+    target = torch.zeros(Gn, C, N, dtype=torch.bfloat16, device=DEV)
+    perm = [3, 0, 5, 1, 4, 2]
+    table = torch.tensor([target[perm[g]].data_ptr() for g in range(Gn)], dtype=torch.int64, device=DEV)
+    G.grouped_nt(x, w, counts, b_div=W, d_table=table)
+    for g in range(Gn):
+        n = int(counts[g])
+        if n:
+            _close(target[perm[g], :n], ref[g, :n])
