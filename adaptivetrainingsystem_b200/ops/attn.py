@@ -32,17 +32,22 @@ def supported(q, k, v, causal, q_offset) -> bool:
 
 
 def backend_for(q, k, causal=True, q_offset=0) -> str:
+    """"tcgen05" (own kernel) or "sdpa" (PyTorch library kernel) for these operands."""
     B, Lq, Hq, D = q.shape
     Lk = k.shape[1]
-    if _native_available() and D in (64, 128) and Lq % 128 == 0 and Lk % 128 == 0 and causal and Lq == Lk and q_offset == 0:
-        return "tcgen05"
+    if _native_available() and D in (64, 128) and Lq % 128 == 0 and causal and Lq == Lk and q_offset == 0:
+        from .attention_native import layout_ok
+        if layout_ok(q) and layout_ok(k):
+            return "tcgen05"
     return "sdpa"
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True, q_offset: int = 0) -> torch.Tensor:
     """q: [B, Lq, Hq, D]; k, v: [B, Lk, Hkv, D] -> [B, Lq, Hq, D]."""
     if backend_for(q, k, causal, q_offset) == "tcgen05":
-        from .attention_native import flash_attention_native
+        from .attention_native import flash_attention_native, layout_ok
+        if not layout_ok(v):
+            v = v.contiguous()
         return flash_attention_native(q, k, v)
     B, Lq, Hq, D = q.shape
     Lk, Hkv = k.shape[1], k.shape[2]

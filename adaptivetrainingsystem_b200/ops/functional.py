@@ -51,7 +51,7 @@ def _L():
         sig("ats_gate_bwd_dw", _vp, _vp, _vp, _c_int, _c_ll, _c_int, _c_int, _vp)
         sig("ats_topk_softmax", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _vp)
         sig("ats_plan_slots", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
-        sig("ats_dispatch_rows", _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
+        sig("ats_dispatch_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
         sig("ats_combine_rows", _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_slot_dot", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_mod_select", _vp, _vp, _c_int, _c_int, _c_int, _vp)

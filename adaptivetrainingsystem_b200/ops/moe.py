@@ -132,17 +132,18 @@ def _ptr_table(t: torch.Tensor) -> torch.Tensor:
 
 def dispatch(x: torch.Tensor, topk_idx: torch.Tensor, slot_pos: torch.Tensor, counts: torch.Tensor,
              num_experts: int, capacity: int, slot_scale: Optional[torch.Tensor] = None,
-             out: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None,
+             count_table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x[T,H] -> buf[E, C, H] with row ``slot_pos`` of expert ``topk_idx`` holding (scaled) x[t]."""
     T, H = x.shape
     k = topk_idx.shape[1]
-    if out is None:
+    if out is None and table is None:
         out = torch.empty(num_experts, capacity, H, dtype=x.dtype, device=x.device)
     if _lib.use_cuda_kernels(x):
         if table is None:
             table = _ptr_table(out)
-        _CK(_L().ats_dispatch_rows(_P(x), _P(topk_idx), _P(slot_pos), _P(slot_scale), _P(table), _P(counts), T * k, k, H,
-                                   num_experts, capacity, 1, _S(x.device)), "dispatch_rows")
+        _CK(_L().ats_dispatch_rows(_P(x), _P(topk_idx), _P(slot_pos), _P(slot_scale), _P(table), _P(counts),
+                                   _P(count_table), T * k, k, H, num_experts, capacity, 1, _S(x.device)), "dispatch_rows")
         return out
     out.zero_()
     flat_e = topk_idx.reshape(-1).long()

@@ -1,5 +1,222 @@
-"""Expert parallelism (placeholder until the peer-memory path lands in this file)."""
+"""Expert parallelism: every rank of the ``ep`` group owns ``E / W`` experts of each MoE layer and all ranks exchange
+routed tokens.
+
+Layout.  Source rank ``s`` routes its ``T`` tokens, ranks the (token, k) slots per expert in token order and keeps at
+most ``C`` of them per expert (per-source capacity, as DeepSpeed-MoE / the reference's vendored routers do,
+``colossalai/moe/routers.py:47-58``).  The owner of expert ``e`` holds a receive buffer ``[E_local, W, C, H]``: block
+``(e_local, s)`` is filled by source ``s``.  The grouped GEMM then runs over ``E_local * W`` row groups with one weight
+per ``W`` groups; outputs go back to the sources' ``[E, C, H]`` return buffers, where the combine kernel forms the
+weighted sum.
+
+Two transports with identical numerics:
+
+* **fused** (default on NVLink): the dispatch kernel writes token rows, pad rows and row counts straight into the
+  owner's receive buffer on the peer GPU; the down-projection GEMM's epilogue writes its output tiles straight into the
+  source rank's return buffer on the peer GPU; flag barriers (one warp, bounded wait) separate the phases.  Routing,
+  permutation, the grouped SwiGLU GEMMs and the all-to-all traffic are the same kernels -- no collective library call.
+* **nccl** (baseline, also what runs on CPU/Gloo): ``all_to_all_single`` on the capacity layout plus the same grouped
+  GEMMs -- what ColossalAI's ``SparseMLP`` does (``colossalai/moe/layers.py:221-249``, ``moe/_operation.py:132-135``).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import gemm as G
+from ..ops import moe as M
+from ..ops.functional import _L, _P, _S, _CK, _deliver_grad
 
 
-def attach_expert_parallel(model, mesh, cfg, use_fused=True):
-    raise NotImplementedError
+class _LayerBuffers:
+    """Per-layer exchange buffers (symmetric when fused)."""
+
+    def __init__(self, comm: "ExpertParallelComm", E: int, C: int, H: int, dtype: torch.dtype, device):
+        W, r = comm.W, comm.rank
+        El = E // W
+        self.E, self.El, self.C, self.H = E, El, C, H
+        n_recv = El * W * C * H
+        n_ret = E * C * H
+        es = torch.empty((), dtype=dtype).element_size()
+        if comm.fused:
+            from .peer import SymmetricBuffer
+            # one symmetric allocation: recv_x | ret_y | recv_g | ret_dx | counts
+            off = [0]
+            for n in (n_recv * es, n_ret * es, n_recv * es, n_ret * es, El * W * 4):
+                off.append(off[-1] + (n + 255) // 256 * 256)
+            self.sym = SymmetricBuffer(off[-1], comm.group, device)
+            s = self.sym
+            self.recv_x = s.tensor(dtype, n_recv, off[0]).view(El * W, C, H)
+            self.ret_y = s.tensor(dtype, n_ret, off[1]).view(E, C, H)
+            self.recv_g = s.tensor(dtype, n_recv, off[2]).view(El * W, C, H)
+            self.ret_dx = s.tensor(dtype, n_ret, off[3]).view(E, C, H)
+            self.counts = s.tensor(torch.int32, El * W, off[4])
+            e = torch.arange(E, dtype=torch.int64)
+            owner, el = e // El, e % El
+            base = torch.tensor(s.ptrs, dtype=torch.int64)
+            block = (el * W + r) * C * H * es
+            # where this rank's rows for expert e go (forward activations / backward gradients) and its count
+            self.t_disp_x = (base[owner] + off[0] + block).to(device)
+            self.t_disp_g = (base[owner] + off[2] + block).to(device)
+            self.t_count = (base[owner] + off[4] + (el * W + r) * 4).to(device)
+            # where the output of local group g = e_local * W + src goes on rank src
+            g = torch.arange(El * W, dtype=torch.int64)
+            gel, src = g // W, g % W
+            back = ((r * El + gel) * C * H) * es
+            self.t_ret_y = (base[src] + off[1] + back).to(device)
+            self.t_ret_dx = (base[src] + off[3] + back).to(device)
+        else:
+            self.sym = None
+            self.recv_x = torch.zeros(El * W, C, H, dtype=dtype, device=device)
+            self.ret_y = torch.zeros(E, C, H, dtype=dtype, device=device)
+            self.recv_g = torch.zeros(El * W, C, H, dtype=dtype, device=device)
+            self.ret_dx = torch.zeros(E, C, H, dtype=dtype, device=device)
+            self.counts = torch.zeros(El * W, dtype=torch.int32, device=device)
+
+
+class ExpertParallelComm:
+    def __init__(self, mesh, fused: bool = True):
+        self.mesh = mesh
+        self.group = mesh.group("ep")
+        self.W = mesh.ep_size
+        self.rank = mesh.coord.ep
+        self.fused = bool(fused) and torch.cuda.is_available()
+        self.barrier = None
+        if self.fused:
+            from .peer import PeerBarrier
+            self.barrier = PeerBarrier(self.group)
+        self._layers: Dict[Tuple[int, int, int, int], _LayerBuffers] = {}
+        self.bytes_dispatched = 0
+
+    def buffers(self, layer_idx: int, E: int, C: int, H: int, dtype, device) -> _LayerBuffers:
+        key = (layer_idx, E, C, H)
+        b = self._layers.get(key)
+        if b is None:
+            for k in [k for k in self._layers if k[0] == layer_idx]:
+                del self._layers[k]
+            b = _LayerBuffers(self, E, C, H, dtype, device)
+            self._layers[key] = b
+            if self.fused:
+                dist.barrier(self.group)  # all peers have mapped the new buffers
+        return b
+
+    # -- transports -----------------------------------------------------------------------------------------
+    def exchange_to_owners(self, send: torch.Tensor, recv: torch.Tensor) -> None:
+        """send [E, C, H] (by global expert = [W_owner, El, C, H]) -> recv [El * W_src, C, H]."""
+        W = self.W
+        El = send.shape[0] // W
+        tmp = torch.empty_like(send)
+        dist.all_to_all_single(tmp, send.contiguous(), group=self.group)  # tmp = [W_src, El, C, H]
+        recv.copy_(tmp.view(W, El, *send.shape[1:]).transpose(0, 1).reshape(recv.shape))
+
+    def exchange_to_sources(self, out: torch.Tensor, ret: torch.Tensor) -> None:
+        """out [El * W_src, C, H] -> ret [E, C, H] on every source."""
+        W = self.W
+        El = out.shape[0] // W
+        send = out.view(El, W, *out.shape[1:]).transpose(0, 1).contiguous()  # [W_src, El, C, H]
+        dist.all_to_all_single(ret.view(W, El, *out.shape[1:]), send, group=self.group)
+
+    def exchange_counts(self, counts: torch.Tensor, recv_counts: torch.Tensor) -> None:
+        W = self.W
+        El = counts.numel() // W
+        tmp = torch.empty_like(counts)
+        dist.all_to_all_single(tmp, counts.contiguous(), group=self.group)  # [W_src, El]
+        recv_counts.copy_(tmp.view(W, El).t().reshape(-1))
+
+
+class _EPMoEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topk_idx, topk_w, w1, w2, capacity, residual, comm: ExpertParallelComm, buf: _LayerBuffers):
+        T, H = x.shape
+        E, W, C = buf.E, comm.W, capacity
+        slot_pos, counts, totals = M.plan_slots(topk_idx, E, C)
+        if comm.fused:
+            M.dispatch(x, topk_idx, slot_pos, counts, E, C, table=buf.t_disp_x, count_table=buf.t_count)
+            comm.barrier()
+        else:
+            send = M.dispatch(x, topk_idx, slot_pos, counts, E, C)
+            comm.exchange_to_owners(send, buf.recv_x)
+            comm.exchange_counts(counts, buf.counts)
+        need_bwd = any(ctx.needs_input_grad)
+        pre = torch.empty(buf.El * W, C, w1.shape[1], dtype=x.dtype, device=x.device) if need_bwd else None
+        h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, pre_act=pre, b_div=W)
+        if comm.fused:
+            G.grouped_nt(h, w2, buf.counts, b_div=W, d_table=buf.t_ret_y)
+            comm.barrier()
+        else:
+            ye = G.grouped_nt(h, w2, buf.counts, b_div=W)
+            comm.exchange_to_sources(ye, buf.ret_y)
+        out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual)
+        ctx.save_for_backward(topk_idx, slot_pos, counts, topk_w, w1, w2, pre)
+        ctx.comm, ctx.buf, ctx.capacity, ctx.has_res = comm, buf, capacity, residual is not None
+        ctx.mark_non_differentiable(totals)
+        return out, totals
+
+    @staticmethod
+    def backward(ctx, dout, _dt=None):
+        topk_idx, slot_pos, counts, topk_w, w1, w2, pre = ctx.saved_tensors
+        comm, buf, C = ctx.comm, ctx.buf, ctx.capacity
+        E, W = buf.E, comm.W
+        T = dout.shape[0]
+        inter = w2.shape[2]
+        dout = dout.contiguous()
+        dw_topk = M.slot_dot(buf.ret_y, topk_idx, slot_pos, dout) if ctx.needs_input_grad[2] else None
+        scale = topk_w.contiguous().float()
+        if comm.fused:
+            M.dispatch(dout, topk_idx, slot_pos, counts, E, C, slot_scale=scale, table=buf.t_disp_g)
+            comm.barrier()
+        else:
+            send = M.dispatch(dout, topk_idx, slot_pos, counts, E, C, slot_scale=scale)
+            comm.exchange_to_owners(send, buf.recv_g)
+        dh = G.grouped_nn(buf.recv_g, w2, buf.counts, b_div=W)
+        if _lib.use_cuda_kernels(pre):
+            dgu = torch.empty_like(pre)
+            h = torch.empty(buf.El * W, C, inter, dtype=pre.dtype, device=pre.device)
+            _CK(_L().ats_swiglu_bwd(_P(pre), _P(dh), _P(dgu), _P(h), buf.El * W * C, inter, _S(pre.device)), "swiglu_bwd")
+        else:
+            g, u = pre.float().chunk(2, dim=-1)
+            s = torch.sigmoid(g)
+            dhf = dh.float()
+            dgu = torch.cat([dhf * u * (s + g * s * (1 - s)), dhf * g * s], dim=-1).to(pre.dtype)
+            h = (g * s * u).to(pre.dtype)
+        dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(buf.recv_g, h, buf.counts, out=out, accumulate=acc, k_segs=W))
+        dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, buf.recv_x, buf.counts, out=out, accumulate=acc, k_segs=W))
+        if comm.fused:
+            G.grouped_nn(dgu, w1, buf.counts, b_div=W, d_table=buf.t_ret_dx)
+            comm.barrier()
+        else:
+            dxe = G.grouped_nn(dgu, w1, buf.counts, b_div=W)
+            comm.exchange_to_sources(dxe, buf.ret_dx)
+        dx = M.combine(buf.ret_dx, topk_idx, slot_pos, None, T, None)
+        return dx, None, dw_topk, dw1, dw2, None, (dout if ctx.has_res else None), None, None
+
+
+class EPLayer:
+    """Bound to one MoE layer as ``layer.ep``; ``moe_ffn`` has the signature of the local MoE function."""
+
+    def __init__(self, comm: ExpertParallelComm, layer_idx: int, num_experts: int):
+        self.comm, self.layer_idx, self.num_experts = comm, layer_idx, num_experts
+
+    def moe_ffn(self, x, topk_idx, topk_w, w1, w2, capacity, residual=None):
+        buf = self.comm.buffers(self.layer_idx, self.num_experts, capacity, x.shape[1], x.dtype, x.device)
+        return _EPMoEFn.apply(x, topk_idx, topk_w, w1, w2, capacity, residual, self.comm, buf)
+
+
+def attach_expert_parallel(model, mesh, cfg=None, use_fused: bool = True):
+    """Wire every MoE layer of ``model`` to the expert-parallel transport of ``mesh``.  Returns the peer-memory
+    communicator for the optimiser step (``None`` on the NCCL/Gloo baseline path)."""
+    fused_ok = bool(use_fused) and torch.cuda.is_available()
+    if fused_ok:
+        from .peer import peers_available
+        fused_ok = peers_available(None)
+    if mesh.ep_size > 1:
+        comm = ExpertParallelComm(mesh, fused=fused_ok)
+        for layer in model.get_moe_layers():
+            layer.ep = EPLayer(comm, layer.layer_idx, layer.num_experts)
+        model._ep_comm = comm
+    if fused_ok and mesh.world > 1:
+        from .fused import FusedComm
+        return FusedComm(mesh)
+    return None

@@ -176,8 +176,6 @@ class ShardedEngine:
         lo, hi = b.owned_range()
         if b.W == 1 or b.group is None and not dist.is_initialized():
             return b.flat_grad[lo:hi]
-        if self.fused is not None and self.fused.can_reduce(b):
-            return self.fused.reduce_scatter(b) if b.shard_states else self.fused.all_reduce(b)
         if b.shard_states:
             out = b.flat_grad[lo:hi]
             if dist.get_backend(b.group) == "gloo":
@@ -190,9 +188,6 @@ class ShardedEngine:
 
     def _gather(self, b: Bucket) -> None:
         if b.W == 1 or not b.shard_states or not dist.is_initialized():
-            return
-        if self.fused is not None and self.fused.can_gather(b):
-            self.fused.all_gather(b)
             return
         lo, hi = b.owned_range()
         if dist.get_backend(b.group) == "gloo":
@@ -209,6 +204,12 @@ class ShardedEngine:
         self.step_count += 1
         self._hyper_host[5] = float(self.step_count)
         self.hyper[5] = float(self.step_count)
+        if self.fused is not None and self.fused.usable(self):
+            # reduce-scatter, norm, AdamW and all-gather done by peer-memory kernels (parallel/fused.py)
+            self.fused.step(self)
+            self.zero_grad()
+            self.last_grad_norm = self.clip_state[1]
+            return {"grad_norm": self.clip_state[1], "skipped": self.clip_state[2]}
         reduced = []
         first = True
         for b in self.buckets:

@@ -216,11 +216,13 @@ plan_slots_kernel(const int* __restrict__ topk_idx, int* __restrict__ slot_pos, 
 __global__ void __launch_bounds__(256)
 dispatch_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ topk_idx,
                      const int* __restrict__ slot_pos, const float* __restrict__ slot_scale,
-                     __nv_bfloat16* const* __restrict__ dst_base, const int* __restrict__ counts, long long slots, int k,
-                     int hidden, int experts, int capacity) {
+                     __nv_bfloat16* const* __restrict__ dst_base, const int* __restrict__ counts,
+                     int* const* __restrict__ count_dst, long long slots, int k, int hidden, int experts, int capacity) {
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int vpr = hidden >> 3;
+  // publish how many rows each expert receives from this rank (the expert's owner may be a peer GPU)
+  if (count_dst && blockIdx.x == 0 && threadIdx.x < experts) *count_dst[threadIdx.x] = counts[threadIdx.x];
   if (w < slots) {
     const int pos = slot_pos[w];
     if (pos < 0) return;
@@ -409,14 +411,15 @@ ATS_API int ats_plan_slots(const int* topk_idx, int* slot_pos, int* counts, int*
 }
 
 ATS_API int ats_dispatch_rows(const void* src, const int* topk_idx, const int* slot_pos, const float* slot_scale,
-                              void* const* dst_base, const int* counts, long long slots, int k, int hidden, int experts,
-                              int capacity, int zero_pad, void* stream) {
-  if (hidden & 7) return 1003;
+                              void* const* dst_base, const int* counts, void* const* count_dst, long long slots, int k,
+                              int hidden, int experts, int capacity, int zero_pad, void* stream) {
+  if ((hidden & 7) || experts > 256) return 1003;
   const long long warps = slots + (zero_pad ? (long long)experts * 128 : 0);
   if (warps == 0) return 0;
   dispatch_rows_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(src), topk_idx, slot_pos, slot_scale,
-      reinterpret_cast<__nv_bfloat16* const*>(dst_base), counts, slots, k, hidden, experts, capacity);
+      reinterpret_cast<__nv_bfloat16* const*>(dst_base), counts, reinterpret_cast<int* const*>(count_dst), slots, k, hidden,
+      experts, capacity);
   return int(cudaGetLastError());
 }
 

@@ -1,0 +1,96 @@
+"""Worker run under ``torch.distributed.run`` by test_gpu_multi.py (one rank per GPU, NCCL).
+
+Checks, on real peer memory: (a) flag barrier + payload, (b) fused reduce-scatter/AdamW/all-gather step == NCCL step,
+(c) fused expert-parallel dispatch/GEMM/combine == NCCL all-to-all path, forward and backward.
+NVLS is disabled by the launcher (NCCL_NVLS_ENABLE=0); the kernels here use plain peer loads/stores only."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from adaptivetrainingsystem_b200 import ops  # noqa: E402
+from adaptivetrainingsystem_b200.config import ModelConfig  # noqa: E402
+from adaptivetrainingsystem_b200.models import DeepSeekTransformer  # noqa: E402
+from adaptivetrainingsystem_b200.parallel import ProcessMesh, init_distributed  # noqa: E402
+from adaptivetrainingsystem_b200.parallel.expert_parallel import attach_expert_parallel  # noqa: E402
+from adaptivetrainingsystem_b200.parallel.zero import ShardedEngine  # noqa: E402
+
+
+def close(a, b, tol, what):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    den = b.abs().max().item() + 1e-9
+    assert err / den < tol, f"{what}: err {err} scale {den}"
+
+
+def build(cfg, mesh, fused, seed=0):
+    torch.manual_seed(seed)
+    full = DeepSeekTransformer(cfg)  # identical on every rank (CPU RNG)
+    sd = full.state_dict()
+    model = DeepSeekTransformer(cfg, ep_size=mesh.ep_size, ep_rank=mesh.coord.ep)
+    model.load_state_dict(sd)
+    model = model.to("cuda", torch.bfloat16)
+    comm = attach_expert_parallel(model, mesh, None, use_fused=fused)
+    eng = ShardedEngine(model, lr=1e-2, zero_stage=1, max_grad_norm=1.0, mesh=mesh, fused_comm=comm)
+    return model, eng
+
+
+def main():
+    rank, local, world = init_distributed()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    from adaptivetrainingsystem_b200.parallel.peer import PeerBarrier, peers_available
+    assert peers_available(None), "GPUs cannot map each other's memory"
+    # (a) barrier with payload
+    bar = PeerBarrier(None, dev)
+    val = torch.tensor([float(rank + 1)], device=dev)
+    bar(val)
+    torch.cuda.synchronize()
+    assert bar.slots[:world].tolist() == [float(i + 1) for i in range(world)], bar.slots[:world].tolist()
+    ops.check_status()
+
+    cfg = ModelConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=512,
+                      seq_length=128, use_moe=True, num_experts=4, moe_top_k=2, capacity_factor=2.0, tie_word_embeddings=False)
+    ep = 2 if world % 2 == 0 else 1
+    mesh = ProcessMesh(world, rank, ep_size=ep)
+    g = torch.Generator().manual_seed(7)
+    ids_all = torch.randint(0, 1024, (2 * world, 129), generator=g)
+    mine = ids_all[2 * rank:2 * rank + 2].to(dev)
+    results = {}
+    for name, fused in (("nccl", False), ("fused", True)):
+        model, eng = build(cfg, mesh, fused)
+        losses = []
+        for _ in range(3):
+            out = model.forward_loss(mine[:, :-1], mine[:, 1:])
+            out["loss"].backward()
+            eng.step()
+            losses.append(out["loss"].detach().float())
+        torch.cuda.synchronize()
+        ops.check_status()
+        results[name] = (torch.stack(losses).cpu(), {k: v.detach().float().cpu() for k, v in model.state_dict().items()},
+                         float(eng.last_grad_norm))
+        if name == "fused":
+            assert eng.fused is not None and eng.fused.usable(eng), "fused step was not used"
+    ln, sn, gn = results["nccl"]
+    lf, sf, gf = results["fused"]
+    assert torch.allclose(ln, lf, rtol=2e-2, atol=2e-2), (ln, lf)
+    assert abs(gn - gf) < 3e-2 * abs(gn) + 1e-3, (gn, gf)
+    for k in sn:
+        close(sf[k], sn[k], 3e-2, k)
+    # every rank must hold identical dense parameters after the fused all-gather
+    for n, p in model.named_parameters():
+        if getattr(p, "_ats_expert", False):
+            continue
+        t = p.detach().float().clone()
+        ref = t.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(t, ref), f"{n} differs across ranks"
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_GPU_OK", world, "losses", lf.tolist())
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -261,3 +261,26 @@ def test_model_bf16_matches_fp32_oracle():
     g16 = m16.layers[0].self_attn.qkv_proj.grad
     g32 = m32.layers[0].self_attn.qkv_proj.grad
     _close(g16, g32, tol=0.15, what="qkv grad")
+
+
+@pytest.mark.parametrize("B,L,hq,hkv,d", [(2, 256, 4, 2, 128), (1, 512, 8, 2, 64), (2, 128, 4, 4, 64)])
+def test_flash_attention_tcgen05(B, L, hq, hkv, d):
+    from adaptivetrainingsystem_b200.ops import attn as A
+    torch.manual_seed(13)
+    width = (hq + 2 * hkv) * d
+    qkv = _rand(B, L, width).requires_grad_()
+    q = qkv[..., : hq * d].view(B, L, hq, d)
+    k = qkv[..., hq * d:(hq + hkv) * d].view(B, L, hkv, d)
+    v = qkv[..., (hq + hkv) * d:].view(B, L, hkv, d)
+    assert A.backend_for(q, k) == "tcgen05"
+    o = ops.attention(q, k, v)
+    g = _rand(B, L, hq, d)
+    o.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    qf = ref_in[..., : hq * d].view(B, L, hq, d)
+    kf = ref_in[..., hq * d:(hq + hkv) * d].view(B, L, hkv, d)
+    vf = ref_in[..., (hq + hkv) * d:].view(B, L, hkv, d)
+    of = ops.attention_reference(qf, kf, vf)
+    of.backward(g.float())
+    _close(o, of, tol=2e-2, what="attention out")
+    _close(qkv.grad, ref_in.grad, tol=3e-2, what="attention grads")
