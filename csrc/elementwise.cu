@@ -433,3 +433,61 @@ ATS_API int ats_cast_f32_bf16(const float* in, void* out, long long n, int accum
       in, static_cast<__nv_bfloat16*>(out), n, accumulate, scale);
   return int(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in ats_noalloc.h).
+//
+// ats_rmsnorm_bwd needs an fp32 scratch of nblocks * cols floats for the per-block weight-gradient partials and
+// leaves its allocation to the caller.  Some callers cannot allocate at all: code running inside a CUDA-graph
+// capture or another region where cudaMalloc is illegal, a real-time loop that must not touch the driver's
+// allocator, a host application that hands this library a fixed memory budget.  For them the partials live in
+// the file-scope device array below, which every GPU that loads this library keeps until the process exits
+// (kNoAllocMaxBlocks * kNoAllocMaxCols * 4 bytes = 4 MiB).
+// ------------------------------------------------------------------------------------------------
+namespace ats {
+constexpr int kNoAllocMaxBlocks = 128;
+constexpr int kNoAllocMaxCols = 8192;
+constexpr int kNoAllocMaxDevices = 64;
+static __device__ __align__(256) float g_rmsnorm_bwd_partials[kNoAllocMaxBlocks * kNoAllocMaxCols];
+// Device address of the array above, per device.  The array's name is only a host-side handle in host code;
+// the address a kernel can use comes from cudaGetSymbolAddress with that device current.
+static float* g_rmsnorm_bwd_partials_addr[kNoAllocMaxDevices] = {};
+}  // namespace ats
+
+ATS_API int ats_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, const void* dres_in,
+                                    void* dx, void* dw_bf16, float* dw_f32, int accumulate, long long rows, int cols,
+                                    void* stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7)) return 1003;
+  if (cols > kNoAllocMaxCols) return 2001;  // ATS_ERR_NOALLOC_TOO_LARGE
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return int(e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return 2002;  // ATS_ERR_NOALLOC_DEVICE
+  if (!g_rmsnorm_bwd_partials_addr[dev]) {
+    // first call on this device: resolve the device address once (do this before any stream capture)
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_bwd_partials);
+    if (e != cudaSuccess) return int(e);
+    g_rmsnorm_bwd_partials_addr[dev] = p;
+  }
+  float* partial = g_rmsnorm_bwd_partials_addr[dev];
+  const int nblocks = rows < kNoAllocMaxBlocks ? int(rows) : kNoAllocMaxBlocks;
+  // Every partial that the reduction reads (nblocks rows of cols floats) is written by the first kernel of this
+  // same call, so nothing has to be cleared even though the array still holds the previous call's values.
+  return ats_rmsnorm_bwd(x, w, dy, rstd, dres_in, dx, partial, nblocks, dw_bf16, dw_f32, accumulate, rows, cols, stream);
+}
+
+ATS_API void ats_rmsnorm_bwd_noalloc_limits(int* max_cols, long long* scratch_bytes) {
+  if (max_cols) *max_cols = kNoAllocMaxCols;
+  if (scratch_bytes) *scratch_bytes = (long long)kNoAllocMaxBlocks * kNoAllocMaxCols * 4;
+}
+
+ATS_API const char* ats_noalloc_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case 1003: return "bad shape: rows and cols must be positive and cols a multiple of 8";
+    case 2001: return "problem too large for the built-in scratch: cols exceeds the limit reported by ats_rmsnorm_bwd_noalloc_limits";
+    case 2002: return "device ordinal outside the range this library keeps scratch addresses for";
+    default: return "CUDA runtime error (the code is a cudaError_t)";
+  }
+}
