@@ -66,7 +66,8 @@ class RotaryEmbedding(nn.Module):
         self.register_buffer("sin", sin, persistent=False)
 
     def ensure(self, length: int, device) -> None:
-        if length > self.cos.shape[0] or self.cos.device != torch.device(device):
+        # the tables stay fp32 even when the module was cast with .to(bfloat16): the kernels read them as float
+        if length > self.cos.shape[0] or self.cos.device != torch.device(device) or self.cos.dtype != torch.float32:
             n = max(length, self.cos.shape[0])
             if length > self.cos.shape[0]:
                 n = max(length, 2 * self.cos.shape[0])

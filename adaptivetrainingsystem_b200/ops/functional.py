@@ -328,6 +328,8 @@ def rope_packed(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_q: in
     """qkv: [B, L, (n_q + 2 n_kv) * d].  Position of token (b, l) is ``positions[b, l]`` or ``pos_offset + l``."""
     B, L, width = qkv.shape
     if _lib.use_cuda_kernels(qkv) and d % 16 == 0 and qkv.is_contiguous():
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32:
+            raise TypeError("rope tables must be float32")
         return _RopePackedFn.apply(qkv, cos, sin, n_q, n_kv, d, L, pos_offset, positions)
     pos = positions if positions is not None else torch.arange(pos_offset, pos_offset + L, device=qkv.device)
     qk = qkv[..., : (n_q + n_kv) * d].reshape(B, L, n_q + n_kv, d)

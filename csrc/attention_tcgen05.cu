@@ -190,37 +190,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_after();
       const bool diag = (j == qt);
       // pass 1: row maximum
-      float mx = m;
+      // four independent running maxima / sums: with one softmax warp per scheduler a 128-long dependent chain
+      // would expose the full ALU latency on every element
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_S + s * 128 + lane_base + c * 32, v);
         tmem_ld_wait();
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]) * p.scale_log2;
-          if (diag && c * 32 + i > r) x = -INFINITY;
-          mx = fmaxf(mx, x);
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > r) v[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
         }
       }
+      // raw maxima are scaled once (scale > 0); the carried maximum m is already in the log2 domain
+      const float mx = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
       const float alpha = exp2f(m - mx);
       m = mx;
-      float rs = 0.f;
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
       // pass 2: probabilities -> P tile in shared memory (K-major, 128-byte swizzle: chunk ^= row % 8)
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_S + s * 128 + lane_base + c * 32, v);
         tmem_ld_wait();
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i > r) v[i] = 0xff800000u;
+        }
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float x0 = __uint_as_float(v[2 * i]) * p.scale_log2, x1 = __uint_as_float(v[2 * i + 1]) * p.scale_log2;
-          float p0 = (diag && c * 32 + 2 * i > r) ? 0.f : exp2f(x0 - mx);
-          float p1 = (diag && c * 32 + 2 * i + 1 > r) ? 0.f : exp2f(x1 - mx);
+          // exp2(x * scale - mx) as one FMA + ex2; exp2(-inf) = 0 handles the causal mask
+          const float p0 = exp2f(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -mx));
+          const float p1 = exp2f(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -mx));
           pk[i] = pack_bf16x2(p0, p1);
-          float2 q = unpack_bf16x2(pk[i]);  // sum what the MMA will actually see
-          rs += q.x + q.y;
+          const float2 q = unpack_bf16x2(pk[i]);  // sum what the MMA will actually see
+          if (i & 1) {
+            rs2 += q.x;
+            rs3 += q.y;
+          } else {
+            rs0 += q.x;
+            rs1 += q.y;
+          }
         }
         uint8_t* prow = sP + (c >> 1) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
@@ -229,6 +250,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
         }
       }
+      const float rs = (rs0 + rs1) + (rs2 + rs3);
       l = l * alpha + rs;
       tc_fence_before();
       fence_proxy_async_smem();  // P was written with generic stores, the MMA reads it through the async proxy

@@ -76,8 +76,13 @@ def main():
     lf, sf, gf = results["fused"]
     assert torch.allclose(ln, lf, rtol=2e-2, atol=2e-2), (ln, lf)
     assert abs(gn - gf) < 3e-2 * abs(gn) + 1e-3, (gn, gf)
+    # AdamW moves every element by about lr per step in the direction of sign(g): where a gradient is almost zero
+    # the summation order (fp32 peer reduce vs NCCL's bf16 ring) can flip single elements, so compare in aggregate
     for k in sn:
-        close(sf[k], sn[k], 3e-2, k)
+        a, b = sf[k].flatten(), sn[k].flatten()
+        cos = torch.nn.functional.cosine_similarity(a, b, dim=0).item()
+        mean_diff = (a - b).abs().mean().item()
+        assert cos > 0.999 and mean_diff < 1e-3 + 0.02 * b.abs().mean().item(), (k, cos, mean_diff)
     # every rank must hold identical dense parameters after the fused all-gather
     for n, p in model.named_parameters():
         if getattr(p, "_ats_expert", False):
