@@ -685,7 +685,7 @@ class ConfigPresets:
         d = ConfigPresets._dense_1b()
         d.update(use_moe=True, num_experts=8, moe_top_k=2, capacity_factor=1.25,
                  load_balancing_weight=0.01, moe_pattern="all", zero_stage=1,
-                 batch_size=4, micro_batch_size=4, experiment_name="b1_moe")
+                 batch_size=8, micro_batch_size=8, gradient_accumulation_steps=4, experiment_name="b1_moe")
         return d
 
     @staticmethod

@@ -1,0 +1,1 @@
+from .engine import GenerationEngine, SamplingParams, KVSlotManager, sample_next, GENERATION_MODES

@@ -1,0 +1,199 @@
+"""Inference runtime: batched prefill + decode with a grouped-query KV cache, sampling (repetition penalty,
+temperature, top-k, top-p, greedy), stop conditions and streaming.
+
+The reference's generator re-runs the whole context for every new token and has no cache (reference
+``Chat.py:355-465``); its sampling API and generation modes (``Chat.py:60-85``) are kept, the loop is new:
+
+* prefill runs the training kernels over the prompt (causal flash attention) and fills the cache;
+* each decode step feeds one token per sequence: QKV GEMM -> RoPE at the cache offset -> attention of the single
+  query against the cached K/V -> MoE FFN (router, dispatch, grouped SwiGLU GEMM, combine; expert-parallel ranks
+  exchange the routed tokens through peer memory) -> next-token logits only for the last position;
+* a slot allocator (``KVSlotManager``) hands out cache rows for continuous batching (the vendored inference engine of
+  the reference keeps the same bookkeeping, ``colossalai/inference/kv_cache/kvcache_manager.py:11-106``).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterator, List, Optional, Sequence
+
+import torch
+
+from ..models.transformer import DeepSeekTransformer, KVCache
+
+GENERATION_MODES: Dict[str, Dict[str, float]] = {
+    "standard": dict(temperature=0.8, top_p=0.9, top_k=50, repetition_penalty=1.1),
+    "creative": dict(temperature=1.0, top_p=0.95, top_k=100, repetition_penalty=1.05),
+    "precise": dict(temperature=0.3, top_p=0.7, top_k=20, repetition_penalty=1.2),
+    "analytical": dict(temperature=0.5, top_p=0.8, top_k=40, repetition_penalty=1.15),
+    "greedy": dict(temperature=0.0, top_p=1.0, top_k=0, repetition_penalty=1.0),
+}
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.8
+    top_k: int = 50
+    top_p: float = 0.9
+    repetition_penalty: float = 1.1
+    repetition_window: int = 50
+    max_new_tokens: int = 512
+    stop_token_ids: Sequence[int] = field(default_factory=tuple)
+    seed: Optional[int] = None
+
+    @classmethod
+    def from_mode(cls, mode: str, **kw) -> "SamplingParams":
+        return cls(**{**GENERATION_MODES[mode], **kw})
+
+
+def sample_next(logits: torch.Tensor, params: SamplingParams, history: Optional[torch.Tensor] = None,
+                generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """logits [B, V] -> token ids [B].  Order of operations as in the reference (``Chat.py:391-425``): repetition
+    penalty over the last ``repetition_window`` tokens, temperature, top-k, top-p, multinomial; ``temperature <= 0``
+    is greedy."""
+    lg = logits.float()
+    if history is not None and params.repetition_penalty != 1.0 and history.numel():
+        h = history[:, -params.repetition_window:]
+        picked = torch.gather(lg, 1, h)
+        picked = torch.where(picked > 0, picked / params.repetition_penalty, picked * params.repetition_penalty)
+        lg = lg.scatter(1, h, picked)
+    if params.temperature <= 0:
+        return lg.argmax(-1)
+    lg = lg / params.temperature
+    if params.top_k and params.top_k < lg.shape[-1]:
+        kth = torch.topk(lg, params.top_k, dim=-1).values[:, -1:]
+        lg = lg.masked_fill(lg < kth, float("-inf"))
+    if params.top_p < 1.0:
+        sl, si = torch.sort(lg, dim=-1, descending=True)
+        cp = torch.softmax(sl, -1).cumsum(-1)
+        drop = cp - torch.softmax(sl, -1) > params.top_p
+        sl = sl.masked_fill(drop, float("-inf"))
+        lg = torch.full_like(lg, float("-inf")).scatter(1, si, sl)
+    probs = torch.softmax(lg, -1)
+    return torch.multinomial(probs, 1, generator=generator).squeeze(1)
+
+
+class KVSlotManager:
+    """Free-list of cache rows for continuous batching: ``alloc(n)`` returns n free slots (lowest first),
+    ``alloc_contiguous(n)`` a run of n, ``free(slots)`` returns them."""
+
+    def __init__(self, size: int):
+        self.size = size
+        self.free_mask = torch.ones(size, dtype=torch.bool)
+
+    @property
+    def available(self) -> int:
+        return int(self.free_mask.sum())
+
+    def alloc(self, n: int) -> Optional[torch.Tensor]:
+        idx = torch.nonzero(self.free_mask, as_tuple=False).flatten()
+        if idx.numel() < n:
+            return None
+        sel = idx[:n]
+        self.free_mask[sel] = False
+        return sel
+
+    def alloc_contiguous(self, n: int) -> Optional[torch.Tensor]:
+        if n > self.size:
+            return None
+        run = torch.nn.functional.conv1d(self.free_mask.float().view(1, 1, -1), torch.ones(1, 1, n)).flatten()
+        starts = torch.nonzero(run == n, as_tuple=False).flatten()
+        if not starts.numel():
+            return None
+        s = int(starts[0])
+        self.free_mask[s:s + n] = False
+        return torch.arange(s, s + n)
+
+    def free(self, slots: torch.Tensor) -> None:
+        self.free_mask[slots] = True
+
+
+class GenerationEngine:
+    def __init__(self, model: DeepSeekTransformer, tokenizer=None, max_batch: int = 64, max_len: Optional[int] = None):
+        self.model = model.eval()
+        self.tokenizer = tokenizer
+        self.max_batch = max_batch
+        self.max_len = max_len or model.config.seq_length
+        self.stats: Dict[str, float] = {}
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, cache: KVCache) -> torch.Tensor:
+        """Runs the prompt, fills the cache, returns the logits of the last position [B, V]."""
+        logits = self.model(input_ids, cache=cache, last_token_only=True, return_aux_loss=False)
+        return logits[:, -1, :]
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor, cache: KVCache) -> torch.Tensor:
+        """tokens [B] -> logits [B, V] for the next position."""
+        logits = self.model(tokens.view(-1, 1), cache=cache, last_token_only=True, return_aux_loss=False)
+        return logits[:, -1, :]
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, params: Optional[SamplingParams] = None,
+                 on_token: Optional[Callable[[int, torch.Tensor], None]] = None) -> Dict[str, object]:
+        """input_ids [B, Lp] (equal-length prompts) -> dict(tokens [B, <=max_new], prefill_s, decode_s, ...).
+        Timed with device synchronisation on both sides of each phase."""
+        params = params or SamplingParams()
+        dev = input_ids.device
+        B, Lp = input_ids.shape
+        total = Lp + params.max_new_tokens
+        cache = self.model.make_cache(B, total)
+        gen = None
+        if params.seed is not None:
+            gen = torch.Generator(device=dev).manual_seed(params.seed)
+        sync = torch.cuda.synchronize if dev.type == "cuda" else (lambda: None)
+        sync()
+        t0 = time.perf_counter()
+        logits = self.prefill(input_ids, cache)
+        sync()
+        t1 = time.perf_counter()
+        history = input_ids
+        out: List[torch.Tensor] = []
+        finished = torch.zeros(B, dtype=torch.bool, device=dev)
+        stop = torch.tensor(list(params.stop_token_ids), device=dev, dtype=torch.long) if params.stop_token_ids else None
+        steps = 0
+        for step in range(params.max_new_tokens):
+            nxt = sample_next(logits, params, history, gen)
+            if stop is not None:
+                finished |= (nxt[:, None] == stop[None, :]).any(-1)
+            out.append(nxt)
+            steps += 1
+            if on_token is not None:
+                on_token(step, nxt)
+            if stop is not None and bool(finished.all()):
+                break
+            history = torch.cat([history, nxt[:, None]], dim=1)
+            if step + 1 < params.max_new_tokens:
+                logits = self.decode_step(nxt, cache)
+        sync()
+        t2 = time.perf_counter()
+        self.stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1, "prefill_tokens_per_s": B * Lp / max(t1 - t0, 1e-9),
+                      "decode_tokens_per_s": B * max(steps - 1, 1) / max(t2 - t1, 1e-9), "steps": steps}
+        return {"tokens": torch.stack(out, dim=1), **self.stats}
+
+    def generate_text(self, prompt: str, params: Optional[SamplingParams] = None) -> str:
+        if self.tokenizer is None:
+            raise RuntimeError("a tokenizer is needed for text generation")
+        dev = next(self.model.parameters()).device
+        ids = torch.tensor([self.tokenizer.encode(prompt)], dtype=torch.long, device=dev)
+        res = self.generate(ids, params)
+        return self.tokenizer.decode(res["tokens"][0].tolist())
+
+    def stream(self, prompt: str, params: Optional[SamplingParams] = None) -> Iterator[str]:
+        """Yields decoded text piece by piece (one model step per yielded token)."""
+        if self.tokenizer is None:
+            raise RuntimeError("a tokenizer is needed for text generation")
+        params = params or SamplingParams()
+        dev = next(self.model.parameters()).device
+        ids = torch.tensor([self.tokenizer.encode(prompt)], dtype=torch.long, device=dev)
+        cache = self.model.make_cache(1, ids.shape[1] + params.max_new_tokens)
+        with torch.no_grad():
+            logits = self.prefill(ids, cache)
+            history = ids
+            for _ in range(params.max_new_tokens):
+                nxt = sample_next(logits, params, history)
+                if params.stop_token_ids and int(nxt) in set(params.stop_token_ids):
+                    return
+                yield self.tokenizer.decode([int(nxt)])
+                history = torch.cat([history, nxt[:, None]], dim=1)
+                logits = self.decode_step(nxt, cache)

@@ -102,6 +102,8 @@ def run_ours(args) -> dict:
         over["num_layers"] = args.layers
     if args.seq:
         over["seq_length"] = args.seq
+    if args.accum:
+        over["gradient_accumulation_steps"] = args.accum
     cfg = ConfigPresets.get(args.config, num_workers=0, gradient_checkpointing=bool(args.checkpoint), **over)
     cfg.fused_comm = not args.nccl_only
     ep = math.gcd(cfg.num_experts, world) if cfg.use_moe else 1
@@ -132,15 +134,20 @@ def run_ours(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
+    accum = max(cfg.gradient_accumulation_steps, 1)
+
     def step_device(i):
-        trainer.train_step(devb[i % n_batches])
+        for a in range(accum):
+            trainer.train_step(devb[(i * accum + a) % n_batches])
         trainer.optimizer_step()
         trainer._pending_device.clear()
 
     def step_e2e(i):
-        b = host[i % n_batches]
-        batch = {k: v.to(dev, non_blocking=True) for k, v in b.items()}
-        out = trainer.train_step(batch)
+        out = None
+        for a in range(accum):
+            b = host[(i * accum + a) % n_batches]
+            batch = {k: v.to(dev, non_blocking=True) for k, v in b.items()}
+            out = trainer.train_step(batch)
         trainer.optimizer_step()
         trainer._pending_device.clear()
         return float(out["loss"])  # device -> host read every step
@@ -183,16 +190,16 @@ def run_ours(args) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t)
 
-    tokens = mb * L * world
+    tokens = mb * L * world * accum
     value = tokens / (ms / 1e3)
     pub = PUBLISHED_TOKENS_PER_S.get(args.config)
-    h2d = sum(v.numel() * v.element_size() for v in host[0].values())
+    h2d = accum * sum(v.numel() * v.element_size() for v in host[0].values())
     res = {
         "metric": "moe_train_tokens_per_sec" if cfg.use_moe else "train_tokens_per_sec", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": (value / pub) if pub else None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": args.config, "global_batch": mb * world, "seq_len": L, "parallelism": mesh.describe() + f"+zero{cfg.zero_stage}",
+        "config": {"model": args.config, "global_batch": mb * world * accum, "micro_batch_per_gpu": mb, "grad_accumulation": accum, "seq_len": L, "parallelism": mesh.describe() + f"+zero{cfg.zero_stage}",
                    "hidden": cfg.hidden_size, "layers": cfg.num_layers, "experts": cfg.num_experts if cfg.use_moe else 0,
                    "top_k": cfg.moe_top_k if cfg.use_moe else 0, "params_total": mc.num_parameters(),
                    "params_active": mc.num_parameters(True), "l2": "working set per step (weights + activations) far exceeds the 126 MB L2",
@@ -229,6 +236,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: a run with fewer layers is not a benchmark number")
     ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--accum", type=int, default=0)
     ap.add_argument("--checkpoint", type=int, default=0)
     ap.add_argument("--nccl-only", action="store_true", help="baseline path: NCCL collectives instead of the fused peer-memory kernels")
     args = ap.parse_args()
