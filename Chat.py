@@ -63,13 +63,13 @@ class ChatInterface:
         self.model = self.model.to(self.device, dtype).eval()
         self.tokenizer = ConversationTokenizer()
         self.engine = GenerationEngine(self.model, self.tokenizer)
-        self.params = SamplingParams.from_mode(mode, max_new_tokens=256,
+        self.params = SamplingParams.from_mode(mode, max_new_tokens=min(256, max(cfg.seq_length // 2, 1)),
                                                stop_token_ids=(self.tokenizer.special_tokens["<|im_end|>"], self.tokenizer.eos_token_id))
         self.history = []
 
     def _format_prompt(self, user_text: str):
         msgs = self.history + [{"role": "user", "content": user_text}]
-        enc = self.tokenizer.encode_conversation(msgs, max_length=self.model.config.seq_length - self.params.max_new_tokens,
+        enc = self.tokenizer.encode_conversation(msgs, max_length=max(self.model.config.seq_length - self.params.max_new_tokens, 8),
                                                  truncation="keep_system", add_generation_prompt=True)
         return torch.tensor([enc["input_ids"]], dtype=torch.long, device=self.device).clamp(max=self.model.config.vocab_size - 1)
 

@@ -1,0 +1,247 @@
+"""Config, data, tokenizer, orchestrator, Chinchilla planner, monitoring, inference sampling, security -- all on CPU."""
+import json
+import math
+import os
+import time
+
+import pytest
+import torch
+
+from adaptivetrainingsystem_b200.config import Config, ConfigManager, ConfigPresets, ModelConfig
+from adaptivetrainingsystem_b200.data import (BaseTrainingDataset, ConversationDataset, InterleavedDataset, SyntheticTokenDataset,
+                                              create_dataloader, setup_datasets)
+from adaptivetrainingsystem_b200.data.tokenizer import ConversationTokenizer
+from adaptivetrainingsystem_b200.inference import KVSlotManager, SamplingParams, sample_next
+from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+from adaptivetrainingsystem_b200.monitoring.logger import MetricsCollector, TrainingHealthMonitor
+from adaptivetrainingsystem_b200.security import AuthManager, InputValidator, RateLimiter
+from adaptivetrainingsystem_b200.training import EnhancedConversationTrainer, LRSchedule
+from adaptivetrainingsystem_b200.training.chinchilla import ConvergenceDetector, EnhancedChinchillaScaler
+from adaptivetrainingsystem_b200.training.orchestrator import (AdaptiveTrainingOrchestrator, ArchitectureEvolution, MetaLearningEngine,
+                                                               RealTimeAnalytics)
+from adaptivetrainingsystem_b200.training.trainer import TrainingMetrics
+
+
+# -- config -------------------------------------------------------------------------------------------------------
+def test_config_validation_presets_and_round_trip(tmp_dir):
+    with pytest.raises(ValueError):
+        Config(hidden_size=100, num_heads=8)
+    with pytest.raises(ValueError):
+        Config(precision="fp7")
+    c = Config(num_experts=4, precision="mixed_fp8")  # both rejected by the reference, documented as supported
+    assert c.to_model_config().fp8 and c.intermediate_size % 64 == 0 and c.vocab_size % 64 == 0
+    for name in ConfigPresets.names():
+        p = ConfigPresets.get(name)
+        assert p.hidden_size % p.num_heads == 0 and p.num_parameters() > 0
+    mix = ConfigPresets.mixtral_8x7b()
+    assert 45e9 < mix.num_parameters() < 48e9 and 12e9 < mix.num_parameters(True) < 14e9
+    for ext in ("yaml", "json"):
+        path = os.path.join(tmp_dir, f"c.{ext}")
+        c.some_runtime_flag = 3
+        c.save(path)
+        d = Config.load(path)
+        assert d.hidden_size == c.hidden_size and d.some_runtime_flag == 3 and d.precision == "mixed_fp8"
+    ds = c.to_deepspeed_config()
+    assert ds["zero_optimization"]["stage"] == c.zero_stage and ds["moe"]["num_experts"] == 4
+    fitted = ConfigManager.optimize_for_hardware(ConfigPresets.b7(), device_memory_gb=180, world_size=8)
+    assert fitted.zero_stage >= 1 and fitted.expert_parallel_size == 8
+    assert isinstance(ConfigManager.validate_config(Config(learning_rate=0.1)), list)
+    assert "b7" in ConfigPresets.compare_presets()
+
+
+def test_model_config_layer_patterns():
+    m = ModelConfig(num_layers=8, use_moe=True, moe_pattern="every_4th", use_mod=True)
+    assert [m.is_moe_layer(i) for i in range(8)] == [False, False, False, True, False, False, False, True]
+    assert m.is_mod_layer(0) and not m.is_mod_layer(3)
+    s = ModelConfig(num_layers=8, use_moe=True, moe_pattern="sandwich")
+    assert [s.is_moe_layer(i) for i in range(8)] == [False, False, True, True, True, True, False, False]
+
+
+# -- data ---------------------------------------------------------------------------------------------------------
+def test_datasets_and_loader(tmp_dir):
+    tok = ConversationTokenizer()
+    conv = os.path.join(tmp_dir, "c.jsonl")
+    with open(conv, "w") as f:
+        for i in range(10):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"question {i}"}, {"role": "assistant", "content": f"answer {i}"}]}) + "\n")
+        f.write("not json\n")
+        f.write(json.dumps({"messages": [{"role": "alien", "content": "x"}]}) + "\n")
+    txt = os.path.join(tmp_dir, "b.txt")
+    with open(txt, "w") as f:
+        f.write("\n\n".join("paragraph %d " % i * 20 for i in range(30)))
+    cd = ConversationDataset([conv], tok, 64, assistant_loss_weight=2.0)
+    assert len(cd) == 10 and cd.stats["invalid"] == 2
+    item = cd[0]
+    assert set(item) == {"input_ids", "labels", "attention_mask", "loss_weights"} and item["input_ids"].shape == (64,)
+    assert item["loss_weights"].max() == 2.0 and (item["labels"] == -100).any()
+    valid = item["labels"] != -100
+    assert torch.equal(item["labels"][valid][:-1], item["input_ids"][1:][valid[:-1]][: valid.sum() - 1])
+    bd = BaseTrainingDataset([txt], tok, 64)
+    assert len(bd) > 0 and torch.equal(bd[0]["labels"][:-1], bd[0]["input_ids"][1:])
+    cfg = Config(seq_length=64, batch_size=2, training_mode="interleaved", base_training_paths=[txt], finetuning_paths=[conv],
+                 train_data_path=conv, eval_data_path=conv, num_workers=0, vocab_size=tok.vocab_size)
+    tr, ev = setup_datasets(cfg, tok)
+    assert isinstance(tr, InterleavedDataset) and len(tr) == len(bd) + len(cd) and len(ev) == 10
+    batch = next(iter(create_dataloader(tr, cfg)))
+    assert batch["input_ids"].shape == (2, 64)
+    s = SyntheticTokenDataset(1000, 16, 4, seed=3)
+    assert torch.equal(s[2]["input_ids"], SyntheticTokenDataset(1000, 16, 4, seed=3)[2]["input_ids"])
+
+
+def test_tokenizer():
+    t = ConversationTokenizer()
+    assert t.vocab_size % 128 == 0 and t.pad_token_id >= t.base_vocab_size and len(t.special_tokens) == 13
+    text = "héllo wörld ✓"
+    assert t.decode(t.encode(text)) == text
+    enc = t.encode_conversation([{"role": "system", "content": "s" * 50}, {"role": "user", "content": "u" * 200}], max_length=100,
+                                truncation="keep_system")
+    assert len(enc["input_ids"]) == 100 and enc["roles"][0] == "system" and enc["roles"][-1] == "user"
+    assert len(t.encode_batch(["a", "bb"] * 40)) == 80
+
+
+# -- schedulers ---------------------------------------------------------------------------------------------------
+def test_lr_schedules():
+    for kind in ("cosine", "linear", "onecycle", "constant"):
+        s = LRSchedule(kind, 1e-3, 100, warmup_ratio=0.1, min_lr=1e-5)
+        lrs = [s.step() for _ in range(100)]
+        assert all(0 < x <= 1e-3 + 1e-12 for x in lrs)
+        if kind in ("cosine", "linear"):
+            assert lrs[-1] == pytest.approx(1e-5, rel=1e-3) and max(lrs) == pytest.approx(1e-3, rel=0.02)
+    s = LRSchedule("cosine", 1e-3, 100)
+    s.scale_base(0.1)
+    assert s.lr_at(0) == pytest.approx(1e-4)
+
+
+# -- orchestrator ---------------------------------------------------------------------------------------------------
+def _tm(step, loss, gn=1.0, util=None):
+    return TrainingMetrics(epoch=0, step=step, loss=loss, grad_norm=gn, learning_rate=1e-3, expert_utilization=util or {})
+
+
+def test_anomaly_detection():
+    a = RealTimeAnalytics(min_samples=50)
+    for i in range(80):
+        assert not a.detect_training_anomalies(_tm(i, 2.0 + 0.01 * math.sin(i)))
+    kinds = set()
+    for i in range(12):
+        kinds |= {x["type"] for x in a.detect_training_anomalies(_tm(80 + i, 4.0))}
+    assert "loss_spike" in kinds
+    assert {x["type"] for x in a.detect_training_anomalies(_tm(100, 2.0, gn=500.0))} >= {"gradient_explosion"}
+    assert a.detect_training_anomalies(_tm(101, float("nan")))[0]["type"] == "divergence"
+    util = {f"layer_0_expert_{j}": v for j, v in enumerate([0.5, 60.0, 20.0, 19.5])}
+    assert "expert_collapse" in {x["type"] for x in a.detect_training_anomalies(_tm(102, 2.0, util=util))}
+
+
+def test_orchestrator_decisions_drive_the_trainer(tmp_dir):
+    cfg = Config(vocab_size=512, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=128, seq_length=32,
+                 batch_size=4, micro_batch_size=4, gradient_accumulation_steps=1, num_epochs=1, precision="fp32", use_moe=True,
+                 num_experts=4, output_dir=tmp_dir, experiment_name="o", log_every_n_steps=1, num_workers=0, gradient_checkpointing=False)
+    torch.manual_seed(0)
+    model = DeepSeekTransformer(cfg.to_model_config())
+    orch = AdaptiveTrainingOrchestrator(cfg, model=model)
+    tr = orch.initialize_training()
+    lr0 = tr.engine.get_lr()
+    orch._handle_training_anomaly({"type": "gradient_explosion", "severity": "critical", "detail": "test"}, _tm(1, 2.0, 500.0))
+    assert tr.engine.get_lr() < lr0 / 5 and orch.decisions[-1].applied
+    orch._decide("add_expert", {"layer_idx": 0}, 0.8, "test")
+    assert tr.model.get_moe_layers()[0].num_experts == 5
+    orch._decide("prune_expert", {"layer_idx": 0, "expert_idx": 4}, 0.8, "test")
+    assert tr.model.get_moe_layers()[0].num_experts == 4
+    orch._decide("expert_rebalance", {"temperature_factor": 1.5, "capacity_factor": 1.2}, 0.8, "test")
+    assert tr.model.get_moe_layers()[0].routing_temperature == pytest.approx(1.5)
+    from adaptivetrainingsystem_b200.data import SyntheticTokenDataset as S
+    summary = orch.run_adaptive_training(S(512, 32, 16, seed=0))
+    assert summary["global_step"] == 4 and summary["adaptive"]["decisions_total"] >= 4
+    assert os.path.exists(os.path.join(tmp_dir, "o", "adaptive_learning_summary.json"))
+    assert os.path.exists(os.path.join(tmp_dir, "o", "meta_learning_state.pkl"))
+    # a decision posted from another thread is applied at the next step boundary, not concurrently
+    import threading
+    t = threading.Thread(target=lambda: tr.adjust_learning_rate(3.3e-6))
+    t.start(); t.join()
+    assert tr.engine.get_lr() != pytest.approx(3.3e-6) and len(tr._pending) == 1
+    batch = next(iter(tr._make_loader(S(512, 32, 4, seed=0), False)))
+    tr.train_step(batch); tr.optimizer_step()
+    assert tr.engine.get_lr() == pytest.approx(3.3e-6)
+    orch.cleanup()
+
+
+def test_meta_learning_and_architecture_policy(tmp_dir):
+    p = os.path.join(tmp_dir, "m.pkl")
+    m = MetaLearningEngine(p)
+    m.record_run({"parameters": 1e9, "learning_rate": 2e-4}, 2.5, True)
+    m.save()
+    m2 = MetaLearningEngine(p)
+    assert m2.suggest_hyperparameters({"parameters": 2e9})["learning_rate"] == 2e-4
+    traj = m2.predict_training_trajectory([5.0 / (i + 1) ** 0.3 for i in range(100)])
+    assert traj["slope"] < 0
+    with open(p, "wb") as f:
+        f.write(b"garbage")
+    assert MetaLearningEngine(p).training_history == []  # a corrupt state file is survivable
+    props = ArchitectureEvolution().propose({"layer_3": {"expert_usage": [0.9, 0.05, 0.03, 0.02, 0.0]}})
+    assert props[0]["action"] == "add_expert" and props[0]["layer_idx"] == 3
+    props = ArchitectureEvolution().propose({"layer_1": {"expert_usage": [0.3, 0.3, 0.3, 0.099, 0.001]}})
+    assert props[0]["action"] == "prune_expert" and props[0]["expert_idx"] == 4
+
+
+# -- chinchilla / monitoring ------------------------------------------------------------------------------------------
+def test_chinchilla_planner(tmp_dir):
+    cfg = Config(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, vocab_size=512, use_moe=True, num_experts=8, seq_length=32)
+    sc = EnhancedChinchillaScaler(cfg, dataset_tokens=10_000)
+    assert sc.active_params < sc.total_params
+    assert sc.get_optimal_epochs() == max(1, min(50, math.ceil(20 * sc.active_params / 10_000)))
+    for i in range(600):
+        sc.update_metrics(i, 3.0, 1000.0, 1.0)
+    assert sc.convergence.status()["state"] in ("plateau", "slowing") and sc.should_stop_early()
+    sc.save_state(os.path.join(tmp_dir, "s.json"))
+    det = ConvergenceDetector(window=20)
+    for i in range(100):
+        det.update(5.0 - 0.03 * i)
+    assert det.status()["state"] == "improving"
+
+
+def test_monitoring():
+    c = MetricsCollector()
+    for i in range(30):
+        c.add_many({"loss": 2.0 - 0.01 * i, "grad_norm": 1.0}, i)
+    assert c.trend("loss") < 0 and c.health_score() > 0.9
+    assert any(a.message == "loss spike" for a in c.add("loss", 9.0, 31))
+    assert c.add("grad_norm", 1e4, 32)[0].level == "critical"
+    h = TrainingHealthMonitor(check_interval=10)
+    for i in range(120):
+        h.update(i, 3.0 * math.exp(-i / 40), 1.0, 1e-3, 1000.0)
+    assert h.phase in ("rapid_learning", "steady_learning") and h.get_report()["checks"]
+
+
+# -- inference sampling / security ---------------------------------------------------------------------------------------
+def test_sampling_rules():
+    torch.manual_seed(0)
+    logits = torch.tensor([[0.0, 5.0, 4.0, -1.0, 3.0]])
+    assert sample_next(logits, SamplingParams(temperature=0.0)).item() == 1
+    hist = torch.tensor([[1, 1]])
+    assert sample_next(logits, SamplingParams(temperature=0.0, repetition_penalty=2.0), hist).item() == 2
+    picks = {sample_next(logits, SamplingParams(temperature=1.0, top_k=2, top_p=1.0, repetition_penalty=1.0)).item() for _ in range(50)}
+    assert picks <= {1, 2}
+    picks = {sample_next(logits, SamplingParams(temperature=1.0, top_k=0, top_p=0.5, repetition_penalty=1.0)).item() for _ in range(50)}
+    assert picks == {1}
+    s = KVSlotManager(8)
+    a = s.alloc(3)
+    assert s.alloc_contiguous(6) is None and s.alloc_contiguous(5).tolist() == [3, 4, 5, 6, 7]
+    s.free(a)
+    assert s.available == 3
+
+
+def test_security_primitives():
+    a = AuthManager(iterations=1000, max_attempts=2, lockout_s=60)
+    a.create_user("alice", "correct horse")
+    tok = a.authenticate("alice", "correct horse")
+    assert a.verify(tok)["sub"] == "alice" and a.verify(tok + "x") is None
+    assert a.authenticate("alice", "bad") is None and a.authenticate("alice", "bad") is None
+    assert a.authenticate("alice", "correct horse") is None  # locked out
+    a.logout(tok)
+    assert a.verify(tok) is None
+    now = [0.0]
+    r = RateLimiter(2, 10.0, clock=lambda: now[0])
+    assert r.allow("k")[0] and r.allow("k")[0] and not r.allow("k")[0]
+    now[0] = 11.0
+    assert r.allow("k")[0]
+    v = InputValidator(max_length=50)
+    assert v.validate("hello")[0] and not v.validate("<script>alert(1)</script>")[0] and not v.validate("x" * 51)[0]
