@@ -1,0 +1,104 @@
+"""Pipeline (1F1B), tensor parallel, vocabulary-parallel loss and head-scatter sequence parallel against single-process
+results, on Gloo ranks."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from dist_utils import run_dist  # noqa: E402
+
+from adaptivetrainingsystem_b200.config import ModelConfig  # noqa: E402
+from adaptivetrainingsystem_b200.models import DeepSeekTransformer  # noqa: E402
+
+pytestmark = pytest.mark.dist
+CFG = dict(vocab_size=256, hidden_size=64, num_layers=4, num_heads=4, num_kv_heads=2, intermediate_size=128, seq_length=16,
+           tie_word_embeddings=False)
+
+
+def _pp_worker(rank, world, path):
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200.parallel.pipeline import OneFOneBSchedule, PipelineStage, partition_layers
+    assert partition_layers(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    ref = torch.load(path)
+    torch.manual_seed(0)
+    model = DeepSeekTransformer(ModelConfig(**CFG))
+    model.load_state_dict(ref["init"])
+    stage = PipelineStage(model, rank, world)
+    sched = OneFOneBSchedule(stage, dist.group.WORLD, 4, (2, 16, 64), torch.float32, torch.device("cpu"))
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 256, (8, 17), generator=g)
+    mbs = [{"input_ids": ids[2 * i:2 * i + 2, :-1], "labels": ids[2 * i:2 * i + 2, 1:]} for i in range(4)]
+    loss = sched.run(mbs)
+    if rank == world - 1:
+        assert abs(loss.item() - ref["loss"]) < 1e-4, (loss.item(), ref["loss"])
+    for n, p in model.named_parameters():
+        if p.requires_grad and p.grad is not None:
+            assert torch.allclose(p.grad, ref["grads"][n], atol=1e-5), n
+
+
+def test_pipeline_1f1b_matches_single_process(tmp_path):
+    torch.manual_seed(0)
+    model = DeepSeekTransformer(ModelConfig(**CFG))
+    init = {k: v.clone() for k, v in model.state_dict().items()}
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 256, (8, 17), generator=g)
+    total = 0.0
+    for i in range(4):
+        out = model.forward_loss(ids[2 * i:2 * i + 2, :-1], ids[2 * i:2 * i + 2, 1:])
+        (out["loss"] / 4).backward()
+        total += out["loss"].item() / 4
+    path = str(tmp_path / "ref.pt")
+    torch.save({"init": init, "loss": total, "grads": {n: p.grad.clone() for n, p in model.named_parameters()}}, path)
+    run_dist(_pp_worker, 2, (path,))
+
+
+def _tp_worker(rank, world):
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200.parallel.sequence_parallel import ulysses_attention
+    from adaptivetrainingsystem_b200.parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding,
+                                                                      vocab_parallel_cross_entropy)
+    from adaptivetrainingsystem_b200 import ops
+    torch.manual_seed(0)
+    w1, w2 = torch.randn(32, 16) * 0.1, torch.randn(16, 32) * 0.1
+    x = torch.randn(2, 8, 16)
+    for sp in (False, True):
+        xin = (x.chunk(world, dim=1)[rank] if sp else x).clone().requires_grad_()
+        col = ColumnParallelLinear.from_full(w1, None, sequence_parallel=sp)
+        row = RowParallelLinear.from_full(w2, None, sequence_parallel=sp)
+        y = row(torch.relu(col(xin)))
+        y.sum().backward()
+        xr = x.clone().requires_grad_()
+        w1r = w1.clone().requires_grad_()
+        yr = torch.relu(xr @ w1r.t()) @ w2.t()
+        yr.sum().backward()
+        y_ref = yr.chunk(world, dim=1)[rank] if sp else yr
+        g_ref = xr.grad.chunk(world, dim=1)[rank] if sp else xr.grad
+        assert torch.allclose(y, y_ref, atol=1e-5) and torch.allclose(xin.grad, g_ref, atol=1e-5), sp
+        assert torch.allclose(col.weight.grad, w1r.grad.chunk(world, 0)[rank], atol=1e-5), sp
+    # vocabulary-parallel embedding and loss
+    table = torch.randn(20, 8)
+    emb = VocabParallelEmbedding(20, 8)
+    emb.weight.data.copy_(table.chunk(world, 0)[rank])
+    ids = torch.randint(0, 20, (3, 5))
+    assert torch.allclose(emb(ids), table[ids], atol=1e-6)
+    logits = torch.randn(15, 20)
+    labels = torch.randint(0, 20, (15,))
+    labels[0] = -100
+    ll = logits.chunk(world, -1)[rank].clone().requires_grad_()
+    loss = vocab_parallel_cross_entropy(ll, labels)
+    loss.backward()
+    lr = logits.clone().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lr, labels, ignore_index=-100)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 1e-5 and torch.allclose(ll.grad, lr.grad.chunk(world, -1)[rank], atol=1e-6)
+    # head-scatter sequence parallel attention
+    q, k, v = torch.randn(1, 8, 4, 8), torch.randn(1, 8, 2, 8), torch.randn(1, 8, 2, 8)
+    o_ref = ops.attention_reference(q, k, v)
+    o = ulysses_attention(*(t.chunk(world, dim=1)[rank].contiguous() for t in (q, k, v)))
+    assert torch.allclose(o, o_ref.chunk(world, dim=1)[rank], atol=1e-5)
+
+
+def test_tensor_sequence_vocab_parallel():
+    run_dist(_tp_worker, 2)
