@@ -61,7 +61,11 @@ class CheckpointManager:
                         metrics: Optional[Dict[str, Any]] = None, suffix: Optional[str] = None, mesh=None,
                         is_best: bool = False, eval_loss: Optional[float] = None) -> Optional[str]:
         rank = dist.get_rank() if dist.is_initialized() else 0
+        if engine is not None and hasattr(engine, "gather_full_parameters"):
+            engine.gather_full_parameters()  # ZeRO-3: materialise every block for the state dict
         model_sd = self._gather_model_state(model, mesh)
+        if engine is not None and hasattr(engine, "release_parameters"):
+            engine.release_parameters()
         opt_sd = engine.state_dict() if (engine is not None and getattr(self.config, "save_optimizer_states", True)) else None
         if opt_sd is not None and mesh is not None and mesh.ep_size > 1 and dist.is_initialized():
             mine = {k: v for k, v in opt_sd["state"].items() if "experts_w" in k}
@@ -168,7 +172,9 @@ class CheckpointManager:
             for k in ARCH_KEYS:
                 if k in mc and getattr(model.config, k, mc[k]) != mc[k]:
                     raise CheckpointError(f"architecture mismatch on {k}: checkpoint {mc[k]} vs model {getattr(model.config, k)}")
-        target = next(model.parameters())
+        if engine is not None and hasattr(engine, "gather_full_parameters"):
+            engine.gather_full_parameters()
+        target = next(p for p in model.parameters() if p.numel() > 0)
         res = model.load_state_dict({k: v.to(target.dtype) if v.is_floating_point() else v for k, v in sd.items()}, strict=strict)
         if engine is not None:
             osd = ckpt.get("optimizer_state_dict")

@@ -91,11 +91,14 @@ class EnhancedConversationTrainer:
         self.pad_token_id = getattr(tokenizer, "pad_token_id", None)
         self.ignore_index = -100
 
-        self.engine = ShardedEngine(
-            model, lr=self.config.learning_rate, betas=(self.config.adam_beta1, self.config.adam_beta2),
-            eps=self.config.adam_eps, weight_decay=self.config.weight_decay,
-            max_grad_norm=getattr(self.config, "max_grad_norm", 1.0), zero_stage=self.config.zero_stage,
-            mesh=self.mesh, fused_comm=fused_comm, grad_accumulation_steps=self.config.gradient_accumulation_steps)
+        opt = dict(lr=self.config.learning_rate, betas=(self.config.adam_beta1, self.config.adam_beta2), eps=self.config.adam_eps,
+                   weight_decay=self.config.weight_decay, max_grad_norm=getattr(self.config, "max_grad_norm", 1.0), mesh=self.mesh,
+                   grad_accumulation_steps=self.config.gradient_accumulation_steps)
+        if self.config.zero_stage >= 3 and self.mesh.ep_size == 1 and self.mesh.world > 1:
+            from ..parallel.zero3 import ZeRO3Engine
+            self.engine = ZeRO3Engine(model, **opt)  # per-block gather / release; expert-parallel models use stage <= 2
+        else:
+            self.engine = ShardedEngine(model, zero_stage=min(self.config.zero_stage, 2), fused_comm=fused_comm, **opt)
         self.optimizer = self.engine  # reference attribute name
         self.scheduler = None
         self.use_deepspeed = False
