@@ -121,6 +121,9 @@ class GroupedQueryAttention(nn.Module):
         qkv = ops.linear(h, self.qkv_proj)
         qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=offset, positions=positions)
         nq, nk = self.n_q * self.d, self.n_kv * self.d
+        if cache is None and attention_mask is None and ops.attention_packed_available(qkv, self.d, L):
+            a = ops.attention_packed(qkv, self.n_q, self.n_kv, self.d)
+            return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
         q = qkv[..., :nq].view(B, L, self.n_q, self.d)
         k = qkv[..., nq:nq + nk].view(B, L, self.n_kv, self.d)
         v = qkv[..., nq + nk:].view(B, L, self.n_kv, self.d)

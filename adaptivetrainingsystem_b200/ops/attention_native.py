@@ -1,15 +1,15 @@
-"""Autograd wrapper of the tcgen05 flash-attention forward kernel (``csrc/attention_tcgen05.cu``).
+"""Autograd wrappers of the tcgen05 flash-attention kernels (``csrc/attention_tcgen05.cu`` forward,
+``csrc/attention_bwd_tcgen05.cu`` backward).
 
-Forward reads q / k / v in place from the packed projection (strided views are passed as tensor maps).  The backward
-pass currently re-derives the gradients through PyTorch's fused SDPA (a library call) from the saved inputs; the
-tcgen05 backward kernel replaces it when ``ats_attn_bwd`` is present in the library.
+Both directions read q / k / v in place from the packed QKV projection (strided views become tensor maps).  The packed
+entry point takes the whole ``[B, L, (Hq + 2 Hkv) * D]`` projection and returns its gradient as one tensor, so autograd
+never has to zero-pad and add three sliced gradients.
 """
 from __future__ import annotations
 
 import ctypes
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib
 
@@ -17,15 +17,18 @@ _vp, _ci, _cll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 _sig = False
 
 
-def _fn():
+def _lib_fns():
     global _sig
     lib = _lib.cuda_lib()
     if not _sig:
         lib.ats_attn_fwd.restype = _ci
         lib.ats_attn_fwd.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp,
                                      _ci, _ci, _ci, _ci, _ci, _vp, _vp]
+        lib.ats_attn_bwd.restype = _ci
+        lib.ats_attn_bwd.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                     _cll, _cll, _ci, _ci, _ci, _ci, _ci, _vp, _vp]
         _sig = True
-    return lib.ats_attn_fwd
+    return lib
 
 
 def layout_ok(t: torch.Tensor) -> bool:
@@ -35,30 +38,79 @@ def layout_ok(t: torch.Tensor) -> bool:
     return (s[3] == 1 and s[2] == D and s[0] == L * s[1] and s[1] % 8 == 0 and t.data_ptr() % 16 == 0)
 
 
+def _fwd(q, k, v):
+    B, L, Hq, D = q.shape
+    Hkv = k.shape[2]
+    out = torch.empty(B, L, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
+    st = _lib.status_tensor(q.device)
+    err = _lib_fns().ats_attn_fwd(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),
+                                  Hkv * D, 0, _lib.ptr(out), _lib.ptr(lse), B, L, Hq, Hkv, D, _lib.ptr(st), _lib.stream_ptr(q.device))
+    _lib.check(err, "ats_attn_fwd")
+    return out, lse
+
+
+def _bwd(q, k, v, out, dout, lse, dq, dk, dv):
+    B, L, Hq, D = q.shape
+    Hkv = k.shape[2]
+    delta = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
+    st = _lib.status_tensor(q.device)
+    err = _lib_fns().ats_attn_bwd(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),
+                                  Hkv * D, 0, _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk),
+                                  _lib.ptr(dv), dq.stride(1), dk.stride(1), B, L, Hq, Hkv, D, _lib.ptr(st), _lib.stream_ptr(q.device))
+    _lib.check(err, "ats_attn_bwd")
+
+
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v):
-        B, L, Hq, D = q.shape
-        Hkv = k.shape[2]
-        out = torch.empty(B, L, Hq, D, dtype=q.dtype, device=q.device)
-        lse = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
-        st = _lib.status_tensor(q.device)
-        err = _fn()(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1), Hkv * D, 0,
-                    _lib.ptr(out), _lib.ptr(lse), B, L, Hq, Hkv, D, _lib.ptr(st), _lib.stream_ptr(q.device))
-        _lib.check(err, "ats_attn_fwd")
+        out, lse = _fwd(q, k, v)
         ctx.save_for_backward(q, k, v, out, lse)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        with torch.enable_grad():
-            qd, kd, vd = [t.detach().requires_grad_() for t in (q, k, v)]
-            o = F.scaled_dot_product_attention(qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2), is_causal=True,
-                                               enable_gqa=q.shape[2] != k.shape[2]).transpose(1, 2)
-            dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), dout)
+        dout = dout.contiguous()
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        _bwd(q, k, v, out, dout, lse, dq, dk, dv)
         return dq, dk, dv
+
+
+class _FlashAttnPackedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, n_q, n_kv, d):
+        B, L, W = qkv.shape
+        nq, nk = n_q * d, n_kv * d
+        q = qkv[..., :nq].view(B, L, n_q, d)
+        k = qkv[..., nq:nq + nk].view(B, L, n_kv, d)
+        v = qkv[..., nq + nk:].view(B, L, n_kv, d)
+        out, lse = _fwd(q, k, v)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.dims = (n_q, n_kv, d)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        n_q, n_kv, d = ctx.dims
+        B, L, W = qkv.shape
+        nq, nk = n_q * d, n_kv * d
+        q = qkv[..., :nq].view(B, L, n_q, d)
+        k = qkv[..., nq:nq + nk].view(B, L, n_kv, d)
+        v = qkv[..., nq + nk:].view(B, L, n_kv, d)
+        dqkv = torch.empty_like(qkv)
+        _bwd(q, k, v, out, dout.contiguous(), lse, dqkv[..., :nq].view(B, L, n_q, d), dqkv[..., nq:nq + nk].view(B, L, n_kv, d),
+             dqkv[..., nq + nk:].view(B, L, n_kv, d))
+        return dqkv, None, None, None
 
 
 def flash_attention_native(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     return _FlashAttnFn.apply(q, k, v)
+
+
+def flash_attention_packed(qkv: torch.Tensor, n_q: int, n_kv: int, d: int) -> torch.Tensor:
+    """qkv: [B, L, (n_q + 2 n_kv) * d] contiguous -> [B, L, n_q, d]; causal, grouped-query."""
+    return _FlashAttnPackedFn.apply(qkv, n_q, n_kv, d)

@@ -538,6 +538,18 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     return attention_reference(q, k, v, causal, q_offset, key_mask)
 
 
+def attention_packed_available(qkv: torch.Tensor, d: int, seq_len: int) -> bool:
+    from . import attn as A
+    return (_lib.use_cuda_kernels(qkv) and A._native_available() and d in (64, 128) and seq_len % 128 == 0 and qkv.is_contiguous()
+            and qkv.shape[-1] % 8 == 0)
+
+
+def attention_packed(qkv: torch.Tensor, n_q: int, n_kv: int, d: int) -> torch.Tensor:
+    """Causal grouped-query attention straight on the packed projection [B, L, (n_q + 2 n_kv) * d] -> [B, L, n_q, d]."""
+    from .attention_native import flash_attention_packed
+    return flash_attention_packed(qkv, n_q, n_kv, d)
+
+
 # ----------------------------------------------------------------------------------------------------------
 # Optimiser / norm helpers (no autograd)
 # ----------------------------------------------------------------------------------------------------------

@@ -96,6 +96,18 @@ def main():
         from adaptivetrainingsystem_b200.ops import attn as A
         lib = time_cuda(lambda: torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True))
         report(f"attention_fwd[{A.backend_for(q, k)}] B{bsz} L{L} H{hq}/{hkv} d{d}", time_cuda(lambda: ops.attention(q, k, v)), fl, lib_ms=lib)
+        # backward alone: time (fwd + bwd) - fwd for both
+        go = rnd(bsz, L, hq, d)
+
+        def fb_ours():
+            qq, kk, vv = q.detach().requires_grad_(), k.detach().requires_grad_(), v.detach().requires_grad_()
+            ops.attention(qq, kk, vv).backward(go)
+
+        def fb_lib():
+            qq, kk, vv = q.detach().requires_grad_(), k.detach().requires_grad_(), v.detach().requires_grad_()
+            torch.nn.functional.scaled_dot_product_attention(qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=True,
+                                                             enable_gqa=True).backward(go.transpose(1, 2))
+        report(f"attention_fwd+bwd[{A.backend_for(q, k)}] B{bsz} L{L} H{hq}/{hkv} d{d}", time_cuda(fb_ours), fl * 3.5, lib_ms=time_cuda(fb_lib))
     ops.check_status()
     if args.json:
         with open(args.json, "w") as f:

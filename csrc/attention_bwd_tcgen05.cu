@@ -1,0 +1,410 @@
+// Causal grouped-query flash attention backward for sm_100a on tcgen05 tensor cores.
+//
+// Two passes share one kernel template (plus a tiny pre-pass delta = rowsum(dO * O)):
+//   MODE 0 (dK, dV): one CTA per (128-key tile j, kv head, batch).  K_j and V_j stay in shared memory; for every query
+//           head of the group and every query tile i >= j the CTA streams Q_i and dO_i, recomputes S = Q K^T and
+//           dP = dO V^T on the tensor cores, forms P = exp(S - lse) and dS = P * (dP - delta) * scale in registers, and
+//           accumulates dV += P^T dO and dK += dS^T Q in TMEM across all iterations (no atomics, deterministic).
+//   MODE 1 (dQ):     one CTA per (128-query tile i, query head, batch).  Q_i and dO_i stay resident, K_j / V_j stream for
+//           j <= i, and dQ += dS K accumulates in TMEM.
+// S and dP are recomputed in both passes (7 tile products per tile pair instead of 5) in exchange for an atomics-free,
+// deterministic dQ.  P and dS live in shared memory as [query x key] bf16 tiles in the 128-byte-swizzled layout, which
+// the same bytes serve both as a K-major operand (dS K) and as an MN-major operand (P^T dO, dS^T Q).
+//
+//   warp 0: TMA producer   warp 1: TMEM owner + MMA issuer   warps 2..5: one query row per thread
+// Every wait is bounded (status word + clean unwind); no load uses cluster multicast.
+//
+// Replaces the flash-attn / SDPA backward the reference relies on (reference core/model.py:763-768).
+#include "common.cuh"
+
+namespace ats {
+
+constexpr int AB_THREADS = 192;
+
+struct AttnBwdArgs {
+  int B, L, Hq, Hkv, D;
+  int q_col0, k_col0, v_col0;
+  const float* lse;    // [B, Hq, L] natural log
+  const float* delta;  // [B, Hq, L]
+  __nv_bfloat16* dq;   // row = token, pitch ld_dq elements, head h at column h * D
+  __nv_bfloat16* dk;   // row = token, pitch ld_dkv
+  __nv_bfloat16* dv;
+  long long ld_dq, ld_dkv;
+  float scale, scale_log2;
+  int* status;
+};
+
+template <int D, int MODE>
+struct AttnBwdSmem {
+  static constexpr int ST = (MODE == 1) ? 2 : (D == 64 ? 2 : 1);
+  static constexpr int TB = 128 * D * 2;
+  static constexpr int R1 = 0, R2 = TB;
+  static constexpr int T1 = 2 * TB;            // ST stages
+  static constexpr int T2 = T1 + ST * TB;      // ST stages
+  static constexpr int P_OFF = T2 + ST * TB;   // MODE 0 only
+  static constexpr int DS_OFF = P_OFF + (MODE == 0 ? 32768 : 0);
+  static constexpr int BAR_OFF = DS_OFF + 32768;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                  float* __restrict__ delta, int B, int L, int Hq, int D) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * L * Hq;
+  if (w >= total) return;
+  const int h = int(w % Hq);
+  const long long tok = w / Hq;
+  const int b = int(tok / L), i = int(tok % L);
+  const __nv_bfloat16* a = dout + w * D;
+  const __nv_bfloat16* o = out + w * D;
+  float acc = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + d));
+    float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + d));
+    acc += x.x * y.x + x.y * y.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[((long long)b * Hq + h) * L + i] = acc;
+}
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(AB_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const AttnBwdArgs p) {
+  using SM = AttnBwdSmem<D, MODE>;
+  constexpr int ST = SM::ST;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sR1 = smem + SM::R1;
+  uint8_t* sR2 = smem + SM::R2;
+  uint8_t* sT1 = smem + SM::T1;
+  uint8_t* sT2 = smem + SM::T2;
+  uint8_t* sP = smem + SM::P_OFF;
+  uint8_t* sDS = smem + SM::DS_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* res_full = bars;       // 1
+  uint64_t* t_full = bars + 1;     // [2]
+  uint64_t* t_empty = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;     // S and dP ready
+  uint64_t* sd_free = bars + 6;    // 4 arrivals: S / dP read out of TMEM
+  uint64_t* pds_full = bars + 7;   // 4 arrivals: P / dS written to shared memory
+  uint64_t* pds_free = bars + 8;   // accumulate MMAs have consumed P / dS
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = p.L / 128;
+  const int rep = p.Hq / p.Hkv;
+  const int b = blockIdx.z;
+  // fixed tile of this CTA and iteration space
+  int fixed, head, n_iter;
+  if (MODE == 0) {
+    fixed = blockIdx.x;  // key tile j (j = 0 has the most work and starts first)
+    head = blockIdx.y;   // kv head
+    n_iter = rep * (nq - fixed);
+  } else {
+    fixed = nq - 1 - blockIdx.x;  // query tile i, heaviest first
+    head = blockIdx.y;            // query head
+    n_iter = fixed + 1;
+  }
+  const int hk = MODE == 0 ? head : head / rep;
+
+  if (threadIdx.x == 0) {
+    mbar_init(res_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&t_full[s], 1);
+      mbar_init(&t_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(sd_free, 4);
+    mbar_init(pds_full, 4);
+    mbar_init(pds_free, 1);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_A1 = tmem_base + 256, tmem_A2 = tmem_base + 256 + D;
+
+  // iteration t -> (query head, query tile, key tile)
+  auto decode = [&](int t, int& h, int& qi, int& kj) {
+    if (MODE == 0) {
+      const int per = nq - fixed;
+      h = head * rep + t / per;
+      qi = fixed + t % per;
+      kj = fixed;
+    } else {
+      h = head;
+      qi = fixed;
+      kj = t;
+    }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ producer
+      mbar_expect_tx(res_full, 2 * SM::TB);
+      if (MODE == 0) {
+        const int row = b * p.L + fixed * 128;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_2d(sR1 + c * 16384, &map_k, res_full, p.k_col0 + hk * D + 64 * c, row);
+          tma_load_2d(sR2 + c * 16384, &map_v, res_full, p.v_col0 + hk * D + 64 * c, row);
+        }
+      } else {
+        const int row = b * p.L + fixed * 128;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_2d(sR1 + c * 16384, &map_q, res_full, p.q_col0 + head * D + 64 * c, row);
+          tma_load_2d(sR2 + c * 16384, &map_do, res_full, head * D + 64 * c, row);
+        }
+      }
+      for (int t = 0; t < n_iter; ++t) {
+        const int s = t % ST, ph = (t / ST) & 1;
+        int h, qi, kj;
+        decode(t, h, qi, kj);
+        if (!mbar_wait_bounded(&t_empty[s], ph ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_expect_tx(&t_full[s], 2 * SM::TB);
+        if (MODE == 0) {
+          const int row = b * p.L + qi * 128;
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            tma_load_2d(sT1 + s * SM::TB + c * 16384, &map_q, &t_full[s], p.q_col0 + h * D + 64 * c, row);
+            tma_load_2d(sT2 + s * SM::TB + c * 16384, &map_do, &t_full[s], h * D + 64 * c, row);
+          }
+        } else {
+          const int row = b * p.L + kj * 128;
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            tma_load_2d(sT1 + s * SM::TB + c * 16384, &map_k, &t_full[s], p.k_col0 + hk * D + 64 * c, row);
+            tma_load_2d(sT2 + s * SM::TB + c * 16384, &map_v, &t_full[s], p.v_col0 + hk * D + 64 * c, row);
+          }
+        }
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 20000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      const uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
+      const uint32_t idesc_acc0 = make_idesc(128, D, 1, 1, 1, 1);  // A^T B with both operands MN-major
+      const uint32_t idesc_acc1 = make_idesc(128, D, 1, 1, 0, 1);  // dS (K-major) x K (MN-major)
+      bool ok = mbar_wait_bounded(res_full, 0, abort_flag, p.status, kTimeoutFull);
+      for (int t = 0; ok && t < n_iter; ++t) {
+        const int s = t % ST, ph = (t / ST) & 1;
+        if (!mbar_wait_bounded(&t_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
+        if (!mbar_wait_bounded(sd_free, (t & 1) ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(MODE == 0 ? sT1 + s * SM::TB : sR1);
+        const uint32_t do_addr = smem_u32(MODE == 0 ? sT2 + s * SM::TB : sR2);
+        const uint32_t k_addr = smem_u32(MODE == 0 ? sR1 : sT1 + s * SM::TB);
+        const uint32_t v_addr = smem_u32(MODE == 0 ? sR2 : sT2 + s * SM::TB);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          tc_mma_f16(tmem_S, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          tc_mma_f16(tmem_dP, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, k != 0);
+        }
+        tc_commit(s_full);
+        if (!mbar_wait_bounded(pds_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+        if (MODE == 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // reduction over the 128 queries, 16 per step
+            tc_mma_f16(tmem_A1, make_smem_desc_sw128(p_addr + k * 2048, 16384, 1024),
+                       make_smem_desc_sw128(do_addr + k * 2048, 16384, 1024), idesc_acc0, (t | k) != 0);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            tc_mma_f16(tmem_A2, make_smem_desc_sw128(ds_addr + k * 2048, 16384, 1024),
+                       make_smem_desc_sw128(q_addr + k * 2048, 16384, 1024), idesc_acc0, (t | k) != 0);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // reduction over the 128 keys
+            tc_mma_f16(tmem_A1, make_smem_desc_sw128(ds_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                       make_smem_desc_sw128(k_addr + k * 2048, 16384, 1024), idesc_acc1, (t | k) != 0);
+          }
+        }
+        tc_commit(pds_free);
+        tc_commit(&t_empty[s]);
+      }
+      tc_commit(acc_done);
+    }
+  } else {
+    // -------------------------------------------------------------------- softmax-gradient threads (one query row each)
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    bool ok = true;
+    float lse2 = 0.f, dl = 0.f;
+    int cur_h = -1, cur_qi = -1;
+    for (int t = 0; t < n_iter; ++t) {
+      int h, qi, kj;
+      decode(t, h, qi, kj);
+      if (h != cur_h || qi != cur_qi) {
+        const long long idx = ((long long)b * p.Hq + h) * p.L + qi * 128 + r;
+        lse2 = p.lse[idx] * 1.4426950408889634f;
+        dl = p.delta[idx];
+        cur_h = h;
+        cur_qi = qi;
+      }
+      if (!mbar_wait_bounded(s_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // the accumulate MMAs of the previous iteration must be done with P / dS before they are overwritten
+      if (!mbar_wait_bounded(pds_free, (t & 1) ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) {
+        ok = false;
+        break;
+      }
+      const bool diag = (qi == kj);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tmem_S + lane_base + c * 32, sv);
+        tmem_ld_32x32(tmem_dP + lane_base + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = exp2f(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -lse2));
+          float p1 = exp2f(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -lse2));
+          if (diag) {
+            if (c * 32 + 2 * i > r) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > r) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dv[2 * i]) - dl) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - dl) * p.scale;
+          pk[i] = pack_bf16x2(p0, p1);
+          dk[i] = pack_bf16x2(d0, d1);
+        }
+        const int roff = (c >> 1) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
+          if (MODE == 0) *reinterpret_cast<uint4*>(sP + roff + chunk) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+          *reinterpret_cast<uint4*>(sDS + roff + chunk) = make_uint4(dk[4 * g], dk[4 * g + 1], dk[4 * g + 2], dk[4 * g + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sd_free);
+        mbar_arrive(pds_full);
+      }
+    }
+    if (ok && mbar_wait_bounded(acc_done, 0, abort_flag, p.status, kTimeoutTmemFull)) {
+      tc_fence_after();
+      const long long tok = (long long)b * p.L + fixed * 128 + r;
+      __nv_bfloat16* o1 = MODE == 0 ? p.dv + tok * p.ld_dkv + head * D : p.dq + tok * p.ld_dq + head * D;
+      __nv_bfloat16* o2 = MODE == 0 ? p.dk + tok * p.ld_dkv + head * D : nullptr;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_A1 + lane_base + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(o1 + c * 32 + g * 8) =
+              make_uint4(pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])), pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                         pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])), pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+        if (MODE == 0) {
+          tmem_ld_32x32(tmem_A2 + lane_base + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(o2 + c * 32 + g * 8) =
+                make_uint4(pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])), pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                           pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])), pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ats
+
+using namespace ats;
+
+template <int D, int MODE>
+static int launch_attn_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                           const AttnBwdArgs& p, cudaStream_t s) {
+  using SM = AttnBwdSmem<D, MODE>;
+  cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  if (ce != cudaSuccess) return int(ce);
+  dim3 grid(p.L / 128, MODE == 0 ? p.Hkv : p.Hq, p.B);
+  attn_bwd_kernel<D, MODE><<<grid, AB_THREADS, SM::TOTAL, s>>>(mq, mk, mv, mdo, p);
+  return int(cudaGetLastError());
+}
+
+// q/k/v as for ats_attn_fwd; out, dout: [B, L, Hq, D] contiguous; lse [B, Hq, L]; delta: fp32 scratch [B, Hq, L];
+// dq: rows = tokens with pitch ld_dq, dk / dv with pitch ld_dkv (so all three can be slices of one packed gradient).
+ATS_API int ats_attn_bwd(const void* q, long long ld_q, long long q_cols, int q_col0, const void* k, long long ld_k,
+                         long long k_cols, int k_col0, const void* v, long long ld_v, long long v_cols, int v_col0,
+                         const void* out, const void* dout, const float* lse, float* delta, void* dq, void* dk, void* dv,
+                         long long ld_dq, long long ld_dkv, int B, int L, int Hq, int Hkv, int D, int* status, void* stream) {
+  if ((D != 64 && D != 128) || (L % 128) || Hq % Hkv || (q_col0 & 7) || (k_col0 & 7) || (v_col0 & 7) || (ld_dq & 7) || (ld_dkv & 7))
+    return 1003;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap mq, mk, mv, mdo;
+  int e;
+  const unsigned long long rows = (unsigned long long)B * L;
+  if ((e = make_tmap_2d(&mq, q, rows, q_cols, ld_q, 2, 64, 128))) return e;
+  if ((e = make_tmap_2d(&mk, k, rows, k_cols, ld_k, 2, 64, 128))) return e;
+  if ((e = make_tmap_2d(&mv, v, rows, v_cols, ld_v, 2, 64, 128))) return e;
+  if ((e = make_tmap_2d(&mdo, dout, rows, (unsigned long long)Hq * D, (unsigned long long)Hq * D, 2, 64, 128))) return e;
+  const long long warps = (long long)B * L * Hq;
+  attn_delta_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout),
+                                                                      static_cast<const __nv_bfloat16*>(out), delta, B, L, Hq, D);
+  AttnBwdArgs p;
+  p.B = B; p.L = L; p.Hq = Hq; p.Hkv = Hkv; p.D = D;
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.lse = lse; p.delta = delta;
+  p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.ld_dq = ld_dq; p.ld_dkv = ld_dkv;
+  p.scale = 1.f / sqrtf(float(D));
+  p.scale_log2 = 1.4426950408889634f * p.scale;
+  p.status = status;
+  if (D == 128) {
+    if ((e = launch_attn_bwd<128, 0>(mq, mk, mv, mdo, p, s))) return e;
+    return launch_attn_bwd<128, 1>(mq, mk, mv, mdo, p, s);
+  }
+  if ((e = launch_attn_bwd<64, 0>(mq, mk, mv, mdo, p, s))) return e;
+  return launch_attn_bwd<64, 1>(mq, mk, mv, mdo, p, s);
+}

@@ -288,3 +288,10 @@ def test_flash_attention_tcgen05(B, L, hq, hkv, d):
     of.backward(g.float())
     _close(o, of, tol=2e-2, what="attention out")
     _close(qkv.grad, ref_in.grad, tol=3e-2, what="attention grads")
+    # the packed entry point (one gradient tensor for the whole projection)
+    qkv2 = qkv.detach().clone().requires_grad_()
+    assert ops.attention_packed_available(qkv2, d, L)
+    o2 = ops.attention_packed(qkv2, hq, hkv, d)
+    o2.backward(g)
+    _close(o2, of, tol=2e-2, what="packed attention out")
+    _close(qkv2.grad, ref_in.grad, tol=3e-2, what="packed attention grads")
