@@ -276,6 +276,7 @@ class Config:
     expert_parallel_size: Optional[int] = None
     # -- sharding (DeepSpeed-compatible names) -----------------------------
     use_deepspeed: bool = False
+    optimizer: str = "adamw"  # adamw | lamb | sgd
     zero_stage: int = 0
     cpu_offload: bool = False
     cpu_offload_optimizer: bool = False

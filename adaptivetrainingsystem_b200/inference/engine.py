@@ -50,7 +50,12 @@ def sample_next(logits: torch.Tensor, params: SamplingParams, history: Optional[
                 generator: Optional[torch.Generator] = None) -> torch.Tensor:
     """logits [B, V] -> token ids [B].  Order of operations as in the reference (``Chat.py:391-425``): repetition
     penalty over the last ``repetition_window`` tokens, temperature, top-k, top-p, multinomial; ``temperature <= 0``
-    is greedy."""
+    is greedy.  On a GPU the whole chain is one kernel launch per step (bisection on the logit values instead of a sort)."""
+    if logits.is_cuda and logits.dim() == 2:
+        from ..ops import serving
+        hist = history[:, -params.repetition_window:] if history is not None and history.numel() else None
+        return serving.sample_tokens(logits, params.temperature, params.top_k, params.top_p, params.repetition_penalty, hist,
+                                     generator=generator)
     lg = logits.float()
     if history is not None and params.repetition_penalty != 1.0 and history.numel():
         h = history[:, -params.repetition_window:]

@@ -124,6 +124,11 @@ class GroupedQueryAttention(nn.Module):
         if cache is None and attention_mask is None and ops.attention_packed_available(qkv, self.d, L):
             a = ops.attention_packed(qkv, self.n_q, self.n_kv, self.d)
             return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
+        if (cache is not None and L == 1 and attention_mask is None and positions is None
+                and ops.decode_attention_available(qkv, self.n_q, self.n_kv, self.d)):
+            # single-token step: the kernel appends K / V to the cache and attends in one pass over the cache
+            a = ops.decode_attention(qkv, cache.k[self.layer_idx], cache.v[self.layer_idx], cache.length, self.n_q, self.n_kv, self.d)
+            return ops.linear(a, self.o_proj, residual=residual)
         q = qkv[..., :nq].view(B, L, self.n_q, self.d)
         k = qkv[..., nq:nq + nk].view(B, L, self.n_kv, self.d)
         v = qkv[..., nq + nk:].view(B, L, self.n_kv, self.d)

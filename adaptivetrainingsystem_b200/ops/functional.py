@@ -131,8 +131,105 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Opti
     return rms_norm_reference(x, w, eps)
 
 
-def layer_norm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
+def layer_norm_reference(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
     return F.layer_norm(x.float(), (x.shape[-1],), w.float(), None if b is None else b.float(), eps).to(x.dtype)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H).contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        lib = _norm_lib()
+        _CK(lib.ats_layernorm_fwd(_P(x2), _P(w), _P(b), _P(y), _P(mean), _P(rstd), rows, H, eps, _S(x.device)), "ats_layernorm_fwd")
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.has_bias, ctx.shape = b is not None, x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, mean, rstd = ctx.saved_tensors
+        rows, H = x2.shape
+        dy2 = dy.reshape(rows, H).contiguous()
+        dx = torch.empty_like(x2)
+        blocks = max(1, min(rows, _NORM_BLOCKS))
+        partials = torch.empty(blocks, 2, H, dtype=torch.float32, device=x2.device)
+        dgamma = torch.empty(H, dtype=torch.float32, device=x2.device)
+        dbeta = torch.empty(H, dtype=torch.float32, device=x2.device) if ctx.has_bias else None
+        _CK(_norm_lib().ats_layernorm_bwd(_P(dy2), _P(x2), _P(w), _P(mean), _P(rstd), _P(dx), _P(partials), blocks, _P(dgamma), _P(dbeta),
+                                          rows, H, _S(x2.device)), "ats_layernorm_bwd")
+        return dx.view(ctx.shape), dgamma.to(w.dtype), None if dbeta is None else dbeta.to(w.dtype), None
+
+
+_norm_sig = False
+
+
+def _norm_lib():
+    global _norm_sig
+    lib = _lib.cuda_lib()
+    if not _norm_sig:
+        def sig(name, *args):
+            f = getattr(lib, name)
+            f.restype = _c_int
+            f.argtypes = list(args)
+        sig("ats_layernorm_fwd", _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_f, _vp)
+        sig("ats_layernorm_bwd", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _vp, _vp, _c_ll, _c_int, _vp)
+        sig("ats_masked_softmax_fwd", _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_int, _vp)
+        sig("ats_masked_softmax_bwd", _vp, _vp, _vp, _c_ll, _c_int, _c_f, _vp)
+        _norm_sig = True
+    return lib
+
+
+def layer_norm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm over the last dimension, optional bias (reference ``core/model.py:307-327``)."""
+    if _lib.use_cuda_kernels(x) and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return _LayerNormFn.apply(x, w, b, eps)
+    return layer_norm_reference(x, w, b, eps)
+
+
+def masked_softmax_reference(scores: torch.Tensor, mask: Optional[torch.Tensor], scale: float, causal: bool) -> torch.Tensor:
+    s = scores.float() * scale
+    Lq, Lk = scores.shape[-2], scores.shape[-1]
+    if causal:
+        qi = torch.arange(Lq, device=s.device)[:, None] + (Lk - Lq)
+        s = s.masked_fill(torch.arange(Lk, device=s.device)[None, :] > qi, float("-inf"))
+    if mask is not None:
+        s = s.masked_fill(mask.bool()[:, None], float("-inf"))
+    return torch.nan_to_num(torch.softmax(s, -1)).to(scores.dtype)
+
+
+class _MaskedSoftmaxFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, scores, mask, scale, causal):
+        B, Hh, Lq, Lk = scores.shape
+        x = scores.contiguous()
+        y = torch.empty_like(x)
+        m8 = None if mask is None else mask.to(torch.uint8).contiguous()
+        _CK(_norm_lib().ats_masked_softmax_fwd(_P(x), _P(m8), _P(y), B * Hh * Lq, Lk, Hh, Lq, scale, int(causal), _S(x.device)),
+            "ats_masked_softmax_fwd")
+        ctx.save_for_backward(y)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        dx = torch.empty_like(y)
+        _CK(_norm_lib().ats_masked_softmax_bwd(_P(dy.contiguous()), _P(y), _P(dx), y.numel() // y.shape[-1], y.shape[-1], ctx.scale,
+                                               _S(y.device)), "ats_masked_softmax_bwd")
+        return dx, None, None, None
+
+
+def masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False) -> torch.Tensor:
+    """softmax(scale * scores) over keys.  scores: [B, heads, Lq, Lk]; mask: [B, Lq, Lk] with True / 1 = masked out (shared
+    by the heads); ``causal`` hides key j > query i + (Lk - Lq).  Fully masked rows give zeros."""
+    if _lib.use_cuda_kernels(scores) and scores.dim() == 4:
+        return _MaskedSoftmaxFn.apply(scores, mask, float(scale), bool(causal))
+    return masked_softmax_reference(scores, mask, scale, causal)
 
 
 # ----------------------------------------------------------------------------------------------------------

@@ -81,6 +81,15 @@ class Bucket:
         for p in self.params:
             p._ats_grad_fresh = True
 
+    def segments_in(self, lo: int, hi: int) -> List[Tuple[int, int, int]]:
+        """(start relative to lo, length, parameter index) of every parameter's part inside [lo, hi) (per-tensor optimisers)."""
+        out = []
+        for i, (p, o) in enumerate(zip(self.params, self.offsets)):
+            a, b = max(o, lo), min(o + p.numel(), hi)
+            if b > a:
+                out.append((a - lo, b - a, i))
+        return out
+
     def collect_autograd_grads(self) -> None:
         """Gradients that arrived through plain autograd (``p.grad``) are folded into the flat buffer; parameters
         that received nothing this step are zeroed."""
@@ -103,8 +112,16 @@ class ShardedEngine:
 
     def __init__(self, model: nn.Module, lr: float = 1e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_grad_norm: float = 1.0, zero_stage: int = 1,
-                 mesh: Optional[ProcessMesh] = None, fused_comm=None, grad_accumulation_steps: int = 1):
+                 mesh: Optional[ProcessMesh] = None, fused_comm=None, grad_accumulation_steps: int = 1,
+                 optimizer: str = "adamw", optimizer_kwargs: Optional[Dict[str, Any]] = None):
         self.model = model
+        # "adamw" runs the built-in (and peer-memory fused) path; "lamb", "sgd" and "adamw_host" (optimiser state offloaded
+        # to pinned host memory) go through an update rule of the optim package
+        self.optimizer_name = optimizer.lower()
+        self.rule = None
+        if self.optimizer_name != "adamw":
+            from ..optim import make_rule
+            self.rule = make_rule(self.optimizer_name, **(optimizer_kwargs or {}))
         self.mesh = mesh or ProcessMesh(create_groups=False)
         self.zero_stage = zero_stage
         self.max_grad_norm = max_grad_norm
@@ -204,7 +221,7 @@ class ShardedEngine:
         self.step_count += 1
         self._hyper_host[5] = float(self.step_count)
         self.hyper[5] = float(self.step_count)
-        if self.fused is not None and self.fused.usable(self):
+        if self.rule is None and self.fused is not None and self.fused.usable(self):
             # reduce-scatter, norm, AdamW and all-gather done by peer-memory kernels (parallel/fused.py)
             self.fused.step(self)
             self.zero_grad()
@@ -229,8 +246,16 @@ class ShardedEngine:
         ops.clip_coef(self.sumsq, self.clip_state, scale, self.max_grad_norm)
         for b, g in zip(self.buckets, reduced):
             lo, hi = b.owned_range()
-            ops.adamw_step(b.master, b.exp_avg, b.exp_avg_sq, g, b.flat_param[lo:hi], self.hyper, self.clip_state,
-                           1.0 if b.decay else 0.0)
+            if self.rule is None:
+                ops.adamw_step(b.master, b.exp_avg, b.exp_avg_sq, g, b.flat_param[lo:hi], self.hyper, self.clip_state,
+                               1.0 if b.decay else 0.0)
+            else:
+                if getattr(b, "rule_state", None) is None:
+                    b.rule_state = self.rule.init_state(b.master)
+                    if self.optimizer_name == "adamw_host":  # the device copies of the state are not needed any more
+                        b.exp_avg = b.exp_avg_sq = torch.zeros(0, device=self.device)
+                self.rule.update(b.rule_state, b.master, g, b.flat_param[lo:hi], self.hyper, self.clip_state, b.decay,
+                                 segments=b.segments_in(lo, hi), group=b.group if b.shard_states and b.W > 1 else None)
             self._gather(b)
         self.zero_grad()
         self.last_grad_norm = self.clip_state[1]

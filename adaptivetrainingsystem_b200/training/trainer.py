@@ -98,7 +98,12 @@ class EnhancedConversationTrainer:
             from ..parallel.zero3 import ZeRO3Engine
             self.engine = ZeRO3Engine(model, **opt)  # per-block gather / release; expert-parallel models use stage <= 2
         else:
-            self.engine = ShardedEngine(model, zero_stage=min(self.config.zero_stage, 2), fused_comm=fused_comm, **opt)
+            # optimiser choice: config.optimizer ("adamw" | "lamb" | "sgd"); the offload flags of the reference's DeepSpeed
+            # section (cpu_offload / cpu_offload_optimizer) move the AdamW state to pinned host memory
+            name = str(getattr(self.config, "optimizer", "adamw")).lower()
+            if name == "adamw" and (self.config.cpu_offload or self.config.cpu_offload_optimizer):
+                name = "adamw_host"
+            self.engine = ShardedEngine(model, zero_stage=min(self.config.zero_stage, 2), fused_comm=fused_comm, optimizer=name, **opt)
         self.optimizer = self.engine  # reference attribute name
         self.scheduler = None
         self.use_deepspeed = False

@@ -11,7 +11,7 @@
 // deterministic dQ.  P and dS live in shared memory as [query x key] bf16 tiles in the 128-byte-swizzled layout, which
 // the same bytes serve both as a K-major operand (dS K) and as an MN-major operand (P^T dO, dS^T Q).
 //
-//   warp 0: TMA producer   warp 1: TMEM owner + MMA issuer   warps 2..5: one query row per thread
+//   warp 0: TMA producer   warp 1: TMEM owner + MMA issuer   warps 2..9: two threads per query row (64 key columns each)
 // Every wait is bounded (status word + clean unwind); no load uses cluster multicast.
 //
 // Replaces the flash-attn / SDPA backward the reference relies on (reference core/model.py:763-768).
@@ -19,7 +19,7 @@
 
 namespace ats {
 
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;  // TMA warp, MMA warp, 8 softmax-gradient warps
 
 struct AttnBwdArgs {
   int B, L, Hq, Hkv, D;
@@ -87,8 +87,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* t_full = bars + 1;     // [2]
   uint64_t* t_empty = bars + 3;    // [2]
   uint64_t* s_full = bars + 5;     // S and dP ready
-  uint64_t* sd_free = bars + 6;    // 4 arrivals: S / dP read out of TMEM
-  uint64_t* pds_full = bars + 7;   // 4 arrivals: P / dS written to shared memory
+  uint64_t* sd_free = bars + 6;    // 8 arrivals: S / dP read out of TMEM
+  uint64_t* pds_full = bars + 7;   // 8 arrivals: P / dS written to shared memory
   uint64_t* pds_free = bars + 8;   // accumulate MMAs have consumed P / dS
   uint64_t* acc_done = bars + 9;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
@@ -118,8 +118,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_init(&t_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(sd_free, 4);
-    mbar_init(pds_full, 4);
+    mbar_init(sd_free, 8);
+    mbar_init(pds_full, 8);
     mbar_init(pds_free, 1);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -254,8 +254,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_commit(acc_done);
     }
   } else {
-    // -------------------------------------------------------------------- softmax-gradient threads (one query row each)
+    // ---------------------------------------- softmax-gradient threads: a TMEM lane quadrant is open to warps with the
+    // same (warp % 4), so warps w and w + 4 share 32 query rows and take 64 key columns each
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
     bool ok = true;
@@ -283,7 +285,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       const bool diag = (qi == kj);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tmem_S + lane_base + c * 32, sv);
         tmem_ld_32x32(tmem_dP + lane_base + c * 32, dv);
@@ -324,7 +326,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       __nv_bfloat16* o1 = MODE == 0 ? p.dv + tok * p.ld_dkv + head * D : p.dq + tok * p.ld_dq + head * D;
       __nv_bfloat16* o2 = MODE == 0 ? p.dk + tok * p.ld_dkv + head * D : nullptr;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_A1 + lane_base + c * 32, v);
         tmem_ld_wait();

@@ -185,15 +185,9 @@ struct SampleArgs {
   int top_k;
 };
 
-__device__ __forceinline__ int block_count(bool pred, int* red) {
-  const int c = __syncthreads_count(pred);
-  (void)red;
-  return c;
-}
-
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const SampleArgs p) {
   __shared__ float red[33];
-  __shared__ int s_arg;
+  __shared__ int s_arg, s_pick;
   __shared__ float s_scan[SMP_THREADS / 32 + 1];
   const int b = blockIdx.x, tid = threadIdx.x, V = p.V;
   float* w = p.work + (long long)b * V;
@@ -293,7 +287,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const SampleArgs p)
   const float base = (warp ? s_scan[warp - 1] : 0.f) + incl - local;
   const float total = s_scan[32];
   const float target = p.uniform[b] * total;
-  if (tid == 0) s_arg = V;
+  if (tid == 0) s_pick = V;
   __syncthreads();
   if (local > 0.f && target >= base && target < base + local) {
     float run = base;
@@ -305,22 +299,11 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const SampleArgs p)
         if (target < run) break;
       }
     }
-    if (pick >= 0) atomicMin(&s_arg, pick);
+    if (pick >= 0) atomicMin(&s_pick, pick);
   }
   __syncthreads();
-  if (tid == 0) {
-    // rounding can leave the target just past the last segment: fall back to the arg-max, which is always kept
-    if (s_arg >= V) {
-      int a = V;
-      (void)a;
-    }
-    p.out[b] = s_arg;
-  }
-}
-
-__global__ void sample_fixup_kernel(long long* out, const long long* fallback, int B, int V) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < B && (out[i] < 0 || out[i] >= V)) out[i] = fallback[i];
+  // rounding can leave the target just past the last kept element: fall back to the arg-max, which is always kept
+  if (tid == 0) p.out[b] = s_pick < V ? s_pick : s_arg;
 }
 
 }  // namespace ats

@@ -295,3 +295,127 @@ def test_flash_attention_tcgen05(B, L, hq, hkv, d):
     o2.backward(g)
     _close(o2, of, tol=2e-2, what="packed attention out")
     _close(qkv2.grad, ref_in.grad, tol=3e-2, what="packed attention grads")
+
+
+@pytest.mark.parametrize("B,hq,hkv,d,length", [(4, 32, 4, 64, 700), (3, 32, 8, 128, 255), (2, 8, 8, 64, 0), (5, 16, 8, 128, 1279)])
+def test_decode_attention(B, hq, hkv, d, length):
+    from adaptivetrainingsystem_b200.ops import serving
+    torch.manual_seed(21)
+    max_len = 1280
+    kc = _rand(B, max_len, hkv, d)
+    vc = _rand(B, max_len, hkv, d)
+    qkv = _rand(B, 1, (hq + 2 * hkv) * d)
+    assert serving.decode_attention_available(qkv, hq, hkv, d)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    out = serving.decode_attention(qkv, kc, vc, length, hq, hkv, d)
+    ref = serving.decode_attention_reference(qkv.float(), kc_ref, vc_ref, length, hq, hkv, d)
+    _close(out, ref, tol=2e-2, what="decode attention")
+    assert torch.equal(kc[:, length], kc_ref[:, length]) and torch.equal(vc[:, length], vc_ref[:, length])
+    # per-sequence lengths
+    lens = torch.randint(0, max_len - 1, (B,), dtype=torch.int32, device="cuda")
+    kc2, vc2 = kc_ref.clone(), vc_ref.clone()
+    out2 = serving.decode_attention(qkv, kc2, vc2, lens, hq, hkv, d)
+    ref2 = serving.decode_attention_reference(qkv.float(), kc_ref, vc_ref, lens, hq, hkv, d)
+    _close(out2, ref2, tol=2e-2, what="decode attention (ragged)")
+
+
+def test_sampling_kernel():
+    from adaptivetrainingsystem_b200.ops import serving
+    torch.manual_seed(5)
+    B, V = 64, 32000
+    logits = (torch.randn(B, V, device="cuda") * 3).float()
+    hist = torch.randint(0, V, (B, 50), device="cuda")
+    # greedy and top-k = 1 are the arg-max of the penalised logits
+    g = serving.sample_tokens(logits, 0.0, 0, 1.0, 1.2, hist)
+    assert torch.equal(g, serving.sample_reference(logits, 0.0, 0, 1.0, 1.2, hist))
+    u = torch.rand(B, device="cuda")
+    assert torch.equal(serving.sample_tokens(logits, 0.8, 1, 1.0, 1.0, None, u), logits.argmax(-1))
+    for (t, k, p, rp) in [(0.8, 50, 0.9, 1.1), (1.0, 0, 0.95, 1.0), (0.5, 40, 1.0, 1.15), (1.0, 0, 1.0, 1.0)]:
+        got = serving.sample_tokens(logits, t, k, p, rp, hist, u)
+        ref = serving.sample_reference(logits, t, k, p, rp, hist, u)
+        agree = (got == ref).float().mean().item()
+        assert agree >= 0.9, f"sampling agreement {agree} at T={t} k={k} p={p}"
+        # every drawn token lies in the kept set of the reference (non-zero probability after filtering)
+        lg = logits.clone()
+        picked = torch.gather(lg, 1, hist)
+        lg = lg.scatter(1, hist, torch.where(picked > 0, picked / rp, picked * rp)) / t
+        if k:
+            kth = torch.topk(lg, k, dim=-1).values[:, -1:]
+            assert (torch.gather(lg, 1, got[:, None]) >= kth).all()
+    # bf16 logits take the same path
+    gb = serving.sample_tokens(logits.bfloat16(), 0.0, 0, 1.0)
+    lb = logits.bfloat16().float()
+    assert torch.equal(torch.gather(lb, 1, gb[:, None]).squeeze(1), lb.max(-1).values)
+    # the distribution: many draws of one row follow softmax
+    row = torch.randn(1, 64, device="cuda").repeat(4096, 1)
+    draws = serving.sample_tokens(row.contiguous(), 1.0, 0, 1.0)
+    freq = torch.bincount(draws, minlength=64).float() / 4096
+    assert (freq - torch.softmax(row[0], -1)).abs().max().item() < 0.03
+
+
+def test_layer_norm_kernel():
+    torch.manual_seed(3)
+    x = _rand(1000, 2048).requires_grad_()
+    w = (1 + 0.1 * _rand(2048)).detach().requires_grad_()
+    b = (0.1 * _rand(2048)).detach().requires_grad_()
+    g = _rand(1000, 2048)
+    y = ops.layer_norm(x, w, b, 1e-5)
+    y.backward(g)
+    xf, wf, bf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yf = ops.layer_norm_reference(xf, wf, bf, 1e-5)
+    yf.backward(g.float())
+    _close(y, yf, tol=2e-2, what="layernorm out")
+    _close(x.grad, xf.grad, tol=2e-2, what="layernorm dx")
+    _close(w.grad, wf.grad, tol=2e-2, what="layernorm dgamma")
+    _close(b.grad, bf.grad, tol=2e-2, what="layernorm dbeta")
+    # without bias
+    y2 = ops.layer_norm(x.detach(), w.detach(), None, 1e-5)
+    _close(y2, ops.layer_norm_reference(xf.detach(), wf.detach(), None, 1e-5), tol=2e-2, what="layernorm no-bias")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_masked_softmax_kernel(causal):
+    torch.manual_seed(4)
+    B, H, Lq, Lk = 2, 4, 96, 160
+    s = (_rand(B, H, Lq, Lk) * 4).requires_grad_()
+    mask = torch.rand(B, Lq, Lk, device="cuda") < 0.2
+    mask[0, 5] = True  # a fully masked row
+    g = _rand(B, H, Lq, Lk)
+    y = ops.masked_softmax(s, mask, 0.125, causal)
+    y.backward(g)
+    sf = s.detach().float().requires_grad_()
+    yf = ops.masked_softmax_reference(sf, mask, 0.125, causal)
+    yf.backward(g.float())
+    _close(y, yf, tol=2e-2, what="masked softmax")
+    _close(s.grad, sf.grad, tol=3e-2, what="masked softmax grad")
+    assert float(y[0, :, 5].abs().sum()) == 0.0
+
+
+def test_extra_optimizer_kernels():
+    from adaptivetrainingsystem_b200 import optim
+    torch.manual_seed(6)
+    n = 100_003
+    hyper = torch.tensor([1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0], device="cuda")
+    clip = torch.tensor([0.5, 0.0, 0.0, 0.0], device="cuda")
+    for name, kw in (("sgd", dict(momentum=0.9, nesterov=True)), ("lamb", {})):
+        w0 = torch.randn(n, device="cuda")
+        segs = [(0, 60_000, 0), (60_000, n - 60_000, 1)]
+        dev_rule, cpu_rule = optim.make_rule(name, **kw), optim.make_rule(name, **kw)
+        md, mc = w0.clone(), w0.cpu().clone()
+        sd, sc = dev_rule.init_state(md), cpu_rule.init_state(mc)
+        od, oc = torch.zeros(n, dtype=torch.bfloat16, device="cuda"), torch.zeros(n, dtype=torch.bfloat16)
+        for step in range(1, 4):
+            g = torch.randn(n, device="cuda").bfloat16()
+            hyper[5] = float(step)
+            dev_rule.update(sd, md, g, od, hyper, clip, True, segments=segs)
+            cpu_rule.update(sc, mc, g.cpu(), oc, hyper.cpu(), clip.cpu(), True, segments=segs)
+        assert torch.allclose(md.cpu(), mc, atol=1e-5, rtol=1e-4), name
+        assert torch.equal(od.cpu(), md.bfloat16().cpu()), name
+    x = torch.randn(50_000, device="cuda").bfloat16()
+    out, flag = optim.scale_check(x, 0.25)
+    assert torch.equal(out, x.float() * 0.25) and int(flag) == 0
+    x[123] = float("inf")
+    _, flag = optim.scale_check(x, 0.25)
+    assert int(flag) == 1
+    x[123] = -7.5
+    assert float(optim.absmax(x)) == float(x.float().abs().max())
