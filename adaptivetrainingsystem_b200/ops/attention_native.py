@@ -8,6 +8,7 @@ never has to zero-pad and add three sliced gradients.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -24,6 +25,9 @@ def _lib_fns():
         lib.ats_attn_fwd.restype = _ci
         lib.ats_attn_fwd.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp,
                                      _ci, _ci, _ci, _ci, _ci, _vp, _vp]
+        lib.ats_attn_fwd2.restype = _ci
+        lib.ats_attn_fwd2.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp,
+                                      _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp]
         lib.ats_attn_bwd.restype = _ci
         lib.ats_attn_bwd.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                      _cll, _cll, _ci, _ci, _ci, _ci, _ci, _vp, _vp]
@@ -38,12 +42,23 @@ def layout_ok(t: torch.Tensor) -> bool:
     return (s[3] == 1 and s[2] == D and s[0] == L * s[1] and s[1] % 8 == 0 and t.data_ptr() % 16 == 0)
 
 
+# Forward variant: "v1" = one query tile per CTA; "v2s" / "v2t" = two query tiles per CTA with the probabilities staged
+# through shared memory / tensor memory (sequence length must be a multiple of 256, else v1 runs).
+FWD_VARIANT = os.environ.get("ATS_ATTN_FWD", "v2t")
+
+
 def _fwd(q, k, v):
     B, L, Hq, D = q.shape
     Hkv = k.shape[2]
     out = torch.empty(B, L, Hq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
     st = _lib.status_tensor(q.device)
+    if FWD_VARIANT != "v1" and L % 256 == 0:
+        err = _lib_fns().ats_attn_fwd2(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),
+                                       Hkv * D, 0, _lib.ptr(out), _lib.ptr(lse), B, L, Hq, Hkv, D, int(FWD_VARIANT == "v2t"), _lib.ptr(st),
+                                       _lib.stream_ptr(q.device))
+        _lib.check(err, "ats_attn_fwd2")
+        return out, lse
     err = _lib_fns().ats_attn_fwd(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),
                                   Hkv * D, 0, _lib.ptr(out), _lib.ptr(lse), B, L, Hq, Hkv, D, _lib.ptr(st), _lib.stream_ptr(q.device))
     _lib.check(err, "ats_attn_fwd")

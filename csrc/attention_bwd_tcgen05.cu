@@ -206,12 +206,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
       const uint32_t idesc_acc0 = make_idesc(128, D, 1, 1, 1, 1);  // A^T B with both operands MN-major
       const uint32_t idesc_acc1 = make_idesc(128, D, 1, 1, 0, 1);  // dS (K-major) x K (MN-major)
-      bool ok = mbar_wait_bounded(res_full, 0, abort_flag, p.status, kTimeoutFull);
-      for (int t = 0; ok && t < n_iter; ++t) {
-        const int s = t % ST, ph = (t / ST) & 1;
-        if (!mbar_wait_bounded(&t_full[s], ph, abort_flag, p.status, kTimeoutFull)) break;
-        if (!mbar_wait_bounded(sd_free, (t & 1) ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
-        tc_fence_after();
+      auto issue_scores = [&](int t) {  // S = Q K^T and dP = dO V^T of iteration t
+        const int s = t % ST;
         const uint32_t q_addr = smem_u32(MODE == 0 ? sT1 + s * SM::TB : sR1);
         const uint32_t do_addr = smem_u32(MODE == 0 ? sT2 + s * SM::TB : sR2);
         const uint32_t k_addr = smem_u32(MODE == 0 ? sR1 : sT1 + s * SM::TB);
@@ -227,8 +223,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tc_mma_f16(tmem_dP, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, k != 0);
         }
         tc_commit(s_full);
-        if (!mbar_wait_bounded(pds_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
-        tc_fence_after();
+      };
+      auto issue_acc = [&](int t) {  // the gradient products that consume P / dS of iteration t
+        const int s = t % ST;
+        const uint32_t q_addr = smem_u32(MODE == 0 ? sT1 + s * SM::TB : sR1);
+        const uint32_t do_addr = smem_u32(MODE == 0 ? sT2 + s * SM::TB : sR2);
+        const uint32_t k_addr = smem_u32(MODE == 0 ? sR1 : sT1 + s * SM::TB);
         const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
         if (MODE == 0) {
 #pragma unroll
@@ -250,6 +250,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tc_commit(pds_free);
         tc_commit(&t_empty[s]);
+      };
+      bool ok = mbar_wait_bounded(res_full, 0, abort_flag, p.status, kTimeoutFull);
+      if (ST >= 2) {
+        // The scores of iteration t + 1 are issued as soon as the soft-max threads have S / dP of iteration t in registers,
+        // so the tensor cores work on them while those threads do the exponentials of iteration t.
+        ok = ok && mbar_wait_bounded(&t_full[0], 0, abort_flag, p.status, kTimeoutFull);
+        if (ok) {
+          tc_fence_after();
+          issue_scores(0);
+        }
+        for (int t = 0; ok && t < n_iter; ++t) {
+          if (t + 1 < n_iter) {
+            if (!mbar_wait_bounded(&t_full[(t + 1) % ST], ((t + 1) / ST) & 1, abort_flag, p.status, kTimeoutFull)) break;
+            if (!mbar_wait_bounded(sd_free, t & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+            tc_fence_after();
+            issue_scores(t + 1);
+          }
+          if (!mbar_wait_bounded(pds_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+          tc_fence_after();
+          issue_acc(t);
+        }
+      } else {
+        // one streamed stage: the next tile can only be fetched after this iteration's products, so the order is serial
+        for (int t = 0; ok && t < n_iter; ++t) {
+          if (!mbar_wait_bounded(&t_full[0], t & 1, abort_flag, p.status, kTimeoutFull)) break;
+          if (!mbar_wait_bounded(sd_free, (t & 1) ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+          tc_fence_after();
+          issue_scores(t);
+          if (!mbar_wait_bounded(pds_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+          tc_fence_after();
+          issue_acc(t);
+        }
       }
       tc_commit(acc_done);
     }
@@ -278,47 +310,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         break;
       }
       tc_fence_after();
-      // the accumulate MMAs of the previous iteration must be done with P / dS before they are overwritten
+      // this thread's half row of S and dP -> registers; the TMEM tiles are then free for the next iteration's scores
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(tmem_S + lane_base + half * 64, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+      tmem_ld_32x32(tmem_S + lane_base + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+      tmem_ld_32x32(tmem_dP + lane_base + half * 64, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
+      tmem_ld_32x32(tmem_dP + lane_base + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sd_free);
+      // P = exp2(S * scale_log2 - lse2), dS = P * (dP - delta) * scale, two elements per packed fp32x2 instruction
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
+      const float2 ndl2 = make_float2(-dl, -dl), scale2 = make_float2(p.scale, p.scale);
+      const bool diag = (qi == kj);
+      uint32_t pk[32], dk[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float2 xs = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sc2, nl2);
+        float2 pr = make_float2(exp2f(xs.x), exp2f(xs.y));
+        if (diag) {
+          if (half * 64 + 2 * i > r) pr.x = 0.f;
+          if (half * 64 + 2 * i + 1 > r) pr.y = 0.f;
+        }
+        const float2 dd = __fmul2_rn(__fmul2_rn(pr, scale2), __fadd2_rn(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), ndl2));
+        pk[i] = pack_bf16x2(pr.x, pr.y);
+        dk[i] = pack_bf16x2(dd.x, dd.y);
+      }
+      // the gradient products of the previous iteration must be done with P / dS before they are overwritten
       if (!mbar_wait_bounded(pds_free, (t & 1) ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) {
         ok = false;
         break;
       }
-      const bool diag = (qi == kj);
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tmem_S + lane_base + c * 32, sv);
-        tmem_ld_32x32(tmem_dP + lane_base + c * 32, dv);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
+      {
+        const int roff = half * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -lse2));
-          float p1 = exp2f(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -lse2));
-          if (diag) {
-            if (c * 32 + 2 * i > r) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > r) p1 = 0.f;
-          }
-          const float d0 = p0 * (__uint_as_float(dv[2 * i]) - dl) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - dl) * p.scale;
-          pk[i] = pack_bf16x2(p0, p1);
-          dk[i] = pack_bf16x2(d0, d1);
-        }
-        const int roff = (c >> 1) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = (((c & 1) * 4 + g) ^ (r & 7)) << 4;
+        for (int g = 0; g < 8; ++g) {
+          const int chunk = (g ^ (r & 7)) << 4;
           if (MODE == 0) *reinterpret_cast<uint4*>(sP + roff + chunk) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
           *reinterpret_cast<uint4*>(sDS + roff + chunk) = make_uint4(dk[4 * g], dk[4 * g + 1], dk[4 * g + 2], dk[4 * g + 3]);
         }
       }
-      tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(sd_free);
-        mbar_arrive(pds_full);
-      }
+      if (lane == 0) mbar_arrive(pds_full);
     }
     if (ok && mbar_wait_bounded(acc_done, 0, abort_flag, p.status, kTimeoutTmemFull)) {
       tc_fence_after();

@@ -1,0 +1,364 @@
+// Causal grouped-query flash attention forward for sm_100a, two query tiles per CTA.
+//
+// One CTA owns 256 consecutive queries of one head as two 128-row tiles (A, B).  Both tiles score against the same
+// K / V stream (every K / V tile is fetched once for 256 queries) and ping-pong on the tensor cores: while the four
+// soft-max warps of tile A work on S_A(j), the tensor cores compute S_B(j) and the P V product of the tile that finished
+// before.  The output accumulators O_A / O_B stay in tensor memory for the whole row sweep; a soft-max thread rescales
+// its row of O only when the running maximum has grown by more than 2^8 (a stale maximum cancels in O / l, so the result
+// is exact), which removes the per-block round trip of the accumulator.
+//
+//   warps 0..3   soft-max of tile A, one query row per thread (S row read from TMEM in one go)
+//   warps 4..7   soft-max of tile B
+//   warp 8       TMA producer: Q_A, Q_B once, then K_j / V_j through a multi-stage ring
+//   warp 9       TMEM owner and MMA issuer, order per block: P V (A), S_A(j+1), P V (B), S_B(j+1)
+// A soft-max thread holds a whole 128-element score row in registers (168 registers per thread, no spills); the rare
+// accumulator rescale works in 16-column pieces to stay inside that budget.
+//
+// PT = true keeps P in tensor memory (bf16 pairs written over the first 64 columns of the S tile, read by the MMA as
+// its A operand); PT = false stages P through shared memory in the 128-byte-swizzled K-major layout.
+// Every wait is bounded (status word + clean unwind); no load uses cluster multicast.
+// Replaces flash_attn_func of the reference model (reference core/model.py:763-768) without expanding K / V per query head.
+#include "common.cuh"
+
+namespace ats {
+
+constexpr int A2_THREADS = 320;  // soft-max A (warps 0-3), soft-max B (4-7), TMA (8), MMA (9)
+
+struct Attn2Args {
+  int B, L, Hq, Hkv;
+  int q_col0, k_col0, v_col0;
+  __nv_bfloat16* out;  // [B, L, Hq, D]
+  float* lse;          // [B, Hq, L]
+  float scale_log2;
+  int* status;
+};
+
+template <int D, bool PT>
+struct Attn2Smem {
+  static constexpr int TB = 128 * D * 2;
+  static constexpr int KST = (D == 64) ? 3 : 2;
+  static constexpr int VST = (D == 64) ? 3 : (PT ? 2 : 1);
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = 2 * TB;
+  static constexpr int V_OFF = K_OFF + KST * TB;
+  static constexpr int P_OFF = V_OFF + VST * TB;
+  static constexpr int BAR_OFF = P_OFF + (PT ? 0 : 65536);
+  static constexpr int TOTAL = BAR_OFF + 512 + 1024;
+};
+
+template <int D, bool PT>
+__global__ void __launch_bounds__(A2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const Attn2Args p) {
+  using SM = Attn2Smem<D, PT>;
+  constexpr int TB = SM::TB, KST = SM::KST, VST = SM::VST;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + SM::Q_OFF;
+  uint8_t* sK = smem + SM::K_OFF;
+  uint8_t* sV = smem + SM::V_OFF;
+  uint8_t* sP = smem + SM::P_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* q_full = bars;         // 1
+  uint64_t* k_full = bars + 1;     // [3]
+  uint64_t* k_empty = bars + 4;    // [3]
+  uint64_t* v_full = bars + 7;     // [3]
+  uint64_t* v_empty = bars + 10;   // [3]
+  uint64_t* s_full = bars + 13;    // [2] per tile
+  uint64_t* s_empty = bars + 15;   // [2] per tile, 4 arrivals (PT = false only)
+  uint64_t* p_full = bars + 17;    // [2] per tile, 4 arrivals
+  uint64_t* o_done = bars + 19;    // [2] per tile: last P V finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = gridDim.x - 1 - blockIdx.x;  // pair index, heaviest first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int nbA = 2 * t + 1, nbB = 2 * t + 2;  // key blocks seen by tile A / tile B
+  const int row0 = b * p.L + t * 256;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&s_full[x], 1);
+      mbar_init(&s_empty[x], 4);
+      mbar_init(&p_full[x], 4);
+      mbar_init(&o_done[x], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // columns: S_A [0,128)  S_B [128,256)  O_A [256, 256+D)  O_B [256+D, 256+2D)
+
+  if (warp == 8) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ producer
+      mbar_expect_tx(q_full, 2 * TB);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(sQ + x * TB + c * 16384, &map_q, q_full, p.q_col0 + h * D + 64 * c, row0 + x * 128);
+      for (int j = 0; j < nbB; ++j) {
+        const int krow = b * p.L + j * 128;
+        const int sk = j % KST, sv = j % VST;
+        if (!mbar_wait_bounded(&k_empty[sk], ((j / KST) & 1) ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_expect_tx(&k_full[sk], TB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(sK + sk * TB + c * 16384, &map_k, &k_full[sk], p.k_col0 + hk * D + 64 * c, krow);
+        if (!mbar_wait_bounded(&v_empty[sv], ((j / VST) & 1) ^ 1, abort_flag, p.status, kTimeoutEmpty)) break;
+        mbar_expect_tx(&v_full[sv], TB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(sV + sv * TB + c * 16384, &map_v, &v_full[sv], p.v_col0 + hk * D + 64 * c, krow);
+      }
+      if (*abort_flag) {  // give copies already in flight time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 20000ull) {
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      const uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
+      const uint32_t idesc_o = make_idesc(128, D, 1, 1, 0, 1);
+      auto issue_s = [&](int x, int j) {
+        const uint32_t q_addr = smem_u32(sQ + x * TB), k_addr = smem_u32(sK + (j % KST) * TB);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          tc_mma_f16(tmem_base + x * 128, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                     idesc_s, k != 0);
+        }
+        tc_commit(&s_full[x]);
+      };
+      auto issue_pv = [&](int x, int j) {
+        const uint32_t v_addr = smem_u32(sV + (j % VST) * TB);
+        const uint32_t o_tmem = tmem_base + 256 + x * D;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t bdesc = make_smem_desc_sw128(v_addr + k * 2048, 16384, 1024);  // MN-major: D contiguous
+          if (PT) {
+            tc_mma_f16_ts(o_tmem, tmem_base + x * 128 + k * 8, bdesc, idesc_o, (j | k) != 0);
+          } else {
+            const uint32_t p_addr = smem_u32(sP + x * 32768);
+            tc_mma_f16(o_tmem, make_smem_desc_sw128(p_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), bdesc, idesc_o, (j | k) != 0);
+          }
+        }
+      };
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFull);
+      ok = ok && mbar_wait_bounded(&k_full[0], 0, abort_flag, p.status, kTimeoutFull);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        issue_s(1, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int j = 0; ok && j < nbB; ++j) {
+        const int nk = (j + 1) % KST, nk_ph = ((j + 1) / KST) & 1;
+        if (!mbar_wait_bounded(&v_full[j % VST], (j / VST) & 1, abort_flag, p.status, kTimeoutFull)) break;
+        if (j < nbA) {
+          if (!mbar_wait_bounded(&p_full[0], j & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+          tc_fence_after();
+          issue_pv(0, j);
+          if (j == nbA - 1) tc_commit(&o_done[0]);
+          if (j + 1 < nbA) {
+            if (!mbar_wait_bounded(&k_full[nk], nk_ph, abort_flag, p.status, kTimeoutFull)) break;
+            if (!PT && !mbar_wait_bounded(&s_empty[0], j & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+            tc_fence_after();
+            issue_s(0, j + 1);
+          }
+        }
+        if (!mbar_wait_bounded(&p_full[1], j & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+        tc_fence_after();
+        issue_pv(1, j);
+        tc_commit(&v_empty[j % VST]);
+        if (j == nbB - 1) tc_commit(&o_done[1]);
+        if (j + 1 < nbB) {
+          if (!mbar_wait_bounded(&k_full[nk], nk_ph, abort_flag, p.status, kTimeoutFull)) break;
+          if (!PT && !mbar_wait_bounded(&s_empty[1], j & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+          tc_fence_after();
+          issue_s(1, j + 1);
+          tc_commit(&k_empty[nk]);
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // -------------------------------------------------------------------- soft-max groups
+    const int x = warp >> 2;        // 0 = tile A, 1 = tile B
+    const int quad = warp & 3;      // TMEM lane quadrant this warp may touch
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
+    const uint32_t tmem_S = tmem_base + x * 128 + lane_base;
+    const uint32_t tmem_O = tmem_base + 256 + x * D + lane_base;
+    const int qt = 2 * t + x;
+    const int nb = qt + 1;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nb; ++i) {
+      if (!mbar_wait_bounded(&s_full[x], i & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t v[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_S + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
+      tmem_ld_wait();
+      if (!PT) {  // the S tile may be overwritten as soon as every row is in registers
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[x]);
+      }
+      if (i == qt) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (c > r) v[c] = 0xff800000u;  // -inf above the diagonal
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 128; c += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(v[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(v[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(v[c + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(v[c + 3]));
+      }
+      const float mnew = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+      if (i == 0) {
+        m = mnew;
+      } else if (__any_sync(0xffffffffu, mnew > m + 8.f)) {
+        // S(i) ready implies the previous P V of this tile has completed (it was issued before S(i)), so O is stable
+        const float alpha = exp2f(m - mnew);
+        m = mnew;
+        l *= alpha;
+#pragma unroll 1
+        for (int c = 0; c < D / 16; ++c) {  // rare path: narrow pieces keep its register footprint small
+          uint32_t o[16];
+          tmem_ld_32x16(tmem_O + c * 16, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st_32x16(tmem_O + c * 16, o);
+        }
+        tmem_st_wait();
+      }
+      // exp2(x * scale - m) with packed fp32x2 arithmetic (one FMA and one ADD per two elements); the row sum is taken
+      // over the fp32 probabilities
+      float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m, -m);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float2 xs = __ffma2_rn(make_float2(__uint_as_float(v[c * 32 + 2 * e]), __uint_as_float(v[c * 32 + 2 * e + 1])), sc2, nm2);
+          const float2 pr = make_float2(exp2f(xs.x), exp2f(xs.y));
+          pk[e] = pack_bf16x2(pr.x, pr.y);
+          if (e & 1) rsb = __fadd2_rn(rsb, pr);
+          else rsa = __fadd2_rn(rsa, pr);
+        }
+        if (PT) {
+          tmem_st_32x16(tmem_S + c * 16, pk);
+        } else {
+          uint8_t* prow = sP + x * 32768 + (c >> 1) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = (c & 1) * 4 + g;
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+          }
+        }
+      }
+      l += (rsa.x + rsa.y) + (rsb.x + rsb.y);
+      if (PT) tmem_st_wait();
+      tc_fence_before();
+      if (!PT) fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[x]);
+    }
+    if (ok && mbar_wait_bounded(&o_done[x], 0, abort_flag, p.status, kTimeoutTmemFull)) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+      const long long tok = (long long)row0 + x * 128 + r;
+      __nv_bfloat16* orow = p.out + (tok * p.Hq + h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_O + c * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) =
+              make_uint4(pack_bf16x2(__uint_as_float(o[8 * g]) * inv, __uint_as_float(o[8 * g + 1]) * inv),
+                         pack_bf16x2(__uint_as_float(o[8 * g + 2]) * inv, __uint_as_float(o[8 * g + 3]) * inv),
+                         pack_bf16x2(__uint_as_float(o[8 * g + 4]) * inv, __uint_as_float(o[8 * g + 5]) * inv),
+                         pack_bf16x2(__uint_as_float(o[8 * g + 6]) * inv, __uint_as_float(o[8 * g + 7]) * inv));
+      }
+      if (p.lse) p.lse[((long long)b * p.Hq + h) * p.L + (long long)qt * 128 + r] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace ats
+
+using namespace ats;
+
+template <int D, bool PT>
+static int launch_fwd2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Attn2Args& p, int B, int L, int Hq,
+                       cudaStream_t s) {
+  using SM = Attn2Smem<D, PT>;
+  cudaError_t ce = cudaFuncSetAttribute(attn_fwd2_kernel<D, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  if (ce != cudaSuccess) return int(ce);
+  dim3 grid(L / 256, Hq, B);
+  attn_fwd2_kernel<D, PT><<<grid, A2_THREADS, SM::TOTAL, s>>>(mq, mk, mv, p);
+  return int(cudaGetLastError());
+}
+
+// Same contract as ats_attn_fwd, for L a multiple of 256.  p_in_tmem selects where the probabilities are staged.
+ATS_API int ats_attn_fwd2(const void* q, long long ld_q, long long q_cols, int q_col0, const void* k, long long ld_k,
+                          long long k_cols, int k_col0, const void* v, long long ld_v, long long v_cols, int v_col0,
+                          void* out, float* lse, int B, int L, int Hq, int Hkv, int D, int p_in_tmem, int* status, void* stream) {
+  if ((D != 64 && D != 128) || (L % 256) || Hq % Hkv || (q_col0 & 7) || (k_col0 & 7) || (v_col0 & 7)) return 1003;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
+  CUtensorMap mq, mk, mv;
+  int e;
+  const unsigned long long rows = (unsigned long long)B * L;
+  if ((e = make_tmap_2d(&mq, q, rows, q_cols, ld_q, 2, 64, 128))) return e;
+  if ((e = make_tmap_2d(&mk, k, rows, k_cols, ld_k, 2, 64, 128))) return e;
+  if ((e = make_tmap_2d(&mv, v, rows, v_cols, ld_v, 2, 64, 128))) return e;
+  Attn2Args p;
+  p.B = B; p.L = L; p.Hq = Hq; p.Hkv = Hkv;
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
+  p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
+  p.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128) return p_in_tmem ? launch_fwd2<128, true>(mq, mk, mv, p, B, L, Hq, s) : launch_fwd2<128, false>(mq, mk, mv, p, B, L, Hq, s);
+  return p_in_tmem ? launch_fwd2<64, true>(mq, mk, mv, p, B, L, Hq, s) : launch_fwd2<64, false>(mq, mk, mv, p, B, L, Hq, s);
+}

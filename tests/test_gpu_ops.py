@@ -419,3 +419,26 @@ def test_extra_optimizer_kernels():
     assert int(flag) == 1
     x[123] = -7.5
     assert float(optim.absmax(x)) == float(x.float().abs().max())
+
+
+@pytest.mark.parametrize("variant", ["v1", "v2s", "v2t"])
+@pytest.mark.parametrize("B,L,hq,hkv,d", [(2, 256, 4, 2, 128), (1, 1024, 8, 2, 64), (2, 768, 4, 4, 64), (1, 2048, 4, 1, 128)])
+def test_flash_attention_forward_variants(variant, B, L, hq, hkv, d, monkeypatch):
+    from adaptivetrainingsystem_b200.ops import attention_native as AN
+    monkeypatch.setattr(AN, "FWD_VARIANT", variant)
+    torch.manual_seed(17)
+    qkv = _rand(B, L, (hq + 2 * hkv) * d) * 2  # wider scores: the running maximum moves, so the lazy rescale path runs
+    o = ops.attention_packed(qkv, hq, hkv, d)
+    qf = qkv.float()
+    of = ops.attention_reference(qf[..., : hq * d].view(B, L, hq, d), qf[..., hq * d:(hq + hkv) * d].view(B, L, hkv, d),
+                                 qf[..., (hq + hkv) * d:].view(B, L, hkv, d))
+    _close(o, of, tol=2e-2, what=f"attention forward {variant}")
+    # log-sum-exp feeds the backward: check it through the gradients
+    q2 = qkv.detach().clone().requires_grad_()
+    g = _rand(B, L, hq, d)
+    ops.attention_packed(q2, hq, hkv, d).backward(g)
+    r2 = qkv.detach().float().requires_grad_()
+    ops.attention_reference(r2[..., : hq * d].view(B, L, hq, d), r2[..., hq * d:(hq + hkv) * d].view(B, L, hkv, d),
+                            r2[..., (hq + hkv) * d:].view(B, L, hkv, d)).backward(g.float())
+    _close(q2.grad, r2.grad, tol=3e-2, what=f"attention grads {variant}")
+    ops.check_status()
