@@ -30,7 +30,7 @@ def _lib_fns():
                                       _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp]
         lib.ats_attn_bwd.restype = _ci
         lib.ats_attn_bwd.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                                     _cll, _cll, _ci, _ci, _ci, _ci, _ci, _vp, _vp]
+                                     _cll, _cll, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp]
         _sig = True
     return lib
 
@@ -65,6 +65,11 @@ def _fwd(q, k, v):
     return out, lse
 
 
+# Diagnostics: set to an int64 CUDA tensor of 32 elements to receive per-phase cycle totals of one CTA of each backward
+# pass ([0:16] dK/dV pass, [16:32] dQ pass: total, waits of the MMA thread, issue time; [8:13] phases of one softmax warp).
+PHASE_PROFILE = None
+
+
 def _bwd(q, k, v, out, dout, lse, dq, dk, dv):
     B, L, Hq, D = q.shape
     Hkv = k.shape[2]
@@ -72,7 +77,8 @@ def _bwd(q, k, v, out, dout, lse, dq, dk, dv):
     st = _lib.status_tensor(q.device)
     err = _lib_fns().ats_attn_bwd(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),
                                   Hkv * D, 0, _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk),
-                                  _lib.ptr(dv), dq.stride(1), dk.stride(1), B, L, Hq, Hkv, D, _lib.ptr(st), _lib.stream_ptr(q.device))
+                                  _lib.ptr(dv), dq.stride(1), dk.stride(1), B, L, Hq, Hkv, D, _lib.ptr(st), _lib.ptr(PHASE_PROFILE),
+                                  _lib.stream_ptr(q.device))
     _lib.check(err, "ats_attn_bwd")
 
 

@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-library", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="print per-phase cycle totals of one CTA of each backward pass")
     ap.add_argument("--fwd", default=None, help="forward variant: v1 | v2s | v2t")
     a = ap.parse_args()
     if a.fwd:
@@ -76,6 +77,17 @@ def main():
         lf = time_cuda(lib_f, a.iters)
         lfb = time_cuda(lib_fb, a.iters)
         out.update({"library_fwd_ms": lf, "library_bwd_ms": lfb - lf})
+    if a.phases:
+        from adaptivetrainingsystem_b200.ops import attention_native as AN
+        AN.PHASE_PROFILE = torch.zeros(32, dtype=torch.int64, device=dev)
+        fwd_bwd()
+        torch.cuda.synchronize()
+        pp = AN.PHASE_PROFILE.tolist()
+        AN.PHASE_PROFILE = None
+        names = ["total", "wait_tile", "wait_scores_read", "wait_p_ds", "issue", "iterations", "", "", "sm_wait_scores", "sm_tmem_load", "sm_math",
+                 "sm_wait_products", "sm_store"]
+        out["phases_dkv"] = {n: v for n, v in zip(names, pp[:13]) if n}
+        out["phases_dq"] = {n: v for n, v in zip(names, pp[16:29]) if n}
     ops.check_status()
     print(json.dumps(out))
 

@@ -6,7 +6,7 @@
 //           dP = dO V^T on the tensor cores, forms P = exp(S - lse) and dS = P * (dP - delta) * scale in registers, and
 //           accumulates dV += P^T dO and dK += dS^T Q in TMEM across all iterations (no atomics, deterministic).
 //   MODE 1 (dQ):     one CTA per (128-query tile i, query head, batch).  Q_i and dO_i stay resident, K_j / V_j stream for
-//           j <= i, and dQ += dS K accumulates in TMEM.
+//           j <= i, and dQ += dS K accumulates in TMEM; dS goes back to tensor memory as bf16 and is the MMA's A operand.
 // S and dP are recomputed in both passes (7 tile products per tile pair instead of 5) in exchange for an atomics-free,
 // deterministic dQ.  P and dS live in shared memory as [query x key] bf16 tiles in the 128-byte-swizzled layout, which
 // the same bytes serve both as a K-major operand (dS K) and as an MN-major operand (P^T dO, dS^T Q).
@@ -19,7 +19,9 @@
 
 namespace ats {
 
-constexpr int AB_THREADS = 320;  // TMA warp, MMA warp, 8 softmax-gradient warps
+constexpr int AB_SPLIT = 2;                       // threads per query row in the softmax-gradient stage
+constexpr int AB_COLS = 128 / AB_SPLIT;           // key columns per thread
+constexpr int AB_THREADS = 64 + 128 * AB_SPLIT;   // TMA warp, MMA warp, 4 * AB_SPLIT softmax-gradient warps
 
 struct AttnBwdArgs {
   int B, L, Hq, Hkv, D;
@@ -32,18 +34,21 @@ struct AttnBwdArgs {
   long long ld_dq, ld_dkv;
   float scale, scale_log2;
   int* status;
+  long long* prof;  // optional [16]: cycle totals per phase, written by one CTA (diagnostics; null in normal use)
 };
 
 template <int D, int MODE>
 struct AttnBwdSmem {
-  static constexpr int ST = (MODE == 1) ? 2 : (D == 64 ? 2 : 1);
+  // streamed stages: a stage is held until the gradient products that read it have finished, and a refill takes a
+  // TMA round trip, so the ring must be deep enough to have the next tiles in flight meanwhile
+  static constexpr int ST = (D == 64) ? 4 : (MODE == 1 ? 2 : 1);
   static constexpr int TB = 128 * D * 2;
   static constexpr int R1 = 0, R2 = TB;
   static constexpr int T1 = 2 * TB;            // ST stages
   static constexpr int T2 = T1 + ST * TB;      // ST stages
   static constexpr int P_OFF = T2 + ST * TB;   // MODE 0 only
   static constexpr int DS_OFF = P_OFF + (MODE == 0 ? 32768 : 0);
-  static constexpr int BAR_OFF = DS_OFF + 32768;
+  static constexpr int BAR_OFF = DS_OFF + (MODE == 0 ? 32768 : 0);  // the dQ pass keeps dS in tensor memory
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -84,14 +89,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint8_t* sDS = smem + SM::DS_OFF;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* res_full = bars;       // 1
-  uint64_t* t_full = bars + 1;     // [2]
-  uint64_t* t_empty = bars + 3;    // [2]
-  uint64_t* s_full = bars + 5;     // S and dP ready
-  uint64_t* sd_free = bars + 6;    // 8 arrivals: S / dP read out of TMEM
-  uint64_t* pds_full = bars + 7;   // 8 arrivals: P / dS written to shared memory
-  uint64_t* pds_free = bars + 8;   // accumulate MMAs have consumed P / dS
-  uint64_t* acc_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* t_full = bars + 1;     // [4]
+  uint64_t* t_empty = bars + 5;    // [4]
+  uint64_t* s_full = bars + 9;     // S and dP ready
+  uint64_t* sd_free = bars + 10;   // one arrival per softmax warp: S / dP read out of TMEM
+  uint64_t* pds_full = bars + 11;  // one arrival per softmax warp: P / dS written to shared memory
+  uint64_t* pds_free = bars + 12;  // accumulate MMAs have consumed P / dS
+  uint64_t* acc_done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -113,13 +118,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(res_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&t_full[s], 1);
       mbar_init(&t_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(sd_free, 8);
-    mbar_init(pds_full, 8);
+    mbar_init(sd_free, 4 * AB_SPLIT);
+    mbar_init(pds_full, 4 * AB_SPLIT);
     mbar_init(pds_free, 1);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -138,6 +143,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_A1 = tmem_base + 256, tmem_A2 = tmem_base + 256 + D;
+  const uint32_t tmem_dS = tmem_base + 384;  // MODE 1: dS as bf16 pairs, 64 columns, the A operand of dQ += dS K
 
   // iteration t -> (query head, query tile, key tile)
   auto decode = [&](int t, int& h, int& qi, int& kj) {
@@ -206,47 +212,44 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
       const uint32_t idesc_acc0 = make_idesc(128, D, 1, 1, 1, 1);  // A^T B with both operands MN-major
       const uint32_t idesc_acc1 = make_idesc(128, D, 1, 1, 0, 1);  // dS (K-major) x K (MN-major)
+      // Descriptors are built once: per operand one base descriptor for the K-major view and one for the MN-major view;
+      // inside the loops a descriptor is the base plus a constant (the issue rate of this one thread bounds the kernel).
+      const uint64_t r1_k = make_smem_desc_sw128(smem_u32(sR1), 16, 1024), r2_k = make_smem_desc_sw128(smem_u32(sR2), 16, 1024);
+      const uint64_t r1_mn = make_smem_desc_sw128(smem_u32(sR1), 16384, 1024), r2_mn = make_smem_desc_sw128(smem_u32(sR2), 16384, 1024);
+      const uint64_t t1_k = make_smem_desc_sw128(smem_u32(sT1), 16, 1024), t2_k = make_smem_desc_sw128(smem_u32(sT2), 16, 1024);
+      const uint64_t t1_mn = make_smem_desc_sw128(smem_u32(sT1), 16384, 1024), t2_mn = make_smem_desc_sw128(smem_u32(sT2), 16384, 1024);
+      const uint64_t p_mn = make_smem_desc_sw128(smem_u32(sP), 16384, 1024), ds_mn = make_smem_desc_sw128(smem_u32(sDS), 16384, 1024);
       auto issue_scores = [&](int t) {  // S = Q K^T and dP = dO V^T of iteration t
-        const int s = t % ST;
-        const uint32_t q_addr = smem_u32(MODE == 0 ? sT1 + s * SM::TB : sR1);
-        const uint32_t do_addr = smem_u32(MODE == 0 ? sT2 + s * SM::TB : sR2);
-        const uint32_t k_addr = smem_u32(MODE == 0 ? sR1 : sT1 + s * SM::TB);
-        const uint32_t v_addr = smem_u32(MODE == 0 ? sR2 : sT2 + s * SM::TB);
+        const uint32_t so = uint32_t(t % ST) * SM::TB;
+        const uint64_t q_d = MODE == 0 ? desc_advance(t1_k, so) : r1_k, do_d = MODE == 0 ? desc_advance(t2_k, so) : r2_k;
+        const uint64_t k_d = MODE == 0 ? r1_k : desc_advance(t1_k, so), v_d = MODE == 0 ? r2_k : desc_advance(t2_k, so);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          tc_mma_f16(tmem_S, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
+          tc_mma_f16(tmem_S, desc_advance(q_d, off), desc_advance(k_d, off), idesc_s, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          tc_mma_f16(tmem_dP, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, k != 0);
+          tc_mma_f16(tmem_dP, desc_advance(do_d, off), desc_advance(v_d, off), idesc_s, k != 0);
         }
         tc_commit(s_full);
       };
       auto issue_acc = [&](int t) {  // the gradient products that consume P / dS of iteration t
         const int s = t % ST;
-        const uint32_t q_addr = smem_u32(MODE == 0 ? sT1 + s * SM::TB : sR1);
-        const uint32_t do_addr = smem_u32(MODE == 0 ? sT2 + s * SM::TB : sR2);
-        const uint32_t k_addr = smem_u32(MODE == 0 ? sR1 : sT1 + s * SM::TB);
-        const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+        const uint32_t so = uint32_t(s) * SM::TB;
         if (MODE == 0) {
+          const uint64_t do_d = desc_advance(t2_mn, so), q_d = desc_advance(t1_mn, so);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {  // reduction over the 128 queries, 16 per step
-            tc_mma_f16(tmem_A1, make_smem_desc_sw128(p_addr + k * 2048, 16384, 1024),
-                       make_smem_desc_sw128(do_addr + k * 2048, 16384, 1024), idesc_acc0, (t | k) != 0);
-          }
+          for (int k = 0; k < 8; ++k)  // reduction over the 128 queries, 16 per step
+            tc_mma_f16(tmem_A1, desc_advance(p_mn, k * 2048), desc_advance(do_d, k * 2048), idesc_acc0, (t | k) != 0);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            tc_mma_f16(tmem_A2, make_smem_desc_sw128(ds_addr + k * 2048, 16384, 1024),
-                       make_smem_desc_sw128(q_addr + k * 2048, 16384, 1024), idesc_acc0, (t | k) != 0);
-          }
+          for (int k = 0; k < 8; ++k) tc_mma_f16(tmem_A2, desc_advance(ds_mn, k * 2048), desc_advance(q_d, k * 2048), idesc_acc0, (t | k) != 0);
         } else {
+          const uint64_t k_d = desc_advance(t1_mn, so);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {  // reduction over the 128 keys
-            tc_mma_f16(tmem_A1, make_smem_desc_sw128(ds_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
-                       make_smem_desc_sw128(k_addr + k * 2048, 16384, 1024), idesc_acc1, (t | k) != 0);
-          }
+          for (int k = 0; k < 8; ++k)  // reduction over the 128 keys; dS is read from tensor memory (8 columns per 16 keys)
+            tc_mma_f16_ts(tmem_A1, tmem_dS + k * 8, desc_advance(k_d, k * 2048), idesc_acc1, (t | k) != 0);
         }
         tc_commit(pds_free);
         tc_commit(&t_empty[s]);
@@ -260,16 +263,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tc_fence_after();
           issue_scores(0);
         }
+        const bool rec = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        long long w_tfull = 0, w_sdfree = 0, w_pdsfull = 0, t_issue = 0, c0 = 0, c1 = 0;
+        const long long t_begin = clock64();
         for (int t = 0; ok && t < n_iter; ++t) {
           if (t + 1 < n_iter) {
+            if (rec) c0 = clock64();
             if (!mbar_wait_bounded(&t_full[(t + 1) % ST], ((t + 1) / ST) & 1, abort_flag, p.status, kTimeoutFull)) break;
+            if (rec) { c1 = clock64(); w_tfull += c1 - c0; }
             if (!mbar_wait_bounded(sd_free, t & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+            if (rec) { c0 = clock64(); w_sdfree += c0 - c1; }
             tc_fence_after();
             issue_scores(t + 1);
+            if (rec) { c1 = clock64(); t_issue += c1 - c0; }
           }
+          if (rec) c0 = clock64();
           if (!mbar_wait_bounded(pds_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+          if (rec) { c1 = clock64(); w_pdsfull += c1 - c0; }
           tc_fence_after();
           issue_acc(t);
+          if (rec) { c0 = clock64(); t_issue += c0 - c1; }
+        }
+        if (rec) {
+          p.prof[0] = clock64() - t_begin;
+          p.prof[1] = w_tfull; p.prof[2] = w_sdfree; p.prof[3] = w_pdsfull; p.prof[4] = t_issue; p.prof[5] = n_iter;
         }
       } else {
         // one streamed stage: the next tile can only be fetched after this iteration's products, so the order is serial
@@ -287,95 +304,125 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else {
     // ---------------------------------------- softmax-gradient threads: a TMEM lane quadrant is open to warps with the
-    // same (warp % 4), so warps w and w + 4 share 32 query rows and take 64 key columns each
+    // same (warp % 4), so the AB_SPLIT warps w, w + 4, ... share 32 query rows and take AB_COLS key columns each
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;  // which AB_COLS key columns of the 128
     const int r = quad * 32 + lane;
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
     bool ok = true;
-    float lse2 = 0.f, dl = 0.f;
-    int cur_h = -1, cur_qi = -1;
+    // log-sum-exp and delta of this thread's query row, fetched one iteration ahead so the loads never sit on the critical path
+    auto row_stats = [&](int t, float& l2, float& d) {
+      int h, qi, kj;
+      decode(t, h, qi, kj);
+      const long long idx = ((long long)b * p.Hq + h) * p.L + qi * 128 + r;
+      l2 = p.lse[idx] * 1.4426950408889634f;
+      d = p.delta[idx];
+    };
+    float lse2 = 0.f, dl = 0.f, lse2_n = 0.f, dl_n = 0.f;
+    if (n_iter > 0) row_stats(0, lse2_n, dl_n);
+    const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), scale2 = make_float2(p.scale, p.scale);
+    const bool rec = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
+    long long w_sfull = 0, t_load = 0, t_math = 0, w_pdsfree = 0, t_store = 0, c0 = 0, c1 = 0;
     for (int t = 0; t < n_iter; ++t) {
       int h, qi, kj;
       decode(t, h, qi, kj);
-      if (h != cur_h || qi != cur_qi) {
-        const long long idx = ((long long)b * p.Hq + h) * p.L + qi * 128 + r;
-        lse2 = p.lse[idx] * 1.4426950408889634f;
-        dl = p.delta[idx];
-        cur_h = h;
-        cur_qi = qi;
-      }
+      lse2 = lse2_n;
+      dl = dl_n;
+      if (t + 1 < n_iter && (MODE == 0)) row_stats(t + 1, lse2_n, dl_n);  // MODE 1 keeps the same query rows throughout
+      if (rec) c0 = clock64();
       if (!mbar_wait_bounded(s_full, t & 1, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
+      if (rec) { c1 = clock64(); w_sfull += c1 - c0; }
       tc_fence_after();
-      // this thread's half row of S and dP -> registers; the TMEM tiles are then free for the next iteration's scores
-      uint32_t sv[64], dv[64];
-      tmem_ld_32x32(tmem_S + lane_base + half * 64, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
-      tmem_ld_32x32(tmem_S + lane_base + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
-      tmem_ld_32x32(tmem_dP + lane_base + half * 64, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
-      tmem_ld_32x32(tmem_dP + lane_base + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
+      // this thread's columns of S, then of dP; the exponentials start while the dP load is still in flight
+      uint32_t sv[AB_COLS], dv[AB_COLS];
+#pragma unroll
+      for (int c = 0; c < AB_COLS / 32; ++c) tmem_ld_32x32(tmem_S + lane_base + part * AB_COLS + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+      tmem_ld_wait();
+      if (rec) { c0 = clock64(); t_load += c0 - c1; }
+#pragma unroll
+      for (int c = 0; c < AB_COLS / 32; ++c) tmem_ld_32x32(tmem_dP + lane_base + part * AB_COLS + c * 32, reinterpret_cast<uint32_t(&)[32]>(dv[c * 32]));
+      const float2 nl2 = make_float2(-lse2, -lse2), ndl2 = make_float2(-dl, -dl);
+      const bool diag = (qi == kj);
+      float2 pr[AB_COLS / 2];
+      uint32_t pk[AB_COLS / 2], dk[AB_COLS / 2];
+#pragma unroll
+      for (int i = 0; i < AB_COLS / 2; ++i) {
+        const float2 xs = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sc2, nl2);
+        pr[i] = make_float2(exp2f(xs.x), exp2f(xs.y));
+        if (diag) {
+          if (part * AB_COLS + 2 * i > r) pr[i].x = 0.f;
+          if (part * AB_COLS + 2 * i + 1 > r) pr[i].y = 0.f;
+        }
+        pk[i] = pack_bf16x2(pr[i].x, pr[i].y);
+      }
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(sd_free);
-      // P = exp2(S * scale_log2 - lse2), dS = P * (dP - delta) * scale, two elements per packed fp32x2 instruction
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
-      const float2 ndl2 = make_float2(-dl, -dl), scale2 = make_float2(p.scale, p.scale);
-      const bool diag = (qi == kj);
-      uint32_t pk[32], dk[32];
+      if (lane == 0) mbar_arrive(sd_free);  // S and dP are in registers: the tensor cores may start the next scores
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float2 xs = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sc2, nl2);
-        float2 pr = make_float2(exp2f(xs.x), exp2f(xs.y));
-        if (diag) {
-          if (half * 64 + 2 * i > r) pr.x = 0.f;
-          if (half * 64 + 2 * i + 1 > r) pr.y = 0.f;
-        }
-        const float2 dd = __fmul2_rn(__fmul2_rn(pr, scale2), __fadd2_rn(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), ndl2));
-        pk[i] = pack_bf16x2(pr.x, pr.y);
+      for (int i = 0; i < AB_COLS / 2; ++i) {
+        const float2 dd = __fmul2_rn(__fmul2_rn(pr[i], scale2), __fadd2_rn(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), ndl2));
         dk[i] = pack_bf16x2(dd.x, dd.y);
       }
       // the gradient products of the previous iteration must be done with P / dS before they are overwritten
+      if (rec) { c1 = clock64(); t_math += c1 - c0; }
       if (!mbar_wait_bounded(pds_free, (t & 1) ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) {
         ok = false;
         break;
       }
-      {
-        const int roff = half * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+      if (rec) { c0 = clock64(); w_pdsfree += c0 - c1; }
+      if (MODE == 1) {
+        // dQ pass: dS never touches shared memory
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const int chunk = (g ^ (r & 7)) << 4;
-          if (MODE == 0) *reinterpret_cast<uint4*>(sP + roff + chunk) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+        for (int c = 0; c < AB_COLS / 64; ++c)
+          tmem_st_32x32(tmem_dS + lane_base + part * (AB_COLS / 2) + c * 32, reinterpret_cast<uint32_t(&)[32]>(dk[c * 32]));
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        constexpr int CH = AB_COLS / 8;  // 16-byte chunks per thread
+        const int col0 = part * AB_COLS;
+        const int roff = (col0 >> 6) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int g = 0; g < CH; ++g) {
+          const int chunk = ((((col0 & 63) >> 3) + g) ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(sP + roff + chunk) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
           *reinterpret_cast<uint4*>(sDS + roff + chunk) = make_uint4(dk[4 * g], dk[4 * g + 1], dk[4 * g + 2], dk[4 * g + 3]);
         }
+        fence_proxy_async_smem();
       }
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (rec) { c1 = clock64(); t_store += c1 - c0; }
+    }
+    if (rec) {
+      p.prof[8] = w_sfull; p.prof[9] = t_load; p.prof[10] = t_math; p.prof[11] = w_pdsfree; p.prof[12] = t_store;
     }
     if (ok && mbar_wait_bounded(acc_done, 0, abort_flag, p.status, kTimeoutTmemFull)) {
       tc_fence_after();
       const long long tok = (long long)b * p.L + fixed * 128 + r;
       __nv_bfloat16* o1 = MODE == 0 ? p.dv + tok * p.ld_dkv + head * D : p.dq + tok * p.ld_dq + head * D;
       __nv_bfloat16* o2 = MODE == 0 ? p.dk + tok * p.ld_dkv + head * D : nullptr;
+      // the AB_SPLIT threads of a row store D / AB_SPLIT columns each, 16 at a time
+      constexpr int PIECES = D / 16 / AB_SPLIT;
 #pragma unroll
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_A1 + lane_base + c * 32, v);
+      for (int c = part * PIECES; c < (part + 1) * PIECES; ++c) {
+        uint32_t v[16];
+        tmem_ld_32x16(tmem_A1 + lane_base + c * 16, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(o1 + c * 32 + g * 8) =
+        for (int g = 0; g < 2; ++g)
+          *reinterpret_cast<uint4*>(o1 + c * 16 + g * 8) =
               make_uint4(pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])), pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
                          pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])), pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
         if (MODE == 0) {
-          tmem_ld_32x32(tmem_A2 + lane_base + c * 32, v);
+          tmem_ld_32x16(tmem_A2 + lane_base + c * 16, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(o2 + c * 32 + g * 8) =
+          for (int g = 0; g < 2; ++g)
+            *reinterpret_cast<uint4*>(o2 + c * 16 + g * 8) =
                 make_uint4(pack_bf16x2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])), pack_bf16x2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
                            pack_bf16x2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])), pack_bf16x2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
         }
@@ -407,10 +454,11 @@ static int launch_attn_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const C
 
 // q/k/v as for ats_attn_fwd; out, dout: [B, L, Hq, D] contiguous; lse [B, Hq, L]; delta: fp32 scratch [B, Hq, L];
 // dq: rows = tokens with pitch ld_dq, dk / dv with pitch ld_dkv (so all three can be slices of one packed gradient).
+// prof: null, or 32 int64 that receive per-phase cycle totals of CTA (0,0,0) of each pass (diagnostics).
 ATS_API int ats_attn_bwd(const void* q, long long ld_q, long long q_cols, int q_col0, const void* k, long long ld_k,
                          long long k_cols, int k_col0, const void* v, long long ld_v, long long v_cols, int v_col0,
                          const void* out, const void* dout, const float* lse, float* delta, void* dq, void* dk, void* dv,
-                         long long ld_dq, long long ld_dkv, int B, int L, int Hq, int Hkv, int D, int* status, void* stream) {
+                         long long ld_dq, long long ld_dkv, int B, int L, int Hq, int Hkv, int D, int* status, long long* prof, void* stream) {
   if ((D != 64 && D != 128) || (L % 128) || Hq % Hkv || (q_col0 & 7) || (k_col0 & 7) || (v_col0 & 7) || (ld_dq & 7) || (ld_dkv & 7))
     return 1003;
   static thread_local bool ctx_bound = false;
@@ -438,10 +486,13 @@ ATS_API int ats_attn_bwd(const void* q, long long ld_q, long long q_cols, int q_
   p.scale = 1.f / sqrtf(float(D));
   p.scale_log2 = 1.4426950408889634f * p.scale;
   p.status = status;
+  p.prof = prof;
   if (D == 128) {
     if ((e = launch_attn_bwd<128, 0>(mq, mk, mv, mdo, p, s))) return e;
+    if (prof) p.prof = prof + 16;
     return launch_attn_bwd<128, 1>(mq, mk, mv, mdo, p, s);
   }
   if ((e = launch_attn_bwd<64, 0>(mq, mk, mv, mdo, p, s))) return e;
+  if (prof) p.prof = prof + 16;
   return launch_attn_bwd<64, 1>(mq, mk, mv, mdo, p, s);
 }

@@ -139,28 +139,27 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // ------------------------------------------------------------------ MMA issuer
       const uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
       const uint32_t idesc_o = make_idesc(128, D, 1, 1, 0, 1);
+      // base descriptors are built once; inside the loops a descriptor is a base plus a constant, because the issue rate
+      // of this one thread bounds the kernel when the MMAs are as small as 128 x 64 x 16
+      const uint64_t q_k = make_smem_desc_sw128(smem_u32(sQ), 16, 1024), k_k = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t v_mn = make_smem_desc_sw128(smem_u32(sV), 16384, 1024), p_k = make_smem_desc_sw128(smem_u32(sP), 16, 1024);
       auto issue_s = [&](int x, int j) {
-        const uint32_t q_addr = smem_u32(sQ + x * TB), k_addr = smem_u32(sK + (j % KST) * TB);
+        const uint64_t q_d = desc_advance(q_k, uint32_t(x) * TB), k_d = desc_advance(k_k, uint32_t(j % KST) * TB);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          tc_mma_f16(tmem_base + x * 128, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                     idesc_s, k != 0);
+          tc_mma_f16(tmem_base + x * 128, desc_advance(q_d, off), desc_advance(k_d, off), idesc_s, k != 0);
         }
         tc_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j) {
-        const uint32_t v_addr = smem_u32(sV + (j % VST) * TB);
+        const uint64_t v_d = desc_advance(v_mn, uint32_t(j % VST) * TB);  // MN-major: D contiguous
         const uint32_t o_tmem = tmem_base + 256 + x * D;
+        const uint64_t p_d = desc_advance(p_k, uint32_t(x) * 32768);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint64_t bdesc = make_smem_desc_sw128(v_addr + k * 2048, 16384, 1024);  // MN-major: D contiguous
-          if (PT) {
-            tc_mma_f16_ts(o_tmem, tmem_base + x * 128 + k * 8, bdesc, idesc_o, (j | k) != 0);
-          } else {
-            const uint32_t p_addr = smem_u32(sP + x * 32768);
-            tc_mma_f16(o_tmem, make_smem_desc_sw128(p_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), bdesc, idesc_o, (j | k) != 0);
-          }
+          if (PT) tc_mma_f16_ts(o_tmem, tmem_base + x * 128 + k * 8, desc_advance(v_d, k * 2048), idesc_o, (j | k) != 0);
+          else tc_mma_f16(o_tmem, desc_advance(p_d, (k >> 2) * 16384 + (k & 3) * 32), desc_advance(v_d, k * 2048), idesc_o, (j | k) != 0);
         }
       };
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFull);
