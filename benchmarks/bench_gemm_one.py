@@ -1,0 +1,60 @@
+"""One tcgen05 GEMM shape, timed against torch.matmul; small enough for a profiler capture:
+
+    python benchmarks/bench_gemm_one.py --m 8192 --n 8192 --k 8192 --iters 5
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from adaptivetrainingsystem_b200.ops import gemm as G  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--mode", default="nt", choices=["nt", "nn", "tn"])
+    a = ap.parse_args()
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    w = torch.randn(a.n, a.k, device=dev).bfloat16()
+    out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+
+    if a.mode == "nt":
+        ours, lib = (lambda: G.gemm_nt(x, w, out=out)), (lambda: torch.matmul(x, w.t(), out=out))
+    elif a.mode == "nn":
+        wt = w.t().contiguous()
+        ours, lib = (lambda: G.gemm_nn(x, wt, out=out)), (lambda: torch.matmul(x, wt, out=out))
+    else:
+        xt, wt = x.t().contiguous(), w.t().contiguous()
+        ours, lib = (lambda: G.gemm_tn(xt, wt, out=out)), (lambda: torch.matmul(xt.t(), wt, out=out))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        tot = 0.0
+        for _ in range(a.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / a.iters
+    t_o, t_l = timed(ours), timed(lib)
+    fl = 2.0 * a.m * a.n * a.k
+    print(json.dumps({"gemm": [a.m, a.n, a.k], "mode": a.mode, "ms": t_o, "tflops": fl / t_o / 1e9, "library_ms": t_l,
+                      "library_tflops": fl / t_l / 1e9, "l2": "flushed between iterations"}))
+
+
+if __name__ == "__main__":
+    main()
