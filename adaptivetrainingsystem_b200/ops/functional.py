@@ -285,6 +285,9 @@ class _LinearFn(torch.autograd.Function):
 def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w.T (+ residual)`` -- the residual add is fused into the GEMM epilogue."""
     if _lib.use_cuda_kernels(x):
+        from . import fp8
+        if fp8.enabled() and x.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0:
+            return fp8.linear_fp8(x, w, residual)
         return _LinearFn.apply(x, w, residual)
     y = F.linear(x, w)
     return y + residual if residual is not None else y
@@ -337,10 +340,20 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         x2 = x.reshape(-1, shape[-1])
         need_bwd = any(ctx.needs_input_grad)
         pre = torch.empty(x2.shape[0], w1.shape[0], dtype=x.dtype, device=x.device) if need_bwd else None
-        h = G.gemm_nt_swiglu(x2, w1, pre_act=pre)
         r2 = residual.reshape(-1, w2.shape[0]) if residual is not None else None
         y = torch.empty(*shape[:-1], w2.shape[0], dtype=x.dtype, device=x.device)
-        G.gemm_nt(h, w2, out=y.view(-1, w2.shape[0]), add=r2)
+        from . import fp8
+        if fp8.enabled() and x2.shape[1] % 16 == 0 and w1.shape[0] % 32 == 0:
+            # e4m3 forward products (per-token / per-channel scales); the backward below stays in bf16
+            xq, xs = fp8.quantize_rows(x2)
+            w1q, w1s = fp8.quantized_weight(w1)
+            h = fp8.gemm_nt_fp8(xq, xs, w1q, w1s, swiglu=True, aux=pre)
+            hq, hs = fp8.quantize_rows(h)
+            w2q, w2s = fp8.quantized_weight(w2)
+            fp8.gemm_nt_fp8(hq, hs, w2q, w2s, out=y.view(-1, w2.shape[0]), add=r2)
+        else:
+            h = G.gemm_nt_swiglu(x2, w1, pre_act=pre)
+            G.gemm_nt(h, w2, out=y.view(-1, w2.shape[0]), add=r2)
         ctx.save_for_backward(x2, w1, w2, pre)
         ctx.shape = shape
         ctx.has_res = residual is not None

@@ -221,6 +221,7 @@ class ShardedEngine:
         self.step_count += 1
         self._hyper_host[5] = float(self.step_count)
         self.hyper[5] = float(self.step_count)
+        ops.fp8.weights_changed()  # cached quantised weights are stale after this step
         if self.rule is None and self.fused is not None and self.fused.usable(self):
             # reduce-scatter, norm, AdamW and all-gather done by peer-memory kernels (parallel/fused.py)
             self.fused.step(self)

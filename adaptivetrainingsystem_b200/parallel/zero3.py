@@ -218,6 +218,7 @@ class ZeRO3Engine:
         self.step_count += 1
         self._hyper_host[5] = float(self.step_count)
         self.hyper[5] = float(self.step_count)
+        ops.fp8.weights_changed()  # cached quantised weights are stale after this step
         self._flush_pending()
         self.root.reduce_grads()
         units = self.units + [self.root]

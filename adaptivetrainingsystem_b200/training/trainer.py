@@ -86,6 +86,9 @@ class EnhancedConversationTrainer:
         self.mesh = mesh or ProcessMesh(create_groups=False)
         self.device = next(model.parameters()).device
         self.precision_manager = PrecisionManager(self.config, self.device)
+        # fp8 precisions switch the linear layers' forward products to the e4m3 tcgen05 GEMM (process-wide switch)
+        from .. import ops as _ops
+        _ops.fp8.set_enabled(self.precision_manager.uses_fp8 and self.device.type == "cuda")
         self.quantization_manager = QuantizationManager(self.config)
         self.moe_manager = MoEOptimizationManager(self.config)
         self.pad_token_id = getattr(tokenizer, "pad_token_id", None)

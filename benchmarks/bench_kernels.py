@@ -56,6 +56,16 @@ def main():
         report(f"gemm_nt {m}x{n}x{k}", time_cuda(lambda: G.gemm_nt(a, b, out=out)), fl, lib_ms=lib)
         report(f"gemm_nn {m}x{n}x{k}", time_cuda(lambda: G.gemm_nn(a, bt, out=out)), fl, lib_ms=time_cuda(lambda: torch.matmul(a, bt, out=out)))
         report(f"gemm_tn {m}x{n}x{k}", time_cuda(lambda: G.gemm_tn(at, bt, out=out)), fl, lib_ms=time_cuda(lambda: torch.matmul(at.t(), bt, out=out)))
+    # fp8 (e4m3, per-row / per-channel scales) forward GEMM against the bf16 kernel and the library
+    from adaptivetrainingsystem_b200.ops import fp8
+    for (m, n, k) in [(8192, 8192, 8192), (16384, 2560, 2048)]:
+        a, b = rnd(m, k), rnd(n, k, scale=0.05)
+        aq, sa = fp8.quantize_rows(a)
+        bq, sb = fp8.quantize_rows(b)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        report(f"gemm_nt_fp8 {m}x{n}x{k}", time_cuda(lambda: fp8.gemm_nt_fp8(aq, sa, bq, sb, out=out)), 2.0 * m * n * k,
+               lib_ms=time_cuda(lambda: torch.matmul(a, b.t(), out=out)))
+        report(f"quantize_rows_e4m3 {m}x{k}", time_cuda(lambda: fp8.quantize_rows(a)), nbytes=3.0 * m * k)
     # SwiGLU-fused GEMM
     for (m, k, i) in [(8192, 2048, 5632), (4096, 4096, 14336)]:
         a, w = rnd(m, k), rnd(2 * i, k, scale=0.05)

@@ -219,11 +219,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   d |= 2ull << 61;  // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor, kind::f16 / kind::f8f6f4: fp32 accumulate, M x N tile, operand majors.
-//   fmt: 0 = f16 (or e4m3 for f8f6f4), 1 = bf16 (or e5m2).
 // Descriptor of the same operand `byte_off` bytes further on (the start-address field counts 16-byte units and sits in
 // the low bits, so this is one add; shared-memory addresses are < 256 KB and never carry out of the field).
 __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_off) { return desc + (byte_off >> 4); }
+// Instruction descriptor, kind::f16 / kind::f8f6f4: fp32 accumulate, M x N tile, operand majors.
+//   fmt: 0 = f16 (or e4m3 for f8f6f4), 1 = bf16 (or e5m2).
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_fmt, int b_fmt, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (uint32_t(a_fmt) << 7) | (uint32_t(b_fmt) << 10) | (uint32_t(a_mn_major) << 15) |
          (uint32_t(b_mn_major) << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);

@@ -491,3 +491,53 @@ ATS_API const char* ats_noalloc_error_string(int code) {
     default: return "CUDA runtime error (the code is a cudaError_t)";
   }
 }
+
+// ------------------------------------------------------------------------------------------------ fp8 quantisation
+#include <cuda_fp8.h>
+
+namespace ats {
+
+// One CTA per row: scale = amax / 448 (e4m3 max), q = x / scale.  The row is read twice (second time from L1 / L2).
+__global__ void __launch_bounds__(256) quantize_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ x, long long ld, uint8_t* __restrict__ q,
+                                                                 long long ldq, float* __restrict__ scale, int cols) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * ld;
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < cols; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  amax = block_max(amax, red);
+  const float sc = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+  const float inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[row] = sc;
+  uint8_t* qr = q + row * ldq;
+  for (int i = threadIdx.x * 8; i < cols; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    uint16_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]);
+      o[j] = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+    }
+    *reinterpret_cast<uint2*>(qr + i) = make_uint2(uint32_t(o[0]) | (uint32_t(o[1]) << 16), uint32_t(o[2]) | (uint32_t(o[3]) << 16));
+  }
+}
+
+}  // namespace ats
+
+// x: bf16 [rows, cols] with pitch ld; q: e4m3 bytes [rows, cols] with pitch ldq; scale: fp32 [rows].  cols % 8 == 0.
+ATS_API int ats_quantize_rows_e4m3(const void* x, long long ld, void* q, long long ldq, float* scale, long long rows, int cols, void* stream) {
+  if ((cols & 7) || (ld & 7) || (ldq & 7)) return 1003;
+  if (rows == 0) return 0;
+  ats::quantize_rows_e4m3_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ld, static_cast<uint8_t*>(q), ldq, scale, cols);
+  return int(cudaGetLastError());
+}

@@ -58,6 +58,13 @@ struct GemmArgs {
   int k_segs;            // ragged == 2: the reduction of group g runs over k_segs blocks of rows, seg_stride apart,
   int seg_stride;        //              block s holding counts[g * k_segs + s] rows
   void* const* d_table;  // optional per-group output base pointers (e.g. buffers on peer GPUs)
+  // fp8 (e4m3) operands: one byte per element, 128 elements per swizzle row and per K block, kind::f8f6f4 MMAs (K = 32).
+  // The fp32 accumulator is multiplied by row_scale[row] * col_scale[col] in the epilogue (per-token activation scales,
+  // per-output-channel weight scales), so the main loop needs no per-block promotion.
+  int fp8;
+  const float* row_scale;  // [groups * rs_gs] or null
+  const float* col_scale;  // [weights * cs_gs] or null
+  long long rs_gs, cs_gs;
   int* status;
 };
 
@@ -106,7 +113,8 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   t.g = g;
   t.m0 = mt * BM;
   t.n0 = nt * (p.epilogue == kSwiGLU ? 128 : BN);
-  t.k_iters = (kg + BK - 1) / BK;
+  const int bk = p.fp8 ? 2 * BK : BK;  // elements per K block (always 128 bytes)
+  t.k_iters = (kg + bk - 1) / bk;
   t.valid = mg;
   return t;
 }
@@ -191,7 +199,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           armed_phase = (armed_phase & ~(1u << stage)) | (uint32_t(phase) << stage);
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
-          const int k0 = seg * p.seg_stride + kpos * BK;
+          const int k0 = seg * p.seg_stride + kpos * (p.fp8 ? 2 * BK : BK);
           ++kpos;
           --seg_left;
           if (!p.a_mn) {
@@ -230,7 +238,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
+      const uint32_t idesc = p.fp8 ? make_idesc(BM, BN, 0, 0, 0, 0)  // e4m3 x e4m3, both K-major
+                                   : make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
       int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -252,7 +261,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                           : make_smem_desc_sw128(a_addr + k * (UK * 2), 16, 1024);
             const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_addr + k * (UK * 128), BK * 128, 1024)
                                           : make_smem_desc_sw128(b_addr + k * (UK * 2), 16, 1024);
-            tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            if (p.fp8) tc_mma_f8(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);  // 32 bytes of K per MMA either way
+            else tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
           }
           tc_commit(&empty[stage]);  // the stage is free once these MMAs have read it
           if (++stage == STAGES) {
@@ -282,6 +292,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int row = t.m0 + row_in_tile;
       const bool row_ok = row < t.valid;
       const bool have_acc = t.k_iters > 0;
+      const float rs = (p.row_scale && row_ok) ? p.row_scale[p.rs_gs * t.g + row] * p.alpha : p.alpha;
+      const float* cs = p.col_scale ? p.col_scale + p.cs_gs * (t.g / p.b_div) : nullptr;
       if (p.epilogue == kSwiGLU) {
         __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
         __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
@@ -300,8 +312,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 uint32_t h[4], gg[4], uu[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * p.alpha, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * p.alpha;
-                  float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * p.alpha, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * p.alpha;
+                  float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * rs, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * rs;
+                  float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * rs, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * rs;
+                  if (cs) {
+                    g0 *= cs[col + 2 * e];
+                    g1 *= cs[col + 2 * e + 1];
+                    u0 *= cs[p.up_offset + col + 2 * e];
+                    u1 *= cs[p.up_offset + col + 2 * e + 1];
+                  }
                   gg[e] = pack_bf16x2(g0, g1);
                   uu[e] = pack_bf16x2(u0, u1);
                   // activation on the bf16-rounded values so a separate SwiGLU pass gives identical bits
@@ -356,7 +374,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               if (col < p.N) {
                 float f[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * rs;
+                if (cs) {
+                  const float4 c0 = *reinterpret_cast<const float4*>(cs + col), c1 = *reinterpret_cast<const float4*>(cs + col + 4);
+                  f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
+                  f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
+                }
                 if (crow) {
                   uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
                   float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
@@ -433,6 +456,9 @@ static int num_sms() {
 
 using namespace ats;
 
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
+                       int max_ctas, void* stream);
+
 // Generic entry point. The global 2-D extents of both operands are given explicitly (rows x cols, cols contiguous,
 // pitch ld elements); for a K-major operand cols is the reduction dimension, for an MN-major operand rows is.
 // Returns 0 or an error code (>= 1000: tensor-map encode, otherwise cudaError_t of the launch).
@@ -470,7 +496,47 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = a_mn; p.b_mn = b_mn; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
   p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table;
+  p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
+  return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
+}
 
+// fp8 (e4m3) A [groups x M, K] and B [weights x N, K], both K-major and row-quantised: D = (A_q B_q^T) * row_scale * col_scale.
+// a_gs_mn / b_gs_mn: row shift per group / per weight inside the 2-D operand; rs_gs / cs_gs: scale offsets per group / weight.
+// Epilogues: store, +C, SwiGLU (up_offset as in the bf16 entry).  ragged: 0, or 1 with per-group row counts.
+ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long long lda, const void* B, long long b_rows,
+                         long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
+                         int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
+                         int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
+                         const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
+                         void* stream) {
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
+  if (groups < 1 || groups > MAX_GROUPS) return 1002;
+  if ((N & 7) || (K & 15) || (lda & 15) || (ldb & 15) || (ldd & 7) || (d_gs & 7) || (a_gs_mn & 7) || (b_gs_mn & 7)) return 1003;
+  if (epilogue == kF32 || (epilogue == kSwiGLU && (up_offset & 7))) return 1004;
+  if ((ragged && !counts) || ragged > 1 || b_div < 1) return 1005;
+  CUtensorMap ma, mb;
+  int e;
+  if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 1, 128, 128))) return e;
+  if ((e = make_tmap_2d(&mb, B, b_rows, b_cols, ldb, 1, 128, 128))) return e;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K; p.groups = groups; p.ragged = ragged; p.counts = counts;
+  p.a_gs_mn = a_gs_mn; p.a_gs_k = 0; p.b_gs_mn = b_gs_mn; p.b_gs_k = 0;
+  p.d_gs = d_gs; p.c_gs = c_gs; p.aux_gs = aux_gs;
+  p.D = static_cast<__nv_bfloat16*>(D); p.C = static_cast<const __nv_bfloat16*>(C);
+  p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
+  p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
+  p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
+  p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
+  p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
+  return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
+}
+
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
+                       int max_ctas, void* stream) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);

@@ -442,3 +442,67 @@ def test_flash_attention_forward_variants(variant, B, L, hq, hkv, d, monkeypatch
                             r2[..., (hq + hkv) * d:].view(B, L, hkv, d)).backward(g.float())
     _close(q2.grad, r2.grad, tol=3e-2, what=f"attention grads {variant}")
     ops.check_status()
+
+
+def test_fp8_quantize_and_gemm():
+    from adaptivetrainingsystem_b200.ops import fp8
+    torch.manual_seed(8)
+    x = _rand(1000, 2048) * 3
+    q, s = fp8.quantize_rows(x)
+    qr, sr = fp8.quantize_rows_reference(x)
+    assert torch.allclose(s, sr, rtol=1e-6)
+    # same grid points up to ties in rounding: dequantised values within one e4m3 step of the input
+    deq = q.float() * s[:, None]
+    assert ((deq - x.float()).abs() <= x.float().abs() * 0.0625 + s[:, None] * 0.002).all()
+    assert (q.float() == qr.float()).float().mean().item() > 0.999
+    for (M, N, K) in [(512, 768, 1024), (1000, 2560, 2048), (130, 136, 144)]:
+        a, b = _rand(M, K), _rand(N, K) * 0.05
+        aq, sa = fp8.quantize_rows(a)
+        bq, sb = fp8.quantize_rows(b)
+        res = _rand(M, N)
+        out = fp8.gemm_nt_fp8(aq, sa, bq, sb, add=res)
+        ref = (aq.float() * sa[:, None]) @ (bq.float() * sb[:, None]).t() + res.float()
+        _close(out, ref, tol=1e-2, what=f"fp8 gemm {M}x{N}x{K}")  # against the product of the dequantised operands
+        _close(out, a.float() @ b.float().t() + res.float(), tol=8e-2, what="fp8 gemm vs unquantised")
+    # SwiGLU epilogue
+    a, w = _rand(384, 1024), _rand(2 * 640, 1024) * 0.05
+    aq, sa = fp8.quantize_rows(a)
+    wq, sw = fp8.quantize_rows(w)
+    pre = torch.empty(384, 1280, dtype=torch.bfloat16, device="cuda")
+    h = fp8.gemm_nt_fp8(aq, sa, wq, sw, swiglu=True, aux=pre)
+    gu = ((aq.float() * sa[:, None]) @ (wq.float() * sw[:, None]).t())
+    _close(pre, gu, tol=1e-2, what="fp8 swiglu pre-activations")
+    g, u = gu[:, :640].bfloat16().float(), gu[:, 640:].bfloat16().float()
+    _close(h, torch.nn.functional.silu(g) * u, tol=2e-2, what="fp8 swiglu out")
+
+
+def test_fp8_linear_and_mlp_autograd():
+    from adaptivetrainingsystem_b200.ops import fp8
+    torch.manual_seed(9)
+    x = _rand(4, 64, 512).requires_grad_()
+    w = (_rand(768, 512) * 0.05).requires_grad_()
+    w1 = (_rand(2 * 1024, 512) * 0.05).requires_grad_()
+    w2 = (_rand(512, 1024) * 0.05).requires_grad_()
+    fp8.set_enabled(True)
+    try:
+        y = ops.linear(x, w)
+        z = ops.swiglu_mlp(x, w1, w2, residual=x)
+        (y.float().pow(2).mean() + z.float().pow(2).mean()).backward()
+    finally:
+        fp8.set_enabled(False)
+    xr, wr, w1r, w2r = [t.detach().float().requires_grad_() for t in (x, w, w1, w2)]
+    yr = torch.nn.functional.linear(xr, wr)
+    gu = torch.nn.functional.linear(xr, w1r)
+    zr = torch.nn.functional.linear(torch.nn.functional.silu(gu[..., :1024]) * gu[..., 1024:], w2r) + xr
+    (yr.pow(2).mean() + zr.pow(2).mean()).backward()
+    _close(y, yr, tol=8e-2, what="fp8 linear out")
+    _close(z, zr, tol=8e-2, what="fp8 mlp out")
+    for a, b, n in ((x.grad, xr.grad, "dx"), (w.grad, wr.grad, "dw"), (w1.grad, w1r.grad, "dw1"), (w2.grad, w2r.grad, "dw2")):
+        cos = torch.nn.functional.cosine_similarity(a.float().flatten(), b.flatten(), dim=0).item()
+        assert cos > 0.99, (n, cos)
+    # the weight cache follows parameter updates made behind autograd's back
+    q0, _ = fp8.quantized_weight(w)
+    w.data.mul_(2.0)
+    fp8.weights_changed()
+    q1, s1 = fp8.quantized_weight(w)
+    assert torch.allclose(q1.float() * s1[:, None], w.detach().float(), rtol=0.07, atol=1e-3)
