@@ -32,7 +32,7 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 256;  // TMA, MMA, 4 epilogue warps, 2 copy warps (idle unless B is gathered from peers)
 constexpr int MAX_GROUPS = 256;
 constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + (MAX_GROUPS + 1) * 4;
 
@@ -61,6 +61,18 @@ struct GemmArgs {
   // fp8 (e4m3) operands: one byte per element, 128 elements per swizzle row and per K block, kind::f8f6f4 MMAs (K = 32).
   // The fp32 accumulator is multiplied by row_scale[row] * col_scale[col] in the epilogue (per-token activation scales,
   // per-output-channel weight scales), so the main loop needs no per-block promotion.
+  // All-gather fused into the GEMM (n_copy != 0): two warps of every CTA pull B, shard by shard, from the GPUs that own it
+  // (peer memory) into the local buffer that map_b covers and count every 4 KB piece into b_ready[chunk] (chunks of
+  // `ready_rows` rows).  The TMA producer waits (bounded) until the chunks its tile reads are complete (counter >= epoch),
+  // and tiles start at the columns of this rank's own shard, which is read in place: each remote byte crosses NVLink once
+  // while the tensor cores are already working.
+  int n_copy;
+  const void* const* b_src;  // [b_shards] base address of every rank's shard
+  long long shard_bytes, chunk_bytes;
+  uint8_t* b_dst;
+  int* b_ready;
+  int ready_rows, n_chunks, epoch, first_chunk, n_rot;
+  int own_row0, own_rows;    // rows of B that live in this rank's shard (read through map_b_own)
   int fp8;
   const float* row_scale;  // [groups * rs_gs] or null
   const float* col_scale;  // [weights * cs_gs] or null
@@ -109,7 +121,9 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   const int panel = local / (PANEL_N * tm);
   const int within = local - panel * PANEL_N * tm;
   const int width = min(PANEL_N, tn - panel * PANEL_N);
-  const int mt = within / width, nt = panel * PANEL_N + (within - mt * width);
+  const int mt = within / width;
+  int nt = panel * PANEL_N + (within - mt * width);
+  if (p.n_rot) nt = (nt + p.n_rot) % tn;  // gathered B: begin with the columns whose rows are already local
   t.g = g;
   t.m0 = mt * BM;
   t.n0 = nt * (p.epilogue == kSwiGLU ? 128 : BN);
@@ -121,7 +135,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const GemmArgs p) {
+                 const __grid_constant__ CUtensorMap map_b_own, const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -161,6 +175,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     prefix[p.groups] = acc;
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if (p.n_copy) tma_prefetch_desc(&map_b_own);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -171,15 +186,72 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = prefix[p.groups];
+  const int first_tile = int(blockIdx.x);
+  const int tile_step = int(gridDim.x);
 
-  if (warp == 0) {
+  if (warp >= 6) {
+    // ------------------------------------------------------------------ copy warps (gathered B only)
+    // Two warps of every CTA pull the remote shards of B into the local staging buffer, 4 KB per warp and step, in the
+    // order in which the tiles will need them; consecutive pieces of a chunk go to different CTAs, so the ~300 copy
+    // warps of the grid keep more than a megabyte in flight on NVLink.  A chunk's counter grows by one per piece.
+    if (p.n_copy) {
+      const long long cps = p.shard_bytes / p.chunk_bytes;
+      const long long per_chunk = p.chunk_bytes / 4096;
+      const long long total = (long long)(p.n_chunks - cps) * per_chunk;
+      const int own_hi = p.first_chunk + int(cps);
+      for (long long i = (warp - 6) + 2LL * blockIdx.x; i < total; i += 2LL * gridDim.x) {
+        const long long ci = i / per_chunk, pi = i - ci * per_chunk;
+        const int chunk = int((own_hi + ci) % p.n_chunks);
+        const long long off = (chunk % cps) * p.chunk_bytes + pi * 4096 + lane * 16;
+        const uint8_t* src = static_cast<const uint8_t*>(p.b_src[chunk / cps]) + off;
+        uint8_t* dst = p.b_dst + (long long)chunk * p.chunk_bytes + pi * 4096 + lane * 16;
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const uint4*>(src + j * 512);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(dst + j * 512) = v[j];
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");  // the tiles are read through the async proxy (TMA)
+        __syncwarp();
+        if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.b_ready + chunk) : "memory");
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0, phase = 0, g_hint = 0;
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      int ready_lo = 0, ready_hi = -1;  // chunk range of gathered B known to be present
+      auto wait_chunk = [&](int c) -> bool {
+        if (c >= p.n_chunks) c = p.n_chunks - 1;
+        if (c >= ready_lo && c <= ready_hi) return true;
+        if (c >= p.first_chunk && c < p.first_chunk + int(p.shard_bytes / p.chunk_bytes)) return true;  // own shard: read in place
+        const uint64_t t0 = globaltimer_ns();
+        int v;
+        do {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.b_ready + c) : "memory");
+          if (v >= p.epoch) break;  // epoch = pieces per chunk x number of calls so far
+          if (*abort_flag) return false;
+          if (globaltimer_ns() - t0 > ATS_WAIT_BUDGET_NS) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, int(kTimeoutPeerFlag));
+            return false;
+          }
+        } while (true);
+        if (c == ready_hi + 1) ready_hi = c;
+        else ready_lo = ready_hi = c;
+        asm volatile("fence.proxy.async;" ::: "memory");  // the data was written through the async proxy of another CTA
+        return true;
+      };
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint);
+        if (p.n_copy) {
+          const int r0 = t.n0, r1 = p.epilogue == kSwiGLU ? t.n0 + p.up_offset : t.n0 + 128;
+          ok = wait_chunk(r0 / p.ready_rows) && wait_chunk((r0 + 127) / p.ready_rows) && wait_chunk(r1 / p.ready_rows) &&
+               wait_chunk((r1 + 127) / p.ready_rows);
+          if (!ok) break;
+        }
         const int a_mn_c = t.m0 + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
         const int gb = t.g / p.b_div;
         const int b_mn_c = t.n0 + p.b_gs_mn * gb, b_k_c = p.b_gs_k * gb;
@@ -212,8 +284,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (!p.b_mn) {
             // two boxes of 64 x 128 rows; SwiGLU takes the second from the "up" half
             const int second = p.epilogue == kSwiGLU ? b_mn_c + p.up_offset : b_mn_c + 128;
-            tma_load_2d(b_dst, &map_b, &full[stage], b_k_c + k0, b_mn_c);
-            tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], b_k_c + k0, second);
+            if (p.n_copy) {
+              // gathered B: rows of this rank's own shard are read in place, the others from the staging buffer
+              const int o0 = b_mn_c - p.own_row0, o1 = second - p.own_row0;
+              if (o0 >= 0 && o0 < p.own_rows) tma_load_2d(b_dst, &map_b_own, &full[stage], k0, o0);
+              else tma_load_2d(b_dst, &map_b, &full[stage], k0, b_mn_c);
+              if (o1 >= 0 && o1 < p.own_rows) tma_load_2d(b_dst + 128 * 128, &map_b_own, &full[stage], k0, o1);
+              else tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], k0, second);
+            } else {
+              tma_load_2d(b_dst, &map_b, &full[stage], b_k_c + k0, b_mn_c);
+              tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], b_k_c + k0, second);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -242,7 +323,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                    : make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
       int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint);
         if (!mbar_wait_bounded(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
@@ -284,7 +365,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     int acc = 0, acc_phase = 0, g_hint = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
       TileCoord t = decode_tile(p, prefix, tile, g_hint);
       if (!mbar_wait_bounded(&tfull[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) break;
       tc_fence_after();
@@ -457,7 +538,7 @@ static int num_sms() {
 using namespace ats;
 
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
-                       int max_ctas, void* stream);
+                       int max_ctas, void* stream, const CUtensorMap* mb_own = nullptr);
 
 // Generic entry point. The global 2-D extents of both operands are given explicitly (rows x cols, cols contiguous,
 // pitch ld elements); for a K-major operand cols is the reduction dimension, for an MN-major operand rows is.
@@ -497,6 +578,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
   p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
+  p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
 
@@ -532,11 +614,56 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
   p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
+  p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
 
+// All-gather + GEMM in one kernel: D = A [M, K] * B^T with B [b_rows, K] row-sharded over `b_shards` GPUs.  `b_src` is a DEVICE
+// array of the shards' base addresses (peer memory; entry `my_rank` is local), `B_local` the [b_rows, K] staging buffer on this
+// GPU that the copy CTAs fill with the REMOTE shards and the GEMM reads (this rank's rows are read in place from `own_shard`), `b_ready` an int32 array of b_rows / ready_rows flags that only ever grow
+// (`calls` = how many times this weight has been gathered with these flags, this call included).  Epilogues: store, +C, SwiGLU.
+ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_local, const void* own_shard, long long b_rows, const void* const* b_src,
+                                   int b_shards, int my_rank, int ready_rows, int* b_ready, int calls, void* D, int ldd,
+                                   const void* C, int ldc, void* aux, int ldaux, int M, int N, int K, int epilogue, int up_offset,
+                                   int* status, void* stream) {
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
+  if (b_shards < 1 || my_rank < 0 || my_rank >= b_shards || ready_rows < 64 || calls < 1) return 1002;
+  if (((long long)ready_rows * K * 2) % 4096) return 1003;
+  if ((N & 7) || (K & 7) || (ldd & 7) || (b_rows % b_shards) || ((b_rows / b_shards) % ready_rows)) return 1003;
+  if (epilogue == kF32 || (epilogue == kSwiGLU && (up_offset & 7))) return 1004;
+  CUtensorMap ma, mb;
+  int e;
+  if ((e = make_tmap_2d(&ma, A, M, K, lda, 2, 64, 128))) return e;
+  if ((e = make_tmap_2d(&mb, B_local, b_rows, K, K, 2, 64, 128))) return e;
+  CUtensorMap mb_own;
+  if ((e = make_tmap_2d(&mb_own, own_shard, b_rows / b_shards, K, K, 2, 64, 128))) return e;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K; p.groups = 1; p.ragged = 0; p.counts = nullptr;
+  p.a_gs_mn = 0; p.a_gs_k = 0; p.b_gs_mn = 0; p.b_gs_k = 0; p.d_gs = 0; p.c_gs = 0; p.aux_gs = 0;
+  p.D = static_cast<__nv_bfloat16*>(D); p.C = static_cast<const __nv_bfloat16*>(C);
+  p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
+  p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
+  p.up_offset = up_offset; p.alpha = 1.f; p.beta = 0; p.status = status;
+  p.b_div = 1; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
+  p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
+  const long long shard_rows = b_rows / b_shards;
+  p.n_copy = 1; p.b_src = b_src; p.b_dst = static_cast<uint8_t*>(const_cast<void*>(B_local));
+  p.shard_bytes = shard_rows * K * 2; p.chunk_bytes = (long long)ready_rows * K * 2;
+  p.b_ready = b_ready; p.ready_rows = ready_rows; p.n_chunks = int(b_rows / ready_rows);
+  p.epoch = int(calls * (p.chunk_bytes / 4096));  // every call adds chunk_bytes / 4096 to each remote chunk's counter
+  p.first_chunk = int(my_rank * (shard_rows / ready_rows));
+  p.own_row0 = int(my_rank * shard_rows); p.own_rows = int(shard_rows);
+  const int tile_w = epilogue == kSwiGLU ? 128 : BN;
+  p.n_rot = int((my_rank * shard_rows) % (epilogue == kSwiGLU ? (long long)up_offset : b_rows) / tile_w);
+  return launch_gemm(ma, mb, p, epilogue, 1, M, N, 0, stream, &mb_own);
+}
+
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
-                       int max_ctas, void* stream) {
+                       int max_ctas, void* stream, const CUtensorMap* mb_own) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
@@ -547,8 +674,12 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
   long long upper = (long long)groups * ((M + BM - 1) / BM) * tn;
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (upper < grid) grid = int(upper);
+  if (p.n_copy > 0) {
+    // producers wait on the copy warps of other CTAs of this launch: keep the whole grid (one CTA per SM) resident
+  } else if (upper < grid) {
+    grid = int(upper);
+  }
   if (grid < 1) return 0;
-  gemm_bf16_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+  gemm_bf16_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, mb_own ? *mb_own : mb, p);
   return int(cudaGetLastError());
 }
