@@ -323,6 +323,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                    : make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
       int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
       bool ok = true;
+      // K-major operand: 32 bytes per MMA along the swizzle row; MN-major: 16 K-rows of 128 bytes per MMA
+      const uint64_t a_desc0 = p.a_mn ? make_smem_desc_sw128(smem_u32(sA), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sA), 16, 1024);
+      const uint64_t b_desc0 = p.b_mn ? make_smem_desc_sw128(smem_u32(sB), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sB), 16, 1024);
+      const uint64_t a_step16 = (p.a_mn ? UK * 128 : UK * 2) >> 4, b_step16 = (p.b_mn ? UK * 128 : UK * 2) >> 4;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint);
         if (!mbar_wait_bounded(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
@@ -334,16 +338,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+          // descriptors: one base per operand (built before the tile loop), advanced by constants
+          const uint64_t adesc = desc_advance(a_desc0, uint32_t(stage) * A_STAGE_BYTES);
+          const uint64_t bdesc = desc_advance(b_desc0, uint32_t(stage) * B_STAGE_BYTES);
+          if (p.fp8) {
 #pragma unroll
-          for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(a_addr + k * (UK * 128), BK * 128, 1024)
-                                          : make_smem_desc_sw128(a_addr + k * (UK * 2), 16, 1024);
-            const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_addr + k * (UK * 128), BK * 128, 1024)
-                                          : make_smem_desc_sw128(b_addr + k * (UK * 2), 16, 1024);
-            if (p.fp8) tc_mma_f8(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);  // 32 bytes of K per MMA either way
-            else tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / UK; ++k) tc_mma_f8(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / UK; ++k) tc_mma_f16(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
           }
           tc_commit(&empty[stage]);  // the stage is free once these MMAs have read it
           if (++stage == STAGES) {
@@ -680,6 +683,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     grid = int(upper);
   }
   if (grid < 1) return 0;
-  gemm_bf16_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, mb_own ? *mb_own : mb, p);
+  // the two copy warps exist only in launches that gather B from peers
+  gemm_bf16_kernel<<<grid, p.n_copy ? GEMM_THREADS : GEMM_THREADS - 64, GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+      ma, mb, mb_own ? *mb_own : mb, p);
   return int(cudaGetLastError());
 }
