@@ -52,7 +52,7 @@ def _L():
         sig("ats_topk_softmax", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _vp)
         sig("ats_plan_slots", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_dispatch_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
-        sig("ats_combine_rows", _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
+        sig("ats_combine_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_slot_dot", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_mod_select", _vp, _vp, _c_int, _c_int, _c_int, _vp)
         _sig_done = True
@@ -235,18 +235,40 @@ def masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor] = None, sc
 # ----------------------------------------------------------------------------------------------------------
 # Linear
 # ----------------------------------------------------------------------------------------------------------
+_SINK_OWNERS = {}  # data_ptr -> parameter that carries the sink attributes
+
+
+def register_grad_sink(p: torch.Tensor) -> None:
+    """Engines call this for every parameter they give an ``_ats_grad`` view.  Under activation checkpointing the tensors a
+    backward function gets back from ``saved_tensors`` are new Python objects without the attributes; the owner is then
+    found again by the storage address."""
+    _SINK_OWNERS[p.data_ptr()] = p
+
+
+def _sink_owner(w: torch.Tensor):
+    if hasattr(w, "_ats_grad"):
+        return w
+    o = _SINK_OWNERS.get(w.data_ptr())
+    if o is not None and o.shape == w.shape and o.data_ptr() == w.data_ptr() and hasattr(o, "_ats_grad"):
+        return o
+    return None
+
+
 def _grad_sink(w: torch.Tensor):
     """A parameter may carry ``_ats_grad`` (a view into a flat gradient bucket).  Weight gradients are then
     written (first micro-batch) or accumulated (later ones) straight into it by the GEMM epilogue, and autograd
     receives ``None``."""
-    return getattr(w, "_ats_grad", None)
+    o = _sink_owner(w)
+    return None if o is None else o._ats_grad
 
 
 def _deliver_grad(w: torch.Tensor, compute):
     """compute(out, accumulate) -> tensor.  Returns what autograd should see for ``w``."""
-    sink = _grad_sink(w)
+    o = _sink_owner(w)
+    sink = None if o is None else o._ats_grad
     if sink is None:
         return compute(None, False)
+    w = o
     fresh = getattr(w, "_ats_grad_fresh", True)
     compute(sink.view(w.shape), not fresh)
     w._ats_grad_fresh = False

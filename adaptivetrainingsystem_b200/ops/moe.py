@@ -158,16 +158,20 @@ def dispatch(x: torch.Tensor, topk_idx: torch.Tensor, slot_pos: torch.Tensor, co
 
 
 def combine(buf: torch.Tensor, topk_idx: torch.Tensor, slot_pos: torch.Tensor, topk_w: Optional[torch.Tensor],
-            tokens: int, residual: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = residual[t] + sum_j w[t,j] * buf[e_j, pos_j] over kept slots."""
+            tokens: int, residual: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None,
+            keep_copy: bool = False) -> torch.Tensor:
+    """out[t] = residual[t] + sum_j w[t,j] * buf[e_j, pos_j] over kept slots.  ``table`` (int64 [E]) replaces the base address
+    of every expert's rows (e.g. buffers on the GPUs that own the experts: the rows are then pulled over NVLink);
+    ``keep_copy`` stores the pulled rows into ``buf`` as well."""
     E, C, H = buf.shape
     k = topk_idx.shape[1]
     if _lib.use_cuda_kernels(buf):
         out = torch.empty(tokens, H, dtype=buf.dtype, device=buf.device)
+        copy_table = _ptr_table(buf) if (keep_copy and table is not None) else None
         if table is None:
             table = _ptr_table(buf)
         w = topk_w.contiguous().float() if topk_w is not None else None
-        _CK(_L().ats_combine_rows(_P(table), _P(topk_idx), _P(slot_pos), _P(w), _P(residual), _P(out), tokens, k, H,
+        _CK(_L().ats_combine_rows(_P(table), _P(copy_table), _P(topk_idx), _P(slot_pos), _P(w), _P(residual), _P(out), tokens, k, H,
                                   _S(buf.device)), "combine_rows")
         return out
     flat_e = topk_idx.reshape(-1).long()

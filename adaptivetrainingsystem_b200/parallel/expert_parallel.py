@@ -19,6 +19,8 @@ Two transports with identical numerics:
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -42,9 +44,9 @@ class _LayerBuffers:
         es = torch.empty((), dtype=dtype).element_size()
         if comm.fused:
             from .peer import SymmetricBuffer
-            # one symmetric allocation: recv_x | ret_y | recv_g | ret_dx | counts
+            # one symmetric allocation: recv_x | ret_y | recv_g | ret_dx | counts | own_y | own_dx
             off = [0]
-            for n in (n_recv * es, n_ret * es, n_recv * es, n_ret * es, El * W * 4):
+            for n in (n_recv * es, n_ret * es, n_recv * es, n_ret * es, El * W * 4, n_recv * es, n_recv * es):
                 off.append(off[-1] + (n + 255) // 256 * 256)
             self.sym = SymmetricBuffer(off[-1], comm.group, device)
             s = self.sym
@@ -53,6 +55,10 @@ class _LayerBuffers:
             self.recv_g = s.tensor(dtype, n_recv, off[2]).view(El * W, C, H)
             self.ret_dx = s.tensor(dtype, n_ret, off[3]).view(E, C, H)
             self.counts = s.tensor(torch.int32, El * W, off[4])
+            # expert outputs (forward) and input gradients (backward) stay on the GPU that computed them; the source ranks
+            # pull their rows in the combine kernel (coalesced 4 KB row reads instead of scattered remote stores)
+            self.own_y = s.tensor(dtype, n_recv, off[5]).view(El * W, C, H)
+            self.own_dx = s.tensor(dtype, n_recv, off[6]).view(El * W, C, H)
             e = torch.arange(E, dtype=torch.int64)
             owner, el = e // El, e % El
             base = torch.tensor(s.ptrs, dtype=torch.int64)
@@ -61,6 +67,9 @@ class _LayerBuffers:
             self.t_disp_x = (base[owner] + off[0] + block).to(device)
             self.t_disp_g = (base[owner] + off[2] + block).to(device)
             self.t_count = (base[owner] + off[4] + (el * W + r) * 4).to(device)
+            # ... and where the results for this rank's rows of expert e can be read from
+            self.t_pull_y = (base[owner] + off[5] + block).to(device)
+            self.t_pull_dx = (base[owner] + off[6] + block).to(device)
             # where the output of local group g = e_local * W + src goes on rank src
             g = torch.arange(El * W, dtype=torch.int64)
             gel, src = g // W, g % W
@@ -83,6 +92,8 @@ class ExpertParallelComm:
         self.W = mesh.ep_size
         self.rank = mesh.coord.ep
         self.fused = bool(fused) and torch.cuda.is_available()
+        # results travel back by pull (the combine kernel reads the owners' buffers) or by push (GEMM epilogue stores)
+        self.pull_results = os.environ.get("ATS_EP_RETURN", "pull") == "pull"
         self.barrier = None
         if self.fused:
             from .peer import PeerBarrier
@@ -142,13 +153,18 @@ class _EPMoEFn(torch.autograd.Function):
         need_bwd = any(ctx.needs_input_grad)
         pre = torch.empty(buf.El * W, C, w1.shape[1], dtype=x.dtype, device=x.device) if need_bwd else None
         h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, pre_act=pre, b_div=W)
-        if comm.fused:
-            G.grouped_nt(h, w2, buf.counts, b_div=W, d_table=buf.t_ret_y)
+        if comm.fused and comm.pull_results:
+            G.grouped_nt(h, w2, buf.counts, b_div=W, out=buf.own_y)
             comm.barrier()
+            out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual, table=buf.t_pull_y, keep_copy=True)
         else:
-            ye = G.grouped_nt(h, w2, buf.counts, b_div=W)
-            comm.exchange_to_sources(ye, buf.ret_y)
-        out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual)
+            if comm.fused:
+                G.grouped_nt(h, w2, buf.counts, b_div=W, d_table=buf.t_ret_y)
+                comm.barrier()
+            else:
+                ye = G.grouped_nt(h, w2, buf.counts, b_div=W)
+                comm.exchange_to_sources(ye, buf.ret_y)
+            out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual)
         ctx.save_for_backward(topk_idx, slot_pos, counts, topk_w, w1, w2, pre)
         ctx.comm, ctx.buf, ctx.capacity, ctx.has_res = comm, buf, capacity, residual is not None
         ctx.mark_non_differentiable(totals)
@@ -183,13 +199,18 @@ class _EPMoEFn(torch.autograd.Function):
             h = (g * s * u).to(pre.dtype)
         dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(buf.recv_g, h, buf.counts, out=out, accumulate=acc, k_segs=W))
         dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, buf.recv_x, buf.counts, out=out, accumulate=acc, k_segs=W))
-        if comm.fused:
-            G.grouped_nn(dgu, w1, buf.counts, b_div=W, d_table=buf.t_ret_dx)
+        if comm.fused and comm.pull_results:
+            G.grouped_nn(dgu, w1, buf.counts, b_div=W, out=buf.own_dx)
             comm.barrier()
+            dx = M.combine(buf.ret_dx, topk_idx, slot_pos, None, T, None, table=buf.t_pull_dx)
         else:
-            dxe = G.grouped_nn(dgu, w1, buf.counts, b_div=W)
-            comm.exchange_to_sources(dxe, buf.ret_dx)
-        dx = M.combine(buf.ret_dx, topk_idx, slot_pos, None, T, None)
+            if comm.fused:
+                G.grouped_nn(dgu, w1, buf.counts, b_div=W, d_table=buf.t_ret_dx)
+                comm.barrier()
+            else:
+                dxe = G.grouped_nn(dgu, w1, buf.counts, b_div=W)
+                comm.exchange_to_sources(dxe, buf.ret_dx)
+            dx = M.combine(buf.ret_dx, topk_idx, slot_pos, None, T, None)
         return dx, None, dw_topk, dw1, dw2, None, (dout if ctx.has_res else None), None, None
 
 

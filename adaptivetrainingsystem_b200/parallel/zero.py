@@ -62,6 +62,7 @@ class Bucket:
             p.data = self.flat_param[o:o + p.numel()].view(p.shape)
             p._ats_grad = self.flat_grad[o:o + p.numel()]
             p._ats_grad_fresh = True
+            ops.functional.register_grad_sink(p)
             p.grad = None
         lo, hi = self.owned_range()
         self.master = self.flat_param[lo:hi].float().clone()

@@ -257,8 +257,8 @@ dispatch_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restric
 
 // Combine: out[t] = (res[t]) + sum_j w[t,j] * rows[e_j][pos_j]   over kept slots; one warp per token.
 __global__ void __launch_bounds__(256)
-combine_rows_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restrict__ topk_idx,
-                    const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
+combine_rows_kernel(__nv_bfloat16* const* __restrict__ src_base, __nv_bfloat16* const* __restrict__ copy_base,
+                    const int* __restrict__ topk_idx, const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
                     const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, long long tokens, int k, int hidden) {
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -275,7 +275,10 @@ combine_rows_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __re
       const int pos = slot_pos[t * k + j];
       if (pos < 0) continue;
       const float wt = topk_w ? topk_w[t * k + j] : 1.f;
-      uint4 a = reinterpret_cast<const uint4*>(src_base[topk_idx[t * k + j]] + (long long)pos * hidden)[v];
+      const int e = topk_idx[t * k + j];
+      uint4 a = reinterpret_cast<const uint4*>(src_base[e] + (long long)pos * hidden)[v];
+      // rows pulled from a peer GPU are kept in a local copy for the backward pass (gate-weight gradient)
+      if (copy_base) reinterpret_cast<uint4*>(copy_base[e] + (long long)pos * hidden)[v] = a;
       float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
       acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
       acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
@@ -423,13 +426,13 @@ ATS_API int ats_dispatch_rows(const void* src, const int* topk_idx, const int* s
   return int(cudaGetLastError());
 }
 
-ATS_API int ats_combine_rows(void* const* src_base, const int* topk_idx, const int* slot_pos, const float* topk_w,
+ATS_API int ats_combine_rows(void* const* src_base, void* const* copy_base, const int* topk_idx, const int* slot_pos, const float* topk_w,
                              const void* res, void* out, long long tokens, int k, int hidden, void* stream) {
   if (hidden & 7) return 1003;
   if (tokens == 0) return 0;
   combine_rows_kernel<<<unsigned((tokens * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<__nv_bfloat16* const*>(src_base), topk_idx, slot_pos, topk_w, static_cast<const __nv_bfloat16*>(res),
-      static_cast<__nv_bfloat16*>(out), tokens, k, hidden);
+      reinterpret_cast<__nv_bfloat16* const*>(src_base), reinterpret_cast<__nv_bfloat16* const*>(copy_base), topk_idx, slot_pos, topk_w,
+      static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(out), tokens, k, hidden);
   return int(cudaGetLastError());
 }
 
