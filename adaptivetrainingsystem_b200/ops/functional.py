@@ -39,6 +39,7 @@ def _L():
         sig("ats_rope", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
         sig("ats_swiglu_fwd", _vp, _vp, _c_ll, _c_int, _vp)
         sig("ats_swiglu_bwd", _vp, _vp, _vp, _vp, _c_ll, _c_int, _vp)
+        sig("ats_swiglu_bwd_grouped", _vp, _vp, _vp, _vp, _c_int, _c_int, _vp, _c_int, _vp)
         sig("ats_embedding_fwd", _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _vp)
         sig("ats_embedding_bwd", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _c_int, _vp)
         sig("ats_cast_f32_bf16", _vp, _vp, _c_ll, _c_int, _c_f, _vp)
@@ -60,7 +61,9 @@ def _L():
 
 
 _P, _S, _CK = _lib.ptr, _lib.stream_ptr, _lib.check
-_NORM_BLOCKS = 296  # 2 CTAs per SM for the row-walking backward kernels
+import os as _os
+
+_NORM_BLOCKS = int(_os.environ.get("ATS_NORM_BLOCKS", "1184"))  # CTAs of the row-walking backward kernels (8 per SM keeps enough rows in flight)
 
 
 # ----------------------------------------------------------------------------------------------------------

@@ -243,7 +243,7 @@ class _MoEFFNFn(torch.autograd.Function):
         if _lib.use_cuda_kernels(pre):
             dgu = torch.empty_like(pre)
             h = torch.empty(E, C, inter, dtype=pre.dtype, device=pre.device)
-            _CK(_L().ats_swiglu_bwd(_P(pre), _P(dh), _P(dgu), _P(h), E * C, inter, _S(pre.device)), "swiglu_bwd")
+            _CK(_L().ats_swiglu_bwd_grouped(_P(pre), _P(dh), _P(dgu), _P(h), E, C, _P(counts), inter, _S(pre.device)), "swiglu_bwd")
         else:
             g, u = pre.float().chunk(2, dim=-1)
             s = torch.sigmoid(g)

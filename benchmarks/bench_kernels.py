@@ -84,6 +84,11 @@ def main():
     # memory-bound kernels
     rows_, cols = 16384, 2048
     x, wn = rnd(rows_, cols), torch.ones(cols, device=DEV, dtype=torch.bfloat16)
+    xg = x.detach().clone().requires_grad_()
+    wg = wn.detach().clone().requires_grad_()
+    yg = ops.rms_norm(xg, wg, 1e-6)
+    gy = rnd(rows_, cols)
+    report("rmsnorm_bwd 16384x2048", time_cuda(lambda: torch.autograd.grad(yg, (xg, wg), gy, retain_graph=True)), nbytes=3.0 * rows_ * cols * 2)
     report("rmsnorm_fwd 16384x2048", time_cuda(lambda: ops.rms_norm(x, wn, 1e-6)), nbytes=2.0 * rows_ * cols * 2,
            lib_ms=time_cuda(lambda: ops.rms_norm_reference(x, wn, 1e-6)))
     gu = rnd(rows_, 2 * 5632)

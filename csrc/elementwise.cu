@@ -146,15 +146,25 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-// dw[c] (+)= sum_b partial[b][c]; output bf16 or fp32.
-__global__ void colsum_partial_kernel(const float* __restrict__ partial, int nblocks, int cols,
-                                      __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// dw[c] (+)= sum_b partial[b][c]; output bf16 or fp32.  One CTA per 32 columns: 8 row lanes x 32 columns read the partials
+// with 128-byte coalesced accesses, then the row lanes are folded through shared memory (fixed order: deterministic).
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const float* __restrict__ partial, int nblocks, int cols,
+                                                             __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32, int accumulate) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * cols + c];
-  if (out_f32) out_f32[c] = accumulate ? out_f32[c] + s : s;
-  if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + s : s);
+  if (c < cols)
+    for (int b = rl; b < nblocks; b += 8) s += partial[(long long)b * cols + c];
+  red[rl][lane] = s;
+  __syncthreads();
+  if (rl == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += red[j][lane];
+    if (out_f32) out_f32[c] = accumulate ? out_f32[c] + t : t;
+    if (out_bf16) out_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(out_bf16[c]) + t : t);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -218,14 +228,21 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
   }
 }
 
+// counts != nullptr: the rows form groups of `cap` rows (expert capacity layout, blockIdx.y = group) of which only the first
+// round_up_128(counts[g]) are in use; the rest is neither read nor written (the ragged GEMMs never look at it).
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh,
                                   __nv_bfloat16* __restrict__ dgu, __nv_bfloat16* __restrict__ h_out, long long rows,
-                                  int inter) {
+                                  int inter, const int* __restrict__ counts, int cap) {
   const int vpr = inter >> 3;
+  long long row0 = 0;
+  if (counts) {
+    row0 = (long long)blockIdx.y * cap;
+    rows = min((counts[blockIdx.y] + 127) & ~127, cap);
+  }
   const long long total = rows * vpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / vpr;
-    const int v = int(i - r * vpr);
+    const long long r = row0 + i / vpr;
+    const int v = int(i % vpr);
     const __nv_bfloat16* row = gu + r * 2 * inter;
     uint4 g = reinterpret_cast<const uint4*>(row)[v];
     uint4 u = reinterpret_cast<const uint4*>(row + inter)[v];
@@ -366,14 +383,14 @@ ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
   else if (cols <= 256 * 32) rmsnorm_bwd_kernel<256><<<nblocks, 256, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else if (cols <= 512 * 32) rmsnorm_bwd_kernel<512><<<nblocks, 512, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else return 1003;
-  colsum_partial_kernel<<<(cols + 255) / 256, 256, 0, s>>>(dw_partial, nblocks, cols, static_cast<__nv_bfloat16*>(dw_bf16),
+  colsum_partial_kernel<<<(cols + 31) / 32, 256, 0, s>>>(dw_partial, nblocks, cols, static_cast<__nv_bfloat16*>(dw_bf16),
                                                           dw_f32, accumulate);
   return int(cudaGetLastError());
 }
 
 ATS_API int ats_colsum_partial(const float* partial, int nblocks, int cols, void* out_bf16, float* out_f32, int accumulate,
                                void* stream) {
-  colsum_partial_kernel<<<(cols + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  colsum_partial_kernel<<<(cols + 31) / 32, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       partial, nblocks, cols, static_cast<__nv_bfloat16*>(out_bf16), out_f32, accumulate);
   return int(cudaGetLastError());
 }
@@ -402,7 +419,21 @@ ATS_API int ats_swiglu_bwd(const void* gu, const void* dh, void* dgu, void* h_ou
   if (rows == 0) return 0;
   swiglu_bwd_kernel<<<grid_for(rows * (inter >> 3), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh), static_cast<__nv_bfloat16*>(dgu),
-      static_cast<__nv_bfloat16*>(h_out), rows, inter);
+      static_cast<__nv_bfloat16*>(h_out), rows, inter, nullptr, 0);
+  return int(cudaGetLastError());
+}
+
+// Capacity layout [groups, cap, *]: only the first round_up_128(counts[g]) rows of every group are processed.
+ATS_API int ats_swiglu_bwd_grouped(const void* gu, const void* dh, void* dgu, void* h_out, int groups, int cap, const int* counts, int inter,
+                                   void* stream) {
+  if ((inter & 7) || groups > 65535) return 1003;
+  if (groups == 0 || cap == 0) return 0;
+  unsigned gx = grid_for((long long)cap * (inter >> 3), 256);
+  const unsigned per_group = (148u * 16u + groups - 1) / groups;  // about 16 CTAs per SM over all groups
+  if (gx > per_group) gx = per_group;
+  swiglu_bwd_kernel<<<dim3(gx, groups), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh), static_cast<__nv_bfloat16*>(dgu),
+      static_cast<__nv_bfloat16*>(h_out), 0, inter, counts, cap);
   return int(cudaGetLastError());
 }
 
