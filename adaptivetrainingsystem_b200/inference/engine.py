@@ -134,8 +134,13 @@ class GenerationEngine:
         return logits[:, -1, :]
 
     @torch.no_grad()
+    def graph_decoder(self, cache: KVCache) -> "GraphDecoder":
+        """Capture one decode step (all layers, launch-bound at batch <= 64) into a CUDA graph bound to ``cache``."""
+        return GraphDecoder(self.model, cache)
+
+    @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, params: Optional[SamplingParams] = None,
-                 on_token: Optional[Callable[[int, torch.Tensor], None]] = None) -> Dict[str, object]:
+                 on_token: Optional[Callable[[int, torch.Tensor], None]] = None, use_graph: Optional[bool] = None) -> Dict[str, object]:
         """input_ids [B, Lp] (equal-length prompts) -> dict(tokens [B, <=max_new], prefill_s, decode_s, ...).
         Timed with device synchronisation on both sides of each phase."""
         params = params or SamplingParams()
@@ -154,6 +159,11 @@ class GenerationEngine:
         t1 = time.perf_counter()
         history = input_ids
         out: List[torch.Tensor] = []
+        decoder = None
+        if use_graph is None:
+            use_graph = dev.type == "cuda" and next(self.model.parameters()).dtype == torch.bfloat16 and params.max_new_tokens > 8
+        if use_graph:
+            decoder = self.graph_decoder(cache)  # capture is part of the timed decode phase
         finished = torch.zeros(B, dtype=torch.bool, device=dev)
         stop = torch.tensor(list(params.stop_token_ids), device=dev, dtype=torch.long) if params.stop_token_ids else None
         steps = 0
@@ -169,13 +179,14 @@ class GenerationEngine:
                 break
             history = torch.cat([history, nxt[:, None]], dim=1)
             if step + 1 < params.max_new_tokens:
-                logits = self.decode_step(nxt, cache)
+                logits = decoder.step(nxt) if decoder is not None else self.decode_step(nxt, cache)
         sync()
         t2 = time.perf_counter()
         self.stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1, "prefill_tokens_per_s": B * Lp / max(t1 - t0, 1e-9),
                       "decode_tokens_per_s": B * max(steps - 1, 1) / max(t2 - t1, 1e-9), "steps": steps}
         return {"tokens": torch.stack(out, dim=1), **self.stats}
 
+    # ---------------------------------------------------------------------------------------------------------------
     def generate_text(self, prompt: str, params: Optional[SamplingParams] = None) -> str:
         if self.tokenizer is None:
             raise RuntimeError("a tokenizer is needed for text generation")
@@ -202,3 +213,45 @@ class GenerationEngine:
                 yield self.tokenizer.decode([int(nxt)])
                 history = torch.cat([history, nxt[:, None]], dim=1)
                 logits = self.decode_step(nxt, cache)
+
+
+class GraphDecoder:
+    """One decode step of the whole model as a CUDA graph.  A decode step at serving batch sizes is a few hundred small
+    launches whose host-side cost exceeds their device time; replaying a captured graph removes that cost.  Everything that
+    changes from step to step lives in device memory: the input tokens (a static buffer), the cache fill level and the RoPE
+    positions (``KVCache.device_lengths`` / ``device_positions``, advanced inside the graph)."""
+
+    def __init__(self, model: DeepSeekTransformer, cache: KVCache, warmup: int = 2):
+        self.model, self.cache = model, cache
+        dev = cache.k[0].device
+        B = cache.k[0].shape[0]
+        self.tokens = torch.zeros(B, 1, dtype=torch.long, device=dev)
+        start = cache.length
+        cache.enable_device_lengths()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(warmup):  # builds every lazily created buffer / function attribute outside the capture
+                self._run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        cache.device_lengths.fill_(start)   # the warm-up wrote K / V beyond the fill level: harmless, rewind the counters
+        cache.device_positions.fill_(start)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.logits = self._run()
+        cache.device_lengths.fill_(start)   # capture does not execute, but keep the invariant explicit
+        cache.device_positions.fill_(start)
+
+    def _run(self) -> torch.Tensor:
+        logits = self.model(self.tokens, cache=self.cache, last_token_only=True, return_aux_loss=False)[:, -1, :]
+        self.cache.device_advance()
+        return logits
+
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B] -> logits [B, V] (a static buffer that the next step overwrites)."""
+        if self.cache.length + 1 > self.cache.max_len:
+            raise RuntimeError(f"KV cache overflow: {self.cache.length}+1 > {self.cache.max_len}")
+        self.tokens.copy_(tokens.view(-1, 1))
+        self.graph.replay()
+        self.cache.length += 1
+        return self.logits

@@ -87,6 +87,21 @@ class KVCache:
         self.v = [torch.zeros(batch, max_len, n_kv, head_dim, dtype=dtype, device=device) for _ in range(num_layers)]
         self.length = 0
         self.max_len = max_len
+        # device-side copy of the fill level, used when the decode step is replayed from a CUDA graph (a Python integer
+        # would be frozen into the captured launches): per-sequence lengths for the attention kernel, positions for RoPE
+        self.device_lengths: Optional[torch.Tensor] = None
+        self.device_positions: Optional[torch.Tensor] = None
+
+    def enable_device_lengths(self) -> None:
+        dev = self.k[0].device
+        B = self.k[0].shape[0]
+        self.device_lengths = torch.full((B,), self.length, dtype=torch.int32, device=dev)
+        self.device_positions = torch.full((B,), self.length, dtype=torch.int32, device=dev)
+
+    def device_advance(self) -> None:
+        """One decoded token: called inside the captured step."""
+        self.device_lengths += 1
+        self.device_positions += 1
 
     def append(self, layer: int, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         n = k.shape[1]
@@ -117,6 +132,14 @@ class GroupedQueryAttention(nn.Module):
                 positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, L, _ = h.shape
         offset = cache.length if cache is not None else 0
+        graph_decode = cache is not None and cache.device_lengths is not None and L == 1
+        if graph_decode:
+            # fill level and positions come from device memory, nothing of this call depends on Python state
+            rope.ensure(cache.max_len, h.device)
+            qkv = ops.linear(h, self.qkv_proj)
+            qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, positions=cache.device_positions.view(B, 1))
+            a = ops.decode_attention(qkv, cache.k[self.layer_idx], cache.v[self.layer_idx], cache.device_lengths, self.n_q, self.n_kv, self.d)
+            return ops.linear(a, self.o_proj, residual=residual)
         rope.ensure(offset + L if positions is None else int(self.cfg.seq_length), h.device)
         qkv = ops.linear(h, self.qkv_proj)
         qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=offset, positions=positions)
@@ -434,8 +457,8 @@ class DeepSeekTransformer(nn.Module):
         for blk in self.layers:
             x, aux = blk(x, self.rope, attention_mask, cache, positions, decode)
             aux_losses.append(aux.float().clamp(max=1.0))
-        if cache is not None:
-            cache.advance(input_ids.shape[1])
+        if cache is not None and not (cache.device_lengths is not None and input_ids.shape[1] == 1):
+            cache.advance(input_ids.shape[1])  # (a graph-replayed decode step advances the device-side counters instead)
         x = self.norm(x)
         return x, aux_losses
 

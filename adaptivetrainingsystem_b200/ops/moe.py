@@ -97,7 +97,10 @@ def load_balancing_loss(clean_probs: torch.Tensor, topk_idx: torch.Tensor, num_e
                         token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """E * sum_e f_e * P_e * weight, clamped to <= 1 (reference ``core/model.py:1244-1263``)."""
     flat = topk_idx.reshape(-1).long()
-    counts = torch.bincount(flat, minlength=num_experts).float()
+    # scatter-add instead of bincount: no device-to-host synchronisation (bincount reads back the maximum), so the host keeps
+    # running ahead of the GPU and the step can be captured in a CUDA graph
+    counts = torch.zeros(num_experts, dtype=torch.float32, device=flat.device).scatter_add_(
+        0, flat, torch.ones(flat.numel(), dtype=torch.float32, device=flat.device))
     f = counts / max(flat.numel(), 1)
     p = clean_probs.mean(0)
     return (num_experts * (f * p).sum() * weight).clamp(max=1.0)

@@ -58,7 +58,7 @@ def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     longest = int(max_tokens if max_tokens is not None else (max_len - 1 if per_seq else length))
     if longest + 1 > max_len:
         raise RuntimeError(f"KV cache overflow: {longest}+1 > {max_len}")
-    if not _lib.use_cuda_kernels(qkv):
+    if not decode_attention_available(qkv, n_q, n_kv, d):
         return decode_attention_reference(qkv, k_cache, v_cache, length, n_q, n_kv, d)
     lib = _fns()
     chunks = lib.ats_decode_attn_chunks(max_len)

@@ -151,3 +151,27 @@ def test_tiny_config_trains_twenty_steps():
         eng.step()
         losses.append(out["lm_loss"].item())
     assert losses[-1] < losses[0] - 0.5 and all(math.isfinite(l) for l in losses)
+
+
+def test_decode_with_device_side_cache_counters_matches_python_counters():
+    """The graph-replayable decode path (fill level and RoPE positions in device tensors) gives the same logits as the
+    ordinary cached decode."""
+    import torch
+    from adaptivetrainingsystem_b200.config import ConfigPresets
+    from adaptivetrainingsystem_b200.models.transformer import DeepSeekTransformer
+    torch.manual_seed(3)
+    cfg = ConfigPresets.tiny_cpu()
+    model = DeepSeekTransformer(cfg.to_model_config()).eval()
+    ids = torch.randint(0, cfg.vocab_size, (2, 9))
+    with torch.no_grad():
+        c1, c2 = model.make_cache(2, 16), model.make_cache(2, 16)
+        model(ids[:, :6], cache=c1, return_aux_loss=False)
+        model(ids[:, :6], cache=c2, return_aux_loss=False)
+        c2.enable_device_lengths()
+        for t in range(6, 9):
+            a = model(ids[:, t:t + 1], cache=c1, last_token_only=True, return_aux_loss=False)
+            b = model(ids[:, t:t + 1], cache=c2, last_token_only=True, return_aux_loss=False)
+            c2.device_advance()
+            c2.length += 1
+            assert torch.allclose(a, b, atol=1e-5), t
+        assert c2.device_lengths.tolist() == [9, 9] and c1.length == 9
