@@ -66,6 +66,10 @@ def run(args, published) -> dict:
     dev = torch.device("cuda", local)
     shape = dict(SHAPES[args.config])
     mb, accum = shape.pop("micro_batch"), shape.pop("accum")
+    if world > 1 and args.config == "b1_moe" and not args.layers:
+        # the micro-batch the reference's single-GPU run settles at after its out-of-memory halving (8 -> 2, same tokens per
+        # step); ranks of a multi-GPU job cannot halve independently without desynchronising their collectives
+        mb, accum = 2, 16
     if args.micro_batch:
         mb = args.micro_batch
     if args.accum:
@@ -98,6 +102,10 @@ def run(args, published) -> dict:
                              gradient_checkpointing=False, learning_rate=1e-4)
                 cfg.max_grad_norm = 1.0
                 cfg.fsdp_sharding_strategy = "FULL_SHARD"
+                # The size-based wrap policy of the reference's FSDP backend calls a bool (backend_fsdp.py:183-185, "recurse(module)")
+                # and raises TypeError under this PyTorch; its own switch for running without a policy is a threshold <= 0
+                # (backend_fsdp.py:166-167), which wraps the model as one FSDP unit.
+                cfg.fsdp_auto_wrap_threshold = 0
                 model = DeepSeekTransformer(mcfg)
                 for m in model.modules():  # the entry script re-initialises every Linear / Embedding with N(0, 0.02)
                     if isinstance(m, (torch.nn.Linear, torch.nn.Embedding)):
@@ -106,6 +114,10 @@ def run(args, published) -> dict:
                     trainer = EnhancedConversationTrainer(model, _Tokenizer(shape["vocab_size"]), cfg, logging.getLogger("reference"))
                     backend = None
                 else:
+                    # bf16 MixedPrecision of the reference's FSDP backend breaks inside its own MoE layer (index_add_ of a float
+                    # source into a bf16 buffer raises); the configuration of its single-GPU path -- fp32 parameters, bf16 autocast
+                    # around the forward -- is what runs here as well (precision "fp32" selects no MixedPrecision policy).
+                    cfg.precision = "fp32"
                     backend = FSDPBackend(model, cfg)
                     trainer = None
             L, V = shape["seq_length"], shape["vocab_size"]
@@ -173,6 +185,8 @@ def run(args, published) -> dict:
             tokens_per_step = mb * L * accum * world
             break
         except torch.cuda.OutOfMemoryError:
+            if world > 1:  # ranks cannot halve independently without desynchronising their collectives
+                return {"impl": "reference", "unavailable": f"reference FSDP backend runs out of memory on config {args.config} at {world} GPUs"}
             if mb == 1:
                 return {"impl": "reference", "unavailable": f"reference runs out of memory on config {args.config} at {world} GPU(s) even with micro-batch 1"}
             trainer = backend = model = devb = host = None
@@ -180,6 +194,8 @@ def run(args, published) -> dict:
             gc.collect()
             torch.cuda.empty_cache()
             mb, accum = mb // 2, accum * 2
+        except Exception as e:  # a defect of the reference on this software stack: report, do not crash the benchmark
+            return {"impl": "reference", "unavailable": f"reference failed on its own code path: {type(e).__name__}: {e}"[:300]}
     t = torch.tensor([ms, e2e_ms], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -243,7 +243,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
-    if res:
+    if res and int(os.environ.get("RANK", "0")) == 0:  # one JSON line per job
         print(json.dumps(res), flush=True)
 
 

@@ -511,13 +511,13 @@ def test_fp8_linear_and_mlp_autograd():
 def test_graph_decoder_matches_eager_decode():
     """CUDA-graph replay of the decode step against the eager cached decode on a small MoE model."""
     from adaptivetrainingsystem_b200.config import ModelConfig
-    from adaptivetrainingsystem_b200.inference.engine import InferenceEngine, SamplingParams
+    from adaptivetrainingsystem_b200.inference.engine import GenerationEngine, SamplingParams
     from adaptivetrainingsystem_b200.models.transformer import DeepSeekTransformer
     torch.manual_seed(2)
     cfg = ModelConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=512, seq_length=256,
                       use_moe=True, num_experts=4, moe_top_k=2, capacity_factor=4.0, tie_word_embeddings=False)
     model = DeepSeekTransformer(cfg).cuda().to(torch.bfloat16).eval()
-    eng = InferenceEngine(model, max_batch=4)
+    eng = GenerationEngine(model, max_batch=4)
     prompt = torch.randint(0, 1024, (4, 32), device="cuda")
     greedy = SamplingParams.from_mode("greedy", max_new_tokens=24)
     a = eng.generate(prompt, greedy, use_graph=False)["tokens"]
