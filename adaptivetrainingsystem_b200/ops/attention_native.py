@@ -27,7 +27,11 @@ def _lib_fns():
                                      _ci, _ci, _ci, _ci, _ci, _vp, _vp]
         lib.ats_attn_fwd2.restype = _ci
         lib.ats_attn_fwd2.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp,
-                                      _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp]
+                                      _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp]
+        lib.ats_attn_fwd2_set_poly.restype = _ci
+        lib.ats_attn_fwd2_set_poly.argtypes = [_ci]
+        if "ATS_ATTN_POLY" in os.environ:
+            lib.ats_attn_fwd2_set_poly(int(os.environ["ATS_ATTN_POLY"]))
         lib.ats_attn_bwd.restype = _ci
         lib.ats_attn_bwd.argtypes = [_vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _cll, _cll, _ci, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                      _cll, _cll, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp]
@@ -45,6 +49,10 @@ def layout_ok(t: torch.Tensor) -> bool:
 # Forward variant: "v1" = one query tile per CTA; "v2s" / "v2t" = two query tiles per CTA with the probabilities staged
 # through shared memory / tensor memory (sequence length must be a multiple of 256, else v1 runs).
 FWD_VARIANT = os.environ.get("ATS_ATTN_FWD", "v2t")
+# Diagnostics: an int64 CUDA tensor of 16 elements receives per-phase cycle totals of one CTA of the two-tile forward kernel
+# ([0:5] MMA thread: total, wait for V, wait for P, issue, iterations; [8:13] one soft-max warp: wait for S, TMEM load, row
+# maximum, exponentials + store, signalling).
+FWD_PHASE_PROFILE = None
 
 
 def _fwd(q, k, v):
@@ -56,7 +64,7 @@ def _fwd(q, k, v):
     if FWD_VARIANT != "v1" and L % 256 == 0:
         err = _lib_fns().ats_attn_fwd2(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),
                                        Hkv * D, 0, _lib.ptr(out), _lib.ptr(lse), B, L, Hq, Hkv, D, int(FWD_VARIANT == "v2t"), _lib.ptr(st),
-                                       _lib.stream_ptr(q.device))
+                                       _lib.ptr(FWD_PHASE_PROFILE), _lib.stream_ptr(q.device))
         _lib.check(err, "ats_attn_fwd2")
         return out, lse
     err = _lib_fns().ats_attn_fwd(_lib.ptr(q), q.stride(1), Hq * D, 0, _lib.ptr(k), k.stride(1), Hkv * D, 0, _lib.ptr(v), v.stride(1),

@@ -80,10 +80,14 @@ def main():
     if a.phases:
         from adaptivetrainingsystem_b200.ops import attention_native as AN
         AN.PHASE_PROFILE = torch.zeros(32, dtype=torch.int64, device=dev)
+        AN.FWD_PHASE_PROFILE = torch.zeros(16, dtype=torch.int64, device=dev)
         fwd_bwd()
         torch.cuda.synchronize()
         pp = AN.PHASE_PROFILE.tolist()
-        AN.PHASE_PROFILE = None
+        fp = AN.FWD_PHASE_PROFILE.tolist()
+        AN.PHASE_PROFILE = AN.FWD_PHASE_PROFILE = None
+        out["phases_fwd"] = dict(zip(["total", "wait_v", "wait_p", "issue", "iterations"], fp[:5]))
+        out["phases_fwd"].update(dict(zip(["sm_wait_s", "sm_tmem_load", "sm_max", "sm_exp_store", "sm_signal"], fp[8:13])))
         names = ["total", "wait_tile", "wait_scores_read", "wait_p_ds", "issue", "iterations", "", "", "sm_wait_scores", "sm_tmem_load", "sm_math",
                  "sm_wait_products", "sm_store"]
         out["phases_dkv"] = {n: v for n, v in zip(names, pp[:13]) if n}

@@ -31,6 +31,7 @@ struct Attn2Args {
   float* lse;          // [B, Hq, L]
   float scale_log2;
   int* status;
+  long long* prof;  // optional [16]: cycle totals per phase of CTA (0,0,0) (diagnostics; null in normal use)
 };
 
 template <int D, bool PT>
@@ -46,7 +47,25 @@ struct Attn2Smem {
   static constexpr int TOTAL = BAR_OFF + 512 + 1024;
 };
 
-template <int D, bool PT>
+// exp2 on the FMA pipe: round-to-nearest range reduction with the 1.5 * 2^23 trick, degree-3 polynomial on [-0.5, 0.5]
+// (relative error 6e-4, below the bf16 rounding of P), exponent added with one integer shift-add.  The 16 MUFU lanes of an SM
+// are the bottleneck of the forward pass at D = 64, so part of the exponentials is computed this way.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p = __ffma2_rn(f, make_float2(0.0555041f, 0.0555041f), make_float2(0.2402265f, 0.2402265f));
+  p = __ffma2_rn(p, f, make_float2(0.6931472f, 0.6931472f));
+  p = __ffma2_rn(p, f, make_float2(1.f, 1.f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+}
+
+// POLY: 0 = every exponential on the MUFU; n > 0 = one pair of every n goes through exp2_poly2.
+template <int D, bool PT, bool PROF, int POLY>
 __global__ void __launch_bounds__(A2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const Attn2Args p) {
@@ -68,7 +87,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* s_empty = bars + 15;   // [2] per tile, 4 arrivals (PT = false only)
   uint64_t* p_full = bars + 17;    // [2] per tile, 4 arrivals
   uint64_t* o_done = bars + 19;    // [2] per tile: last P V finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* pv_done = bars + 21;   // [2] per tile: every P V (EARLY mode: P buffer free again, O stable)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
+  // SEP: P has tensor-memory columns of its own (D = 64 leaves room), so the scores of block j + 1 can be computed while the
+  // soft-max of block j is still running; the same holds when P is staged in shared memory.  Otherwise P overwrites S.
+  constexpr bool SEP = PT && D == 64;
+  constexpr bool EARLY = !PT || SEP;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,6 +115,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(&s_empty[x], 4);
       mbar_init(&p_full[x], 4);
       mbar_init(&o_done[x], 1);
+      mbar_init(&pv_done[x], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -106,7 +131,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: S_A [0,128)  S_B [128,256)  O_A [256, 256+D)  O_B [256+D, 256+2D)
+  // columns: S_A [0,128)  S_B [128,256)  O_A [256, 256+D)  O_B [256+D, 256+2D)  and, when SEP, P_A [384,448)  P_B [448,512)
 
   if (warp == 8) {
     if (lane == 0) {
@@ -158,7 +183,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint64_t p_d = desc_advance(p_k, uint32_t(x) * 32768);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          if (PT) tc_mma_f16_ts(o_tmem, tmem_base + x * 128 + k * 8, desc_advance(v_d, k * 2048), idesc_o, (j | k) != 0);
+          if (PT) tc_mma_f16_ts(o_tmem, (SEP ? tmem_base + 384 + x * 64 : tmem_base + x * 128) + k * 8, desc_advance(v_d, k * 2048), idesc_o, (j | k) != 0);
           else tc_mma_f16(o_tmem, desc_advance(p_d, (k >> 2) * 16384 + (k & 3) * 32), desc_advance(v_d, k * 2048), idesc_o, (j | k) != 0);
         }
       };
@@ -170,11 +195,52 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         issue_s(1, 0);
         tc_commit(&k_empty[0]);
       }
+      const bool rec = PROF && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+      long long w_load = 0, w_p = 0, t_issue = 0, c0 = 0, c1 = 0;
+      const long long t_begin = clock64();
+      if (EARLY) {
+        for (int j = 0; ok && j < nbB; ++j) {
+          const int nk = (j + 1) % KST, nk_ph = ((j + 1) / KST) & 1;
+          if (rec) c0 = clock64();
+          // scores of the next block first: they only need the S tiles to have been read into registers
+          if (j + 1 < nbB) {
+            if (!mbar_wait_bounded(&k_full[nk], nk_ph, abort_flag, p.status, kTimeoutFull)) break;
+            if (j + 1 < nbA) {
+              if (!mbar_wait_bounded(&s_empty[0], j & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+              tc_fence_after();
+              issue_s(0, j + 1);
+            }
+            if (!mbar_wait_bounded(&s_empty[1], j & 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+            tc_fence_after();
+            issue_s(1, j + 1);
+            tc_commit(&k_empty[nk]);
+          }
+          if (!mbar_wait_bounded(&v_full[j % VST], (j / VST) & 1, abort_flag, p.status, kTimeoutFull)) break;
+          if (rec) { c1 = clock64(); w_load += c1 - c0; }
+          if (j < nbA) {
+            if (!mbar_wait_bounded(&p_full[0], j & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+            if (rec) { c0 = clock64(); w_p += c0 - c1; c1 = c0; }
+            tc_fence_after();
+            issue_pv(0, j);
+            tc_commit(&pv_done[0]);
+          }
+          if (!mbar_wait_bounded(&p_full[1], j & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+          if (rec) { c0 = clock64(); w_p += c0 - c1; }
+          tc_fence_after();
+          issue_pv(1, j);
+          tc_commit(&pv_done[1]);
+          tc_commit(&v_empty[j % VST]);
+          if (rec) { c1 = clock64(); t_issue += c1 - c0; }
+        }
+      } else
       for (int j = 0; ok && j < nbB; ++j) {
         const int nk = (j + 1) % KST, nk_ph = ((j + 1) / KST) & 1;
+        if (rec) c0 = clock64();
         if (!mbar_wait_bounded(&v_full[j % VST], (j / VST) & 1, abort_flag, p.status, kTimeoutFull)) break;
+        if (rec) { c1 = clock64(); w_load += c1 - c0; }
         if (j < nbA) {
           if (!mbar_wait_bounded(&p_full[0], j & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+          if (rec) { c0 = clock64(); w_p += c0 - c1; }
           tc_fence_after();
           issue_pv(0, j);
           if (j == nbA - 1) tc_commit(&o_done[0]);
@@ -184,8 +250,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tc_fence_after();
             issue_s(0, j + 1);
           }
+          if (rec) { c1 = clock64(); t_issue += c1 - c0; }
         }
+        if (rec) c0 = clock64();
         if (!mbar_wait_bounded(&p_full[1], j & 1, abort_flag, p.status, kTimeoutTmemFull)) break;
+        if (rec) { c1 = clock64(); w_p += c1 - c0; }
         tc_fence_after();
         issue_pv(1, j);
         tc_commit(&v_empty[j % VST]);
@@ -197,6 +266,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           issue_s(1, j + 1);
           tc_commit(&k_empty[nk]);
         }
+        if (rec) { c0 = clock64(); t_issue += c0 - c1; }
+      }
+      if (rec) {
+        p.prof[0] = clock64() - t_begin; p.prof[1] = w_load; p.prof[2] = w_p; p.prof[3] = t_issue; p.prof[4] = nbB;
       }
     }
   } else if (warp < 8) {
@@ -211,17 +284,22 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int nb = qt + 1;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    const bool rec = PROF && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 4 && lane == 0;
+    long long w_s = 0, t_ld = 0, t_max = 0, t_exp = 0, t_sig = 0, c0 = 0, c1 = 0;
     for (int i = 0; i < nb; ++i) {
+      if (rec) c0 = clock64();
       if (!mbar_wait_bounded(&s_full[x], i & 1, abort_flag, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
+      if (rec) { c1 = clock64(); w_s += c1 - c0; }
       tc_fence_after();
       uint32_t v[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_S + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
       tmem_ld_wait();
-      if (!PT) {  // the S tile may be overwritten as soon as every row is in registers
+      if (rec) { c0 = clock64(); t_ld += c0 - c1; }
+      if (EARLY) {  // the S tile may be overwritten as soon as every row is in registers
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[x]);
@@ -240,10 +318,17 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mx3 = fmaxf(mx3, __uint_as_float(v[c + 3]));
       }
       const float mnew = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+      if (EARLY && i > 0) {  // the previous P V of this tile must be finished: O stable, P buffer free
+        if (!mbar_wait_bounded(&pv_done[x], (i - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
       if (i == 0) {
         m = mnew;
       } else if (__any_sync(0xffffffffu, mnew > m + 8.f)) {
-        // S(i) ready implies the previous P V of this tile has completed (it was issued before S(i)), so O is stable
+        // the previous P V of this tile has completed (implied by S(i) being ready when P aliases S, waited for above otherwise)
         const float alpha = exp2f(m - mnew);
         m = mnew;
         l *= alpha;
@@ -258,6 +343,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         tmem_st_wait();
       }
+      if (rec) { c1 = clock64(); t_max += c1 - c0; }
       // exp2(x * scale - m) with packed fp32x2 arithmetic (one FMA and one ADD per two elements); the row sum is taken
       // over the fp32 probabilities
       float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
@@ -268,13 +354,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           const float2 xs = __ffma2_rn(make_float2(__uint_as_float(v[c * 32 + 2 * e]), __uint_as_float(v[c * 32 + 2 * e + 1])), sc2, nm2);
-          const float2 pr = make_float2(exp2f(xs.x), exp2f(xs.y));
+          const float2 pr = (POLY > 0 && (e % (POLY > 0 ? POLY : 1)) == (POLY > 0 ? POLY : 1) - 1) ? exp2_poly2(xs) : make_float2(exp2f(xs.x), exp2f(xs.y));
           pk[e] = pack_bf16x2(pr.x, pr.y);
           if (e & 1) rsb = __fadd2_rn(rsb, pr);
           else rsa = __fadd2_rn(rsa, pr);
         }
         if (PT) {
-          tmem_st_32x16(tmem_S + c * 16, pk);
+          tmem_st_32x16((SEP ? tmem_base + 384 + x * 64 + lane_base : tmem_S) + c * 16, pk);
         } else {
           uint8_t* prow = sP + x * 32768 + (c >> 1) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
@@ -285,13 +371,19 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
       }
       l += (rsa.x + rsa.y) + (rsb.x + rsb.y);
+      if (rec) { c0 = clock64(); t_exp += c0 - c1; }
       if (PT) tmem_st_wait();
       tc_fence_before();
       if (!PT) fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
+      if (rec) { c1 = clock64(); t_sig += c1 - c0; }
     }
-    if (ok && mbar_wait_bounded(&o_done[x], 0, abort_flag, p.status, kTimeoutTmemFull)) {
+    if (rec) {
+      p.prof[8] = w_s; p.prof[9] = t_ld; p.prof[10] = t_max; p.prof[11] = t_exp; p.prof[12] = t_sig;
+    }
+    if (ok && (EARLY ? mbar_wait_bounded(&pv_done[x], (nb - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)
+                     : mbar_wait_bounded(&o_done[x], 0, abort_flag, p.status, kTimeoutTmemFull))) {
       tc_fence_after();
       const float inv = 1.f / l;
       const long long tok = (long long)row0 + x * 128 + r;
@@ -324,21 +416,41 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
 using namespace ats;
 
-template <int D, bool PT>
-static int launch_fwd2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Attn2Args& p, int B, int L, int Hq,
+static int g_fwd2_poly = 0;  // measured on B200: the polynomial path does not pay off (0.284 ms vs 0.291 / 0.302 ms at every 4th / 2nd pair)
+
+template <int D, bool PT, bool PROF, int POLY>
+static int launch_fwd2_impl(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Attn2Args& p, int B, int L, int Hq,
                        cudaStream_t s) {
   using SM = Attn2Smem<D, PT>;
-  cudaError_t ce = cudaFuncSetAttribute(attn_fwd2_kernel<D, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  cudaError_t ce = cudaFuncSetAttribute(attn_fwd2_kernel<D, PT, PROF, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
   if (ce != cudaSuccess) return int(ce);
   dim3 grid(L / 256, Hq, B);
-  attn_fwd2_kernel<D, PT><<<grid, A2_THREADS, SM::TOTAL, s>>>(mq, mk, mv, p);
+  attn_fwd2_kernel<D, PT, PROF, POLY><<<grid, A2_THREADS, SM::TOTAL, s>>>(mq, mk, mv, p);
   return int(cudaGetLastError());
 }
 
+template <int D, bool PT>
+static int launch_fwd2(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Attn2Args& p, int B, int L, int Hq,
+                       cudaStream_t s) {
+  // the instrumented build of the kernel runs only when a profile buffer is given
+  if (p.prof) return launch_fwd2_impl<D, PT, true, 0>(mq, mk, mv, p, B, L, Hq, s);
+  if (g_fwd2_poly == 2) return launch_fwd2_impl<D, PT, false, 2>(mq, mk, mv, p, B, L, Hq, s);
+  if (g_fwd2_poly == 4) return launch_fwd2_impl<D, PT, false, 4>(mq, mk, mv, p, B, L, Hq, s);
+  return launch_fwd2_impl<D, PT, false, 0>(mq, mk, mv, p, B, L, Hq, s);
+}
+
+// Share of the forward pass's exponentials computed on the FMA pipe: 0 = none, 2 = every second pair, 4 = every fourth.
+ATS_API int ats_attn_fwd2_set_poly(int every) {
+  if (every != 0 && every != 2 && every != 4) return 1003;
+  g_fwd2_poly = every;
+  return 0;
+}
+
 // Same contract as ats_attn_fwd, for L a multiple of 256.  p_in_tmem selects where the probabilities are staged.
+// prof: null, or 16 int64 that receive per-phase cycle totals of CTA (0,0,0) (diagnostics).
 ATS_API int ats_attn_fwd2(const void* q, long long ld_q, long long q_cols, int q_col0, const void* k, long long ld_k,
                           long long k_cols, int k_col0, const void* v, long long ld_v, long long v_cols, int v_col0,
-                          void* out, float* lse, int B, int L, int Hq, int Hkv, int D, int p_in_tmem, int* status, void* stream) {
+                          void* out, float* lse, int B, int L, int Hq, int Hkv, int D, int p_in_tmem, int* status, long long* prof, void* stream) {
   if ((D != 64 && D != 128) || (L % 256) || Hq % Hkv || (q_col0 & 7) || (k_col0 & 7) || (v_col0 & 7)) return 1003;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
@@ -357,6 +469,7 @@ ATS_API int ats_attn_fwd2(const void* q, long long ld_q, long long q_cols, int q
   p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
   p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
   p.status = status;
+  p.prof = prof;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return p_in_tmem ? launch_fwd2<128, true>(mq, mk, mv, p, B, L, Hq, s) : launch_fwd2<128, false>(mq, mk, mv, p, B, L, Hq, s);
   return p_in_tmem ? launch_fwd2<64, true>(mq, mk, mv, p, B, L, Hq, s) : launch_fwd2<64, false>(mq, mk, mv, p, B, L, Hq, s);
