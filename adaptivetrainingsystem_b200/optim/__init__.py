@@ -162,10 +162,10 @@ class LAMBRule(UpdateRule):
                 o += c
         return starts, lens, segs
 
-    def update(self, state, master, grad, param_out, hyper, clip_state, decay, segments=None, group=None):
+    def update(self, state, master, grad, param_out, hyper, clip_state, decay, segments=None, group=None, n_segments=None):
         import torch.distributed as dist
         segments = [tuple(x) if len(x) == 3 else (x[0], x[1], i) for i, x in enumerate(segments)] if segments else [(0, master.numel(), 0)]
-        n_seg = max(x[2] for x in segments) + 1
+        n_seg = int(n_segments) if n_segments else max(x[2] for x in segments) + 1  # the table must have the same size on every rank
         multi = group is not None and dist.is_initialized() and dist.get_world_size(group) > 1
         if master.is_cuda and grad.dtype == torch.bfloat16:
             lib = _fns()
