@@ -28,7 +28,7 @@ HOST_LIB = os.path.join(OUT_DIR, "libats_host.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared"]
-# Files listed in .gpurunignore.multi (kernels that may only run in single-GPU jobs) are built into a
+# Kernels that may only run in single-GPU jobs (none at present) would be listed here and built into a
 # separate library so the main one never names a multicast load.
 SINGLE_GPU_ONLY: List[str] = []
 

@@ -20,6 +20,7 @@ def main():
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--mode", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--phases", action="store_true", help="cycle totals of one CTA's MMA thread")
     a = ap.parse_args()
     dev = torch.device("cuda")
     torch.manual_seed(0)
@@ -51,9 +52,21 @@ def main():
             tot += e0.elapsed_time(e1)
         return tot / a.iters
     t_o, t_l = timed(ours), timed(lib)
+    phases = None
+    if a.phases:
+        import ctypes
+        from adaptivetrainingsystem_b200.ops import _lib
+        buf = torch.zeros(8, dtype=torch.int64, device=dev)
+        lib_c = _lib.cuda_lib()
+        lib_c.ats_gemm_set_profile.argtypes = [ctypes.c_void_p]
+        lib_c.ats_gemm_set_profile(ctypes.c_void_p(buf.data_ptr()))
+        ours()
+        torch.cuda.synchronize()
+        lib_c.ats_gemm_set_profile(None)
+        phases = dict(zip(["total", "wait_stage", "wait_accumulator", "issue", "k_blocks"], buf.tolist()[:5]))
     fl = 2.0 * a.m * a.n * a.k
     print(json.dumps({"gemm": [a.m, a.n, a.k], "mode": a.mode, "ms": t_o, "tflops": fl / t_o / 1e9, "library_ms": t_l,
-                      "library_tflops": fl / t_l / 1e9, "l2": "flushed between iterations"}))
+                      "library_tflops": fl / t_l / 1e9, "l2": "flushed between iterations", "mma_thread_cycles": phases}))
 
 
 if __name__ == "__main__":

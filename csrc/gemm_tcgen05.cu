@@ -73,6 +73,7 @@ struct GemmArgs {
   int* b_ready;
   int ready_rows, n_chunks, epoch, first_chunk, n_rot;
   int own_row0, own_rows;    // rows of B that live in this rank's shard (read through map_b_own)
+  long long* prof;           // optional [8]: cycle totals of CTA 0's MMA thread (total, wait for stage, wait for accumulator, issue, k-blocks)
   int fp8;
   const float* row_scale;  // [groups * rs_gs] or null
   const float* col_scale;  // [weights * cs_gs] or null
@@ -327,16 +328,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint64_t a_desc0 = p.a_mn ? make_smem_desc_sw128(smem_u32(sA), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sA), 16, 1024);
       const uint64_t b_desc0 = p.b_mn ? make_smem_desc_sw128(smem_u32(sB), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sB), 16, 1024);
       const uint64_t a_step16 = (p.a_mn ? UK * 128 : UK * 2) >> 4, b_step16 = (p.b_mn ? UK * 128 : UK * 2) >> 4;
+      const bool rec = p.prof != nullptr && blockIdx.x == 0;
+      long long w_full = 0, w_acc = 0, t_issue = 0, n_kb = 0, c0 = 0, c1 = 0;
+      const long long t_begin = clock64();
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint);
+        if (rec) c0 = clock64();
         if (!mbar_wait_bounded(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+        if (rec) { c1 = clock64(); w_acc += c1 - c0; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < t.k_iters; ++kb) {
+          if (rec) c0 = clock64();
           if (!mbar_wait_bounded(&full[stage], phase, abort_flag, p.status, kTimeoutFull)) {
             ok = false;
             break;
           }
+          if (rec) { c1 = clock64(); w_full += c1 - c0; ++n_kb; }
           tc_fence_after();
           // descriptors: one base per operand (built before the tile loop), advanced by constants
           const uint64_t adesc = desc_advance(a_desc0, uint32_t(stage) * A_STAGE_BYTES);
@@ -349,6 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int k = 0; k < BK / UK; ++k) tc_mma_f16(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
           }
           tc_commit(&empty[stage]);  // the stage is free once these MMAs have read it
+          if (rec) t_issue += clock64() - c1;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -361,6 +370,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           acc = 0;
           acc_phase ^= 1;
         }
+      }
+      if (rec) {
+        p.prof[0] = clock64() - t_begin; p.prof[1] = w_full; p.prof[2] = w_acc; p.prof[3] = t_issue; p.prof[4] = n_kb;
       }
     }
   } else {
@@ -542,6 +554,11 @@ using namespace ats;
 
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
                        int max_ctas, void* stream, const CUtensorMap* mb_own = nullptr);
+static long long* g_gemm_prof = nullptr;
+
+// Diagnostics: device buffer of 8 int64 that the next bf16 GEMM launches fill with cycle totals of CTA 0's MMA thread
+// (total, wait for a loaded stage, wait for a free accumulator, issue, k-blocks); null switches it off.
+ATS_API void ats_gemm_set_profile(long long* buf) { g_gemm_prof = buf; }
 
 // Generic entry point. The global 2-D extents of both operands are given explicitly (rows x cols, cols contiguous,
 // pitch ld elements); for a K-major operand cols is the reduction dimension, for an MN-major operand rows is.
@@ -581,7 +598,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
   p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
-  p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0;
+  p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = g_gemm_prof;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
 
@@ -617,7 +634,7 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
   p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
-  p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0;
+  p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
 
@@ -659,7 +676,7 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   p.b_ready = b_ready; p.ready_rows = ready_rows; p.n_chunks = int(b_rows / ready_rows);
   p.epoch = int(calls * (p.chunk_bytes / 4096));  // every call adds chunk_bytes / 4096 to each remote chunk's counter
   p.first_chunk = int(my_rank * (shard_rows / ready_rows));
-  p.own_row0 = int(my_rank * shard_rows); p.own_rows = int(shard_rows);
+  p.own_row0 = int(my_rank * shard_rows); p.own_rows = int(shard_rows); p.prof = nullptr;
   const int tile_w = epilogue == kSwiGLU ? 128 : BN;
   p.n_rot = int((my_rank * shard_rows) % (epilogue == kSwiGLU ? (long long)up_offset : b_rows) / tile_w);
   return launch_gemm(ma, mb, p, epilogue, 1, M, N, 0, stream, &mb_own);
