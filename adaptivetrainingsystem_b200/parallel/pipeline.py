@@ -159,3 +159,114 @@ class OneFOneBSchedule:
         if m.is_last:
             return torch.stack(losses).sum()
         return None
+
+
+class InterleavedStages(nn.Module):
+    """``chunks`` model chunks per rank: virtual stage ``k = c * stages + rank`` owns a contiguous slice of the decoder
+    (virtual pipeline of ``stages * chunks`` stages, the placement of the reference's vendored interleaved schedule,
+    ``colossalai/pipeline/schedule/interleaved_pp.py``)."""
+
+    def __init__(self, model, rank: int, num_stages: int, chunks: int):
+        super().__init__()
+        self.model, self.rank, self.num_stages, self.chunks = model, rank, num_stages, chunks
+        total = num_stages * chunks
+        parts = partition_layers(len(model.layers), total)
+        self.ranges = [parts[c * num_stages + rank] for c in range(chunks)]
+        self.virtual = [c * num_stages + rank for c in range(chunks)]
+        self.total = total
+        keep = {i for (a, b) in self.ranges for i in range(a, b)}
+        for i, blk in enumerate(model.layers):
+            if i not in keep:
+                for p in blk.parameters():
+                    p.requires_grad_(False)
+        if 0 not in self.virtual:
+            model.embed_tokens.weight.requires_grad_(False)
+        if total - 1 not in self.virtual:
+            model.norm.weight.requires_grad_(False)
+            if model.lm_head_weight is not None:
+                model.lm_head_weight.requires_grad_(False)
+
+    def forward_chunk(self, c: int, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        m = self.model
+        k = self.virtual[c]
+        if k == 0:
+            import math
+            from .. import ops
+            x = ops.embedding(x, m.embed_tokens.weight, math.sqrt(m.config.hidden_size) if m.config.use_stable_embedding else 1.0)
+        aux = x.new_zeros((), dtype=torch.float32)
+        a, b = self.ranges[c]
+        for blk in m.layers[a:b]:
+            x, al = blk(x, m.rope)
+            aux = aux + al.float().clamp(max=1.0)
+        if k == self.total - 1:
+            x = m.norm(x)
+        return x, aux
+
+    def loss(self, hidden: torch.Tensor, labels: torch.Tensor, weights=None):
+        from .. import ops
+        return ops.linear_cross_entropy(hidden, self.model.lm_head, labels, weights)[0]
+
+
+class InterleavedSchedule:
+    """Runs the virtual pipeline of :class:`InterleavedStages` breadth-first: all micro-batches through chunk 0 of every rank,
+    then chunk 1 (whose first stage receives from the last rank), ...; backward in the reverse order.  Sends are posted
+    asynchronously and completed at the end of each phase, so a rank never blocks on a neighbour that has not reached the
+    matching receive yet.  Activations of all micro-batches are kept until their backward (GPipe memory profile)."""
+
+    def __init__(self, stages: InterleavedStages, group, num_microbatches: int, act_shape: Tuple[int, int, int], dtype, device):
+        self.m, self.group, self.n = stages, group, num_microbatches
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.ranks = dist.get_process_group_ranks(group)
+        self.shape, self.dtype, self.device = act_shape, dtype, device
+
+    def run(self, microbatches: List[Dict[str, torch.Tensor]]) -> Optional[torch.Tensor]:
+        m, n, S, r = self.m, self.n, self.world, self.rank
+        nxt, prv = self.ranks[(r + 1) % S], self.ranks[(r - 1) % S]
+        saved: Dict[Tuple[int, int], Tuple[Optional[torch.Tensor], torch.Tensor, torch.Tensor]] = {}
+        losses: List[torch.Tensor] = []
+        pending = []
+        for c in range(m.chunks):
+            k = m.virtual[c]
+            for i, mb in enumerate(microbatches):
+                if k == 0:
+                    x_in = None
+                    out, aux = m.forward_chunk(c, mb["input_ids"])
+                else:
+                    x_in = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+                    dist.recv(x_in, prv, group=self.group)
+                    x_in.requires_grad_()
+                    out, aux = m.forward_chunk(c, x_in)
+                if k == m.total - 1:
+                    loss = (m.loss(out, mb["labels"], mb.get("loss_weights")) + aux) / n
+                    losses.append(loss.detach())
+                    out = loss
+                else:
+                    pending.append(dist.isend(out.detach().contiguous(), nxt, group=self.group))
+                saved[(c, i)] = (x_in, out, aux)
+        for h in pending:
+            h.wait()
+        pending = []
+        keep_alive = []
+        for c in reversed(range(m.chunks)):
+            k = m.virtual[c]
+            for i in range(n):
+                x_in, out, aux = saved.pop((c, i))
+                if k == m.total - 1:
+                    out.backward()
+                else:
+                    g = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+                    dist.recv(g, nxt, group=self.group)
+                    if aux.requires_grad:
+                        torch.autograd.backward([out, aux / n], [g, torch.ones_like(aux)])
+                    else:
+                        out.backward(g)
+                if k != 0:
+                    gin = x_in.grad.contiguous()
+                    keep_alive.append(gin)
+                    pending.append(dist.isend(gin, prv, group=self.group))
+        for h in pending:
+            h.wait()
+        if m.total - 1 in m.virtual:
+            return torch.stack(losses).sum()
+        return None

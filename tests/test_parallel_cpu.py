@@ -38,6 +38,30 @@ def _pp_worker(rank, world, path):
             assert torch.allclose(p.grad, ref["grads"][n], atol=1e-5), n
 
 
+def _pp_interleaved_worker(rank, world, path):
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200.parallel.pipeline import InterleavedSchedule, InterleavedStages
+    ref = torch.load(path)
+    torch.manual_seed(0)
+    model = DeepSeekTransformer(ModelConfig(**CFG))
+    model.load_state_dict(ref["init"])
+    stages = InterleavedStages(model, rank, world, chunks=2)  # 4 layers -> 4 virtual stages, two per rank
+    assert stages.virtual == [rank, world + rank]
+    sched = InterleavedSchedule(stages, dist.group.WORLD, 4, (2, 16, 64), torch.float32, torch.device("cpu"))
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 256, (8, 17), generator=g)
+    mbs = [{"input_ids": ids[2 * i:2 * i + 2, :-1], "labels": ids[2 * i:2 * i + 2, 1:]} for i in range(4)]
+    loss = sched.run(mbs)
+    if rank == world - 1:
+        assert abs(loss.item() - ref["loss"]) < 1e-4, (loss.item(), ref["loss"])
+    checked = 0
+    for n, p in model.named_parameters():
+        if p.requires_grad and p.grad is not None:
+            assert torch.allclose(p.grad, ref["grads"][n], atol=1e-5), n
+            checked += 1
+    assert checked > 0
+
+
 def test_pipeline_1f1b_matches_single_process(tmp_path):
     torch.manual_seed(0)
     model = DeepSeekTransformer(ModelConfig(**CFG))
@@ -52,6 +76,7 @@ def test_pipeline_1f1b_matches_single_process(tmp_path):
     path = str(tmp_path / "ref.pt")
     torch.save({"init": init, "loss": total, "grads": {n: p.grad.clone() for n, p in model.named_parameters()}}, path)
     run_dist(_pp_worker, 2, (path,))
+    run_dist(_pp_interleaved_worker, 2, (path,))
 
 
 def _tp_worker(rank, world):
@@ -102,3 +127,64 @@ def _tp_worker(rank, world):
 
 def test_tensor_sequence_vocab_parallel():
     run_dist(_tp_worker, 2)
+
+
+def _ring_worker(rank, world):
+    import torch
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200 import ops
+    from adaptivetrainingsystem_b200.parallel.ring import linear_ring_reducescatter, ring_allgather_linear, ring_attention
+    torch.manual_seed(0)
+    L, K, N = 8 * world, 12, 10
+    x_full = torch.randn(L, K, dtype=torch.float64)
+    w_full = torch.randn(N * world, K, dtype=torch.float64)
+    Lc = L // world
+    # column-parallel linear behind a ring all-gather of the sequence shards
+    x = x_full[rank * Lc:(rank + 1) * Lc].clone().requires_grad_()
+    w = w_full[rank * N:(rank + 1) * N].clone().requires_grad_()
+    y = ring_allgather_linear(x, w)
+    xr = x_full.clone().requires_grad_()
+    wr = w_full.clone().requires_grad_()
+    yr = xr @ wr.t()
+    assert torch.allclose(y, yr[:, rank * N:(rank + 1) * N].detach())
+    gy = torch.randn(L, N * world, dtype=torch.float64)
+    y.backward(gy[:, rank * N:(rank + 1) * N])
+    yr.backward(gy)
+    assert torch.allclose(w.grad, wr.grad[rank * N:(rank + 1) * N])
+    assert torch.allclose(x.grad, xr.grad[rank * Lc:(rank + 1) * Lc])
+    # row-parallel linear followed by a ring reduce-scatter back to sequence shards
+    Kl = K // world if K % world == 0 else K
+    x2_full = torch.randn(L, Kl * world, dtype=torch.float64)
+    w2_full = torch.randn(N, Kl * world, dtype=torch.float64)
+    x2 = x2_full[:, rank * Kl:(rank + 1) * Kl].clone().requires_grad_()
+    w2 = w2_full[:, rank * Kl:(rank + 1) * Kl].clone().requires_grad_()
+    y2 = linear_ring_reducescatter(x2, w2)
+    ref2 = (x2_full @ w2_full.t())
+    assert torch.allclose(y2, ref2[rank * Lc:(rank + 1) * Lc])
+    g2 = torch.randn(L, N, dtype=torch.float64)
+    y2.backward(g2[rank * Lc:(rank + 1) * Lc])
+    assert torch.allclose(x2.grad, (g2 @ w2_full)[:, rank * Kl:(rank + 1) * Kl])
+    assert torch.allclose(w2.grad, (g2.t() @ x2_full)[:, rank * Kl:(rank + 1) * Kl])
+    # ring attention against full causal attention
+    B, Hq, Hkv, D = 2, 4, 2, 8
+    q_full = torch.randn(B, L, Hq, D)
+    k_full = torch.randn(B, L, Hkv, D)
+    v_full = torch.randn(B, L, Hkv, D)
+    sl = slice(rank * Lc, (rank + 1) * Lc)
+    q, k, v = (t[:, sl].clone().requires_grad_() for t in (q_full, k_full, v_full))
+    o = ring_attention(q, k, v)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q_full, k_full, v_full))
+    o_ref = ops.attention_reference(qr, kr, vr)
+    assert torch.allclose(o, o_ref[:, sl].detach(), atol=1e-5)
+    go = torch.randn(B, L, Hq, D)
+    o.backward(go[:, sl])
+    o_ref.backward(go)
+    assert torch.allclose(q.grad, qr.grad[:, sl], atol=1e-4)
+    assert torch.allclose(k.grad, kr.grad[:, sl], atol=1e-4)
+    assert torch.allclose(v.grad, vr.grad[:, sl], atol=1e-4)
+
+
+def test_ring_sequence_parallel_and_ring_attention():
+    from dist_utils import run_dist
+    run_dist(_ring_worker, world=2)
+    run_dist(_ring_worker, world=3)
