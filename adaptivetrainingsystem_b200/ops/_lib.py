@@ -64,7 +64,8 @@ def build(force: bool = False, verbose: bool = False) -> None:
         nvcc = _nvcc()
         if nvcc is None:
             raise RuntimeError("nvcc not found; cannot build the sm_100a kernels")
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", CUDA_LIB + ".tmp"] + srcs
+        extra = os.environ.get("ATS_NVCC_EXTRA", "").split()  # e.g. -DATS_AB_SPLIT=4 for kernel tuning experiments
+        cmd = [nvcc] + NVCC_FLAGS + extra + ["-I", CSRC, "-o", CUDA_LIB + ".tmp"] + srcs
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -19,7 +19,10 @@
 
 namespace ats {
 
-constexpr int AB_SPLIT = 2;                       // threads per query row in the softmax-gradient stage
+#ifndef ATS_AB_SPLIT
+#define ATS_AB_SPLIT 2
+#endif
+constexpr int AB_SPLIT = ATS_AB_SPLIT;             // threads per query row in the softmax-gradient stage (2 or 4)
 constexpr int AB_COLS = 128 / AB_SPLIT;           // key columns per thread
 constexpr int AB_THREADS = 64 + 128 * AB_SPLIT;   // TMA warp, MMA warp, 4 * AB_SPLIT softmax-gradient warps
 
@@ -376,9 +379,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (rec) { c0 = clock64(); w_pdsfree += c0 - c1; }
       if (MODE == 1) {
         // dQ pass: dS never touches shared memory
-#pragma unroll
-        for (int c = 0; c < AB_COLS / 64; ++c)
-          tmem_st_32x32(tmem_dS + lane_base + part * (AB_COLS / 2) + c * 32, reinterpret_cast<uint32_t(&)[32]>(dk[c * 32]));
+        if (AB_COLS == 64) tmem_st_32x32(tmem_dS + lane_base + part * 32, reinterpret_cast<uint32_t(&)[32]>(dk[0]));
+        else tmem_st_32x16(tmem_dS + lane_base + part * 16, reinterpret_cast<uint32_t(&)[16]>(dk[0]));
         tmem_st_wait();
         tc_fence_before();
       } else {
