@@ -55,25 +55,30 @@ struct AttnBwdSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
-                                  float* __restrict__ delta, int B, int L, int Hq, int D) {
-  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d].  Eight elements (16 bytes) per thread, D / 8 threads per row, so a
+// warp covers 32 / (D / 8) rows with fully coalesced 512-byte accesses.
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                                         float* __restrict__ delta, int B, int L, int Hq, int D) {
+  const int tpr = D >> 3;  // threads per row: 8 (D = 64) or 16 (D = 128)
+  const long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long row = g / tpr;  // (token, head) row
+  const int part = int(g % tpr);
   const long long total = (long long)B * L * Hq;
-  if (w >= total) return;
-  const int h = int(w % Hq);
-  const long long tok = w / Hq;
-  const int b = int(tok / L), i = int(tok % L);
-  const __nv_bfloat16* a = dout + w * D;
-  const __nv_bfloat16* o = out + w * D;
   float acc = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + d));
-    float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + d));
-    acc += x.x * y.x + x.y * y.y;
+  if (row < total) {
+    const uint4 a = reinterpret_cast<const uint4*>(dout + row * D)[part];
+    const uint4 o = reinterpret_cast<const uint4*>(out + row * D)[part];
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y), o2 = unpack_bf16x2(o.z), o3 = unpack_bf16x2(o.w);
+    acc = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y + a2.x * o2.x + a2.y * o2.y + a3.x * o3.x + a3.y * o3.y;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[((long long)b * Hq + h) * L + i] = acc;
+  for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < total && part == 0) {
+    const int h = int(row % Hq);
+    const long long tok = row / Hq;
+    const int b = int(tok / L), i = int(tok % L);
+    delta[((long long)b * Hq + h) * L + i] = acc;
+  }
 }
 
 template <int D, int MODE>
@@ -476,8 +481,8 @@ ATS_API int ats_attn_bwd(const void* q, long long ld_q, long long q_cols, int q_
   if ((e = make_tmap_2d(&mk, k, rows, k_cols, ld_k, 2, 64, 128))) return e;
   if ((e = make_tmap_2d(&mv, v, rows, v_cols, ld_v, 2, 64, 128))) return e;
   if ((e = make_tmap_2d(&mdo, dout, rows, (unsigned long long)Hq * D, (unsigned long long)Hq * D, 2, 64, 128))) return e;
-  const long long warps = (long long)B * L * Hq;
-  attn_delta_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout),
+  const long long delta_threads = (long long)B * L * Hq * (D / 8);
+  attn_delta_kernel<<<unsigned((delta_threads + 255) / 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout),
                                                                       static_cast<const __nv_bfloat16*>(out), delta, B, L, Hq, D);
   AttnBwdArgs p;
   p.B = B; p.L = L; p.Hq = Hq; p.Hkv = Hkv; p.D = D;

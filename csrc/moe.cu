@@ -47,6 +47,51 @@ gate_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+// Same product with the router weight staged once per CTA in shared memory and two tokens per warp step, so that a weight
+// vector read from shared memory is used for two tokens (used when E * hidden * 2 bytes fit in 64 KB).
+template <int EMAX>
+__global__ void __launch_bounds__(256)
+gate_fwd_smem_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, float* __restrict__ logits,
+                     long long tokens, int hidden, int experts) {
+  extern __shared__ uint4 s_w[];  // [experts][hidden / 8]
+  const int nvec = hidden >> 3;
+  for (int i = threadIdx.x; i < experts * nvec; i += blockDim.x) s_w[i] = reinterpret_cast<const uint4*>(wg)[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (long long t0 = ((long long)blockIdx.x * wpb + warp) * 2; t0 < tokens; t0 += (long long)gridDim.x * wpb * 2) {
+    const bool two = t0 + 1 < tokens;
+    float acc0[EMAX], acc1[EMAX];
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) acc0[e] = acc1[e] = 0.f;
+    const uint4* xr0 = reinterpret_cast<const uint4*>(x + t0 * hidden);
+    const uint4* xr1 = reinterpret_cast<const uint4*>(x + (t0 + (two ? 1 : 0)) * hidden);
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 a = xr0[v], b = xr1[v];
+      const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+      const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e) {
+        if (e < experts) {
+          const uint4 w = s_w[e * nvec + v];
+          const float2 w0 = unpack_bf16x2(w.x), w1 = unpack_bf16x2(w.y), w2 = unpack_bf16x2(w.z), w3 = unpack_bf16x2(w.w);
+          acc0[e] += a0.x * w0.x + a0.y * w0.y + a1.x * w1.x + a1.y * w1.y + a2.x * w2.x + a2.y * w2.y + a3.x * w3.x + a3.y * w3.y;
+          acc1[e] += b0.x * w0.x + b0.y * w0.y + b1.x * w1.x + b1.y * w1.y + b2.x * w2.x + b2.y * w2.y + b3.x * w3.x + b3.y * w3.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      if (e < experts) {
+        const float s0 = warp_sum(acc0[e]), s1 = warp_sum(acc1[e]);
+        if (lane == 0) {
+          logits[t0 * experts + e] = s0;
+          if (two) logits[(t0 + 1) * experts + e] = s1;
+        }
+      }
+    }
+  }
+}
+
 // dx[t, h] (+)= sum_e dlogits[t, e] * wg[e, h]
 __global__ void __launch_bounds__(256)
 gate_bwd_dx_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ wg, __nv_bfloat16* __restrict__ dx,
@@ -369,6 +414,25 @@ ATS_API int ats_gate_fwd(const void* x, const void* wg, float* logits, long long
   const unsigned blocks = unsigned((tokens * 32 + 255) / 256);
   auto X = static_cast<const __nv_bfloat16*>(x);
   auto W = static_cast<const __nv_bfloat16*>(wg);
+  const size_t w_bytes = size_t(experts) * hidden * 2;
+  if (experts <= 16 && w_bytes <= 65536) {
+    static bool attr8 = false, attr16 = false;
+    const unsigned grid = 148 * 3;
+    if (experts <= 8) {
+      if (!attr8) {
+        cudaFuncSetAttribute(gate_fwd_smem_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+        attr8 = true;
+      }
+      gate_fwd_smem_kernel<8><<<grid, 256, w_bytes, s>>>(X, W, logits, tokens, hidden, experts);
+    } else {
+      if (!attr16) {
+        cudaFuncSetAttribute(gate_fwd_smem_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+        attr16 = true;
+      }
+      gate_fwd_smem_kernel<16><<<grid, 256, w_bytes, s>>>(X, W, logits, tokens, hidden, experts);
+    }
+    return int(cudaGetLastError());
+  }
   if (experts <= 8) gate_fwd_kernel<8><<<blocks, 256, 0, s>>>(X, W, logits, tokens, hidden, experts);
   else if (experts <= 16) gate_fwd_kernel<16><<<blocks, 256, 0, s>>>(X, W, logits, tokens, hidden, experts);
   else gate_fwd_kernel<64><<<blocks, 256, 0, s>>>(X, W, logits, tokens, hidden, experts);
