@@ -41,6 +41,11 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rms_norm(x, self.weight, self.eps)
 
+    def with_skip(self, x: torch.Tensor):
+        """-> (norm(x), x) as one autograd node: the gradients of the normalised branch and of the residual branch are
+        summed inside the norm's backward kernel."""
+        return ops.rms_norm_skip(x, self.weight, self.eps)
+
 
 class LayerNorm(nn.Module):
     """Bias-optional LayerNorm kept for API parity (reference ``core/model.py:307-327``)."""
@@ -142,8 +147,13 @@ class GroupedQueryAttention(nn.Module):
             return ops.linear(a, self.o_proj, residual=residual)
         rope.ensure(offset + L if positions is None else int(self.cfg.seq_length), h.device)
         qkv = ops.linear(h, self.qkv_proj)
-        qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=offset, positions=positions)
         nq, nk = self.n_q * self.d, self.n_kv * self.d
+        if (cache is None and attention_mask is None and positions is None and self.d % 16 == 0
+                and ops.attention_packed_available(qkv, self.d, L)):
+            # training / scoring path: rotation and attention are one autograd node on the projection buffer
+            a = ops.rope_attention_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=0)
+            return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
+        qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=offset, positions=positions)
         if cache is None and attention_mask is None and ops.attention_packed_available(qkv, self.d, L):
             a = ops.attention_packed(qkv, self.n_q, self.n_kv, self.d)
             return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
@@ -365,8 +375,9 @@ class TransformerBlock(nn.Module):
             self.ffn_kind = "dense"
 
     def _body(self, x, rope, attention_mask, cache, positions, decode):
-        x = self.self_attn(self.input_norm(x), x, rope, attention_mask, cache, positions)
-        h = self.post_attn_norm(x)
+        h, x = self.input_norm.with_skip(x)
+        x = self.self_attn(h, x, rope, attention_mask, cache, positions)
+        h, x = self.post_attn_norm.with_skip(x)
         if self.ffn_kind == "mod":
             x, aux = self.ffn(h, x, decode=decode)
         else:

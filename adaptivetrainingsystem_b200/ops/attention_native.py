@@ -136,6 +136,47 @@ class _FlashAttnPackedFn(torch.autograd.Function):
         return dqkv, None, None, None
 
 
+class _RopeAttnPackedFn(torch.autograd.Function):
+    """RoPE (in place on the packed projection) followed by causal attention, as one autograd node: the backward pass rotates
+    the gradient of q / k back inside the buffer the attention backward has just written, without a defensive copy."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_q, n_kv, d, pos_offset):
+        from .functional import _L, _P, _S, _CK
+        B, L, W = qkv.shape
+        ctx.mark_dirty(qkv)
+        _CK(_L().ats_rope(_P(qkv), _P(cos), _P(sin), None, B * L, L, pos_offset, W, 0, n_q + n_kv, d, 0, _S(qkv.device)), "rope")
+        nq, nk = n_q * d, n_kv * d
+        out, lse = _fwd(qkv[..., :nq].view(B, L, n_q, d), qkv[..., nq:nq + nk].view(B, L, n_kv, d), qkv[..., nq + nk:].view(B, L, n_kv, d))
+        ctx.save_for_backward(qkv, out, lse, cos, sin)
+        ctx.dims = (n_q, n_kv, d, pos_offset)
+        return qkv, out
+
+    @staticmethod
+    def backward(ctx, _dqkv_unused, dout):
+        from .functional import _L, _P, _S, _CK
+        qkv, out, lse, cos, sin = ctx.saved_tensors
+        n_q, n_kv, d, pos_offset = ctx.dims
+        B, L, W = qkv.shape
+        nq, nk = n_q * d, n_kv * d
+        dqkv = torch.empty_like(qkv)
+        _bwd(qkv[..., :nq].view(B, L, n_q, d), qkv[..., nq:nq + nk].view(B, L, n_kv, d), qkv[..., nq + nk:].view(B, L, n_kv, d), out,
+             dout.contiguous(), lse, dqkv[..., :nq].view(B, L, n_q, d), dqkv[..., nq:nq + nk].view(B, L, n_kv, d),
+             dqkv[..., nq + nk:].view(B, L, n_kv, d))
+        if _dqkv_unused is not None:  # the rotated projection itself was used downstream as well
+            dqkv += _dqkv_unused
+        _CK(_L().ats_rope(_P(dqkv), _P(cos), _P(sin), None, B * L, L, pos_offset, W, 0, n_q + n_kv, d, 1, _S(dqkv.device)), "rope_bwd")
+        return dqkv, None, None, None, None, None, None
+
+
+def rope_flash_attention_packed(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_q: int, n_kv: int, d: int,
+                                pos_offset: int = 0) -> torch.Tensor:
+    """qkv [B, L, (n_q + 2 n_kv) d] straight from the projection GEMM -> attention output [B, L, n_q, d]; qkv is rotated in place."""
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32:
+        raise TypeError("rope tables must be float32")
+    return _RopeAttnPackedFn.apply(qkv, cos, sin, n_q, n_kv, d, pos_offset)[1]
+
+
 def flash_attention_native(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     return _FlashAttnFn.apply(q, k, v)
 

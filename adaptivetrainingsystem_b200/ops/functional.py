@@ -52,6 +52,7 @@ def _L():
         sig("ats_gate_bwd_dw", _vp, _vp, _vp, _c_int, _c_ll, _c_int, _c_int, _vp)
         sig("ats_topk_softmax", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _vp)
         sig("ats_plan_slots", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
+        sig("ats_plan_slots_chunked", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_dispatch_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
         sig("ats_combine_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_slot_dot", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
@@ -122,6 +123,52 @@ class _RMSNormFn(torch.autograd.Function):
                                  rows, cols, _S(xin.device)), "rmsnorm_bwd")
         dxv = dx.view(ctx.shape)
         return dxv, dw, None, (dxv if ctx.has_res else None)
+
+
+class _RMSNormSkipFn(torch.autograd.Function):
+    """(rms_norm(x), x): the pre-norm pattern, where x also feeds the residual connection.  As one autograd node it receives
+    both gradients, and the backward kernel adds the residual branch's gradient while it writes dx (no separate add pass)."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows, cols = x2.shape
+        y = torch.empty(shape, dtype=x.dtype, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _CK(_L().ats_rmsnorm_fwd(_P(x2), None, _P(w), _P(y), None, _P(rstd), rows, cols, eps, _S(x.device)), "rmsnorm_fwd")
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.shape = shape
+        return y, x
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        xin, w, rstd = ctx.saved_tensors
+        rows, cols = xin.shape
+        dy2 = dy.reshape(rows, cols)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        ds = None
+        if dskip is not None:
+            ds = dskip.reshape(rows, cols)
+            if not ds.is_contiguous():
+                ds = ds.contiguous()
+        dx = torch.empty_like(xin)
+        nb = min(_NORM_BLOCKS, rows)
+        partial = torch.empty(nb, cols, dtype=torch.float32, device=xin.device)
+        dw = torch.empty_like(w)
+        _CK(_L().ats_rmsnorm_bwd(_P(xin), _P(w), _P(dy2), _P(rstd), _P(ds), _P(dx), _P(partial), nb, _P(dw), None, 0,
+                                 rows, cols, _S(xin.device)), "rmsnorm_bwd")
+        return dx.view(ctx.shape), dw, None
+
+
+def rms_norm_skip(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6):
+    """-> (rms_norm(x), x) for the pre-norm residual pattern; use the second value as the residual input downstream."""
+    if _lib.use_cuda_kernels(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and torch.is_grad_enabled() and x.requires_grad:
+        return _RMSNormSkipFn.apply(x, w, eps)
+    return rms_norm(x, w, eps), x
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None):
@@ -677,6 +724,13 @@ def attention_packed_available(qkv: torch.Tensor, d: int, seq_len: int) -> bool:
     from . import attn as A
     return (_lib.use_cuda_kernels(qkv) and A._native_available() and d in (64, 128) and seq_len % 128 == 0 and qkv.is_contiguous()
             and qkv.shape[-1] % 8 == 0)
+
+
+def rope_attention_packed(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_q: int, n_kv: int, d: int,
+                          pos_offset: int = 0) -> torch.Tensor:
+    """RoPE + causal grouped-query attention on the packed projection as one autograd node (see ``attention_packed``)."""
+    from .attention_native import rope_flash_attention_packed
+    return rope_flash_attention_packed(qkv, cos, sin, n_q, n_kv, d, pos_offset)
 
 
 def attention_packed(qkv: torch.Tensor, n_q: int, n_kv: int, d: int) -> torch.Tensor:

@@ -116,8 +116,13 @@ def plan_slots(topk_idx: torch.Tensor, num_experts: int, capacity: int):
         slot_pos = torch.empty(flat.numel(), dtype=torch.int32, device=flat.device)
         counts = torch.empty(num_experts, dtype=torch.int32, device=flat.device)
         totals = torch.empty(num_experts, dtype=torch.int32, device=flat.device)
-        _CK(_L().ats_plan_slots(_P(flat), _P(slot_pos), _P(counts), _P(totals), flat.numel(), num_experts, capacity,
-                                _S(flat.device)), "plan_slots")
+        if flat.numel() > 4096:  # many slots: two multi-CTA passes instead of one CTA walking the whole list
+            chunk_cnt = torch.empty((flat.numel() + 1023) // 1024 * num_experts, dtype=torch.int32, device=flat.device)
+            _CK(_L().ats_plan_slots_chunked(_P(flat), _P(slot_pos), _P(counts), _P(totals), _P(chunk_cnt), flat.numel(), num_experts,
+                                            capacity, _S(flat.device)), "plan_slots_chunked")
+        else:
+            _CK(_L().ats_plan_slots(_P(flat), _P(slot_pos), _P(counts), _P(totals), flat.numel(), num_experts, capacity,
+                                    _S(flat.device)), "plan_slots")
         return slot_pos, counts, totals
     oh = F.one_hot(flat.long(), num_experts)
     rank = (oh.cumsum(0) - oh).gather(1, flat.long()[:, None]).squeeze(1)

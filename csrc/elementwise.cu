@@ -71,14 +71,16 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // RMSNorm backward. Each CTA walks rows blockIdx.x, +gridDim.x, ...; dx per row, dw partial per CTA (fp32),
 // reduced by rmsnorm_dw_reduce_kernel.  dx = rstd * (dy*w - xhat * mean(dy*w*xhat)), xhat = x * rstd.
 // If dres_in is given it is added to dx (gradient arriving through the residual branch).
-template <int THREADS>
+// NV = 16-byte vectors per thread (THREADS * NV * 8 >= cols): the per-thread arrays are sized by it, so the common widths
+// get a small register footprint and enough CTAs per SM to keep HBM busy (one CTA has one row in flight).
+template <int THREADS, int NV = 4>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, int rows, int cols) {
   __shared__ float red[33];
-  constexpr int MAXV = 4;
+  constexpr int MAXV = NV;
   const int nvec = cols >> 3;
   float dwacc[MAXV][8];
   float wreg[MAXV][8];
@@ -379,7 +381,9 @@ ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
   auto DY = static_cast<const __nv_bfloat16*>(dy);
   auto DR = static_cast<const __nv_bfloat16*>(dres_in);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (cols <= 128 * 32) rmsnorm_bwd_kernel<128><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+  if (cols <= 128 * 8) rmsnorm_bwd_kernel<128, 1><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+  else if (cols <= 128 * 16) rmsnorm_bwd_kernel<128, 2><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+  else if (cols <= 128 * 32) rmsnorm_bwd_kernel<128><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else if (cols <= 256 * 32) rmsnorm_bwd_kernel<256><<<nblocks, 256, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else if (cols <= 512 * 32) rmsnorm_bwd_kernel<512><<<nblocks, 512, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else return 1003;

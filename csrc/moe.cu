@@ -252,6 +252,62 @@ plan_slots_kernel(const int* __restrict__ topk_idx, int* __restrict__ slot_pos, 
   }
 }
 
+// Multi-CTA form of the same plan (same ranks, so still deterministic): chunks of 1024 slots; pass 1 counts the experts of
+// every chunk, pass 2 adds the counts of the earlier chunks to the rank inside the chunk.
+__device__ __forceinline__ void chunk_ranks(int e, int experts, int (*warp_cnt)[64 + 1], int& rank_in_warp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  rank_in_warp = 0;
+  for (int x = 0; x < experts; ++x) {
+    const unsigned mask = __ballot_sync(0xffffffffu, e == x);
+    if (e == x) rank_in_warp = __popc(mask & ((1u << lane) - 1u));
+    if (lane == 0) warp_cnt[warp][x] = __popc(mask);
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+plan_count_kernel(const int* __restrict__ topk_idx, int* __restrict__ chunk_cnt, long long slots, int experts) {
+  __shared__ int warp_cnt[32][64 + 1];
+  const long long s = (long long)blockIdx.x * 1024 + threadIdx.x;
+  const int e = s < slots ? topk_idx[s] : -1;
+  int r;
+  chunk_ranks(e, experts, warp_cnt, r);
+  __syncthreads();
+  if (threadIdx.x < experts) {
+    int tot = 0;
+    for (int w = 0; w < 32; ++w) tot += warp_cnt[w][threadIdx.x];
+    chunk_cnt[blockIdx.x * experts + threadIdx.x] = tot;
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+plan_rank_kernel(const int* __restrict__ topk_idx, const int* __restrict__ chunk_cnt, int* __restrict__ slot_pos,
+                 int* __restrict__ counts, int* __restrict__ totals, long long slots, int experts, int capacity) {
+  __shared__ int warp_cnt[32][64 + 1];
+  __shared__ int before_chunk[64];
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x < experts) {
+    int acc = 0;
+    for (int c = 0; c < int(blockIdx.x); ++c) acc += chunk_cnt[c * experts + threadIdx.x];
+    before_chunk[threadIdx.x] = acc;
+    if (blockIdx.x == gridDim.x - 1) {  // the last chunk knows the totals
+      const int tot = acc + chunk_cnt[blockIdx.x * experts + threadIdx.x];
+      counts[threadIdx.x] = tot < capacity ? tot : capacity;
+      if (totals) totals[threadIdx.x] = tot;
+    }
+  }
+  const long long s = (long long)blockIdx.x * 1024 + threadIdx.x;
+  const int e = s < slots ? topk_idx[s] : -1;
+  int r;
+  chunk_ranks(e, experts, warp_cnt, r);
+  __syncthreads();
+  if (e >= 0) {
+    int before = before_chunk[e];
+    for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+    const int rank = before + r;
+    slot_pos[s] = rank < capacity ? rank : -1;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Dispatch: for every kept slot copy (optionally scaled) row src[t] into dst_base[e] + pos * hidden, where
 // dst_base is a table of per-expert base pointers (a peer GPU's receive buffer under expert parallelism).
@@ -474,6 +530,17 @@ ATS_API int ats_plan_slots(const int* topk_idx, int* slot_pos, int* counts, int*
                            int capacity, void* stream) {
   if (experts > 64) return 1003;
   plan_slots_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(topk_idx, slot_pos, counts, totals, slots, experts, capacity);
+  return int(cudaGetLastError());
+}
+
+// Same result from two multi-CTA passes.  chunk_cnt: int32 scratch of ceil(slots / 1024) * experts entries.
+ATS_API int ats_plan_slots_chunked(const int* topk_idx, int* slot_pos, int* counts, int* totals, int* chunk_cnt, long long slots,
+                                   int experts, int capacity, void* stream) {
+  if (experts > 64 || slots <= 0) return 1003;
+  const unsigned chunks = unsigned((slots + 1023) / 1024);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  plan_count_kernel<<<chunks, 1024, 0, s>>>(topk_idx, chunk_cnt, slots, experts);
+  plan_rank_kernel<<<chunks, 1024, 0, s>>>(topk_idx, chunk_cnt, slot_pos, counts, totals, slots, experts, capacity);
   return int(cudaGetLastError());
 }
 

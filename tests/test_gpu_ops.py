@@ -202,6 +202,12 @@ def test_gate_topk_plan():
     pos, counts, totals = M.plan_slots(idx, E, cap)
     pos_r, counts_r, totals_r = M.plan_slots(idx.cpu(), E, cap)
     assert torch.equal(pos.cpu(), pos_r) and torch.equal(counts.cpu(), counts_r) and torch.equal(totals.cpu(), totals_r)
+    # many slots: the two-pass multi-CTA planner gives the same ranks (sizes off the 1024-slot chunk grid, tight capacity)
+    for n_slots, n_exp, cap2 in ((32768, 8, 5120), (10007, 6, 900), (5000, 64, 50)):
+        big = torch.randint(0, n_exp, (n_slots,), device=DEV, dtype=torch.int32).view(-1, 1)
+        p2, c2, t2 = M.plan_slots(big, n_exp, cap2)
+        pr, cr, tr = M.plan_slots(big.cpu(), n_exp, cap2)
+        assert torch.equal(p2.cpu(), pr) and torch.equal(c2.cpu(), cr) and torch.equal(t2.cpu(), tr), (n_slots, n_exp)
 
 
 def test_moe_ffn_fwd_bwd():
