@@ -228,13 +228,18 @@ class MoEFFNLayer(nn.Module):
         T = x.shape[0]
         E, k = self.num_experts, self.top_k
         logits = moe_ops.gate_logits(x, self.gate.weight)
-        idx, w, clean = moe_ops.route(logits, k, self.routing_temperature, self.routing_noise_std, self.training)
+        fused_route = logits.is_cuda and not (self.training and self.routing_noise_std > 0) and logits.dtype == torch.float32
+        if fused_route:
+            idx, w, aux = moe_ops.route_and_balance(logits, k, self.routing_temperature, self.load_balancing_weight)
+        else:
+            idx, w, clean = moe_ops.route(logits, k, self.routing_temperature, self.routing_noise_std, self.training)
         if self.training and self.expert_dropout > 0:
             keep = (torch.rand_like(w) >= self.expert_dropout).float()
             keep[:, 0] = 1.0
             w = w * keep
             w = w / w.sum(-1, keepdim=True).clamp(min=1e-20)
-        aux = moe_ops.load_balancing_loss(clean, idx, E, self.load_balancing_weight)
+        if not fused_route:
+            aux = moe_ops.load_balancing_loss(clean, idx, E, self.load_balancing_weight)
         cap = moe_ops.expert_capacity(T, E, k, self.capacity_factor, self.cfg.drop_tokens)
         res2 = residual.reshape(-1, shape[-1]) if residual is not None else None
         if self.ep is not None:

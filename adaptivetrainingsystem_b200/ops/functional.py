@@ -51,6 +51,8 @@ def _L():
         sig("ats_gate_bwd_dx", _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _vp)
         sig("ats_gate_bwd_dw", _vp, _vp, _vp, _c_int, _c_ll, _c_int, _c_int, _vp)
         sig("ats_topk_softmax", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _vp)
+        sig("ats_route_fwd", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _c_f, _vp)
+        sig("ats_route_bwd", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_f, _c_f, _vp)
         sig("ats_plan_slots", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_plan_slots_chunked", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_dispatch_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)

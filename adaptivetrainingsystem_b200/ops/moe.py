@@ -93,6 +93,55 @@ def route(logits: torch.Tensor, top_k: int, temperature: float = 1.0, noise_std:
     return idx.to(torch.int32), w, clean_probs
 
 
+class _RouteFn(torch.autograd.Function):
+    """Soft-max, top-k, renormalised weights and the load-balancing loss in two launches (one more in the backward), instead
+    of some thirty small tensor operations."""
+
+    @staticmethod
+    def forward(ctx, logits, top_k, temperature, weight):
+        T, E = logits.shape
+        lg = logits.contiguous()
+        dev = lg.device
+        probs = torch.empty_like(lg)
+        clean = torch.empty_like(lg) if temperature != 1.0 else None
+        idx = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, top_k, dtype=torch.float32, device=dev)
+        part = torch.empty((T + 255) // 256 * 2 * E, dtype=torch.float32, device=dev)
+        stats = torch.empty(2 * E + 2, dtype=torch.float32, device=dev)
+        _CK(_L().ats_route_fwd(_P(lg), _P(probs), _P(clean), _P(idx), _P(w), _P(part), _P(stats), T, E, top_k, float(temperature),
+                               float(weight), _S(dev)), "route_fwd")
+        ctx.save_for_backward(probs, clean, idx, w, stats) if clean is not None else ctx.save_for_backward(probs, idx, w, stats)
+        ctx.args = (top_k, float(temperature), float(weight), clean is not None)
+        ctx.mark_non_differentiable(idx)
+        aux = stats[2 * E].clone()
+        return idx, w, aux
+
+    @staticmethod
+    def backward(ctx, _didx, dw, daux):
+        top_k, temperature, weight, has_clean = ctx.args
+        if has_clean:
+            probs, clean, idx, w, stats = ctx.saved_tensors
+        else:
+            probs, idx, w, stats = ctx.saved_tensors
+            clean = None
+        T, E = probs.shape
+        dlogits = torch.empty_like(probs)
+        dwc = dw.contiguous().float() if dw is not None else None
+        dac = daux.reshape(1).float().contiguous() if daux is not None else None
+        _CK(_L().ats_route_bwd(_P(probs), _P(clean), _P(idx), _P(w), _P(dwc), _P(dac), _P(stats), _P(dlogits), T, E, top_k,
+                               temperature, weight, _S(probs.device)), "route_bwd")
+        return dlogits, None, None, None
+
+
+def route_and_balance(logits: torch.Tensor, top_k: int, temperature: float, weight: float):
+    """-> (topk_idx int32 [T,k], topk_w fp32 [T,k], load-balancing loss) with one fused forward / backward on CUDA; elsewhere
+    ``route`` + ``load_balancing_loss``."""
+    if logits.is_cuda and logits.dtype == torch.float32 and logits.shape[1] <= 64 and top_k <= 8:
+        return _RouteFn.apply(logits, top_k, temperature, weight)
+    idx, w, clean = route(logits, top_k, temperature, 0.0, False)
+    return idx, w, load_balancing_loss(clean, idx, logits.shape[1], weight)
+
+
 def load_balancing_loss(clean_probs: torch.Tensor, topk_idx: torch.Tensor, num_experts: int, weight: float,
                         token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """E * sum_e f_e * P_e * weight, clamped to <= 1 (reference ``core/model.py:1244-1263``)."""

@@ -208,6 +208,141 @@ __global__ void topk_softmax_kernel(const float* __restrict__ logits, float* __r
 }
 
 // ------------------------------------------------------------------------------------------------
+// Fused routing for training: soft-max of the logits (probabilities at temperature 1 for the balance loss, at 1 / inv_temp
+// for the routing), top-k, renormalised weights, and per-block partial sums of the clean probabilities and of the expert
+// picks (summed in a fixed order by route_finish_kernel -> deterministic).  One thread per token.
+//   aux = E * sum_e (picks_e / (T k)) * (sum_t p_clean[t, e] / T) * weight, clamped to <= 1
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+route_fwd_kernel(const float* __restrict__ logits, float* __restrict__ probs, float* __restrict__ clean, int* __restrict__ topk_idx,
+                 float* __restrict__ topk_w, float* __restrict__ part, long long tokens, int experts, int k, float inv_temp) {
+  __shared__ float s_p[8][64], s_c[64];
+  if (threadIdx.x < 64) s_c[threadIdx.x] = 0.f;
+  __syncthreads();
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float c[64];
+  for (int e = 0; e < experts; ++e) c[e] = 0.f;
+  if (t < tokens) {
+    float p[64];
+    float m = -INFINITY;
+    for (int e = 0; e < experts; ++e) {
+      c[e] = logits[t * experts + e];
+      m = fmaxf(m, c[e]);
+    }
+    float sc = 0.f, sp = 0.f;
+    for (int e = 0; e < experts; ++e) {
+      p[e] = __expf((c[e] - m) * inv_temp);
+      c[e] = __expf(c[e] - m);
+      sc += c[e];
+      sp += p[e];
+    }
+    const float ic = 1.f / sc, ip = 1.f / sp;
+    for (int e = 0; e < experts; ++e) {
+      p[e] *= ip;
+      c[e] *= ic;
+      probs[t * experts + e] = p[e];
+      if (clean) clean[t * experts + e] = c[e];
+    }
+    unsigned long long taken = 0ull;
+    float wsum = 0.f, wk[8];
+    int ik[8];
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int bi = 0;
+      for (int e = 0; e < experts; ++e)
+        if (!((taken >> e) & 1ull) && p[e] > best) {
+          best = p[e];
+          bi = e;
+        }
+      taken |= 1ull << bi;
+      wk[j] = best;
+      ik[j] = bi;
+      wsum += best;
+      atomicAdd(&s_c[bi], 1.f);
+    }
+    const float wi = 1.f / fmaxf(wsum, 1e-20f);
+    for (int j = 0; j < k; ++j) {
+      topk_idx[t * k + j] = ik[j];
+      topk_w[t * k + j] = wk[j] * wi;
+    }
+  }
+  // clean-probability sums: shuffle tree per warp, then the warps in order (fixed order -> reproducible bits);
+  // the pick counts are integers, so their atomics are exact
+  for (int e = 0; e < experts; ++e) {
+    const float ws = warp_sum(c[e]);
+    if (lane == 0) s_p[warp][e] = ws;
+  }
+  __syncthreads();
+  if (threadIdx.x < experts) {
+    float sp = 0.f;
+    for (int w = 0; w < 8; ++w) sp += s_p[w][threadIdx.x];
+    part[(long long)blockIdx.x * 2 * experts + threadIdx.x] = sp;
+    part[(long long)blockIdx.x * 2 * experts + experts + threadIdx.x] = s_c[threadIdx.x];
+  }
+}
+
+// stats[0..E) = mean clean probability, stats[E..2E) = pick fraction f_e, stats[2E] = aux, stats[2E + 1] = 1 if clamped
+__global__ void route_finish_kernel(const float* __restrict__ part, int nblocks, float* __restrict__ stats, long long tokens, int experts,
+                                    int k, float weight) {
+  __shared__ float prod[64];
+  const int e = threadIdx.x;
+  if (e < experts) {
+    float sp = 0.f, sc = 0.f;
+    for (int b = 0; b < nblocks; ++b) {
+      sp += part[(long long)b * 2 * experts + e];
+      sc += part[(long long)b * 2 * experts + experts + e];
+    }
+    const float pm = sp / float(tokens), f = sc / float(tokens * k);
+    stats[e] = pm;
+    stats[experts + e] = f;
+    prod[e] = pm * f;
+  }
+  __syncthreads();
+  if (e == 0) {
+    float a = 0.f;
+    for (int x = 0; x < experts; ++x) a += prod[x];
+    a *= float(experts) * weight;
+    stats[2 * experts + 1] = a > 1.f ? 1.f : 0.f;
+    stats[2 * experts] = fminf(a, 1.f);
+  }
+}
+
+// dlogits = softmax_bwd(clean, dclean) + softmax_bwd(probs, dprobs) * inv_temp with
+//   dclean[e] = daux * E * weight * f_e / T (0 when the loss was clamped),
+//   dprobs[i_j] = (dw_j - sum_m dw_m w_m) / S,  S = sum of the kept probabilities.
+__global__ void __launch_bounds__(256)
+route_bwd_kernel(const float* __restrict__ probs, const float* __restrict__ clean, const int* __restrict__ topk_idx,
+                 const float* __restrict__ topk_w, const float* __restrict__ dw, const float* __restrict__ daux,
+                 const float* __restrict__ stats, float* __restrict__ dlogits, long long tokens, int experts, int k, float inv_temp,
+                 float weight) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  float g[64];
+  for (int e = 0; e < experts; ++e) g[e] = 0.f;
+  if (dw) {
+    float S = 0.f, dot = 0.f;
+    for (int j = 0; j < k; ++j) {
+      S += probs[t * experts + topk_idx[t * k + j]];
+      dot += dw[t * k + j] * topk_w[t * k + j];
+    }
+    const float iS = 1.f / fmaxf(S, 1e-20f);
+    for (int j = 0; j < k; ++j) g[topk_idx[t * k + j]] = (dw[t * k + j] - dot) * iS;
+    float pg = 0.f;
+    for (int e = 0; e < experts; ++e) pg += probs[t * experts + e] * g[e];
+    for (int e = 0; e < experts; ++e) g[e] = probs[t * experts + e] * (g[e] - pg) * inv_temp;
+  }
+  if (daux && stats[2 * experts + 1] == 0.f) {
+    const float scale = daux[0] * float(experts) * weight / float(tokens);
+    const float* cl = clean ? clean : probs;
+    float pg = 0.f;
+    for (int e = 0; e < experts; ++e) pg += cl[t * experts + e] * scale * stats[experts + e];
+    for (int e = 0; e < experts; ++e) g[e] += cl[t * experts + e] * (scale * stats[experts + e] - pg);
+  }
+  for (int e = 0; e < experts; ++e) dlogits[t * experts + e] = g[e];
+}
+
+// ------------------------------------------------------------------------------------------------
 // Slot planning (single CTA, deterministic): slot s = t*k + j goes to expert e = topk_idx[s]; its rank is the
 // number of earlier slots with the same expert.  rank >= capacity -> dropped (pos = -1).
 //   slot_pos[s] = rank (row inside the expert's region)   counts[e] = min(total_e, capacity)
@@ -523,6 +658,29 @@ ATS_API int ats_topk_softmax(const float* logits, float* probs, int* topk_idx, f
   if (tokens == 0) return 0;
   topk_softmax_kernel<<<unsigned((tokens + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       logits, probs, topk_idx, topk_w, tokens, experts, k, 1.f / temperature);
+  return int(cudaGetLastError());
+}
+
+// Fused training router.  clean: [T, E] or null when temperature == 1 (then probs doubles as the clean probabilities).
+// part: fp32 scratch [ceil(T / 256), 2, E]; stats: fp32 [2 E + 2] (see route_finish_kernel).
+ATS_API int ats_route_fwd(const float* logits, float* probs, float* clean, int* topk_idx, float* topk_w, float* part, float* stats,
+                          long long tokens, int experts, int k, float temperature, float weight, void* stream) {
+  if (experts > 64 || k > 8 || k > experts) return 1003;
+  if (tokens == 0) return 0;
+  const int nblocks = int((tokens + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  route_fwd_kernel<<<nblocks, 256, 0, s>>>(logits, probs, clean, topk_idx, topk_w, part, tokens, experts, k, 1.f / temperature);
+  route_finish_kernel<<<1, 64, 0, s>>>(part, nblocks, stats, tokens, experts, k, weight);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_route_bwd(const float* probs, const float* clean, const int* topk_idx, const float* topk_w, const float* dw,
+                          const float* daux, const float* stats, float* dlogits, long long tokens, int experts, int k,
+                          float temperature, float weight, void* stream) {
+  if (experts > 64 || k > 8) return 1003;
+  if (tokens == 0) return 0;
+  route_bwd_kernel<<<unsigned((tokens + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      probs, clean, topk_idx, topk_w, dw, daux, stats, dlogits, tokens, experts, k, 1.f / temperature, weight);
   return int(cudaGetLastError());
 }
 

@@ -532,3 +532,25 @@ def test_graph_decoder_matches_eager_decode():
     agree = (a == b).float().mean().item()
     assert agree > 0.9, agree  # bf16 arg-max ties may flip a late token; the prefix must agree
     assert torch.equal(a[:, :8], b[:, :8])
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+def test_fused_router_matches_torch_ops(temperature):
+    from adaptivetrainingsystem_b200.ops import moe as M
+    torch.manual_seed(12)
+    T, E, k, weight = 5000, 8, 2, 0.01
+    logits = (torch.randn(T, E, device="cuda") * 2).requires_grad_()
+    idx, w, aux = M.route_and_balance(logits, k, temperature, weight)
+    gw = torch.randn(T, k, device="cuda")
+    ((w * gw).sum() + 3.0 * aux).backward()
+    ref = logits.detach().clone().requires_grad_()
+    idx_r, w_r, clean = M.route(ref, k, temperature, 0.0, True)  # grad enabled -> PyTorch ops
+    aux_r = M.load_balancing_loss(clean, idx_r, E, weight)
+    ((w_r * gw).sum() + 3.0 * aux_r).backward()
+    assert torch.equal(idx, idx_r)
+    assert torch.allclose(w, w_r, atol=1e-5)
+    assert abs(float(aux) - float(aux_r)) < 1e-6 * max(1.0, abs(float(aux_r)))
+    assert torch.allclose(logits.grad, ref.grad, atol=2e-6, rtol=1e-3), (logits.grad - ref.grad).abs().max().item()
+    # reproducible bits
+    idx2, w2, aux2 = M.route_and_balance(logits.detach(), k, temperature, weight)
+    assert torch.equal(aux2, aux.detach()) and torch.equal(w2, w.detach())
