@@ -5,7 +5,8 @@ from .functional import (rms_norm, rms_norm_skip, rms_norm_reference, layer_norm
                          rope_tables, rope_reference, rope_packed, embedding, cross_entropy,
                          cross_entropy_reference, linear_cross_entropy, attention, attention_reference, attention_packed, attention_packed_available, rope_attention_packed,
                          sumsq, clip_coef, adamw_step)
-from .gemm import gemm_nt, gemm_nn, gemm_tn, gemm_nt_swiglu, grouped_nt, grouped_nn, grouped_tn
+from .gemm import (gemm_nt, gemm_nn, gemm_tn, gemm_nt_swiglu, gemm_nn_swiglu_bwd, grouped_nt, grouped_nn, grouped_nn_swiglu_bwd,
+                   grouped_tn)
 from .moe import (expert_capacity, gate_logits, route, load_balancing_loss, plan_slots, dispatch, combine,
                   slot_dot, moe_ffn, moe_ffn_reference)
 from .serving import (decode_attention, decode_attention_available, decode_attention_reference, sample_tokens,  # noqa: E402,F401

@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 
-EPI_STORE, EPI_ADDC, EPI_F32, EPI_SWIGLU = 0, 1, 2, 3
+EPI_STORE, EPI_ADDC, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 
 _c_int, _c_ll, _c_f, _vp = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 _configured = False
@@ -164,6 +164,30 @@ def gemm_nt_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch
     return out
 
 
+def swiglu_bwd_reference(pre: torch.Tensor, dh: torch.Tensor):
+    """(dgu [.., 2I], h [.., I]) of h = silu(gate) * up from the saved pre-activations [.., 2I] and dh [.., I], in fp32."""
+    g, u = pre.float().chunk(2, dim=-1)
+    sg = torch.sigmoid(g)
+    dhf = dh.float()
+    return torch.cat([dhf * u * (sg + g * sg * (1 - sg)), dhf * g * sg], dim=-1).to(pre.dtype), (g * sg * u).to(pre.dtype)
+
+
+def gemm_nn_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, pre: torch.Tensor):
+    """dy [M, H] · w_down [H, I] = dh, pushed through the SwiGLU backward in the GEMM epilogue: -> (dgu [M, 2I], h [M, I])
+    from the saved pre-activations ``pre`` [M, 2I]; dh is never written."""
+    inter = w_down.shape[1]
+    if not _lib.use_cuda_kernels(dy):
+        return swiglu_bwd_reference(pre, (dy.float() @ w_down.float()).to(dy.dtype))
+    dy, w = _check2d(dy), _check2d(w_down)
+    M, H = dy.shape
+    assert pre.is_contiguous() and pre.shape == (M, 2 * inter)
+    dgu = torch.empty_like(pre)
+    h = torch.empty(M, inter, dtype=pre.dtype, device=pre.device)
+    _raw(dy, M, H, dy.stride(0), 0, w, H, inter, w.stride(0), 1, dgu, 2 * inter, h, inter, pre, 2 * inter, M, inter, H,
+         epilogue=EPI_SWIGLU_BWD, up_offset=inter)
+    return dgu, h
+
+
 # ----------------------------------------------------------------------------------------------------------
 # grouped (expert) products on the capacity layout
 # ----------------------------------------------------------------------------------------------------------
@@ -224,6 +248,25 @@ def grouped_nn(dy: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, out: Opt
     _raw(dy, Gn * C, N, N, 0, w, w.shape[0] * N, K, K, 1, out, K, None, 0, None, 0, C, K, N,
          groups=Gn, ragged=1, counts=counts, a_gs_mn=C, b_gs_k=N, d_gs=C * K, b_div=b_div, d_table=d_table)
     return out
+
+
+def grouped_nn_swiglu_bwd(dy: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, pre: torch.Tensor, b_div: int = 1):
+    """Backward through ``h = silu(gate) * up`` fused into the product ``dh = dy · w``: dy [G,C,N], w [E,N,I], pre [G,C,2I]
+    (saved gate / up pre-activations) -> (dgu [G,C,2I], h [G,C,I]); dh itself is never written.  Rows beyond the padded
+    count of a group are left untouched.  The training path keeps the two-launch form: with K = hidden = 2048 the
+    epilogue (two gathered reads and three stores per element from four warps) outlasts the main loop of the next tile,
+    and a step measured 2.5 % slower than GEMM + streaming element-wise kernel."""
+    Gn, C, N = dy.shape
+    inter = w.shape[2]
+    if not _lib.use_cuda_kernels(dy):
+        return swiglu_bwd_reference(pre, grouped_nn(dy, w, counts, b_div=b_div))
+    assert dy.is_contiguous() and w.is_contiguous() and pre.is_contiguous() and C % 128 == 0
+    dgu = torch.empty_like(pre)
+    h = torch.empty(Gn, C, inter, dtype=pre.dtype, device=pre.device)
+    _raw(dy, Gn * C, N, N, 0, w, w.shape[0] * N, inter, inter, 1, dgu, 2 * inter, h, inter, pre, 2 * inter, C, inter, N,
+         epilogue=EPI_SWIGLU_BWD, up_offset=inter, groups=Gn, ragged=1, counts=counts, a_gs_mn=C, b_gs_k=N, d_gs=C * 2 * inter,
+         c_gs=C * inter, aux_gs=C * 2 * inter, b_div=b_div)
+    return dgu, h
 
 
 def grouped_tn(dy: torch.Tensor, x: torch.Tensor, counts: torch.Tensor, out: Optional[torch.Tensor] = None,

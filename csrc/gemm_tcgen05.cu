@@ -36,7 +36,7 @@ constexpr int GEMM_THREADS = 256;  // TMA, MMA, 4 epilogue warps, 2 copy warps (
 constexpr int MAX_GROUPS = 256;
 constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + (MAX_GROUPS + 1) * 4;
 
-enum Epilogue : int { kStore = 0, kAddC = 1, kF32 = 2, kSwiGLU = 3 };
+enum Epilogue : int { kStore = 0, kAddC = 1, kF32 = 2, kSwiGLU = 3, kSwiGLUBwd = 4 };
 
 struct GemmArgs {
   int M, N, K;
@@ -74,6 +74,11 @@ struct GemmArgs {
   int ready_rows, n_chunks, epoch, first_chunk, n_rot;
   int own_row0, own_rows;    // rows of B that live in this rank's shard (read through map_b_own)
   long long* prof;           // optional [8]: cycle totals of CTA 0's MMA thread (total, wait for stage, wait for accumulator, issue, k-blocks)
+  // kSwiGLUBwd: the product is dh (gradient of h = silu(gate) * up); `aux` holds the saved pre-activations [gate | up] (read),
+  // D receives [dgate | dup] in the same layout and out2 the recomputed h, so dh itself never goes to memory.
+  __nv_bfloat16* out2;
+  int ldout2;
+  long long out2_gs;
   int fp8;
   const float* row_scale;  // [groups * rs_gs] or null
   const float* col_scale;  // [weights * cs_gs] or null
@@ -431,6 +436,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
+      } else if (p.epilogue == kSwiGLUBwd) {
+        __nv_bfloat16* dbase = p.D + p.d_gs * t.g + (long long)row * p.ldd;
+        const __nv_bfloat16* arow = p.aux + p.aux_gs * t.g + (long long)row * p.ldaux;
+        __nv_bfloat16* hrow = p.out2 ? p.out2 + p.out2_gs * t.g + (long long)row * p.ldout2 : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0;
+          }
+          if (!row_ok) continue;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c * 32 + v * 8;
+            if (col < p.N) {
+              const uint4 gq = *reinterpret_cast<const uint4*>(arow + col);
+              const uint4 uq = *reinterpret_cast<const uint4*>(arow + p.up_offset + col);
+              const uint32_t gg[4] = {gq.x, gq.y, gq.z, gq.w}, uu[4] = {uq.x, uq.y, uq.z, uq.w};
+              uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                // dh rounded to bf16 first: bit-identical to writing dh and running the separate backward kernel
+                const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[v * 8 + 2 * e]) * rs, __uint_as_float(r[v * 8 + 2 * e + 1]) * rs));
+                const float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]);
+                const float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
+                const float si0 = a.x * s0, si1 = a.y * s1;
+                og[e] = pack_bf16x2(d.x * b.x * (s0 + si0 * (1.f - s0)), d.y * b.y * (s1 + si1 * (1.f - s1)));
+                ou[e] = pack_bf16x2(d.x * si0, d.y * si1);
+                oh[e] = pack_bf16x2(si0 * b.x, si1 * b.y);
+              }
+              *reinterpret_cast<uint4*>(dbase + col) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(dbase + p.up_offset + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              if (hrow) *reinterpret_cast<uint4*>(hrow + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            }
+          }
+        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -599,6 +644,13 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = g_gemm_prof;
+  p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
+  if (epilogue == kSwiGLUBwd) {
+    // second output (h) travels in the C slot of this entry point: C / ldc / c_gs
+    if (!aux || (up_offset & 7) || (ldaux & 7)) return 1004;
+    p.out2 = static_cast<__nv_bfloat16*>(const_cast<void*>(C)); p.ldout2 = ldc; p.out2_gs = c_gs;
+    p.C = nullptr;
+  }
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
 
@@ -635,6 +687,7 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
+  p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
 
@@ -677,6 +730,7 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   p.epoch = int(calls * (p.chunk_bytes / 4096));  // every call adds chunk_bytes / 4096 to each remote chunk's counter
   p.first_chunk = int(my_rank * (shard_rows / ready_rows));
   p.own_row0 = int(my_rank * shard_rows); p.own_rows = int(shard_rows); p.prof = nullptr;
+  p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
   const int tile_w = epilogue == kSwiGLU ? 128 : BN;
   p.n_rot = int((my_rank * shard_rows) % (epilogue == kSwiGLU ? (long long)up_offset : b_rows) / tile_w);
   return launch_gemm(ma, mb, p, epilogue, 1, M, N, 0, stream, &mb_own);

@@ -158,3 +158,35 @@ def test_grouped_expert_parallel_layout():
         n = int(counts[g])
         if n:
             _close(target[perm[g], :n], ref[g, :n])
+
+
+def test_gemm_swiglu_backward_epilogue_matches_separate_kernel():
+    """dh = dy · w2 fused with the SwiGLU backward against the unfused sequence (GEMM, then the element-wise kernel)."""
+    import ctypes  # noqa: F401
+    from adaptivetrainingsystem_b200.ops import functional as Fn
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    torch.manual_seed(4)
+    M, H, I = 900, 512, 1408
+    dy = (torch.randn(M, H, device="cuda") * 0.5).bfloat16()
+    w2 = (torch.randn(H, I, device="cuda") * 0.05).bfloat16()
+    pre = torch.randn(M, 2 * I, device="cuda").bfloat16()
+    dgu, h = G.gemm_nn_swiglu_bwd(dy, w2, pre)
+    dh = G.gemm_nn(dy, w2)
+    dgu_ref = torch.empty_like(pre)
+    h_ref = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    Fn._CK(Fn._L().ats_swiglu_bwd(Fn._P(pre), Fn._P(dh), Fn._P(dgu_ref), Fn._P(h_ref), M, I, Fn._S(pre.device)), "swiglu_bwd")
+    assert torch.equal(dgu, dgu_ref) and torch.equal(h, h_ref)
+    # grouped form on the capacity layout
+    E, C = 3, 256
+    counts = torch.tensor([200, 0, 130], dtype=torch.int32, device="cuda")
+    dye = (torch.randn(E, C, H, device="cuda") * 0.5).bfloat16()
+    for e, c in enumerate(counts.tolist()):
+        dye[e, c:] = 0
+    w2e = (torch.randn(E, H, I, device="cuda") * 0.05).bfloat16()
+    pre_e = torch.randn(E, C, 2 * I, device="cuda").bfloat16()
+    dgu_e, h_e = G.grouped_nn_swiglu_bwd(dye, w2e, counts, pre_e)
+    for e, c in enumerate(counts.tolist()):
+        if c == 0:
+            continue
+        d1, h1 = G.gemm_nn_swiglu_bwd(dye[e, :c].contiguous(), w2e[e], pre_e[e, :c].contiguous())
+        assert torch.equal(dgu_e[e, :c], d1) and torch.equal(h_e[e, :c], h1), e
