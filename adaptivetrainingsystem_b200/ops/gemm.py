@@ -10,6 +10,7 @@ group ``e`` actually used; pad rows up to the next multiple of 128 must be zero)
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -37,8 +38,18 @@ def _fn():
             _c_ll, _c_ll, _c_ll,  # d_gs c_gs aux_gs
             _c_int, _c_int, _c_int, _vp,  # b_div k_segs seg_stride d_table
             _vp, _c_int, _vp]  # status, max_ctas, stream
+        lib.ats_gemm_set_pair.restype = None
+        lib.ats_gemm_set_pair.argtypes = [_c_int]
+        if os.environ.get("ATS_GEMM_PAIR") is not None:
+            lib.ats_gemm_set_pair(int(os.environ["ATS_GEMM_PAIR"]))
         _configured = True
     return lib.ats_gemm_bf16
+
+
+def set_pair_kernels(on: bool) -> None:
+    """Products with at least 256 rows run on pairs of CTAs (``tcgen05.mma.cta_group::2``, the default) or on single CTAs."""
+    _fn()
+    _lib.cuda_lib().ats_gemm_set_pair(int(bool(on)))
 
 
 def _raw(a, a_rows, a_cols, lda, a_mn, b, b_rows, b_cols, ldb, b_mn, d, ldd, c, ldc, aux, ldaux,

@@ -111,7 +111,7 @@ __device__ __forceinline__ int tiles_n_of(const GemmArgs& p) {
   return p.epilogue == kSwiGLU ? (p.N + 127) / 128 : (p.N + BN - 1) / BN;
 }
 
-__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* prefix, int tile, int& g_hint) {
+__device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* prefix, int tile, int& g_hint, int bm = BM) {
   TileCoord t;
   int g = g_hint;
   while (g + 1 < p.groups && tile >= prefix[g + 1]) ++g;
@@ -123,7 +123,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   // Rasterisation: panels of PANEL_N tile columns, rows fastest-varying across panels' columns, so that the ~148
   // tiles in flight touch about as many rows of A as of B (keeps both operands L2-resident per wave).
   constexpr int PANEL_N = 8;
-  const int tm = (mg + BM - 1) / BM;
+  const int tm = (mg + bm - 1) / bm;
   const int panel = local / (PANEL_N * tm);
   const int within = local - panel * PANEL_N * tm;
   const int width = min(PANEL_N, tn - panel * PANEL_N);
@@ -131,12 +131,161 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   int nt = panel * PANEL_N + (within - mt * width);
   if (p.n_rot) nt = (nt + p.n_rot) % tn;  // gathered B: begin with the columns whose rows are already local
   t.g = g;
-  t.m0 = mt * BM;
+  t.m0 = mt * bm;
   t.n0 = nt * (p.epilogue == kSwiGLU ? 128 : BN);
   const int bk = p.fp8 ? 2 * BK : BK;  // elements per K block (always 128 bytes)
   t.k_iters = (kg + bk - 1) / bk;
   t.valid = mg;
   return t;
+}
+
+// Epilogue of one tile for one warp: `taddr` = TMEM address of the accumulator at this warp's lane quadrant, `row_in_tile` =
+// the accumulator row (TMEM lane) that this thread owns.
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord& t, uint32_t taddr, int row_in_tile) {
+  const int row = t.m0 + row_in_tile;
+  const bool row_ok = row < t.valid;
+  const bool have_acc = t.k_iters > 0;
+  const float rs = (p.row_scale && row_ok) ? p.row_scale[p.rs_gs * t.g + row] * p.alpha : p.alpha;
+  const float* cs = p.col_scale ? p.col_scale + p.cs_gs * (t.g / p.b_div) : nullptr;
+  if (p.epilogue == kSwiGLU) {
+    __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
+    __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
+    __nv_bfloat16* arow = p.aux ? p.aux + p.aux_gs * t.g + (long long)row * p.ldaux : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t gr[32], ur[32];
+      tmem_ld_32x32(taddr + c * 32, gr);
+      tmem_ld_32x32(taddr + 128 + c * 32, ur);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = t.n0 + c * 32 + v * 8;
+          if (col < p.N) {
+            uint32_t h[4], gg[4], uu[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * rs, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * rs;
+              float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * rs, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * rs;
+              if (cs) {
+                g0 *= cs[col + 2 * e];
+                g1 *= cs[col + 2 * e + 1];
+                u0 *= cs[p.up_offset + col + 2 * e];
+                u1 *= cs[p.up_offset + col + 2 * e + 1];
+              }
+              gg[e] = pack_bf16x2(g0, g1);
+              uu[e] = pack_bf16x2(u0, u1);
+              // activation on the bf16-rounded values so a separate SwiGLU pass gives identical bits
+              float2 gq = unpack_bf16x2(gg[e]), uq = unpack_bf16x2(uu[e]);
+              h[e] = pack_bf16x2(silu_f(gq.x) * uq.x, silu_f(gq.y) * uq.y);
+            }
+            *reinterpret_cast<uint4*>(drow + col) = make_uint4(h[0], h[1], h[2], h[3]);
+            if (arow) {
+              *reinterpret_cast<uint4*>(arow + col) = make_uint4(gg[0], gg[1], gg[2], gg[3]);
+              *reinterpret_cast<uint4*>(arow + p.up_offset + col) = make_uint4(uu[0], uu[1], uu[2], uu[3]);
+            }
+          }
+        }
+      }
+    }
+  } else if (p.epilogue == kSwiGLUBwd) {
+    __nv_bfloat16* dbase = p.D + p.d_gs * t.g + (long long)row * p.ldd;
+    const __nv_bfloat16* arow = p.aux + p.aux_gs * t.g + (long long)row * p.ldaux;
+    __nv_bfloat16* hrow = p.out2 ? p.out2 + p.out2_gs * t.g + (long long)row * p.ldout2 : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      if (have_acc) {
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0;
+      }
+      if (!row_ok) continue;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const int col = t.n0 + c * 32 + v * 8;
+        if (col < p.N) {
+          const uint4 gq = *reinterpret_cast<const uint4*>(arow + col);
+          const uint4 uq = *reinterpret_cast<const uint4*>(arow + p.up_offset + col);
+          const uint32_t gg[4] = {gq.x, gq.y, gq.z, gq.w}, uu[4] = {uq.x, uq.y, uq.z, uq.w};
+          uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            // dh rounded to bf16 first: bit-identical to writing dh and running the separate backward kernel
+            const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[v * 8 + 2 * e]) * rs, __uint_as_float(r[v * 8 + 2 * e + 1]) * rs));
+            const float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]);
+            const float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
+            const float si0 = a.x * s0, si1 = a.y * s1;
+            og[e] = pack_bf16x2(d.x * b.x * (s0 + si0 * (1.f - s0)), d.y * b.y * (s1 + si1 * (1.f - s1)));
+            ou[e] = pack_bf16x2(d.x * si0, d.y * si1);
+            oh[e] = pack_bf16x2(si0 * b.x, si1 * b.y);
+          }
+          *reinterpret_cast<uint4*>(dbase + col) = make_uint4(og[0], og[1], og[2], og[3]);
+          *reinterpret_cast<uint4*>(dbase + p.up_offset + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          if (hrow) *reinterpret_cast<uint4*>(hrow + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      if (have_acc) {
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0;
+      }
+      if (!row_ok) continue;
+      const int colbase = t.n0 + c * 32;
+      if (p.epilogue == kF32) {
+        float* drow = p.Df32 + p.d_gs * t.g + (long long)row * p.ldd;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int col = colbase + v * 4;
+          if (col < p.N) {
+            float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
+                                   __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
+            if (p.beta) {
+              float4 old = *reinterpret_cast<float4*>(drow + col);
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(drow + col) = o;
+          }
+        }
+      } else {
+        __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
+        __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
+        const __nv_bfloat16* crow =
+            p.epilogue == kAddC ? p.C + p.c_gs * t.g + (long long)row * p.ldc : nullptr;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = colbase + v * 8;
+          if (col < p.N) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * rs;
+            if (cs) {
+              const float4 c0 = *reinterpret_cast<const float4*>(cs + col), c1 = *reinterpret_cast<const float4*>(cs + col + 4);
+              f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
+              f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
+            }
+            if (crow) {
+              uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
+              float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
+              f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
+              f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
+            }
+            *reinterpret_cast<uint4*>(drow + col) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                               pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          }
+        }
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -390,150 +539,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (!mbar_wait_bounded(&tfull[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
-      const int row = t.m0 + row_in_tile;
-      const bool row_ok = row < t.valid;
-      const bool have_acc = t.k_iters > 0;
-      const float rs = (p.row_scale && row_ok) ? p.row_scale[p.rs_gs * t.g + row] * p.alpha : p.alpha;
-      const float* cs = p.col_scale ? p.col_scale + p.cs_gs * (t.g / p.b_div) : nullptr;
-      if (p.epilogue == kSwiGLU) {
-        __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
-        __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
-        __nv_bfloat16* arow = p.aux ? p.aux + p.aux_gs * t.g + (long long)row * p.ldaux : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t gr[32], ur[32];
-          tmem_ld_32x32(taddr + c * 32, gr);
-          tmem_ld_32x32(taddr + 128 + c * 32, ur);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int col = t.n0 + c * 32 + v * 8;
-              if (col < p.N) {
-                uint32_t h[4], gg[4], uu[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * rs, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * rs;
-                  float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * rs, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * rs;
-                  if (cs) {
-                    g0 *= cs[col + 2 * e];
-                    g1 *= cs[col + 2 * e + 1];
-                    u0 *= cs[p.up_offset + col + 2 * e];
-                    u1 *= cs[p.up_offset + col + 2 * e + 1];
-                  }
-                  gg[e] = pack_bf16x2(g0, g1);
-                  uu[e] = pack_bf16x2(u0, u1);
-                  // activation on the bf16-rounded values so a separate SwiGLU pass gives identical bits
-                  float2 gq = unpack_bf16x2(gg[e]), uq = unpack_bf16x2(uu[e]);
-                  h[e] = pack_bf16x2(silu_f(gq.x) * uq.x, silu_f(gq.y) * uq.y);
-                }
-                *reinterpret_cast<uint4*>(drow + col) = make_uint4(h[0], h[1], h[2], h[3]);
-                if (arow) {
-                  *reinterpret_cast<uint4*>(arow + col) = make_uint4(gg[0], gg[1], gg[2], gg[3]);
-                  *reinterpret_cast<uint4*>(arow + p.up_offset + col) = make_uint4(uu[0], uu[1], uu[2], uu[3]);
-                }
-              }
-            }
-          }
-        }
-      } else if (p.epilogue == kSwiGLUBwd) {
-        __nv_bfloat16* dbase = p.D + p.d_gs * t.g + (long long)row * p.ldd;
-        const __nv_bfloat16* arow = p.aux + p.aux_gs * t.g + (long long)row * p.ldaux;
-        __nv_bfloat16* hrow = p.out2 ? p.out2 + p.out2_gs * t.g + (long long)row * p.ldout2 : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          if (have_acc) {
-            tmem_ld_32x32(taddr + c * 32, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0;
-          }
-          if (!row_ok) continue;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = t.n0 + c * 32 + v * 8;
-            if (col < p.N) {
-              const uint4 gq = *reinterpret_cast<const uint4*>(arow + col);
-              const uint4 uq = *reinterpret_cast<const uint4*>(arow + p.up_offset + col);
-              const uint32_t gg[4] = {gq.x, gq.y, gq.z, gq.w}, uu[4] = {uq.x, uq.y, uq.z, uq.w};
-              uint32_t og[4], ou[4], oh[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                // dh rounded to bf16 first: bit-identical to writing dh and running the separate backward kernel
-                const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[v * 8 + 2 * e]) * rs, __uint_as_float(r[v * 8 + 2 * e + 1]) * rs));
-                const float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]);
-                const float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
-                const float si0 = a.x * s0, si1 = a.y * s1;
-                og[e] = pack_bf16x2(d.x * b.x * (s0 + si0 * (1.f - s0)), d.y * b.y * (s1 + si1 * (1.f - s1)));
-                ou[e] = pack_bf16x2(d.x * si0, d.y * si1);
-                oh[e] = pack_bf16x2(si0 * b.x, si1 * b.y);
-              }
-              *reinterpret_cast<uint4*>(dbase + col) = make_uint4(og[0], og[1], og[2], og[3]);
-              *reinterpret_cast<uint4*>(dbase + p.up_offset + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-              if (hrow) *reinterpret_cast<uint4*>(hrow + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          if (have_acc) {
-            tmem_ld_32x32(taddr + c * 32, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0;
-          }
-          if (!row_ok) continue;
-          const int colbase = t.n0 + c * 32;
-          if (p.epilogue == kF32) {
-            float* drow = p.Df32 + p.d_gs * t.g + (long long)row * p.ldd;
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              const int col = colbase + v * 4;
-              if (col < p.N) {
-                float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
-                                       __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
-                if (p.beta) {
-                  float4 old = *reinterpret_cast<float4*>(drow + col);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(drow + col) = o;
-              }
-            }
-          } else {
-            __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
-            __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
-            const __nv_bfloat16* crow =
-                p.epilogue == kAddC ? p.C + p.c_gs * t.g + (long long)row * p.ldc : nullptr;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int col = colbase + v * 8;
-              if (col < p.N) {
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * rs;
-                if (cs) {
-                  const float4 c0 = *reinterpret_cast<const float4*>(cs + col), c1 = *reinterpret_cast<const float4*>(cs + col + 4);
-                  f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
-                  f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
-                }
-                if (crow) {
-                  uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
-                  float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
-                  f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
-                  f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
-                }
-                *reinterpret_cast<uint4*>(drow + col) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
-                                                                   pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile(p, t, taddr, row_in_tile);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -549,6 +555,224 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (two SMs) works on one 256 x 256 tile with `tcgen05.mma.cta_group::2`.
+// Each CTA stages its own 128 rows of A and only HALF of the B tile (128 of the 256 rows), so a pair pulls 64 KB per
+// k-block from L2 where two independent CTAs pull 96 KB, and a stage is 32 KB, which makes room for six stages.
+// One thread of the leader CTA (cluster rank 0) issues every MMA; both CTAs hold their 128 accumulator rows in
+// their own TMEM and run their own epilogue.
+//
+//   full[s]   leader's barrier: its producer arrives with the byte count of BOTH CTAs, the loads of both CTAs
+//             (`.cta_group::2`, no multicast) complete on it
+//   empty[s]  one per CTA: freed by the leader's commit, delivered to both CTAs
+//   tfull[a]  one per CTA: accumulator ready (same commit form)
+//   tempty[a] leader's barrier: the epilogue warps of both CTAs arrive (the partner's through its cluster address)
+// ------------------------------------------------------------------------------------------------
+constexpr int PAIR_BM = 2 * BM;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_STAGE_BYTES = (BN / 2) * BK * 2;
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
+constexpr int PAIR_THREADS = 192;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + (MAX_GROUPS + 1) * 4;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + PAIR_STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+  uint64_t* full = bars;                         // [PAIR_STAGES]
+  uint64_t* empty = bars + PAIR_STAGES;          // [PAIR_STAGES]
+  uint64_t* tfull = bars + 2 * PAIR_STAGES;      // [2]
+  uint64_t* tempty = bars + 2 * PAIR_STAGES + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PAIR_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* prefix = reinterpret_cast<int*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256);  // [groups + 1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0 = leader
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 8);  // four epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    int acc = 0;
+    const int tn = tiles_n_of(p);
+    for (int g = 0; g < p.groups; ++g) {
+      prefix[g] = acc;
+      int mg, kg;
+      group_extents(p, g, mg, kg);
+      acc += ((mg + PAIR_BM - 1) / PAIR_BM) * tn;
+    }
+    prefix[p.groups] = acc;
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = prefix[p.groups];
+  const int first_tile = int(cluster_id_x());
+  const int tile_step = int(cluster_count_x());
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0, phase = 0, g_hint = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+        TileCoord t = decode_tile(p, prefix, tile, g_hint, PAIR_BM);
+        const int a_mn_c = t.m0 + int(rank) * BM + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
+        const int gb = t.g / p.b_div;
+        const int b_k_c = p.b_gs_k * gb;
+        // this CTA's half of the B tile: rows n0 .. n0+127 for the leader, the next 128 (SwiGLU: the "up" rows) for the partner
+        const int b_mn_c = t.n0 + p.b_gs_mn * gb + (rank ? (p.epilogue == kSwiGLU ? p.up_offset : 128) : 0);
+        int seg = 0, seg_left = seg_iters_of(p, t.g, 0, t.k_iters), kpos = 0;
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          while (seg_left == 0) {
+            ++seg;
+            seg_left = seg_iters_of(p, t.g, seg, t.k_iters);
+            kpos = 0;
+          }
+          if (!mbar_wait_bounded(&empty[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * PAIR_STAGE_BYTES);
+          const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * PAIR_B_STAGE_BYTES;
+          const int k0 = seg * p.seg_stride + kpos * BK;
+          ++kpos;
+          --seg_left;
+          if (!p.a_mn) {
+            tma_load_2d_pair(a_dst, &map_a, bar, a_k_c + k0, a_mn_c);  // box 64 x 128
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)  // box 64 (MN) x 64 (K rows)
+              tma_load_2d_pair(a_dst + j * (BK * 128), &map_a, bar, a_mn_c + 64 * j, a_k_c + k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(b_dst, &map_b, bar, b_k_c + k0, b_mn_c);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, bar, b_mn_c + 64 * j, b_k_c + k0);
+          }
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // a wait ran out: give the copies issued last time to land before this CTA's shared memory goes away
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(PAIR_BM, BN, 1, 1, p.a_mn, p.b_mn);
+      int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
+      bool ok = true;
+      const uint64_t a_desc0 = p.a_mn ? make_smem_desc_sw128(smem_u32(sA), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sA), 16, 1024);
+      const uint64_t b_desc0 = p.b_mn ? make_smem_desc_sw128(smem_u32(sB), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sB), 16, 1024);
+      const uint64_t a_step16 = (p.a_mn ? UK * 128 : UK * 2) >> 4, b_step16 = (p.b_mn ? UK * 128 : UK * 2) >> 4;
+      const bool rec = p.prof != nullptr && blockIdx.x == 0;
+      long long w_full = 0, w_acc = 0, t_issue = 0, n_kb = 0, c0 = 0, c1 = 0;
+      const long long t_begin = clock64();
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+        TileCoord t = decode_tile(p, prefix, tile, g_hint, PAIR_BM);
+        if (rec) c0 = clock64();
+        if (!mbar_wait_bounded(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, kTimeoutTmemEmpty)) break;
+        if (rec) { c1 = clock64(); w_acc += c1 - c0; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.k_iters; ++kb) {
+          if (rec) c0 = clock64();
+          if (!mbar_wait_bounded(&full[stage], phase, abort_flag, p.status, kTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          if (rec) { c1 = clock64(); w_full += c1 - c0; ++n_kb; }
+          tc_fence_after();
+          const uint64_t adesc = desc_advance(a_desc0, uint32_t(stage) * A_STAGE_BYTES);
+          const uint64_t bdesc = desc_advance(b_desc0, uint32_t(stage) * PAIR_B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) tc_mma_f16_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+          tc_commit_pair(&empty[stage], 3);  // both CTAs get their stage back once these MMAs have read it
+          if (rec) t_issue += clock64() - c1;
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (t.k_iters > 0) {
+          tc_commit_pair(&tfull[acc], 3);
+        } else {
+          mbar_arrive(&tfull[acc]);
+          mbar_arrive_cluster(mapa_shared(smem_u32(&tfull[acc]), 1));
+        }
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+      if (rec) {
+        p.prof[0] = clock64() - t_begin; p.prof[1] = w_full; p.prof[2] = w_acc; p.prof[3] = t_issue; p.prof[4] = n_kb;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0, acc_phase = 0, g_hint = 0;
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
+      TileCoord t = decode_tile(p, prefix, tile, g_hint, PAIR_BM);
+      t.m0 += int(rank) * BM;
+      if (!mbar_wait_bounded(&tfull[acc], acc_phase, abort_flag, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
+      epilogue_tile(p, t, taddr, row_in_tile);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // Neither CTA may leave (or give TMEM back) while its partner can still signal its barriers or read its shared memory.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -604,6 +828,9 @@ static long long* g_gemm_prof = nullptr;
 // Diagnostics: device buffer of 8 int64 that the next bf16 GEMM launches fill with cycle totals of CTA 0's MMA thread
 // (total, wait for a loaded stage, wait for a free accumulator, issue, k-blocks); null switches it off.
 ATS_API void ats_gemm_set_profile(long long* buf) { g_gemm_prof = buf; }
+// 1 (default): bf16 products with at least 256 rows run on CTA pairs (cta_group::2); 0: one CTA per 128 x 256 tile everywhere.
+static int g_gemm_pair = 1;
+ATS_API void ats_gemm_set_pair(int on) { g_gemm_pair = on; }
 
 // Generic entry point. The global 2-D extents of both operands are given explicitly (rows x cols, cols contiguous,
 // pitch ld elements); for a K-major operand cols is the reduction dimension, for an MN-major operand rows is.
@@ -745,6 +972,29 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     attr_set = true;
   }
   const int tn = epilogue == kSwiGLU ? (N + 127) / 128 : (N + BN - 1) / BN;
+  if (g_gemm_pair && !p.fp8 && !p.n_copy && M >= PAIR_BM) {
+    // two SMs per 256 x 256 tile
+    static int pair_clusters = -1;
+    if (pair_clusters < 0) {
+      cudaError_t ce = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+      if (ce != cudaSuccess) return int(ce);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(unsigned(num_sms() & ~1));
+      cfg.blockDim = dim3(PAIR_THREADS);
+      cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+      int n = 0;
+      ce = cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel, &cfg);
+      if (ce != cudaSuccess) return int(ce);
+      pair_clusters = n < 1 ? 1 : (n > num_sms() / 2 ? num_sms() / 2 : n);
+    }
+    const long long pair_tiles = (long long)groups * ((M + PAIR_BM - 1) / PAIR_BM) * tn;
+    int clusters = pair_clusters;
+    if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2 < 1 ? 1 : max_ctas / 2;
+    if (pair_tiles < clusters) clusters = int(pair_tiles);
+    if (clusters < 1) return 0;
+    gemm_bf16_pair_kernel<<<2 * clusters, PAIR_THREADS, PAIR_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+    return int(cudaGetLastError());
+  }
   long long upper = (long long)groups * ((M + BM - 1) / BM) * tn;
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
