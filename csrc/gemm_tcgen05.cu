@@ -122,7 +122,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   group_extents(p, g, mg, kg);
   // Rasterisation: panels of PANEL_N tile columns, rows fastest-varying across panels' columns, so that the ~148
   // tiles in flight touch about as many rows of A as of B (keeps both operands L2-resident per wave).
-  constexpr int PANEL_N = 8;
+#ifndef ATS_PANEL_N
+#define ATS_PANEL_N 8
+#endif
+  constexpr int PANEL_N = ATS_PANEL_N;
   const int tm = (mg + bm - 1) / bm;
   const int panel = local / (PANEL_N * tm);
   const int within = local - panel * PANEL_N * tm;
@@ -572,7 +575,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 //   tempty[a] leader's barrier: the epilogue warps of both CTAs arrive (the partner's through its cluster address)
 // ------------------------------------------------------------------------------------------------
 constexpr int PAIR_BM = 2 * BM;
-constexpr int PAIR_STAGES = 6;
+#ifndef ATS_PAIR_STAGES
+#define ATS_PAIR_STAGES 6
+#endif
+constexpr int PAIR_STAGES = ATS_PAIR_STAGES;
 constexpr int PAIR_B_STAGE_BYTES = (BN / 2) * BK * 2;
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
 constexpr int PAIR_THREADS = 192;
@@ -660,7 +666,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * PAIR_B_STAGE_BYTES;
-          const int k0 = seg * p.seg_stride + kpos * BK;
+          const int k0 = seg * p.seg_stride + kpos * (p.fp8 ? 2 * BK : BK);
           ++kpos;
           --seg_left;
           if (!p.a_mn) {
@@ -693,7 +699,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_idesc(PAIR_BM, BN, 1, 1, p.a_mn, p.b_mn);
+      const uint32_t idesc = p.fp8 ? make_idesc(PAIR_BM, BN, 0, 0, 0, 0) : make_idesc(PAIR_BM, BN, 1, 1, p.a_mn, p.b_mn);
       int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
       bool ok = true;
       const uint64_t a_desc0 = p.a_mn ? make_smem_desc_sw128(smem_u32(sA), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sA), 16, 1024);
@@ -719,8 +725,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           tc_fence_after();
           const uint64_t adesc = desc_advance(a_desc0, uint32_t(stage) * A_STAGE_BYTES);
           const uint64_t bdesc = desc_advance(b_desc0, uint32_t(stage) * PAIR_B_STAGE_BYTES);
+          if (p.fp8) {
 #pragma unroll
-          for (int k = 0; k < BK / UK; ++k) tc_mma_f16_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / UK; ++k) tc_mma_f8_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / UK; ++k) tc_mma_f16_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+          }
           tc_commit_pair(&empty[stage], 3);  // both CTAs get their stage back once these MMAs have read it
           if (rec) t_issue += clock64() - c1;
           if (++stage == PAIR_STAGES) {
@@ -972,7 +983,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     attr_set = true;
   }
   const int tn = epilogue == kSwiGLU ? (N + 127) / 128 : (N + BN - 1) / BN;
-  if (g_gemm_pair && !p.fp8 && !p.n_copy && M >= PAIR_BM) {
+  if (g_gemm_pair && !p.n_copy && M >= PAIR_BM) {
     // two SMs per 256 x 256 tile
     static int pair_clusters = -1;
     if (pair_clusters < 0) {
