@@ -142,6 +142,59 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
   return t;
 }
 
+// Copy warps of a launch that gathers B from its owners: two warps of every CTA pull the remote shards into the local staging
+// buffer, 4 KB per warp and step, in the order in which the tiles will need them; consecutive pieces of a chunk go to different
+// CTAs, so the ~300 copy warps of the grid keep more than a megabyte in flight on NVLink.  A chunk's counter grows by one per piece.
+__device__ __forceinline__ void copy_remote_shards(const GemmArgs& p, int copy_warp, int lane) {
+  const long long cps = p.shard_bytes / p.chunk_bytes;
+  const long long per_chunk = p.chunk_bytes / 4096;
+  const long long total = (long long)(p.n_chunks - cps) * per_chunk;
+  const int own_hi = p.first_chunk + int(cps);
+  for (long long i = copy_warp + 2LL * blockIdx.x; i < total; i += 2LL * gridDim.x) {
+    const long long ci = i / per_chunk, pi = i - ci * per_chunk;
+    const int chunk = int((own_hi + ci) % p.n_chunks);
+    const long long off = (chunk % cps) * p.chunk_bytes + pi * 4096 + lane * 16;
+    const uint8_t* src = static_cast<const uint8_t*>(p.b_src[chunk / cps]) + off;
+    uint8_t* dst = p.b_dst + (long long)chunk * p.chunk_bytes + pi * 4096 + lane * 16;
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const uint4*>(src + j * 512);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(dst + j * 512) = v[j];
+    __threadfence();
+    asm volatile("fence.proxy.async;" ::: "memory");  // the tiles are read through the async proxy (TMA)
+    __syncwarp();
+    if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.b_ready + chunk) : "memory");
+  }
+}
+
+// Chunks of gathered B that the calling producer thread already knows to be present (a contiguous range), and the bounded wait for
+// one more: returns false when the wait was abandoned.
+struct ChunkRange {
+  int lo = 0, hi = -1;
+};
+__device__ __forceinline__ bool wait_chunk(const GemmArgs& p, ChunkRange& r, int c, volatile int* abort_flag) {
+  if (c >= p.n_chunks) c = p.n_chunks - 1;
+  if (c >= r.lo && c <= r.hi) return true;
+  if (c >= p.first_chunk && c < p.first_chunk + int(p.shard_bytes / p.chunk_bytes)) return true;  // own shard: read in place
+  const uint64_t t0 = globaltimer_ns();
+  int v;
+  do {
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.b_ready + c) : "memory");
+    if (v >= p.epoch) break;  // epoch = pieces per chunk x number of calls so far
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > ATS_WAIT_BUDGET_NS) {
+      *abort_flag = 1;
+      if (p.status) atomicCAS(p.status, 0, int(kTimeoutPeerFlag));
+      return false;
+    }
+  } while (true);
+  if (c == r.hi + 1) r.hi = c;
+  else r.lo = r.hi = c;
+  asm volatile("fence.proxy.async;" ::: "memory");  // the data was written through the generic proxy of another CTA, TMA reads it
+  return true;
+}
+
 // Epilogue of one tile for one warp: `taddr` = TMEM address of the accumulator at this warp's lane quadrant, `row_in_tile` =
 // the accumulator row (TMEM lane) that this thread owns.
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord& t, uint32_t taddr, int row_in_tile) {
@@ -352,62 +405,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // Two warps of every CTA pull the remote shards of B into the local staging buffer, 4 KB per warp and step, in the
     // order in which the tiles will need them; consecutive pieces of a chunk go to different CTAs, so the ~300 copy
     // warps of the grid keep more than a megabyte in flight on NVLink.  A chunk's counter grows by one per piece.
-    if (p.n_copy) {
-      const long long cps = p.shard_bytes / p.chunk_bytes;
-      const long long per_chunk = p.chunk_bytes / 4096;
-      const long long total = (long long)(p.n_chunks - cps) * per_chunk;
-      const int own_hi = p.first_chunk + int(cps);
-      for (long long i = (warp - 6) + 2LL * blockIdx.x; i < total; i += 2LL * gridDim.x) {
-        const long long ci = i / per_chunk, pi = i - ci * per_chunk;
-        const int chunk = int((own_hi + ci) % p.n_chunks);
-        const long long off = (chunk % cps) * p.chunk_bytes + pi * 4096 + lane * 16;
-        const uint8_t* src = static_cast<const uint8_t*>(p.b_src[chunk / cps]) + off;
-        uint8_t* dst = p.b_dst + (long long)chunk * p.chunk_bytes + pi * 4096 + lane * 16;
-        uint4 v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const uint4*>(src + j * 512);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(dst + j * 512) = v[j];
-        __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");  // the tiles are read through the async proxy (TMA)
-        __syncwarp();
-        if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.b_ready + chunk) : "memory");
-      }
-    }
+    if (p.n_copy) copy_remote_shards(p, warp - 6, lane);
   } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0, phase = 0, g_hint = 0;
       uint32_t armed = 0, armed_phase = 0;
       bool ok = true;
-      int ready_lo = 0, ready_hi = -1;  // chunk range of gathered B known to be present
-      auto wait_chunk = [&](int c) -> bool {
-        if (c >= p.n_chunks) c = p.n_chunks - 1;
-        if (c >= ready_lo && c <= ready_hi) return true;
-        if (c >= p.first_chunk && c < p.first_chunk + int(p.shard_bytes / p.chunk_bytes)) return true;  // own shard: read in place
-        const uint64_t t0 = globaltimer_ns();
-        int v;
-        do {
-          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.b_ready + c) : "memory");
-          if (v >= p.epoch) break;  // epoch = pieces per chunk x number of calls so far
-          if (*abort_flag) return false;
-          if (globaltimer_ns() - t0 > ATS_WAIT_BUDGET_NS) {
-            *abort_flag = 1;
-            if (p.status) atomicCAS(p.status, 0, int(kTimeoutPeerFlag));
-            return false;
-          }
-        } while (true);
-        if (c == ready_hi + 1) ready_hi = c;
-        else ready_lo = ready_hi = c;
-        asm volatile("fence.proxy.async;" ::: "memory");  // the data was written through the async proxy of another CTA
-        return true;
-      };
+      ChunkRange ready;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint);
         if (p.n_copy) {
           const int r0 = t.n0, r1 = p.epilogue == kSwiGLU ? t.n0 + p.up_offset : t.n0 + 128;
-          ok = wait_chunk(r0 / p.ready_rows) && wait_chunk((r0 + 127) / p.ready_rows) && wait_chunk(r1 / p.ready_rows) &&
-               wait_chunk((r1 + 127) / p.ready_rows);
+          ok = wait_chunk(p, ready, r0 / p.ready_rows, abort_flag) && wait_chunk(p, ready, (r0 + 127) / p.ready_rows, abort_flag) &&
+               wait_chunk(p, ready, r1 / p.ready_rows, abort_flag) && wait_chunk(p, ready, (r1 + 127) / p.ready_rows, abort_flag);
           if (!ok) break;
         }
         const int a_mn_c = t.m0 + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
@@ -584,8 +595,9 @@ constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_STAGE_BYTES;
 constexpr int PAIR_THREADS = 192;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + (MAX_GROUPS + 1) * 4;
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + 64, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_b_own, const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -625,6 +637,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     prefix[p.groups] = acc;
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if (p.n_copy) tma_prefetch_desc(&map_b_own);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -639,11 +652,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int first_tile = int(cluster_id_x());
   const int tile_step = int(cluster_count_x());
 
-  if (warp == 0) {
+  if (warp >= 6) {
+    // ------------------------------------------------------------------ copy warps (launches that gather B from its owners)
+    if (p.n_copy) copy_remote_shards(p, warp - 6, lane);
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0, phase = 0, g_hint = 0;
       bool ok = true;
+      ChunkRange ready;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint, PAIR_BM);
         const int a_mn_c = t.m0 + int(rank) * BM + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
@@ -651,6 +668,18 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int b_k_c = p.b_gs_k * gb;
         // this CTA's half of the B tile: rows n0 .. n0+127 for the leader, the next 128 (SwiGLU: the "up" rows) for the partner
         const int b_mn_c = t.n0 + p.b_gs_mn * gb + (rank ? (p.epilogue == kSwiGLU ? p.up_offset : 128) : 0);
+        const CUtensorMap* bmap = &map_b;
+        int b_row = b_mn_c;
+        if (p.n_copy) {
+          // gathered B: rows of this rank's own shard are read in place, the others from the staging buffer once they are there
+          ok = wait_chunk(p, ready, b_mn_c / p.ready_rows, abort_flag) && wait_chunk(p, ready, (b_mn_c + 127) / p.ready_rows, abort_flag);
+          if (!ok) break;
+          const int o = b_mn_c - p.own_row0;
+          if (o >= 0 && o < p.own_rows) {
+            bmap = &map_b_own;
+            b_row = o;
+          }
+        }
         int seg = 0, seg_left = seg_iters_of(p, t.g, 0, t.k_iters), kpos = 0;
         for (int kb = 0; kb < t.k_iters; ++kb) {
           while (seg_left == 0) {
@@ -677,7 +706,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               tma_load_2d_pair(a_dst + j * (BK * 128), &map_a, bar, a_mn_c + 64 * j, a_k_c + k0);
           }
           if (!p.b_mn) {
-            tma_load_2d_pair(b_dst, &map_b, bar, b_k_c + k0, b_mn_c);
+            tma_load_2d_pair(b_dst, bmap, bar, b_k_c + k0, b_row);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 128; ++j)
@@ -983,7 +1012,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     attr_set = true;
   }
   const int tn = epilogue == kSwiGLU ? (N + 127) / 128 : (N + BN - 1) / BN;
-  if (g_gemm_pair && !p.n_copy && M >= PAIR_BM) {
+  if (g_gemm_pair && M >= PAIR_BM) {
     // two SMs per 256 x 256 tile
     static int pair_clusters = -1;
     if (pair_clusters < 0) {
@@ -1000,10 +1029,16 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     }
     const long long pair_tiles = (long long)groups * ((M + PAIR_BM - 1) / PAIR_BM) * tn;
     int clusters = pair_clusters;
-    if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2 < 1 ? 1 : max_ctas / 2;
-    if (pair_tiles < clusters) clusters = int(pair_tiles);
+    if (p.n_copy > 0) {
+      // producers wait on the copy warps of other CTAs of this launch: keep the whole grid resident
+    } else {
+      if (max_ctas > 0 && max_ctas / 2 < clusters) clusters = max_ctas / 2 < 1 ? 1 : max_ctas / 2;
+      if (pair_tiles < clusters) clusters = int(pair_tiles);
+    }
     if (clusters < 1) return 0;
-    gemm_bf16_pair_kernel<<<2 * clusters, PAIR_THREADS, PAIR_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(ma, mb, p);
+    // the two copy warps exist only in launches that gather B from peers
+    gemm_bf16_pair_kernel<<<2 * clusters, p.n_copy ? PAIR_THREADS + 64 : PAIR_THREADS, PAIR_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        ma, mb, mb_own ? *mb_own : mb, p);
     return int(cudaGetLastError());
   }
   long long upper = (long long)groups * ((M + BM - 1) / BM) * tn;
