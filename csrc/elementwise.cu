@@ -4,6 +4,7 @@
 // Counterparts in the reference: core/transformer_ops.cu:61-315 (fp32 CUDA-core RMSNorm / RoPE / SwiGLU) and
 // the eager PyTorch paths in core/model.py:228-304, 470-524, 1082-1088, 1924-1931.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace ats {
 
@@ -146,6 +147,89 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       reinterpret_cast<float4*>(out)[2 * v + 1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
     }
   }
+}
+
+// Warp-per-row form of the RMSNorm backward for rows of up to 32 * 8 * NV elements: a warp keeps its whole row (x, dy and
+// the residual-branch gradient) in registers as packed bf16, reduces with shuffles only and never meets a CTA barrier
+// inside the row loop, so every warp keeps 3 * NV 16-byte loads in flight.  The weight-gradient partials of the four warps
+// of a CTA are folded in shared memory (fixed order) into one partial row per CTA.
+template <int NV>
+__global__ void __launch_bounds__(128, 2)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                        const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw_partial, int rows, int cols) {
+  extern __shared__ float fold[];  // [4][cols] fp32, then the weight row as bf16 (zero-padded to 256 * NV elements)
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int nvec = cols >> 3;
+  const float inv_cols = 1.f / float(cols);
+  uint4* wsm = reinterpret_cast<uint4*>(fold + 4 * cols);
+  for (int v = threadIdx.x; v < 32 * NV; v += 128) wsm[v] = v < nvec ? reinterpret_cast<const uint4*>(w)[v] : make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  float dwacc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+  }
+  for (long long row = blockIdx.x * 4 + wib; row < rows; row += 4LL * gridDim.x) {
+    const float r = rstd[row];
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + row * cols);
+    const uint4* cr = dres_in ? reinterpret_cast<const uint4*>(dres_in + row * cols) : nullptr;
+    uint4 a[NV], b[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      const bool in = v < nvec;
+      a[i] = in ? xr[v] : make_uint4(0, 0, 0, 0);
+      b[i] = in ? dr[v] : make_uint4(0, 0, 0, 0);
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const uint4 wq = wsm[lane + 32 * i];
+      const uint32_t au[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, bu[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+      const uint32_t wu[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 xv = unpack_bf16x2(au[e]), dv = unpack_bf16x2(bu[e]), ww = unpack_bf16x2(wu[e]);
+        const float xh0 = xv.x * r, xh1 = xv.y * r;
+        dot += dv.x * ww.x * xh0 + dv.y * ww.y * xh1;
+        dwacc[i][2 * e] += dv.x * xh0;
+        dwacc[i][2 * e + 1] += dv.y * xh1;
+      }
+    }
+    dot = warp_sum(dot) * inv_cols;
+    uint4* outr = reinterpret_cast<uint4*>(dx + row * cols);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      const uint4 wq = wsm[v];
+      const uint4 cq = (cr && v < nvec) ? cr[v] : make_uint4(0, 0, 0, 0);
+      const uint32_t au[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, bu[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+      const uint32_t wu[4] = {wq.x, wq.y, wq.z, wq.w}, cu[4] = {cq.x, cq.y, cq.z, cq.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 xv = unpack_bf16x2(au[e]), dv = unpack_bf16x2(bu[e]), ww = unpack_bf16x2(wu[e]), cc = unpack_bf16x2(cu[e]);
+        o[e] = pack_bf16x2(r * (dv.x * ww.x - xv.x * r * dot) + cc.x, r * (dv.y * ww.y - xv.y * r * dot) + cc.y);
+      }
+      if (v < nvec) outr[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float* f = fold + wib * cols + 8 * v;
+      reinterpret_cast<float4*>(f)[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      reinterpret_cast<float4*>(f)[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+  __syncthreads();
+  float* out = dw_partial + (long long)blockIdx.x * cols;
+  for (int col = threadIdx.x; col < cols; col += 128) out[col] = (fold[col] + fold[cols + col]) + (fold[2 * cols + col] + fold[3 * cols + col]);
 }
 
 // dw[c] (+)= sum_b partial[b][c]; output bf16 or fp32.  One CTA per 32 columns: 8 row lanes x 32 columns read the partials
@@ -371,9 +455,9 @@ ATS_API int ats_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
 }
 
 // dw_partial: fp32 scratch of nblocks*cols; dw written as bf16 (dw_bf16) and/or fp32 (dw_f32).
-ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres_in, void* dx,
-                            float* dw_partial, int nblocks, void* dw_bf16, float* dw_f32, int accumulate, long long rows,
-                            int cols, void* stream) {
+static int rmsnorm_bwd_launch(const void* x, const void* w, const void* dy, const float* rstd, const void* dres_in, void* dx,
+                              float* dw_partial, int nblocks, void* dw_bf16, float* dw_f32, int accumulate, long long rows,
+                              int cols, void* stream, bool warp_rows) {
   if (cols & 7) return 1003;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   auto X = static_cast<const __nv_bfloat16*>(x);
@@ -381,6 +465,19 @@ ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
   auto DY = static_cast<const __nv_bfloat16*>(dy);
   auto DR = static_cast<const __nv_bfloat16*>(dres_in);
   auto DX = static_cast<__nv_bfloat16*>(dx);
+  static const bool warp_rows_on = [] {
+    const char* e = getenv("ATS_NORM_WARP_ROWS");  // "0" keeps the CTA-per-row kernels everywhere (for comparisons)
+    return !(e && e[0] == '0');
+  }();
+  if (warp_rows && warp_rows_on && cols <= 2048 && rows >= 1024 && nblocks >= 1) {
+    // many rows of moderate width: one warp per row, two CTAs of four warps per SM
+    const int nb = nblocks < 296 ? nblocks : 296;
+    const size_t sm = size_t(4) * cols * sizeof(float) + (cols <= 1024 ? 4 : 8) * 512;
+    if (cols <= 1024) rmsnorm_bwd_warp_kernel<4><<<nb, 128, sm, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+    else rmsnorm_bwd_warp_kernel<8><<<nb, 128, sm, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
+    colsum_partial_kernel<<<(cols + 31) / 32, 256, 0, s>>>(dw_partial, nb, cols, static_cast<__nv_bfloat16*>(dw_bf16), dw_f32, accumulate);
+    return int(cudaGetLastError());
+  }
   if (cols <= 128 * 8) rmsnorm_bwd_kernel<128, 1><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else if (cols <= 128 * 16) rmsnorm_bwd_kernel<128, 2><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
   else if (cols <= 128 * 32) rmsnorm_bwd_kernel<128><<<nblocks, 128, 0, s>>>(X, W, DY, rstd, DR, DX, dw_partial, (int)rows, cols);
@@ -390,6 +487,12 @@ ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const 
   colsum_partial_kernel<<<(cols + 31) / 32, 256, 0, s>>>(dw_partial, nblocks, cols, static_cast<__nv_bfloat16*>(dw_bf16),
                                                           dw_f32, accumulate);
   return int(cudaGetLastError());
+}
+
+ATS_API int ats_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres_in, void* dx,
+                            float* dw_partial, int nblocks, void* dw_bf16, float* dw_f32, int accumulate, long long rows,
+                            int cols, void* stream) {
+  return rmsnorm_bwd_launch(x, w, dy, rstd, dres_in, dx, dw_partial, nblocks, dw_bf16, dw_f32, accumulate, rows, cols, stream, true);
 }
 
 ATS_API int ats_colsum_partial(const float* partial, int nblocks, int cols, void* out_bf16, float* out_f32, int accumulate,
@@ -509,7 +612,7 @@ ATS_API int ats_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy
   const int nblocks = rows < kNoAllocMaxBlocks ? int(rows) : kNoAllocMaxBlocks;
   // Every partial that the reduction reads (nblocks rows of cols floats) is written by the first kernel of this
   // same call, so nothing has to be cleared even though the array still holds the previous call's values.
-  return ats_rmsnorm_bwd(x, w, dy, rstd, dres_in, dx, partial, nblocks, dw_bf16, dw_f32, accumulate, rows, cols, stream);
+  return rmsnorm_bwd_launch(x, w, dy, rstd, dres_in, dx, partial, nblocks, dw_bf16, dw_f32, accumulate, rows, cols, stream, false);
 }
 
 ATS_API void ats_rmsnorm_bwd_noalloc_limits(int* max_cols, long long* scratch_bytes) {
