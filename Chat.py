@@ -53,7 +53,7 @@ def load_checkpoint_smart(path: str):
 
 
 class ChatInterface:
-    def __init__(self, checkpoint: str, device: str = "auto", mode: str = "standard"):
+    def __init__(self, checkpoint: str, device: str = "auto", mode: str = "standard", quantize: str = None):
         self.device = torch.device("cuda" if (device == "auto" and torch.cuda.is_available()) else ("cpu" if device == "auto" else device))
         sd, cfg = load_checkpoint_smart(checkpoint)
         cfg.gradient_checkpointing = False
@@ -61,6 +61,12 @@ class ChatInterface:
         self.model = DeepSeekTransformer(cfg)
         self.model.load_state_dict({k: v for k, v in sd.items()}, strict=False)
         self.model = self.model.to(self.device, dtype).eval()
+        if quantize:
+            if self.device.type != "cuda":
+                raise SystemExit("--quantize needs a GPU: the fp8 path runs on the tensor-core GEMM")
+            from types import SimpleNamespace
+            from adaptivetrainingsystem_b200.training import QuantizationManager
+            QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=8)).quantize_model(self.model)
         self.tokenizer = ConversationTokenizer()
         self.engine = GenerationEngine(self.model, self.tokenizer)
         self.params = SamplingParams.from_mode(mode, max_new_tokens=min(256, max(cfg.seq_length // 2, 1)),
@@ -121,8 +127,9 @@ if __name__ == "__main__":
     ap.add_argument("--mode", default="standard", choices=list(GENERATION_MODES))
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--device", default="auto")
+    ap.add_argument("--quantize", default=None, choices=["fp8"], help="post-training quantisation of the projection weights")
     a = ap.parse_args()
-    chat = ChatInterface(a.checkpoint, a.device, a.mode)
+    chat = ChatInterface(a.checkpoint, a.device, a.mode, a.quantize)
     if a.prompt:
         print(chat.respond(a.prompt))
     else:

@@ -42,6 +42,10 @@ def _fn():
         lib.ats_gemm_set_pair.argtypes = [_c_int]
         if os.environ.get("ATS_GEMM_PAIR") is not None:
             lib.ats_gemm_set_pair(int(os.environ["ATS_GEMM_PAIR"]))
+        lib.ats_gemm_set_wide_stores.restype = None
+        lib.ats_gemm_set_wide_stores.argtypes = [_c_int]
+        if os.environ.get("ATS_GEMM_WIDE_STORES") is not None:
+            lib.ats_gemm_set_wide_stores(int(os.environ["ATS_GEMM_WIDE_STORES"]))
         _configured = True
     return lib.ats_gemm_bf16
 

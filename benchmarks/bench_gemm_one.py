@@ -19,7 +19,8 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--mode", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--mode", default="nt", choices=["nt", "nn", "tn", "swiglu"],
+                    help="swiglu: n = 2 x intermediate rows [gate; up], SwiGLU epilogue writing h and the pre-activations")
     ap.add_argument("--phases", action="store_true", help="cycle totals of one CTA's MMA thread")
     a = ap.parse_args()
     dev = torch.device("cuda")
@@ -34,6 +35,13 @@ def main():
     elif a.mode == "nn":
         wt = w.t().contiguous()
         ours, lib = (lambda: G.gemm_nn(x, wt, out=out)), (lambda: torch.matmul(x, wt, out=out))
+    elif a.mode == "swiglu":
+        h = torch.empty(a.m, a.n // 2, device=dev, dtype=torch.bfloat16)
+
+        def lib_swiglu():
+            torch.matmul(x, w.t(), out=out)
+            torch.mul(torch.nn.functional.silu(out[:, : a.n // 2]), out[:, a.n // 2:], out=h)
+        ours, lib = (lambda: G.gemm_nt_swiglu(x, w, out=h, pre_act=out)), lib_swiglu
     else:
         xt, wt = x.t().contiguous(), w.t().contiguous()
         ours, lib = (lambda: G.gemm_tn(xt, wt, out=out)), (lambda: torch.matmul(xt.t(), wt, out=out))

@@ -79,6 +79,7 @@ struct GemmArgs {
   __nv_bfloat16* out2;
   int ldout2;
   long long out2_gs;
+  int wide;                // D (and aux) rows are 32-byte aligned at every 16th column: the bf16 epilogues store whole sectors
   int fp8;
   const float* row_scale;  // [groups * rs_gs] or null
   const float* col_scale;  // [weights * cs_gs] or null
@@ -214,31 +215,64 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
       tmem_ld_32x32(taddr + 128 + c * 32, ur);
       tmem_ld_wait();
       if (row_ok) {
+        // eight columns: h, gate and up as four packed bf16 pairs each
+        auto piece = [&](int v, int col, uint4& hq, uint4& gq4, uint4& uq4) {
+          uint32_t h[4], gg[4], uu[4];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const int col = t.n0 + c * 32 + v * 8;
-          if (col < p.N) {
-            uint32_t h[4], gg[4], uu[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * rs, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * rs;
-              float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * rs, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * rs;
-              if (cs) {
-                g0 *= cs[col + 2 * e];
-                g1 *= cs[col + 2 * e + 1];
-                u0 *= cs[p.up_offset + col + 2 * e];
-                u1 *= cs[p.up_offset + col + 2 * e + 1];
-              }
-              gg[e] = pack_bf16x2(g0, g1);
-              uu[e] = pack_bf16x2(u0, u1);
-              // activation on the bf16-rounded values so a separate SwiGLU pass gives identical bits
-              float2 gq = unpack_bf16x2(gg[e]), uq = unpack_bf16x2(uu[e]);
-              h[e] = pack_bf16x2(silu_f(gq.x) * uq.x, silu_f(gq.y) * uq.y);
+          for (int e = 0; e < 4; ++e) {
+            float g0 = __uint_as_float(gr[v * 8 + 2 * e]) * rs, g1 = __uint_as_float(gr[v * 8 + 2 * e + 1]) * rs;
+            float u0 = __uint_as_float(ur[v * 8 + 2 * e]) * rs, u1 = __uint_as_float(ur[v * 8 + 2 * e + 1]) * rs;
+            if (cs) {
+              g0 *= cs[col + 2 * e];
+              g1 *= cs[col + 2 * e + 1];
+              u0 *= cs[p.up_offset + col + 2 * e];
+              u1 *= cs[p.up_offset + col + 2 * e + 1];
             }
-            *reinterpret_cast<uint4*>(drow + col) = make_uint4(h[0], h[1], h[2], h[3]);
-            if (arow) {
-              *reinterpret_cast<uint4*>(arow + col) = make_uint4(gg[0], gg[1], gg[2], gg[3]);
-              *reinterpret_cast<uint4*>(arow + p.up_offset + col) = make_uint4(uu[0], uu[1], uu[2], uu[3]);
+            gg[e] = pack_bf16x2(g0, g1);
+            uu[e] = pack_bf16x2(u0, u1);
+            // activation on the bf16-rounded values so a separate SwiGLU pass gives identical bits
+            float2 gq = unpack_bf16x2(gg[e]), uq = unpack_bf16x2(uu[e]);
+            h[e] = pack_bf16x2(silu_f(gq.x) * uq.x, silu_f(gq.y) * uq.y);
+          }
+          hq = make_uint4(h[0], h[1], h[2], h[3]);
+          gq4 = make_uint4(gg[0], gg[1], gg[2], gg[3]);
+          uq4 = make_uint4(uu[0], uu[1], uu[2], uu[3]);
+        };
+        if (p.wide) {
+#pragma unroll
+          for (int v = 0; v < 4; v += 2) {
+            const int col = t.n0 + c * 32 + v * 8;
+            if (col + 16 <= p.N) {
+              uint4 h0, g0, u0, h1, g1, u1;
+              piece(v, col, h0, g0, u0);
+              piece(v + 1, col + 8, h1, g1, u1);
+              st_global_32B(drow + col, h0, h1);
+              if (arow) {
+                st_global_32B(arow + col, g0, g1);
+                st_global_32B(arow + p.up_offset + col, u0, u1);
+              }
+            } else if (col < p.N) {
+              uint4 h0, g0, u0;
+              piece(v, col, h0, g0, u0);
+              *reinterpret_cast<uint4*>(drow + col) = h0;
+              if (arow) {
+                *reinterpret_cast<uint4*>(arow + col) = g0;
+                *reinterpret_cast<uint4*>(arow + p.up_offset + col) = u0;
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c * 32 + v * 8;
+            if (col < p.N) {
+              uint4 h0, g0, u0;
+              piece(v, col, h0, g0, u0);
+              *reinterpret_cast<uint4*>(drow + col) = h0;
+              if (arow) {
+                *reinterpret_cast<uint4*>(arow + col) = g0;
+                *reinterpret_cast<uint4*>(arow + p.up_offset + col) = u0;
+              }
             }
           }
         }
@@ -317,26 +351,35 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
         __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
         const __nv_bfloat16* crow =
             p.epilogue == kAddC ? p.C + p.c_gs * t.g + (long long)row * p.ldc : nullptr;
+        auto piece = [&](int v, int col) -> uint4 {
+          float f[8];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const int col = colbase + v * 8;
-          if (col < p.N) {
-            float f[8];
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * rs;
+          if (cs) {
+            const float4 c0 = *reinterpret_cast<const float4*>(cs + col), c1 = *reinterpret_cast<const float4*>(cs + col + 4);
+            f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
+            f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
+          }
+          if (crow) {
+            uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
+            float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
+            f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
+            f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
+          }
+          return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        };
+        if (p.wide) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * rs;
-            if (cs) {
-              const float4 c0 = *reinterpret_cast<const float4*>(cs + col), c1 = *reinterpret_cast<const float4*>(cs + col + 4);
-              f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
-              f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
-            }
-            if (crow) {
-              uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
-              float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
-              f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
-              f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
-            }
-            *reinterpret_cast<uint4*>(drow + col) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
-                                                               pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          for (int v = 0; v < 4; v += 2) {
+            const int col = colbase + v * 8;
+            if (col + 16 <= p.N) st_global_32B(drow + col, piece(v, col), piece(v + 1, col + 8));
+            else if (col < p.N) *reinterpret_cast<uint4*>(drow + col) = piece(v, col);
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = colbase + v * 8;
+            if (col < p.N) *reinterpret_cast<uint4*>(drow + col) = piece(v, col);
           }
         }
       }
@@ -870,6 +913,9 @@ static long long* g_gemm_prof = nullptr;
 ATS_API void ats_gemm_set_profile(long long* buf) { g_gemm_prof = buf; }
 // 1 (default): bf16 products with at least 256 rows run on CTA pairs (cta_group::2); 0: one CTA per 128 x 256 tile everywhere.
 static int g_gemm_pair = 1;
+// 1 (default): bf16 epilogues write 32 bytes per store where the output layout allows it; 0: 16-byte stores everywhere.
+static int g_gemm_wide = 1;
+ATS_API void ats_gemm_set_wide_stores(int on) { g_gemm_wide = on; }
 ATS_API void ats_gemm_set_pair(int on) { g_gemm_pair = on; }
 
 // Generic entry point. The global 2-D extents of both operands are given explicitly (rows x cols, cols contiguous,
@@ -1003,8 +1049,20 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   return launch_gemm(ma, mb, p, epilogue, 1, M, N, 0, stream, &mb_own);
 }
 
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
+// Whole-sector stores need every row of D (and of aux for SwiGLU) to start 32-byte aligned at every 16th column.
+static int sector_aligned_outputs(const GemmArgs& p) {
+  if (!g_gemm_wide || p.d_table) return 0;
+  if (p.epilogue == kF32 || p.epilogue == kSwiGLUBwd) return 0;
+  auto ok = [](const void* ptr, long long ld, long long gs) { return (reinterpret_cast<uintptr_t>(ptr) & 31) == 0 && (ld & 15) == 0 && (gs & 15) == 0; };
+  if (!ok(p.D, p.ldd, p.d_gs)) return 0;
+  if (p.epilogue == kSwiGLU && p.aux && (!ok(p.aux, p.ldaux, p.aux_gs) || (p.up_offset & 15))) return 0;
+  return 1;
+}
+
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p_in, int epilogue, int groups, int M, int N,
                        int max_ctas, void* stream, const CUtensorMap* mb_own) {
+  GemmArgs p = p_in;
+  p.wide = sector_aligned_outputs(p);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);

@@ -554,3 +554,34 @@ def test_fused_router_matches_torch_ops(temperature):
     # reproducible bits
     idx2, w2, aux2 = M.route_and_balance(logits.detach(), k, temperature, weight)
     assert torch.equal(aux2, aux.detach()) and torch.equal(w2, w.detach())
+
+
+def test_quantization_manager_fp8_inference_close_to_bf16():
+    """Post-training fp8 quantisation through the manager: logits of a small dense model stay close to the bf16 ones."""
+    from types import SimpleNamespace
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.ops import fp8
+    from adaptivetrainingsystem_b200.training import QuantizationManager
+    torch.manual_seed(21)
+    cfg = ModelConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=512, seq_length=128,
+                      use_moe=False)
+    model = DeepSeekTransformer(cfg).to("cuda", torch.bfloat16)
+    ids = torch.randint(0, 512, (2, 128), device="cuda")
+    with torch.no_grad():
+        ref = model(ids)
+        ref = ref[0] if isinstance(ref, tuple) else ref
+        qm = QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=8))
+        try:
+            qm.quantize_model(model)
+            st = qm.status()
+            assert st["applied"] and st["method"] == "fp8" and st["tensors"] >= 2 * 4
+            out = model(ids)
+            out = out[0] if isinstance(out, tuple) else out
+        finally:
+            fp8.set_enabled(False)
+            fp8.clear_weight_cache()
+    cos = torch.nn.functional.cosine_similarity(out.float().flatten(), ref.float().flatten(), dim=0).item()
+    assert cos > 0.995, cos
+    with pytest.raises(RuntimeError):
+        QuantizationManager(SimpleNamespace(quantization_method="gptq", quantization_bits=4)).quantize_model(model)
