@@ -440,10 +440,7 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, w2.shape[0])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dh = G.gemm_nn(dy2, w2)
-        dgu = torch.empty_like(pre)
-        h = torch.empty(pre.shape[0], inter, dtype=pre.dtype, device=pre.device)
-        _CK(_L().ats_swiglu_bwd(_P(pre), _P(dh), _P(dgu), _P(h), pre.shape[0], inter, _S(pre.device)), "swiglu_bwd")
+        dgu, h = G.gemm_nn_swiglu_bwd(dy2, w2, pre)  # dh = dy · w2 goes through the SwiGLU backward in the GEMM epilogue
         dw2 = _deliver_grad(w2, lambda out, acc: G.gemm_tn(dy2, h, out=out, accumulate=acc))
         dw1 = _deliver_grad(w1, lambda out, acc: G.gemm_tn(dgu, x2, out=out, accumulate=acc))
         dx = G.gemm_nn(dgu, w1).view(ctx.shape)

@@ -12,6 +12,7 @@ multiple of 128 rows so GEMM tiles are whole); slots are ranked in token order, 
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -20,6 +21,11 @@ import torch.nn.functional as F
 from . import _lib
 from . import gemm as G
 from .functional import _L, _P, _S, _CK, _deliver_grad
+
+
+# SwiGLU backward of the expert FFN inside the epilogue of the dh GEMM (default; measured 1 % faster per step once the epilogue
+# reads and writes whole 32-byte sectors) or, with ATS_SWIGLU_BWD_FUSED=0, as a separate streaming kernel after the GEMM.
+FUSED_SWIGLU_BWD = os.environ.get("ATS_SWIGLU_BWD_FUSED", "1") == "1"
 
 
 def expert_capacity(tokens: int, num_experts: int, top_k: int, capacity_factor: float, drop_tokens: bool = True,
@@ -296,16 +302,13 @@ class _MoEFFNFn(torch.autograd.Function):
         dout = dout.contiguous()
         dw_topk = slot_dot(ye, topk_idx, slot_pos, dout) if ctx.needs_input_grad[2] else None
         dye = dispatch(dout, topk_idx, slot_pos, counts, E, C, slot_scale=topk_w.contiguous().float())
-        # dh = dye · w2, then the SwiGLU backward as its own bandwidth-bound launch: the same math in the GEMM epilogue
-        # (``G.grouped_nn_swiglu_bwd``) measured 2.5 % slower per step, its four epilogue warps cannot stream the saved
-        # pre-activations as fast as a full grid does
-        dh = G.grouped_nn(dye, w2, counts)
-        if _lib.use_cuda_kernels(pre):
+        if FUSED_SWIGLU_BWD or not _lib.use_cuda_kernels(pre):
+            dgu, h = G.grouped_nn_swiglu_bwd(dye, w2, counts, pre)  # dh = dye · w2 never leaves the GEMM: its epilogue does the SwiGLU backward
+        else:
+            dh = G.grouped_nn(dye, w2, counts)
             dgu = torch.empty_like(pre)
             h = torch.empty(E, C, inter, dtype=pre.dtype, device=pre.device)
             _CK(_L().ats_swiglu_bwd_grouped(_P(pre), _P(dh), _P(dgu), _P(h), E, C, _P(counts), inter, _S(pre.device)), "swiglu_bwd")
-        else:
-            dgu, h = G.swiglu_bwd_reference(pre, dh)
         dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(dye, h, counts, out=out, accumulate=acc))
         dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, xe, counts, out=out, accumulate=acc))
         dxe = G.grouped_nn(dgu, w1, counts)

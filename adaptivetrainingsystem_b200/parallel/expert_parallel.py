@@ -186,18 +186,14 @@ class _EPMoEFn(torch.autograd.Function):
         else:
             send = M.dispatch(dout, topk_idx, slot_pos, counts, E, C, slot_scale=scale)
             comm.exchange_to_owners(send, buf.recv_g)
-        dh = G.grouped_nn(buf.recv_g, w2, buf.counts, b_div=W)
-        if _lib.use_cuda_kernels(pre):
+        if M.FUSED_SWIGLU_BWD or not _lib.use_cuda_kernels(pre):
+            dgu, h = G.grouped_nn_swiglu_bwd(buf.recv_g, w2, buf.counts, pre, b_div=W)  # dh and the SwiGLU backward in one kernel
+        else:
+            dh = G.grouped_nn(buf.recv_g, w2, buf.counts, b_div=W)
             dgu = torch.empty_like(pre)
             h = torch.empty(buf.El * W, C, inter, dtype=pre.dtype, device=pre.device)
             _CK(_L().ats_swiglu_bwd_grouped(_P(pre), _P(dh), _P(dgu), _P(h), buf.El * W, C, _P(buf.counts), inter, _S(pre.device)),
                 "swiglu_bwd")
-        else:
-            g, u = pre.float().chunk(2, dim=-1)
-            s = torch.sigmoid(g)
-            dhf = dh.float()
-            dgu = torch.cat([dhf * u * (s + g * s * (1 - s)), dhf * g * s], dim=-1).to(pre.dtype)
-            h = (g * s * u).to(pre.dtype)
         dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(buf.recv_g, h, buf.counts, out=out, accumulate=acc, k_segs=W))
         dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, buf.recv_x, buf.counts, out=out, accumulate=acc, k_segs=W))
         if comm.fused and comm.pull_results:

@@ -319,6 +319,13 @@ __device__ __forceinline__ void st_global_32B(void* ptr, uint4 lo, uint4 hi) {
                "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
                : "memory");
 }
+// One 32-byte load from one thread; the address must be 32-byte aligned.
+__device__ __forceinline__ void ld_global_32B(const void* ptr, uint4& lo, uint4& hi) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+               : "l"(ptr)
+               : "memory");
+}
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

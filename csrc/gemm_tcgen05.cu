@@ -284,6 +284,20 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
     __nv_bfloat16* hrow = p.out2 ? p.out2 + p.out2_gs * t.g + (long long)row * p.ldout2 : nullptr;
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
+      uint4 g[4], u[4];  // the chunk's 32 gate and 32 up values, requested before the accumulator is read
+      if (p.wide && row_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; v += 2) {
+          const int col = t.n0 + c * 32 + v * 8;
+          if (col + 16 <= p.N) {
+            ld_global_32B(arow + col, g[v], g[v + 1]);
+            ld_global_32B(arow + p.up_offset + col, u[v], u[v + 1]);
+          } else if (col < p.N) {
+            g[v] = *reinterpret_cast<const uint4*>(arow + col);
+            u[v] = *reinterpret_cast<const uint4*>(arow + p.up_offset + col);
+          }
+        }
+      }
       uint32_t r[32];
       if (have_acc) {
         tmem_ld_32x32(taddr + c * 32, r);
@@ -293,28 +307,54 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
         for (int i = 0; i < 32; ++i) r[i] = 0;
       }
       if (!row_ok) continue;
+      // eight columns from the saved gate / up values and the accumulator
+      auto piece = [&](int v, const uint4& gq, const uint4& uq, uint4& og4, uint4& ou4, uint4& oh4) {
+        const uint32_t gg[4] = {gq.x, gq.y, gq.z, gq.w}, uu[4] = {uq.x, uq.y, uq.z, uq.w};
+        uint32_t og[4], ou[4], oh[4];
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        const int col = t.n0 + c * 32 + v * 8;
-        if (col < p.N) {
-          const uint4 gq = *reinterpret_cast<const uint4*>(arow + col);
-          const uint4 uq = *reinterpret_cast<const uint4*>(arow + p.up_offset + col);
-          const uint32_t gg[4] = {gq.x, gq.y, gq.z, gq.w}, uu[4] = {uq.x, uq.y, uq.z, uq.w};
-          uint32_t og[4], ou[4], oh[4];
+        for (int e = 0; e < 4; ++e) {
+          // dh rounded to bf16 first: bit-identical to writing dh and running the separate backward kernel
+          const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[v * 8 + 2 * e]) * rs, __uint_as_float(r[v * 8 + 2 * e + 1]) * rs));
+          const float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]);
+          const float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
+          const float si0 = a.x * s0, si1 = a.y * s1;
+          og[e] = pack_bf16x2(d.x * b.x * (s0 + si0 * (1.f - s0)), d.y * b.y * (s1 + si1 * (1.f - s1)));
+          ou[e] = pack_bf16x2(d.x * si0, d.y * si1);
+          oh[e] = pack_bf16x2(si0 * b.x, si1 * b.y);
+        }
+        og4 = make_uint4(og[0], og[1], og[2], og[3]);
+        ou4 = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+        oh4 = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+      };
+      if (p.wide) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            // dh rounded to bf16 first: bit-identical to writing dh and running the separate backward kernel
-            const float2 d = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[v * 8 + 2 * e]) * rs, __uint_as_float(r[v * 8 + 2 * e + 1]) * rs));
-            const float2 a = unpack_bf16x2(gg[e]), b = unpack_bf16x2(uu[e]);
-            const float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
-            const float si0 = a.x * s0, si1 = a.y * s1;
-            og[e] = pack_bf16x2(d.x * b.x * (s0 + si0 * (1.f - s0)), d.y * b.y * (s1 + si1 * (1.f - s1)));
-            ou[e] = pack_bf16x2(d.x * si0, d.y * si1);
-            oh[e] = pack_bf16x2(si0 * b.x, si1 * b.y);
+        for (int v = 0; v < 4; v += 2) {
+          const int col = t.n0 + c * 32 + v * 8;
+          uint4 a0, b0, c0, a1, b1, c1;
+          if (col + 16 <= p.N) {
+            piece(v, g[v], u[v], a0, b0, c0);
+            piece(v + 1, g[v + 1], u[v + 1], a1, b1, c1);
+            st_global_32B(dbase + col, a0, a1);
+            st_global_32B(dbase + p.up_offset + col, b0, b1);
+            if (hrow) st_global_32B(hrow + col, c0, c1);
+          } else if (col < p.N) {
+            piece(v, g[v], u[v], a0, b0, c0);
+            *reinterpret_cast<uint4*>(dbase + col) = a0;
+            *reinterpret_cast<uint4*>(dbase + p.up_offset + col) = b0;
+            if (hrow) *reinterpret_cast<uint4*>(hrow + col) = c0;
           }
-          *reinterpret_cast<uint4*>(dbase + col) = make_uint4(og[0], og[1], og[2], og[3]);
-          *reinterpret_cast<uint4*>(dbase + p.up_offset + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-          if (hrow) *reinterpret_cast<uint4*>(hrow + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = t.n0 + c * 32 + v * 8;
+          if (col < p.N) {
+            uint4 a0, b0, c0;
+            piece(v, *reinterpret_cast<const uint4*>(arow + col), *reinterpret_cast<const uint4*>(arow + p.up_offset + col), a0, b0, c0);
+            *reinterpret_cast<uint4*>(dbase + col) = a0;
+            *reinterpret_cast<uint4*>(dbase + p.up_offset + col) = b0;
+            if (hrow) *reinterpret_cast<uint4*>(hrow + col) = c0;
+          }
         }
       }
     }
@@ -351,7 +391,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
         __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
         const __nv_bfloat16* crow =
             p.epilogue == kAddC ? p.C + p.c_gs * t.g + (long long)row * p.ldc : nullptr;
-        auto piece = [&](int v, int col) -> uint4 {
+        auto piece = [&](int v, int col, const uint4& cv) -> uint4 {
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * rs;
@@ -361,25 +401,30 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
             f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
           }
           if (crow) {
-            uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
             float2 c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y), c2 = unpack_bf16x2(cv.z), c3 = unpack_bf16x2(cv.w);
             f[0] += c0.x; f[1] += c0.y; f[2] += c1.x; f[3] += c1.y;
             f[4] += c2.x; f[5] += c2.y; f[6] += c3.x; f[7] += c3.y;
           }
           return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
         };
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
         if (p.wide) {
 #pragma unroll
           for (int v = 0; v < 4; v += 2) {
             const int col = colbase + v * 8;
-            if (col + 16 <= p.N) st_global_32B(drow + col, piece(v, col), piece(v + 1, col + 8));
-            else if (col < p.N) *reinterpret_cast<uint4*>(drow + col) = piece(v, col);
+            if (col + 16 <= p.N) {
+              uint4 c0 = zero4, c1 = zero4;
+              if (crow) ld_global_32B(crow + col, c0, c1);
+              st_global_32B(drow + col, piece(v, col, c0), piece(v + 1, col + 8, c1));
+            } else if (col < p.N) {
+              *reinterpret_cast<uint4*>(drow + col) = piece(v, col, crow ? *reinterpret_cast<const uint4*>(crow + col) : zero4);
+            }
           }
         } else {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int col = colbase + v * 8;
-            if (col < p.N) *reinterpret_cast<uint4*>(drow + col) = piece(v, col);
+            if (col < p.N) *reinterpret_cast<uint4*>(drow + col) = piece(v, col, crow ? *reinterpret_cast<const uint4*>(crow + col) : zero4);
           }
         }
       }
@@ -1052,9 +1097,12 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
 // Whole-sector stores need every row of D (and of aux for SwiGLU) to start 32-byte aligned at every 16th column.
 static int sector_aligned_outputs(const GemmArgs& p) {
   if (!g_gemm_wide || p.d_table) return 0;
-  if (p.epilogue == kF32 || p.epilogue == kSwiGLUBwd) return 0;
+  if (p.epilogue == kF32) return 0;
   auto ok = [](const void* ptr, long long ld, long long gs) { return (reinterpret_cast<uintptr_t>(ptr) & 31) == 0 && (ld & 15) == 0 && (gs & 15) == 0; };
   if (!ok(p.D, p.ldd, p.d_gs)) return 0;
+  if (p.epilogue == kAddC && !ok(p.C, p.ldc, p.c_gs)) return 0;
+  if (p.epilogue == kSwiGLUBwd)
+    return ok(p.aux, p.ldaux, p.aux_gs) && (p.up_offset & 15) == 0 && (!p.out2 || ok(p.out2, p.ldout2, p.out2_gs));
   if (p.epilogue == kSwiGLU && p.aux && (!ok(p.aux, p.ldaux, p.aux_gs) || (p.up_offset & 15))) return 0;
   return 1;
 }
