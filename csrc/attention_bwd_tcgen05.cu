@@ -110,16 +110,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = p.L / 128;
   const int rep = p.Hq / p.Hkv;
-  const int b = blockIdx.z;
+  // Grid = (heads, batch, tiles): CTAs are handed out x-fastest, so with the tile index slowest every CTA of the heaviest
+  // tile (of all heads and sequences) starts before any lighter one.  With the tile index fastest, a heavy tile of the
+  // last heads started late and the causal imbalance left SMs idle for a quarter of the dK/dV pass.
+  const int b = blockIdx.y;
   // fixed tile of this CTA and iteration space
   int fixed, head, n_iter;
   if (MODE == 0) {
-    fixed = blockIdx.x;  // key tile j (j = 0 has the most work and starts first)
-    head = blockIdx.y;   // kv head
+    fixed = blockIdx.z;  // key tile j (j = 0 has the most work)
+    head = blockIdx.x;   // kv head
     n_iter = rep * (nq - fixed);
   } else {
-    fixed = nq - 1 - blockIdx.x;  // query tile i, heaviest first
-    head = blockIdx.y;            // query head
+    fixed = nq - 1 - blockIdx.z;  // query tile i (the last one has the most work)
+    head = blockIdx.x;            // query head
     n_iter = fixed + 1;
   }
   const int hk = MODE == 0 ? head : head / rep;
@@ -454,7 +457,7 @@ static int launch_attn_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const C
   using SM = AttnBwdSmem<D, MODE>;
   cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
   if (ce != cudaSuccess) return int(ce);
-  dim3 grid(p.L / 128, MODE == 0 ? p.Hkv : p.Hq, p.B);
+  dim3 grid(MODE == 0 ? p.Hkv : p.Hq, p.B, p.L / 128);
   attn_bwd_kernel<D, MODE><<<grid, AB_THREADS, SM::TOTAL, s>>>(mq, mk, mv, mdo, p);
   return int(cudaGetLastError());
 }

@@ -96,8 +96,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = gridDim.x - 1 - blockIdx.x;  // pair index, heaviest first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid = (heads, batch, tile pairs): x is handed out fastest, so all CTAs of the heaviest pair index start first
+  const int t = gridDim.z - 1 - blockIdx.z;  // pair index, heaviest first
+  const int h = blockIdx.x, b = blockIdx.y;
   const int hk = h / (p.Hq / p.Hkv);
   const int nbA = 2 * t + 1, nbB = 2 * t + 2;  // key blocks seen by tile A / tile B
   const int row0 = b * p.L + t * 256;
@@ -424,7 +425,7 @@ static int launch_fwd2_impl(const CUtensorMap& mq, const CUtensorMap& mk, const 
   using SM = Attn2Smem<D, PT>;
   cudaError_t ce = cudaFuncSetAttribute(attn_fwd2_kernel<D, PT, PROF, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
   if (ce != cudaSuccess) return int(ce);
-  dim3 grid(L / 256, Hq, B);
+  dim3 grid(Hq, B, L / 256);
   attn_fwd2_kernel<D, PT, PROF, POLY><<<grid, A2_THREADS, SM::TOTAL, s>>>(mq, mk, mv, p);
   return int(cudaGetLastError());
 }

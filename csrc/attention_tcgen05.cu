@@ -68,8 +68,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid = (heads, batch, query tiles): x is handed out fastest, so all CTAs of the heaviest tile index start first
+  const int qt = gridDim.z - 1 - blockIdx.z;  // heaviest tiles first
+  const int h = blockIdx.x, b = blockIdx.y;
   const int hk = h / (p.Hq / p.Hkv);
   const int n_blocks = qt + 1;
   const int row0 = b * p.L + qt * ATT_BM;     // token row of the first query
@@ -323,7 +324,7 @@ ATS_API int ats_attn_fwd(const void* q, long long ld_q, long long q_cols, int q_
   p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse;
   p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
   p.status = status;
-  dim3 grid(L / ATT_BM, Hq, B);
+  dim3 grid(Hq, B, L / ATT_BM);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t ce;
   if (D == 128) {
