@@ -145,6 +145,9 @@ class _RopeAttnPackedFn(torch.autograd.Function):
         from .functional import _L, _P, _S, _CK
         B, L, W = qkv.shape
         ctx.mark_dirty(qkv)
+        # the rotated projection is returned only because it was modified in place; when nothing downstream uses it, its
+        # gradient must arrive as None, not as a zero tensor of the projection's size that backward would fill and add
+        ctx.set_materialize_grads(False)
         _CK(_L().ats_rope(_P(qkv), _P(cos), _P(sin), None, B * L, L, pos_offset, W, 0, n_q + n_kv, d, 0, _S(qkv.device)), "rope")
         nq, nk = n_q * d, n_kv * d
         out, lse = _fwd(qkv[..., :nq].view(B, L, n_q, d), qkv[..., nq:nq + nk].view(B, L, n_kv, d), qkv[..., nq + nk:].view(B, L, n_kv, d))
@@ -159,6 +162,10 @@ class _RopeAttnPackedFn(torch.autograd.Function):
         n_q, n_kv, d, pos_offset = ctx.dims
         B, L, W = qkv.shape
         nq, nk = n_q * d, n_kv * d
+        if dout is None:  # only the rotated projection was used downstream
+            dqkv = _dqkv_unused.clone() if _dqkv_unused is not None else torch.zeros_like(qkv)
+            _CK(_L().ats_rope(_P(dqkv), _P(cos), _P(sin), None, B * L, L, pos_offset, W, 0, n_q + n_kv, d, 1, _S(dqkv.device)), "rope_bwd")
+            return dqkv, None, None, None, None, None, None
         dqkv = torch.empty_like(qkv)
         _bwd(qkv[..., :nq].view(B, L, n_q, d), qkv[..., nq:nq + nk].view(B, L, n_kv, d), qkv[..., nq + nk:].view(B, L, n_kv, d), out,
              dout.contiguous(), lse, dqkv[..., :nq].view(B, L, n_q, d), dqkv[..., nq:nq + nk].view(B, L, n_kv, d),
