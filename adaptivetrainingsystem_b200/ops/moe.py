@@ -46,8 +46,13 @@ class _GateFn(torch.autograd.Function):
     def forward(ctx, x, wg):
         T, H = x.shape
         E = wg.shape[0]
-        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
-        _CK(_L().ats_gate_fwd(_P(x), _P(wg), _P(logits), T, H, E, _S(x.device)), "gate_fwd")
+        if T >= 256 and E % 8 == 0 and H % 64 == 0 and x.is_contiguous() and wg.is_contiguous():
+            # tensor cores, fp32 logits: the 256-column tile is mostly padding (rows of wg beyond E read as zeros), yet the
+            # product then costs about one pass over x, a third of the CUDA-core kernel's time
+            logits = G.gemm_nt(x, wg, out_fp32=True)
+        else:
+            logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+            _CK(_L().ats_gate_fwd(_P(x), _P(wg), _P(logits), T, H, E, _S(x.device)), "gate_fwd")
         ctx.save_for_backward(x, wg)
         return logits
 

@@ -119,6 +119,40 @@ gate_bwd_dx_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __res
   }
 }
 
+// Same for up to eight experts with the weights in registers: a thread owns eight columns and walks over tokens, so a token
+// costs eight broadcast loads of dlogits, 64 FMAs and one 16-byte store instead of eight more weight loads.
+__global__ void __launch_bounds__(256)
+gate_bwd_dx_reg_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ wg, __nv_bfloat16* __restrict__ dx,
+                       long long tokens, int hidden, int experts, int accumulate) {
+  const int v = blockIdx.y * 256 + threadIdx.x;
+  if (v >= (hidden >> 3)) return;
+  float w[8][8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    uint4 b = e < experts ? reinterpret_cast<const uint4*>(wg + (long long)e * hidden)[v] : make_uint4(0, 0, 0, 0);
+    float2 w0 = unpack_bf16x2(b.x), w1 = unpack_bf16x2(b.y), w2 = unpack_bf16x2(b.z), w3 = unpack_bf16x2(b.w);
+    w[e][0] = w0.x; w[e][1] = w0.y; w[e][2] = w1.x; w[e][3] = w1.y; w[e][4] = w2.x; w[e][5] = w2.y; w[e][6] = w3.x; w[e][7] = w3.y;
+  }
+  for (long long t = blockIdx.x; t < tokens; t += gridDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (e < experts) {
+        const float d = dlogits[t * experts + e];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] += d * w[e][c];
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(dx + t * hidden) + v;
+    if (accumulate) {
+      uint4 o = *dst;
+      float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+    *dst = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
 // dwg partial: block b sums tokens [b*chunk, (b+1)*chunk): partial[b][e][h] = sum_t dlogits[t,e] * x[t,h]
 __global__ void __launch_bounds__(256)
 gate_bwd_dw_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __restrict__ x, float* __restrict__ partial,
@@ -132,16 +166,25 @@ gate_bwd_dw_kernel(const float* __restrict__ dlogits, const __nv_bfloat16* __res
       for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 8; ++b) acc[a][b] = 0.f;
-      for (long long t = t0; t < t1; ++t) {
-        uint4 q = reinterpret_cast<const uint4*>(x + t * hidden)[v];
-        float2 x0 = unpack_bf16x2(q.x), x1 = unpack_bf16x2(q.y), x2 = unpack_bf16x2(q.z), x3 = unpack_bf16x2(q.w);
-        float xs[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+      // four tokens per step, their rows requested before any arithmetic: one load in flight per thread left HBM idle
+      for (long long tb = t0; tb < t1; tb += 4) {
+        uint4 q[4];
 #pragma unroll
-        for (int a = 0; a < 8; ++a) {
-          if (e0 + a < experts) {
-            const float d = dlogits[t * experts + e0 + a];
+        for (int j = 0; j < 4; ++j)
+          q[j] = tb + j < t1 ? reinterpret_cast<const uint4*>(x + (tb + j) * hidden)[v] : make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int b = 0; b < 8; ++b) acc[a][b] += d * xs[b];
+        for (int j = 0; j < 4; ++j) {
+          if (tb + j >= t1) break;
+          const long long t = tb + j;
+          float2 x0 = unpack_bf16x2(q[j].x), x1 = unpack_bf16x2(q[j].y), x2 = unpack_bf16x2(q[j].z), x3 = unpack_bf16x2(q[j].w);
+          float xs[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+#pragma unroll
+          for (int a = 0; a < 8; ++a) {
+            if (e0 + a < experts) {
+              const float d = dlogits[t * experts + e0 + a];
+#pragma unroll
+              for (int b = 0; b < 8; ++b) acc[a][b] += d * xs[b];
+            }
           }
         }
       }
@@ -634,6 +677,14 @@ ATS_API int ats_gate_bwd_dx(const float* dlogits, const void* wg, void* dx, long
                             int accumulate, void* stream) {
   if (hidden & 7) return 1003;
   if (tokens == 0) return 0;
+  if (experts <= 8) {
+    const unsigned col_blocks = unsigned(((hidden >> 3) + 255) / 256);
+    unsigned row_blocks = 148 * 8 / col_blocks;
+    if ((long long)row_blocks > tokens) row_blocks = unsigned(tokens);
+    gate_bwd_dx_reg_kernel<<<dim3(row_blocks, col_blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        dlogits, static_cast<const __nv_bfloat16*>(wg), static_cast<__nv_bfloat16*>(dx), tokens, hidden, experts, accumulate);
+    return int(cudaGetLastError());
+  }
   long long work = tokens * (hidden >> 3);
   long long blocks = (work + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
