@@ -245,3 +245,32 @@ def test_security_primitives():
     assert r.allow("k")[0]
     v = InputValidator(max_length=50)
     assert v.validate("hello")[0] and not v.validate("<script>alert(1)</script>")[0] and not v.validate("x" * 51)[0]
+
+
+def test_quantization_manager_methods_and_refusals():
+    """bits=8 without a method selects the native fp8 path; external backends that are not installed are refused."""
+    from types import SimpleNamespace
+    from adaptivetrainingsystem_b200.training import QuantizationManager
+    qm = QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=8))
+    st = qm.status()
+    assert st["method"] == "fp8" and not st["applied"] and "bitsandbytes" in st["backends"]
+    assert QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=None)).quantize_model("m") == "m"
+    with pytest.raises(RuntimeError):
+        QuantizationManager(SimpleNamespace(quantization_method="gptq", quantization_bits=4)).quantize_model(None)
+
+
+def test_swiglu_backward_gemm_reference_matches_autograd():
+    """CPU definition of the fused dh GEMM + SwiGLU backward against autograd through silu(gate) * up."""
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    torch.manual_seed(0)
+    M, H, I = 12, 16, 24
+    dy, w2 = torch.randn(M, H), torch.randn(H, I)
+    pre = torch.randn(M, 2 * I, requires_grad=True)
+    g, u = pre.chunk(2, dim=-1)
+    h_ref = torch.nn.functional.silu(g) * u
+    h_ref.backward(dy @ w2)
+    dgu, h = G.gemm_nn_swiglu_bwd(dy, w2, pre.detach())
+    assert torch.allclose(h, h_ref.detach(), atol=1e-5) and torch.allclose(dgu, pre.grad, atol=1e-5)
+    counts = torch.tensor([M], dtype=torch.int32)
+    dgu_g, h_g = G.grouped_nn_swiglu_bwd(dy.view(1, M, H), w2.view(1, H, I), counts, pre.detach().view(1, M, 2 * I))
+    assert torch.allclose(dgu_g[0], pre.grad, atol=1e-5) and torch.allclose(h_g[0], h_ref.detach(), atol=1e-5)
