@@ -78,6 +78,38 @@ def _check2d(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+# Skinny products (a decode step: M = batch rows, few 256-column output tiles) would occupy N / 256 of the 148 SMs and stream
+# the weight at a fraction of HBM bandwidth; the reduction dimension is split over groups of the grouped kernel instead, every
+# group writing an fp32 partial product that a small reduction folds.  ATS_SPLIT_K=0 switches it off.
+SPLIT_K_SKINNY = os.environ.get("ATS_SPLIT_K", "1") == "1"
+
+
+def _skinny_splits(M: int, N: int, K: int) -> int:
+    if M > 128 or K < 2048:
+        return 1
+    tiles = (N + 255) // 256
+    s = 1
+    while s * 2 * tiles <= 160 and K % (s * 2 * 64) == 0 and K // (s * 2) >= 512 and s < 16:
+        s *= 2
+    return s
+
+
+def _gemm_nt_split_k(a, b, out, add, alpha, splits):
+    M, K = a.shape
+    N = b.shape[0]
+    kp = K // splits
+    part = torch.empty(splits, M, N, dtype=torch.float32, device=a.device)
+    _raw(a, M, K, a.stride(0), 0, b, N, K, b.stride(0), 0, part, N, None, 0, None, 0, M, N, kp, alpha=alpha, beta=0,
+         epilogue=EPI_F32, groups=splits, a_gs_k=kp, b_gs_k=kp, d_gs=M * N)
+    res = part.sum(0)
+    if add is not None:
+        res += add
+    if out is None:
+        return res.to(a.dtype)
+    out.copy_(res)
+    return out
+
+
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
             add: Optional[torch.Tensor] = None, alpha: float = 1.0, out_fp32: bool = False,
             accumulate: bool = False, max_ctas: int = 0) -> torch.Tensor:
@@ -99,6 +131,9 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     a, b = _check2d(a), _check2d(b)
     M, K = a.shape
     N = b.shape[0]
+    splits = _skinny_splits(M, N, K) if not out_fp32 and SPLIT_K_SKINNY else 1
+    if splits > 1:
+        return _gemm_nt_split_k(a, b, out, add, alpha, splits)
     if out is None:
         out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else a.dtype, device=a.device)
     epi = EPI_F32 if out_fp32 else (EPI_ADDC if add is not None else EPI_STORE)

@@ -190,3 +190,22 @@ def test_gemm_swiglu_backward_epilogue_matches_separate_kernel():
             continue
         d1, h1 = G.gemm_nn_swiglu_bwd(dye[e, :c].contiguous(), w2e[e], pre_e[e, :c].contiguous())
         assert torch.equal(dgu_e[e, :c], d1) and torch.equal(h_e[e, :c], h1), e
+
+
+def test_skinny_gemm_splits_the_reduction():
+    """Decode-shaped products (few output tiles) run as split-K groups with fp32 partials: same result as the fp32 reference."""
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    torch.manual_seed(5)
+    for (M, N, K) in [(64, 4096, 14336), (64, 6144, 4096), (17, 1024, 2048), (128, 512, 8192)]:
+        assert G._skinny_splits(M, N, K) > 1, (M, N, K)
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        res = torch.randn(M, N, device="cuda").bfloat16()
+        ref = a.float() @ b.float().t()
+        out = G.gemm_nt(a, b)
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3, (M, N, K)
+        out2 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        G.gemm_nt(a, b, out=out2, add=res)
+        ref2 = ref + res.float()
+        assert (out2.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item() + 1e-3, (M, N, K)
+    assert G._skinny_splits(64, 28672, 4096) == 1 and G._skinny_splits(4096, 4096, 4096) == 1
