@@ -114,12 +114,36 @@ class KVSlotManager:
 
 
 class GenerationEngine:
-    def __init__(self, model: DeepSeekTransformer, tokenizer=None, max_batch: int = 64, max_len: Optional[int] = None):
+    def __init__(self, model: DeepSeekTransformer, tokenizer=None, max_batch: int = 64, max_len: Optional[int] = None,
+                 pack_experts: bool = False):
         self.model = model.eval()
         self.tokenizer = tokenizer
         self.max_batch = max_batch
         self.max_len = max_len or model.config.seq_length
         self.stats: Dict[str, float] = {}
+        if pack_experts:
+            self.pack_expert_weights()
+
+    @torch.no_grad()
+    def pack_expert_weights(self) -> int:
+        """Re-store every expert weight tile by tile (``ops.gemm.pack_kmajor``) for serving: a decode step reads each expert
+        weight exactly once, and whole-page reads stream it faster than 128-byte row pieces.  The model can no longer be
+        trained or saved in the reference layout afterwards (``ops.gemm.unpack_kmajor`` restores a tensor).  Returns the
+        number of tensors packed."""
+        from ..ops import gemm as G
+        n = 0
+        for mod in self.model.modules():
+            w1, w2 = getattr(mod, "experts_w1", None), getattr(mod, "experts_w2", None)
+            if w1 is None or w2 is None or getattr(w1, "_ats_packed", False) or not w1.is_cuda:
+                continue
+            if w1.shape[1] % 256 or w1.shape[2] % 64 or w2.shape[1] % 128 or w2.shape[2] % 64:
+                continue
+            for w in (w1, w2):
+                w.requires_grad_(False)
+                w.data = G.pack_kmajor(w.data)
+                w._ats_packed = True
+                n += 1
+        return n
 
     @torch.no_grad()
     def prefill(self, input_ids: torch.Tensor, cache: KVCache) -> torch.Tensor:

@@ -245,16 +245,36 @@ def _ref_mask(counts: torch.Tensor, cap: int) -> torch.Tensor:
     return (torch.arange(cap, device=counts.device)[None, :] < counts[:, None].long())
 
 
+def pack_kmajor(w: torch.Tensor) -> torch.Tensor:
+    """[.., N, K] weight -> the same shape with the elements stored tile by tile ([N / 128][K / 64][128][64]): every
+    128 x 64 box the GEMM loads is then 16 KB of consecutive memory, which lets a weight that is read once per step (decode)
+    stream at close to HBM speed instead of touching 128 bytes per DRAM page.  Needs N % 128 == 0 and K % 64 == 0."""
+    *lead, N, K = w.shape
+    if N % 128 or K % 64:
+        raise ValueError("pack_kmajor needs N % 128 == 0 and K % 64 == 0")
+    t = w.reshape(-1, N // 128, 128, K // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
+    return t.view(*lead, N, K)
+
+
+def unpack_kmajor(w: torch.Tensor) -> torch.Tensor:
+    """Inverse of :func:`pack_kmajor`."""
+    *lead, N, K = w.shape
+    t = w.reshape(-1, N // 128, K // 64, 128, 64).permute(0, 1, 3, 2, 4).contiguous()
+    return t.view(*lead, N, K)
+
+
 def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: bool = False,
                pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, b_div: int = 1,
-               d_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+               d_table: Optional[torch.Tensor] = None, packed: bool = False) -> torch.Tensor:
     """x[G,C,K] · w[E,N,K]^T -> [G,C,N] (or [G,C,N/2] through SwiGLU) for the first counts[g] rows of every
     group; group g uses weight g // b_div (G = E * b_div: several token blocks per expert, one per source rank).
     Rows beyond the padded count are left untouched.  ``d_table`` (int64 [G]) redirects the output of group g to
-    an arbitrary base address (a buffer on a peer GPU)."""
+    an arbitrary base address (a buffer on a peer GPU).  ``packed``: ``w`` is stored as :func:`pack_kmajor` leaves it."""
     Gn, C, K = x.shape
     N = w.shape[1]
     if not _lib.use_cuda_kernels(x):
+        if packed:
+            w = unpack_kmajor(w)
         wx = w.repeat_interleave(b_div, dim=0) if b_div > 1 else w
         y = torch.einsum("eck,enk->ecn", x.float(), wx.float()).to(x.dtype)
         mask = _ref_mask(counts, C)[..., None]
@@ -272,7 +292,8 @@ def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: b
     n_out = N // 2 if swiglu else N
     if out is None and d_table is None:
         out = torch.empty(Gn, C, n_out, dtype=x.dtype, device=x.device)
-    _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 0, out, n_out, None, 0, pre_act, N if pre_act is not None else 0,
+    _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 2 if packed else 0, out, n_out, None, 0, pre_act,
+         N if pre_act is not None else 0,
          C, n_out, K, epilogue=EPI_SWIGLU if swiglu else EPI_STORE, up_offset=N // 2 if swiglu else 0,
          groups=Gn, ragged=1, counts=counts, a_gs_mn=C, b_gs_mn=N, d_gs=C * n_out,
          aux_gs=C * N if pre_act is not None else 0, b_div=b_div, d_table=d_table)

@@ -289,8 +289,11 @@ class _MoEFFNFn(torch.autograd.Function):
         xe = dispatch(x, topk_idx, slot_pos, counts, E, capacity)
         need_bwd = any(ctx.needs_input_grad)
         pre = torch.empty(E, capacity, w1.shape[1], dtype=x.dtype, device=x.device) if need_bwd else None
-        h = G.grouped_nt(xe, w1, counts, swiglu=True, pre_act=pre)
-        ye = G.grouped_nt(h, w2, counts)
+        packed = bool(getattr(w1, "_ats_packed", False))  # serving: expert weights stored tile by tile (GenerationEngine)
+        if packed and need_bwd:
+            raise RuntimeError("expert weights are packed for serving; the backward pass needs the plain layout")
+        h = G.grouped_nt(xe, w1, counts, swiglu=True, pre_act=pre, packed=packed)
+        ye = G.grouped_nt(h, w2, counts, packed=packed)
         out = combine(ye, topk_idx, slot_pos, topk_w, T, residual)
         ctx.save_for_backward(topk_idx, slot_pos, counts, topk_w, w1, w2, xe, pre, ye)
         ctx.capacity = capacity

@@ -152,17 +152,20 @@ class _EPMoEFn(torch.autograd.Function):
             comm.exchange_counts(counts, buf.counts)
         need_bwd = any(ctx.needs_input_grad)
         pre = torch.empty(buf.El * W, C, w1.shape[1], dtype=x.dtype, device=x.device) if need_bwd else None
-        h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, pre_act=pre, b_div=W)
+        packed = bool(getattr(w1, "_ats_packed", False))  # serving: expert weights stored tile by tile
+        if packed and need_bwd:
+            raise RuntimeError("expert weights are packed for serving; the backward pass needs the plain layout")
+        h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, pre_act=pre, b_div=W, packed=packed)
         if comm.fused and comm.pull_results:
-            G.grouped_nt(h, w2, buf.counts, b_div=W, out=buf.own_y)
+            G.grouped_nt(h, w2, buf.counts, b_div=W, out=buf.own_y, packed=packed)
             comm.barrier()
             out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual, table=buf.t_pull_y, keep_copy=True)
         else:
             if comm.fused:
-                G.grouped_nt(h, w2, buf.counts, b_div=W, d_table=buf.t_ret_y)
+                G.grouped_nt(h, w2, buf.counts, b_div=W, d_table=buf.t_ret_y, packed=packed)
                 comm.barrier()
             else:
-                ye = G.grouped_nt(h, w2, buf.counts, b_div=W)
+                ye = G.grouped_nt(h, w2, buf.counts, b_div=W, packed=packed)
                 comm.exchange_to_sources(ye, buf.ret_y)
             out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual)
         ctx.save_for_backward(topk_idx, slot_pos, counts, topk_w, w1, w2, pre)

@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug only")
     ap.add_argument("--repeat", type=int, default=2)
+    ap.add_argument("--pack-experts", type=int, default=1, help="store the expert weights tile by tile for serving (1) or keep the training layout (0)")
     a = ap.parse_args()
     rank, local, world = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -57,7 +58,7 @@ def main():
     if world > 1:
         from adaptivetrainingsystem_b200.parallel.expert_parallel import attach_expert_parallel
         attach_expert_parallel(model, mesh, cfg, use_fused=True)
-    eng = GenerationEngine(model)
+    eng = GenerationEngine(model, pack_experts=bool(a.pack_experts))
     g = torch.Generator().manual_seed(7)  # same prompts on every rank
     ids = torch.randint(0, mc.vocab_size, (a.batch, a.prompt), generator=g).to(dev)
     params = SamplingParams.from_mode("greedy", max_new_tokens=a.new)
@@ -78,7 +79,8 @@ def main():
            "prefill_tokens_per_sec": a.batch * a.prompt / best["prefill_s"], "n_gpus": world, "dtype": "bf16", "data": "synthetic",
            "ms_per_decode_step": 1e3 * best["decode_s"] / (a.new - 1),
            "config": {"model": a.config, "batch": a.batch, "prompt": a.prompt, "new_tokens": a.new, "layers": mc.num_layers,
-                      "parallelism": f"ep{ep}", "params_total": mc.num_parameters()},
+                      "parallelism": f"ep{ep}", "params_total": mc.num_parameters(),
+                      "expert_weights": "tile-packed" if a.pack_experts else "row-major"},
            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -79,6 +79,9 @@ struct GemmArgs {
   __nv_bfloat16* out2;
   int ldout2;
   long long out2_gs;
+  // b_packed: the K-major B operand is stored tile by tile ([weights][N / 128][K / 64][128 rows][64 elements], one 16 KB box
+  // contiguous in memory) so that streaming a weight that is read once (decode) touches whole DRAM pages; b_kblocks = K / 64.
+  int b_packed, b_kblocks;
   int wide;                // D (and aux) rows are 32-byte aligned at every 16th column: the bf16 epilogues store whole sectors
   int fp8;
   const float* row_scale;  // [groups * rs_gs] or null
@@ -548,6 +551,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               else tma_load_2d(b_dst, &map_b, &full[stage], k0, b_mn_c);
               if (o1 >= 0 && o1 < p.own_rows) tma_load_2d(b_dst + 128 * 128, &map_b_own, &full[stage], k0, o1);
               else tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], k0, second);
+            } else if (p.b_packed) {
+              const int kb_idx = k0 >> 6;
+              tma_load_2d(b_dst, &map_b, &full[stage], 0, ((b_mn_c >> 7) * p.b_kblocks + kb_idx) << 7);
+              tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], 0, ((second >> 7) * p.b_kblocks + kb_idx) << 7);
             } else {
               tma_load_2d(b_dst, &map_b, &full[stage], b_k_c + k0, b_mn_c);
               tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], b_k_c + k0, second);
@@ -794,7 +801,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               tma_load_2d_pair(a_dst + j * (BK * 128), &map_a, bar, a_mn_c + 64 * j, a_k_c + k0);
           }
           if (!p.b_mn) {
-            tma_load_2d_pair(b_dst, bmap, bar, b_k_c + k0, b_row);
+            if (p.b_packed) tma_load_2d_pair(b_dst, bmap, bar, 0, ((b_row >> 7) * p.b_kblocks + (k0 >> 6)) << 7);
+            else tma_load_2d_pair(b_dst, bmap, bar, b_k_c + k0, b_row);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 128; ++j)
@@ -984,14 +992,24 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   }
   if (groups < 1 || groups > MAX_GROUPS) return 1002;
   if ((N & 7) || (a_gs_mn & 7) || (a_gs_k & 7) || (b_gs_mn & 7) || (b_gs_k & 7) || (ldd & 7) || (d_gs & 7)) return 1003;
+  const int b_packed = b_mn == 2 ? 1 : 0;  // K-major, stored tile by tile (see GemmArgs::b_packed)
+  if (b_packed) {
+    b_mn = 0;
+    if ((b_rows & 127) || (b_cols & 63) || (b_gs_mn & 127) || b_gs_k || ragged == 2 || (epilogue == kSwiGLU && (up_offset & 127))) return 1007;
+  }
   if (epilogue == kSwiGLU && (b_mn || (up_offset & 7))) return 1004;
   if (ragged && !counts) return 1005;
   if (b_div < 1 || k_segs < 1 || (seg_stride & 7) || (k_segs > 1 && ragged != 2)) return 1006;
   CUtensorMap ma, mb;
   int e;
   if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 2, 64, a_mn ? 64 : 128))) return e;
-  if ((e = make_tmap_2d(&mb, B, b_rows, b_cols, ldb, 2, 64, b_mn ? 64 : 128))) return e;
+  if (b_packed) {
+    if ((e = make_tmap_2d(&mb, B, (uint64_t)b_rows * (uint64_t)(b_cols / 64), 64, 64, 2, 64, 128))) return e;
+  } else if ((e = make_tmap_2d(&mb, B, b_rows, b_cols, ldb, 2, 64, b_mn ? 64 : 128))) {
+    return e;
+  }
   GemmArgs p;
+  p.b_packed = b_packed; p.b_kblocks = int(b_cols / 64);
   p.M = M; p.N = N; p.K = K; p.groups = groups; p.ragged = ragged; p.counts = counts;
   p.a_gs_mn = a_gs_mn; p.a_gs_k = a_gs_k; p.b_gs_mn = b_gs_mn; p.b_gs_k = b_gs_k;
   p.d_gs = d_gs; p.c_gs = c_gs; p.aux_gs = aux_gs;
@@ -1043,6 +1061,7 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
   p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
+  p.b_packed = 0; p.b_kblocks = 0;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
@@ -1082,6 +1101,7 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   p.b_div = 1; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   const long long shard_rows = b_rows / b_shards;
+  p.b_packed = 0; p.b_kblocks = 0;
   p.n_copy = 1; p.b_src = b_src; p.b_dst = static_cast<uint8_t*>(const_cast<void*>(B_local));
   p.shard_bytes = shard_rows * K * 2; p.chunk_bytes = (long long)ready_rows * K * 2;
   p.b_ready = b_ready; p.ready_rows = ready_rows; p.n_chunks = int(b_rows / ready_rows);

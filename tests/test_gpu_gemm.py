@@ -209,3 +209,31 @@ def test_skinny_gemm_splits_the_reduction():
         ref2 = ref + res.float()
         assert (out2.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item() + 1e-3, (M, N, K)
     assert G._skinny_splits(64, 28672, 4096) == 1 and G._skinny_splits(4096, 4096, 4096) == 1
+
+
+def test_grouped_gemm_with_tile_packed_weights():
+    """Expert weights stored tile by tile (serving layout) give bit-identical products, on single CTAs (C = 128) and CTA pairs."""
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    torch.manual_seed(6)
+    E, N, K = 3, 512, 384
+    w = (torch.randn(E, N, K, device="cuda") * 0.05).bfloat16()
+    wp = G.pack_kmajor(w)
+    assert torch.equal(G.unpack_kmajor(wp), w)
+    for C, cnt in ((128, [100, 0, 128]), (512, [300, 512, 17])):
+        x = torch.randn(E, C, K, device="cuda").bfloat16()
+        counts = torch.tensor(cnt, dtype=torch.int32, device="cuda")
+        for swiglu in (False, True):
+            pre_a = torch.zeros(E, C, N, device="cuda", dtype=torch.bfloat16) if swiglu else None
+            pre_b = torch.zeros(E, C, N, device="cuda", dtype=torch.bfloat16) if swiglu else None
+            a = G.grouped_nt(x, w, counts, swiglu=swiglu, pre_act=pre_a, out=torch.zeros(E, C, N // 2 if swiglu else N, device="cuda", dtype=torch.bfloat16))
+            b = G.grouped_nt(x, wp, counts, swiglu=swiglu, pre_act=pre_b, out=torch.zeros(E, C, N // 2 if swiglu else N, device="cuda", dtype=torch.bfloat16),
+                             packed=True)
+            assert torch.equal(a, b), (C, swiglu)
+            if swiglu:
+                assert torch.equal(pre_a, pre_b)
+    # two token blocks per weight (expert parallel receive layout)
+    x = torch.randn(2 * E, 128, K, device="cuda").bfloat16()
+    counts = torch.tensor([128, 3, 0, 64, 128, 1], dtype=torch.int32, device="cuda")
+    a = G.grouped_nt(x, w, counts, b_div=2, out=torch.zeros(2 * E, 128, N, device="cuda", dtype=torch.bfloat16))
+    b = G.grouped_nt(x, wp, counts, b_div=2, out=torch.zeros(2 * E, 128, N, device="cuda", dtype=torch.bfloat16), packed=True)
+    assert torch.equal(a, b)
