@@ -143,6 +143,10 @@ class GenerationEngine:
                 w.data = G.pack_kmajor(w.data)
                 w._ats_packed = True
                 n += 1
+        if n and torch.cuda.is_available():
+            # the plain copies went back to PyTorch's caching allocator; the peer-memory exchange buffers of expert
+            # parallelism are allocated outside it and need that memory returned to the driver
+            torch.cuda.empty_cache()
         return n
 
     @torch.no_grad()

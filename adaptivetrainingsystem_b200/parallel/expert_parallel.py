@@ -221,7 +221,11 @@ class EPLayer:
         self.comm, self.layer_idx, self.num_experts = comm, layer_idx, num_experts
 
     def moe_ffn(self, x, topk_idx, topk_w, w1, w2, capacity, residual=None):
-        buf = self.comm.buffers(self.layer_idx, self.num_experts, capacity, x.shape[1], x.dtype, x.device)
+        # Training keeps one set of exchange buffers per layer (the backward pass reads what the forward pass received).
+        # Without autograd nothing outlives the layer call, and the barriers inside it order every reuse, so all layers share
+        # one set: a 64 x 1024-token prefill needs 12 GiB of buffers once instead of once per layer.
+        key = self.layer_idx if torch.is_grad_enabled() else -1
+        buf = self.comm.buffers(key, self.num_experts, capacity, x.shape[1], x.dtype, x.device)
         return _EPMoEFn.apply(x, topk_idx, topk_w, w1, w2, capacity, residual, self.comm, buf)
 
 

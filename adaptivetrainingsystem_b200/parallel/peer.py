@@ -68,7 +68,15 @@ class SymmetricBuffer:
         lib = _L()
         local = _vp()
         handle = ctypes.create_string_buffer(64)
-        _lib.check(lib.ats_ipc_alloc(self.nbytes, ctypes.byref(local), handle), "ipc_alloc")
+        err = lib.ats_ipc_alloc(self.nbytes, ctypes.byref(local), handle)
+        if err == 2:  # out of memory: give PyTorch's cached blocks back to the driver and try once more
+            torch.cuda.empty_cache()
+            err = lib.ats_ipc_alloc(self.nbytes, ctypes.byref(local), handle)
+        if err:
+            free, total = torch.cuda.mem_get_info(self.device)
+            raise _lib.KernelError(f"ipc_alloc of {self.nbytes / 2**30:.2f} GiB failed with CUDA error {err}: {free / 2**30:.1f} of "
+                                   f"{total / 2**30:.1f} GiB free on the device, {torch.cuda.memory_reserved(self.device) / 2**30:.1f} GiB "
+                                   f"reserved by PyTorch")
         self.local_ptr = int(local.value)
         self.ptrs: List[int] = [0] * self.world
         self.ptrs[self.rank] = self.local_ptr
