@@ -518,15 +518,25 @@ class EnhancedConversationTrainer:
     def add_expert(self, layer_idx: Optional[int] = None) -> int:
         """Append one expert to the targeted MoE layers: weights = mean of the existing experts + N(0, 0.01) noise,
         new gate row N(0, 0.01); optimiser state of surviving parameters is kept (reference ``trainer.py:1270-1376``).
-        Returns the number of layers changed."""
+
+        Under expert parallelism every rank appends one expert to ITS experts (mean of its local experts), so the layer
+        grows by ``ep_size`` experts and stays evenly divided; global expert ids are re-planned as rank-major blocks
+        (rank r owns ids ``r * E_local .. (r + 1) * E_local - 1``) and the replicated gate matrix gets its new rows at the
+        end of every rank's block, drawn from a generator seeded identically on all ranks.  Returns the number of layers
+        changed."""
         changed = 0
         maps: Dict[str, List[int]] = {}
         for layer in self._moe_layers(layer_idx):
-            if layer.ep_size > 1:
-                raise NotImplementedError("expert add/prune under expert parallelism needs a re-plan of the EP layout")
-            rows = list(range(layer.num_experts)) + [-1]
-            for suffix in ("experts_w1", "experts_w2", "gate.weight"):
-                maps[f"layers.{layer.layer_idx}.ffn.{suffix}"] = rows
+            W = layer.ep_size
+            e_local = layer.num_experts // W
+            local_rows = list(range(e_local)) + [-1]
+            gate_rows: List[int] = []
+            for r in range(W):
+                gate_rows += [r * e_local + j for j in range(e_local)] + [-1]
+            prefix = f"layers.{layer.layer_idx}.ffn."
+            maps[prefix + "experts_w1"] = local_rows
+            maps[prefix + "experts_w2"] = local_rows
+            maps[prefix + "gate.weight"] = gate_rows
             for attr in ("experts_w1", "experts_w2"):
                 w = getattr(layer, attr)
                 new = w.data.float().mean(0, keepdim=True) + 0.01 * torch.randn_like(w.data[:1].float())
@@ -534,10 +544,16 @@ class EnhancedConversationTrainer:
                 p._ats_expert = True
                 setattr(layer, attr, p)
             g = layer.gate.weight
-            row = 0.01 * torch.randn(1, g.shape[1], device=g.device, dtype=torch.float32)
-            layer.gate.weight = nn.Parameter(torch.cat([g.data, row.to(g.dtype)], dim=0))
-            layer.gate.out_features += 1
-            layer.num_experts += 1
+            gen = torch.Generator().manual_seed(7919 * (layer.layer_idx + 1) + layer.num_experts)  # same rows on every rank
+            fresh = (0.01 * torch.randn(W, g.shape[1], generator=gen)).to(device=g.device, dtype=g.dtype)
+            blocks = []
+            for r in range(W):
+                blocks += [g.data[r * e_local:(r + 1) * e_local], fresh[r:r + 1]]
+            layer.gate.weight = nn.Parameter(torch.cat(blocks, dim=0))
+            layer.gate.out_features += W
+            layer.num_experts += W
+            if layer.ep is not None:
+                layer.ep.num_experts = layer.num_experts
             layer.expert_demand = torch.zeros(layer.num_experts, dtype=torch.float64, device=g.device)
             changed += 1
         if changed:
@@ -549,29 +565,41 @@ class EnhancedConversationTrainer:
     @torch.no_grad()
     def prune_expert(self, layer_idx: int, expert_idx: int) -> bool:
         """Remove one expert and its gate row; its optimiser state is dropped with it (the reference leaves the
-        dead parameters in the optimiser, ``trainer.py:1408-1426``)."""
+        dead parameters in the optimiser, ``trainer.py:1408-1426``).
+
+        Under expert parallelism the layer must stay evenly divided, so the expert at the same LOCAL position as
+        ``expert_idx`` is removed on every rank (``ep_size`` experts in all, the named one among them) and the remaining
+        experts keep their order inside every rank's block of ids."""
         done = False
         maps: Dict[str, List[int]] = {}
         for layer in self._moe_layers(layer_idx):
-            if layer.ep_size > 1:
-                raise NotImplementedError("expert add/prune under expert parallelism needs a re-plan of the EP layout")
-            if layer.num_experts <= max(layer.top_k, 2) or not 0 <= expert_idx < layer.num_experts:
+            W = layer.ep_size
+            e_local = layer.num_experts // W
+            if not 0 <= expert_idx < layer.num_experts or e_local < 2 or layer.num_experts - W < max(layer.top_k, 2):
                 return False
-            keep = [i for i in range(layer.num_experts) if i != expert_idx]
-            for suffix in ("experts_w1", "experts_w2", "gate.weight"):
-                maps[f"layers.{layer.layer_idx}.ffn.{suffix}"] = keep
+            slot = expert_idx % e_local
+            keep_local = [i for i in range(e_local) if i != slot]
+            keep_gate = [r * e_local + i for r in range(W) for i in keep_local]
+            prefix = f"layers.{layer.layer_idx}.ffn."
+            maps[prefix + "experts_w1"] = keep_local
+            maps[prefix + "experts_w2"] = keep_local
+            maps[prefix + "gate.weight"] = keep_gate
             for attr in ("experts_w1", "experts_w2"):
                 w = getattr(layer, attr)
-                p = nn.Parameter(w.data[keep].clone())
+                p = nn.Parameter(w.data[keep_local].clone())
                 p._ats_expert = True
                 setattr(layer, attr, p)
             g = layer.gate.weight
-            layer.gate.weight = nn.Parameter(g.data[keep].clone())
-            layer.gate.out_features -= 1
-            layer.num_experts -= 1
+            layer.gate.weight = nn.Parameter(g.data[keep_gate].clone())
+            layer.gate.out_features -= W
+            layer.num_experts -= W
+            if layer.ep is not None:
+                layer.ep.num_experts = layer.num_experts
             layer.expert_demand = torch.zeros(layer.num_experts, dtype=torch.float64, device=g.device)
             done = True
         if done:
+            self.model.config.num_experts = max(l.num_experts for l in self.model.get_moe_layers())
+            self.config.num_experts = self.model.config.num_experts
             self.engine.rebuild(maps)
         return done
 

@@ -141,3 +141,64 @@ def test_zero3_matches_single_process(tmp_path):
     path = str(tmp_path / "ref3.pt")
     torch.save({k: v.clone() for k, v in model.state_dict().items()}, path)
     run_dist(_zero3_worker, 2, (path,))
+
+
+def _ep_add_prune_worker(rank, world, out_dir):
+    """Expert add / prune under expert parallelism: every rank grows / shrinks by one local expert, the replicated gate is
+    re-planned identically on all ranks, optimiser state of the surviving experts is kept, and training goes on."""
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200.config import Config
+    from adaptivetrainingsystem_b200.parallel import ProcessMesh
+    from adaptivetrainingsystem_b200.parallel.expert_parallel import attach_expert_parallel
+    from adaptivetrainingsystem_b200.training import EnhancedConversationTrainer
+    cfg = Config(vocab_size=512, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=128, seq_length=32,
+                 batch_size=2, micro_batch_size=2, gradient_accumulation_steps=1, num_epochs=1, precision="fp32", use_moe=True,
+                 num_experts=4, moe_top_k=2, capacity_factor=8.0, learning_rate=1e-3, output_dir=out_dir, experiment_name=f"r{rank}",
+                 log_every_n_steps=1, num_workers=0, gradient_checkpointing=False, zero_stage=1)
+    mesh = ProcessMesh(world, rank, ep_size=2)
+    cfg.world_size, cfg.expert_parallel_size = world, 2
+    torch.manual_seed(0)
+    full = DeepSeekTransformer(cfg.to_model_config())
+    model = DeepSeekTransformer(cfg.to_model_config(), ep_size=2, ep_rank=rank)
+    model.load_state_dict(full.state_dict())
+    attach_expert_parallel(model, mesh, cfg, use_fused=False)
+    tr = EnhancedConversationTrainer(model, None, cfg, mesh=mesh)
+    g = torch.Generator().manual_seed(11 + rank)
+    ids = torch.randint(0, 512, (2, 33), generator=g)
+    batch = {"input_ids": ids[:, :-1], "labels": ids[:, 1:]}
+
+    def one_step():
+        out = tr.train_step(batch)
+        tr.optimizer_step()
+        assert torch.isfinite(torch.as_tensor(float(out["loss"])))
+
+    one_step()
+    layer = model.get_moe_layers()[0]
+    w1_before = layer.experts_w1.data.clone()
+    st_before = tr.engine.state_dict()["state"]["layers.0.ffn.experts_w1"]["exp_avg"].clone()
+    assert tr.add_expert(0) == 1
+    assert layer.num_experts == 6 and layer.experts_w1.shape[0] == 3 and layer.gate.weight.shape[0] == 6 and layer.ep.num_experts == 6
+    assert torch.equal(layer.experts_w1.data[:2], w1_before)  # surviving local experts untouched
+    st_after = tr.engine.state_dict()["state"]["layers.0.ffn.experts_w1"]["exp_avg"]
+    assert torch.equal(st_after[:2], st_before) and float(st_after[2].abs().sum()) == 0.0  # moments kept / zero for the new expert
+    gate = layer.gate.weight.data.clone()
+    ref = gate.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(gate, ref), "gate rows differ across ranks after add_expert"
+    one_step()
+    one_step()
+    # prune the expert with global id 4 (= rank 1, local slot 1): slot 1 goes on every rank
+    assert tr.prune_expert(0, 4)
+    assert layer.num_experts == 4 and layer.experts_w1.shape[0] == 2 and layer.gate.weight.shape[0] == 4
+    gate = layer.gate.weight.data.clone()
+    ref = gate.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(gate, ref)
+    one_step()
+    assert not tr.prune_expert(0, 99)
+    # the other layer is untouched
+    assert model.get_moe_layers()[1].num_experts == 4
+
+
+def test_expert_add_prune_under_expert_parallelism(tmp_path):
+    run_dist(_ep_add_prune_worker, 2, (str(tmp_path),))
