@@ -202,3 +202,32 @@ def _ep_add_prune_worker(rank, world, out_dir):
 
 def test_expert_add_prune_under_expert_parallelism(tmp_path):
     run_dist(_ep_add_prune_worker, 2, (str(tmp_path),))
+
+
+def _ep_eval_worker(rank, world):
+    """Without autograd all MoE layers share one set of exchange buffers: the expert-parallel forward still equals the
+    single-process forward, for two different batch shapes in a row (buffers re-created on the capacity change)."""
+    from adaptivetrainingsystem_b200.inference import GenerationEngine
+    from adaptivetrainingsystem_b200.parallel import ProcessMesh
+    from adaptivetrainingsystem_b200.parallel.expert_parallel import attach_expert_parallel
+    mesh = ProcessMesh(world, rank, ep_size=2)
+    torch.manual_seed(0)
+    full = DeepSeekTransformer(ModelConfig(**CFG)).eval()
+    model = DeepSeekTransformer(ModelConfig(**CFG), ep_size=2, ep_rank=rank)
+    model.load_state_dict(full.state_dict())
+    comm = attach_expert_parallel(model, mesh, None, use_fused=False)
+    eng = GenerationEngine(model, pack_experts=True)  # packing is a GPU layout: a no-op for CPU weights
+    assert not getattr(model.get_moe_layers()[0].experts_w1, "_ats_packed", False)
+    g = torch.Generator().manual_seed(3)  # the same batch on every rank, as the serving path runs it
+    for shape in ((2, 32), (3, 17)):
+        ids = torch.randint(0, 512, shape, generator=g)
+        with torch.no_grad():
+            ref = full(ids, return_aux_loss=False)
+            out = eng.model(ids, return_aux_loss=False)
+        assert torch.allclose(out, ref, atol=2e-5, rtol=1e-4), (shape, (out - ref).abs().max())
+    ep_comm = model.get_moe_layers()[0].ep.comm
+    assert all(k[0] == -1 for k in ep_comm._layers), list(ep_comm._layers)  # one shared set, none per layer
+
+
+def test_expert_parallel_eval_shares_buffers():
+    run_dist(_ep_eval_worker, 2)
