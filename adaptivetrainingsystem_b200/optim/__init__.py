@@ -12,6 +12,7 @@ the vendored multi-tensor Adam / LAMB / SGD and CPU Adam kernels (colossalai ``e
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -223,8 +224,13 @@ class HostAdamWRule(UpdateRule):
     gradients.  ``master`` handed to ``update`` is ignored after the first call (the host copy is authoritative)."""
     name = "adamw_host"
 
-    def __init__(self, pin: bool = True):
+    def __init__(self, pin: bool = True, spill_dir: Optional[str] = None):
+        """``spill_dir``: keep master / m / v in memory-mapped files of that directory (a local NVMe mount) instead of pinned
+        host memory: the page cache holds what fits and the rest lives on the drive (the reference's ``nvme_offload_optimizer``
+        / ``nvme_path`` flags, which it only forwards to DeepSpeed, ``config/config_manager.py:79-85``)."""
         self.pin = pin
+        self.spill_dir = spill_dir
+        self._files = 0
         self._host: Dict[int, Dict[str, torch.Tensor]] = {}
 
     @staticmethod
@@ -236,7 +242,18 @@ class HostAdamWRule(UpdateRule):
         n = master.numel()
         pin = self.pin and torch.cuda.is_available()
         mk = lambda dt: torch.zeros(n, dtype=dt).pin_memory() if pin else torch.zeros(n, dtype=dt)  # noqa: E731
-        st = {"master_host": mk(torch.float32), "exp_avg": mk(torch.float32), "exp_avg_sq": mk(torch.float32),
+
+        def mapped(tag):
+            # file-backed fp32 state: written through the mapping by the host kernel, paged by the OS
+            os.makedirs(self.spill_dir, exist_ok=True)
+            path = os.path.join(self.spill_dir, f"ats_optim_{os.getpid()}_{self._files}_{tag}.bin")
+            self._files += 1
+            t = torch.from_file(path, shared=True, size=max(n, 1), dtype=torch.float32)[:n]
+            t.zero_()
+            return t
+
+        big = mapped if self.spill_dir else (lambda tag: mk(torch.float32))
+        st = {"master_host": big("master"), "exp_avg": big("m"), "exp_avg_sq": big("v"),
               "grad_host": mk(torch.bfloat16), "param_host": mk(torch.bfloat16)}
         st["master_host"].copy_(master.detach().float().cpu())
         return st

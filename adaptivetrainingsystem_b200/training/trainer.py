@@ -104,9 +104,13 @@ class EnhancedConversationTrainer:
             # optimiser choice: config.optimizer ("adamw" | "lamb" | "sgd"); the offload flags of the reference's DeepSpeed
             # section (cpu_offload / cpu_offload_optimizer) move the AdamW state to pinned host memory
             name = str(getattr(self.config, "optimizer", "adamw")).lower()
-            if name == "adamw" and (self.config.cpu_offload or self.config.cpu_offload_optimizer):
+            nvme = bool(getattr(self.config, "nvme_offload_optimizer", False) and getattr(self.config, "nvme_path", None))
+            if name == "adamw" and (self.config.cpu_offload or self.config.cpu_offload_optimizer or nvme):
                 name = "adamw_host"
-            self.engine = ShardedEngine(model, zero_stage=min(self.config.zero_stage, 2), fused_comm=fused_comm, optimizer=name, **opt)
+            # nvme_offload_optimizer + nvme_path: the host-side state lives in memory-mapped files under that path
+            okw = {"spill_dir": os.path.join(self.config.nvme_path, "ats_optimizer_state")} if (nvme and name == "adamw_host") else None
+            self.engine = ShardedEngine(model, zero_stage=min(self.config.zero_stage, 2), fused_comm=fused_comm, optimizer=name,
+                                        optimizer_kwargs=okw, **opt)
         self.optimizer = self.engine  # reference attribute name
         self.scheduler = None
         self.use_deepspeed = False

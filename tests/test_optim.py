@@ -1,4 +1,5 @@
 """Update rules (CPU bodies), host AdamW library, data-index and checkpoint-planner helpers."""
+import os
 import ctypes
 
 import numpy as np
@@ -188,3 +189,40 @@ def _lamb_sharded_worker(rank, world):
 def test_lamb_sharded_over_two_gloo_ranks():
     from dist_utils import run_dist
     run_dist(_lamb_sharded_worker, world=2)
+
+
+def test_host_adamw_with_file_backed_state(tmp_path):
+    """Optimiser state in memory-mapped files (the nvme_offload_optimizer / nvme_path flags): same numbers as the in-memory
+    rule, state files on disk, and a trainer built from the flags uses them."""
+    torch.manual_seed(3)
+    n = 4099
+    w0 = torch.randn(n)
+    a, b = optim.HostAdamWRule(pin=False), optim.HostAdamWRule(pin=False, spill_dir=str(tmp_path / "spill"))
+    ma, mb = w0.clone(), w0.clone()
+    sa, sb = a.init_state(ma), b.init_state(mb)
+    oa, ob = torch.zeros(n, dtype=torch.bfloat16), torch.zeros(n, dtype=torch.bfloat16)
+    for step in range(1, 4):
+        g = torch.randn(n).bfloat16()
+        a.update(sa, ma, g, oa, _hyper(step=float(step)), torch.tensor([1.0, 0.0, 0.0, 0.0]), True)
+        b.update(sb, mb, g, ob, _hyper(step=float(step)), torch.tensor([1.0, 0.0, 0.0, 0.0]), True)
+    assert torch.equal(sa["master_host"], sb["master_host"]) and torch.equal(oa, ob)
+    files = sorted(os.listdir(tmp_path / "spill"))
+    assert len(files) == 3 and all(os.path.getsize(tmp_path / "spill" / f) >= 4 * n for f in files)
+    # through the trainer's configuration flags
+    from adaptivetrainingsystem_b200.config import ConfigPresets
+    from adaptivetrainingsystem_b200.models.transformer import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.training import EnhancedConversationTrainer
+    cfg = ConfigPresets.tiny_cpu()
+    cfg.nvme_offload_optimizer, cfg.nvme_path, cfg.output_dir = True, str(tmp_path / "nvme"), str(tmp_path / "out")
+    torch.manual_seed(0)
+    model = DeepSeekTransformer(cfg.to_model_config())
+    tr = EnhancedConversationTrainer(model, None, cfg)
+    assert tr.engine.optimizer_name == "adamw_host" and tr.engine.rule.spill_dir.startswith(str(tmp_path / "nvme"))
+    ids = torch.randint(0, cfg.vocab_size, (2, 17))
+    first = None
+    for _ in range(4):
+        out = tr.train_step({"input_ids": ids[:, :-1], "labels": ids[:, 1:]})
+        tr.optimizer_step()
+        first = first if first is not None else float(out["loss"])
+    assert float(out["loss"]) < first
+    assert os.listdir(tmp_path / "nvme" / "ats_optimizer_state")
