@@ -24,7 +24,7 @@ def _close(got, ref, tol=2e-2, what=""):
     assert err / denom < tol, f"{what}: max err {err} vs scale {denom}"
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (37, 4096), (16, 8192)])
+@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (37, 4096), (16, 8192), (4096, 2048), (2048, 1024)])
 def test_rmsnorm_fwd_bwd(rows, cols):
     torch.manual_seed(0)
     x = _rand(rows, cols).requires_grad_()
@@ -35,6 +35,23 @@ def test_rmsnorm_fwd_bwd(rows, cols):
     xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
     yf = ops.rms_norm_reference(xf, wf, 1e-6)
     yf.backward(gy.float())
+    _close(y, yf, what="y")
+    _close(x.grad, xf.grad, what="dx")
+    _close(w.grad, wf.grad, tol=3e-2, what="dw")
+
+
+def test_rmsnorm_skip_backward_many_rows():
+    """Pre-norm node (norm output + residual pass-through) at a row count that takes the warp-per-row backward kernel."""
+    torch.manual_seed(2)
+    rows, cols = 2048, 2048
+    x = _rand(rows, cols).requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y, skip = ops.functional.rms_norm_skip(x, w, 1e-6)
+    gy, gs = _rand(rows, cols), _rand(rows, cols)
+    torch.autograd.backward([y, skip], [gy, gs])
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = ops.rms_norm_reference(xf, wf, 1e-6)
+    torch.autograd.backward([yf, xf * 1.0], [gy.float(), gs.float()])
     _close(y, yf, what="y")
     _close(x.grad, xf.grad, what="dx")
     _close(w.grad, wf.grad, tol=3e-2, what="dw")
