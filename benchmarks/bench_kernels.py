@@ -3,7 +3,9 @@
 the fraction of the measured roofline (``MEASURED_PEAKS.json``: cuBLAS bf16 burst throughput, STREAM-style copy
 bandwidth).  A library column (cuBLAS / PyTorch eager) is printed next to each kernel for comparison.
 
-    python benchmarks/bench_kernels.py [--quick] [--json out.json]
+    python benchmarks/bench_kernels.py [--quick] [--json out.json] [--only gemm,fp8,swiglu,grouped,memory,adamw,attention]
+
+``--only memory`` (or any other single section) keeps a run short enough for a profiler capture of one kernel.
 """
 from __future__ import annotations
 
@@ -31,7 +33,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--json", default="")
+    ap.add_argument("--only", default="", help="comma-separated sections: gemm, fp8, swiglu, grouped, memory, adamw, attention")
     args = ap.parse_args()
+    only = {t.strip() for t in args.only.split(",") if t.strip()}
+
+    def want(section):
+        return not only or section in only
     pk = measured_peaks()
     rows = []
 
@@ -48,7 +55,7 @@ def main():
               (4096, 28672, 4096), (4096, 4096, 14336), (8192, 8192, 8192)]
     if args.quick:
         shapes = shapes[:2] + shapes[-1:]
-    for (m, n, k) in shapes:
+    for (m, n, k) in shapes if want("gemm") else []:
         a, b, bt, at = rnd(m, k), rnd(n, k), rnd(k, n), rnd(k, m)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
         fl = 2.0 * m * n * k
@@ -58,7 +65,7 @@ def main():
         report(f"gemm_tn {m}x{n}x{k}", time_cuda(lambda: G.gemm_tn(at, bt, out=out)), fl, lib_ms=time_cuda(lambda: torch.matmul(at.t(), bt, out=out)))
     # fp8 (e4m3, per-row / per-channel scales) forward GEMM against the bf16 kernel and the library
     from adaptivetrainingsystem_b200.ops import fp8
-    for (m, n, k) in [(8192, 8192, 8192), (16384, 2560, 2048)]:
+    for (m, n, k) in [(8192, 8192, 8192), (16384, 2560, 2048)] if want("fp8") else []:
         a, b = rnd(m, k), rnd(n, k, scale=0.05)
         aq, sa = fp8.quantize_rows(a)
         bq, sb = fp8.quantize_rows(b)
@@ -67,13 +74,13 @@ def main():
                lib_ms=time_cuda(lambda: torch.matmul(a, b.t(), out=out)))
         report(f"quantize_rows_e4m3 {m}x{k}", time_cuda(lambda: fp8.quantize_rows(a)), nbytes=3.0 * m * k)
     # SwiGLU-fused GEMM
-    for (m, k, i) in [(8192, 2048, 5632), (4096, 4096, 14336)]:
+    for (m, k, i) in [(8192, 2048, 5632), (4096, 4096, 14336)] if want("swiglu") else []:
         a, w = rnd(m, k), rnd(2 * i, k, scale=0.05)
         h = torch.empty(m, i, dtype=torch.bfloat16, device=DEV)
         lib = time_cuda(lambda: ops.swiglu_reference(torch.matmul(a, w.t())))
         report(f"gemm_swiglu {m}x{2 * i}x{k}", time_cuda(lambda: G.gemm_nt_swiglu(a, w, out=h)), 2.0 * m * 2 * i * k, lib_ms=lib)
     # grouped expert GEMM (8 experts, capacity layout)
-    for (e, c, k, n) in [(8, 2560, 2048, 11264), (8, 1280, 4096, 28672)][: 1 if args.quick else 2]:
+    for (e, c, k, n) in [(8, 2560, 2048, 11264), (8, 1280, 4096, 28672)][: 1 if args.quick else 2] if want("grouped") else []:
         x, w = rnd(e, c, k), rnd(e, n, k, scale=0.05)
         counts = torch.full((e,), c - 200, dtype=torch.int32, device=DEV)
         out = torch.empty(e, c, n // 2, dtype=torch.bfloat16, device=DEV)
@@ -81,31 +88,40 @@ def main():
         lib = time_cuda(lambda: [torch.matmul(x[j], w[j].t()) for j in range(e)])
         report(f"grouped_swiglu E{e} C{c} {k}->{n}", time_cuda(lambda: G.grouped_nt(x, w, counts, swiglu=True, out=out)),
                2.0 * e * used * n * k, lib_ms=lib)
-    # memory-bound kernels
-    rows_, cols = 16384, 2048
-    x, wn = rnd(rows_, cols), torch.ones(cols, device=DEV, dtype=torch.bfloat16)
-    xg = x.detach().clone().requires_grad_()
-    wg = wn.detach().clone().requires_grad_()
-    yg = ops.rms_norm(xg, wg, 1e-6)
-    gy = rnd(rows_, cols)
-    report("rmsnorm_bwd 16384x2048", time_cuda(lambda: torch.autograd.grad(yg, (xg, wg), gy, retain_graph=True)), nbytes=3.0 * rows_ * cols * 2)
-    report("rmsnorm_fwd 16384x2048", time_cuda(lambda: ops.rms_norm(x, wn, 1e-6)), nbytes=2.0 * rows_ * cols * 2,
-           lib_ms=time_cuda(lambda: ops.rms_norm_reference(x, wn, 1e-6)))
-    gu = rnd(rows_, 2 * 5632)
-    report("swiglu_fwd 16384x5632", time_cuda(lambda: ops.swiglu(gu)), nbytes=3.0 * rows_ * 5632 * 2,
-           lib_ms=time_cuda(lambda: ops.swiglu_reference(gu)))
-    logits = rnd(4096, 32000)
-    labels = torch.randint(0, 32000, (4096,), device=DEV)
-    report("cross_entropy 4096x32000 (fwd+grad)", time_cuda(lambda: ops.cross_entropy(logits, labels)[0]), nbytes=2.0 * 4096 * 32000 * 2,
-           lib_ms=time_cuda(lambda: torch.nn.functional.cross_entropy(logits.float(), labels)))
-    n = 256 * 1024 * 1024
-    master, m1, v1 = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
-    g, p = rnd(n), rnd(n)
-    hyper = torch.tensor([1e-3, 0.9, 0.95, 1e-8, 0.01, 1.0], device=DEV)
-    report("adamw 256M", time_cuda(lambda: ops.adamw_step(master, m1, v1, g, p, hyper, None), iters=5), nbytes=n * (12 * 2 + 2 + 2))
-    del master, m1, v1, g, p
+    def memory_section():
+        # memory-bound kernels
+        rows_, cols = 16384, 2048
+        x, wn = rnd(rows_, cols), torch.ones(cols, device=DEV, dtype=torch.bfloat16)
+        xg = x.detach().clone().requires_grad_()
+        wg = wn.detach().clone().requires_grad_()
+        yg = ops.rms_norm(xg, wg, 1e-6)
+        gy = rnd(rows_, cols)
+        report("rmsnorm_bwd 16384x2048", time_cuda(lambda: torch.autograd.grad(yg, (xg, wg), gy, retain_graph=True)), nbytes=3.0 * rows_ * cols * 2)
+        report("rmsnorm_fwd 16384x2048", time_cuda(lambda: ops.rms_norm(x, wn, 1e-6)), nbytes=2.0 * rows_ * cols * 2,
+               lib_ms=time_cuda(lambda: ops.rms_norm_reference(x, wn, 1e-6)))
+        gu = rnd(rows_, 2 * 5632)
+        report("swiglu_fwd 16384x5632", time_cuda(lambda: ops.swiglu(gu)), nbytes=3.0 * rows_ * 5632 * 2,
+               lib_ms=time_cuda(lambda: ops.swiglu_reference(gu)))
+        logits = rnd(4096, 32000)
+        labels = torch.randint(0, 32000, (4096,), device=DEV)
+        report("cross_entropy 4096x32000 (fwd+grad)", time_cuda(lambda: ops.cross_entropy(logits, labels)[0]), nbytes=2.0 * 4096 * 32000 * 2,
+               lib_ms=time_cuda(lambda: torch.nn.functional.cross_entropy(logits.float(), labels)))
+
+    if want("memory"):
+        memory_section()
+
+    def adamw_section():
+        n = 256 * 1024 * 1024
+        master, m1, v1 = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        g, p = rnd(n), rnd(n)
+        hyper = torch.tensor([1e-3, 0.9, 0.95, 1e-8, 0.01, 1.0], device=DEV)
+        report("adamw 256M", time_cuda(lambda: ops.adamw_step(master, m1, v1, g, p, hyper, None), iters=5), nbytes=n * (12 * 2 + 2 + 2))
+        del master, m1, v1, g, p
+
+    if want("adamw"):
+        adamw_section()
     # attention
-    for (bsz, L, hq, hkv, d) in [(4, 2048, 32, 4, 64), (1, 4096, 32, 8, 128)]:
+    for (bsz, L, hq, hkv, d) in [(4, 2048, 32, 4, 64), (1, 4096, 32, 8, 128)] if want("attention") else []:
         q, k, v = rnd(bsz, L, hq, d), rnd(bsz, L, hkv, d), rnd(bsz, L, hkv, d)
         fl = 4.0 * bsz * hq * L * L * d / 2
         from adaptivetrainingsystem_b200.ops import attn as A
