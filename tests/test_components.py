@@ -274,3 +274,27 @@ def test_swiglu_backward_gemm_reference_matches_autograd():
     counts = torch.tensor([M], dtype=torch.int32)
     dgu_g, h_g = G.grouped_nn_swiglu_bwd(dy.view(1, M, H), w2.view(1, H, I), counts, pre.detach().view(1, M, 2 * I))
     assert torch.allclose(dgu_g[0], pre.grad, atol=1e-5) and torch.allclose(h_g[0], h_ref.detach(), atol=1e-5)
+
+
+def test_skinny_product_split_rule_and_weight_packing():
+    """Host-side rules of the serving GEMM paths: when the reduction is split, and the tile-packed weight layout."""
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    assert G._skinny_splits(64, 4096, 14336) == 8      # 16 output tiles: spread over 8 x 16 CTAs
+    assert G._skinny_splits(64, 6144, 4096) == 4
+    assert G._skinny_splits(64, 28672, 4096) == 1      # 112 tiles already fill the GPU
+    assert G._skinny_splits(256, 4096, 14336) == 1     # not skinny
+    assert G._skinny_splits(64, 4096, 1024) == 1       # reduction too short to split
+    for m, n, k in ((1, 256, 2048), (128, 512, 8192), (64, 4096, 4096)):
+        s = G._skinny_splits(m, n, k)
+        assert k % (s * 64) == 0 and k // s >= 512 and s * ((n + 255) // 256) <= 160
+    w = torch.arange(2 * 256 * 128, dtype=torch.float32).view(2, 256, 128)
+    p = G.pack_kmajor(w)
+    assert p.shape == w.shape and torch.equal(G.unpack_kmajor(p), w)
+    # box (weight 1, row block 1, k block 1) is one contiguous run of 128 x 64 elements
+    off = ((1 * 2 + 1) * 2 + 1) * 128 * 64
+    assert torch.equal(p.reshape(-1)[off:off + 128 * 64].view(128, 64), w[1, 128:256, 64:128])
+    with pytest.raises(ValueError):
+        G.pack_kmajor(torch.zeros(100, 64))
+    x = torch.randn(2, 128, 128)
+    counts = torch.tensor([128, 7], dtype=torch.int32)
+    assert torch.allclose(G.grouped_nt(x, w * 1e-4, counts), G.grouped_nt(x, G.pack_kmajor(w * 1e-4), counts, packed=True))
