@@ -1,5 +1,20 @@
+"""Uniform backend wrapper (reference ``backend/backend_fsdp.py:311-616``, ``backend_deepspeed.py:211-467``,
+``backend_colossalai.py:79-141``): ``__call__ / backward / step / zero_grad / train / eval / state_dict / load_state_dict /
+get_lr / get_global_grad_norm / save_checkpoint / load_checkpoint / module / world_size / local_rank / is_main_process /
+get_memory_stats``.  The three factory names of the reference select a sharding stage of the native engines:
+
+* FSDP ``FULL_SHARD`` / ``HYBRID_SHARD``, DeepSpeed ``zero_stage=3`` and the ColossalAI ``gemini`` plugin build
+  :class:`~adaptivetrainingsystem_b200.parallel.zero3.ZeRO3Engine` (parameters, gradients and optimiser state sharded);
+* ``SHARD_GRAD_OP`` / stage 1-2 / ``low_level_zero`` build :class:`~adaptivetrainingsystem_b200.parallel.zero.ShardedEngine`
+  (replicated bf16 parameters, sharded fp32 master weights and moments, fused peer-memory step);
+* ``NO_SHARD`` / stage 0 is bucketed data parallelism.
+
+Expert-parallel models keep their experts partitioned by expert parallelism and run the dense part at stage <= 2 (a stage-3
+request is downgraded with a warning, never silently).
+"""
 from __future__ import annotations
 
+import logging
 import os
 from typing import Any, Dict, Optional
 
@@ -24,9 +39,18 @@ class NativeBackend:
         if self.mesh.world > 1 and getattr(config, "fused_comm", True) and torch.cuda.is_available():
             from ..parallel.expert_parallel import attach_expert_parallel
             fused = attach_expert_parallel(model, self.mesh, config, use_fused=True)
-        self.engine = ShardedEngine(model, lr=config.learning_rate, betas=(config.adam_beta1, config.adam_beta2), eps=config.adam_eps,
-                                    weight_decay=config.weight_decay, max_grad_norm=config.max_grad_norm, zero_stage=min(stage, 2),
-                                    mesh=self.mesh, fused_comm=fused, grad_accumulation_steps=config.gradient_accumulation_steps)
+        opt = dict(lr=config.learning_rate, betas=(config.adam_beta1, config.adam_beta2), eps=config.adam_eps,
+                   weight_decay=config.weight_decay, max_grad_norm=config.max_grad_norm, mesh=self.mesh,
+                   grad_accumulation_steps=config.gradient_accumulation_steps)
+        self.requested_stage = stage
+        if stage >= 3 and self.mesh.ep_size == 1 and self.mesh.world > 1:
+            from ..parallel.zero3 import ZeRO3Engine
+            self.engine = ZeRO3Engine(model, fused_comm=fused, **opt)
+        else:
+            if stage >= 3:
+                why = "one process" if self.mesh.world == 1 else f"expert parallelism (ep={self.mesh.ep_size}) partitions the experts"
+                logging.getLogger(__name__).warning("%s backend: stage 3 requested, running stage 2 (%s)", name, why)
+            self.engine = ShardedEngine(model, zero_stage=min(stage, 2), fused_comm=fused, **opt)
         self.scheduler = None
         self.checkpoints = CheckpointManager(config, os.path.join(config.output_dir, config.experiment_name or "run", "checkpoints"))
         self.global_step = 0

@@ -267,6 +267,7 @@ class Config:
     num_experts: int = 8
     moe_top_k: int = 2
     capacity_factor: float = 1.25
+    drop_tokens: bool = True  # enforce capacity_factor (routed slots beyond it are dropped); False = dropless, as the reference's live layer
     load_balancing_weight: float = 0.01
     routing_temperature: float = 1.0
     routing_noise_std: float = 0.0
@@ -320,8 +321,9 @@ class Config:
     enable_wandb: bool = False
     wandb_project: Optional[str] = None
     wandb_entity: Optional[str] = None
-    comm_timeout_s: float = 1.0
-    heartbeat_interval_s: float = 0.5
+    comm_timeout_s: float = 1.0        # budget of every in-kernel wait on a peer (flag barriers, gathered-weight chunks)
+    heartbeat_interval_s: float = 0.5  # period of the rank heartbeat (parallel/health.py); 0 switches the watchdog off
+    heartbeat_timeout_s: float = 30.0  # a peer whose heartbeat is older than this counts as lost
     # -- adaptive LR ------------------------------------------------------------
     enable_adaptive_lr: bool = True
     allow_scheduler_override: bool = True
@@ -480,7 +482,7 @@ class Config:
             use_stable_embedding=self.use_stable_embedding, tie_word_embeddings=self.tie_word_embeddings,
             gradient_checkpointing=self.gradient_checkpointing, use_flash_attention=self.use_flash_attention,
             use_moe=self.use_moe, num_experts=self.num_experts, moe_top_k=self.moe_top_k,
-            capacity_factor=self.capacity_factor, load_balancing_weight=self.load_balancing_weight,
+            capacity_factor=self.capacity_factor, drop_tokens=self.drop_tokens, load_balancing_weight=self.load_balancing_weight,
             routing_temperature=self.routing_temperature, routing_noise_std=self.routing_noise_std,
             moe_pattern=self.moe_pattern, use_mod=self.use_mod, mod_capacity_factor=self.mod_capacity_factor,
             mod_routing_temperature=self.mod_routing_temperature,

@@ -63,6 +63,7 @@ class FusedComm:
         lib = _L()
         stream = _lib.stream_ptr(self.device)
         W, r = self.world, self.rank
+        status = _lib.status_tensor(self.device)  # kernels after a timed-out barrier leave every buffer as it is
         for b in engine.buckets:
             b.collect_autograd_grads()
         self.barrier()  # (1)
@@ -77,7 +78,7 @@ class FusedComm:
                     self._g32[id(b)] = g32
                 _lib.check(lib.ats_peer_reduce_shard(self._table(b.flat_grad), W, r, r * b.shard, b.shard, _lib.ptr(g32),
                                                      _lib.ptr(self._partial), _lib.ptr(self._sumsq), 0 if first else 1,
-                                                     stream), "peer_reduce_shard")
+                                                     _lib.ptr(status), stream), "peer_reduce_shard")
             first = False
         self.barrier(self._sumsq)  # (3)
         scale = 1.0 / (engine.mesh.dp_size * engine.grad_accumulation_steps)
@@ -92,7 +93,8 @@ class FusedComm:
             else:
                 _lib.check(lib.ats_adamw_push(_lib.ptr(b.master), _lib.ptr(b.exp_avg), _lib.ptr(b.exp_avg_sq),
                                               _lib.ptr(self._g32[id(b)]), self._table(b.flat_param), W, r, r * b.shard, b.shard,
-                                              _lib.ptr(engine.hyper), _lib.ptr(engine.clip_state), wd, stream), "adamw_push")
+                                              _lib.ptr(engine.hyper), _lib.ptr(engine.clip_state), wd, _lib.ptr(status), stream),
+                           "adamw_push")
         self.barrier()  # (5)
 
     def bytes_over_nvlink_per_step(self, engine) -> int:

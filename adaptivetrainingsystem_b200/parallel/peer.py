@@ -35,10 +35,14 @@ def _L():
         sig("ats_ipc_open", ctypes.c_char_p, ctypes.POINTER(_vp))
         sig("ats_ipc_close", _vp)
         sig("ats_ipc_free", _vp)
-        sig("ats_peer_barrier", ctypes.POINTER(_vp), ctypes.POINTER(_vp), _vp, _c_int, _c_int, _c_int, _vp, _vp)
-        sig("ats_peer_reduce_shard", ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _vp, _c_int, _vp)
+        sig("ats_peer_barrier", ctypes.POINTER(_vp), ctypes.POINTER(_vp), _vp, _c_int, _c_int, _vp, _vp, _vp)
+        sig("ats_peer_reduce_shard", ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _vp, _c_int, _vp, _vp)
         sig("ats_clip_coef_slots", _vp, _c_int, _c_f, _c_f, _vp, _vp)
-        sig("ats_adamw_push", _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _c_f, _vp)
+        sig("ats_adamw_push", _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _c_f, _vp, _vp)
+        lib.ats_set_wait_budget_ns.restype = None
+        lib.ats_set_wait_budget_ns.argtypes = [ctypes.c_ulonglong]
+        lib.ats_get_wait_budget_ns.restype = ctypes.c_ulonglong
+        lib.ats_get_wait_budget_ns.argtypes = []
         sig("ats_peer_copy", _vp, _vp, _c_ll, _c_int, _vp)
         _sig = True
     return lib
@@ -120,27 +124,46 @@ class SymmetricBuffer:
             self.local_ptr = 0
 
 
+def set_wait_budget(seconds: Optional[float]) -> None:
+    """Budget of every wait on a peer (flag barriers, gathered-weight chunks) in launches issued after this call;
+    ``None`` restores the default of one second.  ``Config.peer_wait_budget_s`` is applied through this."""
+    _L().ats_set_wait_budget_ns(0 if seconds is None else max(1, int(seconds * 1e9)))
+
+
+def get_wait_budget() -> float:
+    return _L().ats_get_wait_budget_ns() / 1e9
+
+
 class PeerBarrier:
     """Flag barrier across the ranks of a group, executed by a one-warp kernel on the caller's stream.  Optionally
-    carries one float from every rank to every rank (``slots`` then holds the ``world`` values)."""
+    carries one float from every rank to every rank (``slots`` then holds the ``world`` values).
+
+    The epoch that the ranks exchange is a counter in device memory which the kernel itself advances, so a barrier
+    that was captured into a CUDA graph synchronises on every replay (a host-side epoch would be frozen into the
+    captured launch and every replay after the first would fall through on the stale flags)."""
 
     def __init__(self, group=None, device: Optional[torch.device] = None):
         self.group = group
-        self.buf = SymmetricBuffer(1024, group, device)  # [0:256) flags (int32[<=64]), [256:512) payload slots (float[<=64])
+        # [0:256) flags (int32[<=64]), [256:512) payload slots (float[<=64]), [512:516) this rank's epoch counter
+        self.buf = SymmetricBuffer(1024, group, device)
         self.world, self.rank = self.buf.world, self.buf.rank
-        self.epoch = 0
         self.flags = self.buf.tensor(torch.int32, 64, 0)
         self.slots = self.buf.tensor(torch.float32, 64, 256)
+        self.epoch_counter = self.buf.tensor(torch.int32, 1, 512)
         self._flag_table = self.buf.table(0)
         self._slot_table = self.buf.table(256)
         if self.world > 1:
             dist.barrier(group)  # every rank's flags are zeroed and mapped before the first device barrier
 
+    @property
+    def epoch(self) -> int:
+        """Number of barriers executed so far (reads device memory: diagnostics and tests only)."""
+        return int(self.epoch_counter.item())
+
     def __call__(self, payload: Optional[torch.Tensor] = None) -> None:
-        self.epoch += 1
         st = _lib.status_tensor(self.buf.device)
         _lib.check(_L().ats_peer_barrier(self._flag_table, self._slot_table if payload is not None else None,
-                                         _lib.ptr(payload), self.rank, self.world, self.epoch, _lib.ptr(st),
+                                         _lib.ptr(payload), self.rank, self.world, _lib.ptr(self.epoch_counter), _lib.ptr(st),
                                          _lib.stream_ptr(self.buf.device)), "peer_barrier")
 
 

@@ -135,7 +135,8 @@ class ZeRO3Engine:
     ``set_lr`` ...), for dense models split into block units."""
 
     def __init__(self, model: nn.Module, lr: float = 1e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.01,
-                 max_grad_norm: float = 1.0, mesh: Optional[ProcessMesh] = None, grad_accumulation_steps: int = 1, prefetch: bool = True):
+                 max_grad_norm: float = 1.0, mesh: Optional[ProcessMesh] = None, grad_accumulation_steps: int = 1, prefetch: bool = True,
+                 fused_comm=None):
         self.model = model
         self.mesh = mesh or ProcessMesh(create_groups=False)
         self.zero_stage = 3

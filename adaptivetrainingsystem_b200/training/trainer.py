@@ -99,8 +99,11 @@ class EnhancedConversationTrainer:
                    grad_accumulation_steps=self.config.gradient_accumulation_steps)
         if self.config.zero_stage >= 3 and self.mesh.ep_size == 1 and self.mesh.world > 1:
             from ..parallel.zero3 import ZeRO3Engine
-            self.engine = ZeRO3Engine(model, **opt)  # per-block gather / release; expert-parallel models use stage <= 2
+            self.engine = ZeRO3Engine(model, fused_comm=fused_comm, **opt)  # per-block gather / release
         else:
+            if self.config.zero_stage >= 3 and self.mesh.world > 1:
+                self.logger.warning("zero_stage 3 requested with expert parallelism (ep=%d): experts stay partitioned by expert "
+                                    "parallelism, the dense part runs stage 2", self.mesh.ep_size)
             # optimiser choice: config.optimizer ("adamw" | "lamb" | "sgd"); the offload flags of the reference's DeepSpeed
             # section (cpu_offload / cpu_offload_optimizer) move the AdamW state to pinned host memory
             name = str(getattr(self.config, "optimizer", "adamw")).lower()
@@ -147,6 +150,19 @@ class EnhancedConversationTrainer:
         self._last_step_time = time.perf_counter()
         self._inject_oom_at: Optional[int] = None
 
+        # failure detection: in-kernel waits on peers give up after comm_timeout_s (status word -> KernelError on the host);
+        # a heartbeat through the rendezvous store tells the survivors of a lost rank before they launch the next step
+        self.heartbeat = None
+        if self.mesh.world > 1:
+            import torch.distributed as _dist
+            if fused_comm is not None and self.device.type == "cuda":
+                from ..parallel.peer import set_wait_budget
+                set_wait_budget(float(getattr(self.config, "comm_timeout_s", 1.0) or 1.0))
+            hb = float(getattr(self.config, "heartbeat_interval_s", 0.0) or 0.0)
+            if hb > 0 and _dist.is_initialized():
+                from ..parallel.health import Heartbeat
+                self.heartbeat = Heartbeat(interval_s=hb, timeout_s=float(getattr(self.config, "heartbeat_timeout_s", 30.0))).start()
+
     # ------------------------------------------------------------------------------------------------------
     # loss
     # ------------------------------------------------------------------------------------------------------
@@ -179,6 +195,8 @@ class EnhancedConversationTrainer:
         if self._inject_oom_at is not None and self.micro_step == self._inject_oom_at:
             self._inject_oom_at = None
             raise SyntheticOOM()
+        if self.heartbeat is not None:
+            self.heartbeat.check()  # a lost peer surfaces here, on the host, before any kernel waits for it
         self.model.train()
         batch = self._to_device(batch)
         labels = batch["labels"]
@@ -423,6 +441,12 @@ class EnhancedConversationTrainer:
         except OSError:
             pass
 
+    def shutdown(self, leaving: bool = False) -> None:
+        """Stop the heartbeat thread.  ``leaving=True`` announces an orderly departure to the peers (only between steps)."""
+        if self.heartbeat is not None:
+            (self.heartbeat.leave if leaving else self.heartbeat.stop)()
+            self.heartbeat = None
+
     def inject_oom(self, at_micro_step: Optional[int] = None) -> None:
         """Host-side fault injection: the next (or the given) micro-step raises a synthetic OOM."""
         self._inject_oom_at = self.micro_step if at_micro_step is None else at_micro_step
@@ -431,6 +455,8 @@ class EnhancedConversationTrainer:
     # checkpoints
     # ------------------------------------------------------------------------------------------------------
     def save_checkpoint(self, epoch: int, tag: Optional[str] = None) -> Optional[str]:
+        if self.device.type == "cuda":
+            ops.check_status()  # never write a state that a timed-out kernel wait may have left half-updated
         return self.checkpoint_manager.save_checkpoint(
             self.model, self.engine, self.scheduler, self.global_step, epoch, self.metrics, tag, mesh=self.mesh)
 

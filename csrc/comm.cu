@@ -30,11 +30,25 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// flags.p[r] = base of rank r's flag array (int[world]).  Thread t: optionally stores the payload into peer t's
-// payload slot [rank], releases epoch into peer t's flags[rank], then waits for flags[t] of its own array.
+// Wait budget of every peer wait in this library (nanoseconds of %globaltimer).  A host-side value handed to the kernels as
+// an argument, so a test can make a wait give up after a few milliseconds and production runs can allow slow peers more
+// than the one-second default.
+static unsigned long long g_wait_budget_ns = ATS_WAIT_BUDGET_NS;
+
+// flags.p[r] = base of rank r's flag array (int[world]).  The epoch lives in device memory (`epoch_counter`, private to
+// this rank): thread 0 advances it, so a launch that is replayed from a CUDA graph still waits for a NEW arrival of
+// every peer instead of re-using the epoch that was frozen into the captured arguments.  All ranks issue their barriers
+// in the same order, so their counters agree.  Thread t: optionally stores the payload into peer t's payload slot
+// [rank], releases the epoch into peer t's flags[rank], then waits (bounded) for flags[t] of its own array.
 __global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const float* payload_src, int rank, int world,
-                                    int epoch, int* status) {
+                                    int* epoch_counter, unsigned long long budget_ns, int* status) {
   const int t = threadIdx.x;
+  int epoch = 0;
+  if (t == 0) {
+    epoch = *epoch_counter + 1;
+    *epoch_counter = epoch;
+  }
+  epoch = __shfl_sync(0xffffffffu, epoch, 0);
   if (t >= world) return;
   if (payload_src) {
     float v = *payload_src;
@@ -45,7 +59,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const 
   const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + t;
   const uint64_t t0 = globaltimer_ns();
   while (ld_acquire_sys(mine) < epoch) {
-    if (globaltimer_ns() - t0 > ATS_WAIT_BUDGET_NS) {
+    if (globaltimer_ns() - t0 > budget_ns) {
       if (status) atomicCAS(status, 0, kTimeoutPeerFlag);
       return;
     }
@@ -57,9 +71,15 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const 
 // out32[i] = sum_p grads_p[offset + i]  (i < n, n % 8 == 0); partial[block] = sum of squares of this block's part.
 __global__ void __launch_bounds__(256)
 peer_reduce_shard_kernel(PeerPtrs grads, int world, int rank, long long offset, long long n, float* __restrict__ out32,
-                         float* __restrict__ partial) {
+                         float* __restrict__ partial, const int* __restrict__ status) {
   __shared__ float red[33];
   float ss = 0.f;
+  // a barrier before this launch gave up on a peer: its gradients may be partial, so nothing is read or written
+  // (the update kernel makes the same check; the host raises at its next status check)
+  if (status && *status != 0) {
+    if (threadIdx.x == 0) partial[blockIdx.x] = 0.f;
+    return;
+  }
   const long long nvec = n >> 3;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -104,7 +124,8 @@ __global__ void clip_coef_slots_kernel(const float* slots, int world, float pre_
 __global__ void __launch_bounds__(256)
 adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, const float* __restrict__ g32,
                   PeerPtrs params, int world, int rank, long long offset, long long n, const float* __restrict__ hyper,
-                  const float* __restrict__ clip_state, float wd_mult) {
+                  const float* __restrict__ clip_state, float wd_mult, const int* __restrict__ status) {
+  if (status && *status != 0) return;  // a peer wait of this step gave up: keep master weights, moments and parameters as they are
   const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4] * wd_mult, step = hyper[5];
   float gscale = 1.f;
   if (clip_state) {
@@ -184,26 +205,32 @@ ATS_API int ats_ipc_free(void* ptr) { return int(cudaFree(ptr)); }
 
 // ---- kernels ------------------------------------------------------------------------------------------------
 // flags / payload_dst: host arrays of `world` device pointers (one per rank, peer-mapped).
+// epoch_counter: one int in this rank's device memory, zero before the first barrier of this flag set.
 ATS_API int ats_peer_barrier(void* const* flags, void* const* payload_dst, const float* payload_src, int rank, int world,
-                             int epoch, int* status, void* stream) {
-  if (world > MAX_PEERS) return 1003;
+                             int* epoch_counter, int* status, void* stream) {
+  if (world > MAX_PEERS || !epoch_counter) return 1003;
   PeerPtrs none = {};
   peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(flags, world),
                                                                       payload_dst ? to_peers(payload_dst, world) : none,
-                                                                      payload_src, rank, world, epoch, status);
+                                                                      payload_src, rank, world, epoch_counter, g_wait_budget_ns,
+                                                                      status);
   return int(cudaGetLastError());
 }
+
+// Budget of every peer wait launched after this call (0 restores the default of one second).
+ATS_API void ats_set_wait_budget_ns(unsigned long long ns) { g_wait_budget_ns = ns ? ns : ATS_WAIT_BUDGET_NS; }
+ATS_API unsigned long long ats_get_wait_budget_ns() { return g_wait_budget_ns; }
 
 // Reduce this rank's shard [offset, offset + n) of the gradient buckets of all ranks into out32 and its squared sum
 // into sumsq[0] (added when accumulate).  partial: >= 1184 floats of scratch.
 ATS_API int ats_peer_reduce_shard(void* const* grads, int world, int rank, long long offset, long long n, float* out32,
-                                  float* partial, float* sumsq, int accumulate, void* stream) {
+                                  float* partial, float* sumsq, int accumulate, const int* status, void* stream) {
   if (world > MAX_PEERS || (n & 7) || (offset & 7)) return 1003;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   long long blocks = (n / 8 + 255) / 256;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  peer_reduce_shard_kernel<<<(unsigned)blocks, 256, 0, s>>>(to_peers(grads, world), world, rank, offset, n, out32, partial);
+  peer_reduce_shard_kernel<<<(unsigned)blocks, 256, 0, s>>>(to_peers(grads, world), world, rank, offset, n, out32, partial, status);
   sum_partials_kernel<<<1, 256, 0, s>>>(partial, (int)blocks, sumsq, accumulate);
   return int(cudaGetLastError());
 }
@@ -215,13 +242,13 @@ ATS_API int ats_clip_coef_slots(const float* slots, int world, float pre_scale, 
 
 ATS_API int ats_adamw_push(float* master, float* m, float* v, const float* g32, void* const* params, int world, int rank,
                            long long offset, long long n, const float* hyper, const float* clip_state, float wd_mult,
-                           void* stream) {
+                           const int* status, void* stream) {
   if (world > MAX_PEERS || (n & 7) || (offset & 7)) return 1003;
   long long blocks = (n / 8 + 255) / 256;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 8) blocks = 148 * 8;
   adamw_push_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(master, m, v, g32, to_peers(params, world),
-                                                                                   world, rank, offset, n, hyper, clip_state, wd_mult);
+                                                                                   world, rank, offset, n, hyper, clip_state, wd_mult, status);
   return int(cudaGetLastError());
 }
 

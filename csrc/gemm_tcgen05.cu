@@ -88,6 +88,7 @@ struct GemmArgs {
   const float* col_scale;  // [weights * cs_gs] or null
   long long rs_gs, cs_gs;
   int* status;
+  unsigned long long wait_budget_ns;  // budget of the waits on peers' data (gathered B), set by the host from ats_get_wait_budget_ns()
 };
 
 struct TileCoord {
@@ -187,7 +188,7 @@ __device__ __forceinline__ bool wait_chunk(const GemmArgs& p, ChunkRange& r, int
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.b_ready + c) : "memory");
     if (v >= p.epoch) break;  // epoch = pieces per chunk x number of calls so far
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > ATS_WAIT_BUDGET_NS) {
+    if (globaltimer_ns() - t0 > p.wait_budget_ns) {
       *abort_flag = 1;
       if (p.status) atomicCAS(p.status, 0, int(kTimeoutPeerFlag));
       return false;
@@ -957,6 +958,7 @@ static int num_sms() {
 
 using namespace ats;
 
+ATS_API unsigned long long ats_get_wait_budget_ns();  // comm.cu
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int epilogue, int groups, int M, int N,
                        int max_ctas, void* stream, const CUtensorMap* mb_own = nullptr);
 static long long* g_gemm_prof = nullptr;
@@ -1131,6 +1133,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
                        int max_ctas, void* stream, const CUtensorMap* mb_own) {
   GemmArgs p = p_in;
   p.wide = sector_aligned_outputs(p);
+  p.wait_budget_ns = ats_get_wait_budget_ns();
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
