@@ -303,6 +303,43 @@ class ShardedEngine:
                 for k in ("master", "exp_avg", "exp_avg_sq"):
                     getattr(b, k)[a - lo:e - lo].copy_(st[k].reshape(-1)[a - o:e - o].to(self.device))
 
+    # -- sharded state: what lives on this rank, piece by piece ---------------------------------------------------
+    def owned_pieces(self, unique: bool = True) -> List[Dict[str, Any]]:
+        """One entry ``{name, shape, expert, start, length, tensors: {master, exp_avg, exp_avg_sq}}`` for every stretch of a
+        parameter (``length`` elements from flat element ``start``) whose optimiser state this rank holds.  With ``unique`` a
+        stretch that is replicated over a group (stage 0, or a group of one) is listed by the group's first rank only, so that
+        the pieces of all ranks together cover every parameter exactly once."""
+        out = []
+        for b in self.buckets:
+            if unique and not (b.shard_states and b.W > 1) and b.r != 0:
+                continue
+            lo, hi = b.owned_range()
+            for rel, length, i in b.segments_in(lo, hi):
+                p = b.params[i]
+                out.append({"name": b.names[i], "shape": tuple(p.shape), "expert": bool(getattr(p, "_ats_expert", False)),
+                            "start": lo + rel - b.offsets[i], "length": length,
+                            "tensors": {k: getattr(b, k)[rel:rel + length] for k in ("master", "exp_avg", "exp_avg_sq")}})
+        return out
+
+    def load_pieces(self, fetch: Callable[[Dict[str, Any]], Optional[Dict[str, torch.Tensor]]], step: Optional[int] = None,
+                    hyper: Optional[List[float]] = None) -> int:
+        """Inverse of :meth:`owned_pieces`: ``fetch(piece)`` returns the three state vectors of that stretch (or ``None`` when
+        the checkpoint has nothing for it).  Returns the number of stretches restored."""
+        if step is not None:
+            self.step_count = int(step)
+        if hyper:
+            self._hyper_host = list(hyper)
+            self.hyper.copy_(torch.tensor(hyper, dtype=torch.float32))
+        n = 0
+        for piece in self.owned_pieces(unique=False):
+            got = fetch(piece)
+            if got is None:
+                continue
+            for k, t in piece["tensors"].items():
+                t.copy_(got[k].reshape(-1).to(t.device, t.dtype))
+            n += 1
+        return n
+
     def resync_master_from_params(self) -> None:
         """After parameters were overwritten (checkpoint load), refresh the fp32 master slices."""
         for b in self.buckets:

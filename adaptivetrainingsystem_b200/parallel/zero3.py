@@ -304,6 +304,38 @@ class ZeRO3Engine:
         self.root.full = None
         self.root.gather()
 
+    def owned_pieces(self, unique: bool = True) -> List[Dict[str, Any]]:
+        """Same contract as :meth:`ShardedEngine.owned_pieces`: every stretch of a parameter whose state this rank holds."""
+        out = []
+        for u in self.units + [self.root]:
+            lo, hi = u.r * u.shard, (u.r + 1) * u.shard
+            for name, o, shp in zip(u.names, u.offsets, u.shapes):
+                a, e = max(o, lo), min(o + shp.numel(), hi)
+                if e > a:
+                    out.append({"name": name, "shape": tuple(shp), "expert": False, "start": a - o, "length": e - a,
+                                "tensors": {k: getattr(u, k)[a - lo:e - lo] for k in ("master", "exp_avg", "exp_avg_sq")}})
+        return out
+
+    def load_pieces(self, fetch, step: Optional[int] = None, hyper: Optional[List[float]] = None) -> int:
+        if step is not None:
+            self.step_count = int(step)
+        if hyper:
+            self._hyper_host = list(hyper)
+            self.hyper.copy_(torch.tensor(self._hyper_host, dtype=torch.float32))
+        n = 0
+        for piece in self.owned_pieces():
+            got = fetch(piece)
+            if got is None:
+                continue
+            for k, t in piece["tensors"].items():
+                t.copy_(got[k].reshape(-1).to(t.device, t.dtype))
+            n += 1
+        for u in self.units + [self.root]:
+            u.param_shard.copy_(u.master.to(u.dtype))
+        self.root.full = None
+        self.root.gather()
+        return n
+
     def resync_master_from_params(self) -> None:
         """Parameters were overwritten while gathered (checkpoint load): refresh shards and masters from them."""
         for u in self.units + [self.root]:

@@ -734,7 +734,7 @@ class MoEOptimizationManager:
         c = self.config
         return {"enabled": c.use_moe, "num_experts": c.num_experts, "top_k": c.moe_top_k,
                 "capacity_factor": c.capacity_factor, "expert_parallel_size": c.expert_parallel_size or 1,
-                "min_capacity": 4, "drop_tokens": True}
+                "min_capacity": 4, "drop_tokens": bool(getattr(c, "drop_tokens", True))}
 
 
 def profile_training_loop_overhead(trainer: EnhancedConversationTrainer, dataloader: Iterable, n: int = 10) -> Dict[str, float]:

@@ -20,7 +20,8 @@
  *
  * Limits and rules
  *   - cols must be a multiple of 8 and at most the max_cols reported by ats_rmsnorm_bwd_noalloc_limits (8192);
- *     larger problems are refused with ATS_ERR_NOALLOC_TOO_LARGE and nothing is launched.  rows is unlimited.
+ *     larger problems are refused with ATS_ERR_NOALLOC_TOO_LARGE and nothing is launched.  rows may be anything up to
+ *     2^31 - 1 (more is refused with ATS_ERR_BAD_SHAPE: the kernels index rows with 32-bit integers).
  *   - Every GPU that loads the library holds the 4 MiB array until the process exits.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, no allocation).  Make
  *     that first call before starting any stream capture on that device.

@@ -596,6 +596,7 @@ ATS_API int ats_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy
                                     void* dx, void* dw_bf16, float* dw_f32, int accumulate, long long rows, int cols,
                                     void* stream) {
   if (rows <= 0 || cols <= 0 || (cols & 7)) return 1003;
+  if (rows > 2147483647LL) return 1003;     // the kernels index rows with 32-bit integers
   if (cols > kNoAllocMaxCols) return 2001;  // ATS_ERR_NOALLOC_TOO_LARGE
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -623,7 +624,7 @@ ATS_API void ats_rmsnorm_bwd_noalloc_limits(int* max_cols, long long* scratch_by
 ATS_API const char* ats_noalloc_error_string(int code) {
   switch (code) {
     case 0: return "success";
-    case 1003: return "bad shape: rows and cols must be positive and cols a multiple of 8";
+    case 1003: return "bad shape: rows and cols must be positive, rows at most 2^31 - 1 and cols a multiple of 8";
     case 2001: return "problem too large for the built-in scratch: cols exceeds the limit reported by ats_rmsnorm_bwd_noalloc_limits";
     case 2002: return "device ordinal outside the range this library keeps scratch addresses for";
     default: return "CUDA runtime error (the code is a cudaError_t)";

@@ -107,6 +107,46 @@ def test_capacity_drops_tokens_in_order():
     assert torch.allclose(out, ref, atol=1e-5)
 
 
+def test_dropless_routing_is_selectable_from_config_and_matches_the_per_expert_loop():
+    """Skewed routing: one expert is wanted by every token, far more than capacity_factor allows.  ``Config(drop_tokens=False)``
+    reaches the layer and gives the dropless result of the reference's live MoE layer (every routed token is computed);
+    the default enforces the capacity and matches the oracle with that capacity."""
+    from adaptivetrainingsystem_b200.config import Config
+    T, E, k = 512, 4, 2
+    x = torch.rand(T, 32, generator=torch.Generator().manual_seed(1)) + 0.1
+    outs = {}
+    for drop in (False, True):
+        cfg = Config(vocab_size=256, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=48, seq_length=64,
+                     use_moe=True, num_experts=E, moe_top_k=k, capacity_factor=1.25, drop_tokens=drop, precision="fp32",
+                     gradient_checkpointing=False)
+        mc = cfg.to_model_config()
+        assert mc.drop_tokens is drop
+        torch.manual_seed(3)
+        layer = MoEFFNLayer(mc, 0).eval()
+        with torch.no_grad():
+            torch.nn.init.normal_(layer.experts_w1, std=0.1)
+            torch.nn.init.normal_(layer.experts_w2, std=0.1)
+            layer.gate.weight.zero_()
+            layer.gate.weight[0] = 4.0  # positive inputs: expert 0 always wins, the second choice varies
+            layer.gate.weight[1:] = torch.randn(3, 32) * 0.05
+            out, _ = layer(x)
+            idx, w, _ = M.route(torch.nn.functional.linear(x, layer.gate.weight), k, 1.0)
+        assert int(torch.bincount(idx.reshape(-1).long(), minlength=E)[0]) == T
+        cap = M.expert_capacity(T, E, k, 1.25, drop)
+        assert cap == (384 if drop else 512)  # ceil(1.25 * 2 * 512 / 4) = 320 -> whole 128-row tiles; dropless: every token
+        assert torch.allclose(out, M.moe_ffn_reference(x, idx, w, layer.experts_w1, layer.experts_w2, cap), atol=1e-5)
+        outs[drop] = out
+        stats = layer.get_routing_stats()
+        assert (stats["dropped_fraction"] > 0.1) == drop
+    loop = torch.zeros_like(x)
+    for e in range(E):  # the reference layer's per-expert loop: gather, FFN, index_add; nothing is dropped
+        tok, kk = (idx.long() == e).nonzero(as_tuple=True)
+        g, u = (x[tok] @ layer.experts_w1[e].t()).chunk(2, dim=-1)
+        loop.index_add_(0, tok, ((torch.nn.functional.silu(g) * u) @ layer.experts_w2[e].t()) * w[tok, kk][:, None])
+    assert torch.allclose(outs[False], loop, atol=1e-5)
+    assert torch.allclose(outs[True][:384], loop[:384], atol=1e-5) and not torch.allclose(outs[True][384:], loop[384:], atol=1e-4)
+
+
 def test_mod_processes_only_the_selected_fraction_per_sequence():
     cfg = ModelConfig(**BASE, use_mod=True, mod_capacity_factor=0.25)
     f = MoDFFN(cfg)
