@@ -36,8 +36,10 @@ def _fn():
             _c_int, _c_int, _vp,  # groups ragged counts
             _c_int, _c_int, _c_int, _c_int,  # group coordinate shifts
             _c_ll, _c_ll, _c_ll,  # d_gs c_gs aux_gs
-            _c_int, _c_int, _c_int, _vp,  # b_div k_segs seg_stride d_table
+            _c_int, _c_int, _c_int, _vp, _c_int,  # b_div k_segs seg_stride d_table k_split
             _vp, _c_int, _vp]  # status, max_ctas, stream
+        lib.ats_splitk_reduce.restype = _c_int
+        lib.ats_splitk_reduce.argtypes = [_vp, _c_int, _c_ll, _c_ll, _vp, _vp, _vp]
         lib.ats_gemm_set_pair.restype = None
         lib.ats_gemm_set_pair.argtypes = [_c_int]
         if os.environ.get("ATS_GEMM_PAIR") is not None:
@@ -59,13 +61,13 @@ def set_pair_kernels(on: bool) -> None:
 def _raw(a, a_rows, a_cols, lda, a_mn, b, b_rows, b_cols, ldb, b_mn, d, ldd, c, ldc, aux, ldaux,
          M, N, K, alpha=1.0, beta=0, epilogue=EPI_STORE, up_offset=0, groups=1, ragged=0, counts=None,
          a_gs_mn=0, a_gs_k=0, b_gs_mn=0, b_gs_k=0, d_gs=0, c_gs=0, aux_gs=0, max_ctas=0,
-         b_div=1, k_segs=1, seg_stride=0, d_table=None):
+         b_div=1, k_segs=1, seg_stride=0, d_table=None, k_split=1):
     st = _lib.status_tensor(a.device)
     err = _fn()(_lib.ptr(a), a_rows, a_cols, lda, a_mn, _lib.ptr(b), b_rows, b_cols, ldb, b_mn,
                 _lib.ptr(d), ldd, _lib.ptr(c), ldc, _lib.ptr(aux), ldaux,
                 M, N, K, alpha, beta, epilogue, up_offset, groups, ragged, _lib.ptr(counts),
                 a_gs_mn, a_gs_k, b_gs_mn, b_gs_k, d_gs, c_gs, aux_gs,
-                b_div, k_segs, seg_stride, _lib.ptr(d_table),
+                b_div, k_segs, seg_stride, _lib.ptr(d_table), k_split,
                 _lib.ptr(st), max_ctas, _lib.stream_ptr(a.device))
     _lib.check(err, "ats_gemm_bf16")
 
@@ -101,13 +103,23 @@ def _gemm_nt_split_k(a, b, out, add, alpha, splits):
     part = torch.empty(splits, M, N, dtype=torch.float32, device=a.device)
     _raw(a, M, K, a.stride(0), 0, b, N, K, b.stride(0), 0, part, N, None, 0, None, 0, M, N, kp, alpha=alpha, beta=0,
          epilogue=EPI_F32, groups=splits, a_gs_k=kp, b_gs_k=kp, d_gs=M * N)
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    if out.is_contiguous() and (add is None or add.is_contiguous()):
+        _fold_partials(part, splits, M * N, 1, out, add)  # one launch: sum of the slices (+ residual) -> bf16
+        return out
     res = part.sum(0)
     if add is not None:
         res += add
-    if out is None:
-        return res.to(a.dtype)
     out.copy_(res)
     return out
+
+
+def _fold_partials(part: torch.Tensor, splits: int, n_inner: int, n_outer: int, out: torch.Tensor, add: Optional[torch.Tensor] = None) -> None:
+    """out[o, :] = sum over the ``splits`` fp32 partial blocks of problem ``o`` (+ add), written as bf16."""
+    _fn()
+    _lib.check(_lib.cuda_lib().ats_splitk_reduce(_lib.ptr(part), splits, n_inner, n_outer, _lib.ptr(out), _lib.ptr(add),
+                                                 _lib.stream_ptr(part.device)), "splitk_reduce")
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -265,7 +277,7 @@ def unpack_kmajor(w: torch.Tensor) -> torch.Tensor:
 
 def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: bool = False,
                pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, b_div: int = 1,
-               d_table: Optional[torch.Tensor] = None, packed: bool = False) -> torch.Tensor:
+               d_table: Optional[torch.Tensor] = None, packed: bool = False, k_split: int = 1) -> torch.Tensor:
     """x[G,C,K] · w[E,N,K]^T -> [G,C,N] (or [G,C,N/2] through SwiGLU) for the first counts[g] rows of every
     group; group g uses weight g // b_div (G = E * b_div: several token blocks per expert, one per source rank).
     Rows beyond the padded count are left untouched.  ``d_table`` (int64 [G]) redirects the output of group g to
@@ -292,6 +304,16 @@ def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: b
     n_out = N // 2 if swiglu else N
     if out is None and d_table is None:
         out = torch.empty(Gn, C, n_out, dtype=x.dtype, device=x.device)
+    if k_split > 1:
+        # few output tiles and a long reduction (the down projection of a decode step): the reduction is cut into k_split
+        # slices, every (group, slice) pair is a work item with an fp32 partial block, and one small launch folds the slices
+        assert not swiglu and d_table is None and pre_act is None and K % (64 * k_split) == 0 and out.is_contiguous()
+        part = torch.empty(Gn * k_split, C, N, dtype=torch.float32, device=x.device)
+        _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 2 if packed else 0, part, N, None, 0, None, 0, C, N, K // k_split,
+             epilogue=EPI_F32, groups=Gn * k_split, ragged=1, counts=counts, a_gs_mn=C, b_gs_mn=N, d_gs=C * N, b_div=b_div,
+             k_split=k_split)
+        _fold_partials(part, k_split, C * N, Gn, out)
+        return out
     _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 2 if packed else 0, out, n_out, None, 0, pre_act,
          N if pre_act is not None else 0,
          C, n_out, K, epilogue=EPI_SWIGLU if swiglu else EPI_STORE, up_offset=N // 2 if swiglu else 0,

@@ -85,6 +85,35 @@ class _LayerBuffers:
             self.counts = torch.zeros(El * W, dtype=torch.int32, device=device)
 
 
+class _ServingBuffers:
+    """Exchange buffers of a decode-sized step (no autograd): every source rank owns ``Cs`` rows of each expert's ONE row
+    block ``[W * Cs, H]`` (``W * Cs`` a multiple of 128), so the expert GEMMs see one group per local expert and stream each
+    weight once, however many ranks sent rows.  ``Cs >= T`` tokens per rank: nothing is ever dropped."""
+
+    def __init__(self, comm: "ExpertParallelComm", E: int, Cs: int, H: int, dtype: torch.dtype, device):
+        from .peer import SymmetricBuffer
+        W, r = comm.W, comm.rank
+        El = E // W
+        self.E, self.El, self.Cs, self.H, self.rows = E, El, Cs, H, W * Cs
+        es = torch.empty((), dtype=dtype).element_size()
+        n = El * W * Cs * H
+        off = [0, (n * es + 255) // 256 * 256]
+        self.sym = SymmetricBuffer(off[1] * 2, comm.group, device)
+        self.recv_x = self.sym.tensor(dtype, n, off[0]).view(El, W * Cs, H)
+        self.own_y = self.sym.tensor(dtype, n, off[1]).view(El, W * Cs, H)
+        e = torch.arange(E, dtype=torch.int64)
+        owner, el = e // El, e % El
+        base = torch.tensor(self.sym.ptrs, dtype=torch.int64)
+        block = (el * W + r) * Cs * H * es  # this rank's rows inside expert e's block on the owner
+        self.t_disp_x = (base[owner] + off[0] + block).to(device)
+        self.t_pull_y = (base[owner] + off[1] + block).to(device)
+        # every row of a block takes part in the products: rows that no token uses hold zeros or an earlier step's (finite)
+        # values, their results are never read, so no row counts need to travel
+        self.counts = torch.full((El,), W * Cs, dtype=torch.int32, device=device)
+        self.local_counts = torch.zeros(E, dtype=torch.int32, device=device)
+        self.shape_probe = torch.empty(1, dtype=dtype, device=device).expand(E, Cs, H)
+
+
 class ExpertParallelComm:
     def __init__(self, mesh, fused: bool = True):
         self.mesh = mesh
@@ -100,6 +129,35 @@ class ExpertParallelComm:
             self.barrier = PeerBarrier(self.group)
         self._layers: Dict[Tuple[int, int, int, int], _LayerBuffers] = {}
         self.bytes_dispatched = 0
+
+    def serving_rows(self, tokens: int) -> int:
+        """Rows per (source rank, expert) of a decode-sized step, or 0 when the step is too large for the one-block layout:
+        the smallest ``Cs >= tokens`` with ``W * Cs`` a multiple of 128, as long as a block stays within 256 rows."""
+        W = self.W
+        if not self.fused or W > 128 or 128 % W:
+            return 0
+        unit = 128 // W
+        cs = (max(tokens, 1) + unit - 1) // unit * unit
+        return cs if W * cs <= 256 else 0
+
+    def serving_buffers(self, E: int, Cs: int, H: int, dtype, device) -> _ServingBuffers:
+        key = ("serve", E, Cs, H)
+        b = self._layers.get(key)
+        if b is None:
+            b = _ServingBuffers(self, E, Cs, H, dtype, device)
+            self._layers[key] = b
+            dist.barrier(self.group)  # all peers have mapped the new buffers
+        return b
+
+    def close(self) -> None:
+        """Give the exchange buffers (device memory outside PyTorch's allocator) back."""
+        for b in self._layers.values():
+            if getattr(b, "sym", None) is not None:
+                b.sym.close()
+        self._layers.clear()
+        if self.barrier is not None:
+            self.barrier.buf.close()
+            self.barrier = None
 
     def buffers(self, layer_idx: int, E: int, C: int, H: int, dtype, device) -> _LayerBuffers:
         key = (layer_idx, E, C, H)
@@ -214,6 +272,38 @@ class _EPMoEFn(torch.autograd.Function):
         return dx, None, dw_topk, dw1, dw2, None, (dout if ctx.has_res else None), None, None
 
 
+def _down_proj_slices(n_groups: int, N: int, K: int) -> int:
+    """Reduction slices for a skinny grouped product with few output tiles: enough (group, slice) work items for all SMs."""
+    tiles = n_groups * ((N + 255) // 256)
+    s = 1
+    while s * 2 * tiles <= 160 and K % (s * 2 * 64) == 0 and K // (s * 2) >= 512 and s < 16:
+        s *= 2
+    return s
+
+
+@torch.no_grad()
+def ep_moe_serving(x, topk_idx, topk_w, w1, w2, residual, comm: "ExpertParallelComm", buf: _ServingBuffers):
+    """One MoE layer of a decode step across the expert-parallel ranks, four launches between two flag barriers:
+
+    slot plan -> dispatch (token rows go straight into the owners' row blocks over NVLink) -> barrier -> grouped SwiGLU
+    up-projection over one 128/256-row block per local expert -> down-projection with the reduction cut into slices so that
+    every SM streams part of the weight -> barrier -> combine (the source ranks pull their rows from the owners).
+
+    Each rank brings its OWN sequences (the batch is split over the ranks, each keeps the KV cache of its sequences); the
+    experts see the rows of all ranks.  Nothing is dropped and no row counts are exchanged."""
+    T, H = x.shape
+    E, Cs = buf.E, buf.Cs
+    slot_pos, counts, totals = M.plan_slots(topk_idx, E, Cs)
+    M.dispatch(x, topk_idx, slot_pos, counts, E, Cs, table=buf.t_disp_x)
+    comm.barrier()
+    packed = bool(getattr(w1, "_ats_packed", False))
+    h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, packed=packed)
+    G.grouped_nt(h, w2, buf.counts, out=buf.own_y, packed=packed, k_split=_down_proj_slices(buf.El, w2.shape[1], w2.shape[2]))
+    comm.barrier()
+    out = M.combine(buf.shape_probe, topk_idx, slot_pos, topk_w, T, residual, table=buf.t_pull_y)
+    return out, totals
+
+
 class EPLayer:
     """Bound to one MoE layer as ``layer.ep``; ``moe_ffn`` has the signature of the local MoE function."""
 
@@ -224,6 +314,11 @@ class EPLayer:
         # Training keeps one set of exchange buffers per layer (the backward pass reads what the forward pass received).
         # Without autograd nothing outlives the layer call, and the barriers inside it order every reuse, so all layers share
         # one set: a 64 x 1024-token prefill needs 12 GiB of buffers once instead of once per layer.
+        if not torch.is_grad_enabled() and _lib.use_cuda_kernels(x):
+            cs = self.comm.serving_rows(x.shape[0])
+            if cs:  # a decode-sized step: one row block per expert, all layers share one set of buffers
+                buf = self.comm.serving_buffers(self.num_experts, cs, x.shape[1], x.dtype, x.device)
+                return ep_moe_serving(x, topk_idx, topk_w, w1, w2, residual, self.comm, buf)
         key = self.layer_idx if torch.is_grad_enabled() else -1
         buf = self.comm.buffers(key, self.num_experts, capacity, x.shape[1], x.dtype, x.device)
         return _EPMoEFn.apply(x, topk_idx, topk_w, w1, w2, capacity, residual, self.comm, buf)

@@ -97,6 +97,15 @@ class FusedComm:
                            "adamw_push")
         self.barrier()  # (5)
 
+    def close(self) -> None:
+        """Give the symmetric buckets (device memory outside PyTorch's allocator) back.  Every tensor that was handed out by
+        :meth:`allocator` dangles afterwards: drop the engine and the model first."""
+        for buf in self._bufs.values():
+            buf.close()
+        self._bufs.clear()
+        self._g32.clear()
+        self.barrier.buf.close()
+
     def bytes_over_nvlink_per_step(self, engine) -> int:
         """Bytes this rank moves over NVLink in one step (pull of W-1 remote gradient shards + push of its
         parameter shard to W-1 peers) -- the numerator of the link-bandwidth roofline."""

@@ -32,6 +32,77 @@ SHAPES = {
 }
 
 
+def reference_decode(shape_name: str, prompt: int = 1024, new_tokens: int = 256, time_limit_s: float = 75.0) -> dict:
+    """The reference's own generator (``Chat.GenerationEngine.generate``: one sequence, no KV cache, the whole context is
+    re-run for every token, fp32 parameters as ``Chat.py`` loads them) on prompts of the serving workload, greedy
+    (top_k = 1), for as many sequences as fit the time limit.  Tokens per second = generated tokens / device-synchronised
+    wall time.  Runs on one GPU: the reference has no multi-device inference path."""
+    import contextlib
+    import io
+    import torch
+    shape = dict(SHAPES[shape_name])
+    shape.pop("micro_batch"), shape.pop("accum")
+    n_params_fp32_gb = None
+    sink = io.StringIO()
+    try:
+        with contextlib.redirect_stdout(sink):
+            import Chat  # the reference's chat script, installed next to its packages
+            from core.model import DeepSeekConfig, DeepSeekTransformer
+    except Exception as e:
+        return {"unavailable": f"reference generator not importable: {e!r}"[:300]}
+    dev = torch.device("cuda", torch.cuda.current_device())
+    h, i, e, l, v = shape["hidden_size"], shape["intermediate_size"], shape["num_experts"], shape["num_layers"], shape["vocab_size"]
+    kv = shape["num_kv_heads"] * (h // shape["num_heads"])
+    n_params = l * ((e if shape["use_moe"] else 1) * 3 * h * i + h * (2 * h + 2 * kv)) + 2 * v * h
+    n_params_fp32_gb = 4 * n_params / 1e9
+    free_gb = torch.cuda.mem_get_info()[0] / 1e9
+    if n_params_fp32_gb > 0.9 * free_gb:
+        return {"unavailable": f"reference generator holds fp32 parameters on one device (Chat.py:544): {n_params / 1e9:.1f} B parameters "
+                               f"= {n_params_fp32_gb:.0f} GB, {free_gb:.0f} GB free; it has no multi-device inference path"}
+    try:
+        with contextlib.redirect_stdout(sink):
+            torch.manual_seed(1234)
+            mcfg = DeepSeekConfig(tie_word_embeddings=False, use_flash_attention=True, gradient_checkpointing=False, **shape)
+            model = DeepSeekTransformer(mcfg)
+            for m in model.modules():
+                if isinstance(m, (torch.nn.Linear, torch.nn.Embedding)):
+                    torch.nn.init.normal_(m.weight, std=0.02)
+            model = model.to(dev)  # fp32, as Chat.py:544 does
+
+            class _Tok:
+                def decode(self, ids):
+                    return ""
+            eng = Chat.GenerationEngine(model, _Tok(), dev)
+            Chat.HardcodedConfig.CONTEXT_WINDOW = max(Chat.HardcodedConfig.CONTEXT_WINDOW, prompt + new_tokens + 16)
+            g = torch.Generator().manual_seed(7)
+            prompts = torch.randint(1, v, (64, prompt), generator=g)
+            eng.generate(prompts[0, :64].tolist(), 4, 1.0, 1.0, 1, 1.0, stream=False)  # warm-up: short prompt, four tokens
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            total, seqs = 0, 0
+            while seqs < 64 and time.perf_counter() - t0 < time_limit_s:
+                budget = time_limit_s - (time.perf_counter() - t0)
+                # a sequence that would overrun the limit by far is cut short: per-token cost is known after the first one
+                n_new = new_tokens if seqs == 0 else max(8, min(new_tokens, int(budget / max(per_token, 1e-6))))
+                toks, _ = eng.generate(prompts[seqs].tolist(), n_new, 1.0, 1.0, 1, 1.0, stream=False)
+                torch.cuda.synchronize()
+                total += len(toks)
+                seqs += 1
+                per_token = (time.perf_counter() - t0) / max(total, 1)
+            dt = time.perf_counter() - t0
+    except Exception as e:
+        return {"unavailable": f"reference generator failed on its own code path: {type(e).__name__}: {e}"[:300]}
+    res = {"metric": "moe_decode_tokens_per_sec", "value": total / dt, "unit": "tokens/s", "ms_per_token": 1e3 * dt / max(total, 1),
+           "n_gpus": 1, "dtype": "fp32 parameters (Chat.py:544)", "data": "synthetic",
+           "config": {"model": shape_name, "batch": 1, "prompt": prompt, "new_tokens": new_tokens, "sequences_run": seqs,
+                      "tokens_generated": total, "time_limit_s": time_limit_s, "kv_cache": "none (whole context re-run per token)",
+                      "sampling": "top_k = 1 through its multinomial sampler"},
+           "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
+    del eng, model
+    torch.cuda.empty_cache()
+    return res
+
+
 class _Tokenizer:
     """Stand-in with the attributes the reference trainer reads; the benchmark feeds token ids directly."""
     pad_token_id = -1  # no id of the synthetic data is padding
@@ -212,6 +283,16 @@ def run(args, published) -> dict:
            "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                    "h2d_bytes_per_step": accum * sum(v.numel() * v.element_size() for v in host[0].values()), "d2h_bytes_per_step": 4},
            "gpu_launches": 0, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
+    if not getattr(args, "no_decode", False):
+        # serving half of the metric: the reference's generator is single-device, so rank 0 runs it alone after the training
+        # objects are gone (the other ranks wait at the barrier below)
+        trainer = backend = model = devb = None
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        if rank == 0:
+            res["decode"] = reference_decode("mixtral_8x7b")
+            res["decode_b1_moe"] = reference_decode("b1_moe")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

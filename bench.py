@@ -12,6 +12,12 @@ For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-n
   copied from pinned host memory and the loss read back to the host every step.
 * weak scaling: the per-GPU micro-batch is fixed, experts are spread over the N ranks (EP = gcd(E, N)), dense weights are
   replicated with ZeRO-1 optimiser sharding.
+* ``decode``: the second half of the metric -- MoE decode tokens/s on the Mixtral-8x7B shape (batch 64 x 1024-token prompts, 256
+  greedy steps, GQA KV cache, experts spread over the N ranks, batch split over the ranks), measured at the same N after the
+  training model has been torn down; ``decode_b1_moe`` is the same workload on the training model's shape, the largest the
+  reference's generator can hold (``--impl reference`` reports its cache-less generator on that shape).
+* ``fused_check`` (N > 1): before the timed run a two-layer slice of the model takes two optimiser steps through the
+  peer-memory kernels and through the NCCL twin of every fused path; the run fails when they disagree.
 
 Synthetic uniform token ids, random-init N(0, 0.02) weights, bf16 compute with fp32 master weights.
 """
@@ -81,6 +87,61 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def fused_check(args, cfg_name, mesh, over) -> dict:
+    """Two optimiser steps of a two-layer slice: fused peer-memory paths against their NCCL twins (same seeds, same batches).
+    Returns the largest relative difference of the losses and of the gradient norms and the smallest cosine similarity of
+    any updated parameter."""
+    import torch
+    import torch.distributed as dist
+    from adaptivetrainingsystem_b200 import ops
+    from adaptivetrainingsystem_b200.config import ConfigPresets
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.parallel.expert_parallel import attach_expert_parallel
+    from adaptivetrainingsystem_b200.parallel.zero import ShardedEngine
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = ConfigPresets.get(cfg_name, num_workers=0, gradient_checkpointing=False, **{**over, "num_layers": 2})
+    mc = cfg.to_model_config()
+    g = torch.Generator().manual_seed(4321 + mesh.rank)
+    ids = torch.randint(0, cfg.vocab_size, (2, 1025), generator=g).to(dev)
+    runs = {}
+    for name, fused in (("nccl", False), ("fused", True)):
+        torch.manual_seed(77)
+        with torch.device(dev):
+            torch.set_default_dtype(torch.bfloat16)
+            model = DeepSeekTransformer(mc, ep_size=mesh.ep_size, ep_rank=mesh.coord.ep)
+            torch.set_default_dtype(torch.float32)
+        model.rope.cos, model.rope.sin = model.rope.cos.float(), model.rope.sin.float()
+        comm = attach_expert_parallel(model, mesh, cfg, use_fused=fused)
+        eng = ShardedEngine(model, lr=1e-3, zero_stage=max(cfg.zero_stage, 1), max_grad_norm=1.0, mesh=mesh, fused_comm=comm)
+        losses = []
+        for _ in range(2):
+            out = model.forward_loss(ids[:, :-1], ids[:, 1:])
+            out["loss"].backward()
+            eng.step()
+            losses.append(out["loss"].detach().float())
+        torch.cuda.synchronize()
+        ops.check_status()
+        runs[name] = (torch.stack(losses), float(eng.last_grad_norm), {k: v.detach().float().clone() for k, v in model.state_dict().items()},
+                      bool(fused and comm is not None and comm.usable(eng)))
+        ep_comm = getattr(model, "_ep_comm", None)
+        del eng, model
+        if ep_comm is not None:
+            ep_comm.close()
+        if comm is not None:
+            comm.close()
+        torch.cuda.empty_cache()
+    (ln, gn, sn, _), (lf, gf, sf, used) = runs["nccl"], runs["fused"]
+    loss_err = float(((ln - lf).abs() / ln.abs().clamp(min=1e-6)).max())
+    norm_err = abs(gn - gf) / max(abs(gn), 1e-6)
+    cos = min(float(torch.nn.functional.cosine_similarity(sf[k].flatten(), sn[k].flatten(), dim=0)) for k in sn if sn[k].numel() > 1)
+    t = torch.tensor([loss_err, norm_err, -cos], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    loss_err, norm_err, cos = float(t[0]), float(t[1]), -float(t[2])
+    ok = used and loss_err < 2e-2 and norm_err < 3e-2 and cos > 0.999
+    return {"max_rel_err": max(loss_err, norm_err), "loss_rel_err": loss_err, "grad_norm_rel_err": norm_err, "min_param_cosine": cos,
+            "fused_step_used": used, "layers": 2, "steps": 2, "ok": bool(ok)}
+
+
 def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -109,6 +170,11 @@ def run_ours(args) -> dict:
     ep = math.gcd(cfg.num_experts, world) if cfg.use_moe else 1
     mesh = ProcessMesh(world, rank, ep_size=ep)
     cfg.world_size, cfg.expert_parallel_size = world, ep
+    check = None
+    if world > 1 and cfg.fused_comm and not args.no_fused_check and cfg.zero_stage <= 2:
+        check = fused_check(args, args.config, mesh, over)
+        if not check["ok"]:
+            raise SystemExit(f"fused paths disagree with their NCCL twins: {json.dumps(check)}")
     torch.manual_seed(1234)
     mc = cfg.to_model_config()
     with torch.device(dev):
@@ -118,7 +184,8 @@ def run_ours(args) -> dict:
     model.rope.cos, model.rope.sin = model.rope.cos.float(), model.rope.sin.float()
     fused = attach_expert_parallel(model, mesh, cfg, use_fused=cfg.fused_comm) if world > 1 else None
     trainer = EnhancedConversationTrainer(model, None, cfg, mesh=mesh, fused_comm=fused)
-    trainer._setup_scheduler(10 ** 6)
+    # a real schedule over the steps this run takes (warm-up, timed, end-to-end): the recorded losses show the model learning
+    trainer._setup_scheduler(args.warmup + 2 * args.steps + 1)
 
     mb, L, V = cfg.micro_batch_size, cfg.seq_length, cfg.vocab_size
     g = torch.Generator().manual_seed(99 + rank)
@@ -137,10 +204,12 @@ def run_ours(args) -> dict:
     accum = max(cfg.gradient_accumulation_steps, 1)
 
     def step_device(i):
+        out = None
         for a in range(accum):
-            trainer.train_step(devb[(i * accum + a) % n_batches])
+            out = trainer.train_step(devb[(i * accum + a) % n_batches])
         trainer.optimizer_step()
         trainer._pending_device.clear()
+        return out["loss"]
 
     def step_e2e(i):
         out = None
@@ -152,8 +221,11 @@ def run_ours(args) -> dict:
         trainer._pending_device.clear()
         return float(out["loss"])  # device -> host read every step
 
+    first_loss = None
     for i in range(args.warmup):
-        step_device(i)
+        loss = step_device(i)
+        if i == 0:
+            first_loss = float(loss)
     ops.check_status()
     barrier()
     launches0 = _lib.launch_count()
@@ -192,6 +264,9 @@ def run_ours(args) -> dict:
 
     tokens = mb * L * world * accum
     value = tokens / (ms / 1e3)
+    routing = model.get_routing_statistics() if cfg.use_moe else {}
+    dropped = [v["dropped_fraction"] for v in routing.values()]
+    dropped_fraction = sum(dropped) / len(dropped) if dropped else 0.0
     pub = PUBLISHED_TOKENS_PER_S.get(args.config)
     h2d = accum * sum(v.numel() * v.element_size() for v in host[0].values())
     res = {
@@ -204,13 +279,34 @@ def run_ours(args) -> dict:
                    "top_k": cfg.moe_top_k if cfg.use_moe else 0, "params_total": mc.num_parameters(),
                    "params_active": mc.num_parameters(True), "l2": "working set per step (weights + activations) far exceeds the 126 MB L2",
                    "fused_comm": bool(cfg.fused_comm), "attention_backend": os.environ.get("ATS_ATTN", "native"),
-                   "loss_last": last},
+                   "capacity_factor": cfg.capacity_factor if cfg.use_moe else None, "drop_tokens": bool(cfg.drop_tokens) if cfg.use_moe else None,
+                   "dropped_slot_fraction": dropped_fraction, "lr_schedule_steps": args.warmup + 2 * args.steps + 1,
+                   "loss_first": first_loss, "loss_last": last},
         "clocks": clk.summary(),
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
     }
+    if check is not None:
+        res["fused_check"] = check
+    # tear the training job down (buckets and exchange buffers live outside PyTorch's allocator) before the serving models are built
+    trainer.shutdown()
+    ep_comm = getattr(model, "_ep_comm", None)
+    del trainer, devb, model
+    import gc
+    gc.collect()
+    if ep_comm is not None:
+        ep_comm.close()
+    if fused is not None:
+        fused.close()
+    torch.cuda.empty_cache()
+    if not args.no_decode:
+        from adaptivetrainingsystem_b200.inference.benchmark import run_decode_benchmark
+        torch.cuda.reset_peak_memory_stats()
+        res["decode"] = run_decode_benchmark("mixtral_8x7b", 64, 1024, 256, layers=args.decode_layers, repeat=2)
+        torch.cuda.reset_peak_memory_stats()
+        res["decode_b1_moe"] = run_decode_benchmark("b1_moe", 64, 1024, 256, layers=args.decode_layers, repeat=2)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -239,6 +335,9 @@ def main():
     ap.add_argument("--accum", type=int, default=0)
     ap.add_argument("--checkpoint", type=int, default=0)
     ap.add_argument("--nccl-only", action="store_true", help="baseline path: NCCL collectives instead of the fused peer-memory kernels")
+    ap.add_argument("--no-decode", action="store_true", help="skip the serving half of the metric")
+    ap.add_argument("--no-fused-check", action="store_true", help="skip the fused-vs-NCCL check that precedes a multi-GPU run")
+    ap.add_argument("--decode-layers", type=int, default=0, help="debug only: serving models with fewer layers")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

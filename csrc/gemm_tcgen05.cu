@@ -55,6 +55,8 @@ struct GemmArgs {
   float alpha;
   int beta;              // kF32: accumulate into Df32
   int b_div;             // B operand of group g belongs to weight g / b_div (several token blocks per expert)
+  int k_split;           // > 1: group index = problem * k_split + slice; slice s reduces over [s * K, (s + 1) * K) of the problem's
+                         // reduction dimension and owns its own D block (fp32 partial products that a small kernel folds)
   int k_segs;            // ragged == 2: the reduction of group g runs over k_segs blocks of rows, seg_stride apart,
   int seg_stride;        //              block s holding counts[g * k_segs + s] rows
   void* const* d_table;  // optional per-group output base pointers (e.g. buffers on peer GPUs)
@@ -101,7 +103,7 @@ __device__ __forceinline__ int round_up_128(int v) { return (v + 127) & ~127; }
 __device__ __forceinline__ void group_extents(const GemmArgs& p, int g, int& mg, int& kg) {
   mg = p.M;
   kg = p.K;
-  if (p.ragged == 1) mg = min(round_up_128(p.counts[g]), p.M);
+  if (p.ragged == 1) mg = min(round_up_128(p.counts[g / p.k_split]), p.M);
   if (p.ragged == 2) {
     kg = 0;
     for (int s = 0; s < p.k_segs; ++s) kg += min(round_up_128(p.counts[g * p.k_segs + s]), p.K);
@@ -207,7 +209,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
   const bool row_ok = row < t.valid;
   const bool have_acc = t.k_iters > 0;
   const float rs = (p.row_scale && row_ok) ? p.row_scale[p.rs_gs * t.g + row] * p.alpha : p.alpha;
-  const float* cs = p.col_scale ? p.col_scale + p.cs_gs * (t.g / p.b_div) : nullptr;
+  const float* cs = p.col_scale ? p.col_scale + p.cs_gs * (t.g / p.k_split / p.b_div) : nullptr;
   if (p.epilogue == kSwiGLU) {
     __nv_bfloat16* dbase = p.d_table ? static_cast<__nv_bfloat16*>(p.d_table[t.g]) : p.D + p.d_gs * t.g;
     __nv_bfloat16* drow = dbase + (long long)row * p.ldd;
@@ -513,9 +515,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                wait_chunk(p, ready, r1 / p.ready_rows, abort_flag) && wait_chunk(p, ready, (r1 + 127) / p.ready_rows, abort_flag);
           if (!ok) break;
         }
-        const int a_mn_c = t.m0 + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
-        const int gb = t.g / p.b_div;
-        const int b_mn_c = t.n0 + p.b_gs_mn * gb, b_k_c = p.b_gs_k * gb;
+        const int ge = t.g / p.k_split, k_off = (t.g - ge * p.k_split) * p.K;  // problem and reduction slice of this group
+        const int a_mn_c = t.m0 + p.a_gs_mn * ge, a_k_c = p.a_gs_k * ge + k_off;
+        const int gb = ge / p.b_div;
+        const int b_mn_c = t.n0 + p.b_gs_mn * gb, b_k_c = p.b_gs_k * gb + k_off;
         int seg = 0, seg_left = seg_iters_of(p, t.g, 0, t.k_iters), kpos = 0;
         for (int kb = 0; kb < t.k_iters; ++kb) {
           while (seg_left == 0) {
@@ -553,7 +556,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               if (o1 >= 0 && o1 < p.own_rows) tma_load_2d(b_dst + 128 * 128, &map_b_own, &full[stage], k0, o1);
               else tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], k0, second);
             } else if (p.b_packed) {
-              const int kb_idx = k0 >> 6;
+              const int kb_idx = (k0 + k_off) >> 6;
               tma_load_2d(b_dst, &map_b, &full[stage], 0, ((b_mn_c >> 7) * p.b_kblocks + kb_idx) << 7);
               tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], 0, ((second >> 7) * p.b_kblocks + kb_idx) << 7);
             } else {
@@ -759,9 +762,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       ChunkRange ready;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         TileCoord t = decode_tile(p, prefix, tile, g_hint, PAIR_BM);
-        const int a_mn_c = t.m0 + int(rank) * BM + p.a_gs_mn * t.g, a_k_c = p.a_gs_k * t.g;
-        const int gb = t.g / p.b_div;
-        const int b_k_c = p.b_gs_k * gb;
+        const int ge = t.g / p.k_split, k_off = (t.g - ge * p.k_split) * p.K;  // problem and reduction slice of this group
+        const int a_mn_c = t.m0 + int(rank) * BM + p.a_gs_mn * ge, a_k_c = p.a_gs_k * ge + k_off;
+        const int gb = ge / p.b_div;
+        const int b_k_c = p.b_gs_k * gb + k_off;
         // this CTA's half of the B tile: rows n0 .. n0+127 for the leader, the next 128 (SwiGLU: the "up" rows) for the partner
         const int b_mn_c = t.n0 + p.b_gs_mn * gb + (rank ? (p.epilogue == kSwiGLU ? p.up_offset : 128) : 0);
         const CUtensorMap* bmap = &map_b;
@@ -802,7 +806,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               tma_load_2d_pair(a_dst + j * (BK * 128), &map_a, bar, a_mn_c + 64 * j, a_k_c + k0);
           }
           if (!p.b_mn) {
-            if (p.b_packed) tma_load_2d_pair(b_dst, bmap, bar, 0, ((b_row >> 7) * p.b_kblocks + (k0 >> 6)) << 7);
+            if (p.b_packed) tma_load_2d_pair(b_dst, bmap, bar, 0, ((b_row >> 7) * p.b_kblocks + ((k0 + k_off) >> 6)) << 7);
             else tma_load_2d_pair(b_dst, bmap, bar, b_k_c + k0, b_row);
           } else {
 #pragma unroll
@@ -983,7 +987,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
                           int groups, int ragged, const int* counts,
                           int a_gs_mn, int a_gs_k, int b_gs_mn, int b_gs_k,
                           long long d_gs, long long c_gs, long long aux_gs,
-                          int b_div, int k_segs, int seg_stride, void* const* d_table,
+                          int b_div, int k_segs, int seg_stride, void* const* d_table, int k_split,
                           int* status, int max_ctas, void* stream) {
   // The tensor-map encoder is a driver call: make sure this thread (autograd runs backward on its own threads)
   // has the primary context bound before the first use.
@@ -1002,6 +1006,8 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   if (epilogue == kSwiGLU && (b_mn || (up_offset & 7))) return 1004;
   if (ragged && !counts) return 1005;
   if (b_div < 1 || k_segs < 1 || (seg_stride & 7) || (k_segs > 1 && ragged != 2)) return 1006;
+  // reduction slices: whole K blocks per slice, fp32 partial outputs, every `k_split` consecutive groups are one problem
+  if (k_split < 1 || (k_split > 1 && (epilogue != kF32 || ragged == 2 || (K & 63) || groups % k_split || d_table))) return 1008;
   CUtensorMap ma, mb;
   int e;
   if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 2, 64, a_mn ? 64 : 128))) return e;
@@ -1019,7 +1025,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = static_cast<float*>(D);
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = a_mn; p.b_mn = b_mn; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
-  p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table;
+  p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table; p.k_split = k_split;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = g_gemm_prof;
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
@@ -1030,6 +1036,41 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
     p.C = nullptr;
   }
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
+}
+
+// Fold of the fp32 partial products that reduction slices leave (k_split > 1, or the dense form with one group per slice):
+// out[o, i] = sum_s part[(o * splits + s) * n_inner + i] (+ add[o, i]) as bf16, i < n_inner (a multiple of 8), o < n_outer.
+namespace ats {
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, long long n_inner, long long n_outer,
+                                                            __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ add) {
+  const long long nvec = n_inner >> 3, total = nvec * n_outer;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
+    const long long o = v / nvec, i = (v - o * nvec) << 3;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (add) {
+      const uint4 a = *reinterpret_cast<const uint4*>(add + o * n_inner + i);
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+    }
+    const float* src = part + (o * splits) * n_inner + i;
+    for (int s = 0; s < splits; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(src + s * n_inner), b = *reinterpret_cast<const float4*>(src + s * n_inner + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    *reinterpret_cast<uint4*>(out + o * n_inner + i) =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+}  // namespace ats
+
+ATS_API int ats_splitk_reduce(const float* part, int splits, long long n_inner, long long n_outer, void* out, const void* add, void* stream) {
+  if (splits < 1 || n_inner <= 0 || n_outer <= 0 || (n_inner & 7)) return 1003;
+  long long blocks = ((n_inner >> 3) * n_outer + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_reduce_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(part, splits, n_inner, n_outer,
+                                                                                       static_cast<__nv_bfloat16*>(out),
+                                                                                       static_cast<const __nv_bfloat16*>(add));
+  return int(cudaGetLastError());
 }
 
 // fp8 (e4m3) A [groups x M, K] and B [weights x N, K], both K-major and row-quantised: D = (A_q B_q^T) * row_scale * col_scale.
@@ -1062,7 +1103,7 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
-  p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
+  p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1;
   p.b_packed = 0; p.b_kblocks = 0;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
@@ -1100,7 +1141,7 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = 1.f; p.beta = 0; p.status = status;
-  p.b_div = 1; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr;
+  p.b_div = 1; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   const long long shard_rows = b_rows / b_shards;
   p.b_packed = 0; p.b_kblocks = 0;

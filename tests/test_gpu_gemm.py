@@ -237,3 +237,32 @@ def test_grouped_gemm_with_tile_packed_weights():
     a = G.grouped_nt(x, w, counts, b_div=2, out=torch.zeros(2 * E, 128, N, device="cuda", dtype=torch.bfloat16))
     b = G.grouped_nt(x, wp, counts, b_div=2, out=torch.zeros(2 * E, 128, N, device="cuda", dtype=torch.bfloat16), packed=True)
     assert torch.equal(a, b)
+
+
+def test_grouped_gemm_with_reduction_slices():
+    """Grouped products whose reduction is cut into slices (decode-sized down projection: few output tiles, long K): every
+    (group, slice) pair writes an fp32 partial, one launch folds them.  Plain and tile-packed weights, one and several token
+    blocks per weight, ragged row counts; against the fp32 product row by row (error relative to each row's norm)."""
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    torch.manual_seed(8)
+    E, N, K = 3, 512, 2048
+    w = (torch.randn(E, N, K, device="cuda") * 0.03).bfloat16()
+    wp = G.pack_kmajor(w)
+    for C, cnt, b_div in ((128, [128, 128, 128], 1), (128, [100, 0, 128], 1), (256, [256, 130, 256, 1, 256, 256], 2)):
+        Gn = E * b_div
+        x = torch.randn(Gn, C, K, device="cuda").bfloat16()
+        counts = torch.tensor(cnt, dtype=torch.int32, device="cuda")
+        wx = w.repeat_interleave(b_div, dim=0)
+        ref = torch.einsum("gck,gnk->gcn", x.float(), wx.float())
+        for S in (2, 4, 8):
+            for packed in (False, True):
+                out = torch.zeros(Gn, C, N, device="cuda", dtype=torch.bfloat16)
+                G.grouped_nt(x, wp if packed else w, counts, out=out, b_div=b_div, packed=packed, k_split=S)
+                torch.cuda.synchronize()
+                for g in range(Gn):
+                    n = cnt[g]
+                    if n == 0:
+                        continue
+                    err = (out[g, :n].float() - ref[g, :n]).norm(dim=-1) / (ref[g, :n].norm(dim=-1) + 1e-6)
+                    assert err.max().item() < 1e-2, (C, cnt, b_div, S, packed, g, err.max().item())
+    ops.check_status()
