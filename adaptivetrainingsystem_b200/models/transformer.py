@@ -227,6 +227,16 @@ class MoEFFNLayer(nn.Module):
         x = h.reshape(-1, shape[-1])
         T = x.shape[0]
         E, k = self.num_experts, self.top_k
+        if not self.training and moe_ops.serving_path_ok(x, E, k):
+            # decode-sized step: routing, permutation and combine are three small launches around the grouped GEMMs; the
+            # exchange between expert-parallel ranks happens inside them (no auxiliary loss, no statistics while serving)
+            res2 = residual.reshape(-1, shape[-1]) if residual is not None else None
+            if self.ep is not None:
+                served = self.ep.moe_serving(x, self.gate.weight, k, self.routing_temperature, self.experts_w1, self.experts_w2, res2)
+            else:
+                served = moe_ops.moe_ffn_serving(x, self.gate.weight, k, self.routing_temperature, self.experts_w1, self.experts_w2, res2)
+            if served is not None:
+                return served[0].view(shape), None
         logits = moe_ops.gate_logits(x, self.gate.weight)
         fused_route = logits.is_cuda and not (self.training and self.routing_noise_std > 0) and logits.dtype == torch.float32
         if fused_route:
@@ -246,10 +256,11 @@ class MoEFFNLayer(nn.Module):
             out, totals = self.ep.moe_ffn(x, idx, w.to(torch.float32), self.experts_w1, self.experts_w2, cap, res2)
         else:
             out, totals = moe_ops._MoEFFNFn.apply(x, idx, w.to(torch.float32), self.experts_w1, self.experts_w2, cap, res2)
-        with torch.no_grad():
-            self.expert_demand += totals.to(torch.float64)
-            self.tokens_seen += T
-            self.dropped_slots += (totals - totals.clamp(max=cap)).sum().to(torch.float64)
+        if self.training or torch.is_grad_enabled():  # routing statistics are a training-time instrument
+            with torch.no_grad():
+                self.expert_demand += totals.to(torch.float64)
+                self.tokens_seen += T
+                self.dropped_slots += (totals - totals.clamp(max=cap)).sum().to(torch.float64)
         return out.view(shape), aux
 
     @torch.no_grad()

@@ -324,6 +324,79 @@ class _MoEFFNFn(torch.autograd.Function):
         return dx, None, dw_topk, dw1, dw2, None, (dout if ctx.has_res else None)
 
 
+# ----------------------------------------------------------------------------------------------------------
+# decode-sized steps (serving): three small launches around the two grouped GEMMs
+# ----------------------------------------------------------------------------------------------------------
+SERVE_MAX_SLOTS = 1024
+
+
+def serving_path_ok(x: torch.Tensor, num_experts: int, top_k: int) -> bool:
+    """A step small enough for the serving kernels: no autograd, bf16 on the GPU, at most 1024 (token, k) slots."""
+    return (not torch.is_grad_enabled() and _lib.use_cuda_kernels(x) and x.dim() == 2 and x.shape[0] * top_k <= SERVE_MAX_SLOTS
+            and num_experts <= 64 and top_k <= 8 and x.shape[1] % 8 == 0 and x.is_contiguous())
+
+
+def serve_gate_route(x: torch.Tensor, wg: torch.Tensor, top_k: int, temperature: float):
+    """x [T, H], gate weight [E, H] -> (topk_idx int32 [T, k], topk_w fp32 [T, k]): logits, soft-max over all experts at the
+    routing temperature, top-k and renormalisation in one launch."""
+    T, H = x.shape
+    E = wg.shape[0]
+    idx = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
+    _CK(_L().ats_serve_gate_route(_P(x), _P(wg.contiguous()), _P(idx), _P(w), T, H, E, top_k, float(temperature), _S(x.device)),
+        "serve_gate_route")
+    return idx, w
+
+
+def serve_plan_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, num_experts: int, capacity: int, out: Optional[torch.Tensor] = None,
+                        table: Optional[torch.Tensor] = None, want_counts: bool = True):
+    """Slot plan (rank of every (token, k) slot among the earlier slots of its expert) and row copy in one launch.
+    -> (slot_pos int32 [T * k], counts int32 [E] or None, totals int32 [E] or None).  Rows go to ``out`` [E, C, H] or,
+    with ``table`` (int64 [E] base addresses), to blocks that may live on peer GPUs.  Rows that no slot uses are not
+    touched: their products are never read."""
+    T, H = x.shape
+    k = topk_idx.shape[1]
+    slot_pos = torch.empty(T * k, dtype=torch.int32, device=x.device)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=x.device) if want_counts else None
+    totals = torch.empty(num_experts, dtype=torch.int32, device=x.device) if want_counts else None
+    stride = out.stride(0) if out is not None else 0
+    _CK(_L().ats_serve_plan_dispatch(_P(x), _P(topk_idx), _P(slot_pos), _P(counts), _P(totals), _P(table), _P(out) if table is None else None,
+                                     stride, T, k, H, num_experts, capacity, _S(x.device)), "serve_plan_dispatch")
+    return slot_pos, counts, totals
+
+
+def serve_combine(topk_idx: torch.Tensor, slot_pos: torch.Tensor, topk_w: torch.Tensor, tokens: int, hidden: int, dtype, device,
+                  buf: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = residual[t] + sum_j w[t, j] * row(e_j, pos_j); one CTA per token.  Rows come from ``buf`` [E, C, H] or from the
+    blocks ``table`` points to (pulled over NVLink when they live on the experts' owners)."""
+    out = torch.empty(tokens, hidden, dtype=dtype, device=device)
+    k = topk_idx.shape[1]
+    stride = buf.stride(0) if buf is not None else 0
+    _CK(_L().ats_serve_combine(_P(table), _P(buf) if table is None else None, stride, _P(topk_idx), _P(slot_pos), _P(topk_w),
+                               _P(residual), _P(out), tokens, k, hidden, _S(device)), "serve_combine")
+    return out
+
+
+@torch.no_grad()
+def moe_ffn_serving(x: torch.Tensor, wg: torch.Tensor, top_k: int, temperature: float, w1: torch.Tensor, w2: torch.Tensor,
+                    residual: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One MoE layer of a decode-sized step on one GPU: gate + route, plan + dispatch, grouped SwiGLU up-projection, grouped
+    down-projection, combine -- five launches.  Dropless (every expert block has room for every token).
+    -> (output [T, H], demand per expert int32 [E])."""
+    T, H = x.shape
+    E = w1.shape[0]
+    C = (T + 127) // 128 * 128
+    idx, w = serve_gate_route(x, wg, top_k, temperature)
+    xe = torch.empty(E, C, H, dtype=x.dtype, device=x.device)
+    slot_pos, counts, totals = serve_plan_dispatch(x, idx, E, C, out=xe)
+    packed = bool(getattr(w1, "_ats_packed", False))
+    h = G.grouped_nt(xe, w1, counts, swiglu=True, packed=packed)
+    ye = G.grouped_nt(h, w2, counts, packed=packed)
+    out = serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, buf=ye, residual=residual)
+    return out, totals
+
+
 def moe_ffn(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
             capacity: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """-> (output [T,H], demand per expert int32 [E])."""

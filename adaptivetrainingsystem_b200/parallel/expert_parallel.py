@@ -282,26 +282,27 @@ def _down_proj_slices(n_groups: int, N: int, K: int) -> int:
 
 
 @torch.no_grad()
-def ep_moe_serving(x, topk_idx, topk_w, w1, w2, residual, comm: "ExpertParallelComm", buf: _ServingBuffers):
-    """One MoE layer of a decode step across the expert-parallel ranks, four launches between two flag barriers:
+def ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, comm: "ExpertParallelComm", buf: _ServingBuffers):
+    """One MoE layer of a decode step across the expert-parallel ranks, six launches between two flag barriers:
 
-    slot plan -> dispatch (token rows go straight into the owners' row blocks over NVLink) -> barrier -> grouped SwiGLU
-    up-projection over one 128/256-row block per local expert -> down-projection with the reduction cut into slices so that
-    every SM streams part of the weight -> barrier -> combine (the source ranks pull their rows from the owners).
+    gate + route -> slot plan + dispatch (token rows go straight into the owners' row blocks over NVLink) -> barrier ->
+    grouped SwiGLU up-projection over one 128/256-row block per local expert -> down-projection with the reduction cut into
+    slices so that every SM streams part of the weight (+ fold) -> barrier -> combine (the source ranks pull their rows from
+    the owners).
 
     Each rank brings its OWN sequences (the batch is split over the ranks, each keeps the KV cache of its sequences); the
     experts see the rows of all ranks.  Nothing is dropped and no row counts are exchanged."""
     T, H = x.shape
     E, Cs = buf.E, buf.Cs
-    slot_pos, counts, totals = M.plan_slots(topk_idx, E, Cs)
-    M.dispatch(x, topk_idx, slot_pos, counts, E, Cs, table=buf.t_disp_x)
+    idx, w = M.serve_gate_route(x, wg, top_k, temperature)
+    slot_pos, _, _ = M.serve_plan_dispatch(x, idx, E, Cs, table=buf.t_disp_x, want_counts=False)
     comm.barrier()
     packed = bool(getattr(w1, "_ats_packed", False))
     h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, packed=packed)
     G.grouped_nt(h, w2, buf.counts, out=buf.own_y, packed=packed, k_split=_down_proj_slices(buf.El, w2.shape[1], w2.shape[2]))
     comm.barrier()
-    out = M.combine(buf.shape_probe, topk_idx, slot_pos, topk_w, T, residual, table=buf.t_pull_y)
-    return out, totals
+    out = M.serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, table=buf.t_pull_y, residual=residual)
+    return out, None
 
 
 class EPLayer:
@@ -310,15 +311,19 @@ class EPLayer:
     def __init__(self, comm: ExpertParallelComm, layer_idx: int, num_experts: int):
         self.comm, self.layer_idx, self.num_experts = comm, layer_idx, num_experts
 
+    def moe_serving(self, x, wg, top_k, temperature, w1, w2, residual=None):
+        """Decode-sized step (no autograd): one row block per expert, all layers share one set of buffers.  Returns ``None``
+        when the step does not fit that layout (the caller then takes the general path)."""
+        cs = self.comm.serving_rows(x.shape[0])
+        if not cs:
+            return None
+        buf = self.comm.serving_buffers(self.num_experts, cs, x.shape[1], x.dtype, x.device)
+        return ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, self.comm, buf)
+
     def moe_ffn(self, x, topk_idx, topk_w, w1, w2, capacity, residual=None):
         # Training keeps one set of exchange buffers per layer (the backward pass reads what the forward pass received).
         # Without autograd nothing outlives the layer call, and the barriers inside it order every reuse, so all layers share
         # one set: a 64 x 1024-token prefill needs 12 GiB of buffers once instead of once per layer.
-        if not torch.is_grad_enabled() and _lib.use_cuda_kernels(x):
-            cs = self.comm.serving_rows(x.shape[0])
-            if cs:  # a decode-sized step: one row block per expert, all layers share one set of buffers
-                buf = self.comm.serving_buffers(self.num_experts, cs, x.shape[1], x.dtype, x.device)
-                return ep_moe_serving(x, topk_idx, topk_w, w1, w2, residual, self.comm, buf)
         key = self.layer_idx if torch.is_grad_enabled() else -1
         buf = self.comm.buffers(key, self.num_experts, capacity, x.shape[1], x.dtype, x.device)
         return _EPMoEFn.apply(x, topk_idx, topk_w, w1, w2, capacity, residual, self.comm, buf)

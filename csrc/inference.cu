@@ -13,6 +13,7 @@
 // The reference has no KV cache (it re-runs the whole context for every token, reference Chat.py:379-452) and samples
 // with eager tensor ops (reference Chat.py:391-425); the order of the sampling steps follows that code.
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace ats {
 
@@ -41,7 +42,7 @@ template <int D, int REP>
 __global__ void __launch_bounds__(DEC_THREADS) decode_attn_kernel(const DecodeArgs p) {
   __shared__ float s_q[REP][D];
   __shared__ float s_p[REP][DEC_CHUNK];
-  __shared__ float s_red[DEC_THREADS / (D / 2)][REP][D];
+  __shared__ float s_red[DEC_THREADS / 32][REP][D];
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_old = p.lengths ? p.lengths[b] : p.length;
@@ -67,28 +68,49 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attn_kernel(const DecodeAr
   }
   __syncthreads();
 
-  // ---- scores: thread t <-> key k0 + t
-  float acc[REP];
+  // ---- scores: D / 8 lanes share a key row (one 16-byte load each, so a warp's load covers whole rows: with one thread per
+  // row every load instruction touched 32 cache lines and the kernel was bound by L1 wavefronts at a third of HBM speed);
+  // the partial dot products are folded with shuffles.  Four rows per lane group are requested before the first is used.
+  {
+    constexpr int LPR = D / 8, RPW = 32 / LPR, ROWS_PER_PASS = (DEC_THREADS / 32) * RPW, SUNR = 4;
+    const int sub = lane / LPR, l8 = lane % LPR;
+    float q[REP][8];
 #pragma unroll
-  for (int h = 0; h < REP; ++h) acc[h] = -INFINITY;
-  const int key = k0 + tid;
-  if (active && key < k_end) {
+    for (int h = 0; h < REP; ++h)
 #pragma unroll
-    for (int h = 0; h < REP; ++h) acc[h] = 0.f;
-    const __nv_bfloat16* krow = (key == n_old) ? p.k_new + (long long)b * p.ld_qkv + hk * D : kc + key * row_stride;
+      for (int e = 0; e < 8; ++e) q[h][e] = s_q[h][8 * l8 + e];
+    for (int r0 = warp * RPW + sub; r0 < DEC_CHUNK; r0 += ROWS_PER_PASS * SUNR) {
+      uint4 kv[SUNR];
 #pragma unroll
-    for (int d8 = 0; d8 < D / 8; ++d8) {
-      const uint4 kv = *reinterpret_cast<const uint4*>(krow + d8 * 8);
-      const float2 a = unpack_bf16x2(kv.x), bq = unpack_bf16x2(kv.y), c = unpack_bf16x2(kv.z), e = unpack_bf16x2(kv.w);
+      for (int u = 0; u < SUNR; ++u) {
+        const int key = k0 + r0 + u * ROWS_PER_PASS;
+        if (active && key < k_end) {
+          const __nv_bfloat16* krow = (key == n_old) ? p.k_new + (long long)b * p.ld_qkv + hk * D : kc + key * row_stride;
+          kv[u] = *reinterpret_cast<const uint4*>(krow + 8 * l8);
+        } else {
+          kv[u] = make_uint4(0, 0, 0, 0);
+        }
+      }
 #pragma unroll
-      for (int h = 0; h < REP; ++h) {
-        const float* qh = &s_q[h][d8 * 8];
-        acc[h] += a.x * qh[0] + a.y * qh[1] + bq.x * qh[2] + bq.y * qh[3] + c.x * qh[4] + c.y * qh[5] + e.x * qh[6] + e.y * qh[7];
+      for (int u = 0; u < SUNR; ++u) {
+        const int r = r0 + u * ROWS_PER_PASS;
+        const float2 a = unpack_bf16x2(kv[u].x), bq = unpack_bf16x2(kv[u].y), c = unpack_bf16x2(kv[u].z), e = unpack_bf16x2(kv[u].w);
+        float part[REP];
+#pragma unroll
+        for (int h = 0; h < REP; ++h)
+          part[h] = a.x * q[h][0] + a.y * q[h][1] + bq.x * q[h][2] + bq.y * q[h][3] + c.x * q[h][4] + c.y * q[h][5] + e.x * q[h][6] + e.y * q[h][7];
+#pragma unroll
+        for (int off = LPR / 2; off > 0; off >>= 1)
+#pragma unroll
+          for (int h = 0; h < REP; ++h) part[h] += __shfl_xor_sync(0xffffffffu, part[h], off);
+        if (l8 == 0 && r < DEC_CHUNK) {
+          const bool valid = active && (k0 + r) < k_end;
+#pragma unroll
+          for (int h = 0; h < REP; ++h) s_p[h][r] = valid ? part[h] : -INFINITY;
+        }
       }
     }
   }
-#pragma unroll
-  for (int h = 0; h < REP; ++h) s_p[h][tid] = acc[h];
   __syncthreads();
   // ---- chunk softmax: warp h handles head h (REP <= 8 = number of warps)
   if (warp < REP) {
@@ -109,36 +131,228 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attn_kernel(const DecodeAr
     }
   }
   __syncthreads();
-  // ---- P V: thread (g, dp) sums keys g, g + G, ... for dims 2 dp, 2 dp + 1 of every head
-  constexpr int TPR = D / 2, G = DEC_THREADS / TPR;
-  const int g = tid / TPR, dp = tid % TPR;
-  float o0[REP], o1[REP];
+  // ---- P V: thread (g, d8) sums keys g, g + G, ... for the eight dims 8 d8 .. 8 d8 + 7 of every head.  A row is read by
+  // D / 8 threads with 16-byte loads and four rows are requested before the first is used: the loop is bound by the number of
+  // bytes in flight, not by arithmetic.
+  constexpr int TPR = D / 8, G = DEC_THREADS / TPR;  // threads per row, row groups
+  const int g = tid / TPR, d8 = tid % TPR;
+  float o[REP][8];
 #pragma unroll
-  for (int h = 0; h < REP; ++h) o0[h] = o1[h] = 0.f;
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[h][e] = 0.f;
   if (active) {
-    for (int kk = k0 + g; kk < k_end; kk += G) {
-      const __nv_bfloat16* vrow = (kk == n_old) ? p.v_new + (long long)b * p.ld_qkv + hk * D : vc + kk * row_stride;
-      const float2 vv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(vrow + 2 * dp));
+    constexpr int UNR = 4;
+    for (int kk = k0 + g; kk < k_end; kk += G * UNR) {
+      uint4 vv[UNR];
 #pragma unroll
-      for (int h = 0; h < REP; ++h) {
-        const float pr = s_p[h][kk - k0];
-        o0[h] += pr * vv.x;
-        o1[h] += pr * vv.y;
+      for (int u = 0; u < UNR; ++u) {
+        const int kr = kk + u * G;
+        if (kr < k_end) {
+          const __nv_bfloat16* vrow = (kr == n_old) ? p.v_new + (long long)b * p.ld_qkv + hk * D : vc + kr * row_stride;
+          vv[u] = *reinterpret_cast<const uint4*>(vrow + 8 * d8);
+        } else {
+          vv[u] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int kr = kk + u * G;
+        if (kr >= k_end) break;
+        const float2 v0 = unpack_bf16x2(vv[u].x), v1 = unpack_bf16x2(vv[u].y), v2 = unpack_bf16x2(vv[u].z), v3 = unpack_bf16x2(vv[u].w);
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+          const float pr = s_p[h][kr - k0];
+          o[h][0] += pr * v0.x; o[h][1] += pr * v0.y; o[h][2] += pr * v1.x; o[h][3] += pr * v1.y;
+          o[h][4] += pr * v2.x; o[h][5] += pr * v2.y; o[h][6] += pr * v3.x; o[h][7] += pr * v3.y;
+        }
       }
     }
   }
+  // fold the row groups that share a warp (lanes d8 and d8 + TPR, ...), then the warps through shared memory
 #pragma unroll
-  for (int h = 0; h < REP; ++h) {
-    s_red[g][h][2 * dp] = o0[h];
-    s_red[g][h][2 * dp + 1] = o1[h];
+  for (int off = TPR; off < 32; off <<= 1)
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[h][e] += __shfl_xor_sync(0xffffffffu, o[h][e], off);
+  if (lane < TPR) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_red[warp][h][8 * d8 + e] = o[h][e];
   }
   __syncthreads();
   for (int i = tid; i < REP * D; i += DEC_THREADS) {
     const int h = i / D, d = i % D;
     float t = 0.f;
 #pragma unroll
-    for (int gg = 0; gg < G; ++gg) t += s_red[gg][h][d];
+    for (int w = 0; w < DEC_THREADS / 32; ++w) t += s_red[w][h][d];
     p.part_o[(((long long)b * p.Hq + hk * REP + h) * p.n_chunks + chunk) * D + d] = t;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Tensor-core form of the same kernel (default).  With fp32 FMAs the kernel above issues ~1300 warp instructions per 32 keys
+// (four query heads per KV head, D = 128) and is bound by instruction issue at a third of HBM speed; both products are
+// therefore done with warp-level MMAs (m16n8k16, bf16 in, fp32 out) whose 16 rows hold the query heads of the group.  A
+// decode step is bandwidth-bound, so the warp-level MMA is enough; no shared-memory staging or transposing loads are needed:
+//
+// * S = Q K^T: the sum over the head dimension does not care about the order of its terms, so the dimension index is permuted
+//   such that the 16-byte piece a lane loads from a key row IS its B fragment for two consecutive k-steps (words 0,1 and 2,3);
+//   the Q fragments are read from global memory with the same permutation.
+// * O = P V: B wants two KEYS of one dimension in a register, memory holds two DIMENSIONS of one key in a word.  A lane loads
+//   16 bytes (four such words) of four keys and two byte permutes per word turn them into the fragments of TWO column tiles, one
+//   holding the even and one the odd dimension of the words; output columns are just another order of the dimensions.
+// Every warp handles 32 keys of the chunk for all dimensions; the warps' partial outputs are folded through shared memory.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_16816_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int D, int REP>
+__global__ void __launch_bounds__(DEC_THREADS) decode_attn_mma_kernel(const DecodeArgs p) {
+  static_assert(REP <= 8 && D % 32 == 0, "query heads of a group sit in rows 0..7 of the MMA");
+  __shared__ float s_p[REP][DEC_CHUNK];
+  __shared__ __align__(16) float s_red[DEC_THREADS / 32][REP][D];
+  const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_old = p.lengths ? p.lengths[b] : p.length;
+  const int n_tot = n_old + 1;  // the new token attends to itself
+  const int k0 = chunk * DEC_CHUNK;
+  const bool active = k0 < n_tot;
+  const int k_end = min(k0 + DEC_CHUNK, n_tot);
+  __nv_bfloat16* kc = p.k_cache + (long long)b * p.cache_b_stride + (long long)hk * D;
+  __nv_bfloat16* vc = p.v_cache + (long long)b * p.cache_b_stride + (long long)hk * D;
+  const long long row_stride = (long long)p.Hkv * D;
+  const __nv_bfloat16* k_new = p.k_new + (long long)b * p.ld_qkv + hk * D;
+  const __nv_bfloat16* v_new = p.v_new + (long long)b * p.ld_qkv + hk * D;
+  // the new token's K / V row goes into the cache (by the CTA that owns its position); this CTA reads it from the projection
+  if (active && n_old >= k0 && n_old < k0 + DEC_CHUNK && n_old < p.max_len) {
+    for (int d = tid; d < D; d += DEC_THREADS) {
+      kc[n_old * row_stride + d] = k_new[d];
+      vc[n_old * row_stride + d] = v_new[d];
+    }
+  }
+  const int kw0 = warp * 32;  // this warp's keys inside the chunk
+
+  // ---- S = Q K^T
+  {
+    uint32_t qa[D / 16][2];  // A fragments (rows g < REP): [virtual k-step][a0, a2]
+    const uint32_t* qrow = reinterpret_cast<const uint32_t*>(p.q + (long long)b * p.ld_qkv + (hk * REP + (g < REP ? g : 0)) * D);
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (g < REP) w = *reinterpret_cast<const uint4*>(qrow + 4 * (4 * j + t));
+      qa[2 * j][0] = w.x; qa[2 * j][1] = w.y; qa[2 * j + 1][0] = w.z; qa[2 * j + 1][1] = w.w;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int r = kw0 + nt * 8 + g;  // the key whose row this lane loads (column g of the tile)
+      const int key = k0 + r;
+      const bool ok = active && key < k_end;
+      const __nv_bfloat16* krow = (key == n_old) ? k_new : kc + key * row_stride;
+      uint4 kv[D / 32];
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) kv[j] = ok ? *reinterpret_cast<const uint4*>(krow + 8 * (4 * j + t)) : make_uint4(0, 0, 0, 0);
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) {
+        mma_16816_bf16(c, qa[2 * j][0], 0u, qa[2 * j][1], 0u, kv[j].x, kv[j].y);
+        mma_16816_bf16(c, qa[2 * j + 1][0], 0u, qa[2 * j + 1][1], 0u, kv[j].z, kv[j].w);
+      }
+      if (g < REP) {  // c[0], c[1]: head g, keys 2t and 2t + 1 of the tile
+        const int c0 = kw0 + nt * 8 + 2 * t;
+        s_p[g][c0] = (active && k0 + c0 < k_end) ? c[0] * p.scale : -INFINITY;
+        s_p[g][c0 + 1] = (active && k0 + c0 + 1 < k_end) ? c[1] * p.scale : -INFINITY;
+      }
+    }
+  }
+  __syncthreads();
+  // ---- chunk softmax: warp h handles head h (REP <= 8 = number of warps)
+  if (warp < REP) {
+    float m = -INFINITY;
+    for (int i = lane; i < DEC_CHUNK; i += 32) m = fmaxf(m, s_p[warp][i]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int i = lane; i < DEC_CHUNK; i += 32) {
+      const float e = (m == -INFINITY) ? 0.f : __expf(s_p[warp][i] - m);
+      s_p[warp][i] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      float* ml = p.part_ml + (((long long)b * p.Hq + hk * REP + warp) * p.n_chunks + chunk) * 2;
+      ml[0] = m;
+      ml[1] = l;
+    }
+  }
+  __syncthreads();
+  // ---- O = P V over this warp's 32 keys (two blocks of 16), all dimensions.  Lane (g, t) loads 16 bytes (dims 64 rd + 8 g .. + 7)
+  // of four keys: eight lanes cover 128 contiguous bytes of a row.  Word i of the piece holds dims 8 g + 2 i, + 1: the low halves of
+  // two keys form the B fragment of the column tile "even dims of word i", the high halves that of "odd dims of word i".
+  constexpr int RD = D / 64;
+  float oe[RD][4][4], oo[RD][4][4];
+#pragma unroll
+  for (int rd = 0; rd < RD; ++rd)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oe[rd][i][e] = oo[rd][i][e] = 0.f;
+  if (active && k0 + kw0 < k_end) {
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      const int kk0 = kw0 + kb * 16;
+      if (k0 + kk0 >= k_end) break;
+      uint32_t pa0 = 0u, pa2 = 0u;  // P fragments (bf16 pairs): keys 2t, 2t + 1 and 2t + 8, 2t + 9 of head g
+      if (g < REP) {
+        pa0 = pack_bf16x2(s_p[g][kk0 + 2 * t], s_p[g][kk0 + 2 * t + 1]);
+        pa2 = pack_bf16x2(s_p[g][kk0 + 2 * t + 8], s_p[g][kk0 + 2 * t + 9]);
+      }
+      uint4 w[RD][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int key = k0 + kk0 + 2 * t + (i & 1) + (i >> 1) * 8;
+        const __nv_bfloat16* vrow = (key == n_old) ? v_new : vc + key * row_stride;
+#pragma unroll
+        for (int rd = 0; rd < RD; ++rd)
+          w[rd][i] = key < k_end ? *reinterpret_cast<const uint4*>(vrow + 64 * rd + 8 * g) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int rd = 0; rd < RD; ++rd) {
+        const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&w[rd][0]);
+        const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&w[rd][1]);
+        const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&w[rd][2]);
+        const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&w[rd][3]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mma_16816_bf16(oe[rd][i], pa0, 0u, pa2, 0u, __byte_perm(w0[i], w1[i], 0x5410), __byte_perm(w2[i], w3[i], 0x5410));
+          mma_16816_bf16(oo[rd][i], pa0, 0u, pa2, 0u, __byte_perm(w0[i], w1[i], 0x7632), __byte_perm(w2[i], w3[i], 0x7632));
+        }
+      }
+    }
+  }
+  // lane (g, t), head g: accumulator column 2t is dim 64 rd + 16 t + 2 i (+ 1 for the odd tile), column 2t + 1 eight dims further
+  if (g < REP) {
+#pragma unroll
+    for (int rd = 0; rd < RD; ++rd) {
+      float* dst = &s_red[warp][g][64 * rd + 16 * t];
+      *reinterpret_cast<float4*>(dst) = make_float4(oe[rd][0][0], oo[rd][0][0], oe[rd][1][0], oo[rd][1][0]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(oe[rd][2][0], oo[rd][2][0], oe[rd][3][0], oo[rd][3][0]);
+      *reinterpret_cast<float4*>(dst + 8) = make_float4(oe[rd][0][1], oo[rd][0][1], oe[rd][1][1], oo[rd][1][1]);
+      *reinterpret_cast<float4*>(dst + 12) = make_float4(oe[rd][2][1], oo[rd][2][1], oe[rd][3][1], oo[rd][3][1]);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < REP * D; i += DEC_THREADS) {
+    const int h = i / D, d = i % D;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) acc += s_red[w][h][d];
+    p.part_o[(((long long)b * p.Hq + hk * REP + h) * p.n_chunks + chunk) * D + d] = acc;
   }
 }
 
@@ -306,14 +520,155 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const SampleArgs p)
   if (tid == 0) p.out[b] = s_pick < V ? s_pick : s_arg;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Mixture-of-experts routing of a decode-sized step (at most 1024 (token, k) slots): three launches around the two grouped
+// GEMMs instead of gate GEMM + soft-max + top-k + slot plan + dispatch + pointer tables.
+//
+// serve_gate_route_kernel    one CTA per token: gate logits (one warp per expert row, fp32 accumulation), soft-max of
+//                            logits / temperature over ALL experts, top-k, kept probabilities renormalised to sum to one
+//                            (reference core/model.py:1169-1217).
+// serve_plan_dispatch_kernel one warp per slot: its rank among the earlier slots of the same expert (token order, so the
+//                            result equals the training-time plan), then the row copy into the expert's block; the block may
+//                            live on a peer GPU (dst_table) or be e * dst_stride elements into a local buffer.
+// serve_combine_kernel       one CTA per token: out = residual + sum_j w_j * row_j, rows read through the same addressing.
+// ------------------------------------------------------------------------------------------------
+constexpr int SRV_MAX_E = 64, SRV_MAX_K = 8;
+
+__global__ void __launch_bounds__(256) serve_gate_route_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg,
+                                                               int* __restrict__ topk_idx, float* __restrict__ topk_w, int hidden,
+                                                               int experts, int k, float inv_temp) {
+  __shared__ float s_logit[SRV_MAX_E];
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)t * hidden);
+  const int nvec = hidden >> 3;
+  for (int e = warp; e < experts; e += nwarps) {
+    const uint4* wr = reinterpret_cast<const uint4*>(wg + (long long)e * hidden);
+    float acc = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 a = xr[v], b = wr[v];
+      const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+      const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+      acc += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) s_logit[e] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float p[SRV_MAX_E];
+    float m = -INFINITY;
+    for (int e = 0; e < experts; ++e) m = fmaxf(m, s_logit[e]);
+    float sum = 0.f;
+    for (int e = 0; e < experts; ++e) {
+      p[e] = __expf((s_logit[e] - m) * inv_temp);
+      sum += p[e];
+    }
+    const float inv = 1.f / sum;
+    unsigned long long taken = 0ull;
+    float wk[SRV_MAX_K], wsum = 0.f;
+    int ik[SRV_MAX_K];
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int bi = 0;
+      for (int e = 0; e < experts; ++e)
+        if (!((taken >> e) & 1ull) && p[e] * inv > best) {
+          best = p[e] * inv;
+          bi = e;
+        }
+      taken |= 1ull << bi;
+      wk[j] = best;
+      ik[j] = bi;
+      wsum += best;
+    }
+    const float wi = 1.f / fmaxf(wsum, 1e-20f);
+    for (int j = 0; j < k; ++j) {
+      topk_idx[t * k + j] = ik[j];
+      topk_w[t * k + j] = wk[j] * wi;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) serve_plan_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx,
+                                                                  int* __restrict__ slot_pos, int* __restrict__ counts,
+                                                                  int* __restrict__ totals, __nv_bfloat16* const* __restrict__ dst_table,
+                                                                  __nv_bfloat16* dst0, long long dst_stride, int slots, int k, int hidden,
+                                                                  int experts, int capacity) {
+  const int lane = threadIdx.x & 31;
+  const int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // this warp's slot
+  if (blockIdx.x == 0 && (counts || totals)) {
+    // per-expert demand (block 0 only; any order gives the same sums)
+    __shared__ int s_cnt[SRV_MAX_E];
+    if (threadIdx.x < SRV_MAX_E) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < slots; i += blockDim.x) atomicAdd(&s_cnt[topk_idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x < experts) {
+      const int tot = s_cnt[threadIdx.x];
+      if (counts) counts[threadIdx.x] = tot < capacity ? tot : capacity;
+      if (totals) totals[threadIdx.x] = tot;
+    }
+  }
+  if (s >= slots) return;
+  const int e = topk_idx[s];
+  int rank = 0;
+  for (int i = lane; i < s; i += 32) rank += topk_idx[i] == e;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+  const int pos = rank < capacity ? rank : -1;
+  if (lane == 0) slot_pos[s] = pos;
+  if (pos < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)(s / k) * hidden);
+  __nv_bfloat16* base = dst_table ? dst_table[e] : dst0 + (long long)e * dst_stride;
+  uint4* d = reinterpret_cast<uint4*>(base + (long long)pos * hidden);
+  for (int v = lane; v < (hidden >> 3); v += 32) d[v] = src[v];
+}
+
+__global__ void __launch_bounds__(256) serve_combine_kernel(__nv_bfloat16* const* __restrict__ src_table, const __nv_bfloat16* src0,
+                                                            long long src_stride, const int* __restrict__ topk_idx,
+                                                            const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
+                                                            const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int k,
+                                                            int hidden) {
+  const int t = blockIdx.x;
+  const int nvec = hidden >> 3;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (res) {
+      const uint4 a = reinterpret_cast<const uint4*>(res + (long long)t * hidden)[v];
+      const float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+    }
+    for (int j = 0; j < k; ++j) {
+      const int pos = slot_pos[t * k + j];
+      if (pos < 0) continue;
+      const int e = topk_idx[t * k + j];
+      const float wt = topk_w[t * k + j];
+      const __nv_bfloat16* base = src_table ? src_table[e] : src0 + (long long)e * src_stride;
+      const uint4 a = reinterpret_cast<const uint4*>(base + (long long)pos * hidden)[v];
+      const float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
+      acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
+    }
+    reinterpret_cast<uint4*>(out + (long long)t * hidden)[v] =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
 }  // namespace ats
 
 using namespace ats;
 
+// 1 (default): warp-level tensor-core kernel; 0: the fp32 CUDA-core kernel (kept for comparison, ATS_DECODE_ATTN_MMA=0)
+static int g_decode_mma = -1;
 template <int D, int REP>
 static int launch_decode(const DecodeArgs& p, cudaStream_t s) {
+  if (g_decode_mma < 0) {
+    const char* e = getenv("ATS_DECODE_ATTN_MMA");
+    g_decode_mma = (e && e[0] == '0') ? 0 : 1;
+  }
   dim3 grid(p.n_chunks, p.Hkv, p.B);
-  decode_attn_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
+  if (g_decode_mma) decode_attn_mma_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
+  else decode_attn_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
   return int(cudaGetLastError());
 }
 
@@ -364,5 +719,35 @@ ATS_API int ats_sample(const void* logits, int logits_fp32, long long ld, float*
   p.uniform = uniform; p.out = out; p.V = V;
   p.temperature = temperature; p.top_p = top_p; p.rep_penalty = rep_penalty; p.top_k = top_k;
   sample_kernel<<<B, SMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return int(cudaGetLastError());
+}
+
+// ---- decode-sized mixture-of-experts routing (see the kernels above) ----------------------------------------------
+ATS_API int ats_serve_gate_route(const void* x, const void* wg, int* topk_idx, float* topk_w, int tokens, int hidden, int experts, int k,
+                                 float temperature, void* stream) {
+  if (tokens <= 0 || experts < 1 || experts > SRV_MAX_E || k < 1 || k > SRV_MAX_K || k > experts || (hidden & 7)) return 1003;
+  serve_gate_route_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wg), topk_idx, topk_w, hidden, experts, k, 1.f / temperature);
+  return int(cudaGetLastError());
+}
+
+// dst_table: device array of `experts` base pointers (blocks on peer GPUs), or null with dst0 + e * dst_stride (elements).
+ATS_API int ats_serve_plan_dispatch(const void* x, const int* topk_idx, int* slot_pos, int* counts, int* totals, void* const* dst_table,
+                                    void* dst0, long long dst_stride, int tokens, int k, int hidden, int experts, int capacity,
+                                    void* stream) {
+  const int slots = tokens * k;
+  if (slots <= 0 || slots > 1024 || experts < 1 || experts > SRV_MAX_E || (hidden & 7) || (!dst_table && !dst0)) return 1003;
+  serve_plan_dispatch_kernel<<<(slots * 32 + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), topk_idx, slot_pos, counts, totals, reinterpret_cast<__nv_bfloat16* const*>(dst_table),
+      static_cast<__nv_bfloat16*>(dst0), dst_stride, slots, k, hidden, experts, capacity);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_serve_combine(void* const* src_table, const void* src0, long long src_stride, const int* topk_idx, const int* slot_pos,
+                              const float* topk_w, const void* residual, void* out, int tokens, int k, int hidden, void* stream) {
+  if (tokens <= 0 || (hidden & 7) || (!src_table && !src0)) return 1003;
+  serve_combine_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16* const*>(src_table), static_cast<const __nv_bfloat16*>(src0), src_stride, topk_idx, slot_pos, topk_w,
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), k, hidden);
   return int(cudaGetLastError());
 }

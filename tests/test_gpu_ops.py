@@ -602,3 +602,36 @@ def test_quantization_manager_fp8_inference_close_to_bf16():
     assert cos > 0.995, cos
     with pytest.raises(RuntimeError):
         QuantizationManager(SimpleNamespace(quantization_method="gptq", quantization_bits=4)).quantize_model(model)
+
+
+def test_decode_sized_moe_layer_matches_the_general_path():
+    """Serving kernels (gate + route, plan + dispatch, combine in three launches) against the training-time path of the same
+    layer and against the fp32 per-expert loop, for a decode-sized step."""
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models import MoEFFNLayer
+    from adaptivetrainingsystem_b200.ops import moe as M
+    torch.manual_seed(11)
+    cfg = ModelConfig(vocab_size=512, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2, intermediate_size=768, seq_length=64,
+                      use_moe=True, num_experts=8, moe_top_k=2, capacity_factor=1.25, routing_temperature=0.7)
+    layer = MoEFFNLayer(cfg, 0)
+    with torch.no_grad():
+        torch.nn.init.normal_(layer.gate.weight, std=0.2)
+        torch.nn.init.normal_(layer.experts_w1, std=0.05)
+        torch.nn.init.normal_(layer.experts_w2, std=0.05)
+    layer = layer.to("cuda", torch.bfloat16).eval()
+    for T in (1, 7, 64, 200):
+        h = torch.randn(T, 1, 512, device="cuda").bfloat16()
+        res = torch.randn(T, 1, 512, device="cuda").bfloat16()
+        with torch.no_grad():
+            assert M.serving_path_ok(h.reshape(-1, 512), 8, 2)
+            fast, _ = layer(h, res)
+        with torch.enable_grad():  # autograd on: the general (training) path of the same layer
+            slow, _ = layer(h, res)
+        x = h.reshape(-1, 512)
+        logits = x.float() @ layer.gate.weight.float().t()
+        idx, w, _ = M.route(logits, 2, 0.7)
+        ref = M.moe_ffn_reference(x.float(), idx, w, layer.experts_w1.float(), layer.experts_w2.float(), 10 ** 6) + res.reshape(-1, 512).float()
+        for got in (fast, slow.detach()):
+            err = (got.reshape(-1, 512).float() - ref).norm(dim=-1) / (ref.norm(dim=-1) + 1e-6)
+            assert err.max().item() < 2e-2, (T, err.max().item())
+    ops.check_status()

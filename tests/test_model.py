@@ -122,7 +122,7 @@ def test_dropless_routing_is_selectable_from_config_and_matches_the_per_expert_l
         mc = cfg.to_model_config()
         assert mc.drop_tokens is drop
         torch.manual_seed(3)
-        layer = MoEFFNLayer(mc, 0).eval()
+        layer = MoEFFNLayer(mc, 0).train()  # training mode keeps the routing statistics (routing noise is off in this config)
         with torch.no_grad():
             torch.nn.init.normal_(layer.experts_w1, std=0.1)
             torch.nn.init.normal_(layer.experts_w2, std=0.1)
