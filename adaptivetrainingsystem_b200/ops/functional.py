@@ -333,14 +333,28 @@ def _deliver_grad(w: torch.Tensor, compute):
     return None
 
 
+def _z3_gathering(w):
+    """The row-sharded (ZeRO-3) description of ``w`` when its rows are NOT gathered on this rank right now and the product has to
+    pull them itself (``parallel/zero3.py``); otherwise ``None``."""
+    z3 = getattr(w, "_ats_z3", None)
+    return z3 if (z3 is not None and z3.full is None and z3.gather_in_gemm) else None
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, residual):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
-        r2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
-        y = torch.empty(*shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
-        G.gemm_nt(x2, w, out=y.view(-1, w.shape[0]), add=r2)
+        z3 = _z3_gathering(w)
+        n_out = z3.N if z3 is not None else w.shape[0]
+        r2 = residual.reshape(-1, n_out) if residual is not None else None
+        y = torch.empty(*shape[:-1], n_out, dtype=x.dtype, device=x.device)
+        if z3 is not None:
+            # the weight lives as row shards on the data-parallel ranks: the GEMM launch gathers it while it computes
+            from ..parallel.fused_linear import gathered_gemm
+            gathered_gemm(x2, z3, out=y.view(-1, n_out), add=r2)
+        else:
+            G.gemm_nt(x2, w, out=y.view(-1, n_out), add=r2)
         ctx.save_for_backward(x2, w)
         ctx.has_res = residual is not None
         ctx.shape = shape
@@ -363,7 +377,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     """``x @ w.T (+ residual)`` -- the residual add is fused into the GEMM epilogue."""
     if _lib.use_cuda_kernels(x):
         from . import fp8
-        if fp8.enabled() and x.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0:
+        if fp8.enabled() and getattr(w, "_ats_z3", None) is None and x.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0:
             return fp8.linear_fp8(x, w, residual)
         return _LinearFn.apply(x, w, residual)
     y = F.linear(x, w)
@@ -416,11 +430,19 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         need_bwd = any(ctx.needs_input_grad)
-        pre = torch.empty(x2.shape[0], w1.shape[0], dtype=x.dtype, device=x.device) if need_bwd else None
-        r2 = residual.reshape(-1, w2.shape[0]) if residual is not None else None
-        y = torch.empty(*shape[:-1], w2.shape[0], dtype=x.dtype, device=x.device)
+        z1, z2 = _z3_gathering(w1), _z3_gathering(w2)
+        n1 = z1.N if z1 is not None else w1.shape[0]
+        n2 = z2.N if z2 is not None else w2.shape[0]
+        pre = torch.empty(x2.shape[0], n1, dtype=x.dtype, device=x.device) if need_bwd else None
+        r2 = residual.reshape(-1, n2) if residual is not None else None
+        y = torch.empty(*shape[:-1], n2, dtype=x.dtype, device=x.device)
         from . import fp8
-        if fp8.enabled() and x2.shape[1] % 16 == 0 and w1.shape[0] % 32 == 0:
+        if z1 is not None and z2 is not None:
+            # ZeRO-3 row shards: both products gather their weight inside the GEMM launch (SwiGLU and residual epilogues as usual)
+            from ..parallel.fused_linear import gathered_gemm
+            h = gathered_gemm(x2, z1, swiglu=True, pre_act=pre)
+            gathered_gemm(h, z2, out=y.view(-1, n2), add=r2)
+        elif fp8.enabled() and x2.shape[1] % 16 == 0 and w1.shape[0] % 32 == 0:
             # e4m3 forward products (per-token / per-channel scales); the backward below stays in bf16
             xq, xs = fp8.quantize_rows(x2)
             w1q, w1s = fp8.quantized_weight(w1)

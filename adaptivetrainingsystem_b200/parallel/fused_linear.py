@@ -104,7 +104,8 @@ def gathered_gemm(x2: torch.Tensor, w: ShardedWeight, out: Optional[torch.Tensor
         w.calls = 1
     epi = G.EPI_SWIGLU if swiglu else (G.EPI_ADDC if add is not None else G.EPI_STORE)
     st = _lib.status_tensor(x2.device)
-    err = _fn()(_lib.ptr(x2), x2.stride(0), _lib.ptr(ctx.staging), _lib.ptr(w.shard), w.N, _lib.ptr(w.src_table), ctx.world, ctx.rank, GatherContext.READY_ROWS,
+    err = _fn()(_lib.ptr(x2), x2.stride(0), _lib.ptr(ctx.staging), _lib.ptr(w.shard), w.N, _lib.ptr(w.src_table), ctx.world, ctx.rank,
+                getattr(w, "ready_rows", GatherContext.READY_ROWS),
                 _lib.ptr(w.flags), w.calls, _lib.ptr(out), out.stride(0), _lib.ptr(add), add.stride(0) if add is not None else 0,
                 _lib.ptr(pre_act), pre_act.stride(0) if pre_act is not None else 0, M, n_out, K, epi, w.N // 2 if swiglu else 0,
                 _lib.ptr(st), _lib.stream_ptr(x2.device))

@@ -112,7 +112,11 @@ def fused_check(args, cfg_name, mesh, over) -> dict:
             torch.set_default_dtype(torch.float32)
         model.rope.cos, model.rope.sin = model.rope.cos.float(), model.rope.sin.float()
         comm = attach_expert_parallel(model, mesh, cfg, use_fused=fused)
-        eng = ShardedEngine(model, lr=1e-3, zero_stage=max(cfg.zero_stage, 1), max_grad_norm=1.0, mesh=mesh, fused_comm=comm)
+        if cfg.zero_stage >= 3 and mesh.ep_size == 1:
+            from adaptivetrainingsystem_b200.parallel.zero3 import ZeRO3Engine
+            eng = ZeRO3Engine(model, lr=1e-3, max_grad_norm=1.0, mesh=mesh, fused_comm=comm)
+        else:
+            eng = ShardedEngine(model, lr=1e-3, zero_stage=max(min(cfg.zero_stage, 2), 1), max_grad_norm=1.0, mesh=mesh, fused_comm=comm)
         losses = []
         for _ in range(2):
             out = model.forward_loss(ids[:, :-1], ids[:, 1:])
@@ -121,9 +125,15 @@ def fused_check(args, cfg_name, mesh, over) -> dict:
             losses.append(out["loss"].detach().float())
         torch.cuda.synchronize()
         ops.check_status()
-        runs[name] = (torch.stack(losses), float(eng.last_grad_norm), {k: v.detach().float().clone() for k, v in model.state_dict().items()},
-                      bool(fused and comm is not None and comm.usable(eng)))
+        if hasattr(eng, "gather_full_parameters"):
+            eng.gather_full_parameters()
+            used = bool(fused and eng.fused)
+        else:
+            used = bool(fused and comm is not None and comm.usable(eng))
+        runs[name] = (torch.stack(losses), float(eng.last_grad_norm), {k: v.detach().float().clone() for k, v in model.state_dict().items()}, used)
         ep_comm = getattr(model, "_ep_comm", None)
+        if hasattr(eng, "close"):
+            eng.close()
         del eng, model
         if ep_comm is not None:
             ep_comm.close()
@@ -171,7 +181,7 @@ def run_ours(args) -> dict:
     mesh = ProcessMesh(world, rank, ep_size=ep)
     cfg.world_size, cfg.expert_parallel_size = world, ep
     check = None
-    if world > 1 and cfg.fused_comm and not args.no_fused_check and cfg.zero_stage <= 2:
+    if world > 1 and cfg.fused_comm and not args.no_fused_check:
         check = fused_check(args, args.config, mesh, over)
         if not check["ok"]:
             raise SystemExit(f"fused paths disagree with their NCCL twins: {json.dumps(check)}")
@@ -293,6 +303,8 @@ def run_ours(args) -> dict:
     # tear the training job down (buckets and exchange buffers live outside PyTorch's allocator) before the serving models are built
     trainer.shutdown()
     ep_comm = getattr(model, "_ep_comm", None)
+    if hasattr(trainer.engine, "close"):
+        trainer.engine.close()
     del trainer, devb, model
     import gc
     gc.collect()

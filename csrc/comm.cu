@@ -172,6 +172,43 @@ __global__ void __launch_bounds__(256) peer_copy_kernel(const uint4* __restrict_
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
+// All-gather by pulling: dst[q * shard + i] = shards_q[i] for every rank q (this rank's own shard included), 16-byte vectors.
+// Launched on a side stream with a bounded number of CTAs so that it overlaps the compute stream's GEMMs (ZeRO-3 prefetch).
+__global__ void __launch_bounds__(256) peer_gather_kernel(PeerPtrs shards, int world, uint4* __restrict__ dst, long long shard_vec,
+                                                          const int* __restrict__ status) {
+  if (status && *status != 0) return;
+  const long long total = shard_vec * world;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int q = int(i / shard_vec);
+    dst[i] = static_cast<const uint4*>(shards.p[q])[i - q * shard_vec];
+  }
+}
+
+// Reduce-scatter by pulling, for one row-sharded matrix: out32[i] (+)= sum_q grads_q[offset + i], i < n (n, offset % 8 == 0).
+// fp32 accumulation in registers; `accumulate` adds to what out32 holds (later micro-batches of one optimiser step).
+__global__ void __launch_bounds__(256)
+peer_reduce_rows_kernel(PeerPtrs grads, int world, int rank, long long offset, long long n, float* __restrict__ out32, int accumulate,
+                        const int* __restrict__ status) {
+  if (status && *status != 0) return;
+  const long long nvec = n >> 3;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (accumulate) {
+      const float4 a = reinterpret_cast<const float4*>(out32)[2 * v], b = reinterpret_cast<const float4*>(out32)[2 * v + 1];
+      acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+    }
+#pragma unroll 4
+    for (int q = 0; q < world; ++q) {
+      const int p = (rank + q) % world;
+      const uint4 a = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[p]) + offset)[v];
+      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+    reinterpret_cast<float4*>(out32)[2 * v] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    reinterpret_cast<float4*>(out32)[2 * v + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
 static PeerPtrs to_peers(void* const* host_ptrs, int world) {
   PeerPtrs pp;
   for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? host_ptrs[i] : nullptr;
@@ -261,5 +298,29 @@ ATS_API int ats_peer_copy(const void* src, void* dst, long long bytes, int max_b
   if (blocks > cap) blocks = cap;
   peer_copy_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src),
                                                                                   static_cast<uint4*>(dst), nvec);
+  return int(cudaGetLastError());
+}
+
+// shards: host array of `world` device pointers (every rank's shard, this rank's own included); dst: world * shard_bytes.
+ATS_API int ats_peer_gather(void* const* shards, int world, void* dst, long long shard_bytes, int max_blocks, const int* status,
+                            void* stream) {
+  if (world < 1 || world > MAX_PEERS || (shard_bytes & 15) || shard_bytes <= 0) return 1003;
+  const long long total = (shard_bytes >> 4) * world;
+  long long blocks = (total + 255) / 256;
+  const long long cap = max_blocks > 0 ? max_blocks : 148 * 4;
+  if (blocks > cap) blocks = cap;
+  peer_gather_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(shards, world), world, static_cast<uint4*>(dst),
+                                                                                      shard_bytes >> 4, status);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_peer_reduce_rows(void* const* grads, int world, int rank, long long offset, long long n, float* out32, int accumulate,
+                                 const int* status, int max_blocks, void* stream) {
+  if (world < 1 || world > MAX_PEERS || (n & 7) || (offset & 7) || n <= 0) return 1003;
+  long long blocks = (n / 8 + 255) / 256;
+  const long long cap = max_blocks > 0 ? max_blocks : 148 * 4;
+  if (blocks > cap) blocks = cap;
+  peer_reduce_rows_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(grads, world), world, rank, offset, n, out32,
+                                                                                           accumulate, status);
   return int(cudaGetLastError());
 }

@@ -122,8 +122,9 @@ def _zero3_worker(rank, world, ref_path):
     sd = model.state_dict()
     for k, v in ref.items():
         assert torch.allclose(sd[k], v, atol=3e-5, rtol=1e-4), (k, (sd[k] - v).abs().max())
-    u = eng.units[0]
-    assert u.master.numel() * world == u.padded
+    m = eng.matrices[0]
+    assert m.master.numel() * world == m.numel and m.shard.shape == (m.N // world, m.K)  # row shards of every block matrix
+    assert eng.root.master.numel() * world == eng.root.padded                           # flat shard of everything else
 
 
 def test_zero3_matches_single_process(tmp_path):
@@ -231,3 +232,36 @@ def _ep_eval_worker(rank, world):
 
 def test_expert_parallel_eval_shares_buffers():
     run_dist(_ep_eval_worker, 2)
+
+
+def _fsdp_backend_worker(rank, world):
+    """The backend factories of the reference's wrapper API reach the stage-3 engine: FULL_SHARD / gemini / zero_stage 3."""
+    from adaptivetrainingsystem_b200.backend import create_colossalai_backend, create_deepspeed_backend, create_fsdp_backend
+    from adaptivetrainingsystem_b200.config import Config
+    from adaptivetrainingsystem_b200.parallel.zero3 import ZeRO3Engine
+    cfg = Config(vocab_size=512, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=128, seq_length=32, use_moe=False,
+                 precision="fp32", gradient_checkpointing=False, zero_stage=3, output_dir="/tmp/ats_backend_test", experiment_name=f"r{rank}")
+    full_numel = None
+    for make in (lambda m: create_fsdp_backend(m, cfg), lambda m: create_deepspeed_backend(m, cfg), lambda m: create_colossalai_backend(m, cfg, "gemini")):
+        torch.manual_seed(0)
+        model = DeepSeekTransformer(cfg.to_model_config())
+        full_numel = sum(p.numel() for p in model.parameters())
+        be = make(model)
+        assert isinstance(be.engine, ZeRO3Engine) and be.engine.zero_stage == 3
+        block_params = sum(m.numel for m in be.engine.matrices)
+        assert sum(m.shard_numel for m in be.engine.matrices) * world == block_params  # this rank holds 1 / world of every block matrix
+        assert all(m.param.numel() == 0 for m in be.engine.matrices)                      # nothing is gathered at rest
+        g = torch.Generator().manual_seed(5)
+        ids = torch.randint(0, 512, (2, 33), generator=g)
+        out = be._model.forward_loss(ids[:, :-1], ids[:, 1:])
+        be.backward(out["loss"])
+        stats = be.step()
+        assert float(stats["grad_norm"]) > 0
+    cfg.fsdp_sharding_strategy = "SHARD_GRAD_OP"
+    be = create_fsdp_backend(DeepSeekTransformer(cfg.to_model_config()), cfg)
+    assert not isinstance(be.engine, ZeRO3Engine) and be.engine.zero_stage == 2
+    assert full_numel > 0
+
+
+def test_backend_factories_build_the_stage3_engine():
+    run_dist(_fsdp_backend_worker, 2)
