@@ -36,7 +36,7 @@ def _fn():
             _c_int, _c_int, _vp,  # groups ragged counts
             _c_int, _c_int, _c_int, _c_int,  # group coordinate shifts
             _c_ll, _c_ll, _c_ll,  # d_gs c_gs aux_gs
-            _c_int, _c_int, _c_int, _vp, _c_int,  # b_div k_segs seg_stride d_table k_split
+            _c_int, _c_int, _c_int, _vp, _c_int, _c_int,  # b_div k_segs seg_stride d_table k_split scatter_rows
             _vp, _c_int, _vp]  # status, max_ctas, stream
         lib.ats_splitk_reduce.restype = _c_int
         lib.ats_splitk_reduce.argtypes = [_vp, _c_int, _c_ll, _c_ll, _vp, _vp, _vp]
@@ -61,13 +61,13 @@ def set_pair_kernels(on: bool) -> None:
 def _raw(a, a_rows, a_cols, lda, a_mn, b, b_rows, b_cols, ldb, b_mn, d, ldd, c, ldc, aux, ldaux,
          M, N, K, alpha=1.0, beta=0, epilogue=EPI_STORE, up_offset=0, groups=1, ragged=0, counts=None,
          a_gs_mn=0, a_gs_k=0, b_gs_mn=0, b_gs_k=0, d_gs=0, c_gs=0, aux_gs=0, max_ctas=0,
-         b_div=1, k_segs=1, seg_stride=0, d_table=None, k_split=1):
+         b_div=1, k_segs=1, seg_stride=0, d_table=None, k_split=1, scatter_rows=0):
     st = _lib.status_tensor(a.device)
     err = _fn()(_lib.ptr(a), a_rows, a_cols, lda, a_mn, _lib.ptr(b), b_rows, b_cols, ldb, b_mn,
                 _lib.ptr(d), ldd, _lib.ptr(c), ldc, _lib.ptr(aux), ldaux,
                 M, N, K, alpha, beta, epilogue, up_offset, groups, ragged, _lib.ptr(counts),
                 a_gs_mn, a_gs_k, b_gs_mn, b_gs_k, d_gs, c_gs, aux_gs,
-                b_div, k_segs, seg_stride, _lib.ptr(d_table), k_split,
+                b_div, k_segs, seg_stride, _lib.ptr(d_table), k_split, scatter_rows,
                 _lib.ptr(st), max_ctas, _lib.stream_ptr(a.device))
     _lib.check(err, "ats_gemm_bf16")
 
@@ -176,9 +176,30 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+class ScatterTarget:
+    """Destination of a weight-gradient product whose rows are owned by different ranks (ZeRO-3 row shards): ``table`` is a
+    device int64 tensor with the address of every owner's fp32 gradient rows, ``rows`` the number of rows per owner.  Passed
+    as ``out`` to :func:`gemm_tn`, which then adds its result into the owners' buffers from the GEMM epilogue (reduce-scatter
+    fused into the product; always accumulating -- the owners zero their shards once per optimiser step)."""
+
+    def __init__(self, table: torch.Tensor, rows: int, shape):
+        self.table, self.rows, self.shape = table, rows, tuple(shape)
+
+    def view(self, *shape):
+        return self
+
+
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
             alpha: float = 1.0, out_fp32: bool = False, max_ctas: int = 0) -> torch.Tensor:
     """a[K,M]^T @ b[K,N]; ``accumulate`` adds into ``out``."""
+    if isinstance(out, ScatterTarget):
+        a, b = _check2d(a), _check2d(b)
+        K, M = a.shape
+        N = b.shape[1]
+        assert (M, N) == tuple(out.shape) and _lib.use_cuda_kernels(a)
+        _raw(a, K, M, a.stride(0), 1, b, K, N, b.stride(0), 1, None, N, None, 0, None, 0, M, N, K, alpha=alpha, beta=1,
+             epilogue=EPI_F32, max_ctas=max_ctas, d_table=out.table, scatter_rows=out.rows)
+        return out
     if not _lib.use_cuda_kernels(a):
         r = (a.float().t() @ b.float()) * alpha
         if out is not None:

@@ -35,7 +35,7 @@ def _L():
         sig("ats_ipc_open", ctypes.c_char_p, ctypes.POINTER(_vp))
         sig("ats_ipc_close", _vp)
         sig("ats_ipc_free", _vp)
-        sig("ats_peer_barrier", ctypes.POINTER(_vp), ctypes.POINTER(_vp), _vp, _c_int, _c_int, _vp, _vp, _vp)
+        sig("ats_peer_barrier", ctypes.POINTER(_vp), ctypes.POINTER(_vp), _vp, _c_int, _c_int, _vp, _vp, _vp, _vp)
         sig("ats_peer_reduce_shard", ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _vp, _c_int, _vp, _vp)
         sig("ats_clip_coef_slots", _vp, _c_int, _c_f, _c_f, _vp, _vp)
         sig("ats_adamw_push", _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _vp, _c_f, _vp, _vp)
@@ -152,6 +152,8 @@ class PeerBarrier:
         self.flags = self.buf.tensor(torch.int32, 64, 0)
         self.slots = self.buf.tensor(torch.float32, 64, 256)
         self.epoch_counter = self.buf.tensor(torch.int32, 1, 512)
+        # per-peer wait time (ns) and call count, accumulated by the kernel: entry t = time spent waiting for rank t, entry 16 = calls
+        self.wait_ns = torch.zeros(17, dtype=torch.int64, device=self.buf.device)
         self._flag_table = self.buf.table(0)
         self._slot_table = self.buf.table(256)
         if self.world > 1:
@@ -166,7 +168,16 @@ class PeerBarrier:
         st = _lib.status_tensor(self.buf.device)
         _lib.check(_L().ats_peer_barrier(self._flag_table, self._slot_table if payload is not None else None,
                                          _lib.ptr(payload), self.rank, self.world, _lib.ptr(self.epoch_counter), _lib.ptr(st),
-                                         _lib.stream_ptr(self.buf.device)), "peer_barrier")
+                                         _lib.ptr(self.wait_ns), _lib.stream_ptr(self.buf.device)), "peer_barrier")
+
+    def wait_statistics(self, reset: bool = True) -> dict:
+        """Time this rank's barrier kernels spent waiting since the last reset: total of the slowest peer per call is not kept,
+        the per-peer sums are -- ``max_peer_ms`` is the largest of them (the peer this rank waits for most)."""
+        v = self.wait_ns.tolist()
+        if reset:
+            self.wait_ns.zero_()
+        per_peer = [x / 1e6 for x in v[:self.world]]
+        return {"calls": int(v[16]), "max_peer_ms": max(per_peer) if per_peer else 0.0, "per_peer_ms": per_peer}
 
 
 def peers_available(group=None) -> bool:

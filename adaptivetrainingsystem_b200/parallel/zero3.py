@@ -13,10 +13,10 @@ With peer memory (one process per GPU on NVLink) no collective library call is o
   of the GEMM launch pull the remote row shards over NVLink while the tensor cores already work on the local ones), so no
   all-gather precedes the forward pass and no gathered copy outlives the product;
 * backward: the unit below the running one is re-gathered by a pull kernel on a side stream (``BACKWARD_PRE`` prefetch) into
-  one of two rotating buffers; weight-gradient GEMMs write into a rotating, peer-readable gradient buffer, and as soon as a
-  unit's backward is complete a second side stream waits for every rank (flag barrier), pulls THIS rank's rows of the
-  gradient from all peers, adds them in fp32 into the gradient shard (reduce-scatter + accumulate in one pass) and frees the
-  buffer -- all of it while the unit below is computing;
+  one of two rotating buffers; every weight-gradient GEMM does its own reduce-scatter: its epilogue adds each output row
+  straight into the fp32 gradient shard of the rank that owns the row (vector ``red.add`` over NVLink for rows owned by
+  peers), while the main loop of the next tile is running.  No gradient buffer of full size exists, no reduction kernel or
+  collective follows the backward pass, and gradients of several micro-batches accumulate in fp32 in the same place;
 * step: squared norm of the gradient shards -> scalar exchange on a flag barrier -> clip coefficient on the device -> one
   AdamW launch over the whole shard arena that writes the bf16 row shards in place -> flag barrier.  Nothing is gathered
   after the step; the next forward reads the peers' shards directly.
@@ -148,7 +148,7 @@ class ZeRO3Engine:
 
     def __init__(self, model: nn.Module, lr: float = 1e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.01,
                  max_grad_norm: float = 1.0, mesh: Optional[ProcessMesh] = None, grad_accumulation_steps: int = 1, prefetch: bool = True,
-                 fused_comm=None, copy_blocks: int = 24):
+                 fused_comm=None, copy_blocks: int = 64):
         self.model = model
         self.mesh = mesh or ProcessMesh(create_groups=False)
         self.zero_stage = 3
@@ -160,7 +160,8 @@ class ZeRO3Engine:
         # fused_comm: True / a peer-memory communicator -> kernels move everything over NVLink; None / False -> library collectives
         self.fused = bool(fused_comm) and self.device.type == "cuda" and W > 1 and self.dtype == torch.bfloat16 \
             and dist.is_initialized() and W == self.mesh.world
-        self.copy_blocks = copy_blocks  # CTAs of the side-stream pull kernels (they share the GPU with the compute stream's GEMMs)
+        import os as _os
+        self.copy_blocks = int(_os.environ.get("ATS_Z3_COPY_BLOCKS", copy_blocks))  # CTAs of the side-stream pull kernels (they share the GPU with the GEMMs)
         self._sym: List[Any] = []
 
         # -- units -----------------------------------------------------------------------------------------------
@@ -189,17 +190,20 @@ class ZeRO3Engine:
         self.master = self.shard_arena.float().clone()
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
-        self.grad32 = torch.zeros_like(self.master)
+        # with peer memory the gradient shards are written by every rank's weight-gradient GEMMs: peer-mapped, zeroed once per step
+        self.grad32 = self._alloc(self.arena_numel, torch.float32, symmetric=True)
         for m in self.matrices:
             sl = slice(m.arena_off, m.arena_off + m.shard_numel)
             m.master, m.exp_avg, m.exp_avg_sq, m.grad32 = self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], self.grad32[sl]
+            m.scatter = None
             m.param.data = torch.empty(0, dtype=self.dtype, device=self.device)
             m.param._ats_z3 = m
 
         # -- gather / gradient slots (two of each, rotating over the units) -------------------------------------------------
         slot_numel = max([u.full_numel for u in self.units] + [8])
         self.full_slots = [torch.empty(slot_numel, dtype=self.dtype, device=self.device) for _ in range(2)]
-        self.grad_slots = [self._alloc(slot_numel, self.dtype, symmetric=True) for _ in range(2)]
+        # library path only: full-size gradient buffers that are reduce-scattered per matrix
+        self.grad_slots = [] if self.fused else [torch.zeros(slot_numel, dtype=self.dtype, device=self.device) for _ in range(2)]
 
         # -- root --------------------------------------------------------------------------------------------------------
         root = [(n, p) for n, p in model.named_parameters() if p.requires_grad and id(p) not in in_block]
@@ -220,8 +224,13 @@ class ZeRO3Engine:
             from .peer import PeerBarrier
             self.ctx = GatherContext(self.group, self.device)
             self.ctx.reserve(1, max([m.numel for m in self.matrices] + [8]))
+            from ..ops.gemm import ScatterTarget
             arena_ptrs = list(self.shard_arena._ats_sym.ptrs)
+            grad_ptrs = list(self.grad32._ats_sym.ptrs)
             for m in self.matrices:
+                # where the rows of this matrix's gradient live: rank q owns rows [q * rows, (q + 1) * rows) in its own fp32 shard
+                m.scatter = ScatterTarget(torch.tensor([p + m.arena_off * 4 for p in grad_ptrs], dtype=torch.int64, device=self.device),
+                                          m.rows, (m.N, m.K))
                 m.ctx = self.ctx
                 m.peer_ptrs = [p + m.arena_off * 2 for p in arena_ptrs]
                 m.peer_table = (_vp * W)(*[_vp(p) for p in m.peer_ptrs])
@@ -229,15 +238,11 @@ class ZeRO3Engine:
                 m.gather_in_gemm = m.fused_forward_ok()
                 if m.gather_in_gemm:
                     m.flags = torch.zeros(m.N // m.ready_rows, dtype=torch.int32, device=self.device)
-            self.grad_tables = [t._ats_sym.table(0) for t in self.grad_slots]
             self.root_grad_table = self.root.full_grad._ats_sym.table(0)
             self.root_param_table = self.root.full._ats_sym.table(0)
-            self.step_barrier = PeerBarrier(self.group, self.device)     # compute stream
-            self.reduce_barrier = PeerBarrier(self.group, self.device)   # reduce stream (its own flags and epoch)
+            self.step_barrier = PeerBarrier(self.group, self.device)
             self.gather_stream = torch.cuda.Stream(device=self.device)
-            self.reduce_stream = torch.cuda.Stream(device=self.device)
             self.slot_free = [None, None]      # event: the gather slot's last user has finished with it
-            self.grad_free = [None, None]      # event: every rank has pulled its rows out of the gradient slot
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
             self.params_ready = torch.cuda.Event()  # recorded after the barrier that ends a step: every rank's shards are current
@@ -264,7 +269,6 @@ class ZeRO3Engine:
         self._sym = []
         if self.fused:
             self.step_barrier.buf.close()
-            self.reduce_barrier.buf.close()
 
     # -- gather / release of one unit ------------------------------------------------------------------------------------
     def _attach(self, u: BlockUnit, buf: torch.Tensor) -> None:
@@ -328,9 +332,15 @@ class ZeRO3Engine:
 
     # -- gradients -----------------------------------------------------------------------------------------------------------
     def _open_grads(self, u: BlockUnit) -> None:
+        if self.fused:
+            for m in u.matrices:  # the weight-gradient GEMM adds its rows into the owners' shards: nothing to buffer, always accumulating
+                m.param._ats_grad = m.scatter
+                m.param._ats_grad_fresh = False
+                ops.functional.register_grad_sink(m.param)
+                m.param.grad = None
+            u.grads_open = True
+            return
         slot = self.grad_slots[u.slot]
-        if self.fused and self.grad_free[u.slot] is not None:
-            torch.cuda.current_stream(self.device).wait_event(self.grad_free[u.slot])  # every rank has read the previous contents
         for m in u.matrices:
             m.param._ats_grad = slot[m.full_off:m.full_off + m.numel]
             m.param._ats_grad_fresh = True
@@ -339,10 +349,20 @@ class ZeRO3Engine:
         u.grads_open = True
 
     def _reduce_unit(self, u: BlockUnit) -> None:
-        """The unit's backward is complete on this rank: fold what autograd delivered, then reduce-scatter into the fp32 shards."""
+        """The unit's backward is complete on this rank.  Library path: fold what autograd delivered, reduce-scatter every
+        matrix, accumulate into the fp32 shards.  With peer memory the GEMM epilogues have already done all of it."""
         if not u.grads_open:
             return
+        u.grads_open = False
+        if self.fused:
+            for m in u.matrices:
+                if m.param.grad is not None:
+                    raise RuntimeError(f"{m.name}: a gradient arrived through plain autograd; with peer memory the weight-gradient "
+                                       "products of row-sharded matrices must go through ops.linear / ops.swiglu_mlp")
+            self.grad_fresh_units[u.index] = False
+            return
         slot = self.grad_slots[u.slot]
+        acc = not self.grad_fresh_units[u.index]
         for m in u.matrices:
             sink = slot[m.full_off:m.full_off + m.numel]
             p = m.param
@@ -354,43 +374,21 @@ class ZeRO3Engine:
                 p.grad = None
             elif getattr(p, "_ats_grad_fresh", True):
                 sink.zero_()  # the matrix took no part in this backward
-        acc = not self.grad_fresh_units[u.index]
-        if self.fused:
-            from .peer import _L
-            cur = torch.cuda.current_stream(self.device)
-            rs = self.reduce_stream
-            done = torch.cuda.Event()
-            done.record(cur)
-            rs.wait_event(done)
-            st = _lib.status_tensor(self.device)
-            with torch.cuda.stream(rs):
-                self.reduce_barrier()   # every rank has finished this unit's backward
-                for m in u.matrices:
-                    _lib.check(_L().ats_peer_reduce_rows(self.grad_tables[u.slot], self.W, self.r, m.full_off + self.r * m.shard_numel,
-                                                         m.shard_numel, _lib.ptr(m.grad32), int(acc), _lib.ptr(st), self.copy_blocks,
-                                                         _vp(rs.cuda_stream)), "peer_reduce_rows")
-                self.reduce_barrier()   # every rank has read this rank's buffer: it may be written again
-                self.grad_free[u.slot] = torch.cuda.Event()
-                self.grad_free[u.slot].record(rs)
-        else:
-            for m in u.matrices:
-                sink = slot[m.full_off:m.full_off + m.numel]
-                lo = self.r * m.shard_numel
-                if self.W > 1 and dist.is_initialized():
-                    if dist.get_backend(self.group) == "gloo":
-                        dist.all_reduce(sink, group=self.group)
-                        red = sink[lo:lo + m.shard_numel]
-                    else:
-                        red = torch.empty(m.shard_numel, dtype=self.dtype, device=self.device)
-                        dist.reduce_scatter_tensor(red, sink, group=self.group)
-                else:
+            lo = self.r * m.shard_numel
+            if self.W > 1 and dist.is_initialized():
+                if dist.get_backend(self.group) == "gloo":
+                    dist.all_reduce(sink, group=self.group)
                     red = sink[lo:lo + m.shard_numel]
-                if acc:
-                    m.grad32.add_(red.float())
                 else:
-                    m.grad32.copy_(red.float())
+                    red = torch.empty(m.shard_numel, dtype=self.dtype, device=self.device)
+                    dist.reduce_scatter_tensor(red, sink, group=self.group)
+            else:
+                red = sink[lo:lo + m.shard_numel]
+            if acc:
+                m.grad32.add_(red.float())
+            else:
+                m.grad32.copy_(red.float())
         self.grad_fresh_units[u.index] = False
-        u.grads_open = False
 
     # -- hooks ---------------------------------------------------------------------------------------------------------------
     def _install_hooks(self) -> None:
@@ -486,15 +484,17 @@ class ZeRO3Engine:
         root = self.root
         if self.fused:
             cur = torch.cuda.current_stream(self.device)
-            cur.wait_stream(self.reduce_stream)   # every unit's gradient shard is complete
             cur.wait_stream(self.gather_stream)
             root.fold_autograd_grads()
-            self.step_barrier()                   # every rank has finished its backward: root gradients are final everywhere
+            # every rank has finished its backward: all rows that peers added to this rank's gradient shards have landed and the
+            # root gradients are final everywhere
+            self.step_barrier()
         self._reduce_root()
-        for i, fresh in enumerate(self.grad_fresh_units):
-            if fresh:
-                for m in self.units[i].matrices:  # the unit took no part in this step
-                    m.grad32.zero_()
+        if not self.fused:
+            for i, fresh in enumerate(self.grad_fresh_units):
+                if fresh:
+                    for m in self.units[i].matrices:  # the unit took no part in this step
+                        m.grad32.zero_()
         ops.sumsq(self.grad32, self.sumsq, accumulate=False)
         ops.sumsq(root.grad32, self.sumsq, accumulate=True)
         scale = 1.0 / (self.mesh.dp_size * self.grad_accumulation_steps)
@@ -509,7 +509,8 @@ class ZeRO3Engine:
             ops.clip_coef(self.sumsq, self.clip_state, scale, self.max_grad_norm)
         self._adamw()
         if self.fused:
-            self.step_barrier()                   # every shard is updated before anyone's next forward reads it
+            self.grad32.zero_()                   # the next step's weight-gradient GEMMs add into zeros
+            self.step_barrier()                   # every shard is updated (and every gradient shard cleared) before anyone goes on
             self.params_ready = torch.cuda.Event()
             self.params_ready.record(torch.cuda.current_stream(self.device))
         self.zero_grad()
@@ -581,7 +582,7 @@ class ZeRO3Engine:
     def memory_bytes(self) -> Dict[str, int]:
         es = self.shard_arena.element_size()
         return {"params": (self.arena_numel + self.root.padded) * es,
-                "grads": (self.arena_numel + self.root.shard) * 4 + sum(t.numel() for t in self.grad_slots) * es,
+                "grads": (self.arena_numel + self.root.shard) * 4 + sum(t.numel() for t in self.grad_slots) * es + self.root.padded * es,
                 "optimizer": 3 * (self.arena_numel + self.root.shard) * 4}
 
     # -- state: every stretch of a parameter whose optimiser state this rank holds -----------------------------------------------

@@ -238,6 +238,11 @@ def run_ours(args) -> dict:
             first_loss = float(loss)
     ops.check_status()
     barrier()
+    ep_comm0 = getattr(model, "_ep_comm", None)
+    bars = {"expert_exchange": getattr(ep_comm0, "barrier", None), "optimizer_step": getattr(fused, "barrier", None)}
+    for b_ in bars.values():
+        if b_ is not None:
+            b_.wait_statistics(reset=True)
     launches0 = _lib.launch_count()
     with ClockSampler(torch.cuda.current_device()) as clk:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -248,6 +253,16 @@ def run_ours(args) -> dict:
         e1.record()
         barrier()
     launches = _lib.launch_count() - launches0
+    # time the flag barriers of the timed region spent waiting (per rank: the rank that waits least is the one the others wait for)
+    barrier_wait = {}
+    for name, b_ in bars.items():
+        if b_ is None or world == 1:
+            continue
+        stt = b_.wait_statistics(reset=True)
+        t_ = torch.tensor([stt["max_peer_ms"] / args.steps, float(stt["calls"]) / args.steps], device=dev)
+        allr = [torch.zeros_like(t_) for _ in range(world)]
+        dist.all_gather(allr, t_)
+        barrier_wait[name] = {"calls_per_step": allr[0][1].item(), "wait_ms_per_step_by_rank": [round(a[0].item(), 2) for a in allr]}
     ms = e0.elapsed_time(e1) / args.steps
     t = torch.tensor([ms], device=dev)
     if world > 1:
@@ -300,6 +315,8 @@ def run_ours(args) -> dict:
     }
     if check is not None:
         res["fused_check"] = check
+    if barrier_wait:
+        res["barrier_wait"] = barrier_wait
     # tear the training job down (buckets and exchange buffers live outside PyTorch's allocator) before the serving models are built
     trainer.shutdown()
     ep_comm = getattr(model, "_ep_comm", None)

@@ -40,8 +40,10 @@ static unsigned long long g_wait_budget_ns = ATS_WAIT_BUDGET_NS;
 // every peer instead of re-using the epoch that was frozen into the captured arguments.  All ranks issue their barriers
 // in the same order, so their counters agree.  Thread t: optionally stores the payload into peer t's payload slot
 // [rank], releases the epoch into peer t's flags[rank], then waits (bounded) for flags[t] of its own array.
+// `wait_ns` (optional, [MAX_PEERS + 1] int64 in this rank's memory): thread t adds the time it spent waiting for peer t, entry
+// [MAX_PEERS] counts the calls -- how much of a step is spent waiting at barriers, and for whom, without a profiler.
 __global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const float* payload_src, int rank, int world,
-                                    int* epoch_counter, unsigned long long budget_ns, int* status) {
+                                    int* epoch_counter, unsigned long long budget_ns, int* status, long long* wait_ns) {
   const int t = threadIdx.x;
   int epoch = 0;
   if (t == 0) {
@@ -66,6 +68,10 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const 
     __nanosleep(64);
   }
   __threadfence_system();
+  if (wait_ns) {
+    wait_ns[t] += (long long)(globaltimer_ns() - t0);
+    if (t == 0) wait_ns[MAX_PEERS] += 1;
+  }
 }
 
 // out32[i] = sum_p grads_p[offset + i]  (i < n, n % 8 == 0); partial[block] = sum of squares of this block's part.
@@ -174,38 +180,86 @@ __global__ void __launch_bounds__(256) peer_copy_kernel(const uint4* __restrict_
 
 // All-gather by pulling: dst[q * shard + i] = shards_q[i] for every rank q (this rank's own shard included), 16-byte vectors.
 // Launched on a side stream with a bounded number of CTAs so that it overlaps the compute stream's GEMMs (ZeRO-3 prefetch).
+// A read over NVLink takes a few microseconds, so every thread keeps eight 16-byte loads in flight: with one load per thread
+// 24 CTAs moved 70 GB/s and the kernel stayed resident (and in the GEMMs' way) five times longer than the copy needs.
 __global__ void __launch_bounds__(256) peer_gather_kernel(PeerPtrs shards, int world, uint4* __restrict__ dst, long long shard_vec,
                                                           const int* __restrict__ status) {
   if (status && *status != 0) return;
+  constexpr int UNR = 8;
   const long long total = shard_vec * world;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int q = int(i / shard_vec);
-    dst[i] = static_cast<const uint4*>(shards.p[q])[i - q * shard_vec];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total; i0 += stride * UNR) {
+    uint4 v[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int q = int(i / shard_vec);
+        v[u] = static_cast<const uint4*>(shards.p[q])[i - q * shard_vec];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) dst[i] = v[u];
+    }
   }
 }
 
 // Reduce-scatter by pulling, for one row-sharded matrix: out32[i] (+)= sum_q grads_q[offset + i], i < n (n, offset % 8 == 0).
-// fp32 accumulation in registers; `accumulate` adds to what out32 holds (later micro-batches of one optimiser step).
+// fp32 accumulation in registers; `accumulate` adds to what out32 holds (later micro-batches of one optimiser step).  Two
+// vectors per thread, the loads of up to four peers for all of them issued before the first add (memory-level parallelism over
+// NVLink) -- and no more than that, so that the kernel's registers leave room for a GEMM CTA on the same SM.
 __global__ void __launch_bounds__(256)
 peer_reduce_rows_kernel(PeerPtrs grads, int world, int rank, long long offset, long long n, float* __restrict__ out32, int accumulate,
                         const int* __restrict__ status) {
   if (status && *status != 0) return;
+  constexpr int UNR = 2, PG = 4;
   const long long nvec = n >> 3;
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (accumulate) {
-      const float4 a = reinterpret_cast<const float4*>(out32)[2 * v], b = reinterpret_cast<const float4*>(out32)[2 * v + 1];
-      acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * UNR) {
+    float acc[UNR][8];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long v = v0 + u * stride;
+      if (accumulate && v < nvec) {
+        const float4 x = reinterpret_cast<const float4*>(out32)[2 * v], y = reinterpret_cast<const float4*>(out32)[2 * v + 1];
+        acc[u][0] = x.x; acc[u][1] = x.y; acc[u][2] = x.z; acc[u][3] = x.w; acc[u][4] = y.x; acc[u][5] = y.y; acc[u][6] = y.z; acc[u][7] = y.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      }
     }
-#pragma unroll 4
-    for (int q = 0; q < world; ++q) {
-      const int p = (rank + q) % world;
-      const uint4 a = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[p]) + offset)[v];
-      float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
-      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    for (int q0 = 0; q0 < world; q0 += PG) {
+      uint4 a[UNR][PG];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long v = v0 + u * stride;
+#pragma unroll
+        for (int j = 0; j < PG; ++j) {
+          a[u][j] = make_uint4(0, 0, 0, 0);
+          if (q0 + j < world && v < nvec) {
+            const int p = (rank + q0 + j) % world;  // start with the local copy, spread the remote reads over the peers
+            a[u][j] = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[p]) + offset)[v];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int j = 0; j < PG; ++j) {
+          float2 f0 = unpack_bf16x2(a[u][j].x), f1 = unpack_bf16x2(a[u][j].y), f2 = unpack_bf16x2(a[u][j].z), f3 = unpack_bf16x2(a[u][j].w);
+          acc[u][0] += f0.x; acc[u][1] += f0.y; acc[u][2] += f1.x; acc[u][3] += f1.y;
+          acc[u][4] += f2.x; acc[u][5] += f2.y; acc[u][6] += f3.x; acc[u][7] += f3.y;
+        }
     }
-    reinterpret_cast<float4*>(out32)[2 * v] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    reinterpret_cast<float4*>(out32)[2 * v + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long v = v0 + u * stride;
+      if (v >= nvec) continue;
+      reinterpret_cast<float4*>(out32)[2 * v] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+      reinterpret_cast<float4*>(out32)[2 * v + 1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+    }
   }
 }
 
@@ -244,13 +298,13 @@ ATS_API int ats_ipc_free(void* ptr) { return int(cudaFree(ptr)); }
 // flags / payload_dst: host arrays of `world` device pointers (one per rank, peer-mapped).
 // epoch_counter: one int in this rank's device memory, zero before the first barrier of this flag set.
 ATS_API int ats_peer_barrier(void* const* flags, void* const* payload_dst, const float* payload_src, int rank, int world,
-                             int* epoch_counter, int* status, void* stream) {
+                             int* epoch_counter, int* status, long long* wait_ns, void* stream) {
   if (world > MAX_PEERS || !epoch_counter) return 1003;
   PeerPtrs none = {};
   peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(flags, world),
                                                                       payload_dst ? to_peers(payload_dst, world) : none,
                                                                       payload_src, rank, world, epoch_counter, g_wait_budget_ns,
-                                                                      status);
+                                                                      status, wait_ns);
   return int(cudaGetLastError());
 }
 

@@ -60,6 +60,11 @@ struct GemmArgs {
   int k_segs;            // ragged == 2: the reduction of group g runs over k_segs blocks of rows, seg_stride apart,
   int seg_stride;        //              block s holding counts[g * k_segs + s] rows
   void* const* d_table;  // optional per-group output base pointers (e.g. buffers on peer GPUs)
+  // kF32 with scatter_rows > 0: reduce-scatter inside the epilogue.  Row r of the product belongs to rank r / scatter_rows, whose fp32
+  // buffer d_table[r / scatter_rows] receives the row at (r % scatter_rows) * ldd with vector atomic adds (`red.add.v4.f32`, which
+  // travel over NVLink for rows owned by peers): every rank of a data-parallel group adds its partial weight gradient straight
+  // into the owner's gradient shard while the main loop of the next tile runs.
+  int scatter_rows;
   // fp8 (e4m3) operands: one byte per element, 128 elements per swizzle row and per K block, kind::f8f6f4 MMAs (K = 32).
   // The fp32 accumulator is multiplied by row_scale[row] * col_scale[col] in the epilogue (per-token activation scales,
   // per-output-channel weight scales), so the main loop needs no per-block promotion.
@@ -377,7 +382,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
       }
       if (!row_ok) continue;
       const int colbase = t.n0 + c * 32;
-      if (p.epilogue == kF32) {
+      if (p.epilogue == kF32 && p.scatter_rows > 0) {
+        const int owner = row / p.scatter_rows;
+        float* drow = static_cast<float*>(p.d_table[owner]) + (long long)(row - owner * p.scatter_rows) * p.ldd;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int col = colbase + v * 4;
+          if (col < p.N)
+            asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(drow + col), "f"(__uint_as_float(r[v * 4]) * p.alpha),
+                         "f"(__uint_as_float(r[v * 4 + 1]) * p.alpha), "f"(__uint_as_float(r[v * 4 + 2]) * p.alpha),
+                         "f"(__uint_as_float(r[v * 4 + 3]) * p.alpha)
+                         : "memory");
+        }
+      } else if (p.epilogue == kF32) {
         float* drow = p.Df32 + p.d_gs * t.g + (long long)row * p.ldd;
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
@@ -987,7 +1004,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
                           int groups, int ragged, const int* counts,
                           int a_gs_mn, int a_gs_k, int b_gs_mn, int b_gs_k,
                           long long d_gs, long long c_gs, long long aux_gs,
-                          int b_div, int k_segs, int seg_stride, void* const* d_table, int k_split,
+                          int b_div, int k_segs, int seg_stride, void* const* d_table, int k_split, int scatter_rows,
                           int* status, int max_ctas, void* stream) {
   // The tensor-map encoder is a driver call: make sure this thread (autograd runs backward on its own threads)
   // has the primary context bound before the first use.
@@ -1008,6 +1025,8 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   if (b_div < 1 || k_segs < 1 || (seg_stride & 7) || (k_segs > 1 && ragged != 2)) return 1006;
   // reduction slices: whole K blocks per slice, fp32 partial outputs, every `k_split` consecutive groups are one problem
   if (k_split < 1 || (k_split > 1 && (epilogue != kF32 || ragged == 2 || (K & 63) || groups % k_split || d_table))) return 1008;
+  // reduce-scatter epilogue: one problem, fp32 atomic adds into per-owner buffers, whole 16-byte vectors
+  if (scatter_rows < 0 || (scatter_rows > 0 && (epilogue != kF32 || groups != 1 || !d_table || (N & 3) || (ldd & 3) || M % scatter_rows))) return 1009;
   CUtensorMap ma, mb;
   int e;
   if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 2, 64, a_mn ? 64 : 128))) return e;
@@ -1025,7 +1044,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = static_cast<float*>(D);
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = a_mn; p.b_mn = b_mn; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = beta; p.status = status;
-  p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table; p.k_split = k_split;
+  p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table; p.k_split = k_split; p.scatter_rows = scatter_rows;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = g_gemm_prof;
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
@@ -1103,7 +1122,7 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
-  p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1;
+  p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1; p.scatter_rows = 0;
   p.b_packed = 0; p.b_kblocks = 0;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
@@ -1141,7 +1160,7 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = 1.f; p.beta = 0; p.status = status;
-  p.b_div = 1; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1;
+  p.b_div = 1; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1; p.scatter_rows = 0;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   const long long shard_rows = b_rows / b_shards;
   p.b_packed = 0; p.b_kblocks = 0;

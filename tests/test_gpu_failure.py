@@ -31,7 +31,7 @@ def test_peer_flag_wait_gives_up_and_context_survives():
     try:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        _lib.check(lib.ats_peer_barrier(table, None, None, 0, 2, _lib.ptr(counter), _lib.ptr(st), _lib.stream_ptr(dev)), "peer_barrier")
+        _lib.check(lib.ats_peer_barrier(table, None, None, 0, 2, _lib.ptr(counter), _lib.ptr(st), None, _lib.stream_ptr(dev)), "peer_barrier")
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
