@@ -300,6 +300,7 @@ class Config:
     tensor_parallel_size: int = 1
     sequence_parallel_size: int = 1
     num_microbatches: int = 1
+    pipeline_chunks: int = 1  # > 1: interleaved 1F1B with this many model chunks per pipeline rank
     fused_comm: bool = True  # peer-memory kernels; False = NCCL-only baseline path
     use_nvls: bool = False
     # -- production ----------------------------------------------------------

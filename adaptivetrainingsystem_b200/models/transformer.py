@@ -131,11 +131,42 @@ class GroupedQueryAttention(nn.Module):
         width = (self.n_q + 2 * self.n_kv) * self.d
         self.qkv_proj = nn.Parameter(torch.empty(width, cfg.hidden_size))
         self.o_proj = nn.Parameter(torch.empty(cfg.hidden_size, self.n_q * self.d))
+        # set by parallel.strategy: tensor parallelism (this rank's heads only, outputs all-reduced) and head-scatter sequence
+        # parallelism (this rank's tokens only, heads exchanged for tokens around the attention)
+        self.tp_group = None
+        self.sp_group = None
+        self.sp_size, self.sp_rank = 1, 0
+
+    def _project_out(self, a: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        if self.tp_group is None:
+            return ops.linear(a, self.o_proj, residual=residual)
+        from ..parallel.tensor_parallel import _ReduceFromRegion
+        return _ReduceFromRegion.apply(ops.linear(a, self.o_proj), self.tp_group) + residual
+
+    def _forward_sequence_parallel(self, h, residual, rope):
+        """Every rank holds L / W tokens: rotary positions are global, heads are traded for tokens around the attention."""
+        from ..parallel.sequence_parallel import scatter_heads_gather_sequence, scatter_sequence_gather_heads
+        B, L, _ = h.shape
+        W, r = self.sp_size, self.sp_rank
+        rope.ensure(W * L, h.device)
+        qkv = ops.linear(h, self.qkv_proj)
+        qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=r * L)
+        nq, nk = self.n_q * self.d, self.n_kv * self.d
+        q = scatter_heads_gather_sequence(qkv[..., :nq].reshape(B, L, self.n_q, self.d), self.sp_group)
+        k = scatter_heads_gather_sequence(qkv[..., nq:nq + nk].reshape(B, L, self.n_kv, self.d), self.sp_group)
+        v = scatter_heads_gather_sequence(qkv[..., nq + nk:].reshape(B, L, self.n_kv, self.d), self.sp_group)
+        a = scatter_sequence_gather_heads(ops.attention(q, k, v, causal=True), self.sp_group)
+        return self._project_out(a.reshape(B, L, nq), residual)
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, rope: RotaryEmbedding,
                 attention_mask: Optional[torch.Tensor] = None, cache: Optional[KVCache] = None,
                 positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, L, _ = h.shape
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import _CopyToRegion
+            h = _CopyToRegion.apply(h, self.tp_group)
+        if self.sp_group is not None and cache is None and attention_mask is None and positions is None:
+            return self._forward_sequence_parallel(h, residual, rope)
         offset = cache.length if cache is not None else 0
         graph_decode = cache is not None and cache.device_lengths is not None and L == 1
         if graph_decode:
@@ -144,7 +175,7 @@ class GroupedQueryAttention(nn.Module):
             qkv = ops.linear(h, self.qkv_proj)
             qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, positions=cache.device_positions.view(B, 1))
             a = ops.decode_attention(qkv, cache.k[self.layer_idx], cache.v[self.layer_idx], cache.device_lengths, self.n_q, self.n_kv, self.d)
-            return ops.linear(a, self.o_proj, residual=residual)
+            return self._project_out(a, residual)
         rope.ensure(offset + L if positions is None else int(self.cfg.seq_length), h.device)
         qkv = ops.linear(h, self.qkv_proj)
         nq, nk = self.n_q * self.d, self.n_kv * self.d
@@ -152,23 +183,23 @@ class GroupedQueryAttention(nn.Module):
                 and ops.attention_packed_available(qkv, self.d, L)):
             # training / scoring path: rotation and attention are one autograd node on the projection buffer
             a = ops.rope_attention_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=0)
-            return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
+            return self._project_out(a.reshape(B, L, nq), residual)
         qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=offset, positions=positions)
         if cache is None and attention_mask is None and ops.attention_packed_available(qkv, self.d, L):
             a = ops.attention_packed(qkv, self.n_q, self.n_kv, self.d)
-            return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
+            return self._project_out(a.reshape(B, L, nq), residual)
         if (cache is not None and L == 1 and attention_mask is None and positions is None
                 and ops.decode_attention_available(qkv, self.n_q, self.n_kv, self.d)):
             # single-token step: the kernel appends K / V to the cache and attends in one pass over the cache
             a = ops.decode_attention(qkv, cache.k[self.layer_idx], cache.v[self.layer_idx], cache.length, self.n_q, self.n_kv, self.d)
-            return ops.linear(a, self.o_proj, residual=residual)
+            return self._project_out(a, residual)
         q = qkv[..., :nq].view(B, L, self.n_q, self.d)
         k = qkv[..., nq:nq + nk].view(B, L, self.n_kv, self.d)
         v = qkv[..., nq + nk:].view(B, L, self.n_kv, self.d)
         if cache is not None:
             k, v = cache.append(self.layer_idx, k, v)
         a = ops.attention(q, k, v, causal=True, q_offset=offset, key_mask=attention_mask)
-        return ops.linear(a.reshape(B, L, nq), self.o_proj, residual=residual)
+        return self._project_out(a.reshape(B, L, nq), residual)
 
 
 class DenseSwiGLU(nn.Module):
@@ -176,8 +207,13 @@ class DenseSwiGLU(nn.Module):
         super().__init__()
         self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size))
         self.down_proj = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size))
+        self.tp_group = None  # set by parallel.strategy.apply_tensor_parallel: this rank's columns, outputs all-reduced
 
     def forward(self, h: torch.Tensor, residual: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import _CopyToRegion, _ReduceFromRegion
+            y = _ReduceFromRegion.apply(ops.swiglu_mlp(_CopyToRegion.apply(h, self.tp_group), self.gate_up_proj, self.down_proj), self.tp_group)
+            return (y + residual if residual is not None else y), None
         return ops.swiglu_mlp(h, self.gate_up_proj, self.down_proj, residual), None
 
 
@@ -538,8 +574,8 @@ class DeepSeekTransformer(nn.Module):
 
     def make_cache(self, batch: int, max_len: int, dtype=None, device=None) -> KVCache:
         p = self.embed_tokens.weight
-        return KVCache(self.config.num_layers, batch, max_len, self.config.num_kv_heads, self.config.head_dim,
-                       dtype or p.dtype, device or p.device)
+        n_kv = self.layers[0].self_attn.n_kv if len(self.layers) else self.config.num_kv_heads  # this rank's KV heads (tensor parallelism)
+        return KVCache(self.config.num_layers, batch, max_len, n_kv, self.config.head_dim, dtype or p.dtype, device or p.device)
 
 
 # ----------------------------------------------------------------------------------------------------------
@@ -547,9 +583,9 @@ class DeepSeekTransformer(nn.Module):
 # ----------------------------------------------------------------------------------------------------------
 def _export_reference_names(module: DeepSeekTransformer, state: Dict[str, torch.Tensor], prefix: str, _meta) -> None:
     cfg = module.config
-    nq, nk = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
     for i, blk in enumerate(module.layers):
         base = f"{prefix}layers.{i}."
+        nq, nk = blk.self_attn.n_q * cfg.head_dim, blk.self_attn.n_kv * cfg.head_dim  # this rank's heads under tensor parallelism
         qkv = state.pop(base + "self_attn.qkv_proj")
         state[base + "self_attn.q_proj.weight"] = qkv[:nq]
         state[base + "self_attn.k_proj.weight"] = qkv[nq:nq + nk]
@@ -575,13 +611,21 @@ def _import_reference_names(module: DeepSeekTransformer, state: Dict[str, torch.
     cfg = module.config
     for i, blk in enumerate(module.layers):
         base = f"{prefix}layers.{i}."
+        att = blk.self_attn
+        tpw, tpr = getattr(att, "tp_size", 1), getattr(att, "tp_rank", 0)
+
+        def rows(t, full_rows):  # a full tensor loaded into a tensor-parallel model: keep this rank's rows / columns
+            return t[tpr * (full_rows // tpw):(tpr + 1) * (full_rows // tpw)] if (tpw > 1 and t.shape[0] == full_rows) else t
+
+        def cols(t, full_cols):
+            return t[:, tpr * (full_cols // tpw):(tpr + 1) * (full_cols // tpw)] if (tpw > 1 and t.shape[1] == full_cols) else t
         if base + "self_attn.q_proj.weight" in state:
-            q = state.pop(base + "self_attn.q_proj.weight")
-            k = state.pop(base + "self_attn.k_proj.weight")
-            v = state.pop(base + "self_attn.v_proj.weight")
+            q = rows(state.pop(base + "self_attn.q_proj.weight"), cfg.num_heads * cfg.head_dim)
+            k = rows(state.pop(base + "self_attn.k_proj.weight"), cfg.num_kv_heads * cfg.head_dim)
+            v = rows(state.pop(base + "self_attn.v_proj.weight"), cfg.num_kv_heads * cfg.head_dim)
             state[base + "self_attn.qkv_proj"] = torch.cat([q, k, v], dim=0)
         if base + "self_attn.o_proj.weight" in state:
-            state[base + "self_attn.o_proj"] = state.pop(base + "self_attn.o_proj.weight")
+            state[base + "self_attn.o_proj"] = cols(state.pop(base + "self_attn.o_proj.weight"), cfg.num_heads * cfg.head_dim)
         if blk.ffn_kind == "moe":
             e_local = blk.ffn.experts_w1.shape[0]
             first = blk.ffn.ep_rank * e_local
@@ -594,8 +638,14 @@ def _import_reference_names(module: DeepSeekTransformer, state: Dict[str, torch.
                 state.pop(key)
         else:
             if base + "ffn.gate_up_proj.weight" in state:
-                state[base + "ffn.gate_up_proj"] = state.pop(base + "ffn.gate_up_proj.weight")
-                state[base + "ffn.down_proj"] = state.pop(base + "ffn.down_proj.weight")
+                gu, dn = state.pop(base + "ffn.gate_up_proj.weight"), state.pop(base + "ffn.down_proj.weight")
+                ftp, ftr = getattr(blk.ffn, "tp_size", 1), getattr(blk.ffn, "tp_rank", 0)
+                if ftp > 1 and gu.shape[0] == 2 * cfg.intermediate_size:
+                    half, n = cfg.intermediate_size, cfg.intermediate_size // ftp
+                    gu = torch.cat([gu[ftr * n:(ftr + 1) * n], gu[half + ftr * n:half + (ftr + 1) * n]], dim=0)
+                    dn = dn[:, ftr * n:(ftr + 1) * n]
+                state[base + "ffn.gate_up_proj"] = gu
+                state[base + "ffn.down_proj"] = dn
     if prefix + "lm_head.weight" in state:
         w = state.pop(prefix + "lm_head.weight")
         if module.lm_head_weight is not None:

@@ -6,7 +6,8 @@ with pickled metadata per message is done here with a fixed wire format: every m
 ``[micro_batch, seq, hidden]`` tensor in the compute dtype, so nothing is pickled on the hot path.  Schedule:
 ``warmup = stages - stage - 1`` forwards, then steady 1F1B, then ``warmup`` cooldown backwards; the last stage scales
 the loss by ``1 / num_microbatches``; in the steady state a stage posts "send activation" and "receive gradient" as one
-grouped exchange so neighbours never wait on each other.
+grouped exchange so neighbours never wait on each other.  ``InterleavedSchedule`` runs several model chunks per rank in the
+interleaved 1F1B order.  A stage frees the weights of every other stage (``free_foreign_parameters``).
 Pipeline send/recv stays on the collective library by design (compute and transfer overlap through the schedule).
 """
 from __future__ import annotations
@@ -16,6 +17,31 @@ from typing import Callable, Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 import torch.nn as nn
+
+
+def free_foreign_parameters(model, keep_layers, keep_embedding: bool, keep_head: bool) -> int:
+    """A pipeline stage holds only what it runs: the weights of every other stage are released (their tensors become empty and
+    stop requiring gradients), so the memory of a stage is its share of the model.  Returns the number of elements released."""
+    freed = 0
+    dev = next(model.parameters()).device
+
+    def drop(p):
+        nonlocal freed
+        freed += p.numel()
+        p.requires_grad_(False)
+        p.data = torch.empty(0, dtype=p.dtype, device=dev)
+    for i, blk in enumerate(model.layers):
+        if i not in keep_layers:
+            for p in blk.parameters():
+                drop(p)
+    tied = model.lm_head_weight is None
+    if not keep_embedding and not (tied and keep_head):
+        drop(model.embed_tokens.weight)
+    if not keep_head:
+        drop(model.norm.weight)
+        if model.lm_head_weight is not None:
+            drop(model.lm_head_weight)
+    return freed
 
 
 def partition_layers(num_layers: int, num_stages: int) -> List[Tuple[int, int]]:
@@ -38,17 +64,8 @@ class PipelineStage(nn.Module):
         self.start, self.end = partition_layers(len(model.layers), num_stages)[stage]
         self.model = model
         self.is_first, self.is_last = stage == 0, stage == num_stages - 1
-        keep = set(range(self.start, self.end))
-        for i, blk in enumerate(model.layers):  # parameters of foreign stages do not train here
-            if i not in keep:
-                for p in blk.parameters():
-                    p.requires_grad_(False)
-        if not self.is_first:
-            model.embed_tokens.weight.requires_grad_(False)
-        if not self.is_last:
-            model.norm.weight.requires_grad_(False)
-            if model.lm_head_weight is not None:
-                model.lm_head_weight.requires_grad_(False)
+        # parameters of foreign stages neither train nor live here
+        self.freed = free_foreign_parameters(model, set(range(self.start, self.end)), self.is_first, self.is_last)
 
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """x: token ids on the first stage, hidden states otherwise -> (hidden or final hidden, aux loss)."""
@@ -175,16 +192,7 @@ class InterleavedStages(nn.Module):
         self.virtual = [c * num_stages + rank for c in range(chunks)]
         self.total = total
         keep = {i for (a, b) in self.ranges for i in range(a, b)}
-        for i, blk in enumerate(model.layers):
-            if i not in keep:
-                for p in blk.parameters():
-                    p.requires_grad_(False)
-        if 0 not in self.virtual:
-            model.embed_tokens.weight.requires_grad_(False)
-        if total - 1 not in self.virtual:
-            model.norm.weight.requires_grad_(False)
-            if model.lm_head_weight is not None:
-                model.lm_head_weight.requires_grad_(False)
+        self.freed = free_foreign_parameters(model, keep, 0 in self.virtual, total - 1 in self.virtual)
 
     def forward_chunk(self, c: int, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         m = self.model
@@ -207,11 +215,41 @@ class InterleavedStages(nn.Module):
         return ops.linear_cross_entropy(hidden, self.model.lm_head, labels, weights)[0]
 
 
+def interleaved_order(stage: int, num_stages: int, chunks: int, num_microbatches: int) -> List[Tuple[str, int, int]]:
+    """The interleaved 1F1B order of one rank: a list of ``("F" | "B", chunk, micro-batch)``.
+
+    Work comes in groups of ``stages`` micro-batches per chunk (so ``num_microbatches`` must be a multiple of ``stages``):
+    forward operation ``k`` runs chunk ``(k // stages) % chunks`` on micro-batch ``(k // (stages * chunks)) * stages + k % stages``;
+    backward operations walk the chunks in reverse.  A rank starts with
+    ``2 * (stages - stage - 1) + (chunks - 1) * stages`` forwards, then alternates one forward with one backward, then
+    drains the remaining backwards (reference: ``colossalai/pipeline/schedule/interleaved_pp.py:406-470``)."""
+    S, C, n = num_stages, chunks, num_microbatches
+    if n % S:
+        raise ValueError("interleaved 1F1B needs num_microbatches to be a multiple of the pipeline stages")
+    total = n * C
+
+    def fwd(k):
+        return ("F", (k // S) % C, (k // (S * C)) * S + k % S)
+
+    def bwd(k):
+        return ("B", C - 1 - (k // S) % C, (k // (S * C)) * S + k % S)
+    warm = min(2 * (S - stage - 1) + (C - 1) * S, total)
+    order = [fwd(k) for k in range(warm)]
+    for i in range(total - warm):
+        order.append(fwd(warm + i))
+        order.append(bwd(i))
+    order += [bwd(k) for k in range(total - warm, total)]
+    return order
+
+
 class InterleavedSchedule:
-    """Runs the virtual pipeline of :class:`InterleavedStages` breadth-first: all micro-batches through chunk 0 of every rank,
-    then chunk 1 (whose first stage receives from the last rank), ...; backward in the reverse order.  Sends are posted
-    asynchronously and completed at the end of each phase, so a rank never blocks on a neighbour that has not reached the
-    matching receive yet.  Activations of all micro-batches are kept until their backward (GPipe memory profile)."""
+    """Interleaved 1F1B over the virtual pipeline of :class:`InterleavedStages`.
+
+    Every directed link between neighbouring ranks (forward activations ``r -> r + 1``, gradients ``r + 1 -> r``, both around
+    the ring) gets a communicator of its own, so traffic on one link never queues behind traffic on another.  On every link the
+    sender's production order equals the receiver's consumption order (both follow :func:`interleaved_order`), sends are
+    posted asynchronously and a receive is posted right before the operation that needs it; with ``stages`` ranks at most
+    ``warm-up`` activations per chunk are alive on a rank, not all ``num_microbatches``."""
 
     def __init__(self, stages: InterleavedStages, group, num_microbatches: int, act_shape: Tuple[int, int, int], dtype, device):
         self.m, self.group, self.n = stages, group, num_microbatches
@@ -219,44 +257,56 @@ class InterleavedSchedule:
         self.world = dist.get_world_size(group)
         self.ranks = dist.get_process_group_ranks(group)
         self.shape, self.dtype, self.device = act_shape, dtype, device
+        self.order = interleaved_order(self.rank, self.world, stages.chunks, num_microbatches)
+        # one communicator per directed link and kind of traffic (created in the same order on every rank of the pipeline group)
+        self.link: Dict[Tuple[int, int, str], object] = {}
+        S = self.world
+        for src in range(S):
+            for dst, kind in (((src + 1) % S, "act"), ((src - 1) % S, "grad")):
+                if src != dst:
+                    self.link[(src, dst, kind)] = dist.new_group([self.ranks[src], self.ranks[dst]])
+
+    def _isend(self, t: torch.Tensor, dst: int, kind: str):
+        return dist.isend(t, self.ranks[dst], group=self.link[(self.rank, dst, kind)])
+
+    def _recv(self, src: int, kind: str) -> torch.Tensor:
+        buf = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+        dist.recv(buf, self.ranks[src], group=self.link[(src, self.rank, kind)])
+        return buf
 
     def run(self, microbatches: List[Dict[str, torch.Tensor]]) -> Optional[torch.Tensor]:
         m, n, S, r = self.m, self.n, self.world, self.rank
-        nxt, prv = self.ranks[(r + 1) % S], self.ranks[(r - 1) % S]
+        nxt, prv = (r + 1) % S, (r - 1) % S
         saved: Dict[Tuple[int, int], Tuple[Optional[torch.Tensor], torch.Tensor, torch.Tensor]] = {}
         losses: List[torch.Tensor] = []
-        pending = []
-        for c in range(m.chunks):
+        pending, keep_alive = [], []
+        self.max_alive = 0
+        for kind, c, i in self.order:
             k = m.virtual[c]
-            for i, mb in enumerate(microbatches):
+            mb = microbatches[i]
+            if kind == "F":
                 if k == 0:
                     x_in = None
                     out, aux = m.forward_chunk(c, mb["input_ids"])
                 else:
-                    x_in = torch.empty(self.shape, dtype=self.dtype, device=self.device)
-                    dist.recv(x_in, prv, group=self.group)
-                    x_in.requires_grad_()
+                    x_in = self._recv(prv, "act").requires_grad_()
                     out, aux = m.forward_chunk(c, x_in)
                 if k == m.total - 1:
                     loss = (m.loss(out, mb["labels"], mb.get("loss_weights")) + aux) / n
                     losses.append(loss.detach())
                     out = loss
                 else:
-                    pending.append(dist.isend(out.detach().contiguous(), nxt, group=self.group))
+                    act = out.detach().contiguous()
+                    keep_alive.append(act)
+                    pending.append(self._isend(act, nxt, "act"))
                 saved[(c, i)] = (x_in, out, aux)
-        for h in pending:
-            h.wait()
-        pending = []
-        keep_alive = []
-        for c in reversed(range(m.chunks)):
-            k = m.virtual[c]
-            for i in range(n):
+                self.max_alive = max(self.max_alive, len(saved))
+            else:
                 x_in, out, aux = saved.pop((c, i))
                 if k == m.total - 1:
                     out.backward()
                 else:
-                    g = torch.empty(self.shape, dtype=self.dtype, device=self.device)
-                    dist.recv(g, nxt, group=self.group)
+                    g = self._recv(nxt, "grad")
                     if aux.requires_grad:
                         torch.autograd.backward([out, aux / n], [g, torch.ones_like(aux)])
                     else:
@@ -264,7 +314,7 @@ class InterleavedSchedule:
                 if k != 0:
                     gin = x_in.grad.contiguous()
                     keep_alive.append(gin)
-                    pending.append(dist.isend(gin, prv, group=self.group))
+                    pending.append(self._isend(gin, prv, "grad"))
         for h in pending:
             h.wait()
         if m.total - 1 in m.virtual:

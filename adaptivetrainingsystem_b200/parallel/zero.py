@@ -158,11 +158,21 @@ class ShardedEngine:
         shard = self.zero_stage >= 1
         alloc = self.fused.allocator() if self.fused is not None else None
         spec = [("dense_decay", dense_d, "dp", True), ("dense_no_decay", dense_n, "dp", False), ("expert", expert, "edp", True)]
+        tp = getattr(m, "tp_size", 1)
+        if tp > 1:
+            # parameters that tensor parallelism splits differ from rank to rank of a tp group; all others are replicated there and
+            # must count ONCE in the global gradient norm (reference: colossalai/booster/plugin/hybrid_parallel_plugin.py:342-418)
+            split = []
+            for name, plist, axis, decay in spec:
+                split.append((name + "_tp", [(n, p) for n, p in plist if getattr(p, "_ats_tp", None) is not None], axis, decay))
+                split.append((name, [(n, p) for n, p in plist if getattr(p, "_ats_tp", None) is None], axis, decay))
+            spec = split
         for name, plist, axis, decay in spec:
             if not plist:
                 continue
-            self.buckets.append(Bucket(name, plist, m.group(axis), m.size(axis), m.index(axis), decay, shard, self.dtype,
-                                       self.device, alloc))
+            b = Bucket(name, plist, m.group(axis), m.size(axis), m.index(axis), decay, shard, self.dtype, self.device, alloc)
+            b.norm_weight = 1.0 if (tp == 1 or name.endswith("_tp")) else 1.0 / tp
+            self.buckets.append(b)
 
     # -- hyper-parameters -----------------------------------------------------------------------------------
     def set_lr(self, lr: float) -> None:
@@ -237,7 +247,14 @@ class ShardedEngine:
             reduced.append(g)
             lo, hi = b.owned_range()
             nlo, nhi = b.norm_range()
-            ops.sumsq(g[nlo - lo:nhi - lo], self.sumsq, accumulate=not first, scratch=self._scratch)
+            if getattr(b, "norm_weight", 1.0) == 1.0:
+                ops.sumsq(g[nlo - lo:nhi - lo], self.sumsq, accumulate=not first, scratch=self._scratch)
+            else:  # replicated inside a tensor-parallel group: every rank of the group adds 1 / tp of it
+                part = torch.zeros_like(self.sumsq)
+                ops.sumsq(g[nlo - lo:nhi - lo], part, accumulate=False, scratch=self._scratch)
+                if first:
+                    self.sumsq.zero_()
+                self.sumsq.add_(part * b.norm_weight)
             first = False
         # The objective is the mean over the dp_size data-parallel replicas (and over the accumulated
         # micro-batches); expert gradients already hold the contributions of every expert-parallel peer, so the

@@ -85,6 +85,22 @@ class EnhancedConversationTrainer:
         self.logger = logger or log
         self.mesh = mesh or ProcessMesh(create_groups=False)
         self.device = next(model.parameters()).device
+        # parallel strategies of the run (Config.tensor_parallel_size / sequence_parallel_size / pipeline_parallel_size through
+        # ProcessMesh.from_config): the model is converted in place before the engine packs its parameters
+        self.pipeline = None
+        if self.mesh.tp_size > 1 or self.mesh.sp_size > 1:
+            from ..parallel.strategy import apply_sequence_parallel, apply_tensor_parallel
+            apply_tensor_parallel(model, self.mesh)
+            apply_sequence_parallel(model, self.mesh)
+        if self.mesh.pp_size > 1:
+            from ..parallel.pipeline import InterleavedStages, PipelineStage
+            chunks = int(getattr(self.config, "pipeline_chunks", 1) or 1)
+            if chunks > 1:
+                self.pipeline = InterleavedStages(model, self.mesh.coord.pp, self.mesh.pp_size, chunks)
+            else:
+                self.pipeline = PipelineStage(model, self.mesh.coord.pp, self.mesh.pp_size)
+            self._pp_batches: List[Dict[str, torch.Tensor]] = []
+            self._pp_schedule = None
         self.precision_manager = PrecisionManager(self.config, self.device)
         # fp8 precisions switch the linear layers' forward products to the e4m3 tcgen05 GEMM (process-wide switch)
         from .. import ops as _ops
@@ -96,7 +112,8 @@ class EnhancedConversationTrainer:
 
         opt = dict(lr=self.config.learning_rate, betas=(self.config.adam_beta1, self.config.adam_beta2), eps=self.config.adam_eps,
                    weight_decay=self.config.weight_decay, max_grad_norm=getattr(self.config, "max_grad_norm", 1.0), mesh=self.mesh,
-                   grad_accumulation_steps=self.config.gradient_accumulation_steps)
+                   grad_accumulation_steps=1 if self.pipeline is not None else self.config.gradient_accumulation_steps)
+        # (a pipeline schedule already divides the loss by its number of micro-batches)
         if self.config.zero_stage >= 3 and self.mesh.ep_size == 1 and self.mesh.world > 1:
             from ..parallel.zero3 import ZeRO3Engine
             self.engine = ZeRO3Engine(model, fused_comm=fused_comm, **opt)  # per-block gather / release
@@ -199,6 +216,11 @@ class EnhancedConversationTrainer:
             self.heartbeat.check()  # a lost peer surfaces here, on the host, before any kernel waits for it
         self.model.train()
         batch = self._to_device(batch)
+        if self.mesh.sp_size > 1:
+            from ..parallel.strategy import shard_sequence
+            batch = shard_sequence(batch, self.mesh)  # this rank's L / W tokens of every sequence
+        if self.pipeline is not None:
+            return self._pipeline_collect(batch)
         labels = batch["labels"]
         if self.pad_token_id not in (None, 0):
             labels = torch.where(labels == self.pad_token_id, torch.full_like(labels, self.ignore_index), labels)
@@ -215,7 +237,44 @@ class EnhancedConversationTrainer:
         self._pending_device.append(res)
         return res
 
+    # -- pipeline parallelism: micro-batches are collected and run through the schedule at the optimiser step -------------------
+    def _pipeline_collect(self, batch: Dict[str, torch.Tensor]) -> Dict[str, Any]:
+        labels = batch["labels"]
+        if self.pad_token_id not in (None, 0):
+            labels = torch.where(labels == self.pad_token_id, torch.full_like(labels, self.ignore_index), labels)
+        self._pp_batches.append({"input_ids": batch["input_ids"], "labels": labels, "loss_weights": batch.get("loss_weights")})
+        self.micro_step += 1
+        zero = torch.zeros((), device=self.device)
+        res = {"loss": zero, "raw_loss": zero, "perplexity": zero, "valid_tokens": zero, "accuracy": zero, "aux_loss": zero,
+               "tokens": batch["input_ids"].numel(), "pipeline_pending": True}
+        return res
+
+    def _pipeline_run(self) -> None:
+        """All collected micro-batches through the 1F1B (or interleaved 1F1B) schedule; the loss of the last stage is shared
+        with the other stages for logging."""
+        from ..parallel.pipeline import InterleavedSchedule, InterleavedStages, OneFOneBSchedule
+        import torch.distributed as dist
+        mbs, self._pp_batches = self._pp_batches, []
+        if not mbs:
+            return
+        group = self.mesh.group("pp")
+        B, L = mbs[0]["input_ids"].shape
+        shape = (B, L, self.model.config.hidden_size)
+        dtype = next(p for p in self.model.parameters() if p.numel() > 0).dtype
+        key = (len(mbs), shape)
+        if self._pp_schedule is None or self._pp_schedule[0] != key:
+            cls = InterleavedSchedule if isinstance(self.pipeline, InterleavedStages) else OneFOneBSchedule
+            self._pp_schedule = (key, cls(self.pipeline, group, len(mbs), shape, dtype, self.device))
+        loss = self._pp_schedule[1].run(mbs)
+        last = self.mesh.ranks_along("pp")[-1]
+        t = loss.detach().float().reshape(1) if loss is not None else torch.zeros(1, device=self.device)
+        dist.broadcast(t, last, group=group)
+        tokens = sum(m["input_ids"].numel() for m in mbs)
+        self._pending_device.append({"loss": t[0], "raw_loss": t[0], "accuracy": torch.zeros((), device=self.device), "tokens": tokens})
+
     def optimizer_step(self) -> Dict[str, Any]:
+        if self.pipeline is not None:
+            self._pipeline_run()
         with self._lock:
             stats = self.engine.step()
             self.global_step += 1

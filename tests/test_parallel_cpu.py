@@ -26,6 +26,10 @@ def _pp_worker(rank, world, path):
     model = DeepSeekTransformer(ModelConfig(**CFG))
     model.load_state_dict(ref["init"])
     stage = PipelineStage(model, rank, world)
+    # the stage holds its own two layers only: the others' weights are gone, not just frozen
+    foreign = [i for i in range(4) if not (stage.start <= i < stage.end)]
+    assert stage.freed > 0 and all(p.numel() == 0 for i in foreign for p in model.layers[i].parameters())
+    assert all(p.numel() > 0 for i in range(stage.start, stage.end) for p in model.layers[i].parameters())
     sched = OneFOneBSchedule(stage, dist.group.WORLD, 4, (2, 16, 64), torch.float32, torch.device("cpu"))
     g = torch.Generator().manual_seed(3)
     ids = torch.randint(0, 256, (8, 17), generator=g)
@@ -51,7 +55,12 @@ def _pp_interleaved_worker(rank, world, path):
     g = torch.Generator().manual_seed(3)
     ids = torch.randint(0, 256, (8, 17), generator=g)
     mbs = [{"input_ids": ids[2 * i:2 * i + 2, :-1], "labels": ids[2 * i:2 * i + 2, 1:]} for i in range(4)]
+    from adaptivetrainingsystem_b200.parallel.pipeline import interleaved_order
+    order = interleaved_order(rank, world, 2, 4)
+    assert len(order) == 16 and [o[0] for o in order[:2 * (world - rank - 1) + world]] == ["F"] * (2 * (world - rank - 1) + world)
+    assert sorted(o for o in order if o[0] == "F") == sorted(("F", c, i) for c in range(2) for i in range(4))
     loss = sched.run(mbs)
+    assert sched.max_alive < 8  # 1F1B: fewer activations alive than chunks x micro-batches (a breadth-first order would keep all 8)
     if rank == world - 1:
         assert abs(loss.item() - ref["loss"]) < 1e-4, (loss.item(), ref["loss"])
     checked = 0
