@@ -24,6 +24,10 @@ _ROOT = os.path.dirname(_PKG)
 CSRC = os.path.join(_ROOT, "csrc")
 OUT_DIR = os.path.join(_PKG, "_C")
 CUDA_LIB = os.path.join(OUT_DIR, "libats_b200.so")
+# the same kernels with every data-dependent index range-checked (-DATS_DEBUG); loaded instead of the release library when the
+# environment says ATS_DEBUG_BUILD=1
+DEBUG_LIB = os.path.join(OUT_DIR, "libats_b200_debug.so")
+DEBUG_BUILD = os.environ.get("ATS_DEBUG_BUILD", "0") == "1"
 HOST_LIB = os.path.join(OUT_DIR, "libats_host.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -53,6 +57,23 @@ def _stale(target: str, sources: List[str]) -> bool:
 
 def cuda_sources() -> List[str]:
     return sorted(s for s in glob.glob(os.path.join(CSRC, "*.cu")) if os.path.basename(s) not in SINGLE_GPU_ONLY)
+
+
+def build_debug(force: bool = False) -> None:
+    """The bounds-checking build: -DATS_DEBUG, relocatable device code (one report word shared by all translation units)."""
+    os.makedirs(OUT_DIR, exist_ok=True)
+    srcs = cuda_sources()
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h"))
+    if not (force or _stale(DEBUG_LIB, srcs + headers)):
+        return
+    nvcc = _nvcc()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found; cannot build the sm_100a kernels")
+    cmd = [nvcc] + NVCC_FLAGS + ["-DATS_DEBUG", "-rdc=true", "-I", CSRC, "-o", DEBUG_LIB + ".tmp"] + srcs
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc (debug build) failed:\n" + r.stdout + r.stderr)
+    os.replace(DEBUG_LIB + ".tmp", DEBUG_LIB)
 
 
 def build(force: bool = False, verbose: bool = False) -> None:
@@ -91,12 +112,13 @@ def cuda_lib() -> ctypes.CDLL:
     if _cuda is None:
         with _lock:
             if _cuda is None:
-                if not os.path.exists(CUDA_LIB):
+                path = DEBUG_LIB if DEBUG_BUILD else CUDA_LIB
+                if not os.path.exists(path):
                     if _nvcc() is not None:
-                        build()
+                        build_debug() if DEBUG_BUILD else build()
                     else:
-                        raise RuntimeError(f"{CUDA_LIB} is missing and nvcc is unavailable; run __graft_entry__.build()")
-                _cuda = ctypes.CDLL(CUDA_LIB)
+                        raise RuntimeError(f"{path} is missing and nvcc is unavailable; run __graft_entry__.build()")
+                _cuda = ctypes.CDLL(path)
     return _cuda
 
 
@@ -126,6 +148,20 @@ class KernelError(RuntimeError):
 
 _STATUS_NAMES = {1: "TMA stage never arrived", 2: "TMA stage never released", 3: "accumulator never produced",
                  4: "accumulator never released", 5: "peer flag never arrived", 6: "bad argument"}
+_DEBUG_KERNELS = {1: "plan_slots", 2: "dispatch_rows", 3: "combine_rows", 4: "slot_dot", 5: "grouped GEMM row counts", 6: "decode attention",
+                  7: "serve_plan_dispatch", 8: "serve_combine", 9: "embedding_bwd", 10: "peer_reduce"}
+
+
+def debug_report() -> Optional[dict]:
+    """Debug build only: the first failed bounds check since the last call ({kernel, block, detail}), or ``None``; clears it."""
+    if not DEBUG_BUILD or _cuda is None:
+        return None
+    out = (ctypes.c_int * 4)()
+    _cuda.ats_debug_report.restype = ctypes.c_int
+    _cuda.ats_debug_report.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    if _cuda.ats_debug_report(out) != 1 or out[0] == 0:
+        return None
+    return {"code": out[0], "kernel": _DEBUG_KERNELS.get(out[1], out[1]), "block": out[2], "detail": out[3]}
 _status = {}
 
 
@@ -144,6 +180,9 @@ def check_status(device=None) -> None:
         if v != 0:
             t.zero_()
             raise KernelError(f"device {key}: kernel wait timed out: {_STATUS_NAMES.get(v, v)}")
+    rep = debug_report()
+    if rep is not None:
+        raise KernelError(f"bounds check failed in {rep['kernel']} (block {rep['block']}, value {rep['detail']}); the access was skipped")
 
 
 _launches = 0

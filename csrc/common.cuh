@@ -24,6 +24,32 @@ enum Status : int {
   kBadArgument = 6,
 };
 
+// ----------------------------------------------------------------------------------------------
+// Debug build (-DATS_DEBUG, built into a library of its own): every index that comes from data (expert ids, slot positions,
+// row counts, cache lengths) is range-checked before it becomes an address.  A violation records
+// {kBoundsCheck, kernel id, block, detail} in a report word and the thread SKIPS the access -- nothing traps, the context stays
+// usable and the host raises at its next status check.  The release build compiles the checks away.
+// ----------------------------------------------------------------------------------------------
+enum DebugKernel : int {
+  kDbgPlanSlots = 1, kDbgDispatch = 2, kDbgCombine = 3, kDbgSlotDot = 4, kDbgGemmGroups = 5, kDbgDecodeAttn = 6,
+  kDbgServeDispatch = 7, kDbgServeCombine = 8, kDbgEmbeddingBwd = 9, kDbgPeerReduce = 10,
+};
+constexpr int kBoundsCheck = 7;
+#ifdef ATS_DEBUG
+extern __device__ int g_debug_report[4];  // defined in elementwise.cu (the debug library is linked with relocatable device code)
+__device__ __forceinline__ bool dbg_check(bool ok, int kernel_id, long long detail) {
+  if (!ok && atomicCAS(&g_debug_report[0], 0, kBoundsCheck) == 0) {
+    g_debug_report[1] = kernel_id;
+    g_debug_report[2] = int(blockIdx.x);
+    g_debug_report[3] = int(detail);
+  }
+  return ok;
+}
+#define ATS_DBG_CHECK(cond, kernel_id, detail) (::ats::dbg_check((cond), (kernel_id), (long long)(detail)))
+#else
+#define ATS_DBG_CHECK(cond, kernel_id, detail) (true)
+#endif
+
 // Default wait budget in nanoseconds of %globaltimer (1 s).
 #ifndef ATS_WAIT_BUDGET_NS
 #define ATS_WAIT_BUDGET_NS 1000000000ull

@@ -680,3 +680,24 @@ ATS_API int ats_quantize_rows_e4m3(const void* x, long long ld, void* q, long lo
       static_cast<const __nv_bfloat16*>(x), ld, static_cast<uint8_t*>(q), ldq, scale, cols);
   return int(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------ debug build
+#ifdef ATS_DEBUG
+namespace ats {
+__device__ int g_debug_report[4] = {0, 0, 0, 0};
+}
+#endif
+// out4 = {code, kernel id, block, detail} of the first bounds check that failed since the last call (all zero: none), and the
+// report is cleared.  Returns 1 in the debug build, 0 in the release build (which has no checks).
+ATS_API int ats_debug_report(int* out4) {
+#ifdef ATS_DEBUG
+  int zero[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(out4, ats::g_debug_report, sizeof(zero)) != cudaSuccess) return -1;
+  if (cudaMemcpyToSymbol(ats::g_debug_report, zero, sizeof(zero)) != cudaSuccess) return -1;
+  return 1;
+#else
+  for (int i = 0; i < 4; ++i) out4[i] = 0;
+  return 0;
+#endif
+}

@@ -108,7 +108,10 @@ __device__ __forceinline__ int round_up_128(int v) { return (v + 127) & ~127; }
 __device__ __forceinline__ void group_extents(const GemmArgs& p, int g, int& mg, int& kg) {
   mg = p.M;
   kg = p.K;
-  if (p.ragged == 1) mg = min(round_up_128(p.counts[g / p.k_split]), p.M);
+  if (p.ragged == 1) {
+    const int cnt = p.counts[g / p.k_split];
+    mg = ATS_DBG_CHECK(cnt >= 0 && cnt <= p.M, kDbgGemmGroups, cnt) ? min(round_up_128(cnt), p.M) : 0;
+  }
   if (p.ragged == 2) {
     kg = 0;
     for (int s = 0; s < p.k_segs; ++s) kg += min(round_up_128(p.counts[g * p.k_segs + s]), p.K);

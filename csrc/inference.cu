@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attn_mma_kernel(const Deco
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int n_old = p.lengths ? p.lengths[b] : p.length;
+  int n_old = p.lengths ? p.lengths[b] : p.length;
+  if (!ATS_DBG_CHECK(n_old >= 0 && n_old < p.max_len, kDbgDecodeAttn, n_old)) return;
   const int n_tot = n_old + 1;  // the new token attends to itself
   const int k0 = chunk * DEC_CHUNK;
   const bool active = k0 < n_tot;
@@ -611,6 +612,7 @@ __global__ void __launch_bounds__(256) serve_plan_dispatch_kernel(const __nv_bfl
   }
   if (s >= slots) return;
   const int e = topk_idx[s];
+  if (!ATS_DBG_CHECK(e >= 0 && e < experts, kDbgServeDispatch, e)) return;
   int rank = 0;
   for (int i = lane; i < s; i += 32) rank += topk_idx[i] == e;
 #pragma unroll
@@ -642,6 +644,7 @@ __global__ void __launch_bounds__(256) serve_combine_kernel(__nv_bfloat16* const
       const int pos = slot_pos[t * k + j];
       if (pos < 0) continue;
       const int e = topk_idx[t * k + j];
+      if (!ATS_DBG_CHECK(e >= 0 && e < SRV_MAX_E, kDbgServeCombine, e)) continue;
       const float wt = topk_w[t * k + j];
       const __nv_bfloat16* base = src_table ? src_table[e] : src0 + (long long)e * src_stride;
       const uint4 a = reinterpret_cast<const uint4*>(base + (long long)pos * hidden)[v];

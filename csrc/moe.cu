@@ -401,7 +401,8 @@ plan_slots_kernel(const int* __restrict__ topk_idx, int* __restrict__ slot_pos, 
   __syncthreads();
   for (long long base = 0; base < slots; base += blockDim.x) {
     const long long s = base + threadIdx.x;
-    const int e = s < slots ? topk_idx[s] : -1;
+    int e = s < slots ? topk_idx[s] : -1;
+    if (e >= 0 && !ATS_DBG_CHECK(e < experts, kDbgPlanSlots, e)) e = -1;
     int my_rank_in_warp = 0;
     for (int x = 0; x < experts; ++x) {
       const unsigned mask = __ballot_sync(0xffffffffu, e == x);
@@ -506,6 +507,7 @@ dispatch_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restric
     const int pos = slot_pos[w];
     if (pos < 0) return;
     const int e = topk_idx[w];
+    if (!ATS_DBG_CHECK(e >= 0 && e < experts && pos < capacity, kDbgDispatch, e < 0 || e >= experts ? e : pos)) return;
     const long long t = w / k;
     const uint4* s = reinterpret_cast<const uint4*>(src + t * hidden);
     uint4* d = reinterpret_cast<uint4*>(dst_base[e] + (long long)pos * hidden);
@@ -555,6 +557,7 @@ combine_rows_kernel(__nv_bfloat16* const* __restrict__ src_base, __nv_bfloat16* 
       if (pos < 0) continue;
       const float wt = topk_w ? topk_w[t * k + j] : 1.f;
       const int e = topk_idx[t * k + j];
+      if (!ATS_DBG_CHECK(e >= 0 && e < 64, kDbgCombine, e)) continue;
       uint4 a = reinterpret_cast<const uint4*>(src_base[e] + (long long)pos * hidden)[v];
       // rows pulled from a peer GPU are kept in a local copy for the backward pass (gate-weight gradient)
       if (copy_base) reinterpret_cast<uint4*>(copy_base[e] + (long long)pos * hidden)[v] = a;
@@ -577,7 +580,7 @@ slot_dot_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restri
   if (w >= slots) return;
   const int pos = slot_pos[w];
   float acc = 0.f;
-  if (pos >= 0) {
+  if (pos >= 0 && ATS_DBG_CHECK(topk_idx[w] >= 0 && topk_idx[w] < 64, kDbgSlotDot, topk_idx[w])) {
     const long long t = w / k;
     const uint4* a = reinterpret_cast<const uint4*>(dout + t * hidden);
     const uint4* b = reinterpret_cast<const uint4*>(src_base[topk_idx[w]] + (long long)pos * hidden);
