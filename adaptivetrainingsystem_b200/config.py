@@ -325,6 +325,8 @@ class Config:
     comm_timeout_s: float = 1.0        # budget of every in-kernel wait on a peer (flag barriers, gathered-weight chunks)
     heartbeat_interval_s: float = 0.5  # period of the rank heartbeat (parallel/health.py); 0 switches the watchdog off
     heartbeat_timeout_s: float = 30.0  # a peer whose heartbeat is older than this counts as lost
+    expert_rebalance_interval: int = 0    # > 0: every this many optimiser steps hot experts are exchanged between EP ranks
+    expert_rebalance_tolerance: float = 0.1  # stop exchanging when the heaviest rank is within this fraction of the mean
     # -- adaptive LR ------------------------------------------------------------
     enable_adaptive_lr: bool = True
     allow_scheduler_override: bool = True

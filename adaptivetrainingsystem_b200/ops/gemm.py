@@ -176,6 +176,27 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+def _tn_splits(M: int, N: int, K: int, clusters: int = 74) -> int:
+    """Reduction slices for a weight-gradient product whose 256 x 256 tiles fill the CTA pairs badly (e.g. 80 tiles on 74 pairs run
+    two waves at 0.54 utilisation).  Modelled time = waves / slices + the fold of the fp32 partials; returns the best slice count
+    (1 = do not split).  Only long reductions are worth it."""
+    if M < 256 or K < 8192 or os.environ.get("ATS_WGRAD_SPLIT_K", "1") != "1":
+        return 1
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if tiles >= 4 * clusters:
+        return 1
+    wave_us = 256 * 256 * K * 2 / 18.9e6   # one wave of full tiles at the sustained rate of a CTA pair
+    best, best_t = 1, -(-tiles // clusters) * wave_us
+    for s in (2, 3, 4):
+        if K % (64 * s) or K // s < 2048:
+            continue
+        fold_us = ((2 * s * 4 + 4) * M * N) / 6.5e6
+        t = -(-(tiles * s) // clusters) * wave_us / s + fold_us
+        if t < 0.93 * best_t:
+            best, best_t = s, t
+    return best
+
+
 class ScatterTarget:
     """Destination of a weight-gradient product whose rows are owned by different ranks (ZeRO-3 row shards): ``table`` is a
     device int64 tensor with the address of every owner's fp32 gradient rows, ``rows`` the number of rows per owner.  Passed
@@ -215,6 +236,16 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
         out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else a.dtype, device=a.device)
         accumulate = False
     fp32 = out.dtype == torch.float32
+    splits = _tn_splits(M, N, K) if (not fp32 and out.is_contiguous() and alpha == 1.0) else 1
+    if splits > 1:
+        # the reduction (tokens) is cut into slices that run as groups with fp32 partial outputs; one launch folds them (+ the
+        # gradient accumulated so far) into the bf16 result
+        kp = K // splits
+        part = torch.empty(splits, M, N, dtype=torch.float32, device=a.device)
+        _raw(a, K, M, a.stride(0), 1, b, K, N, b.stride(0), 1, part, N, None, 0, None, 0, M, N, kp, epilogue=EPI_F32, groups=splits,
+             a_gs_k=kp, b_gs_k=kp, d_gs=M * N, max_ctas=max_ctas)
+        _fold_partials(part, splits, M * N, 1, out, out if accumulate else None)
+        return out
     epi = EPI_F32 if fp32 else (EPI_ADDC if accumulate else EPI_STORE)
     _raw(a, K, M, a.stride(0), 1, b, K, N, b.stride(0), 1, out, out.stride(0),
          out if (accumulate and not fp32) else None, out.stride(0), None, 0, M, N, K, alpha=alpha,

@@ -357,6 +357,46 @@ class ShardedEngine:
             n += 1
         return n
 
+    # -- row access: moving experts between ranks, permuting router rows -----------------------------------------
+    def _locate(self, name: str) -> Tuple[Bucket, int]:
+        for b in self.buckets:
+            if name in b.names:
+                return b, b.names.index(name)
+        raise KeyError(name)
+
+    def read_rows(self, name: str, rows: List[int]) -> torch.Tensor:
+        """Optimiser state of whole rows (dim 0) of a parameter: ``[3, len(rows), row_numel]`` fp32 (master, exp_avg,
+        exp_avg_sq).  Collective over the parameter's group when its state is sharded: every rank of the group gets all of it."""
+        b, i = self._locate(name)
+        p, o = b.params[i], b.offsets[i]
+        rn = p.numel() // p.shape[0]
+        lo, hi = b.owned_range()
+        out = torch.zeros(3, len(rows), rn, dtype=torch.float32, device=self.device)
+        for j, r in enumerate(rows):
+            base = o + r * rn
+            a, e = max(base, lo), min(base + rn, hi)
+            if e > a:
+                for k, key in enumerate(("master", "exp_avg", "exp_avg_sq")):
+                    out[k, j, a - base:e - base].copy_(getattr(b, key)[a - lo:e - lo])
+        if b.shard_states and b.W > 1 and dist.is_initialized():
+            dist.all_reduce(out, group=b.group)
+        return out
+
+    def write_rows(self, name: str, rows: List[int], state: torch.Tensor) -> None:
+        """Inverse of :meth:`read_rows` (local: every rank writes the stretches it owns); the parameter rows are re-derived from
+        the master values."""
+        b, i = self._locate(name)
+        p, o = b.params[i], b.offsets[i]
+        rn = p.numel() // p.shape[0]
+        lo, hi = b.owned_range()
+        for j, r in enumerate(rows):
+            base = o + r * rn
+            a, e = max(base, lo), min(base + rn, hi)
+            if e > a:
+                for k, key in enumerate(("master", "exp_avg", "exp_avg_sq")):
+                    getattr(b, key)[a - lo:e - lo].copy_(state[k, j, a - base:e - base])
+            p.data[r].copy_(state[0, j].view(p.shape[1:]).to(p.dtype))
+
     def resync_master_from_params(self) -> None:
         """After parameters were overwritten (checkpoint load), refresh the fp32 master slices."""
         for b in self.buckets:

@@ -400,6 +400,9 @@ class EnhancedConversationTrainer:
                     ops.check_status()
                 except ops.KernelError:
                     raise
+            rebalance = int(getattr(self.config, "expert_rebalance_interval", 0) or 0)
+            if rebalance and self.global_step % rebalance == 0:
+                self.rebalance_experts()
             every = getattr(self.config, "save_every_n_batches", 0)
             if every and self.global_step % every == 0:
                 self.save_checkpoint(epoch, tag=f"step_{self.global_step}")
@@ -709,6 +712,26 @@ class EnhancedConversationTrainer:
         ``nn.Dropout`` no forward uses, ``trainer.py:1510-1514``)."""
         for l in self.model.get_moe_layers():
             l.expert_dropout = float(p)
+
+    def rebalance_experts(self) -> Optional[Dict[str, Any]]:
+        """Exchange hot experts between expert-parallel ranks (``parallel/load_balance.py``); collective, between steps.
+        Returns the balancer's report, or ``None`` when the layout leaves nothing to move."""
+        mesh = self.mesh
+        if mesh is None or mesh.ep_size < 2 or not self.model.get_moe_layers():
+            return None
+        if self.model.get_moe_layers()[0].num_experts // mesh.ep_size < 2:
+            return None  # one expert per rank: every placement loads the ranks alike
+        from ..parallel.load_balance import ExpertLoadBalancer
+        # built per call: experts may have been added or pruned since the last one
+        balancer = ExpertLoadBalancer(self.model, mesh, self.engine if hasattr(self.engine, "read_rows") else None,
+                                      tolerance=float(getattr(self.config, "expert_rebalance_tolerance", 0.1)))
+        report = balancer.balance()
+        if report["swaps"] and self.logger is not None:
+            worst = max(r["before"] for r in report["layers"])
+            after = max(r["after"] for r in report["layers"])
+            self.logger.info("expert rebalance at step %d: %d exchanges, heaviest rank / mean %.2f -> %.2f", self.global_step,
+                             report["swaps"], worst, after)
+        return report
 
     def get_expert_statistics(self) -> Dict[str, Any]:
         per_layer = self.model.get_routing_statistics()

@@ -266,3 +266,24 @@ def test_grouped_gemm_with_reduction_slices():
                     err = (out[g, :n].float() - ref[g, :n]).norm(dim=-1) / (ref[g, :n].norm(dim=-1) + 1e-6)
                     assert err.max().item() < 1e-2, (C, cnt, b_div, S, packed, g, err.max().item())
     ops.check_status()
+
+
+def test_weight_gradient_product_with_reduction_slices():
+    """tn products whose tiles fill the CTA pairs badly split the token dimension (fp32 partials + fold): store and accumulate."""
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    torch.manual_seed(9)
+    M, N, K = 2560, 2048, 16384
+    assert G._tn_splits(M, N, K) > 1 and G._tn_splits(2048, 2048, K) == 1
+    dy = (torch.randn(K, M, device="cuda") * 0.1).bfloat16()
+    x = (torch.randn(K, N, device="cuda") * 0.1).bfloat16()
+    ref = dy.float().t() @ x.float()
+    out = G.gemm_tn(dy, x)
+    err = (out.float() - ref).norm(dim=-1) / (ref.norm(dim=-1) + 1e-6)
+    assert err.max().item() < 1e-2
+    acc0 = (torch.randn(M, N, device="cuda") * 2).bfloat16()
+    acc = acc0.clone()
+    G.gemm_tn(dy, x, out=acc, accumulate=True)
+    ref2 = ref + acc0.float()
+    err = (acc.float() - ref2).norm(dim=-1) / (ref2.norm(dim=-1) + 1e-6)
+    assert err.max().item() < 1e-2
+    ops.check_status()
