@@ -30,6 +30,7 @@ from torch.utils.checkpoint import checkpoint
 from ..config import ModelConfig
 from .. import ops
 from ..ops import moe as moe_ops
+from ..ops import mod as mod_ops
 
 
 class RMSNorm(nn.Module):
@@ -400,6 +401,15 @@ class MoDFFN(nn.Module):
             gate = (scores > 0).to(h.dtype).unsqueeze(-1) * torch.sigmoid(scores).to(h.dtype).unsqueeze(-1)
             y = ops.swiglu_mlp(h, self.gate_up_proj, self.down_proj)
             return base + y * gate, None
+        if self.cfg.mod_per_sequence and mod_ops.kernel_path_ok(h, L):
+            # training / prefill on the GPU: scores, selection, gather, weighted scatter-add and all their gradients are kernels
+            r = self.router
+            picked, weight, aux, sel, slot_of, _ = mod_ops.route(h, r.router.weight, r.router.bias, r.temperature, r.keep_count(L))
+            y = ops.swiglu_mlp(picked, self.gate_up_proj, self.down_proj)
+            with torch.no_grad():
+                r.selected_tokens += float(sel.numel())
+                r.total_tokens += float(B * L)
+            return mod_ops.scatter(residual, y, weight, sel, slot_of, L), aux * self.cfg.mod_aux_weight
         sel, weight, aux, _ = self.router(h, per_sequence=self.cfg.mod_per_sequence)
         idx = sel.long()
         picked = torch.gather(h, 1, idx.unsqueeze(-1).expand(-1, -1, H))

@@ -149,7 +149,7 @@ class KernelError(RuntimeError):
 _STATUS_NAMES = {1: "TMA stage never arrived", 2: "TMA stage never released", 3: "accumulator never produced",
                  4: "accumulator never released", 5: "peer flag never arrived", 6: "bad argument"}
 _DEBUG_KERNELS = {1: "plan_slots", 2: "dispatch_rows", 3: "combine_rows", 4: "slot_dot", 5: "grouped GEMM row counts", 6: "decode attention",
-                  7: "serve_plan_dispatch", 8: "serve_combine", 9: "embedding_bwd", 10: "peer_reduce"}
+                  7: "serve_plan_dispatch", 8: "serve_combine", 9: "embedding_bwd", 10: "peer_reduce", 11: "mod_rows"}
 
 
 def debug_report() -> Optional[dict]:

@@ -306,7 +306,9 @@ def run_ours(args) -> dict:
                    "fused_comm": bool(cfg.fused_comm), "attention_backend": os.environ.get("ATS_ATTN", "native"),
                    "capacity_factor": cfg.capacity_factor if cfg.use_moe else None, "drop_tokens": bool(cfg.drop_tokens) if cfg.use_moe else None,
                    "dropped_slot_fraction": dropped_fraction, "lr_schedule_steps": args.warmup + 2 * args.steps + 1,
-                   "loss_first": first_loss, "loss_last": last},
+                   "loss_first": first_loss, "loss_last": last,
+                   **({"precision_note": "the preset names fp8; block-scaled fp8 training GEMMs are not built, every product of this run is bf16"}
+                      if "fp8" in str(cfg.precision) else {})},
         "clocks": clk.summary(),
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4},

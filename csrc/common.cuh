@@ -32,7 +32,7 @@ enum Status : int {
 // ----------------------------------------------------------------------------------------------
 enum DebugKernel : int {
   kDbgPlanSlots = 1, kDbgDispatch = 2, kDbgCombine = 3, kDbgSlotDot = 4, kDbgGemmGroups = 5, kDbgDecodeAttn = 6,
-  kDbgServeDispatch = 7, kDbgServeCombine = 8, kDbgEmbeddingBwd = 9, kDbgPeerReduce = 10,
+  kDbgServeDispatch = 7, kDbgServeCombine = 8, kDbgEmbeddingBwd = 9, kDbgPeerReduce = 10, kDbgModRows = 11,
 };
 constexpr int kBoundsCheck = 7;
 #ifdef ATS_DEBUG

