@@ -150,7 +150,7 @@ class GroupedQueryAttention(nn.Module):
         B, L, _ = h.shape
         W, r = self.sp_size, self.sp_rank
         rope.ensure(W * L, h.device)
-        qkv = ops.linear(h, self.qkv_proj)
+        qkv = ops.linear(h, self.qkv_proj, reduce_group=self.tp_group)
         qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, pos_offset=r * L)
         nq, nk = self.n_q * self.d, self.n_kv * self.d
         q = scatter_heads_gather_sequence(qkv[..., :nq].reshape(B, L, self.n_q, self.d), self.sp_group)
@@ -163,9 +163,6 @@ class GroupedQueryAttention(nn.Module):
                 attention_mask: Optional[torch.Tensor] = None, cache: Optional[KVCache] = None,
                 positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, L, _ = h.shape
-        if self.tp_group is not None:
-            from ..parallel.tensor_parallel import _CopyToRegion
-            h = _CopyToRegion.apply(h, self.tp_group)
         if self.sp_group is not None and cache is None and attention_mask is None and positions is None:
             return self._forward_sequence_parallel(h, residual, rope)
         offset = cache.length if cache is not None else 0
@@ -173,12 +170,12 @@ class GroupedQueryAttention(nn.Module):
         if graph_decode:
             # fill level and positions come from device memory, nothing of this call depends on Python state
             rope.ensure(cache.max_len, h.device)
-            qkv = ops.linear(h, self.qkv_proj)
+            qkv = ops.linear(h, self.qkv_proj, reduce_group=self.tp_group)
             qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, positions=cache.device_positions.view(B, 1))
             a = ops.decode_attention(qkv, cache.k[self.layer_idx], cache.v[self.layer_idx], cache.device_lengths, self.n_q, self.n_kv, self.d)
             return self._project_out(a, residual)
         rope.ensure(offset + L if positions is None else int(self.cfg.seq_length), h.device)
-        qkv = ops.linear(h, self.qkv_proj)
+        qkv = ops.linear(h, self.qkv_proj, reduce_group=self.tp_group)
         nq, nk = self.n_q * self.d, self.n_kv * self.d
         if (cache is None and attention_mask is None and positions is None and self.d % 16 == 0
                 and ops.attention_packed_available(qkv, self.d, L)):
@@ -212,8 +209,9 @@ class DenseSwiGLU(nn.Module):
 
     def forward(self, h: torch.Tensor, residual: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         if self.tp_group is not None:
-            from ..parallel.tensor_parallel import _CopyToRegion, _ReduceFromRegion
-            y = _ReduceFromRegion.apply(ops.swiglu_mlp(_CopyToRegion.apply(h, self.tp_group), self.gate_up_proj, self.down_proj), self.tp_group)
+            from ..parallel.tensor_parallel import _ReduceFromRegion
+            # the all-reduce of the input gradient starts inside the MLP's backward and runs under its weight-gradient products
+            y = _ReduceFromRegion.apply(ops.swiglu_mlp(h, self.gate_up_proj, self.down_proj, reduce_group=self.tp_group), self.tp_group)
             return (y + residual if residual is not None else y), None
         return ops.swiglu_mlp(h, self.gate_up_proj, self.down_proj, residual), None
 

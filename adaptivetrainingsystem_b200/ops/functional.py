@@ -345,9 +345,27 @@ def _z3_gathering(w):
     return z3 if (z3 is not None and z3.full is None and z3.gather_in_gemm) else None
 
 
+def _start_grad_reduce(dx, group):
+    """Tensor parallelism: the input gradient of a column-split product is a partial sum.  Its all-reduce is started here and
+    runs on the communication stream while the caller computes the weight gradient; ``.wait()`` orders the compute stream
+    after it (reference: colossalai ``shardformer/layer/_operation.py:108-167``)."""
+    if group is None or dx is None:
+        return None
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return None
+    return dist.all_reduce(dx, group=group, async_op=True)
+
+
+def _copy_to_region(x, group):
+    from ..parallel.tensor_parallel import _CopyToRegion
+    return _CopyToRegion.apply(x, group)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, residual):
+    def forward(ctx, x, w, residual, reduce_group=None):
+        ctx.reduce_group = reduce_group
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         z3 = _z3_gathering(w)
@@ -372,19 +390,25 @@ class _LinearFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = G.gemm_nn(dy2, w).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        pending = _start_grad_reduce(dx, ctx.reduce_group)  # overlaps the weight-gradient product below
         dw = None
         if ctx.needs_input_grad[1]:
             dw = _deliver_grad(w, lambda out, acc: G.gemm_tn(dy2, x2, out=out, accumulate=acc))
-        return dx, dw, (dy if ctx.has_res else None)
+        if pending is not None:
+            pending.wait()
+        return dx, dw, (dy if ctx.has_res else None), None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x @ w.T (+ residual)`` -- the residual add is fused into the GEMM epilogue."""
+def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None, reduce_group=None) -> torch.Tensor:
+    """``x @ w.T (+ residual)`` -- the residual add is fused into the GEMM epilogue.  ``reduce_group``: ``w`` holds this rank's
+    output columns of a tensor-parallel product, so the input gradient is all-reduced over that group."""
     if _lib.use_cuda_kernels(x):
         from . import fp8
         if fp8.enabled() and getattr(w, "_ats_z3", None) is None and x.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0:
-            return fp8.linear_fp8(x, w, residual)
-        return _LinearFn.apply(x, w, residual)
+            return fp8.linear_fp8(_copy_to_region(x, reduce_group) if reduce_group is not None else x, w, residual)
+        return _LinearFn.apply(x, w, residual, reduce_group)
+    if reduce_group is not None:
+        x = _copy_to_region(x, reduce_group)
     y = F.linear(x, w)
     return y + residual if residual is not None else y
 
@@ -431,7 +455,8 @@ class _SwiGLUMLPFn(torch.autograd.Function):
     """down( silu(x Wg^T) * (x Wu^T) ) with the activation fused into the first GEMM's epilogue."""
 
     @staticmethod
-    def forward(ctx, x, w1, w2, residual):
+    def forward(ctx, x, w1, w2, residual, reduce_group=None):
+        ctx.reduce_group = reduce_group
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         need_bwd = any(ctx.needs_input_grad)
@@ -471,16 +496,25 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dgu, h = G.gemm_nn_swiglu_bwd(dy2, w2, pre)  # dh = dy · w2 goes through the SwiGLU backward in the GEMM epilogue
+        if ctx.reduce_group is not None:
+            # tensor parallel: the input gradient first, so that its all-reduce runs under both weight-gradient products
+            dx = G.gemm_nn(dgu, w1).view(ctx.shape)
+            pending = _start_grad_reduce(dx, ctx.reduce_group)
         dw2 = _deliver_grad(w2, lambda out, acc: G.gemm_tn(dy2, h, out=out, accumulate=acc))
         dw1 = _deliver_grad(w1, lambda out, acc: G.gemm_tn(dgu, x2, out=out, accumulate=acc))
-        dx = G.gemm_nn(dgu, w1).view(ctx.shape)
-        return dx, dw1, dw2, (dy if ctx.has_res else None)
+        if ctx.reduce_group is None:
+            dx = G.gemm_nn(dgu, w1).view(ctx.shape)
+        elif pending is not None:
+            pending.wait()
+        return dx, dw1, dw2, (dy if ctx.has_res else None), None
 
 
 def swiglu_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-               residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+               residual: Optional[torch.Tensor] = None, reduce_group=None) -> torch.Tensor:
     if _lib.use_cuda_kernels(x):
-        return _SwiGLUMLPFn.apply(x, w_gate_up, w_down, residual)
+        return _SwiGLUMLPFn.apply(x, w_gate_up, w_down, residual, reduce_group)
+    if reduce_group is not None:
+        x = _copy_to_region(x, reduce_group)
     y = F.linear(swiglu_reference(F.linear(x, w_gate_up)), w_down)
     return y + residual if residual is not None else y
 
