@@ -5,9 +5,16 @@ GEMM accumulates the raw e4m3 products in fp32 tensor memory over the whole redu
 ``row_scale[m] * col_scale[n]``.  Unlike a 1 x 128 / 128 x 128 block format this needs no per-block promotion inside the
 main loop, so the fp8 main loop is the bf16 one with half the operand bytes and ``kind::f8f6f4`` MMAs.
 
-Forward products run in fp8; the backward products (input and weight gradients) use the saved bf16 activations and the
-bf16 weights, so optimiser state, gradients and master weights are unchanged ("hybrid" precision).  The reference lists
-fp8 precisions but has no fp8 GEMM path at all (reference ``training/trainer.py:440-446`` only wraps autocast).
+Training recipe (``precision = mixed_fp8`` and the other fp8 names): the forward products AND the input-gradient products
+run in fp8, dense linears, the dense SwiGLU MLP and the grouped expert products alike.  An input gradient
+``dx[t, i] = sum_o dy[t, o] W[o, i]`` reduces over the output channels, so its operands are ``dy`` quantised per token and a
+second, transposed copy of the weight quantised per INPUT channel (``quantized_weight_t``; both copies are made once per
+optimiser step and cached).  Weight gradients reduce over the tokens; they stay in bf16 on the saved bf16 activations, because
+quantising both of their operands along the token dimension would need two more transposing passes over the activations
+per product, which costs more than the fp8 product saves at these shapes.  Optimiser state, gradients and master weights
+are unchanged.  The product ``dh = dy W2`` inside the SwiGLU backward keeps its bf16 kernel (its epilogue reads the saved
+pre-activations).  The reference lists fp8 precisions but has no fp8 GEMM path at all (reference ``training/trainer.py:440-446``
+only wraps autocast).
 """
 from __future__ import annotations
 
@@ -100,6 +107,78 @@ def quantized_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 def clear_weight_cache() -> None:
     _weight_cache.clear()
+    _weight_cache_t.clear()
+
+
+_weight_cache_t: Dict[int, Tuple[Tuple[int, int], torch.Tensor, torch.Tensor]] = {}
+
+
+def quantized_weight_t(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The transposed weight quantised per row of the transpose, i.e. per input channel: for ``w`` [N, K] -> e4m3 [K, N] and
+    scales [K]; for stacked expert weights [E, N, K] -> [E * K, N] and [E * K].  Cached until the parameters change."""
+    key = w.data_ptr()
+    stamp = (w._version, _epoch)
+    hit = _weight_cache_t.get(key)
+    if hit is not None and hit[0] == stamp:
+        return hit[1], hit[2]
+    wt = w.detach().transpose(-1, -2).contiguous()
+    q, s = quantize_rows(wt.view(-1, wt.shape[-1]))
+    if len(_weight_cache_t) > 4096:
+        _weight_cache_t.clear()
+    _weight_cache_t[key] = (stamp, q, s)
+    return q, s
+
+
+def quantized_expert_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[E, N, K] -> e4m3 [E * N, K], scales [E * N] (per output channel of every expert), cached."""
+    key = w.data_ptr()
+    stamp = (w._version, _epoch)
+    hit = _weight_cache.get(key)
+    if hit is not None and hit[0] == stamp and hit[1].shape[0] == w.shape[0] * w.shape[1]:
+        return hit[1], hit[2]
+    q, s = quantize_rows(w.detach().view(-1, w.shape[-1]))
+    _weight_cache[key] = (stamp, q, s)
+    return q, s
+
+
+def grouped_usable(x: torch.Tensor, n: int, k: int) -> bool:
+    return enabled() and _lib.use_cuda_kernels(x) and k % 16 == 0 and n % 16 == 0
+
+
+def grouped_nt_fp8(x: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, n: int, counts: torch.Tensor, swiglu: bool = False,
+                   pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, b_div: int = 1) -> torch.Tensor:
+    """x [G, C, K] (bf16, quantised here per row) against the e4m3 weights ``wq`` [E * n, K] with scales ``ws`` [E * n]: the first
+    counts[g] rows of group g times weight g // b_div, -> [G, C, n] or, through SwiGLU, [G, C, n / 2] (+ pre-activations)."""
+    Gn, C, K = x.shape
+    assert x.is_contiguous() and C % 128 == 0 and wq.shape[1] == K
+    xq, xs = quantize_rows(x.view(Gn * C, K))
+    n_out = n // 2 if swiglu else n
+    if out is None:
+        out = torch.empty(Gn, C, n_out, dtype=x.dtype, device=x.device)
+    st = _lib.status_tensor(x.device)
+    err = _fns().ats_gemm_fp8(_lib.ptr(xq), Gn * C, K, xq.stride(0), _lib.ptr(wq), wq.shape[0], K, wq.stride(0), _lib.ptr(out), n_out, None, 0,
+                              _lib.ptr(pre_act), n if pre_act is not None else 0, C, n_out, K, 1.0, G.EPI_SWIGLU if swiglu else G.EPI_STORE,
+                              n // 2 if swiglu else 0, Gn, 1, _lib.ptr(counts), C, n, C * n_out, 0, C * n if pre_act is not None else 0, b_div,
+                              _lib.ptr(xs), C, _lib.ptr(ws), n, _lib.ptr(st), 0, _lib.stream_ptr(x.device))
+    _lib.check(err, "ats_gemm_fp8 (grouped)")
+    return out
+
+
+def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: bool = False, pre_act: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None, b_div: int = 1) -> torch.Tensor:
+    """Forward product of the experts: fp8 when the fp8 recipe is on, else the bf16 grouped GEMM."""
+    if grouped_usable(x, w.shape[1], w.shape[2]) and not getattr(w, "_ats_packed", False):
+        wq, ws = quantized_expert_weight(w)
+        return grouped_nt_fp8(x, wq, ws, w.shape[1], counts, swiglu, pre_act, out, b_div)
+    return G.grouped_nt(x, w, counts, swiglu=swiglu, pre_act=pre_act, out=out, b_div=b_div, packed=bool(getattr(w, "_ats_packed", False)))
+
+
+def grouped_nn(dy: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, b_div: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Input gradient of the expert product: dy [G, C, N] . w [E, N, K] -> [G, C, K]; fp8 on the per-input-channel copy of w."""
+    if grouped_usable(dy, w.shape[2], w.shape[1]):
+        wq, ws = quantized_weight_t(w)            # [E * K, N]
+        return grouped_nt_fp8(dy, wq, ws, w.shape[2], counts, out=out, b_div=b_div)
+    return G.grouped_nn(dy, w, counts, out=out, b_div=b_div)
 
 
 def gemm_nt_fp8(aq: torch.Tensor, a_scale: torch.Tensor, bq: torch.Tensor, b_scale: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -133,6 +212,17 @@ def gemm_nt_fp8(aq: torch.Tensor, a_scale: torch.Tensor, bq: torch.Tensor, b_sca
     return out
 
 
+def input_grad(dy2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """dy2 [T, N] . w [N, K] -> [T, K]: e4m3 product of dy (per token) with the per-input-channel copy of w when the shapes allow
+    it, else the bf16 product."""
+    N, K = w.shape
+    if N % 16 == 0 and K % 8 == 0 and _lib.use_cuda_kernels(dy2):
+        gq, gs = quantize_rows(dy2)
+        wq, ws = quantized_weight_t(w)
+        return gemm_nt_fp8(gq, gs, wq, ws)
+    return G.gemm_nn(dy2, w)
+
+
 class _LinearFP8Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, residual):
@@ -155,7 +245,9 @@ class _LinearFP8Fn(torch.autograd.Function):
         dy2 = dy.reshape(-1, w.shape[0])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dx = G.gemm_nn(dy2, w).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = input_grad(dy2, w).view(ctx.shape)
         dw = None
         if ctx.needs_input_grad[1]:
             dw = _deliver_grad(w, lambda out, acc: G.gemm_tn(dy2, x2, out=out, accumulate=acc))
@@ -163,7 +255,7 @@ class _LinearFP8Fn(torch.autograd.Function):
 
 
 def linear_fp8(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x @ w.T (+ residual)`` with an e4m3 forward product; backward products in bf16."""
+    """``x @ w.T (+ residual)`` with e4m3 forward and input-gradient products; the weight gradient in bf16."""
     if _lib.use_cuda_kernels(x) and x.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0:
         return _LinearFP8Fn.apply(x, w, residual)
     # PyTorch definition: quantised forward value, straight-through gradient of the unquantised product

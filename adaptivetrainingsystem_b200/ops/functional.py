@@ -457,6 +457,7 @@ class _SwiGLUMLPFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w1, w2, residual, reduce_group=None):
         ctx.reduce_group = reduce_group
+        ctx.fp8 = False
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         need_bwd = any(ctx.needs_input_grad)
@@ -473,7 +474,8 @@ class _SwiGLUMLPFn(torch.autograd.Function):
             h = gathered_gemm(x2, z1, swiglu=True, pre_act=pre)
             gathered_gemm(h, z2, out=y.view(-1, n2), add=r2)
         elif fp8.enabled() and x2.shape[1] % 16 == 0 and w1.shape[0] % 32 == 0:
-            # e4m3 forward products (per-token / per-channel scales); the backward below stays in bf16
+            # e4m3 forward products (per-token / per-channel scales); backward: input gradient in e4m3, the rest in bf16
+            ctx.fp8 = True
             xq, xs = fp8.quantize_rows(x2)
             w1q, w1s = fp8.quantized_weight(w1)
             h = fp8.gemm_nt_fp8(xq, xs, w1q, w1s, swiglu=True, aux=pre)
@@ -496,14 +498,19 @@ class _SwiGLUMLPFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dgu, h = G.gemm_nn_swiglu_bwd(dy2, w2, pre)  # dh = dy · w2 goes through the SwiGLU backward in the GEMM epilogue
+        if ctx.fp8:
+            from . import fp8
+            input_grad = lambda: fp8.input_grad(dgu, w1).view(ctx.shape)  # noqa: E731
+        else:
+            input_grad = lambda: G.gemm_nn(dgu, w1).view(ctx.shape)  # noqa: E731
         if ctx.reduce_group is not None:
             # tensor parallel: the input gradient first, so that its all-reduce runs under both weight-gradient products
-            dx = G.gemm_nn(dgu, w1).view(ctx.shape)
+            dx = input_grad()
             pending = _start_grad_reduce(dx, ctx.reduce_group)
         dw2 = _deliver_grad(w2, lambda out, acc: G.gemm_tn(dy2, h, out=out, accumulate=acc))
         dw1 = _deliver_grad(w1, lambda out, acc: G.gemm_tn(dgu, x2, out=out, accumulate=acc))
         if ctx.reduce_group is None:
-            dx = G.gemm_nn(dgu, w1).view(ctx.shape)
+            dx = input_grad()
         elif pending is not None:
             pending.wait()
         return dx, dw1, dw2, (dy if ctx.has_res else None), None

@@ -292,8 +292,9 @@ class _MoEFFNFn(torch.autograd.Function):
         packed = bool(getattr(w1, "_ats_packed", False))  # serving: expert weights stored tile by tile (GenerationEngine)
         if packed and need_bwd:
             raise RuntimeError("expert weights are packed for serving; the backward pass needs the plain layout")
-        h = G.grouped_nt(xe, w1, counts, swiglu=True, pre_act=pre, packed=packed)
-        ye = G.grouped_nt(h, w2, counts, packed=packed)
+        from . import fp8  # the fp8 recipe (when switched on) runs both expert products and the input gradient in e4m3
+        h = fp8.grouped_nt(xe, w1, counts, swiglu=True, pre_act=pre)
+        ye = fp8.grouped_nt(h, w2, counts)
         out = combine(ye, topk_idx, slot_pos, topk_w, T, residual)
         ctx.save_for_backward(topk_idx, slot_pos, counts, topk_w, w1, w2, xe, pre, ye)
         ctx.capacity = capacity
@@ -319,7 +320,8 @@ class _MoEFFNFn(torch.autograd.Function):
             _CK(_L().ats_swiglu_bwd_grouped(_P(pre), _P(dh), _P(dgu), _P(h), E, C, _P(counts), inter, _S(pre.device)), "swiglu_bwd")
         dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(dye, h, counts, out=out, accumulate=acc))
         dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, xe, counts, out=out, accumulate=acc))
-        dxe = G.grouped_nn(dgu, w1, counts)
+        from . import fp8
+        dxe = fp8.grouped_nn(dgu, w1, counts)
         dx = combine(dxe, topk_idx, slot_pos, None, T, None)
         return dx, None, dw_topk, dw1, dw2, None, (dout if ctx.has_res else None)
 

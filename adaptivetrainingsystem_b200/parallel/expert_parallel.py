@@ -213,9 +213,10 @@ class _EPMoEFn(torch.autograd.Function):
         packed = bool(getattr(w1, "_ats_packed", False))  # serving: expert weights stored tile by tile
         if packed and need_bwd:
             raise RuntimeError("expert weights are packed for serving; the backward pass needs the plain layout")
-        h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, pre_act=pre, b_div=W, packed=packed)
+        from ..ops import fp8  # with the fp8 recipe on, the expert products (and the input gradient below) run in e4m3
+        h = fp8.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, pre_act=pre, b_div=W)
         if comm.fused and comm.pull_results:
-            G.grouped_nt(h, w2, buf.counts, b_div=W, out=buf.own_y, packed=packed)
+            fp8.grouped_nt(h, w2, buf.counts, b_div=W, out=buf.own_y)
             comm.barrier()
             out = M.combine(buf.ret_y, topk_idx, slot_pos, topk_w, T, residual, table=buf.t_pull_y, keep_copy=True)
         else:
@@ -258,7 +259,8 @@ class _EPMoEFn(torch.autograd.Function):
         dw2 = _deliver_grad(w2, lambda out, acc: G.grouped_tn(buf.recv_g, h, buf.counts, out=out, accumulate=acc, k_segs=W))
         dw1 = _deliver_grad(w1, lambda out, acc: G.grouped_tn(dgu, buf.recv_x, buf.counts, out=out, accumulate=acc, k_segs=W))
         if comm.fused and comm.pull_results:
-            G.grouped_nn(dgu, w1, buf.counts, b_div=W, out=buf.own_dx)
+            from ..ops import fp8
+            fp8.grouped_nn(dgu, w1, buf.counts, b_div=W, out=buf.own_dx)
             comm.barrier()
             dx = M.combine(buf.ret_dx, topk_idx, slot_pos, None, T, None, table=buf.t_pull_dx)
         else:

@@ -297,7 +297,7 @@ def run_ours(args) -> dict:
     res = {
         "metric": "moe_train_tokens_per_sec" if cfg.use_moe else "train_tokens_per_sec", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": (value / pub) if pub else None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": (value / pub) if pub else None, "dtype": "fp8+bf16" if "fp8" in str(cfg.precision) else "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {"model": args.config, "global_batch": mb * world * accum, "micro_batch_per_gpu": mb, "grad_accumulation": accum, "seq_len": L, "parallelism": mesh.describe() + f"+zero{cfg.zero_stage}",
                    "hidden": cfg.hidden_size, "layers": cfg.num_layers, "experts": cfg.num_experts if cfg.use_moe else 0,
@@ -307,7 +307,7 @@ def run_ours(args) -> dict:
                    "capacity_factor": cfg.capacity_factor if cfg.use_moe else None, "drop_tokens": bool(cfg.drop_tokens) if cfg.use_moe else None,
                    "dropped_slot_fraction": dropped_fraction, "lr_schedule_steps": args.warmup + 2 * args.steps + 1,
                    "loss_first": first_loss, "loss_last": last,
-                   **({"precision_note": "the preset names fp8; block-scaled fp8 training GEMMs are not built, every product of this run is bf16"}
+                   **({"precision_note": "e4m3 with per-token / per-channel scales for the forward and input-gradient products of every linear and expert; weight gradients, attention and the SwiGLU-backward product in bf16; fp32 accumulation, master weights and optimiser state"}
                       if "fp8" in str(cfg.precision) else {})},
         "clocks": clk.summary(),
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,

@@ -572,6 +572,92 @@ def test_fp8_linear_and_mlp_autograd():
     assert torch.allclose(q1.float() * s1[:, None], w.detach().float(), rtol=0.07, atol=1e-3)
 
 
+def test_fp8_grouped_expert_products():
+    """Grouped e4m3 products of the experts (ragged row counts, several row blocks per expert) against the product of the
+    dequantised operands, forward (SwiGLU + pre-activations, plain) and input gradient."""
+    from adaptivetrainingsystem_b200.ops import fp8
+    torch.manual_seed(17)
+    E, bdiv, C, K, I = 3, 2, 256, 512, 384
+    Gn = E * bdiv
+    x = _rand(Gn, C, K)
+    w1 = _rand(E, 2 * I, K) * 0.05
+    w2 = _rand(E, K, I) * 0.05
+    counts = torch.tensor([256, 100, 0, 129, 255, 1], dtype=torch.int32, device=DEV)
+    rows = torch.arange(C, device=DEV)[None, :] < counts[:, None]
+
+    def deq(t):
+        q, sc = fp8.quantize_rows_reference(t.reshape(-1, t.shape[-1]))
+        return (q.float() * sc[:, None]).view(t.shape)
+
+    fp8.set_enabled(True)
+    try:
+        pre = torch.zeros(Gn, C, 2 * I, dtype=torch.bfloat16, device=DEV)
+        h = fp8.grouped_nt(x, w1, counts, swiglu=True, pre_act=pre, b_div=bdiv)
+        y = fp8.grouped_nt(h, w2, counts, b_div=bdiv)
+        dxe = fp8.grouped_nn(pre, w1, counts, b_div=bdiv)      # any [G, C, 2I] tensor serves as the incoming gradient
+    finally:
+        fp8.set_enabled(False)
+    w1x, w2x = deq(w1).repeat_interleave(bdiv, 0), deq(w2).repeat_interleave(bdiv, 0)
+    gu = torch.einsum("gck,gnk->gcn", deq(x), w1x)
+    m = rows[..., None]
+    _close(torch.where(m, pre.float(), 0), torch.where(m, gu, 0), tol=1e-2, what="fp8 grouped pre-activations")
+    gq = gu.bfloat16().float()
+    href = torch.nn.functional.silu(gq[..., :I]) * gq[..., I:]
+    _close(torch.where(m, h.float(), 0), torch.where(m, href, 0), tol=2e-2, what="fp8 grouped swiglu")
+    yref = torch.einsum("gci,gki->gck", deq(torch.where(m, h, 0)), w2x)
+    _close(torch.where(m, y.float(), 0), torch.where(m, yref, 0), tol=1e-2, what="fp8 grouped down projection")
+    w1t = deq(w1.transpose(1, 2).contiguous()).repeat_interleave(bdiv, 0)          # [G, K, 2I], quantised per input channel
+    dref = torch.einsum("gcn,gkn->gck", deq(torch.where(m, pre, 0)), w1t)
+    _close(torch.where(m, dxe.float(), 0), torch.where(m, dref, 0), tol=1e-2, what="fp8 grouped input gradient")
+    ops.check_status()
+
+
+def test_fp8_recipe_tracks_bf16_training():
+    """20 optimiser steps of a small hybrid (MoE + Mixture-of-Depths + dense) model: the e4m3 recipe (forward and input-gradient
+    products) must follow the bf16 run's loss curve."""
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.ops import fp8
+    cfg = dict(vocab_size=1024, hidden_size=256, num_layers=4, num_heads=4, num_kv_heads=2, intermediate_size=512, seq_length=256,
+               use_moe=True, use_mod=True, num_experts=4, moe_top_k=2, capacity_factor=2.0, moe_pattern="every_2nd", mod_capacity_factor=0.5,
+               routing_noise_std=0.0, tie_word_embeddings=False)
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, 1024, (8, 257), generator=g).to(DEV)
+    curves = {}
+    for name in ("bf16", "fp8"):
+        torch.manual_seed(5)
+        with torch.device(DEV):
+            torch.set_default_dtype(torch.bfloat16)
+            model = DeepSeekTransformer(ModelConfig(**cfg))
+            torch.set_default_dtype(torch.float32)
+        master = [p.detach().float().clone() for p in model.parameters()]
+        opt = torch.optim.AdamW(master, lr=2e-3, weight_decay=0.0)
+        fp8.clear_weight_cache()
+        fp8.set_enabled(name == "fp8")
+        losses = []
+        try:
+            for _ in range(20):
+                out = model.forward_loss(ids[:, :-1], ids[:, 1:])
+                out["loss"].backward()
+                for m_, p in zip(master, model.parameters()):
+                    m_.grad = p.grad.float() if p.grad is not None else torch.zeros_like(m_)
+                    p.grad = None
+                opt.step()
+                with torch.no_grad():
+                    for m_, p in zip(master, model.parameters()):
+                        p.copy_(m_)
+                fp8.weights_changed()
+                losses.append(float(out["loss"]))
+        finally:
+            fp8.set_enabled(False)
+        curves[name] = losses
+    a, b = curves["bf16"], curves["fp8"]
+    assert a[-1] < a[0] - 1.0 and b[-1] < b[0] - 1.0, (a, b)
+    assert abs(a[0] - b[0]) < 0.05, (a[0], b[0])
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.15 * (a[0] - a[-1]) + 0.05, (a, b)   # stays within 15 % of the total descent
+    ops.check_status()
+
+
 def test_graph_decoder_matches_eager_decode():
     """CUDA-graph replay of the decode step against the eager cached decode on a small MoE model."""
     from adaptivetrainingsystem_b200.config import ModelConfig
