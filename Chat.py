@@ -86,6 +86,18 @@ class ChatInterface:
         self.history += [{"role": "user", "content": user_text}, {"role": "assistant", "content": text}]
         return text
 
+    def respond_many(self, user_texts, max_batch: int = 16):
+        """Independent single-turn prompts served together: continuous batching over ``max_batch`` cache rows (GPU only)."""
+        from adaptivetrainingsystem_b200.inference import ContinuousBatcher
+        saved, self.history = self.history, []
+        try:
+            prompts = [self._format_prompt(t)[0].tolist() for t in user_texts]
+        finally:
+            self.history = saved
+        rows = max(len(p) for p in prompts) + self.params.max_new_tokens
+        batcher = ContinuousBatcher(self.engine, max_batch=min(max_batch, len(prompts)), max_len=rows, params=self.params)
+        return [self.tokenizer.decode(t) for t in batcher.run(prompts)]
+
     def command(self, line: str) -> bool:
         cmd, *rest = line[1:].split()
         if cmd in ("quit", "exit"):
@@ -128,9 +140,16 @@ if __name__ == "__main__":
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--device", default="auto")
     ap.add_argument("--quantize", default=None, choices=["fp8"], help="post-training quantisation of the projection weights")
+    ap.add_argument("--prompts-file", default=None, help="one prompt per line, answered together by continuous batching")
+    ap.add_argument("--max-batch", type=int, default=16)
     a = ap.parse_args()
     chat = ChatInterface(a.checkpoint, a.device, a.mode, a.quantize)
-    if a.prompt:
+    if a.prompts_file:
+        with open(a.prompts_file) as f:
+            lines = [l.strip() for l in f if l.strip()]
+        for q, ans in zip(lines, chat.respond_many(lines, a.max_batch)):
+            print(f"> {q}\n{ans}\n")
+    elif a.prompt:
         print(chat.respond(a.prompt))
     else:
         chat.run()

@@ -1,1 +1,2 @@
 from .engine import GenerationEngine, SamplingParams, KVSlotManager, sample_next, GENERATION_MODES
+from .scheduler import ContinuousBatcher, Request

@@ -8,8 +8,9 @@ The reference's generator re-runs the whole context for every new token and has 
 * each decode step feeds one token per sequence: QKV GEMM -> RoPE at the cache offset -> attention of the single
   query against the cached K/V -> MoE FFN (router, dispatch, grouped SwiGLU GEMM, combine; expert-parallel ranks
   exchange the routed tokens through peer memory) -> next-token logits only for the last position;
-* a slot allocator (``KVSlotManager``) hands out cache rows for continuous batching (the vendored inference engine of
-  the reference keeps the same bookkeeping, ``colossalai/inference/kv_cache/kvcache_manager.py:11-106``).
+* a slot allocator (``KVSlotManager``) hands out cache rows to ``inference/scheduler.py: ContinuousBatcher``, which admits and
+  retires requests of any length between replays of one captured decode step (the vendored inference engine of the
+  reference keeps the same bookkeeping, ``colossalai/inference/kv_cache/kvcache_manager.py:11-106``).
 """
 from __future__ import annotations
 
