@@ -175,6 +175,8 @@ def run_ours(args) -> dict:
         over["seq_length"] = args.seq
     if args.accum:
         over["gradient_accumulation_steps"] = args.accum
+    if args.precision:
+        over["precision"] = args.precision
     cfg = ConfigPresets.get(args.config, num_workers=0, gradient_checkpointing=bool(args.checkpoint), **over)
     cfg.fused_comm = not args.nccl_only
     ep = math.gcd(cfg.num_experts, world) if cfg.use_moe else 1
@@ -365,6 +367,7 @@ def main():
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--accum", type=int, default=0)
     ap.add_argument("--checkpoint", type=int, default=0)
+    ap.add_argument("--precision", default="", help="override the preset's precision (e.g. mixed_bf16 for the bf16 twin of hybrid_fp8)")
     ap.add_argument("--nccl-only", action="store_true", help="baseline path: NCCL collectives instead of the fused peer-memory kernels")
     ap.add_argument("--no-decode", action="store_true", help="skip the serving half of the metric")
     ap.add_argument("--no-fused-check", action="store_true", help="skip the fused-vs-NCCL check that precedes a multi-GPU run")
