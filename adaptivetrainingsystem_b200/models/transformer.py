@@ -377,7 +377,8 @@ def _mod_select_cuda(scores: torch.Tensor, keep: int) -> torch.Tensor:
     if L > 8192:
         return torch.topk(scores, keep, dim=1).indices.sort(dim=1).values
     sel = torch.empty(B, keep, dtype=torch.int32, device=scores.device)
-    _CK(_L().ats_mod_select(_P(scores.contiguous().float()), _P(sel), B, L, keep, _S(scores.device)), "mod_select")
+    member = torch.empty(B * L, dtype=torch.int32, device=scores.device)
+    _CK(_L().ats_mod_select(_P(scores.contiguous().float()), _P(sel), _P(member), B, L, keep, _S(scores.device)), "mod_select")
     return sel
 
 

@@ -61,12 +61,13 @@ def _L():
         sig("ats_serve_plan_dispatch", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
         sig("ats_serve_combine", _vp, _vp, _c_ll, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _vp)
         sig("ats_slot_dot", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
-        sig("ats_mod_select", _vp, _vp, _c_int, _c_int, _c_int, _vp)
+        sig("ats_mod_select", _vp, _vp, _vp, _c_int, _c_int, _c_int, _vp)
         sig("ats_mod_scores", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_f, _vp)
         sig("ats_mod_gather", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _vp)
         sig("ats_mod_scatter", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _vp)
         sig("ats_mod_scatter_bwd", _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _vp)
         sig("ats_mod_route_bwd", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_f, _vp)
+        sig("ats_mod_wgrad_ctas")
         _sig_done = True
     return lib
 

@@ -38,7 +38,8 @@ class _RouteFn(torch.autograd.Function):
         bb = b.to(torch.bfloat16).contiguous() if b is not None else None
         _CK(lib.ats_mod_scores(_P(h2), _P(wb), _P(bb), _P(scores), B * L, H, float(inv_temp), st), "mod_scores")
         sel = torch.empty(B, keep, dtype=torch.int32, device=dev)
-        _CK(lib.ats_mod_select(_P(scores), _P(sel), B, L, keep, st), "mod_select")
+        member = torch.empty(B * L, dtype=torch.int32, device=dev)
+        _CK(lib.ats_mod_select(_P(scores), _P(sel), _P(member), B, L, keep, st), "mod_select")
         picked = torch.empty(B, keep, H, dtype=h.dtype, device=dev)
         weight = torch.empty(B, keep, dtype=torch.float32, device=dev)
         slot_of = torch.full((B * L,), -1, dtype=torch.int32, device=dev)
@@ -57,12 +58,13 @@ class _RouteFn(torch.autograd.Function):
         dev = h2.device
         dh = torch.empty_like(h2)
         ds = torch.empty(B * L, dtype=torch.float32, device=dev)
-        dwb = torch.zeros(H + 1, dtype=torch.float32, device=dev)  # router weight gradient, then the bias gradient
+        dwb = torch.empty(H + 1, dtype=torch.float32, device=dev)  # router weight gradient, then the bias gradient
+        partial = torch.empty(_L().ats_mod_wgrad_ctas() * (H + 8), dtype=torch.float32, device=dev)
         dp = dpicked.contiguous() if dpicked is not None else None
         dwt = dweight.contiguous().float() if dweight is not None else None
         da = daux.contiguous().float() if daux is not None else None
         _CK(_L().ats_mod_route_bwd(_P(h2), _P(dp), _P(slot_of), _P(scores), _P(dwt), _P(da), None, _P(wb), _P(dh), _P(ds), _P(dwb),
-                                   _P(dwb[H:]), B * L, H, ctx.inv_temp, _S(dev)), "mod_route_bwd")
+                                   _P(partial), B * L, H, ctx.inv_temp, _S(dev)), "mod_route_bwd")
         dw = dwb[:H].view(ctx.w_shape).to(ctx.w_dtype)
         db = dwb[H:].to(ctx.b_dtype) if ctx.has_bias else None
         return dh, dw, db, None, None

@@ -212,8 +212,10 @@ __device__ __forceinline__ void mma_16816_bf16(float (&c)[4], uint32_t a0, uint3
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int D, int REP>
-__global__ void __launch_bounds__(DEC_THREADS) decode_attn_mma_kernel(const DecodeArgs p) {
+// OCC: CTAs per SM the register allocation is cut for (2: 116 registers, no spills; 3: 80 registers, about 240 bytes of spills
+// but half again as many loads in flight).
+template <int D, int REP, int OCC = 2>
+__global__ void __launch_bounds__(DEC_THREADS, OCC) decode_attn_mma_kernel(const DecodeArgs p) {
   static_assert(REP <= 8 && D % 32 == 0, "query heads of a group sit in rows 0..7 of the MMA");
   __shared__ float s_p[REP][DEC_CHUNK];
   __shared__ __align__(16) float s_red[DEC_THREADS / 32][REP][D];
@@ -663,14 +665,18 @@ using namespace ats;
 
 // 1 (default): warp-level tensor-core kernel; 0: the fp32 CUDA-core kernel (kept for comparison, ATS_DECODE_ATTN_MMA=0)
 static int g_decode_mma = -1;
+static int g_decode_occ = 2;  // ATS_DECODE_ATTN_OCC=3 selects the 80-register build of the tensor-core kernel
 template <int D, int REP>
 static int launch_decode(const DecodeArgs& p, cudaStream_t s) {
   if (g_decode_mma < 0) {
     const char* e = getenv("ATS_DECODE_ATTN_MMA");
     g_decode_mma = (e && e[0] == '0') ? 0 : 1;
+    const char* o = getenv("ATS_DECODE_ATTN_OCC");
+    if (o && o[0] == '3') g_decode_occ = 3;
   }
   dim3 grid(p.n_chunks, p.Hkv, p.B);
-  if (g_decode_mma) decode_attn_mma_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
+  if (g_decode_mma && g_decode_occ == 3) decode_attn_mma_kernel<D, REP, 3><<<grid, DEC_THREADS, 0, s>>>(p);
+  else if (g_decode_mma) decode_attn_mma_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
   else decode_attn_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
   return int(cudaGetLastError());
 }

@@ -1,7 +1,7 @@
 // Mixture-of-Depths token routing for training: router scores, selection bookkeeping, row gather, weighted scatter-add and
 // their backward passes.  All of it is memory-bound row movement around the dense SwiGLU GEMMs of the selected tokens:
 //   forward   scores[t] = (h[t] . w + b) / temperature                      (one pass over h, warp per token)
-//             sel = the `keep` best positions of every sequence, ascending  (mod_select_kernel in moe.cu)
+//             sel = the `keep` best positions of every sequence, ascending  (mod_rank_kernel + mod_compact_kernel in moe.cu)
 //             picked[j] = h[token(j)], weight[j] = sigmoid(scores[token(j)]), slot_of[token(j)] = j
 //             aux = mean binary cross-entropy of sigmoid(scores) against membership in the selected set
 //             out[t] = base[t] + (slot_of[t] >= 0 ? weight[slot] * y[slot] : 0)
@@ -182,15 +182,17 @@ mod_route_bwd_kernel(const __nv_bfloat16* __restrict__ dpicked, const int* __res
 }
 
 // ---- router weight gradient: dw[c] = sum_t ds[t] h[t, c], db = sum_t ds[t] ------------------------------------------------------
-// Every CTA walks `rows_per_cta` tokens; a thread owns 8 columns (looping when hidden > 8 * blockDim) and adds its partial
-// sums into the fp32 result (zeroed by the caller) with one atomic per column per CTA.
+// Every CTA walks a contiguous run of tokens; a thread owns 8 columns (looping when hidden > 8 * blockDim) and writes its sums into
+// the CTA's row of `partial` [gridDim.x, hidden + 8] (column `hidden` holds the CTA's sum of ds); a second launch adds the rows up.
 __global__ void __launch_bounds__(256)
-mod_router_wgrad_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ ds, float* __restrict__ dw, float* __restrict__ db,
-                        long long tokens, int hidden, int rows_per_cta) {
+mod_router_wgrad_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ ds, float* __restrict__ partial, long long tokens,
+                        int hidden, int rows_per_cta) {
   const long long t0 = (long long)blockIdx.x * rows_per_cta;
   const long long t1 = t0 + rows_per_cta < tokens ? t0 + rows_per_cta : tokens;
+  float* prow = partial + (long long)blockIdx.x * (hidden + 8);
   for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
     for (long long t = t0; t < t1; ++t) {
       const float d = ds[t];
       const uint4 p = reinterpret_cast<const uint4*>(h + t * hidden)[c];
@@ -198,14 +200,23 @@ mod_router_wgrad_kernel(const __nv_bfloat16* __restrict__ h, const float* __rest
       acc[0] += d * p0.x; acc[1] += d * p0.y; acc[2] += d * p1.x; acc[3] += d * p1.y;
       acc[4] += d * p2.x; acc[5] += d * p2.y; acc[6] += d * p3.x; acc[7] += d * p3.y;
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) atomicAdd(dw + c * 8 + i, acc[i]);
+    *reinterpret_cast<float4*>(prow + c * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(prow + c * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
-  if (threadIdx.x == 0 && db) {
+  if (threadIdx.x == 0) {
     float s = 0.f;
     for (long long t = t0; t < t1; ++t) s += ds[t];
-    atomicAdd(db, s);
+    prow[hidden] = s;
   }
+}
+
+__global__ void __launch_bounds__(256)
+mod_colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int width, int pitch) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  float s = 0.f;
+  for (int r = 0; r < rows; ++r) s += partial[(long long)r * pitch + c];
+  out[c] = s;
 }
 
 }  // namespace ats
@@ -262,9 +273,11 @@ ATS_API int ats_mod_scatter_bwd(const void* dout, const void* y, const int* sel,
   return int(cudaGetLastError());
 }
 
-// dw (hidden floats) and db (one float) must be zero on entry; dpicked, dweight, daux, dscores_ext may each be null.
+// dwb: hidden + 1 floats (router weight gradient, then the bias gradient); partial: scratch of ats_mod_wgrad_ctas() * (hidden + 8)
+// floats; dpicked, dweight, daux, dscores_ext may each be null.
+ATS_API int ats_mod_wgrad_ctas() { return 296; }
 ATS_API int ats_mod_route_bwd(const void* h, const void* dpicked, const int* slot_of, const float* scores, const float* dweight,
-                              const float* daux, const float* dscores_ext, const void* w, void* dh, float* ds, float* dw, float* db,
+                              const float* daux, const float* dscores_ext, const void* w, void* dh, float* ds, float* dwb, float* partial,
                               long long tokens, int hidden, float inv_temp, void* stream) {
   if ((hidden & 7) || hidden > kModMaxHidden) return 1003;
   if (tokens == 0) return 0;
@@ -272,8 +285,10 @@ ATS_API int ats_mod_route_bwd(const void* h, const void* dpicked, const int* slo
   mod_route_bwd_kernel<<<warp_grid(tokens, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dpicked), slot_of, scores, dweight,
                                                                    daux, dscores_ext, static_cast<const __nv_bfloat16*>(w),
                                                                    static_cast<__nv_bfloat16*>(dh), ds, tokens, hidden, inv_temp);
-  const int rows = 64;
-  mod_router_wgrad_kernel<<<unsigned((tokens + rows - 1) / rows), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(h), ds, dw, db, tokens,
-                                                                               hidden, rows);
+  const int ctas = int(tokens < 296 ? tokens : 296);
+  const int rows = int((tokens + ctas - 1) / ctas);
+  const int used = int((tokens + rows - 1) / rows);
+  mod_router_wgrad_kernel<<<used, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(h), ds, partial, tokens, hidden, rows);
+  mod_colsum_kernel<<<(hidden + 1 + 255) / 256, 256, 0, s>>>(partial, dwb, used, hidden + 1, hidden + 8);
   return int(cudaGetLastError());
 }

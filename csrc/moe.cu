@@ -595,41 +595,46 @@ slot_dot_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restri
   if (lane == 0) dw[w] = acc;
 }
 
-// Per-sequence top-k token selection for Mixture-of-Depths: scores[b, l] -> the `keep` largest per sequence,
-// emitted in ascending position order (so causal attention / RoPE positions stay ordered).  One CTA per
-// sequence, rank by counting (L <= 8192).  sel[b, i] = position, i < keep.
-__global__ void __launch_bounds__(1024)
-mod_select_kernel(const float* __restrict__ scores, int* __restrict__ sel, int seq_len, int keep) {
+// Per-sequence top-k token selection for Mixture-of-Depths: scores[b, l] -> the `keep` largest per sequence, emitted in
+// ascending position order (so causal attention / RoPE positions stay ordered), L <= 8192.  Two launches: (1) rank by counting,
+// a CTA per 256 positions of a sequence with the whole sequence's scores in shared memory (ties go to the earlier position);
+// (2) ordered compaction of the membership flags, one CTA per sequence.  sel[b, i] = position, i < keep.
+__global__ void __launch_bounds__(256)
+mod_rank_kernel(const float* __restrict__ scores, int* __restrict__ member, int seq_len, int keep) {
   extern __shared__ float s_sc[];
-  int* s_flag = reinterpret_cast<int*>(s_sc + seq_len);
-  const float* sc = scores + (long long)blockIdx.x * seq_len;
+  const float* sc = scores + (long long)blockIdx.y * seq_len;
   for (int i = threadIdx.x; i < seq_len; i += blockDim.x) s_sc[i] = sc[i];
   __syncthreads();
-  for (int i = threadIdx.x; i < seq_len; i += blockDim.x) {
-    const float v = s_sc[i];
-    int rank = 0;
-    for (int j = 0; j < seq_len; ++j) {
-      const float o = s_sc[j];
-      rank += (o > v) || (o == v && j < i);
-    }
-    s_flag[i] = rank < keep;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= seq_len) return;
+  const float v = s_sc[i];
+  int rank = 0;
+#pragma unroll 8
+  for (int j = 0; j < seq_len; ++j) {
+    const float o = s_sc[j];
+    rank += (o > v) || (o == v && j < i);
   }
-  __syncthreads();
-  // ordered compaction: thread 0 of each warp-sized segment would be slow; use a simple block scan over chunks
+  member[(long long)blockIdx.y * seq_len + i] = rank < keep;
+}
+
+__global__ void __launch_bounds__(1024)
+mod_compact_kernel(const int* __restrict__ member, int* __restrict__ sel, int seq_len, int keep) {
   __shared__ int s_base;
+  __shared__ int wsum[32];
+  const int* flag = member + (long long)blockIdx.x * seq_len;
   if (threadIdx.x == 0) s_base = 0;
   __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int base = 0; base < seq_len; base += blockDim.x) {
     const int i = base + threadIdx.x;
-    const int f = i < seq_len ? s_flag[i] : 0;
+    const int f = i < seq_len ? flag[i] : 0;
     const unsigned mask = __ballot_sync(0xffffffffu, f);
-    __shared__ int wsum[32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) wsum[warp] = __popc(mask);
     __syncthreads();
     int before = s_base;
     for (int w = 0; w < warp; ++w) before += wsum[w];
-    if (f) sel[(long long)blockIdx.x * keep + before + __popc(mask & ((1u << lane) - 1u))] = i;
+    const int pos = before + __popc(mask & ((1u << lane) - 1u));
+    if (f && ATS_DBG_CHECK(pos < keep, kDbgModRows, i)) sel[(long long)blockIdx.x * keep + pos] = i;
     __syncthreads();
     if (threadIdx.x == 0) {
       int tot = 0;
@@ -789,9 +794,12 @@ ATS_API int ats_slot_dot(void* const* src_base, const int* topk_idx, const int* 
   return int(cudaGetLastError());
 }
 
-ATS_API int ats_mod_select(const float* scores, int* sel, int batch, int seq_len, int keep, void* stream) {
-  if (seq_len > 8192 || keep > seq_len) return 1003;
+// member: batch * seq_len ints of scratch (the membership flags; left filled for the caller).
+ATS_API int ats_mod_select(const float* scores, int* sel, int* member, int batch, int seq_len, int keep, void* stream) {
+  if (seq_len > 8192 || keep > seq_len || !member) return 1003;
   if (batch == 0) return 0;
-  mod_select_kernel<<<batch, 1024, seq_len * 8, static_cast<cudaStream_t>(stream)>>>(scores, sel, seq_len, keep);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  mod_rank_kernel<<<dim3((seq_len + 255) / 256, batch), 256, seq_len * 4, s>>>(scores, member, seq_len, keep);
+  mod_compact_kernel<<<batch, 1024, 0, s>>>(member, sel, seq_len, keep);
   return int(cudaGetLastError());
 }
