@@ -1149,6 +1149,9 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   if (b_shards < 1 || my_rank < 0 || my_rank >= b_shards || ready_rows < 64 || calls < 1) return 1002;
   if (((long long)ready_rows * K * 2) % 4096) return 1003;
   if ((N & 7) || (K & 7) || (ldd & 7) || (b_rows % b_shards) || ((b_rows / b_shards) % ready_rows)) return 1003;
+  // B is read in 128-row boxes, each either from this rank's shard in place or from the staging buffer, which holds the remote
+  // shards only: a shard boundary inside a box is not representable
+  if (b_shards > 1 && (b_rows / b_shards) % 128) return 1003;
   if (epilogue == kF32 || (epilogue == kSwiGLU && (up_offset & 7))) return 1004;
   CUtensorMap ma, mb;
   int e;
