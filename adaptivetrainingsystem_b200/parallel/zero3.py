@@ -72,9 +72,9 @@ class Matrix:
                 and param.shape[1] % 8 == 0)
 
     def fused_forward_ok(self) -> bool:
-        # the gathering GEMM reads 128-row boxes of the weight either from this rank's shard in place or from the staging buffer
-        # (remote shards only): a shard boundary inside a box would read rows that neither holds, so shards must be whole boxes
-        return self.rows % 128 == 0 and self.K % 32 == 0 and self.N >= 128
+        # shards of whole 64-row chunks; when a shard begins or ends inside one of the 128-row boxes the GEMM reads, the kernel
+        # stages that edge chunk of the own shard next to the remote ones
+        return self.rows % 64 == 0 and self.K % 32 == 0 and self.N >= 128
 
 
 class BlockUnit:

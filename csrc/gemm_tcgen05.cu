@@ -79,6 +79,9 @@ struct GemmArgs {
   uint8_t* b_dst;
   int* b_ready;
   int ready_rows, n_chunks, epoch, first_chunk, n_rot;
+  // own chunks whose 128-row box is not entirely inside this rank's shard (a shard of 64-row chunks can begin or end in the
+  // middle of a box): they are copied into the staging buffer like remote chunks and their boxes are read from there
+  int n_edge, edge_chunk[2];
   int own_row0, own_rows;    // rows of B that live in this rank's shard (read through map_b_own)
   long long* prof;           // optional [8]: cycle totals of CTA 0's MMA thread (total, wait for stage, wait for accumulator, issue, k-blocks)
   // kSwiGLUBwd: the product is dh (gradient of h = silu(gate) * up); `aux` holds the saved pre-activations [gate | up] (read),
@@ -163,11 +166,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmArgs& p, const int* p
 __device__ __forceinline__ void copy_remote_shards(const GemmArgs& p, int copy_warp, int lane) {
   const long long cps = p.shard_bytes / p.chunk_bytes;
   const long long per_chunk = p.chunk_bytes / 4096;
-  const long long total = (long long)(p.n_chunks - cps) * per_chunk;
+  const long long total = (long long)(p.n_chunks - cps + p.n_edge) * per_chunk;
   const int own_hi = p.first_chunk + int(cps);
   for (long long i = copy_warp + 2LL * blockIdx.x; i < total; i += 2LL * gridDim.x) {
     const long long ci = i / per_chunk, pi = i - ci * per_chunk;
-    const int chunk = int((own_hi + ci) % p.n_chunks);
+    // the edge chunks of the own shard first (the first tiles read them), then the remote chunks in the order of the tiles
+    const int chunk = ci < p.n_edge ? p.edge_chunk[ci] : int((own_hi + (ci - p.n_edge)) % p.n_chunks);
     const long long off = (chunk % cps) * p.chunk_bytes + pi * 4096 + lane * 16;
     const uint8_t* src = static_cast<const uint8_t*>(p.b_src[chunk / cps]) + off;
     uint8_t* dst = p.b_dst + (long long)chunk * p.chunk_bytes + pi * 4096 + lane * 16;
@@ -191,7 +195,9 @@ struct ChunkRange {
 __device__ __forceinline__ bool wait_chunk(const GemmArgs& p, ChunkRange& r, int c, volatile int* abort_flag) {
   if (c >= p.n_chunks) c = p.n_chunks - 1;
   if (c >= r.lo && c <= r.hi) return true;
-  if (c >= p.first_chunk && c < p.first_chunk + int(p.shard_bytes / p.chunk_bytes)) return true;  // own shard: read in place
+  if (c >= p.first_chunk && c < p.first_chunk + int(p.shard_bytes / p.chunk_bytes) &&
+      !((p.n_edge > 0 && c == p.edge_chunk[0]) || (p.n_edge > 1 && c == p.edge_chunk[1])))
+    return true;  // own shard, whole box inside it: read in place
   const uint64_t t0 = globaltimer_ns();
   int v;
   do {
@@ -571,9 +577,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (p.n_copy) {
               // gathered B: rows of this rank's own shard are read in place, the others from the staging buffer
               const int o0 = b_mn_c - p.own_row0, o1 = second - p.own_row0;
-              if (o0 >= 0 && o0 < p.own_rows) tma_load_2d(b_dst, &map_b_own, &full[stage], k0, o0);
+              if (o0 >= 0 && o0 + 128 <= p.own_rows) tma_load_2d(b_dst, &map_b_own, &full[stage], k0, o0);
               else tma_load_2d(b_dst, &map_b, &full[stage], k0, b_mn_c);
-              if (o1 >= 0 && o1 < p.own_rows) tma_load_2d(b_dst + 128 * 128, &map_b_own, &full[stage], k0, o1);
+              if (o1 >= 0 && o1 + 128 <= p.own_rows) tma_load_2d(b_dst + 128 * 128, &map_b_own, &full[stage], k0, o1);
               else tma_load_2d(b_dst + 128 * 128, &map_b, &full[stage], k0, second);
             } else if (p.b_packed) {
               const int kb_idx = (k0 + k_off) >> 6;
@@ -795,7 +801,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           ok = wait_chunk(p, ready, b_mn_c / p.ready_rows, abort_flag) && wait_chunk(p, ready, (b_mn_c + 127) / p.ready_rows, abort_flag);
           if (!ok) break;
           const int o = b_mn_c - p.own_row0;
-          if (o >= 0 && o < p.own_rows) {
+          if (o >= 0 && o + 128 <= p.own_rows) {  // the whole box lies in this rank's shard
             bmap = &map_b_own;
             b_row = o;
           }
@@ -1050,6 +1056,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
   p.b_div = b_div; p.k_segs = k_segs; p.seg_stride = seg_stride; p.d_table = d_table; p.k_split = k_split; p.scatter_rows = scatter_rows;
   p.fp8 = 0; p.row_scale = nullptr; p.col_scale = nullptr; p.rs_gs = 0; p.cs_gs = 0;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = g_gemm_prof;
+  p.n_edge = 0; p.edge_chunk[0] = p.edge_chunk[1] = -1;
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
   if (epilogue == kSwiGLUBwd) {
     // second output (h) travels in the C slot of this entry point: C / ldc / c_gs
@@ -1129,6 +1136,7 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.b_packed = 0; p.b_kblocks = 0;
   p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
+  p.n_edge = 0; p.edge_chunk[0] = p.edge_chunk[1] = -1;
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
 }
@@ -1149,9 +1157,7 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   if (b_shards < 1 || my_rank < 0 || my_rank >= b_shards || ready_rows < 64 || calls < 1) return 1002;
   if (((long long)ready_rows * K * 2) % 4096) return 1003;
   if ((N & 7) || (K & 7) || (ldd & 7) || (b_rows % b_shards) || ((b_rows / b_shards) % ready_rows)) return 1003;
-  // B is read in 128-row boxes, each either from this rank's shard in place or from the staging buffer, which holds the remote
-  // shards only: a shard boundary inside a box is not representable
-  if (b_shards > 1 && (b_rows / b_shards) % 128) return 1003;
+  if (ready_rows != 64 && ready_rows % 128) return 1003;  // chunks are halves or multiples of the 128-row boxes B is read in
   if (epilogue == kF32 || (epilogue == kSwiGLU && (up_offset & 7))) return 1004;
   CUtensorMap ma, mb;
   int e;
@@ -1176,6 +1182,12 @@ ATS_API int ats_gemm_bf16_gathered(const void* A, long long lda, const void* B_l
   p.epoch = int(calls * (p.chunk_bytes / 4096));  // every call adds chunk_bytes / 4096 to each remote chunk's counter
   p.first_chunk = int(my_rank * (shard_rows / ready_rows));
   p.own_row0 = int(my_rank * shard_rows); p.own_rows = int(shard_rows); p.prof = nullptr;
+  p.n_edge = 0; p.edge_chunk[0] = p.edge_chunk[1] = -1;
+  if (b_shards > 1 && ready_rows == 64) {
+    const int cps = int(shard_rows / ready_rows);
+    if (p.own_row0 % 128) p.edge_chunk[p.n_edge++] = p.first_chunk;
+    if ((p.own_row0 + p.own_rows) % 128 && !(p.n_edge && cps == 1)) p.edge_chunk[p.n_edge++] = p.first_chunk + cps - 1;
+  }
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
   const int tile_w = epilogue == kSwiGLU ? 128 : BN;
   p.n_rot = int((my_rank * shard_rows) % (epilogue == kSwiGLU ? (long long)up_offset : b_rows) / tile_w);
