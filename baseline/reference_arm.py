@@ -137,10 +137,11 @@ def run(args, published) -> dict:
     dev = torch.device("cuda", local)
     shape = dict(SHAPES[args.config])
     mb, accum = shape.pop("micro_batch"), shape.pop("accum")
-    if world > 1 and args.config == "b1_moe" and not args.layers:
-        # the micro-batch the reference's single-GPU run settles at after its out-of-memory halving (8 -> 2, same tokens per
-        # step); ranks of a multi-GPU job cannot halve independently without desynchronising their collectives
-        mb, accum = 2, 16
+    if world > 1 and args.config in ("b1_moe", "dense_1b") and not args.layers and mb > 2:
+        # the micro-batch the reference's single-GPU run settles at after its out-of-memory halving (8 -> 2: its attention keeps
+        # the [heads, L, L] score tensors of every layer for the backward pass), with the accumulation raised so that the tokens
+        # per step stay the same; ranks of a multi-GPU job cannot halve independently without desynchronising their collectives
+        mb, accum = 2, accum * (mb // 2)
     if args.micro_batch:
         mb = args.micro_batch
     if args.accum:
