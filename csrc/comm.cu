@@ -44,6 +44,7 @@ static unsigned long long g_wait_budget_ns = ATS_WAIT_BUDGET_NS;
 // [MAX_PEERS] counts the calls -- how much of a step is spent waiting at barriers, and for whom, without a profiler.
 __global__ void peer_barrier_kernel(PeerPtrs flags, PeerPtrs payload_dst, const float* payload_src, int rank, int world,
                                     int* epoch_counter, unsigned long long budget_ns, int* status, long long* wait_ns) {
+  pdl_prologue();
   const int t = threadIdx.x;
   int epoch = 0;
   if (t == 0) {
@@ -301,11 +302,10 @@ ATS_API int ats_peer_barrier(void* const* flags, void* const* payload_dst, const
                              int* epoch_counter, int* status, long long* wait_ns, void* stream) {
   if (world > MAX_PEERS || !epoch_counter) return 1003;
   PeerPtrs none = {};
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(flags, world),
-                                                                      payload_dst ? to_peers(payload_dst, world) : none,
-                                                                      payload_src, rank, world, epoch_counter, g_wait_budget_ns,
-                                                                      status, wait_ns);
-  return int(cudaGetLastError());
+  cudaError_t ce = launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), to_peers(flags, world),
+                              payload_dst ? to_peers(payload_dst, world) : none, payload_src, rank, world, epoch_counter,
+                              (unsigned long long)g_wait_budget_ns, status, wait_ns);
+  return int(ce != cudaSuccess ? ce : cudaGetLastError());
 }
 
 // Budget of every peer wait launched after this call (0 restores the default of one second).

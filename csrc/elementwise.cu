@@ -18,6 +18,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd, int cols, float eps) {
   __shared__ float red[33];
+  pdl_prologue();
   const long long row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
   const uint4* rr = res ? reinterpret_cast<const uint4*>(res + row * cols) : nullptr;
@@ -261,6 +262,7 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const float* __rest
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, const int* __restrict__ pos, int tokens, int seq_len,
                             int pos_offset, int row_stride, int col_offset, int n_heads, int d, float sign) {
+  pdl_prologue();
   const int half = d >> 1;
   const int vec_per_head = half >> 3;  // 8 pairs per 16-byte vector
   const long long total = (long long)tokens * n_heads * vec_per_head;
@@ -358,6 +360,7 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 // ------------------------------------------------------------------------------------------------
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, long long tokens, int hidden, int vocab, float scale) {
+  pdl_prologue();
   const int vpr = hidden >> 3;
   const long long total = tokens * vpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -447,6 +450,11 @@ ATS_API int ats_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto S = static_cast<__nv_bfloat16*>(sum_out);
   if (rows == 0) return 0;
+  if (rows <= 1024 && cols <= 256 * 32) {  // decode-sized: the launch overlaps the tail of the kernel before it
+    cudaError_t ce = cols <= 128 * 32 ? launch_pdl(rmsnorm_fwd_kernel<128>, dim3((unsigned)rows), dim3(128), 0, s, X, R, W, Y, S, rstd, cols, eps)
+                                      : launch_pdl(rmsnorm_fwd_kernel<256>, dim3((unsigned)rows), dim3(256), 0, s, X, R, W, Y, S, rstd, cols, eps);
+    return int(ce != cudaSuccess ? ce : cudaGetLastError());
+  }
   if (cols <= 128 * 32) rmsnorm_fwd_kernel<128><<<(unsigned)rows, 128, 0, s>>>(X, R, W, Y, S, rstd, cols, eps);
   else if (cols <= 256 * 32) rmsnorm_fwd_kernel<256><<<(unsigned)rows, 256, 0, s>>>(X, R, W, Y, S, rstd, cols, eps);
   else if (cols <= 512 * 32) rmsnorm_fwd_kernel<512><<<(unsigned)rows, 512, 0, s>>>(X, R, W, Y, S, rstd, cols, eps);
@@ -507,6 +515,12 @@ ATS_API int ats_rope(void* buf, const float* cos_t, const float* sin_t, const in
   if ((d & 15) || (row_stride & 7) || (col_offset & 7)) return 1003;
   const long long work = tokens * n_heads * (d >> 4);
   if (work == 0) return 0;
+  if (tokens <= 1024) {
+    cudaError_t ce = launch_pdl(rope_kernel, dim3(grid_for(work, 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                static_cast<__nv_bfloat16*>(buf), cos_t, sin_t, pos, (int)tokens, seq_len, pos_offset, row_stride,
+                                col_offset, n_heads, d, inverse ? -1.f : 1.f);
+    return int(ce != cudaSuccess ? ce : cudaGetLastError());
+  }
   rope_kernel<<<grid_for(work, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(buf), cos_t, sin_t, pos, (int)tokens, seq_len, pos_offset, row_stride, col_offset, n_heads, d,
       inverse ? -1.f : 1.f);
@@ -548,6 +562,11 @@ ATS_API int ats_embedding_fwd(const long long* ids, const void* table, void* out
                               float scale, void* stream) {
   if (hidden & 7) return 1003;
   if (tokens == 0) return 0;
+  if (tokens <= 1024) {
+    cudaError_t ce = launch_pdl(embedding_fwd_kernel, dim3(grid_for(tokens * (hidden >> 3), 256)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), tokens, hidden, vocab, scale);
+    return int(ce != cudaSuccess ? ce : cudaGetLastError());
+  }
   embedding_fwd_kernel<<<grid_for(tokens * (hidden >> 3), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), tokens, hidden, vocab, scale);
   return int(cudaGetLastError());

@@ -468,6 +468,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_b_own, const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_prologue();  // decode-sized products are launched programmatically dependent on the kernel before them
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
@@ -1072,6 +1073,7 @@ ATS_API int ats_gemm_bf16(const void* A, long long a_rows, long long a_cols, lon
 namespace ats {
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, long long n_inner, long long n_outer,
                                                             __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ add) {
+  pdl_prologue();
   const long long nvec = n_inner >> 3, total = nvec * n_outer;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
     const long long o = v / nvec, i = (v - o * nvec) << 3;
@@ -1096,10 +1098,9 @@ ATS_API int ats_splitk_reduce(const float* part, int splits, long long n_inner, 
   if (splits < 1 || n_inner <= 0 || n_outer <= 0 || (n_inner & 7)) return 1003;
   long long blocks = ((n_inner >> 3) * n_outer + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  splitk_reduce_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(part, splits, n_inner, n_outer,
-                                                                                       static_cast<__nv_bfloat16*>(out),
-                                                                                       static_cast<const __nv_bfloat16*>(add));
-  return int(cudaGetLastError());
+  cudaError_t ce = launch_pdl(splitk_reduce_kernel, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream), part, splits,
+                              n_inner, n_outer, static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(add));
+  return int(ce != cudaSuccess ? ce : cudaGetLastError());
 }
 
 // fp8 (e4m3) A [groups x M, K] and B [weights x N, K], both K-major and row-quantised: D = (A_q B_q^T) * row_scale * col_scale.
@@ -1257,6 +1258,12 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     grid = int(upper);
   }
   if (grid < 1) return 0;
+  if (M <= BM && p.n_copy == 0) {
+    // a product of a decode step: its launch overlaps the tail of the kernel before it
+    cudaError_t ce = launch_pdl(gemm_bf16_kernel, dim3(grid), dim3(GEMM_THREADS - 64), GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream), ma, mb,
+                                mb_own ? *mb_own : mb, p);
+    return int(ce != cudaSuccess ? ce : cudaGetLastError());
+  }
   // the two copy warps exist only in launches that gather B from peers
   gemm_bf16_kernel<<<grid, p.n_copy ? GEMM_THREADS : GEMM_THREADS - 64, GEMM_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
       ma, mb, mb_own ? *mb_own : mb, p);

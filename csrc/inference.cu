@@ -216,6 +216,7 @@ __device__ __forceinline__ void mma_16816_bf16(float (&c)[4], uint32_t a0, uint3
 // but half again as many loads in flight).
 template <int D, int REP, int OCC = 2>
 __global__ void __launch_bounds__(DEC_THREADS, OCC) decode_attn_mma_kernel(const DecodeArgs p) {
+  pdl_prologue();
   static_assert(REP <= 8 && D % 32 == 0, "query heads of a group sit in rows 0..7 of the MMA");
   __shared__ float s_p[REP][DEC_CHUNK];
   __shared__ __align__(16) float s_red[DEC_THREADS / 32][REP][D];
@@ -362,6 +363,7 @@ __global__ void __launch_bounds__(DEC_THREADS, OCC) decode_attn_mma_kernel(const
 // one warp per (sequence, query head): merge the chunk partials
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int BH, int n_chunks, int D) {
+  pdl_prologue();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= BH) return;
   const float* ml = part_ml + (long long)w * n_chunks * 2;
@@ -403,6 +405,7 @@ struct SampleArgs {
 };
 
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const SampleArgs p) {
+  pdl_prologue();
   __shared__ float red[33];
   __shared__ int s_arg, s_pick;
   __shared__ float s_scan[SMP_THREADS / 32 + 1];
@@ -541,6 +544,7 @@ constexpr int SRV_MAX_E = 64, SRV_MAX_K = 8;
 __global__ void __launch_bounds__(256) serve_gate_route_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg,
                                                                int* __restrict__ topk_idx, float* __restrict__ topk_w, int hidden,
                                                                int experts, int k, float inv_temp) {
+  pdl_prologue();
   __shared__ float s_logit[SRV_MAX_E];
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)t * hidden);
@@ -597,6 +601,7 @@ __global__ void __launch_bounds__(256) serve_plan_dispatch_kernel(const __nv_bfl
                                                                   int* __restrict__ totals, __nv_bfloat16* const* __restrict__ dst_table,
                                                                   __nv_bfloat16* dst0, long long dst_stride, int slots, int k, int hidden,
                                                                   int experts, int capacity) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // this warp's slot
   if (blockIdx.x == 0 && (counts || totals)) {
@@ -633,6 +638,7 @@ __global__ void __launch_bounds__(256) serve_combine_kernel(__nv_bfloat16* const
                                                             const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
                                                             const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int k,
                                                             int hidden) {
+  pdl_prologue();
   const int t = blockIdx.x;
   const int nvec = hidden >> 3;
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
@@ -676,7 +682,10 @@ static int launch_decode(const DecodeArgs& p, cudaStream_t s) {
   }
   dim3 grid(p.n_chunks, p.Hkv, p.B);
   if (g_decode_mma && g_decode_occ == 3) decode_attn_mma_kernel<D, REP, 3><<<grid, DEC_THREADS, 0, s>>>(p);
-  else if (g_decode_mma) decode_attn_mma_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
+  else if (g_decode_mma) {
+    cudaError_t ce = launch_pdl(decode_attn_mma_kernel<D, REP, 2>, grid, dim3(DEC_THREADS), 0, s, p);
+    return int(ce != cudaSuccess ? ce : cudaGetLastError());
+  }
   else decode_attn_kernel<D, REP><<<grid, DEC_THREADS, 0, s>>>(p);
   return int(cudaGetLastError());
 }
@@ -712,7 +721,7 @@ ATS_API int ats_decode_attn(const void* qkv, long long ld_qkv, int q_col0, int k
 #undef ATS_DEC
   if (e) return e;
   const int BH = B * Hq;
-  decode_merge_kernel<<<(BH * 32 + 255) / 256, 256, 0, s>>>(part_o, part_ml, p.out, BH, p.n_chunks, D);
+  launch_pdl(decode_merge_kernel, dim3((BH * 32 + 255) / 256), dim3(256), 0, s, (const float*)part_o, (const float*)part_ml, p.out, BH, p.n_chunks, D);
   return int(cudaGetLastError());
 }
 
@@ -727,7 +736,7 @@ ATS_API int ats_sample(const void* logits, int logits_fp32, long long ld, float*
   p.history = history; p.hist_len = hist_len; p.hist_ld = hist_ld;
   p.uniform = uniform; p.out = out; p.V = V;
   p.temperature = temperature; p.top_p = top_p; p.rep_penalty = rep_penalty; p.top_k = top_k;
-  sample_kernel<<<B, SMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  launch_pdl(sample_kernel, dim3(B), dim3(SMP_THREADS), 0, static_cast<cudaStream_t>(stream), p);
   return int(cudaGetLastError());
 }
 
@@ -735,8 +744,8 @@ ATS_API int ats_sample(const void* logits, int logits_fp32, long long ld, float*
 ATS_API int ats_serve_gate_route(const void* x, const void* wg, int* topk_idx, float* topk_w, int tokens, int hidden, int experts, int k,
                                  float temperature, void* stream) {
   if (tokens <= 0 || experts < 1 || experts > SRV_MAX_E || k < 1 || k > SRV_MAX_K || k > experts || (hidden & 7)) return 1003;
-  serve_gate_route_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wg), topk_idx, topk_w, hidden, experts, k, 1.f / temperature);
+  launch_pdl(serve_gate_route_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wg), topk_idx, topk_w, hidden, experts, k, 1.f / temperature);
   return int(cudaGetLastError());
 }
 
@@ -746,17 +755,17 @@ ATS_API int ats_serve_plan_dispatch(const void* x, const int* topk_idx, int* slo
                                     void* stream) {
   const int slots = tokens * k;
   if (slots <= 0 || slots > 1024 || experts < 1 || experts > SRV_MAX_E || (hidden & 7) || (!dst_table && !dst0)) return 1003;
-  serve_plan_dispatch_kernel<<<(slots * 32 + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), topk_idx, slot_pos, counts, totals, reinterpret_cast<__nv_bfloat16* const*>(dst_table),
-      static_cast<__nv_bfloat16*>(dst0), dst_stride, slots, k, hidden, experts, capacity);
+  launch_pdl(serve_plan_dispatch_kernel, dim3((slots * 32 + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(x), topk_idx, slot_pos, counts, totals, reinterpret_cast<__nv_bfloat16* const*>(dst_table),
+             static_cast<__nv_bfloat16*>(dst0), dst_stride, slots, k, hidden, experts, capacity);
   return int(cudaGetLastError());
 }
 
 ATS_API int ats_serve_combine(void* const* src_table, const void* src0, long long src_stride, const int* topk_idx, const int* slot_pos,
                               const float* topk_w, const void* residual, void* out, int tokens, int k, int hidden, void* stream) {
   if (tokens <= 0 || (hidden & 7) || (!src_table && !src0)) return 1003;
-  serve_combine_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<__nv_bfloat16* const*>(src_table), static_cast<const __nv_bfloat16*>(src0), src_stride, topk_idx, slot_pos, topk_w,
-      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), k, hidden);
+  launch_pdl(serve_combine_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
+             reinterpret_cast<__nv_bfloat16* const*>(src_table), static_cast<const __nv_bfloat16*>(src0), src_stride, topk_idx, slot_pos, topk_w,
+             static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), k, hidden);
   return int(cudaGetLastError());
 }
