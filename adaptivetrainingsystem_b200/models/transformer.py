@@ -161,7 +161,9 @@ class GroupedQueryAttention(nn.Module):
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, rope: RotaryEmbedding,
                 attention_mask: Optional[torch.Tensor] = None, cache: Optional[KVCache] = None,
-                positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+                positions: Optional[torch.Tensor] = None, post_norm: Optional["RMSNorm"] = None):
+        """-> x (= attention output projected + residual).  With ``post_norm`` (graph-replayed decode steps only) -> (x, h) where
+        h = post_norm(x) came out of the launch that folded the output projection, or ``None`` when that form did not apply."""
         B, L, _ = h.shape
         if self.sp_group is not None and cache is None and attention_mask is None and positions is None:
             return self._forward_sequence_parallel(h, residual, rope)
@@ -170,10 +172,20 @@ class GroupedQueryAttention(nn.Module):
         if graph_decode:
             # fill level and positions come from device memory, nothing of this call depends on Python state
             rope.ensure(cache.max_len, h.device)
-            qkv = ops.linear(h, self.qkv_proj, reduce_group=self.tp_group)
-            qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, positions=cache.device_positions.view(B, 1))
+            qkv = None
+            if self.tp_group is None:  # the fold of the split projection also rotates q and k
+                q2 = ops.serving.qkv_rope(h.reshape(B, -1), self.qkv_proj, rope.cos, rope.sin, cache.device_positions, self.n_q, self.n_kv, self.d)
+                qkv = q2.view(B, 1, -1) if q2 is not None else None
+            if qkv is None:
+                qkv = ops.linear(h, self.qkv_proj, reduce_group=self.tp_group)
+                qkv = ops.rope_packed(qkv, rope.cos, rope.sin, self.n_q, self.n_kv, self.d, positions=cache.device_positions.view(B, 1))
             a = ops.decode_attention(qkv, cache.k[self.layer_idx], cache.v[self.layer_idx], cache.device_lengths, self.n_q, self.n_kv, self.d)
-            return self._project_out(a, residual)
+            if post_norm is not None and self.tp_group is None:  # the fold of the output projection adds the residual and normalises
+                fused = ops.serving.out_proj_norm(a.reshape(B, -1), self.o_proj, residual.reshape(B, -1), post_norm.weight, post_norm.eps)
+                if fused is not None:
+                    return fused[0].view(residual.shape), fused[1].view(residual.shape)
+            x = self._project_out(a, residual)
+            return (x, None) if post_norm is not None else x
         rope.ensure(offset + L if positions is None else int(self.cfg.seq_length), h.device)
         qkv = ops.linear(h, self.qkv_proj, reduce_group=self.tp_group)
         nq, nk = self.n_q * self.d, self.n_kv * self.d
@@ -257,7 +269,9 @@ class MoEFFNLayer(nn.Module):
         self.register_buffer("dropped_slots", torch.zeros((), dtype=torch.float64), persistent=False)
         self.ep = None  # set by parallel.expert_parallel.attach when world size > 1
 
-    def forward(self, h: torch.Tensor, residual: Optional[torch.Tensor] = None):
+    def forward(self, h: torch.Tensor, residual: Optional[torch.Tensor] = None, next_norm=None):
+        """-> (output, auxiliary loss); with ``next_norm`` = (weight, eps) on a decode-sized step whose combine launch also
+        normalised its result for the next block -> (output, None, normalised output)."""
         shape = h.shape
         x = h.reshape(-1, shape[-1])
         T = x.shape[0]
@@ -267,10 +281,15 @@ class MoEFFNLayer(nn.Module):
             # exchange between expert-parallel ranks happens inside them (no auxiliary loss, no statistics while serving)
             res2 = residual.reshape(-1, shape[-1]) if residual is not None else None
             if self.ep is not None:
-                served = self.ep.moe_serving(x, self.gate.weight, k, self.routing_temperature, self.experts_w1, self.experts_w2, res2)
+                served = self.ep.moe_serving(x, self.gate.weight, k, self.routing_temperature, self.experts_w1, self.experts_w2, res2,
+                                             next_norm=next_norm)
             else:
-                served = moe_ops.moe_ffn_serving(x, self.gate.weight, k, self.routing_temperature, self.experts_w1, self.experts_w2, res2)
+                served = moe_ops.moe_ffn_serving(x, self.gate.weight, k, self.routing_temperature, self.experts_w1, self.experts_w2, res2,
+                                                 next_norm=next_norm)
             if served is not None:
+                if next_norm is not None:
+                    out, normed = served[0]
+                    return out.view(shape), None, (normed.view(shape) if normed is not None else None)
                 return served[0].view(shape), None
         logits = moe_ops.gate_logits(x, self.gate.weight)
         fused_route = logits.is_cuda and not (self.training and self.routing_noise_std > 0) and logits.dtype == torch.float32
@@ -447,6 +466,29 @@ class TransformerBlock(nn.Module):
             aux = x.new_zeros((), dtype=torch.float32)
         return x, aux
 
+    def decode_step(self, x, rope, cache, h_pre=None, next_norm=None):
+        """One graph-replayed decode step of this block with the norms folded into their producers: ``h_pre`` is this block's
+        normalised input when the block before already produced it, ``next_norm`` = (weight, eps) of the norm that follows this
+        block.  -> (x, normalised x for the next block or None)."""
+        if h_pre is None:
+            h, x = self.input_norm.with_skip(x)
+        else:
+            h = h_pre
+        res = self.self_attn(h, x, rope, None, cache, None, post_norm=self.post_attn_norm)
+        x, h = res if isinstance(res, tuple) else (res, None)
+        if h is None:
+            h, x = self.post_attn_norm.with_skip(x)
+        h_next = None
+        if self.ffn_kind == "moe":
+            res = self.ffn(h, x, next_norm=next_norm)
+            x = res[0]
+            h_next = res[2] if len(res) > 2 else None
+        elif self.ffn_kind == "mod":
+            x, _ = self.ffn(h, x, decode=True)
+        else:
+            x, _ = self.ffn(h, x)
+        return x, h_next
+
     def forward(self, x, rope, attention_mask=None, cache=None, positions=None, decode=False):
         if self.cfg.gradient_checkpointing and self.training and torch.is_grad_enabled() and cache is None:
             return checkpoint(self._body, x, rope, attention_mask, None, positions, decode, use_reentrant=False)
@@ -526,6 +568,15 @@ class DeepSeekTransformer(nn.Module):
         if cfg.dropout > 0 and self.training:
             x = F.dropout(x, cfg.dropout)
         aux_losses: List[torch.Tensor] = []
+        if (cache is not None and cache.device_lengths is not None and input_ids.shape[1] == 1 and attention_mask is None and positions is None
+                and not self.training and not torch.is_grad_enabled() and ops.serving.FUSE_DECODE):
+            # graph-replayed decode step: every norm that can ride on the launch before it does (no auxiliary losses while serving)
+            h_pre = None
+            n = len(self.layers)
+            for i, blk in enumerate(self.layers):
+                nxt = self.layers[i + 1].input_norm if i + 1 < n else self.norm
+                x, h_pre = blk.decode_step(x, self.rope, cache, h_pre, (nxt.weight, nxt.eps))
+            return (h_pre if h_pre is not None else self.norm(x)), aux_losses
         for blk in self.layers:
             x, aux = blk(x, self.rope, attention_mask, cache, positions, decode)
             aux_losses.append(aux.float().clamp(max=1.0))

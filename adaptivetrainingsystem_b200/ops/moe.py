@@ -369,20 +369,26 @@ def serve_plan_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, num_experts: in
 
 def serve_combine(topk_idx: torch.Tensor, slot_pos: torch.Tensor, topk_w: torch.Tensor, tokens: int, hidden: int, dtype, device,
                   buf: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None,
-                  residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  residual: Optional[torch.Tensor] = None, next_norm=None):
     """out[t] = residual[t] + sum_j w[t, j] * row(e_j, pos_j); one CTA per token.  Rows come from ``buf`` [E, C, H] or from the
-    blocks ``table`` points to (pulled over NVLink when they live on the experts' owners)."""
+    blocks ``table`` points to (pulled over NVLink when they live on the experts' owners).  ``next_norm`` = (weight, eps): the same
+    launch also writes RMSNorm(out) * weight, the input of the next block, and the result is ``(out, normed)``."""
     out = torch.empty(tokens, hidden, dtype=dtype, device=device)
     k = topk_idx.shape[1]
     stride = buf.stride(0) if buf is not None else 0
+    fuse = next_norm is not None and next_norm[0].dtype == dtype and dtype == torch.bfloat16
+    normed = torch.empty_like(out) if fuse else None
     _CK(_L().ats_serve_combine(_P(table), _P(buf) if table is None else None, stride, _P(topk_idx), _P(slot_pos), _P(topk_w),
-                               _P(residual), _P(out), tokens, k, hidden, _S(device)), "serve_combine")
+                               _P(residual), _P(out), tokens, k, hidden, _P(next_norm[0]) if fuse else None, _P(normed),
+                               float(next_norm[1]) if fuse else 0.0, _S(device)), "serve_combine")
+    if next_norm is not None:
+        return out, normed   # normed is None when the fused form did not apply: the caller normalises as usual
     return out
 
 
 @torch.no_grad()
 def moe_ffn_serving(x: torch.Tensor, wg: torch.Tensor, top_k: int, temperature: float, w1: torch.Tensor, w2: torch.Tensor,
-                    residual: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                    residual: Optional[torch.Tensor] = None, next_norm=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """One MoE layer of a decode-sized step on one GPU: gate + route, plan + dispatch, grouped SwiGLU up-projection, grouped
     down-projection, combine -- five launches.  Dropless (every expert block has room for every token).
     -> (output [T, H], demand per expert int32 [E])."""
@@ -395,8 +401,8 @@ def moe_ffn_serving(x: torch.Tensor, wg: torch.Tensor, top_k: int, temperature: 
     packed = bool(getattr(w1, "_ats_packed", False))
     h = G.grouped_nt(xe, w1, counts, swiglu=True, packed=packed)
     ye = G.grouped_nt(h, w2, counts, packed=packed)
-    out = serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, buf=ye, residual=residual)
-    return out, totals
+    out = serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, buf=ye, residual=residual, next_norm=next_norm)
+    return out, totals   # with next_norm, out is the pair (output, normalised output)
 
 
 def moe_ffn(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,

@@ -27,6 +27,10 @@ def _fns():
         lib.ats_decode_attn_chunks.argtypes = [_ci]
         lib.ats_decode_attn.restype = _ci
         lib.ats_decode_attn.argtypes = [_vp, _cll, _ci, _ci, _ci, _vp, _vp, _cll, _vp, _ci, _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp]
+        lib.ats_fold_rope.restype = _ci
+        lib.ats_fold_rope.argtypes = [_vp, _ci, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp]
+        lib.ats_fold_add_norm.restype = _ci
+        lib.ats_fold_add_norm.argtypes = [_vp, _ci, _vp, _vp, _vp, _vp, _ci, _ci, _cf, _vp]
         lib.ats_sample.restype = _ci
         lib.ats_sample.argtypes = [_vp, _ci, _cll, _vp, _vp, _ci, _ci, _vp, _vp, _ci, _ci, _cf, _ci, _cf, _cf, _vp]
         _sig = True
@@ -40,6 +44,66 @@ def _buf(key, numel: int, dtype, device) -> torch.Tensor:
         t = torch.empty(numel, dtype=dtype, device=device)
         _scratch[k] = t
     return t
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Fused pieces of a decode step.  With a handful of tokens a projection splits its reduction over the SMs and leaves fp32 partial
+# products; the launch that folds them also does what would otherwise be the next launch: the rotary embedding of the packed
+# q / k / v projection, or the residual add and the RMSNorm that follows the output projection.
+# ----------------------------------------------------------------------------------------------------------
+FUSE_DECODE = __import__("os").environ.get("ATS_DECODE_FUSED", "1") == "1"
+
+
+def _partial_products(x2: torch.Tensor, w: torch.Tensor):
+    """fp32 partial products [splits, T, N] of x2 [T, K] @ w [N, K]^T over slices of the reduction, or ``None`` when this shape
+    does not split (the caller then uses the ordinary product)."""
+    from . import gemm as G
+    T, K = x2.shape
+    N = w.shape[0]
+    if not (FUSE_DECODE and _lib.use_cuda_kernels(x2) and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
+            and x2.is_contiguous() and w.is_contiguous() and not getattr(w, "_ats_z3", None) and G.SPLIT_K_SKINNY):
+        return None
+    splits = G._skinny_splits(T, N, K)
+    if splits < 2:
+        return None
+    kp = K // splits
+    part = torch.empty(splits, T, N, dtype=torch.float32, device=x2.device)
+    G._raw(x2, T, K, K, 0, w, N, K, K, 0, part, N, None, 0, None, 0, T, N, kp, epilogue=G.EPI_F32, groups=splits, a_gs_k=kp, b_gs_k=kp,
+           d_gs=T * N)
+    return part
+
+
+def qkv_rope(h2: torch.Tensor, w_qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor, n_q: int, n_kv: int,
+             d: int) -> Optional[torch.Tensor]:
+    """Packed projection of the new tokens with q and k rotated at ``positions`` [T] (int32): one product + one fold launch.
+    ``None`` when the fused form does not apply."""
+    if d % 16 or positions is None or positions.dtype != torch.int32 or cos.dtype != torch.float32 or w_qkv.shape[0] != (n_q + 2 * n_kv) * d:
+        return None
+    part = _partial_products(h2, w_qkv)
+    if part is None:
+        return None
+    T, N = h2.shape[0], w_qkv.shape[0]
+    out = torch.empty(T, N, dtype=h2.dtype, device=h2.device)
+    err = _fns().ats_fold_rope(_lib.ptr(part), part.shape[0], _lib.ptr(out), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(positions), T, N, n_q, n_kv, d,
+                               _lib.stream_ptr(h2.device))
+    _lib.check(err, "ats_fold_rope")
+    return out
+
+
+def out_proj_norm(a2: torch.Tensor, w_o: torch.Tensor, residual2: torch.Tensor, norm_w: torch.Tensor, eps: float):
+    """x = a2 @ w_o^T + residual2 and h = RMSNorm(x) * norm_w from one product + one fold launch -> (x, h), or ``None``."""
+    if norm_w.dtype != torch.bfloat16 or residual2 is None or not residual2.is_contiguous():
+        return None
+    part = _partial_products(a2, w_o)
+    if part is None:
+        return None
+    T, H = a2.shape[0], w_o.shape[0]
+    x = torch.empty(T, H, dtype=a2.dtype, device=a2.device)
+    h = torch.empty_like(x)
+    err = _fns().ats_fold_add_norm(_lib.ptr(part), part.shape[0], _lib.ptr(residual2), _lib.ptr(norm_w), _lib.ptr(x), _lib.ptr(h), T, H, float(eps),
+                                   _lib.stream_ptr(a2.device))
+    _lib.check(err, "ats_fold_add_norm")
+    return x, h
 
 
 def decode_attention_available(qkv: torch.Tensor, n_q: int, n_kv: int, d: int) -> bool:

@@ -284,7 +284,7 @@ def _down_proj_slices(n_groups: int, N: int, K: int) -> int:
 
 
 @torch.no_grad()
-def ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, comm: "ExpertParallelComm", buf: _ServingBuffers):
+def ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, comm: "ExpertParallelComm", buf: _ServingBuffers, next_norm=None):
     """One MoE layer of a decode step across the expert-parallel ranks, six launches between two flag barriers:
 
     gate + route -> slot plan + dispatch (token rows go straight into the owners' row blocks over NVLink) -> barrier ->
@@ -303,8 +303,8 @@ def ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, comm: "ExpertPar
     h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, packed=packed)
     G.grouped_nt(h, w2, buf.counts, out=buf.own_y, packed=packed, k_split=_down_proj_slices(buf.El, w2.shape[1], w2.shape[2]))
     comm.barrier()
-    out = M.serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, table=buf.t_pull_y, residual=residual)
-    return out, None
+    out = M.serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, table=buf.t_pull_y, residual=residual, next_norm=next_norm)
+    return out, None   # with next_norm, out is the pair (output, normalised output)
 
 
 class EPLayer:
@@ -313,14 +313,14 @@ class EPLayer:
     def __init__(self, comm: ExpertParallelComm, layer_idx: int, num_experts: int):
         self.comm, self.layer_idx, self.num_experts = comm, layer_idx, num_experts
 
-    def moe_serving(self, x, wg, top_k, temperature, w1, w2, residual=None):
+    def moe_serving(self, x, wg, top_k, temperature, w1, w2, residual=None, next_norm=None):
         """Decode-sized step (no autograd): one row block per expert, all layers share one set of buffers.  Returns ``None``
         when the step does not fit that layout (the caller then takes the general path)."""
         cs = self.comm.serving_rows(x.shape[0])
         if not cs:
             return None
         buf = self.comm.serving_buffers(self.num_experts, cs, x.shape[1], x.dtype, x.device)
-        return ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, self.comm, buf)
+        return ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, self.comm, buf, next_norm)
 
     def moe_ffn(self, x, topk_idx, topk_w, w1, w2, capacity, residual=None):
         # Training keeps one set of exchange buffers per layer (the backward pass reads what the forward pass received).

@@ -633,14 +633,33 @@ __global__ void __launch_bounds__(256) serve_plan_dispatch_kernel(const __nv_bfl
   for (int v = lane; v < (hidden >> 3); v += 32) d[v] = src[v];
 }
 
+__device__ __forceinline__ float sumsq_bf16x8(const uint4& o) {
+  const float2 f0 = unpack_bf16x2(o.x), f1 = unpack_bf16x2(o.y), f2 = unpack_bf16x2(o.z), f3 = unpack_bf16x2(o.w);
+  return f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
+}
+// x * rstd * w for eight bf16 values (the arithmetic of rmsnorm_fwd_kernel)
+__device__ __forceinline__ uint4 scale_bf16x8(const uint4& o, const uint4& w, float rstd) {
+  const uint32_t xs[4] = {o.x, o.y, o.z, o.w}, ws[4] = {w.x, w.y, w.z, w.w};
+  uint32_t r[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 x = unpack_bf16x2(xs[e]), g = unpack_bf16x2(ws[e]);
+    r[e] = pack_bf16x2(x.x * rstd * g.x, x.y * rstd * g.y);
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 __global__ void __launch_bounds__(256) serve_combine_kernel(__nv_bfloat16* const* __restrict__ src_table, const __nv_bfloat16* src0,
                                                             long long src_stride, const int* __restrict__ topk_idx,
                                                             const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
                                                             const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int k,
-                                                            int hidden) {
+                                                            int hidden, const __nv_bfloat16* __restrict__ norm_w,
+                                                            __nv_bfloat16* __restrict__ norm_out, float eps) {
   pdl_prologue();
+  __shared__ float red[33];
   const int t = blockIdx.x;
   const int nvec = hidden >> 3;
+  float ss = 0.f;
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (res) {
@@ -660,8 +679,106 @@ __global__ void __launch_bounds__(256) serve_combine_kernel(__nv_bfloat16* const
       acc[0] += wt * f0.x; acc[1] += wt * f0.y; acc[2] += wt * f1.x; acc[3] += wt * f1.y;
       acc[4] += wt * f2.x; acc[5] += wt * f2.y; acc[6] += wt * f3.x; acc[7] += wt * f3.y;
     }
-    reinterpret_cast<uint4*>(out + (long long)t * hidden)[v] =
-        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    reinterpret_cast<uint4*>(out + (long long)t * hidden)[v] = o;
+    if (norm_out) ss += sumsq_bf16x8(o);
+  }
+  if (norm_out) {
+    // RMSNorm of the row just written (the next block's input norm), on the bf16-rounded values as the separate kernel sees them
+    const float rstd = rsqrtf(block_sum(ss, red) / float(hidden) + eps);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 o = reinterpret_cast<const uint4*>(out + (long long)t * hidden)[v];  // written by this thread above
+      reinterpret_cast<uint4*>(norm_out + (long long)t * hidden)[v] = scale_bf16x8(o, reinterpret_cast<const uint4*>(norm_w)[v], rstd);
+    }
+  }
+}
+
+// ---- fold of the reduction slices of the packed projection + rotary embedding of the q / k heads, one CTA per token ---------------
+// part: [splits, tokens, N] fp32 partial products; out: [tokens, N] bf16 with q and k heads rotated at position pos[t].
+__global__ void __launch_bounds__(256) fold_rope_kernel(const float* __restrict__ part, int splits, long long slice_stride,
+                                                        __nv_bfloat16* __restrict__ out, const float* __restrict__ cos_t,
+                                                        const float* __restrict__ sin_t, const int* __restrict__ pos, int N, int n_q,
+                                                        int n_kv, int d) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int half = d >> 1, vph = half >> 3;
+  const int rope_items = (n_q + n_kv) * vph;  // an item: 8 elements of a head's first half and the matching 8 of its second half
+  const int v_items = n_kv * (d >> 3);
+  const float* row = part + (long long)t * N;
+  __nv_bfloat16* orow = out + (long long)t * N;
+  const int p = pos[t];
+  auto fold8 = [&](int col, float (&a)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = 0.f;
+    for (int sl = 0; sl < splits; ++sl) {
+      const float4* src = reinterpret_cast<const float4*>(row + sl * slice_stride + col);
+      const float4 x = src[0], y = src[1];
+      a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w; a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    }
+  };
+  for (int i = threadIdx.x; i < rope_items + v_items; i += blockDim.x) {
+    float a[8];
+    if (i >= rope_items) {
+      const int col = (n_q + n_kv) * d + (i - rope_items) * 8;
+      fold8(col, a);
+      *reinterpret_cast<uint4*>(orow + col) = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+      continue;
+    }
+    const int head = i / vph, v = i - head * vph;
+    const int col = head * d + v * 8;
+    float b[8];
+    fold8(col, a);
+    fold8(col + half, b);
+    const float4* c4 = reinterpret_cast<const float4*>(cos_t + (long long)p * half + v * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_t + (long long)p * half + v * 8);
+    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    const float c[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+    const float sn[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // rounded to bf16 first: the same values the separate fold and rotation kernels exchange through memory
+      const float2 x1 = unpack_bf16x2(pack_bf16x2(a[2 * e], a[2 * e + 1])), x2 = unpack_bf16x2(pack_bf16x2(b[2 * e], b[2 * e + 1]));
+      o1[e] = pack_bf16x2(x1.x * c[2 * e] - x2.x * sn[2 * e], x1.y * c[2 * e + 1] - x2.y * sn[2 * e + 1]);
+      o2[e] = pack_bf16x2(x1.x * sn[2 * e] + x2.x * c[2 * e], x1.y * sn[2 * e + 1] + x2.y * c[2 * e + 1]);
+    }
+    *reinterpret_cast<uint4*>(orow + col) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4*>(orow + col + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+  }
+}
+
+// ---- fold of the reduction slices of the output projection + residual + RMSNorm, one CTA per token ---------------------------------
+// x_out = sum of the slices + residual (bf16); h_out = RMSNorm(x_out) * w.
+__global__ void __launch_bounds__(256) fold_add_norm_kernel(const float* __restrict__ part, int splits, long long slice_stride,
+                                                            const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+                                                            __nv_bfloat16* __restrict__ x_out, __nv_bfloat16* __restrict__ h_out,
+                                                            int hidden, float eps) {
+  pdl_prologue();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int nvec = hidden >> 3;
+  const float* row = part + (long long)t * hidden;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (res) {
+      const uint4 r = reinterpret_cast<const uint4*>(res + (long long)t * hidden)[v];
+      const float2 f0 = unpack_bf16x2(r.x), f1 = unpack_bf16x2(r.y), f2 = unpack_bf16x2(r.z), f3 = unpack_bf16x2(r.w);
+      a[0] = f0.x; a[1] = f0.y; a[2] = f1.x; a[3] = f1.y; a[4] = f2.x; a[5] = f2.y; a[6] = f3.x; a[7] = f3.y;
+    }
+    for (int sl = 0; sl < splits; ++sl) {
+      const float4* src = reinterpret_cast<const float4*>(row + sl * slice_stride + v * 8);
+      const float4 x = src[0], y = src[1];
+      a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w; a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    }
+    const uint4 o = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+    reinterpret_cast<uint4*>(x_out + (long long)t * hidden)[v] = o;
+    ss += sumsq_bf16x8(o);
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / float(hidden) + eps);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 o = reinterpret_cast<const uint4*>(x_out + (long long)t * hidden)[v];  // written by this thread above
+    reinterpret_cast<uint4*>(h_out + (long long)t * hidden)[v] = scale_bf16x8(o, reinterpret_cast<const uint4*>(w)[v], rstd);
   }
 }
 
@@ -761,11 +878,31 @@ ATS_API int ats_serve_plan_dispatch(const void* x, const int* topk_idx, int* slo
   return int(cudaGetLastError());
 }
 
+// norm_w / norm_out (both or neither): also write RMSNorm(out) * norm_w, the input of the next block.
 ATS_API int ats_serve_combine(void* const* src_table, const void* src0, long long src_stride, const int* topk_idx, const int* slot_pos,
-                              const float* topk_w, const void* residual, void* out, int tokens, int k, int hidden, void* stream) {
-  if (tokens <= 0 || (hidden & 7) || (!src_table && !src0)) return 1003;
+                              const float* topk_w, const void* residual, void* out, int tokens, int k, int hidden, const void* norm_w,
+                              void* norm_out, float eps, void* stream) {
+  if (tokens <= 0 || (hidden & 7) || (!src_table && !src0) || ((norm_w == nullptr) != (norm_out == nullptr))) return 1003;
   launch_pdl(serve_combine_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
              reinterpret_cast<__nv_bfloat16* const*>(src_table), static_cast<const __nv_bfloat16*>(src0), src_stride, topk_idx, slot_pos, topk_w,
-             static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), k, hidden);
+             static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), k, hidden, static_cast<const __nv_bfloat16*>(norm_w),
+             static_cast<__nv_bfloat16*>(norm_out), eps);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_fold_rope(const float* part, int splits, void* out, const float* cos_t, const float* sin_t, const int* pos, int tokens, int N,
+                          int n_q, int n_kv, int d, void* stream) {
+  if (tokens <= 0 || splits < 1 || (d & 15) || N != (n_q + 2 * n_kv) * d || !pos) return 1003;
+  launch_pdl(fold_rope_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), part, splits, (long long)tokens * N,
+             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, pos, N, n_q, n_kv, d);
+  return int(cudaGetLastError());
+}
+
+ATS_API int ats_fold_add_norm(const float* part, int splits, const void* residual, const void* norm_w, void* x_out, void* h_out, int tokens,
+                              int hidden, float eps, void* stream) {
+  if (tokens <= 0 || splits < 1 || (hidden & 7) || !norm_w || !x_out || !h_out) return 1003;
+  launch_pdl(fold_add_norm_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream), part, splits, (long long)tokens * hidden,
+             static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), static_cast<__nv_bfloat16*>(x_out),
+             static_cast<__nv_bfloat16*>(h_out), hidden, eps);
   return int(cudaGetLastError());
 }

@@ -869,3 +869,45 @@ def test_continuous_batching_matches_one_by_one_generation(moe):
             assert ref == t, (len(p), ref, t)
     assert same >= 7, same         # a routing near-tie may flip a token of a MoE sequence; most must agree exactly
     ops.check_status()
+
+
+def test_fused_decode_folds_match_separate_launches():
+    """Decode-step fusions: fold of the split projection + rotary embedding, fold + residual + RMSNorm, combine + next norm."""
+    from adaptivetrainingsystem_b200.ops import moe as M
+    from adaptivetrainingsystem_b200.ops import serving
+    torch.manual_seed(8)
+    T, K, n_q, n_kv, d = 8, 4096, 32, 8, 128
+    N = (n_q + 2 * n_kv) * d
+    h = _rand(T, K, scale=0.5)
+    w = _rand(N, K, scale=0.02)
+    cos, sin = ops.rope_tables(2048, d, device=DEV)
+    pos = torch.randint(0, 2048, (T,), device=DEV, dtype=torch.int32)
+    fused = serving.qkv_rope(h, w, cos, sin, pos, n_q, n_kv, d)
+    assert fused is not None, "the projection of 8 tokens must take the split form"
+    ref = ops.rope_packed(ops.linear(h.view(T, 1, K), w), cos, sin, n_q, n_kv, d, positions=pos.view(T, 1)).view(T, N)
+    assert (fused.float() - ref.float()).abs().max().item() <= 2e-2 * ref.float().abs().max().item()
+    assert (fused != ref).float().mean().item() < 1e-3          # the same arithmetic: at most stray last-bit differences
+    # output projection + residual + norm
+    a = _rand(T, n_q * d, scale=0.5)
+    wo = _rand(K, n_q * d, scale=0.02)
+    res = _rand(T, K)
+    nw = (1.0 + 0.1 * torch.randn(K, device=DEV)).bfloat16()
+    out = serving.out_proj_norm(a, wo, res, nw, 1e-6)
+    assert out is not None
+    x_ref = ops.linear(a, wo, residual=res)
+    h_ref = ops.rms_norm(x_ref, nw, 1e-6)
+    assert torch.equal(out[0], x_ref)
+    _close(out[1], h_ref, tol=1e-2, what="fold + residual + norm")
+    assert (out[1] != h_ref).float().mean().item() < 1e-2
+    # combine + the next block's norm
+    E, k, C = 4, 2, 128
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    wts = torch.rand(T, k, device=DEV)
+    xe = torch.empty(E, C, K, dtype=torch.bfloat16, device=DEV)
+    slot_pos, counts, totals = M.serve_plan_dispatch(h, idx, E, C, out=xe)
+    ye = _rand(E, C, K)
+    plain = M.serve_combine(idx, slot_pos, wts, T, K, torch.bfloat16, DEV, buf=ye, residual=res)
+    both = M.serve_combine(idx, slot_pos, wts, T, K, torch.bfloat16, DEV, buf=ye, residual=res, next_norm=(nw, 1e-6))
+    assert torch.equal(both[0], plain) and both[1] is not None
+    _close(both[1], ops.rms_norm(plain, nw, 1e-6), tol=1e-2, what="combine + norm")
+    ops.check_status()
