@@ -26,7 +26,7 @@ def _fns():
         lib.ats_decode_attn_chunks.restype = _ci
         lib.ats_decode_attn_chunks.argtypes = [_ci]
         lib.ats_decode_attn.restype = _ci
-        lib.ats_decode_attn.argtypes = [_vp, _cll, _ci, _ci, _ci, _vp, _vp, _cll, _vp, _ci, _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp]
+        lib.ats_decode_attn.argtypes = [_vp, _cll, _ci, _ci, _ci, _vp, _vp, _cll, _vp, _ci, _ci, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp, _vp]
         lib.ats_fold_rope.restype = _ci
         lib.ats_fold_rope.argtypes = [_vp, _ci, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp]
         lib.ats_fold_add_norm.restype = _ci
@@ -128,10 +128,18 @@ def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     chunks = lib.ats_decode_attn_chunks(max_len)
     part_o = _buf("dec_o", B * n_q * chunks * d, torch.float32, qkv.device)
     part_ml = _buf("dec_ml", B * n_q * chunks * 2, torch.float32, qkv.device)
+    # arrival counters of the (sequence, KV head) pairs: the CTA that arrives last merges the chunk partials and puts its counter
+    # back to zero, so the buffer is zeroed once, when it is made
+    key = ("dec_cnt", torch.int32, qkv.device.index)
+    done = _scratch.get(key)
+    if done is None or done.numel() < B * n_kv:
+        done = torch.zeros(max(B * n_kv, 1024), dtype=torch.int32, device=qkv.device)
+        _scratch[key] = done
     out = torch.empty(B, 1, n_q * d, dtype=qkv.dtype, device=qkv.device)
     err = lib.ats_decode_attn(_lib.ptr(qkv), qkv.stride(0), 0, n_q * d, (n_q + n_kv) * d, _lib.ptr(k_cache), _lib.ptr(v_cache),
                               k_cache.stride(0), _lib.ptr(length) if per_seq else None, 0 if per_seq else int(length), longest, B, n_q,
-                              n_kv, d, max_len, _lib.ptr(part_o), _lib.ptr(part_ml), _lib.ptr(out), _lib.stream_ptr(qkv.device))
+                              n_kv, d, max_len, _lib.ptr(part_o), _lib.ptr(part_ml), _lib.ptr(done) if FUSE_DECODE else None, _lib.ptr(out),
+                              _lib.stream_ptr(qkv.device))
     _lib.check(err, "ats_decode_attn")
     return out
 

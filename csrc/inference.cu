@@ -36,6 +36,7 @@ struct DecodeArgs {
   float* part_ml;  // [B, Hq, n_chunks, 2]
   int n_chunks;
   __nv_bfloat16* out;  // [B, Hq * D]
+  int* chunk_done;     // [B, Hkv] arrival counters (zero between launches) or nullptr: the last CTA of a (sequence, KV head) merges
 };
 
 template <int D, int REP>
@@ -357,6 +358,38 @@ __global__ void __launch_bounds__(DEC_THREADS, OCC) decode_attn_mma_kernel(const
 #pragma unroll
     for (int w = 0; w < DEC_THREADS / 32; ++w) acc += s_red[w][h][d];
     p.part_o[(((long long)b * p.Hq + hk * REP + h) * p.n_chunks + chunk) * D + d] = acc;
+  }
+  if (p.chunk_done == nullptr) return;
+  // The CTA that arrives last for this (sequence, KV head) merges the chunk partials of its query heads: no separate merge launch.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* cnt = p.chunk_done + b * p.Hkv + hk;
+    s_last = atomicAdd(cnt, 1) == int(gridDim.x) - 1;
+    if (s_last) *cnt = 0;  // every CTA of this launch has arrived: ready for the next launch on the stream
+  }
+  __syncthreads();
+  if (!s_last || warp >= REP) return;
+  __threadfence();
+  const long long wq = (long long)b * p.Hq + hk * REP + warp;
+  const float* ml = p.part_ml + wq * p.n_chunks * 2;
+  float m = -INFINITY;
+  for (int c = 0; c < p.n_chunks; ++c) m = fmaxf(m, __ldcg(ml + 2 * c));
+  float l = 0.f;
+  for (int c = 0; c < p.n_chunks; ++c) {
+    const float mc = __ldcg(ml + 2 * c);
+    l += __ldcg(ml + 2 * c + 1) * ((mc == -INFINITY) ? 0.f : __expf(mc - m));
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = lane; d < D; d += 32) {
+    float acc = 0.f;
+    for (int c = 0; c < p.n_chunks; ++c) {
+      const float mc = __ldcg(ml + 2 * c);
+      const float f = (mc == -INFINITY) ? 0.f : __expf(mc - m);
+      acc += __ldcg(p.part_o + (wq * p.n_chunks + c) * D + d) * f;
+    }
+    p.out[wq * D + d] = __float2bfloat16(acc * inv);
   }
 }
 
@@ -814,7 +847,7 @@ ATS_API int ats_decode_attn_chunks(int max_len) { return (max_len + DEC_CHUNK - 
 // lengths: per-sequence cached lengths (device int32) or nullptr for the common `length`.  out: [B, Hq * D] bf16.
 ATS_API int ats_decode_attn(const void* qkv, long long ld_qkv, int q_col0, int k_col0, int v_col0, void* k_cache, void* v_cache,
                             long long cache_b_stride, const int* lengths, int length, int max_tokens, int B, int Hq, int Hkv, int D,
-                            int max_len, float* part_o, float* part_ml, void* out, void* stream) {
+                            int max_len, float* part_o, float* part_ml, int* chunk_done, void* out, void* stream) {
   if ((D != 64 && D != 128) || Hq % Hkv || ((q_col0 | k_col0 | v_col0) & 7) || (ld_qkv & 7)) return 1003;
   const int rep = Hq / Hkv;
   DecodeArgs p;
@@ -832,11 +865,20 @@ ATS_API int ats_decode_attn(const void* qkv, long long ld_qkv, int q_col0, int k
   if (p.n_chunks < 1) p.n_chunks = 1;
   p.out = static_cast<__nv_bfloat16*>(out);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (g_decode_mma < 0) {
+    const char* ev = getenv("ATS_DECODE_ATTN_MMA");
+    g_decode_mma = (ev && ev[0] == '0') ? 0 : 1;
+    const char* o = getenv("ATS_DECODE_ATTN_OCC");
+    if (o && o[0] == '3') g_decode_occ = 3;
+  }
+  const bool merge_inside = chunk_done != nullptr && g_decode_mma == 1 && g_decode_occ == 2;
+  p.chunk_done = merge_inside ? chunk_done : nullptr;
   int e = 1004;
 #define ATS_DEC(DD, RR) if (D == DD && rep == RR) e = launch_decode<DD, RR>(p, s);
   ATS_DEC(64, 1) ATS_DEC(64, 2) ATS_DEC(64, 4) ATS_DEC(64, 8) ATS_DEC(128, 1) ATS_DEC(128, 2) ATS_DEC(128, 4) ATS_DEC(128, 8)
 #undef ATS_DEC
   if (e) return e;
+  if (merge_inside) return int(cudaGetLastError());
   const int BH = B * Hq;
   launch_pdl(decode_merge_kernel, dim3((BH * 32 + 255) / 256), dim3(256), 0, s, (const float*)part_o, (const float*)part_ml, p.out, BH, p.n_chunks, D);
   return int(cudaGetLastError());
