@@ -52,6 +52,11 @@ def _buf(key, numel: int, dtype, device) -> torch.Tensor:
 # q / k / v projection, or the residual add and the RMSNorm that follows the output projection.
 # ----------------------------------------------------------------------------------------------------------
 FUSE_DECODE = __import__("os").environ.get("ATS_DECODE_FUSED", "1") == "1"
+# Flash-decoding merge inside the attention kernel (the CTA that arrives last for a sequence and KV head merges the chunk
+# partials) instead of a launch of its own.  Off by default: measured on one box it changed the decode step by -0.5 % on the
+# 22-layer model (64-wide heads) and +1.6 % on the Mixtral shape, where the merge lengthens the tail of a kernel that is already
+# the long pole of the layer.
+MERGE_INSIDE = __import__("os").environ.get("ATS_DECODE_MERGE_INSIDE", "0") == "1"
 
 
 def _partial_products(x2: torch.Tensor, w: torch.Tensor):
@@ -138,7 +143,7 @@ def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     out = torch.empty(B, 1, n_q * d, dtype=qkv.dtype, device=qkv.device)
     err = lib.ats_decode_attn(_lib.ptr(qkv), qkv.stride(0), 0, n_q * d, (n_q + n_kv) * d, _lib.ptr(k_cache), _lib.ptr(v_cache),
                               k_cache.stride(0), _lib.ptr(length) if per_seq else None, 0 if per_seq else int(length), longest, B, n_q,
-                              n_kv, d, max_len, _lib.ptr(part_o), _lib.ptr(part_ml), _lib.ptr(done) if FUSE_DECODE else None, _lib.ptr(out),
+                              n_kv, d, max_len, _lib.ptr(part_o), _lib.ptr(part_ml), _lib.ptr(done) if MERGE_INSIDE else None, _lib.ptr(out),
                               _lib.stream_ptr(qkv.device))
     _lib.check(err, "ats_decode_attn")
     return out

@@ -384,6 +384,16 @@ def test_decode_attention(B, hq, hkv, d, length):
     out2 = serving.decode_attention(qkv, kc2, vc2, lens, hq, hkv, d)
     ref2 = serving.decode_attention_reference(qkv.float(), kc_ref, vc_ref, lens, hq, hkv, d)
     _close(out2, ref2, tol=2e-2, what="decode attention (ragged)")
+    # the merge of the chunk partials inside the attention kernel (last CTA of a sequence and KV head) gives the same bits, twice
+    # in a row (the arrival counters reset themselves)
+    serving.MERGE_INSIDE = True
+    try:
+        for _ in range(2):
+            kc3, vc3 = kc_ref.clone(), vc_ref.clone()
+            out3 = serving.decode_attention(qkv, kc3, vc3, lens, hq, hkv, d)
+            assert torch.equal(out3, out2)
+    finally:
+        serving.MERGE_INSIDE = False
 
 
 def test_sampling_kernel():
