@@ -298,3 +298,28 @@ def test_skinny_product_split_rule_and_weight_packing():
     x = torch.randn(2, 128, 128)
     counts = torch.tensor([128, 7], dtype=torch.int32)
     assert torch.allclose(G.grouped_nt(x, w * 1e-4, counts), G.grouped_nt(x, G.pack_kmajor(w * 1e-4), counts, packed=True))
+
+
+def test_weight_gradient_split_model_and_fp8_weight_copies():
+    """Pure host logic: the wave model that decides reduction slices for weight-gradient products, and the per-input-channel
+    e4m3 copy of a weight used by the fp8 input-gradient product (PyTorch definitions on CPU)."""
+    from adaptivetrainingsystem_b200.ops import fp8
+    from adaptivetrainingsystem_b200.ops import gemm as G
+    assert G._tn_splits(2560, 2048, 16384) > 1          # 80 tiles on 74 CTA pairs: two waves at 0.54 utilisation
+    assert G._tn_splits(2048, 2048, 16384) == 1         # 64 tiles: one wave
+    assert G._tn_splits(32000, 2048, 16384) == 1        # many waves: the last partial one is noise
+    assert G._tn_splits(2560, 2048, 4096) == 1          # short reduction: the fold would cost more than it saves
+    torch.manual_seed(0)
+    w = torch.randn(48, 32) * torch.logspace(-2, 1, 32)[None, :]     # input channels of very different magnitude
+    fp8.clear_weight_cache()
+    q, s = fp8.quantized_weight_t(w)
+    assert q.shape == (32, 48) and s.shape == (32,)
+    back = (q.float() * s[:, None]).t()
+    assert ((back - w).abs() / w.abs().amax(0, keepdim=True)).max() < 0.07      # every channel resolved on its own scale
+    q2, s2 = fp8.quantized_weight_t(w)
+    assert q2 is q                                        # cached until the weights change
+    fp8.weights_changed()
+    assert fp8.quantized_weight_t(w)[0] is not q
+    stacked = torch.randn(3, 16, 32)
+    qe, se = fp8.quantized_weight_t(stacked)
+    assert qe.shape == (3 * 32, 16) and se.shape == (96,)
