@@ -54,6 +54,9 @@ class ContinuousBatcher:
         self.device = next(self.model.parameters()).device
         if self.device.type != "cuda":
             raise RuntimeError("continuous batching replays a CUDA graph of the decode step: a CUDA device is required")
+        if getattr(self.model, "_ep_comm", None) is not None:
+            # admission prefills one request on one rank, which the expert-parallel exchange (a collective of all ranks) cannot serve
+            raise RuntimeError("continuous batching runs on one GPU (or on replicas): the model must not be expert-parallel")
         self.cache = self.model.make_cache(max_batch, max_len)
         self.slots = KVSlotManager(max_batch)
         self.decoder = GraphDecoder(self.model, self.cache)        # captured once; rows come and go underneath it
