@@ -139,7 +139,7 @@ if __name__ == "__main__":
     ap.add_argument("--mode", default="standard", choices=list(GENERATION_MODES))
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--device", default="auto")
-    ap.add_argument("--quantize", default=None, choices=["fp8"], help="post-training quantisation of the projection weights")
+    ap.add_argument("--quantize", default=None, choices=["fp8", "int8"], help="post-training quantisation of the projection weights")
     ap.add_argument("--prompts-file", default=None, help="one prompt per line, answered together by continuous batching")
     ap.add_argument("--max-batch", type=int, default=16)
     a = ap.parse_args()

@@ -12,3 +12,4 @@ from .moe import (expert_capacity, gate_logits, route, load_balancing_loss, plan
 from .serving import (decode_attention, decode_attention_available, decode_attention_reference, sample_tokens,  # noqa: E402,F401
                       sample_reference)
 from . import fp8  # noqa: E402,F401
+from . import int8  # noqa: E402,F401

@@ -403,6 +403,11 @@ class _LinearFn(torch.autograd.Function):
 def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None, reduce_group=None) -> torch.Tensor:
     """``x @ w.T (+ residual)`` -- the residual add is fused into the GEMM epilogue.  ``reduce_group``: ``w`` holds this rank's
     output columns of a tensor-parallel product, so the input gradient is all-reduced over that group."""
+    from . import int8
+    if int8.observing():
+        int8.record(x.reshape(-1, x.shape[-1]), w)
+    if int8.usable(x, w):
+        return int8.linear_int8(x, w, residual)
     if _lib.use_cuda_kernels(x):
         from . import fp8
         if fp8.enabled() and getattr(w, "_ats_z3", None) is None and x.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0:
@@ -519,6 +524,11 @@ class _SwiGLUMLPFn(torch.autograd.Function):
 
 def swiglu_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
                residual: Optional[torch.Tensor] = None, reduce_group=None) -> torch.Tensor:
+    from . import int8
+    if int8.observing():
+        int8.record(x.reshape(-1, x.shape[-1]), w_gate_up)
+    if reduce_group is None and int8.usable(x, w_gate_up) and w_gate_up.shape[0] % 32 == 0 and w_down.shape[1] % 16 == 0:
+        return int8.swiglu_mlp_int8(x, w_gate_up, w_down, residual)
     if _lib.use_cuda_kernels(x):
         return _SwiGLUMLPFn.apply(x, w_gate_up, w_down, residual, reduce_group)
     if reduce_group is not None:

@@ -86,10 +86,12 @@ class QuantizationManager:
     The reference swaps ``nn.Linear`` for bitsandbytes / GPTQ / quanto modules, none of which ships here.  The native
     method is ``"fp8"`` (``quantization_method="fp8"`` or ``quantization_bits=8`` without a method): every 2-D projection
     weight is quantised per output channel to e4m3, activations per token at run time, and ``ops.linear`` / the SwiGLU MLP
-    run on the ``kind::f8f6f4`` tensor-core GEMM with both scales applied in its epilogue.  The external backends are
-    reported and refused when not installed."""
+    run on the ``kind::f8f6f4`` tensor-core GEMM with both scales applied in its epilogue.  ``"int8"`` is the same scheme with
+    signed bytes on the ``kind::i8`` GEMM (W8A8), and ``"smoothquant"`` is int8 after :meth:`calibrate` has measured the
+    activation range of every projection's input channels and moved it into the weights (``ops/int8.py``).  The external
+    backends are reported and refused when not installed."""
 
-    NATIVE = ("fp8", "fp8_e4m3")
+    NATIVE = ("fp8", "fp8_e4m3", "int8", "smoothquant")
 
     def __init__(self, config):
         self.method = getattr(config, "quantization_method", None)
@@ -97,11 +99,31 @@ class QuantizationManager:
         if self.method is None and self.bits == 8:
             self.method = "fp8"
         self.applied = False
+        self.calibrated = False
         self.quantized_tensors = 0
         self.quantized_bytes = 0
 
+    @torch.no_grad()
+    def calibrate(self, model, batches, alpha: float = 0.5) -> int:
+        """SmoothQuant calibration: run ``batches`` (token id tensors) through the unquantised model while every projection
+        records the largest |x| of each of its input channels.  Returns the number of projections that got smoothing factors."""
+        from ..ops import int8
+        was = model.training
+        model.eval()
+        int8.set_enabled(False)
+        int8.observe(True)
+        try:
+            for ids in batches:
+                model(ids, return_aux_loss=False)
+        finally:
+            int8.observe(False)
+            model.train(was)
+        n = int8.finish_calibration(alpha)
+        self.calibrated = n > 0
+        return n
+
     def available_backends(self) -> Dict[str, bool]:
-        out = {"fp8 (native e4m3 GEMM)": torch.cuda.is_available()}
+        out = {"fp8 (native e4m3 GEMM)": torch.cuda.is_available(), "int8 / smoothquant (native s8 GEMM)": True}
         for mod in ("bitsandbytes", "auto_gptq", "optimum.quanto"):
             try:
                 __import__(mod)
@@ -115,10 +137,21 @@ class QuantizationManager:
             return model
         if self.method not in self.NATIVE:
             raise RuntimeError(f"quantization backend for {self.method!r} is not installed; available: {self.available_backends()}")
-        from ..ops import fp8
+        from ..ops import fp8, int8
         model.eval()
         for p in model.parameters():
             p.requires_grad_(False)
+        if self.method in ("int8", "smoothquant"):
+            if self.method == "smoothquant" and not self.calibrated:
+                raise RuntimeError("smoothquant needs activation ranges: call calibrate(model, batches) before quantize_model")
+            int8.set_enabled(True)
+            for name, p in model.named_parameters():
+                if p.dim() == 2 and p.shape[1] % 16 == 0 and "embed" not in name and "gate.weight" not in name and "router" not in name:
+                    q, sc, _ = int8.quantized_weight(p)
+                    self.quantized_tensors += 1
+                    self.quantized_bytes += q.numel() + sc.numel() * 4
+            self.applied = True
+            return model
         fp8.set_enabled(True)
         if torch.cuda.is_available():
             # quantise once, up front: the cache is keyed on the storage and stays valid while the weights are frozen

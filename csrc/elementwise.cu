@@ -689,6 +689,45 @@ __global__ void __launch_bounds__(256) quantize_rows_e4m3_kernel(const __nv_bflo
   }
 }
 
+// One CTA per row: scale = amax / 127, q = round(x / scale) as signed bytes.  inv_smooth (optional, [cols] bf16): the row is
+// multiplied by it first (SmoothQuant: the per-channel factors that were folded into the weight are divided out of the activations).
+__global__ void __launch_bounds__(256) quantize_rows_int8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int8_t* __restrict__ q,
+                                                                 long long ldq, float* __restrict__ scale, int cols,
+                                                                 const __nv_bfloat16* __restrict__ inv_smooth) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * ld;
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < cols; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint4 sm = inv_smooth ? *reinterpret_cast<const uint4*>(inv_smooth + i) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w}, w[4] = {sm.x, sm.y, sm.z, sm.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]), g = unpack_bf16x2(w[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x * g.x), fabsf(f.y * g.y)));
+    }
+  }
+  amax = block_max(amax, red);
+  const float sc = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+  const float inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[row] = sc;
+  int8_t* qr = q + row * ldq;
+  for (int i = threadIdx.x * 8; i < cols; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint4 sm = inv_smooth ? *reinterpret_cast<const uint4*>(inv_smooth + i) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w}, w[4] = {sm.x, sm.y, sm.z, sm.w};
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]), g = unpack_bf16x2(w[j]);
+      const int a = max(-127, min(127, __float2int_rn(f.x * g.x * inv))), b = max(-127, min(127, __float2int_rn(f.y * g.y * inv)));
+      o[j >> 1] |= (uint32_t(a & 0xff) | (uint32_t(b & 0xff) << 8)) << (16 * (j & 1));
+    }
+    *reinterpret_cast<uint2*>(qr + i) = make_uint2(o[0], o[1]);
+  }
+}
+
 }  // namespace ats
 
 // x: bf16 [rows, cols] with pitch ld; q: e4m3 bytes [rows, cols] with pitch ldq; scale: fp32 [rows].  cols % 8 == 0.
@@ -719,4 +758,13 @@ ATS_API int ats_debug_report(int* out4) {
   for (int i = 0; i < 4; ++i) out4[i] = 0;
   return 0;
 #endif
+}
+
+ATS_API int ats_quantize_rows_int8(const void* x, long long ld, void* q, long long ldq, float* scale, long long rows, int cols,
+                                   const void* inv_smooth, void* stream) {
+  if ((cols & 7) || (ld & 7) || (ldq & 7)) return 1003;
+  if (rows == 0) return 0;
+  ats::quantize_rows_int8_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ld, static_cast<int8_t*>(q), ldq, scale, cols, static_cast<const __nv_bfloat16*>(inv_smooth));
+  return int(cudaGetLastError());
 }

@@ -234,6 +234,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
       tmem_ld_32x32(taddr + c * 32, gr);
       tmem_ld_32x32(taddr + 128 + c * 32, ur);
       tmem_ld_wait();
+      if (p.fp8 == 2) {  // int8 operands: the accumulator columns hold s32
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          gr[i] = __float_as_uint(__int2float_rn(int(gr[i])));
+          ur[i] = __float_as_uint(__int2float_rn(int(ur[i])));
+        }
+      }
       if (row_ok) {
         // eight columns: h, gate and up as four packed bf16 pairs each
         auto piece = [&](int v, int col, uint4& hq, uint4& gq4, uint4& uq4) {
@@ -385,6 +392,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
       if (have_acc) {
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
+        if (p.fp8 == 2) {  // int8 operands: the accumulator columns hold s32
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__int2float_rn(int(r[i])));
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = 0;
@@ -614,8 +625,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = p.fp8 ? make_idesc(BM, BN, 0, 0, 0, 0)  // e4m3 x e4m3, both K-major
-                                   : make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
+      const uint32_t idesc = p.fp8 == 2 ? make_idesc_i8(BM, BN)           // s8 x s8 -> s32, both K-major
+                             : p.fp8 ? make_idesc(BM, BN, 0, 0, 0, 0)   // e4m3 x e4m3, both K-major
+                                     : make_idesc(BM, BN, 1, 1, p.a_mn, p.b_mn);
       int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
       bool ok = true;
       // K-major operand: 32 bytes per MMA along the swizzle row; MN-major: 16 K-rows of 128 bytes per MMA
@@ -644,8 +656,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint64_t adesc = desc_advance(a_desc0, uint32_t(stage) * A_STAGE_BYTES);
           const uint64_t bdesc = desc_advance(b_desc0, uint32_t(stage) * B_STAGE_BYTES);
           if (p.fp8) {
+            if (p.fp8 == 2) {
 #pragma unroll
-            for (int k = 0; k < BK / UK; ++k) tc_mma_f8(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+              for (int k = 0; k < BK / UK; ++k) tc_mma_i8(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+            } else {
+#pragma unroll
+              for (int k = 0; k < BK / UK; ++k) tc_mma_f8(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+            }
           } else {
 #pragma unroll
             for (int k = 0; k < BK / UK; ++k) tc_mma_f16(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
@@ -856,7 +873,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = p.fp8 ? make_idesc(PAIR_BM, BN, 0, 0, 0, 0) : make_idesc(PAIR_BM, BN, 1, 1, p.a_mn, p.b_mn);
+      const uint32_t idesc = p.fp8 == 2 ? make_idesc_i8(PAIR_BM, BN)
+                             : p.fp8 ? make_idesc(PAIR_BM, BN, 0, 0, 0, 0) : make_idesc(PAIR_BM, BN, 1, 1, p.a_mn, p.b_mn);
       int stage = 0, phase = 0, acc = 0, acc_phase = 0, g_hint = 0;
       bool ok = true;
       const uint64_t a_desc0 = p.a_mn ? make_smem_desc_sw128(smem_u32(sA), BK * 128, 1024) : make_smem_desc_sw128(smem_u32(sA), 16, 1024);
@@ -883,8 +901,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const uint64_t adesc = desc_advance(a_desc0, uint32_t(stage) * A_STAGE_BYTES);
           const uint64_t bdesc = desc_advance(b_desc0, uint32_t(stage) * PAIR_B_STAGE_BYTES);
           if (p.fp8) {
+            if (p.fp8 == 2) {
 #pragma unroll
-            for (int k = 0; k < BK / UK; ++k) tc_mma_f8_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+              for (int k = 0; k < BK / UK; ++k) tc_mma_i8_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+            } else {
+#pragma unroll
+              for (int k = 0; k < BK / UK; ++k) tc_mma_f8_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
+            }
           } else {
 #pragma unroll
             for (int k = 0; k < BK / UK; ++k) tc_mma_f16_pair(d_tmem, adesc + k * a_step16, bdesc + k * b_step16, idesc, (kb | k) != 0);
@@ -1106,12 +1129,12 @@ ATS_API int ats_splitk_reduce(const float* part, int splits, long long n_inner, 
 // fp8 (e4m3) A [groups x M, K] and B [weights x N, K], both K-major and row-quantised: D = (A_q B_q^T) * row_scale * col_scale.
 // a_gs_mn / b_gs_mn: row shift per group / per weight inside the 2-D operand; rs_gs / cs_gs: scale offsets per group / weight.
 // Epilogues: store, +C, SwiGLU (up_offset as in the bf16 entry).  ragged: 0, or 1 with per-group row counts.
-ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long long lda, const void* B, long long b_rows,
-                         long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
-                         int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
-                         int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
-                         const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
-                         void* stream) {
+static int gemm_8bit(int kind, const void* A, long long a_rows, long long a_cols, long long lda, const void* B, long long b_rows,
+                     long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
+                     int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
+                     int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
+                     const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
+                     void* stream) {
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
     cudaFree(0);
@@ -1135,11 +1158,33 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
   p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1; p.scatter_rows = 0;
   p.b_packed = 0; p.b_kblocks = 0;
-  p.fp8 = 1; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
+  p.fp8 = kind; p.row_scale = row_scale; p.col_scale = col_scale; p.rs_gs = rs_gs; p.cs_gs = cs_gs;
   p.n_copy = 0; p.n_rot = 0; p.own_row0 = 0; p.own_rows = 0; p.prof = nullptr;
   p.n_edge = 0; p.edge_chunk[0] = p.edge_chunk[1] = -1;
   p.out2 = nullptr; p.ldout2 = 0; p.out2_gs = 0;
   return launch_gemm(ma, mb, p, epilogue, groups, M, N, max_ctas, stream);
+}
+
+ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long long lda, const void* B, long long b_rows,
+                         long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
+                         int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
+                         int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
+                         const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
+                         void* stream) {
+  return gemm_8bit(1, A, a_rows, a_cols, lda, B, b_rows, b_cols, ldb, D, ldd, C, ldc, aux, ldaux, M, N, K, alpha, epilogue, up_offset, groups,
+                   ragged, counts, a_gs_mn, b_gs_mn, d_gs, c_gs, aux_gs, b_div, row_scale, rs_gs, col_scale, cs_gs, status, max_ctas, stream);
+}
+
+// Signed 8-bit operands (W8A8: activations quantised per token, weights per output channel), s32 accumulation on `kind::i8`,
+// both scales applied in the epilogue.  Same arguments and epilogues as the e4m3 entry.
+ATS_API int ats_gemm_int8(const void* A, long long a_rows, long long a_cols, long long lda, const void* B, long long b_rows,
+                          long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
+                          int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
+                          int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
+                          const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
+                          void* stream) {
+  return gemm_8bit(2, A, a_rows, a_cols, lda, B, b_rows, b_cols, ldb, D, ldd, C, ldc, aux, ldaux, M, N, K, alpha, epilogue, up_offset, groups,
+                   ragged, counts, a_gs_mn, b_gs_mn, d_gs, c_gs, aux_gs, b_div, row_scale, rs_gs, col_scale, cs_gs, status, max_ctas, stream);
 }
 
 // All-gather + GEMM in one kernel: D = A [M, K] * B^T with B [b_rows, K] row-sharded over `b_shards` GPUs.  `b_src` is a DEVICE

@@ -323,3 +323,51 @@ def test_weight_gradient_split_model_and_fp8_weight_copies():
     stacked = torch.randn(3, 16, 32)
     qe, se = fp8.quantized_weight_t(stacked)
     assert qe.shape == (3 * 32, 16) and se.shape == (96,)
+
+
+def test_int8_and_smoothquant_post_training_quantisation_cpu():
+    """W8A8 int8 through the manager (PyTorch definitions on CPU): close to the unquantised logits; SmoothQuant refuses to run
+    uncalibrated and, on activations with outlier channels, beats plain int8."""
+    from adaptivetrainingsystem_b200.ops import int8
+    from adaptivetrainingsystem_b200.training.precision import QuantizationManager
+
+    class _C:
+        quantization_bits = 8
+
+        def __init__(self, method):
+            self.quantization_method = method
+
+    torch.manual_seed(0)
+    cfg = ModelConfig(vocab_size=256, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=128, seq_length=32)
+    ids = torch.randint(0, 256, (2, 32))
+    try:
+        model = DeepSeekTransformer(cfg)
+        with torch.no_grad():
+            ref = model(ids, return_aux_loss=False)
+        with pytest.raises(RuntimeError):
+            QuantizationManager(_C("smoothquant")).quantize_model(model)
+        qm = QuantizationManager(_C("int8"))
+        qm.quantize_model(model)
+        with torch.no_grad():
+            out = model(ids, return_aux_loss=False)
+        assert qm.status()["applied"] and qm.status()["tensors"] >= 7
+        assert ((out - ref).norm() / ref.norm()).item() < 3e-2
+        # outlier channels: a few input channels 50 x larger than the rest
+        int8.clear()
+        x = torch.randn(64, 128)
+        x[:, :4] *= 50.0
+        w = torch.randn(96, 128) * 0.05
+        exact = x @ w.t()
+        int8.set_enabled(True)
+        with torch.no_grad():
+            plain = int8.linear_int8(x, w)
+        int8.record(x, w)
+        int8.finish_calibration(0.5)
+        with torch.no_grad():
+            smooth = int8.linear_int8(x, w)
+        e_plain = ((plain - exact).norm() / exact.norm()).item()
+        e_smooth = ((smooth - exact).norm() / exact.norm()).item()
+        assert e_smooth < 0.6 * e_plain and e_smooth < 2e-2, (e_plain, e_smooth)
+    finally:
+        int8.set_enabled(False)
+        int8.clear()

@@ -921,3 +921,57 @@ def test_fused_decode_folds_match_separate_launches():
     assert torch.equal(both[0], plain) and both[1] is not None
     _close(both[1], ops.rms_norm(plain, nw, 1e-6), tol=1e-2, what="combine + norm")
     ops.check_status()
+
+
+def test_int8_gemm_and_quantised_model():
+    """kind::i8 tensor-core GEMM: quantise kernel against its definition, products against the dequantised operands (store, +C,
+    SwiGLU), and a small model served in int8 / SmoothQuant against its bf16 logits."""
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.ops import int8
+    from adaptivetrainingsystem_b200.training.precision import QuantizationManager
+    torch.manual_seed(23)
+    x = _rand(300, 512)
+    sm = (0.5 + torch.rand(512, device=DEV)).bfloat16()
+    q, s = int8.quantize_rows(x, sm)
+    qr, sr = int8.quantize_rows_reference(x, sm)
+    assert torch.allclose(s, sr, rtol=1e-3) and (q.int() - qr.int()).abs().max().item() <= 1
+    for (M, N, K) in [(128, 256, 128), (300, 520, 512), (1024, 2560, 2048), (64, 4096, 4096)]:
+        a, b = _rand(M, K), _rand(N, K, scale=0.05)
+        res = _rand(M, N)
+        aq, sa = int8.quantize_rows(a)
+        bq, sb = int8.quantize_rows(b)
+        ref = (aq.float() * sa[:, None]) @ (bq.float() * sb[:, None]).t() + res.float()
+        out = int8.gemm_nt_int8(aq, sa, bq, sb, add=res)
+        _close(out, ref, tol=1e-2, what=f"int8 gemm {M}x{N}x{K}")
+        _close(out, a.float() @ b.float().t() + res.float(), tol=5e-2, what="int8 gemm vs unquantised")
+    a, w = _rand(256, 512), _rand(2 * 384, 512, scale=0.05)
+    aq, sa = int8.quantize_rows(a)
+    wq, sw = int8.quantize_rows(w)
+    h = int8.gemm_nt_int8(aq, sa, wq, sw, swiglu=True)
+    gu = ((aq.float() * sa[:, None]) @ (wq.float() * sw[:, None]).t()).bfloat16().float()
+    _close(h, torch.nn.functional.silu(gu[:, :384]) * gu[:, 384:], tol=2e-2, what="int8 swiglu")
+
+    class _C:
+        quantization_bits = 8
+        quantization_method = "smoothquant"
+
+    cfg = ModelConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=512, seq_length=128)
+    with torch.device(DEV):
+        torch.set_default_dtype(torch.bfloat16)
+        model = DeepSeekTransformer(cfg)
+        torch.set_default_dtype(torch.float32)
+    ids = torch.randint(0, 1024, (2, 128), device=DEV)
+    try:
+        with torch.no_grad():
+            ref = model(ids, return_aux_loss=False).float()
+        qm = QuantizationManager(_C())
+        assert qm.calibrate(model, [ids]) >= 7
+        qm.quantize_model(model)
+        with torch.no_grad():
+            out = model(ids, return_aux_loss=False).float()
+        assert ((out - ref).norm() / ref.norm()).item() < 5e-2
+    finally:
+        int8.set_enabled(False)
+        int8.clear()
+    ops.check_status()
