@@ -3,7 +3,7 @@
 the fraction of the measured roofline (``MEASURED_PEAKS.json``: cuBLAS bf16 burst throughput, STREAM-style copy
 bandwidth).  A library column (cuBLAS / PyTorch eager) is printed next to each kernel for comparison.
 
-    python benchmarks/bench_kernels.py [--quick] [--json out.json] [--only gemm,fp8,swiglu,grouped,memory,adamw,attention]
+    python benchmarks/bench_kernels.py [--quick] [--json out.json] [--only gemm,fp8,int8,swiglu,grouped,memory,adamw,attention]
 
 ``--only memory`` (or any other single section) keeps a run short enough for a profiler capture of one kernel.
 """
@@ -33,7 +33,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--json", default="")
-    ap.add_argument("--only", default="", help="comma-separated sections: gemm, fp8, swiglu, grouped, memory, adamw, attention")
+    ap.add_argument("--only", default="", help="comma-separated sections: gemm, fp8, int8, swiglu, grouped, memory, adamw, attention")
     args = ap.parse_args()
     only = {t.strip() for t in args.only.split(",") if t.strip()}
 
@@ -73,6 +73,16 @@ def main():
         report(f"gemm_nt_fp8 {m}x{n}x{k}", time_cuda(lambda: fp8.gemm_nt_fp8(aq, sa, bq, sb, out=out)), 2.0 * m * n * k,
                lib_ms=time_cuda(lambda: torch.matmul(a, b.t(), out=out)))
         report(f"quantize_rows_e4m3 {m}x{k}", time_cuda(lambda: fp8.quantize_rows(a)), nbytes=3.0 * m * k)
+    # int8 (kind::i8, s32 accumulation, the same scales) on the same shapes plus two decode-sized ones
+    from adaptivetrainingsystem_b200.ops import int8
+    for (m, n, k) in [(8192, 8192, 8192), (16384, 2560, 2048), (64, 28672, 4096), (64, 4096, 14336)] if want("int8") else []:
+        a, b = rnd(m, k), rnd(n, k, scale=0.05)
+        aq, sa = int8.quantize_rows(a)
+        bq, sb = int8.quantize_rows(b)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        report(f"gemm_nt_int8 {m}x{n}x{k}", time_cuda(lambda: int8.gemm_nt_int8(aq, sa, bq, sb, out=out)), 2.0 * m * n * k,
+               nbytes=float(n * k), lib_ms=time_cuda(lambda: torch.matmul(a, b.t(), out=out)))
+        report(f"quantize_rows_int8 {m}x{k}", time_cuda(lambda: int8.quantize_rows(a)), nbytes=3.0 * m * k)
     # SwiGLU-fused GEMM
     for (m, k, i) in [(8192, 2048, 5632), (4096, 4096, 14336)] if want("swiglu") else []:
         a, w = rnd(m, k), rnd(2 * i, k, scale=0.05)
