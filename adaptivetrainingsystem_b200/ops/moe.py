@@ -396,11 +396,19 @@ def moe_ffn_serving(x: torch.Tensor, wg: torch.Tensor, top_k: int, temperature: 
     E = w1.shape[0]
     C = (T + 127) // 128 * 128
     idx, w = serve_gate_route(x, wg, top_k, temperature)
-    xe = torch.empty(E, C, H, dtype=x.dtype, device=x.device)
-    slot_pos, counts, totals = serve_plan_dispatch(x, idx, E, C, out=xe)
+    from . import fp8
     packed = bool(getattr(w1, "_ats_packed", False))
-    h = G.grouped_nt(xe, w1, counts, swiglu=True, packed=packed)
-    ye = G.grouped_nt(h, w2, counts, packed=packed)
+    if fp8.enabled() and not packed and fp8.grouped_usable(x, w1.shape[1], w1.shape[2]) and w2.shape[2] % 16 == 0:
+        # post-training e4m3 experts: both products stream half the bytes (rows no token uses are zero so that their scales stay finite)
+        xe = torch.zeros(E, C, H, dtype=x.dtype, device=x.device)
+        slot_pos, counts, totals = serve_plan_dispatch(x, idx, E, C, out=xe)
+        h = fp8.grouped_nt(xe, w1, counts, swiglu=True)
+        ye = fp8.grouped_nt(h, w2, counts)
+    else:
+        xe = torch.empty(E, C, H, dtype=x.dtype, device=x.device)
+        slot_pos, counts, totals = serve_plan_dispatch(x, idx, E, C, out=xe)
+        h = G.grouped_nt(xe, w1, counts, swiglu=True, packed=packed)
+        ye = G.grouped_nt(h, w2, counts, packed=packed)
     out = serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, buf=ye, residual=residual, next_norm=next_norm)
     return out, totals   # with next_norm, out is the pair (output, normalised output)
 

@@ -161,6 +161,11 @@ class QuantizationManager:
                     q, sc = fp8.quantized_weight(p)
                     self.quantized_tensors += 1
                     self.quantized_bytes += q.numel() + sc.numel() * 4
+                elif p.dim() == 3 and getattr(p, "_ats_expert", False) and p.is_cuda and p.dtype == torch.bfloat16 and p.shape[2] % 16 == 0 \
+                        and not getattr(p, "_ats_packed", False):
+                    q, sc = fp8.quantized_expert_weight(p)      # stacked expert weights: per output channel of every expert
+                    self.quantized_tensors += 1
+                    self.quantized_bytes += q.numel() + sc.numel() * 4
         self.applied = True
         return model
 

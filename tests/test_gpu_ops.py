@@ -975,3 +975,39 @@ def test_int8_gemm_and_quantised_model():
         int8.set_enabled(False)
         int8.clear()
     ops.check_status()
+
+
+def test_fp8_experts_in_the_serving_path():
+    """Post-training e4m3 quantisation reaches the expert products of a decode-sized step: close to the bf16 layer."""
+    from types import SimpleNamespace
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.models.transformer import MoEFFNLayer
+    from adaptivetrainingsystem_b200.ops import fp8
+    from adaptivetrainingsystem_b200.training.precision import QuantizationManager
+    torch.manual_seed(6)
+    cfg = ModelConfig(vocab_size=512, hidden_size=512, num_layers=1, num_heads=8, num_kv_heads=2, intermediate_size=1024, seq_length=64,
+                      use_moe=True, num_experts=4, moe_top_k=2, routing_noise_std=0.0)
+    with torch.device(DEV):
+        torch.set_default_dtype(torch.bfloat16)
+        layer = MoEFFNLayer(cfg, 0)
+        torch.set_default_dtype(torch.float32)
+    with torch.no_grad():
+        layer.gate.weight.normal_(0, 0.05)
+        layer.experts_w1.normal_(0, 0.04)
+        layer.experts_w2.normal_(0, 0.04)
+    layer.eval()
+    x = _rand(1, 32, 512)
+    res = _rand(1, 32, 512)
+    try:
+        with torch.no_grad():
+            ref, _ = layer(x, res)
+            qm = QuantizationManager(SimpleNamespace(quantization_method="fp8", quantization_bits=8))
+            qm.quantize_model(layer)
+            assert qm.status()["tensors"] >= 2          # both stacked expert weights were quantised up front
+            out, _ = layer(x, res)
+        delta, scale = (out.float() - ref.float()), (ref.float() - res.float())
+        assert (delta.norm() / scale.norm()).item() < 8e-2       # relative to the layer's own contribution
+    finally:
+        fp8.set_enabled(False)
+        fp8.clear_weight_cache()
+    ops.check_status()
