@@ -601,20 +601,27 @@ slot_dot_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restri
 // (2) ordered compaction of the membership flags, one CTA per sequence.  sel[b, i] = position, i < keep.
 __global__ void __launch_bounds__(256)
 mod_rank_kernel(const float* __restrict__ scores, int* __restrict__ member, int seq_len, int keep) {
+  // 64 positions per CTA, four threads per position: each counts a quarter of the sequence, a shuffle adds the quarters
   extern __shared__ float s_sc[];
   const float* sc = scores + (long long)blockIdx.y * seq_len;
   for (int i = threadIdx.x; i < seq_len; i += blockDim.x) s_sc[i] = sc[i];
   __syncthreads();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= seq_len) return;
-  const float v = s_sc[i];
+  const int i = blockIdx.x * 64 + (threadIdx.x >> 2), part = threadIdx.x & 3;
+  const bool live = i < seq_len;
+  const float v = live ? s_sc[i] : 0.f;
+  const int quarter = (seq_len + 3) >> 2;
+  const int j0 = part * quarter, j1 = min(seq_len, j0 + quarter);
   int rank = 0;
+  if (live) {
 #pragma unroll 8
-  for (int j = 0; j < seq_len; ++j) {
-    const float o = s_sc[j];
-    rank += (o > v) || (o == v && j < i);
+    for (int j = j0; j < j1; ++j) {
+      const float o = s_sc[j];
+      rank += (o > v) || (o == v && j < i);
+    }
   }
-  member[(long long)blockIdx.y * seq_len + i] = rank < keep;
+  rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+  rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+  if (live && part == 0) member[(long long)blockIdx.y * seq_len + i] = rank < keep;
 }
 
 __global__ void __launch_bounds__(1024)
@@ -799,7 +806,7 @@ ATS_API int ats_mod_select(const float* scores, int* sel, int* member, int batch
   if (seq_len > 8192 || keep > seq_len || !member) return 1003;
   if (batch == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  mod_rank_kernel<<<dim3((seq_len + 255) / 256, batch), 256, seq_len * 4, s>>>(scores, member, seq_len, keep);
+  mod_rank_kernel<<<dim3((seq_len + 63) / 64, batch), 256, seq_len * 4, s>>>(scores, member, seq_len, keep);
   mod_compact_kernel<<<batch, 1024, 0, s>>>(member, sel, seq_len, keep);
   return int(cudaGetLastError());
 }
