@@ -601,7 +601,7 @@ slot_dot_kernel(__nv_bfloat16* const* __restrict__ src_base, const int* __restri
 // (2) ordered compaction of the membership flags, one CTA per sequence.  sel[b, i] = position, i < keep.
 __global__ void __launch_bounds__(256)
 mod_rank_kernel(const float* __restrict__ scores, int* __restrict__ member, int seq_len, int keep) {
-  // 64 positions per CTA, four threads per position: each counts a quarter of the sequence, a shuffle adds the quarters
+  // 64 positions per CTA, four threads per position: each counts every fourth score, a shuffle adds the four counts
   extern __shared__ float s_sc[];
   const float* sc = scores + (long long)blockIdx.y * seq_len;
   for (int i = threadIdx.x; i < seq_len; i += blockDim.x) s_sc[i] = sc[i];
@@ -609,12 +609,11 @@ mod_rank_kernel(const float* __restrict__ scores, int* __restrict__ member, int 
   const int i = blockIdx.x * 64 + (threadIdx.x >> 2), part = threadIdx.x & 3;
   const bool live = i < seq_len;
   const float v = live ? s_sc[i] : 0.f;
-  const int quarter = (seq_len + 3) >> 2;
-  const int j0 = part * quarter, j1 = min(seq_len, j0 + quarter);
   int rank = 0;
   if (live) {
+    // the four threads of a position take every fourth score: the four addresses of a step are neighbours (no bank conflict)
 #pragma unroll 8
-    for (int j = j0; j < j1; ++j) {
+    for (int j = part; j < seq_len; j += 4) {
       const float o = s_sc[j];
       rank += (o > v) || (o == v && j < i);
     }
