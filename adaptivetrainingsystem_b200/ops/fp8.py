@@ -159,7 +159,7 @@ def grouped_nt_fp8(x: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, n: int, 
     err = _fns().ats_gemm_fp8(_lib.ptr(xq), Gn * C, K, xq.stride(0), _lib.ptr(wq), wq.shape[0], K, wq.stride(0), _lib.ptr(out), n_out, None, 0,
                               _lib.ptr(pre_act), n if pre_act is not None else 0, C, n_out, K, 1.0, G.EPI_SWIGLU if swiglu else G.EPI_STORE,
                               n // 2 if swiglu else 0, Gn, 1, _lib.ptr(counts), C, n, C * n_out, 0, C * n if pre_act is not None else 0, b_div,
-                              _lib.ptr(xs), C, _lib.ptr(ws), n, _lib.ptr(st), 0, _lib.stream_ptr(x.device))
+                              _lib.ptr(xs), C, _lib.ptr(ws), n, 0, 0, _lib.ptr(st), 0, _lib.stream_ptr(x.device))
     _lib.check(err, "ats_gemm_fp8 (grouped)")
     return out
 
@@ -202,11 +202,24 @@ def gemm_nt_fp8(aq: torch.Tensor, a_scale: torch.Tensor, bq: torch.Tensor, b_sca
     n_out = N // 2 if swiglu else N
     if out is None:
         out = torch.empty(M, n_out, dtype=out_dtype, device=aq.device)
-    epi = G.EPI_SWIGLU if swiglu else (G.EPI_ADDC if add is not None else G.EPI_STORE)
     st = _lib.status_tensor(aq.device)
+    splits = G._skinny_splits(M, N, K) if (not swiglu and G.SPLIT_K_SKINNY and out.is_contiguous() and out_dtype == torch.bfloat16
+                                           and (add is None or add.is_contiguous()) and N % 8 == 0) else 1
+    if splits > 1 and (K // splits) % 128 == 0:
+        # a handful of rows against a large weight: slices of the reduction run as groups with fp32 partial outputs (scaled in the
+        # epilogue, the scales distribute over the sum) so that every SM streams part of the weight; one launch folds them
+        kp = K // splits
+        part = torch.empty(splits, M, N, dtype=torch.float32, device=aq.device)
+        err = _fns().ats_gemm_fp8(_lib.ptr(aq), M, K, aq.stride(0), _lib.ptr(bq), N, K, bq.stride(0), _lib.ptr(part), N, None, 0, None, 0, M, N, kp,
+                                  1.0, G.EPI_F32, 0, splits, 0, None, 0, 0, M * N, 0, 0, 1, _lib.ptr(a_scale), 0, _lib.ptr(b_scale), 0, kp, kp,
+                                  _lib.ptr(st), 0, _lib.stream_ptr(aq.device))
+        _lib.check(err, "ats_gemm_fp8 (reduction slices)")
+        G._fold_partials(part, splits, M * N, 1, out, add)
+        return out
+    epi = G.EPI_SWIGLU if swiglu else (G.EPI_ADDC if add is not None else G.EPI_STORE)
     err = _fns().ats_gemm_fp8(_lib.ptr(aq), M, K, aq.stride(0), _lib.ptr(bq), N, K, bq.stride(0), _lib.ptr(out), out.stride(0), _lib.ptr(add),
                               add.stride(0) if add is not None else 0, _lib.ptr(aux), aux.stride(0) if aux is not None else 0, M, n_out, K,
-                              1.0, epi, N // 2 if swiglu else 0, 1, 0, None, 0, 0, 0, 0, 0, 1, _lib.ptr(a_scale), 0, _lib.ptr(b_scale), 0,
+                              1.0, epi, N // 2 if swiglu else 0, 1, 0, None, 0, 0, 0, 0, 0, 1, _lib.ptr(a_scale), 0, _lib.ptr(b_scale), 0, 0, 0,
                               _lib.ptr(st), 0, _lib.stream_ptr(aq.device))
     _lib.check(err, "ats_gemm_fp8")
     return out

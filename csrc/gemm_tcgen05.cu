@@ -420,8 +420,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const TileCoord
         for (int v = 0; v < 8; ++v) {
           const int col = colbase + v * 4;
           if (col < p.N) {
-            float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
-                                   __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
+            // rs = alpha (x the row scale of an 8-bit product); cs = its column scales: both distribute over the sum of the slices
+            float4 o = make_float4(__uint_as_float(r[v * 4]) * rs, __uint_as_float(r[v * 4 + 1]) * rs,
+                                   __uint_as_float(r[v * 4 + 2]) * rs, __uint_as_float(r[v * 4 + 3]) * rs);
+            if (cs) {
+              const float4 c4 = *reinterpret_cast<const float4*>(cs + col);
+              o.x *= c4.x; o.y *= c4.y; o.z *= c4.z; o.w *= c4.w;
+            }
             if (p.beta) {
               float4 old = *reinterpret_cast<float4*>(drow + col);
               o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -1133,8 +1138,8 @@ static int gemm_8bit(int kind, const void* A, long long a_rows, long long a_cols
                      long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
                      int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
                      int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
-                     const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
-                     void* stream) {
+                     const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int a_gs_k, int b_gs_k, int* status,
+                     int max_ctas, void* stream) {
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
     cudaFree(0);
@@ -1142,18 +1147,18 @@ static int gemm_8bit(int kind, const void* A, long long a_rows, long long a_cols
   }
   if (groups < 1 || groups > MAX_GROUPS) return 1002;
   if ((N & 7) || (K & 15) || (lda & 15) || (ldb & 15) || (ldd & 7) || (d_gs & 7) || (a_gs_mn & 7) || (b_gs_mn & 7)) return 1003;
-  if (epilogue == kF32 || (epilogue == kSwiGLU && (up_offset & 7))) return 1004;
-  if ((ragged && !counts) || ragged > 1 || b_div < 1) return 1005;
+  if ((epilogue == kSwiGLU && (up_offset & 7)) || (epilogue == kF32 && ((ldd & 3) || (N & 3)))) return 1004;
+  if ((ragged && !counts) || ragged > 1 || b_div < 1 || (a_gs_k & 127) || (b_gs_k & 127)) return 1005;
   CUtensorMap ma, mb;
   int e;
   if ((e = make_tmap_2d(&ma, A, a_rows, a_cols, lda, 1, 128, 128))) return e;
   if ((e = make_tmap_2d(&mb, B, b_rows, b_cols, ldb, 1, 128, 128))) return e;
   GemmArgs p;
   p.M = M; p.N = N; p.K = K; p.groups = groups; p.ragged = ragged; p.counts = counts;
-  p.a_gs_mn = a_gs_mn; p.a_gs_k = 0; p.b_gs_mn = b_gs_mn; p.b_gs_k = 0;
+  p.a_gs_mn = a_gs_mn; p.a_gs_k = a_gs_k; p.b_gs_mn = b_gs_mn; p.b_gs_k = b_gs_k;  // K shifts per group: reduction slices
   p.d_gs = d_gs; p.c_gs = c_gs; p.aux_gs = aux_gs;
   p.D = static_cast<__nv_bfloat16*>(D); p.C = static_cast<const __nv_bfloat16*>(C);
-  p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = nullptr;
+  p.aux = static_cast<__nv_bfloat16*>(aux); p.Df32 = epilogue == kF32 ? static_cast<float*>(D) : nullptr;
   p.ldd = ldd; p.ldc = ldc; p.ldaux = ldaux; p.a_mn = 0; p.b_mn = 0; p.epilogue = epilogue;
   p.up_offset = up_offset; p.alpha = alpha; p.beta = 0; p.status = status;
   p.b_div = b_div; p.k_segs = 1; p.seg_stride = 0; p.d_table = nullptr; p.k_split = 1; p.scatter_rows = 0;
@@ -1169,10 +1174,11 @@ ATS_API int ats_gemm_fp8(const void* A, long long a_rows, long long a_cols, long
                          long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
                          int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
                          int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
-                         const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
-                         void* stream) {
+                         const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int a_gs_k, int b_gs_k,
+                         int* status, int max_ctas, void* stream) {
   return gemm_8bit(1, A, a_rows, a_cols, lda, B, b_rows, b_cols, ldb, D, ldd, C, ldc, aux, ldaux, M, N, K, alpha, epilogue, up_offset, groups,
-                   ragged, counts, a_gs_mn, b_gs_mn, d_gs, c_gs, aux_gs, b_div, row_scale, rs_gs, col_scale, cs_gs, status, max_ctas, stream);
+                   ragged, counts, a_gs_mn, b_gs_mn, d_gs, c_gs, aux_gs, b_div, row_scale, rs_gs, col_scale, cs_gs, a_gs_k, b_gs_k, status, max_ctas,
+                   stream);
 }
 
 // Signed 8-bit operands (W8A8: activations quantised per token, weights per output channel), s32 accumulation on `kind::i8`,
@@ -1181,10 +1187,11 @@ ATS_API int ats_gemm_int8(const void* A, long long a_rows, long long a_cols, lon
                           long long b_cols, long long ldb, void* D, int ldd, const void* C, int ldc, void* aux, int ldaux, int M,
                           int N, int K, float alpha, int epilogue, int up_offset, int groups, int ragged, const int* counts,
                           int a_gs_mn, int b_gs_mn, long long d_gs, long long c_gs, long long aux_gs, int b_div,
-                          const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int* status, int max_ctas,
-                          void* stream) {
+                          const float* row_scale, long long rs_gs, const float* col_scale, long long cs_gs, int a_gs_k, int b_gs_k,
+                          int* status, int max_ctas, void* stream) {
   return gemm_8bit(2, A, a_rows, a_cols, lda, B, b_rows, b_cols, ldb, D, ldd, C, ldc, aux, ldaux, M, N, K, alpha, epilogue, up_offset, groups,
-                   ragged, counts, a_gs_mn, b_gs_mn, d_gs, c_gs, aux_gs, b_div, row_scale, rs_gs, col_scale, cs_gs, status, max_ctas, stream);
+                   ragged, counts, a_gs_mn, b_gs_mn, d_gs, c_gs, aux_gs, b_div, row_scale, rs_gs, col_scale, cs_gs, a_gs_k, b_gs_k, status, max_ctas,
+                   stream);
 }
 
 // All-gather + GEMM in one kernel: D = A [M, K] * B^T with B [b_rows, K] row-sharded over `b_shards` GPUs.  `b_src` is a DEVICE

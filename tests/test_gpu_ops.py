@@ -532,7 +532,7 @@ def test_fp8_quantize_and_gemm():
     deq = q.float() * s[:, None]
     assert ((deq - x.float()).abs() <= x.float().abs() * 0.0625 + s[:, None] * 0.002).all()
     assert (q.float() == qr.float()).float().mean().item() > 0.999
-    for (M, N, K) in [(512, 768, 1024), (1000, 2560, 2048), (130, 136, 144)]:
+    for (M, N, K) in [(512, 768, 1024), (1000, 2560, 2048), (130, 136, 144), (48, 4096, 4096)]:
         a, b = _rand(M, K), _rand(N, K) * 0.05
         aq, sa = fp8.quantize_rows(a)
         bq, sb = fp8.quantize_rows(b)
