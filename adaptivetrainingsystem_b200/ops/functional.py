@@ -59,7 +59,7 @@ def _L():
         sig("ats_combine_rows", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_serve_gate_route", _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _c_int, _c_f, _vp)
         sig("ats_serve_plan_dispatch", _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _vp)
-        sig("ats_serve_combine", _vp, _vp, _c_ll, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _vp, _vp, _c_f, _vp)
+        sig("ats_serve_combine", _vp, _vp, _c_ll, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, _vp, _vp, _c_f, _vp, _vp, _c_int, _vp, _vp)
         sig("ats_slot_dot", _vp, _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_int, _vp)
         sig("ats_mod_select", _vp, _vp, _vp, _c_int, _c_int, _c_int, _vp)
         sig("ats_mod_scores", _vp, _vp, _vp, _vp, _c_ll, _c_int, _c_f, _vp)

@@ -329,7 +329,7 @@ def unpack_kmajor(w: torch.Tensor) -> torch.Tensor:
 
 def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: bool = False,
                pre_act: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, b_div: int = 1,
-               d_table: Optional[torch.Tensor] = None, packed: bool = False, k_split: int = 1) -> torch.Tensor:
+               d_table: Optional[torch.Tensor] = None, packed: bool = False, k_split: int = 1, fold=None) -> torch.Tensor:
     """x[G,C,K] · w[E,N,K]^T -> [G,C,N] (or [G,C,N/2] through SwiGLU) for the first counts[g] rows of every
     group; group g uses weight g // b_div (G = E * b_div: several token blocks per expert, one per source rank).
     Rows beyond the padded count are left untouched.  ``d_table`` (int64 [G]) redirects the output of group g to
@@ -364,7 +364,8 @@ def grouped_nt(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, swiglu: b
         _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 2 if packed else 0, part, N, None, 0, None, 0, C, N, K // k_split,
              epilogue=EPI_F32, groups=Gn * k_split, ragged=1, counts=counts, a_gs_mn=C, b_gs_mn=N, d_gs=C * N, b_div=b_div,
              k_split=k_split)
-        _fold_partials(part, k_split, C * N, Gn, out)
+        # ``fold(part, k_split, n_inner, n_outer, out)`` replaces the plain fold (e.g. one that also signals the peers that will read out)
+        (fold or _fold_partials)(part, k_split, C * N, Gn, out)
         return out
     _raw(x, Gn * C, K, K, 0, w, w.shape[0] * N, K, K, 2 if packed else 0, out, n_out, None, 0, pre_act,
          N if pre_act is not None else 0,

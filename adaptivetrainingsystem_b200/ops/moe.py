@@ -369,10 +369,11 @@ def serve_plan_dispatch(x: torch.Tensor, topk_idx: torch.Tensor, num_experts: in
 
 def serve_combine(topk_idx: torch.Tensor, slot_pos: torch.Tensor, topk_w: torch.Tensor, tokens: int, hidden: int, dtype, device,
                   buf: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None,
-                  residual: Optional[torch.Tensor] = None, next_norm=None):
+                  residual: Optional[torch.Tensor] = None, next_norm=None, wait=None):
     """out[t] = residual[t] + sum_j w[t, j] * row(e_j, pos_j); one CTA per token.  Rows come from ``buf`` [E, C, H] or from the
     blocks ``table`` points to (pulled over NVLink when they live on the experts' owners).  ``next_norm`` = (weight, eps): the same
-    launch also writes RMSNorm(out) * weight, the input of the next block, and the result is ``(out, normed)``."""
+    launch also writes RMSNorm(out) * weight, the input of the next block, and the result is ``(out, normed)``.  ``wait`` =
+    (flags int32 [W], epoch int32 [1], experts per rank): the kernel waits for the flag of every owner it pulls from."""
     out = torch.empty(tokens, hidden, dtype=dtype, device=device)
     k = topk_idx.shape[1]
     stride = buf.stride(0) if buf is not None else 0
@@ -380,7 +381,8 @@ def serve_combine(topk_idx: torch.Tensor, slot_pos: torch.Tensor, topk_w: torch.
     normed = torch.empty_like(out) if fuse else None
     _CK(_L().ats_serve_combine(_P(table), _P(buf) if table is None else None, stride, _P(topk_idx), _P(slot_pos), _P(topk_w),
                                _P(residual), _P(out), tokens, k, hidden, _P(next_norm[0]) if fuse else None, _P(normed),
-                               float(next_norm[1]) if fuse else 0.0, _S(device)), "serve_combine")
+                               float(next_norm[1]) if fuse else 0.0, _P(wait[0]) if wait else None, _P(wait[1]) if wait else None,
+                               int(wait[2]) if wait else 0, _P(_lib.status_tensor(device)) if wait else None, _S(device)), "serve_combine")
     if next_norm is not None:
         return out, normed   # normed is None when the fused form did not apply: the caller normalises as usual
     return out

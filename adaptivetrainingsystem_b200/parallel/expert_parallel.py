@@ -32,6 +32,11 @@ from ..ops import moe as M
 from ..ops.functional import _L, _P, _S, _CK, _deliver_grad
 
 
+# Decode-sized steps: the owners' "results are ready" flags travel with the fold of the down projection and are awaited inside the
+# combine kernel (1, default) instead of a flag-barrier launch between the two (0).
+FLAG_SYNC = os.environ.get("ATS_EP_FLAG_SYNC", "1") == "1"
+
+
 class _LayerBuffers:
     """Per-layer exchange buffers (symmetric when fused)."""
 
@@ -109,6 +114,13 @@ class _ServingBuffers:
         self.t_pull_y = (base[owner] + off[1] + block).to(device)
         # every row of a block takes part in the products: rows that no token uses hold zeros or an earlier step's (finite)
         # values, their results are never read, so no row counts need to travel
+        # "my down projection of this call is folded" flags: rank q raises entry q of every peer's array from the launch that folds
+        # its down projection; the combine kernels wait on the entries of the owners they pull from (no barrier launch in between)
+        self.flag_buf = SymmetricBuffer(256, comm.group, device)
+        self.ready_flags = self.flag_buf.tensor(torch.int32, 64)
+        self.ready_flags.zero_()
+        self.flag_table = self.flag_buf.table(0)
+        self.sync_state = torch.zeros(2, dtype=torch.int32, device=device)   # [calls so far (the epoch), CTAs done in the current fold]
         self.counts = torch.full((El,), W * Cs, dtype=torch.int32, device=device)
         self.local_counts = torch.zeros(E, dtype=torch.int32, device=device)
         self.shape_probe = torch.empty(1, dtype=dtype, device=device).expand(E, Cs, H)
@@ -154,6 +166,8 @@ class ExpertParallelComm:
         for b in self._layers.values():
             if getattr(b, "sym", None) is not None:
                 b.sym.close()
+            if getattr(b, "flag_buf", None) is not None:
+                b.flag_buf.close()
         self._layers.clear()
         if self.barrier is not None:
             self.barrier.buf.close()
@@ -301,7 +315,20 @@ def ep_moe_serving(x, wg, top_k, temperature, w1, w2, residual, comm: "ExpertPar
     comm.barrier()
     packed = bool(getattr(w1, "_ats_packed", False))
     h = G.grouped_nt(buf.recv_x, w1, buf.counts, swiglu=True, packed=packed)
-    G.grouped_nt(h, w2, buf.counts, out=buf.own_y, packed=packed, k_split=_down_proj_slices(buf.El, w2.shape[1], w2.shape[2]))
+    ks = _down_proj_slices(buf.El, w2.shape[1], w2.shape[2])
+    if ks > 1 and FLAG_SYNC:
+        # the launch that folds the slices of the down projection raises this rank's flag on every peer, and the combine kernels
+        # wait for the owners they read from: the second barrier launch of the layer is gone
+        def fold(part, splits, n_inner, n_outer, out_rows):
+            from .peer import _L as _PL
+            _lib.check(_PL().ats_splitk_reduce_signal(_lib.ptr(part), splits, n_inner, n_outer, _lib.ptr(out_rows), _lib.ptr(buf.sync_state[1:]),
+                                                      _lib.ptr(buf.sync_state), buf.flag_table, comm.rank, comm.W,
+                                                      _lib.stream_ptr(x.device)), "splitk_reduce_signal")
+        G.grouped_nt(h, w2, buf.counts, out=buf.own_y, packed=packed, k_split=ks, fold=fold)
+        out = M.serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, table=buf.t_pull_y, residual=residual, next_norm=next_norm,
+                              wait=(buf.ready_flags, buf.sync_state, buf.El))
+        return out, None
+    G.grouped_nt(h, w2, buf.counts, out=buf.own_y, packed=packed, k_split=ks)
     comm.barrier()
     out = M.serve_combine(idx, slot_pos, w, T, H, x.dtype, x.device, table=buf.t_pull_y, residual=residual, next_norm=next_norm)
     return out, None   # with next_norm, out is the pair (output, normalised output)

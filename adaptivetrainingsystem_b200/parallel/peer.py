@@ -44,6 +44,7 @@ def _L():
         lib.ats_get_wait_budget_ns.restype = ctypes.c_ulonglong
         lib.ats_get_wait_budget_ns.argtypes = []
         sig("ats_peer_copy", _vp, _vp, _c_ll, _c_int, _vp)
+        sig("ats_splitk_reduce_signal", _vp, _c_int, _c_ll, _c_ll, _vp, _vp, _vp, ctypes.POINTER(_vp), _c_int, _c_int, _vp)
         sig("ats_peer_gather", ctypes.POINTER(_vp), _c_int, _vp, _c_ll, _c_int, _vp, _vp)
         sig("ats_peer_reduce_rows", ctypes.POINTER(_vp), _c_int, _c_int, _c_ll, _c_ll, _vp, _c_int, _vp, _c_int, _vp)
         _sig = True

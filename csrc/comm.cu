@@ -264,6 +264,39 @@ peer_reduce_rows_kernel(PeerPtrs grads, int world, int rank, long long offset, l
   }
 }
 
+// Fold of the reduction slices of a grouped product (as ats_splitk_reduce) whose result peers will read: the CTA that finishes last
+// raises this rank's flag on every peer (epoch = this rank's call counter), so that no barrier launch is needed between the
+// product and the peers' reads.  done_counter: one int, zero between launches.  epoch_counter: one int in this rank's memory.
+__global__ void __launch_bounds__(256)
+splitk_reduce_signal_kernel(const float* __restrict__ part, int splits, long long n_inner, long long n_outer, __nv_bfloat16* __restrict__ out,
+                            int* done_counter, int* epoch_counter, PeerPtrs flags, int rank, int world) {
+  pdl_prologue();
+  const long long nvec = n_inner >> 3, total = nvec * n_outer;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
+    const long long o = v / nvec, i = (v - o * nvec) << 3;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const float* src = part + (o * splits) * n_inner + i;
+    for (int s = 0; s < splits; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(src + s * n_inner), b = *reinterpret_cast<const float4*>(src + s * n_inner + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    *reinterpret_cast<uint4*>(out + o * n_inner + i) =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+  __threadfence_system();  // this CTA's rows are visible to the peers before it is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(done_counter, 1) == int(gridDim.x) - 1) {
+      *done_counter = 0;
+      const int e = *epoch_counter + 1;
+      *epoch_counter = e;
+      __threadfence_system();
+      for (int t = 0; t < world; ++t)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(static_cast<int*>(flags.p[t]) + rank), "r"(e) : "memory");
+    }
+  }
+}
+
 static PeerPtrs to_peers(void* const* host_ptrs, int world) {
   PeerPtrs pp;
   for (int i = 0; i < MAX_PEERS; ++i) pp.p[i] = i < world ? host_ptrs[i] : nullptr;
@@ -377,4 +410,15 @@ ATS_API int ats_peer_reduce_rows(void* const* grads, int world, int rank, long l
   peer_reduce_rows_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(to_peers(grads, world), world, rank, offset, n, out32,
                                                                                            accumulate, status);
   return int(cudaGetLastError());
+}
+
+// flags: host array of `world` device pointers, entry t = the int32 flag array [world] in rank t's memory (peer-mapped).
+ATS_API int ats_splitk_reduce_signal(const float* part, int splits, long long n_inner, long long n_outer, void* out, int* done_counter,
+                                     int* epoch_counter, void* const* flags, int rank, int world, void* stream) {
+  if (splits < 1 || n_inner <= 0 || n_outer <= 0 || (n_inner & 7) || world > MAX_PEERS || !done_counter || !epoch_counter) return 1003;
+  long long blocks = ((n_inner >> 3) * n_outer + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaError_t ce = launch_pdl(splitk_reduce_signal_kernel, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream), part, splits,
+                              n_inner, n_outer, static_cast<__nv_bfloat16*>(out), done_counter, epoch_counter, to_peers(flags, world), rank, world);
+  return int(ce != cudaSuccess ? ce : cudaGetLastError());
 }

@@ -687,11 +687,35 @@ __global__ void __launch_bounds__(256) serve_combine_kernel(__nv_bfloat16* const
                                                             const int* __restrict__ slot_pos, const float* __restrict__ topk_w,
                                                             const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int k,
                                                             int hidden, const __nv_bfloat16* __restrict__ norm_w,
-                                                            __nv_bfloat16* __restrict__ norm_out, float eps) {
+                                                            __nv_bfloat16* __restrict__ norm_out, float eps,
+                                                            const int* __restrict__ ready_flags, const int* __restrict__ epoch_counter,
+                                                            int experts_per_rank, unsigned long long budget_ns, int* status) {
   pdl_prologue();
   __shared__ float red[33];
   const int t = blockIdx.x;
   const int nvec = hidden >> 3;
+  if (ready_flags) {
+    // the rows are pulled from the experts' owners: wait (bounded) until each owner this token needs has raised its flag for this
+    // call -- the flag is written by the launch that folded the owner's down projection, so no barrier launch sits in between
+    if (threadIdx.x < k) {
+      const int e = topk_idx[t * k + threadIdx.x];
+      if (slot_pos[t * k + threadIdx.x] >= 0 && e >= 0) {
+        const int want = *epoch_counter;  // this rank's own fold of this call has already counted
+        const int* f = ready_flags + e / experts_per_rank;
+        const uint64_t t0 = globaltimer_ns();
+        int v;
+        do {
+          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+          if (v >= want) break;
+          if (globaltimer_ns() - t0 > budget_ns) {
+            if (status) atomicCAS(status, 0, int(kTimeoutPeerFlag));
+            break;
+          }
+        } while (true);
+      }
+    }
+    __syncthreads();
+  }
   float ss = 0.f;
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -921,14 +945,20 @@ ATS_API int ats_serve_plan_dispatch(const void* x, const int* topk_idx, int* slo
 }
 
 // norm_w / norm_out (both or neither): also write RMSNorm(out) * norm_w, the input of the next block.
+// ready_flags / epoch_counter / experts_per_rank (all or none): the kernel itself waits for the owners of the rows it pulls (see
+// ats_splitk_reduce_signal) instead of relying on a barrier launch before it.
+ATS_API unsigned long long ats_get_wait_budget_ns();  // comm.cu
 ATS_API int ats_serve_combine(void* const* src_table, const void* src0, long long src_stride, const int* topk_idx, const int* slot_pos,
                               const float* topk_w, const void* residual, void* out, int tokens, int k, int hidden, const void* norm_w,
-                              void* norm_out, float eps, void* stream) {
+                              void* norm_out, float eps, const int* ready_flags, const int* epoch_counter, int experts_per_rank, int* status,
+                              void* stream) {
   if (tokens <= 0 || (hidden & 7) || (!src_table && !src0) || ((norm_w == nullptr) != (norm_out == nullptr))) return 1003;
+  if (ready_flags && (!epoch_counter || experts_per_rank < 1 || k > 32)) return 1003;
   launch_pdl(serve_combine_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
              reinterpret_cast<__nv_bfloat16* const*>(src_table), static_cast<const __nv_bfloat16*>(src0), src_stride, topk_idx, slot_pos, topk_w,
              static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), k, hidden, static_cast<const __nv_bfloat16*>(norm_w),
-             static_cast<__nv_bfloat16*>(norm_out), eps);
+             static_cast<__nv_bfloat16*>(norm_out), eps, ready_flags, epoch_counter, experts_per_rank,
+             (unsigned long long)ats_get_wait_budget_ns(), status);
   return int(cudaGetLastError());
 }
 
