@@ -32,9 +32,11 @@ from ..ops import moe as M
 from ..ops.functional import _L, _P, _S, _CK, _deliver_grad
 
 
-# Decode-sized steps: the owners' "results are ready" flags travel with the fold of the down projection and are awaited inside the
-# combine kernel (1, default) instead of a flag-barrier launch between the two (0).
-FLAG_SYNC = os.environ.get("ATS_EP_FLAG_SYNC", "1") == "1"
+# Decode-sized steps: the owners' "results are ready" flags can travel with the fold of the down projection and be awaited inside the
+# combine kernel (1) instead of a flag-barrier launch between the two (0, default).  Measured on 2 GPUs the flag form is slower
+# (8 Mixtral layers 3.16 -> 3.25 ms per step, the 22-layer model 3.75 -> 3.88 ms): a system-scope fence in every CTA of the fold
+# and 64 polling CTAs cost more than the one-warp barrier launch they replace.
+FLAG_SYNC = os.environ.get("ATS_EP_FLAG_SYNC", "0") == "1"
 
 
 class _LayerBuffers:
