@@ -185,6 +185,17 @@ def decode_check(rank, world, dev):
     ops.check_status()
     assert model._ep_comm.serving_rows(4) > 0, "decode did not take the one-block serving layout"
     assert torch.equal(eager, graph), ("graph-replayed decode differs from the eager loop", (eager != graph).nonzero()[:4].tolist())
+    # the optional form in which the owners' flags travel with the fold of the down projection and the combine kernel waits for
+    # them (no second barrier launch): same tokens, eagerly and replayed
+    from adaptivetrainingsystem_b200.parallel import expert_parallel as EP
+    EP.FLAG_SYNC = True
+    try:
+        flagged = GenerationEngine(model).generate(mine, params, use_graph=True)["tokens"]
+        torch.cuda.synchronize()
+        ops.check_status()
+    finally:
+        EP.FLAG_SYNC = False
+    assert torch.equal(flagged, graph), "flag-synchronised decode differs from the barrier form"
     # teacher forcing with the single-GPU tokens: logits of both models step by step
     with torch.no_grad():
         c1, c2 = single.make_cache(4, Lp + new), model.make_cache(4, Lp + new)
