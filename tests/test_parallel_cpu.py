@@ -197,3 +197,40 @@ def test_ring_sequence_parallel_and_ring_attention():
     from dist_utils import run_dist
     run_dist(_ring_worker, world=2)
     run_dist(_ring_worker, world=3)
+
+
+def _pp_generate_worker(rank, world, path):
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.inference import PipelineGenerator, SamplingParams
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    from adaptivetrainingsystem_b200.parallel.pipeline import PipelineStage
+    ref = torch.load(path)
+    cfg = ModelConfig(**ref["cfg"])
+    model = DeepSeekTransformer(cfg)
+    model.load_state_dict(ref["state"])
+    model.eval()
+    stage = PipelineStage(model, rank, world)
+    assert stage.freed > 0
+    gen = PipelineGenerator(stage)
+    for mb in (1, 2, 4):
+        out = gen.generate(ref["prompts"], SamplingParams.from_mode("greedy", max_new_tokens=6), micro_batches=mb)
+        assert torch.equal(out.cpu(), ref["tokens"]), (mb, out.tolist(), ref["tokens"].tolist())
+
+
+@pytest.mark.dist
+@pytest.mark.parametrize("moe", [False, True])
+def test_pipeline_generation_matches_one_process(moe, tmp_path):
+    """Generation across two pipeline stages (each with the cache of its own layers, 1 / 2 / 4 micro-batches in flight) gives the
+    tokens of the single-process cached generator."""
+    from adaptivetrainingsystem_b200.config import ModelConfig
+    from adaptivetrainingsystem_b200.inference import GenerationEngine, SamplingParams
+    from adaptivetrainingsystem_b200.models import DeepSeekTransformer
+    cfgd = dict(vocab_size=128, hidden_size=32, num_layers=4, num_heads=4, num_kv_heads=2, intermediate_size=64, seq_length=32,
+                use_moe=moe, num_experts=4, moe_top_k=2, capacity_factor=8.0, routing_noise_std=0.0, tie_word_embeddings=False)
+    torch.manual_seed(1)
+    model = DeepSeekTransformer(ModelConfig(**cfgd)).eval()
+    prompts = torch.randint(0, 128, (4, 7))
+    tokens = GenerationEngine(model).generate(prompts, SamplingParams.from_mode("greedy", max_new_tokens=6), use_graph=False)["tokens"]
+    path = str(tmp_path / "ref.pt")
+    torch.save({"cfg": cfgd, "state": model.state_dict(), "prompts": prompts, "tokens": tokens}, path)
+    run_dist(_pp_generate_worker, 2, (path,))
