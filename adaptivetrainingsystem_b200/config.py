@@ -80,6 +80,7 @@ class ModelConfig:
     routing_noise_std: float = 0.0
     moe_pattern: str = "all"
     moe_layers: Optional[List[int]] = None  # explicit layer list wins over moe_pattern
+    router_z_loss_weight: float = 0.0  # > 0: adds weight * mean(logsumexp(router logits)^2), which keeps the logits small
     dense_start_layers: int = 2
     dense_end_layers: int = 2
     expert_output_scaling: float = 1.0
@@ -267,6 +268,7 @@ class Config:
     num_experts: int = 8
     moe_top_k: int = 2
     capacity_factor: float = 1.25
+    router_z_loss_weight: float = 0.0  # router z-loss (mean squared log-partition of the gate logits), off by default
     drop_tokens: bool = True  # enforce capacity_factor (routed slots beyond it are dropped); False = dropless, as the reference's live layer
     load_balancing_weight: float = 0.01
     routing_temperature: float = 1.0
@@ -486,6 +488,7 @@ class Config:
             gradient_checkpointing=self.gradient_checkpointing, use_flash_attention=self.use_flash_attention,
             use_moe=self.use_moe, num_experts=self.num_experts, moe_top_k=self.moe_top_k,
             capacity_factor=self.capacity_factor, drop_tokens=self.drop_tokens, load_balancing_weight=self.load_balancing_weight,
+            router_z_loss_weight=getattr(self, "router_z_loss_weight", 0.0),
             routing_temperature=self.routing_temperature, routing_noise_std=self.routing_noise_std,
             moe_pattern=self.moe_pattern, use_mod=self.use_mod, mod_capacity_factor=self.mod_capacity_factor,
             mod_routing_temperature=self.mod_routing_temperature,

@@ -255,6 +255,7 @@ class MoEFFNLayer(nn.Module):
         self.routing_temperature = cfg.routing_temperature
         self.routing_noise_std = cfg.routing_noise_std
         self.load_balancing_weight = cfg.load_balancing_weight
+        self.router_z_loss_weight = float(getattr(cfg, "router_z_loss_weight", 0.0))
         self.expert_dropout = 0.0
         self.ep_size, self.ep_rank = ep_size, ep_rank
         assert cfg.num_experts % ep_size == 0, "num_experts must be divisible by the expert-parallel degree"
@@ -304,6 +305,10 @@ class MoEFFNLayer(nn.Module):
             w = w / w.sum(-1, keepdim=True).clamp(min=1e-20)
         if not fused_route:
             aux = moe_ops.load_balancing_loss(clean, idx, E, self.load_balancing_weight)
+        if self.router_z_loss_weight > 0 and self.training:
+            # router z-loss: mean squared log-partition of the (un-noised) gate logits; it keeps the logits from drifting to magnitudes
+            # where the soft-max saturates (reference: colossalai/moe/routers.py:94-110)
+            aux = aux + self.router_z_loss_weight * torch.logsumexp(logits.float(), dim=-1).pow(2).mean()
         cap = moe_ops.expert_capacity(T, E, k, self.capacity_factor, self.cfg.drop_tokens)
         res2 = residual.reshape(-1, shape[-1]) if residual is not None else None
         if self.ep is not None:

@@ -215,3 +215,23 @@ def test_decode_with_device_side_cache_counters_matches_python_counters():
             c2.length += 1
             assert torch.allclose(a, b, atol=1e-5), t
         assert c2.device_lengths.tolist() == [9, 9] and c1.length == 9
+
+
+def test_router_z_loss_adds_to_the_auxiliary_loss_and_trains_the_gate():
+    torch.manual_seed(0)
+    base = dict(vocab_size=128, hidden_size=32, num_layers=1, num_heads=4, num_kv_heads=2, intermediate_size=64, seq_length=16,
+                use_moe=True, num_experts=4, moe_top_k=2, routing_noise_std=0.0, load_balancing_weight=0.0)
+    ids = torch.randint(0, 128, (2, 16))
+    m0 = DeepSeekTransformer(ModelConfig(**base))
+    m1 = DeepSeekTransformer(ModelConfig(**base, router_z_loss_weight=0.1))
+    m1.load_state_dict(m0.state_dict())
+    a0 = m0.forward_loss(ids, ids)["aux_loss"]
+    out = m1.forward_loss(ids, ids)
+    layer = m1.get_moe_layers()[0]
+    with torch.no_grad():
+        h = m1.layers[0].post_attn_norm(m1.layers[0].self_attn(m1.layers[0].input_norm(m1.embed_tokens(ids) * (32 ** 0.5 if m1.config.use_stable_embedding else 1.0)),
+                                                               m1.embed_tokens(ids) * (32 ** 0.5 if m1.config.use_stable_embedding else 1.0), m1.rope))
+        want = 0.1 * torch.logsumexp(torch.nn.functional.linear(h.reshape(-1, 32), layer.gate.weight).float(), -1).pow(2).mean()
+    assert float(a0) == 0.0 and abs(float(out["aux_loss"]) - float(want)) < 1e-4 * max(1.0, float(want))
+    out["loss"].backward()
+    assert layer.gate.weight.grad is not None and float(layer.gate.weight.grad.abs().sum()) > 0
