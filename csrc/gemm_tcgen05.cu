@@ -1112,6 +1112,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
       acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
     }
     const float* src = part + (o * splits) * n_inner + i;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
       const float4 a = *reinterpret_cast<const float4*>(src + s * n_inner), b = *reinterpret_cast<const float4*>(src + s * n_inner + 4);
       acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;

@@ -585,7 +585,8 @@ __global__ void __launch_bounds__(256) serve_gate_route_kernel(const __nv_bfloat
   for (int e = warp; e < experts; e += nwarps) {
     const uint4* wr = reinterpret_cast<const uint4*>(wg + (long long)e * hidden);
     float acc = 0.f;
-    for (int v = lane; v < nvec; v += 32) {
+#pragma unroll 8
+    for (int v = lane; v < nvec; v += 32) {  // unrolled: the loads of several iterations are in flight together
       const uint4 a = xr[v], b = wr[v];
       const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
       const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
@@ -663,6 +664,7 @@ __global__ void __launch_bounds__(256) serve_plan_dispatch_kernel(const __nv_bfl
   const uint4* src = reinterpret_cast<const uint4*>(x + (long long)(s / k) * hidden);
   __nv_bfloat16* base = dst_table ? dst_table[e] : dst0 + (long long)e * dst_stride;
   uint4* d = reinterpret_cast<uint4*>(base + (long long)pos * hidden);
+#pragma unroll 8
   for (int v = lane; v < (hidden >> 3); v += 32) d[v] = src[v];
 }
 
@@ -767,6 +769,7 @@ __global__ void __launch_bounds__(256) fold_rope_kernel(const float* __restrict_
   auto fold8 = [&](int col, float (&a)[8]) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = 0.f;
+#pragma unroll 4
     for (int sl = 0; sl < splits; ++sl) {
       const float4* src = reinterpret_cast<const float4*>(row + sl * slice_stride + col);
       const float4 x = src[0], y = src[1];
@@ -823,6 +826,7 @@ __global__ void __launch_bounds__(256) fold_add_norm_kernel(const float* __restr
       const float2 f0 = unpack_bf16x2(r.x), f1 = unpack_bf16x2(r.y), f2 = unpack_bf16x2(r.z), f3 = unpack_bf16x2(r.w);
       a[0] = f0.x; a[1] = f0.y; a[2] = f1.x; a[3] = f1.y; a[4] = f2.x; a[5] = f2.y; a[6] = f3.x; a[7] = f3.y;
     }
+#pragma unroll 4
     for (int sl = 0; sl < splits; ++sl) {
       const float4* src = reinterpret_cast<const float4*>(row + sl * slice_stride + v * 8);
       const float4 x = src[0], y = src[1];
