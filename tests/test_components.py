@@ -371,3 +371,11 @@ def test_int8_and_smoothquant_post_training_quantisation_cpu():
     finally:
         int8.set_enabled(False)
         int8.clear()
+
+
+def test_continuous_batcher_needs_a_gpu_and_validates_requests():
+    from adaptivetrainingsystem_b200.inference import ContinuousBatcher, GenerationEngine
+    model = DeepSeekTransformer(ModelConfig(vocab_size=64, hidden_size=32, num_layers=1, num_heads=4, num_kv_heads=2, intermediate_size=64,
+                                            seq_length=32)).eval()
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ContinuousBatcher(GenerationEngine(model), max_batch=2, max_len=16)
