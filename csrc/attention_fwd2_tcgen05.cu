@@ -327,16 +327,20 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mx3 = max3f(mx3, __uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
       }
       const float mnew = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
-      if (EARLY && i > 0) {  // the previous P V of this tile must be finished: O stable, P buffer free
-        if (!mbar_wait_bounded(&pv_done[x], (i - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-      }
+      // The previous P V of this tile must be finished before O is rescaled (rare) or the P buffer is written again.  The
+      // exponentials of the first quarter of the row do not depend on it, so the wait sits behind them.
+      bool pv_waited = !(EARLY && i > 0);
       if (i == 0) {
         m = mnew;
       } else if (__any_sync(0xffffffffu, mnew > m + 8.f)) {
+        if (!pv_waited) {
+          if (!mbar_wait_bounded(&pv_done[x], (i - 1) & 1, abort_flag, p.status, kTimeoutTmemFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          pv_waited = true;
+        }
         // the previous P V of this tile has completed (implied by S(i) being ready when P aliases S, waited for above otherwise)
         const float alpha = exp2f(m - mnew);
         m = mnew;
@@ -368,6 +372,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           if (e & 1) rsb = __fadd2_rn(rsb, pr);
           else rsa = __fadd2_rn(rsa, pr);
         }
+        if (!pv_waited) {  // first quarter done in registers: now the P buffer must be free
+          ok = mbar_wait_bounded(&pv_done[x], (i - 1) & 1, abort_flag, p.status, kTimeoutTmemFull);
+          tc_fence_after();
+          pv_waited = true;
+        }
+        if (!ok) continue;
         if (PT) {
           tmem_st_32x16((SEP ? tmem_base + 384 + x * 64 + lane_base : tmem_S) + c * 16, pk);
         } else {
@@ -379,6 +389,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
         }
       }
+      if (!ok) break;
       l += (rsa.x + rsa.y) + (rsb.x + rsb.y);
       if (rec) { c0 = clock64(); t_exp += c0 - c1; }
       if (PT) tmem_st_wait();
