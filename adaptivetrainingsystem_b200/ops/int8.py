@@ -26,7 +26,8 @@ _enabled = False
 _observing = False
 _weight_cache: Dict[int, Tuple[int, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]] = {}
 _act_amax: Dict[int, torch.Tensor] = {}      # weight storage -> running max |x| per input channel (calibration)
-_smoothing: Dict[int, torch.Tensor] = {}     # weight storage -> s [K] fp32
+_smoothing: Dict[int, torch.Tensor] = {}     # weight storage -> largest |x| per input channel seen during calibration
+_alpha = 0.5                                 # SmoothQuant migration strength: s = amax_x^alpha / amax_w^(1 - alpha)
 
 
 def set_enabled(flag: bool) -> None:
@@ -137,11 +138,12 @@ def record(x2: torch.Tensor, w: torch.Tensor) -> None:
 
 def finish_calibration(alpha: float = 0.5) -> int:
     """Turns the recorded activation ranges into smoothing factors; returns how many weights got one."""
+    global _alpha
+    _alpha = float(alpha)
     n = 0
     for key, a in _act_amax.items():
         _smoothing[key] = a       # the weight's own range is folded in when the weight is quantised (needs the tensor)
         n += 1
-    _smoothing["alpha"] = alpha   # type: ignore[index]
     _weight_cache.clear()
     return n
 
@@ -156,7 +158,7 @@ def quantized_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, Optio
     inv = None
     a = _smoothing.get(key)
     if a is not None:
-        alpha = float(_smoothing.get("alpha", 0.5))  # type: ignore[arg-type]
+        alpha = _alpha
         wmax = wf.abs().amax(0).clamp(min=1e-5)
         s = (a.to(wf.device).clamp(min=1e-5) ** alpha / wmax ** (1.0 - alpha)).clamp(min=1e-3, max=1e3)
         wf = wf * s[None, :]
