@@ -66,7 +66,7 @@ class ChatInterface:
                 raise SystemExit("--quantize needs a GPU: the fp8 path runs on the tensor-core GEMM")
             from types import SimpleNamespace
             from adaptivetrainingsystem_b200.training import QuantizationManager
-            QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=8)).quantize_model(self.model)
+            QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=4 if quantize == "int4" else 8)).quantize_model(self.model)
         self.tokenizer = ConversationTokenizer()
         self.engine = GenerationEngine(self.model, self.tokenizer)
         self.params = SamplingParams.from_mode(mode, max_new_tokens=min(256, max(cfg.seq_length // 2, 1)),
@@ -139,7 +139,7 @@ if __name__ == "__main__":
     ap.add_argument("--mode", default="standard", choices=list(GENERATION_MODES))
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--device", default="auto")
-    ap.add_argument("--quantize", default=None, choices=["fp8", "int8"], help="post-training quantisation of the projection weights")
+    ap.add_argument("--quantize", default=None, choices=["fp8", "int8", "int4"], help="post-training quantisation of the projection weights")
     ap.add_argument("--prompts-file", default=None, help="one prompt per line, answered together by continuous batching")
     ap.add_argument("--max-batch", type=int, default=16)
     a = ap.parse_args()

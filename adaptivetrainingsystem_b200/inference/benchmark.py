@@ -59,7 +59,7 @@ def run_decode_benchmark(config_name: str = "mixtral_8x7b", batch: int = 64, pro
         # post-training quantisation (reported with its own dtype; the headline decode figure is the bf16 one)
         from types import SimpleNamespace
         from ..training.precision import QuantizationManager
-        qm = QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=8))
+        qm = QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=4 if quantize in ("int4", "gptq") else 8))
         qm.quantize_model(model)
     eng = GenerationEngine(model, pack_experts=pack_experts)
     per = batch // world
@@ -106,7 +106,8 @@ def run_decode_benchmark(config_name: str = "mixtral_8x7b", batch: int = 64, pro
     steps = max(new_tokens - 1, 1)
     res = {"metric": "moe_decode_tokens_per_sec", "value": batch * steps / (best["decode_ms"] / 1e3), "unit": "tokens/s",
            "ms_per_decode_step": best["decode_ms"] / steps, "prefill_tokens_per_sec": batch * prompt / (best["prefill_ms"] / 1e3),
-           "prefill_ms": best["prefill_ms"], "n_gpus": world, "dtype": "bf16" if not quantize else f"{quantize} weights and activations, bf16 attention", "data": "synthetic",
+           "prefill_ms": best["prefill_ms"], "n_gpus": world, "dtype": "bf16" if not quantize else (f"{quantize} weights, bf16 activations and attention" if quantize in ("int4", "gptq")
+                                                                   else f"{quantize} weights and activations, bf16 attention"), "data": "synthetic",
            "timing": "CUDA events, max over ranks; decode = sampling kernel + graph-replayed step, ids copied to the host at the end",
            "config": {"model": config_name, "batch": batch, "prompt": prompt, "new_tokens": new_tokens, "layers": mc.num_layers,
                       "parallelism": f"ep{ep}" if ep > 1 else "1 GPU", "sequences_per_rank": per, "params_total": mc.num_parameters(),
@@ -119,12 +120,14 @@ def run_decode_benchmark(config_name: str = "mixtral_8x7b", batch: int = 64, pro
     res["weight_gb_per_step_per_gpu"] = 2 * (dense + expert) / 1e9
     res["weight_stream_tb_per_s_per_gpu"] = 2 * (dense + expert) / 1e12 / (res["ms_per_decode_step"] / 1e3)
     if qm is not None:
-        from ..ops import fp8, int8
+        from ..ops import fp8, int4, int8
         res["quantized_bytes"] = qm.quantized_bytes
         fp8.set_enabled(False)
         fp8.clear_weight_cache()
         int8.set_enabled(False)
         int8.clear()
+        int4.set_enabled(False)
+        int4.clear()
     del eng, model
     if comm is not None:
         comm.close()

@@ -13,3 +13,4 @@ from .serving import (decode_attention, decode_attention_available, decode_atten
                       sample_reference)
 from . import fp8  # noqa: E402,F401
 from . import int8  # noqa: E402,F401
+from . import int4  # noqa: E402,F401

@@ -68,6 +68,9 @@ def _partial_products(x2: torch.Tensor, w: torch.Tensor):
     if not (FUSE_DECODE and _lib.use_cuda_kernels(x2) and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
             and x2.is_contiguous() and w.is_contiguous() and not getattr(w, "_ats_z3", None) and G.SPLIT_K_SKINNY):
         return None
+    from . import int4
+    if int4.enabled() and int4.lookup(w) is not None:
+        return None          # a 4-bit weight: the caller's ordinary product streams the packed copy
     splits = G._skinny_splits(T, N, K)
     if splits < 2:
         return None

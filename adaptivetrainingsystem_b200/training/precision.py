@@ -88,16 +88,22 @@ class QuantizationManager:
     weight is quantised per output channel to e4m3, activations per token at run time, and ``ops.linear`` / the SwiGLU MLP
     run on the ``kind::f8f6f4`` tensor-core GEMM with both scales applied in its epilogue.  ``"int8"`` is the same scheme with
     signed bytes on the ``kind::i8`` GEMM (W8A8), and ``"smoothquant"`` is int8 after :meth:`calibrate` has measured the
-    activation range of every projection's input channels and moved it into the weights (``ops/int8.py``).  The external
-    backends are reported and refused when not installed."""
+    activation range of every projection's input channels and moved it into the weights (``ops/int8.py``).  ``"int4"`` /
+    ``"gptq"`` (or ``quantization_bits=4`` without a method) is weight-only 4-bit with groups of 128 input channels
+    (``ops/int4.py``): codes by GPTQ for every projection :meth:`calibrate` collected a Hessian for, round-to-nearest for the
+    rest; the language-model head, embeddings, routers and stacked expert weights stay in bf16.  The external backends are
+    reported and refused when not installed."""
 
-    NATIVE = ("fp8", "fp8_e4m3", "int8", "smoothquant")
+    NATIVE = ("fp8", "fp8_e4m3", "int8", "smoothquant", "int4", "gptq")
 
     def __init__(self, config):
         self.method = getattr(config, "quantization_method", None)
         self.bits = getattr(config, "quantization_bits", None)
         if self.method is None and self.bits == 8:
             self.method = "fp8"
+        if self.method is None and self.bits == 4:
+            self.method = "int4"
+        self.gptq_weights = 0
         self.applied = False
         self.calibrated = False
         self.quantized_tensors = 0
@@ -105,11 +111,23 @@ class QuantizationManager:
 
     @torch.no_grad()
     def calibrate(self, model, batches, alpha: float = 0.5) -> int:
-        """SmoothQuant calibration: run ``batches`` (token id tensors) through the unquantised model while every projection
-        records the largest |x| of each of its input channels.  Returns the number of projections that got smoothing factors."""
-        from ..ops import int8
+        """Runs ``batches`` (token id tensors) through the unquantised model while every projection records what its method
+        needs: the largest |x| of each input channel (SmoothQuant; returns the number of projections that got smoothing
+        factors) or the Hessian sum x^T x of its input rows (``"int4"`` / ``"gptq"``; returns the number of Hessians)."""
+        from ..ops import int4, int8
         was = model.training
         model.eval()
+        if self.method in ("int4", "gptq"):
+            int4.set_enabled(False)
+            int4.observe(True)
+            try:
+                for ids in batches:
+                    model(ids, return_aux_loss=False)
+            finally:
+                int4.observe(False)
+                model.train(was)
+            self.calibrated = len(int4._hessians) > 0
+            return len(int4._hessians)
         int8.set_enabled(False)
         int8.observe(True)
         try:
@@ -123,7 +141,8 @@ class QuantizationManager:
         return n
 
     def available_backends(self) -> Dict[str, bool]:
-        out = {"fp8 (native e4m3 GEMM)": torch.cuda.is_available(), "int8 / smoothquant (native s8 GEMM)": True}
+        out = {"fp8 (native e4m3 GEMM)": torch.cuda.is_available(), "int8 / smoothquant (native s8 GEMM)": True,
+               "int4 / gptq (native weight-only 4-bit)": True}
         for mod in ("bitsandbytes", "auto_gptq", "optimum.quanto"):
             try:
                 __import__(mod)
@@ -137,10 +156,24 @@ class QuantizationManager:
             return model
         if self.method not in self.NATIVE:
             raise RuntimeError(f"quantization backend for {self.method!r} is not installed; available: {self.available_backends()}")
-        from ..ops import fp8, int8
+        from ..ops import fp8, int4, int8
+        if self.method == "gptq" and not self.calibrated:
+            raise RuntimeError("gptq needs calibration inputs: call calibrate(model, batches) before quantize_model")
         model.eval()
         for p in model.parameters():
             p.requires_grad_(False)
+        if self.method in ("int4", "gptq"):
+            for name, p in model.named_parameters():
+                if (p.dim() == 2 and int4.shape_ok(p.shape[0], p.shape[1]) and "embed" not in name and "lm_head" not in name
+                        and "gate.weight" not in name and "router" not in name and getattr(p, "_ats_z3", None) is None):
+                    packed, meta, used_gptq = int4.register(p)
+                    self.quantized_tensors += 1
+                    self.gptq_weights += int(used_gptq)
+                    self.quantized_bytes += packed.numel() * 4 + meta.numel() * 4
+            int4._hessians.clear()      # K x K fp32 each: not needed once the codes are fixed
+            int4.set_enabled(True)
+            self.applied = True
+            return model
         if self.method in ("int8", "smoothquant"):
             if self.method == "smoothquant" and not self.calibrated:
                 raise RuntimeError("smoothquant needs activation ranges: call calibrate(model, batches) before quantize_model")
@@ -171,4 +204,4 @@ class QuantizationManager:
 
     def status(self) -> Dict[str, Any]:
         return {"method": self.method, "bits": self.bits, "applied": self.applied, "tensors": self.quantized_tensors,
-                "quantized_bytes": self.quantized_bytes, "backends": self.available_backends()}
+                "quantized_bytes": self.quantized_bytes, "gptq_weights": self.gptq_weights, "backends": self.available_backends()}

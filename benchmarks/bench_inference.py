@@ -33,7 +33,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only")
     ap.add_argument("--repeat", type=int, default=2)
     ap.add_argument("--pack-experts", type=int, default=1, help="store the expert weights tile by tile for serving (1) or keep the training layout (0)")
-    ap.add_argument("--quantize", default="", choices=["", "fp8", "int8"],
+    ap.add_argument("--quantize", default="", choices=["", "fp8", "int8", "int4"],
                     help="post-training quantisation of the weights before serving (fp8 covers the experts on one GPU; not the headline figure)")
     a = ap.parse_args()
     rank, local, world = init_distributed()

@@ -3,7 +3,7 @@
 the fraction of the measured roofline (``MEASURED_PEAKS.json``: cuBLAS bf16 burst throughput, STREAM-style copy
 bandwidth).  A library column (cuBLAS / PyTorch eager) is printed next to each kernel for comparison.
 
-    python benchmarks/bench_kernels.py [--quick] [--json out.json] [--only gemm,fp8,int8,swiglu,grouped,memory,adamw,attention]
+    python benchmarks/bench_kernels.py [--quick] [--json out.json] [--only gemm,fp8,int8,int4,swiglu,grouped,memory,adamw,attention]
 
 ``--only memory`` (or any other single section) keeps a run short enough for a profiler capture of one kernel.
 """
@@ -33,7 +33,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--json", default="")
-    ap.add_argument("--only", default="", help="comma-separated sections: gemm, fp8, int8, swiglu, grouped, memory, adamw, attention")
+    ap.add_argument("--only", default="", help="comma-separated sections: gemm, fp8, int8, int4, swiglu, grouped, memory, adamw, attention")
     args = ap.parse_args()
     only = {t.strip() for t in args.only.split(",") if t.strip()}
 
@@ -83,6 +83,24 @@ def main():
         report(f"gemm_nt_int8 {m}x{n}x{k}", time_cuda(lambda: int8.gemm_nt_int8(aq, sa, bq, sb, out=out)), 2.0 * m * n * k,
                nbytes=float(n * k), lib_ms=time_cuda(lambda: torch.matmul(a, b.t(), out=out)))
         report(f"quantize_rows_int8 {m}x{k}", time_cuda(lambda: int8.quantize_rows(a)), nbytes=3.0 * m * k)
+    # weight-only 4-bit: the streaming kernel for 1..16 token rows (bytes = packed weight + scales; library column = cuBLAS on the
+    # bf16 weight, which reads four times the bytes) and the dequantise pass that feeds the tcgen05 GEMM for prompts
+    from adaptivetrainingsystem_b200.ops import int4
+    for (n, k) in [(28672, 4096), (4096, 14336), (11264, 2048), (2048, 5632)] if want("int4") else []:
+        w = rnd(n, k, scale=0.05)
+        q, sc, z = int4.quantize_rtn(w)
+        packed, meta = int4.pack(q), int4.pack_meta(sc, z)
+        wbytes = float(packed.numel() * 4 + meta.numel() * 4)
+        for m in (1, 4, 8, 16):
+            a = rnd(m, k)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+            report(f"gemv_int4 {m}x{n}x{k}", time_cuda(lambda: int4.gemv(a, packed, meta)), 2.0 * m * n * k, nbytes=wbytes,
+                   lib_ms=time_cuda(lambda: torch.matmul(a, w.t(), out=out)))
+        if n == 28672:
+            a = rnd(4, k)
+            report(f"gemv_int4_swiglu 4x{n}x{k}", time_cuda(lambda: int4.gemv(a, packed, meta, swiglu=True)), 2.0 * 4 * n * k, nbytes=wbytes)
+            wd = torch.empty(n, k, dtype=torch.bfloat16, device=DEV)
+            report(f"dequant_int4 {n}x{k}", time_cuda(lambda: int4.dequantize(packed, meta, out=wd)), nbytes=wbytes + 2.0 * n * k)
     # SwiGLU-fused GEMM
     for (m, k, i) in [(8192, 2048, 5632), (4096, 4096, 14336)] if want("swiglu") else []:
         a, w = rnd(m, k), rnd(2 * i, k, scale=0.05)

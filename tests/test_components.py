@@ -248,15 +248,19 @@ def test_security_primitives():
 
 
 def test_quantization_manager_methods_and_refusals():
-    """bits=8 without a method selects the native fp8 path; external backends that are not installed are refused."""
+    """bits=8 without a method selects the native fp8 path and bits=4 the native 4-bit one; GPTQ refuses to run uncalibrated;
+    external backends that are not installed are refused."""
     from types import SimpleNamespace
     from adaptivetrainingsystem_b200.training import QuantizationManager
     qm = QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=8))
     st = qm.status()
     assert st["method"] == "fp8" and not st["applied"] and "bitsandbytes" in st["backends"]
     assert QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=None)).quantize_model("m") == "m"
+    assert QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=4)).status()["method"] == "int4"
     with pytest.raises(RuntimeError):
         QuantizationManager(SimpleNamespace(quantization_method="gptq", quantization_bits=4)).quantize_model(None)
+    with pytest.raises(RuntimeError):
+        QuantizationManager(SimpleNamespace(quantization_method="bnb", quantization_bits=4)).quantize_model(None)
 
 
 def test_swiglu_backward_gemm_reference_matches_autograd():
