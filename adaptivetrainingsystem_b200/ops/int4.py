@@ -122,11 +122,12 @@ def gptq_quantize(w: torch.Tensor, hessian: torch.Tensor, group: int = GROUP, da
 
 # -- packed format ---------------------------------------------------------------------------------------------------------------
 def pack(q: torch.Tensor) -> torch.Tensor:
-    """codes [N, K] (0..15) -> int32 [N / 16, K / 64, 32, 4]: word [T, S, 4 g + t, j], nibble i = feature 16 T + g + 8 (i & 1),
-    input channel 64 S + 16 t + 4 j + 2 ((i >> 1) & 1) + (i >> 2)."""
+    """codes [N, K] (0..15) -> int32 [K / 64, N / 16, 32, 4]: word [S, T, 4 g + t, j], nibble i = feature 16 T + g + 8 (i & 1),
+    input channel 64 S + 16 t + 4 j + 2 ((i >> 1) & 1) + (i >> 2).  The 64-channel step S is the outer index: the CTAs of the
+    streaming kernel own feature tiles T and advance through S together, so what is in flight at any time is contiguous."""
     N, K = q.shape
     v = q.to(torch.int64).view(N // 16, 2, 8, K // 64, 4, 4, 2, 2)          # T, h, g, S, t, j, c, d ; nibble = h + 2 c + 4 d
-    v = v.permute(0, 3, 2, 4, 5, 7, 6, 1).reshape(N // 16, K // 64, 32, 4, 8)   # T, S, (g, t), j, (d, c, h)
+    v = v.permute(3, 0, 2, 4, 5, 7, 6, 1).reshape(K // 64, N // 16, 32, 4, 8)   # S, T, (g, t), j, (d, c, h)
     shifts = torch.arange(8, device=q.device, dtype=torch.int64) * 4
     word = (v << shifts).sum(-1)
     word = torch.where(word >= 2 ** 31, word - 2 ** 32, word)
@@ -134,11 +135,11 @@ def pack(q: torch.Tensor) -> torch.Tensor:
 
 
 def unpack(packed: torch.Tensor) -> torch.Tensor:
-    T, S = packed.shape[:2]
+    S, T = packed.shape[:2]
     word = packed.to(torch.int64) & 0xFFFFFFFF
     shifts = torch.arange(8, device=packed.device, dtype=torch.int64) * 4
-    v = ((word[..., None] >> shifts) & 15).view(T, S, 8, 4, 4, 2, 2, 2)        # T, S, g, t, j, d, c, h
-    return v.permute(0, 7, 2, 1, 3, 4, 6, 5).reshape(T * 16, S * 64).to(torch.uint8)
+    v = ((word[..., None] >> shifts) & 15).view(S, T, 8, 4, 4, 2, 2, 2)        # S, T, g, t, j, d, c, h
+    return v.permute(1, 7, 2, 0, 3, 4, 6, 5).reshape(T * 16, S * 64).to(torch.uint8)
 
 
 def pack_meta(scale: torch.Tensor, zero: torch.Tensor) -> torch.Tensor:
@@ -167,7 +168,7 @@ def dequantize_reference(packed: torch.Tensor, meta: torch.Tensor, group: int = 
 
 def dequantize(packed: torch.Tensor, meta: torch.Tensor, group: int = GROUP, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The bf16 matrix [N, K] the packed weight stands for."""
-    N, K = packed.shape[0] * 16, packed.shape[1] * 64
+    N, K = packed.shape[1] * 16, packed.shape[0] * 64
     if meta.shape != (K // group, N) or not packed.is_contiguous() or not meta.is_contiguous():
         raise ValueError(f"dequantize: scales {tuple(meta.shape)} do not fit the packed weight {N} x {K} (group {group})")
     if not packed.is_cuda:
@@ -190,9 +191,9 @@ def gemv(x2: torch.Tensor, packed: torch.Tensor, meta: torch.Tensor, group: int 
     """x2 [M <= 16, K] bf16 @ W^T (+ add), or silu(gate) * up over the two halves of the features; the packed weight is read
     once."""
     M, K = x2.shape
-    N = packed.shape[0] * 16
-    if K != packed.shape[1] * 64 or meta.shape != (K // group, N) or M > GEMV_MAX_ROWS or not packed.is_contiguous() or not meta.is_contiguous():
-        raise ValueError(f"gemv: activations {tuple(x2.shape)} do not fit the packed weight {N} x {packed.shape[1] * 64} (group {group})")
+    N = packed.shape[1] * 16
+    if K != packed.shape[0] * 64 or meta.shape != (K // group, N) or M > GEMV_MAX_ROWS or not packed.is_contiguous() or not meta.is_contiguous():
+        raise ValueError(f"gemv: activations {tuple(x2.shape)} do not fit the packed weight {N} x {packed.shape[0] * 64} (group {group})")
     n_out = N // 2 if swiglu else N
     if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
         x2 = x2.contiguous()

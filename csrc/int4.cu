@@ -7,7 +7,12 @@
 // out such that the 16 bytes a lane loads ARE its A fragments of four consecutive k-steps:
 //
 //   tile T = 16 output features, super-step S = 64 reduction indices, lane (g, t) = (lane / 4, lane % 4), word j = 0..3:
-//   nibble i of word [T][S][lane][j] holds feature 16 T + g + 8 (i & 1), reduction index 64 S + 16 t + 4 j + 2 ((i >> 1) & 1) + (i >> 2)
+//   nibble i of word [S][T][lane][j] holds feature 16 T + g + 8 (i & 1), reduction index 64 S + 16 t + 4 j + 2 ((i >> 1) & 1) + (i >> 2)
+//
+// The super-step is the OUTER index of the stored array: CTAs own tiles, start together and advance at the same pace, so at any
+// time the CTAs in flight read one contiguous window of the array per warp slot, as a copy kernel does.  With the tile outermost
+// every CTA walked its own 32 KB region 4 KB at a time and the kernel stayed at 1.9 TB/s whatever else was changed (pipeline
+// depth, occupancy, instruction count): DRAM saw several hundred scattered 512-byte streams.
 //
 // (the sum over the reduction index does not care about the order of its terms, so inside a k-step the MMA's logical indices
 // 2t, 2t+1, 2t+8, 2t+9 are mapped to the four consecutive actual indices 16 t + 4 j .. + 3: the B fragment of a lane is then 8
@@ -51,7 +56,7 @@ __device__ __forceinline__ uint32_t dq_scale(uint32_t v, uint32_t zero2, uint32_
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 struct Int4Consts {
-  uint32_t mask, magic, m4, m8, m12;  // 0x000f000f, 0x43004300 (bf16 128.0 twice), 2^28, 2^24, 2^20
+  uint32_t mask, magic, m4, m8, m12, ones;  // 0x000f000f, 0x43004300 (bf16 128.0 twice), 2^28, 2^24, 2^20, bf16 1.0 twice
 };
 // one packed word -> the four A-fragment registers of a k-step (rows g / g + 8 alternate)
 __device__ __forceinline__ void dq_word(uint32_t w, const Int4Consts& k, uint32_t zA, uint32_t sA, uint32_t zB, uint32_t sB, uint32_t (&a)[4]) {
@@ -84,10 +89,10 @@ gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta
   pdl_prologue();
   __shared__ float s_red[GEMV_WARPS][R][8 * NT][16];  // [warp][tile][token][feature of the tile]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int n_super = K >> 6;
+  const int n_super = K >> 6, n_tiles = N >> 4;
   // constants the extraction wants in registers; built from a kernel argument so that they are not folded back into immediates
   const uint32_t one = uint32_t(group_shift > 0);
-  const Int4Consts kc = {0x000f000fu * one, 0x43004300u * one, one << 28, one << 24, one << 20};
+  const Int4Consts kc = {0x000f000fu * one, 0x43004300u * one, one << 28, one << 24, one << 20, 0x3f803f80u * one};
   int tile[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) tile[r] = SWIGLU ? int(blockIdx.x) + r * (N >> 5) : int(blockIdx.x) * R + r;
@@ -108,7 +113,7 @@ gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta
     const long long grp = S >> (group_shift - 6);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      s.w[r] = __ldcs(wq + ((long long)tile[r] * n_super + S) * 32 + lane);
+      s.w[r] = __ldcs(wq + ((long long)S * n_tiles + tile[r]) * 32 + lane);
       const uint32_t* mrow = meta + grp * N + tile[r] * 16 + g;
       s.mA[r] = __ldg(mrow);
       s.mB[r] = __ldg(mrow + 8);
@@ -131,17 +136,36 @@ gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta
       xw[n][0] = s.x[n][0].x; xw[n][1] = s.x[n][0].y; xw[n][2] = s.x[n][0].z; xw[n][3] = s.x[n][0].w;
       xw[n][4] = s.x[n][1].x; xw[n][5] = s.x[n][1].y; xw[n][6] = s.x[n][1].z; xw[n][7] = s.x[n][1].w;
     }
+    // sum of the step's activations per token: a product with an all-ones A operand (every row of the result holds it)
+    float cx[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      cx[n][0] = cx[n][1] = cx[n][2] = cx[n][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mma_16816(cx[n], kc.ones, kc.ones, kc.ones, kc.ones, xw[n][2 * j], xw[n][2 * j + 1]);
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const uint32_t sA = __byte_perm(s.mA[r], s.mA[r], 0x1010), zA = __byte_perm(s.mA[r], s.mA[r], 0x3232);
-      const uint32_t sB = __byte_perm(s.mB[r], s.mB[r], 0x1010), zB = __byte_perm(s.mB[r], s.mB[r], 0x3232);
+      // bf16 -> fp32 is a shift: scale, and 128 + zero, of features g (A) and g + 8 (B)
+      const float sA = __uint_as_float(s.mA[r] << 16), zA = __uint_as_float(s.mA[r] & 0xffff0000u);
+      const float sB = __uint_as_float(s.mB[r] << 16), zB = __uint_as_float(s.mB[r] & 0xffff0000u);
       const uint32_t w4[4] = {s.w[r].x, s.w[r].y, s.w[r].z, s.w[r].w};
+      float cq[NT][4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) cq[n][0] = cq[n][1] = cq[n][2] = cq[n][3] = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        uint32_t a[4];
-        dq_word(w4[j], kc, zA, sA, zB, sB, a);
+        const uint32_t a0 = and_or(w4[j], kc.mask, kc.magic), a1 = and_or(shr_mulhi(w4[j], kc.m4), kc.mask, kc.magic);
+        const uint32_t a2 = and_or(shr_mulhi(w4[j], kc.m8), kc.mask, kc.magic), a3 = and_or(shr_mulhi(w4[j], kc.m12), kc.mask, kc.magic);
 #pragma unroll
-        for (int n = 0; n < NT; ++n) mma_16816(c[r][n], a[0], a[1], a[2], a[3], xw[n][2 * j], xw[n][2 * j + 1]);
+        for (int n = 0; n < NT; ++n) mma_16816(cq[n], a0, a1, a2, a3, xw[n][2 * j], xw[n][2 * j + 1]);
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        c[r][n][0] = fmaf(sA, fmaf(-zA, cx[n][0], cq[n][0]), c[r][n][0]);
+        c[r][n][1] = fmaf(sA, fmaf(-zA, cx[n][1], cq[n][1]), c[r][n][1]);
+        c[r][n][2] = fmaf(sB, fmaf(-zB, cx[n][2], cq[n][2]), c[r][n][2]);
+        c[r][n][3] = fmaf(sB, fmaf(-zB, cx[n][3], cq[n][3]), c[r][n][3]);
       }
     }
   };
@@ -208,16 +232,17 @@ dequant_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ m
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_items) return;
   const int lane = int(i & 31), g = lane >> 2, t = lane & 3;
-  const int n_super = K >> 6;
+  // consecutive warps walk the steps of one tile: the bf16 rows (four fifths of the traffic) are written as contiguous runs
+  const int n_super = K >> 6, n_tiles = N >> 4;
   const int S = int((i >> 5) % n_super), T = int((i >> 5) / n_super);
-  const uint4 w = __ldcs(wq + i);
+  const uint4 w = __ldcs(wq + ((long long)S * n_tiles + T) * 32 + lane);
   const long long grp = S >> (group_shift - 6);
   const uint32_t* mrow = meta + grp * N + T * 16 + g;
   const uint32_t mA = __ldg(mrow), mB = __ldg(mrow + 8);
   const uint32_t sA = __byte_perm(mA, mA, 0x1010), zA = __byte_perm(mA, mA, 0x3232);
   const uint32_t sB = __byte_perm(mB, mB, 0x1010), zB = __byte_perm(mB, mB, 0x3232);
   const uint32_t w4[4] = {w.x, w.y, w.z, w.w};
-  const Int4Consts kc = {0x000f000fu, 0x43004300u, 1u << 28, 1u << 24, 1u << 20};
+  const Int4Consts kc = {0x000f000fu, 0x43004300u, 1u << 28, 1u << 24, 1u << 20, 0x3f803f80u};
   uint32_t ra[8], rb[8];  // features g and g + 8: word 2 j = indices 4 j, 4 j + 1; word 2 j + 1 = indices 4 j + 2, 4 j + 3
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -270,7 +295,7 @@ ATS_API int ats_gemv_int4(const void* wq, const void* meta, const void* x, long 
   if (swiglu)
     err = two ? ATS_GEMV4(2, true, 2, 2, 2, tiles / 2) : ATS_GEMV4(2, true, 1, 2, 2, tiles / 2);
   else
-    err = two ? ATS_GEMV4(1, false, 2, 2, 2, tiles) : ATS_GEMV4(1, false, 1, 3, 4, tiles);
+    err = two ? ATS_GEMV4(1, false, 2, 2, 2, tiles) : ATS_GEMV4(1, false, 1, 3, 3, tiles);
 #undef ATS_GEMV4
   return int(err);
 }

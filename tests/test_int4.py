@@ -15,11 +15,11 @@ def test_packed_format_round_trip_and_nibble_positions():
     N, K = 48, 192
     q = torch.randint(0, 16, (N, K), dtype=torch.uint8)
     packed = int4.pack(q)
-    assert packed.shape == (N // 16, K // 64, 32, 4) and packed.dtype == torch.int32
+    assert packed.shape == (K // 64, N // 16, 32, 4) and packed.dtype == torch.int32
     assert torch.equal(int4.unpack(packed), q)
     # the documented position of a code: tile T, super-step S, lane 4 g + t, word j, nibble i
     for T, S, g, t, j, i in [(0, 0, 0, 0, 0, 0), (2, 1, 5, 3, 2, 7), (1, 2, 7, 1, 3, 4), (0, 1, 3, 2, 1, 3)]:
-        word = int(packed[T, S, 4 * g + t, j]) & 0xFFFFFFFF
+        word = int(packed[S, T, 4 * g + t, j]) & 0xFFFFFFFF
         row = 16 * T + g + 8 * (i & 1)
         col = 64 * S + 16 * t + 4 * j + 2 * ((i >> 1) & 1) + (i >> 2)
         assert (word >> (4 * i)) & 15 == int(q[row, col])
