@@ -68,16 +68,32 @@ __device__ __forceinline__ void dq_word(uint32_t w, const Int4Consts& k, uint32_
 
 constexpr int GEMV_WARPS = 8;
 
-// what a warp loads for one super-step: packed words and scale words of its R tiles, 16 activations per token tile
-template <int R, int NT>
-struct Int4Stage {
-  uint4 w[R];
-  uint32_t mA[R], mB[R];
-  uint4 x[NT][2];
-};
+// Asynchronous copies global -> shared (each lane copies into slots only it reads back, so no barrier is involved: a lane waits
+// for its own copy groups).  Loads into registers did not pipeline here: with five loads per step and stage the kernel waited
+// a full round trip to memory in every step whatever the prefetch depth (1.9 TB/s, warps 68 % of the time on the long
+// scoreboard); copy groups are counted, not score-boarded.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(smem))), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async16_or_zero(void* smem, const void* gmem, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(uint32_t(__cvta_generic_to_shared(smem))), "l"(gmem), "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(uint32_t(__cvta_generic_to_shared(smem))), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// bytes one warp holds per stage: packed words and scale words of R tiles, 16 activations per lane and token tile
+__host__ __device__ constexpr int int4_stage_bytes(int R, int NT) { return 32 * (R * 16 + R * 8 + NT * 32); }
+__host__ __device__ constexpr int int4_ring_bytes(int R, int NT, int DEPTH) { return GEMV_WARPS * DEPTH * int4_stage_bytes(R, NT); }
 
 // R tiles per CTA: one, or with SWIGLU the gate tile and the up tile of the same features.  The warps split the super-steps;
-// every warp keeps the weight and scale loads of DEPTH of its super-steps in flight (registers), so that a CTA's few microseconds
+// every warp keeps the copies of DEPTH of its super-steps in flight (a ring in shared memory), so that a CTA's few microseconds
 // are spent streaming and not waiting for one round trip to memory per step.  One tile per CTA and MINB resident CTAs per SM keep
 // the grid fine-grained: with two tiles and 72 registers the 28,672-feature projection ran as 2.02 waves of CTAs, i.e. three.
 // NT: token tiles of eight rows (the dequantised fragments of a step feed NT MMAs).
@@ -109,32 +125,35 @@ gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta
     xrow[n] = reinterpret_cast<const uint4*>(x + (long long)(tok[n] ? 8 * n + g : 0) * ldx + 16 * t);
   }
 
-  auto issue = [&](Int4Stage<R, NT>& s, int S) {
+  extern __shared__ __align__(16) unsigned char ring[];
+  constexpr int STAGE = int4_stage_bytes(R, NT);
+  unsigned char* my_ring = ring + warp * DEPTH * STAGE;
+  // slots of this lane inside a stage: [R][32] packed words (16 B), [R][32] scale words (2 x 4 B), [2 NT][32] activations (16 B)
+  auto w_slot = [&](int d, int r) { return my_ring + d * STAGE + r * 512 + lane * 16; };
+  auto m_slot = [&](int d, int r) { return my_ring + d * STAGE + R * 512 + r * 256 + lane * 8; };
+  auto x_slot = [&](int d, int i) { return my_ring + d * STAGE + R * 768 + i * 512 + lane * 16; };
+  auto issue = [&](int d, int S) {
     const long long grp = S >> (group_shift - 6);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      s.w[r] = __ldcs(wq + ((long long)S * n_tiles + tile[r]) * 32 + lane);
+      cp_async16(w_slot(d, r), wq + ((long long)S * n_tiles + tile[r]) * 32 + lane);
       const uint32_t* mrow = meta + grp * N + tile[r] * 16 + g;
-      s.mA[r] = __ldg(mrow);
-      s.mB[r] = __ldg(mrow + 8);
+      cp_async4(m_slot(d, r), mrow);
+      cp_async4(m_slot(d, r) + 4, mrow + 8);
     }
-    // a third of these miss L1 (the weight stream passes through it); fetched one step ahead they stalled every step for an L2
-    // round trip, so they travel with the weights, DEPTH steps ahead
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      s.x[n][0] = s.x[n][1] = make_uint4(0, 0, 0, 0);
-      if (tok[n]) {
-        s.x[n][0] = __ldg(xrow[n] + S * 8);
-        s.x[n][1] = __ldg(xrow[n] + S * 8 + 1);
-      }
+    for (int n = 0; n < NT; ++n) {  // lanes without a token get zeros
+      cp_async16_or_zero(x_slot(d, 2 * n), xrow[n] + S * 8, tok[n]);
+      cp_async16_or_zero(x_slot(d, 2 * n + 1), xrow[n] + S * 8 + 1, tok[n]);
     }
   };
-  auto compute = [&](const Int4Stage<R, NT>& s) {
+  auto compute = [&](int d) {
     uint32_t xw[NT][8];
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-      xw[n][0] = s.x[n][0].x; xw[n][1] = s.x[n][0].y; xw[n][2] = s.x[n][0].z; xw[n][3] = s.x[n][0].w;
-      xw[n][4] = s.x[n][1].x; xw[n][5] = s.x[n][1].y; xw[n][6] = s.x[n][1].z; xw[n][7] = s.x[n][1].w;
+      const uint4 x0 = *reinterpret_cast<const uint4*>(x_slot(d, 2 * n)), x1 = *reinterpret_cast<const uint4*>(x_slot(d, 2 * n + 1));
+      xw[n][0] = x0.x; xw[n][1] = x0.y; xw[n][2] = x0.z; xw[n][3] = x0.w;
+      xw[n][4] = x1.x; xw[n][5] = x1.y; xw[n][6] = x1.z; xw[n][7] = x1.w;
     }
     // sum of the step's activations per token: a product with an all-ones A operand (every row of the result holds it)
     float cx[NT][4];
@@ -147,9 +166,11 @@ gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       // bf16 -> fp32 is a shift: scale, and 128 + zero, of features g (A) and g + 8 (B)
-      const float sA = __uint_as_float(s.mA[r] << 16), zA = __uint_as_float(s.mA[r] & 0xffff0000u);
-      const float sB = __uint_as_float(s.mB[r] << 16), zB = __uint_as_float(s.mB[r] & 0xffff0000u);
-      const uint32_t w4[4] = {s.w[r].x, s.w[r].y, s.w[r].z, s.w[r].w};
+      const uint2 mAB = *reinterpret_cast<const uint2*>(m_slot(d, r));
+      const float sA = __uint_as_float(mAB.x << 16), zA = __uint_as_float(mAB.x & 0xffff0000u);
+      const float sB = __uint_as_float(mAB.y << 16), zB = __uint_as_float(mAB.y & 0xffff0000u);
+      const uint4 wv = *reinterpret_cast<const uint4*>(w_slot(d, r));
+      const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
       float cq[NT][4];
 #pragma unroll
       for (int n = 0; n < NT; ++n) cq[n][0] = cq[n][1] = cq[n][2] = cq[n][3] = 0.f;
@@ -170,29 +191,26 @@ gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta
     }
   };
 
-  Int4Stage<R, NT> st[DEPTH];
+  // group i of this lane's copies holds super-step warp + 8 i; one group is committed per step, empty past the end
 #pragma unroll
   for (int d = 0; d < DEPTH; ++d) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      st[d].w[r] = make_uint4(0, 0, 0, 0);
-      st[d].mA[r] = st[d].mB[r] = 0u;
-    }
-#pragma unroll
-    for (int n = 0; n < NT; ++n) st[d].x[n][0] = st[d].x[n][1] = make_uint4(0, 0, 0, 0);
-    if (warp + d * GEMV_WARPS < n_super) issue(st[d], warp + d * GEMV_WARPS);
+    if (warp + d * GEMV_WARPS < n_super) issue(d, warp + d * GEMV_WARPS);
+    cp_async_commit();
   }
   for (int S0 = warp; S0 < n_super; S0 += GEMV_WARPS * DEPTH) {
 #pragma unroll
     for (int d = 0; d < DEPTH; ++d) {
       const int S = S0 + d * GEMV_WARPS;
       if (S < n_super) {  // the same for every lane of the warp
-        compute(st[d]);
+        cp_async_wait<DEPTH - 1>();  // all but the DEPTH - 1 youngest groups have landed: this step's is among them
+        compute(d);
         const int Sn = S + GEMV_WARPS * DEPTH;
-        if (Sn < n_super) issue(st[d], Sn);
+        if (Sn < n_super) issue(d, Sn);  // the slots just read are refilled (their values are in registers by now)
+        cp_async_commit();
       }
     }
   }
+  cp_async_wait<0>();
   // accumulator of token tile n: c[0], c[1] = feature g, tokens 8 n + 2t and + 1; c[2], c[3] = feature g + 8
 #pragma unroll
   for (int r = 0; r < R; ++r)
@@ -289,13 +307,23 @@ ATS_API int ats_gemv_int4(const void* wq, const void* meta, const void* x, long 
   cudaError_t err;
   const dim3 block(ats::GEMV_WARPS * 32);
 #define ATS_GEMV4(R_, SW_, NT_, D_, B_, GRID_)                                                                                        \
-  ats::launch_pdl(ats::gemv_int4_kernel<R_, SW_, NT_, D_, B_>, dim3(GRID_), block, 0, s, w4, mt, xp, ldx, ap, ld_add, op, ld_out, M, N, \
-                  K, gs)
+  [&]() -> cudaError_t {                                                                                                             \
+    constexpr int kRing = ats::int4_ring_bytes(R_, NT_, D_);                                                                         \
+    static bool attr_set = false;                                                                                                    \
+    if (!attr_set) {                                                                                                                 \
+      cudaError_t ce = cudaFuncSetAttribute(ats::gemv_int4_kernel<R_, SW_, NT_, D_, B_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                            kRing);                                                                                  \
+      if (ce != cudaSuccess) return ce;                                                                                              \
+      attr_set = true;                                                                                                               \
+    }                                                                                                                                \
+    return ats::launch_pdl(ats::gemv_int4_kernel<R_, SW_, NT_, D_, B_>, dim3(GRID_), block, kRing, s, w4, mt, xp, ldx, ap, ld_add,  \
+                           op, ld_out, M, N, K, gs);                                                                                 \
+  }()
   const bool two = M > 8;
   if (swiglu)
-    err = two ? ATS_GEMV4(2, true, 2, 2, 2, tiles / 2) : ATS_GEMV4(2, true, 1, 2, 2, tiles / 2);
+    err = two ? ATS_GEMV4(2, true, 2, 3, 2, tiles / 2) : ATS_GEMV4(2, true, 1, 4, 2, tiles / 2);
   else
-    err = two ? ATS_GEMV4(1, false, 2, 2, 2, tiles) : ATS_GEMV4(1, false, 1, 3, 3, tiles);
+    err = two ? ATS_GEMV4(1, false, 2, 4, 2, tiles) : ATS_GEMV4(1, false, 1, 4, 3, tiles);
 #undef ATS_GEMV4
   return int(err);
 }
