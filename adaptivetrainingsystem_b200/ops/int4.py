@@ -6,8 +6,9 @@ codes column by column and pushes each column's rounding error onto the columns 
 Hessian ``(X^T X + damping)^-1`` of the layer's calibration inputs (Frantar et al. 2022); without a Hessian the codes are plain
 round-to-nearest.  The codes are stored in the order the decode kernel's tensor-core fragments want them (``csrc/int4.cu``):
 
-* one to sixteen token rows: ``ats_gemv_int4`` streams the packed weight once (a quarter of the bf16 bytes), dequantises in
-  registers and multiplies with warp-level MMAs; residual add and SwiGLU are fused into its epilogue;
+* one to sixteen token rows: ``ats_gemv_int4`` streams the packed weight once (a quarter of the bf16 bytes) through a ring of
+  asynchronous copies, feeds the codes to warp-level MMAs and applies zero point and scale per 64-channel step in fp32;
+  residual add and SwiGLU are fused into its epilogue;
 * more rows (a prompt): ``ats_dequant_int4`` writes the bf16 matrix and the tcgen05 GEMM does the product.
 
 Only weights registered by :func:`register` (``QuantizationManager.quantize_model`` with method ``"int4"`` / ``"gptq"``) take

@@ -2,7 +2,7 @@
 //
 // A decode step of a few tokens reads every weight once and does almost no arithmetic with it, so the step time is the weight
 // bytes divided by the HBM rate: 4-bit weights cut it to a quarter of bf16.  tcgen05 wants at least 64 token rows and operands
-// in shared memory in its own layout; for one to eight tokens the warp-level MMA (m16n8k16, bf16 in, fp32 out) is the right tool:
+// in shared memory in its own layout; for one to sixteen tokens the warp-level MMA (m16n8k16, bf16 in, fp32 out) is the right tool:
 // the WEIGHTS are the 16-row A operand, the tokens the 8 columns of B, so no tensor row is wasted, and the packed format is laid
 // out such that the 16 bytes a lane loads ARE its A fragments of four consecutive k-steps:
 //
@@ -10,18 +10,20 @@
 //   nibble i of word [S][T][lane][j] holds feature 16 T + g + 8 (i & 1), reduction index 64 S + 16 t + 4 j + 2 ((i >> 1) & 1) + (i >> 2)
 //
 // The super-step is the OUTER index of the stored array: CTAs own tiles, start together and advance at the same pace, so at any
-// time the CTAs in flight read one contiguous window of the array per warp slot, as a copy kernel does.  With the tile outermost
-// every CTA walked its own 32 KB region 4 KB at a time and the kernel stayed at 1.9 TB/s whatever else was changed (pipeline
-// depth, occupancy, instruction count): DRAM saw several hundred scattered 512-byte streams.
+// time the CTAs in flight read one contiguous window of the array per warp slot, as a copy kernel does (measured against the
+// tile-outermost order: no difference at these sizes; kept because it is the order that stays sequential as K grows).
 //
 // (the sum over the reduction index does not care about the order of its terms, so inside a k-step the MMA's logical indices
 // 2t, 2t+1, 2t+8, 2t+9 are mapped to the four consecutive actual indices 16 t + 4 j .. + 3: the B fragment of a lane is then 8
 // consecutive bytes of a token's row, and the 32 bytes it loads per super-step serve four k-steps).  `(w >> 4 r) & 0x000f000f |
-// 0x43004300` turns two nibbles into the bf16 pair (128 + q_lo, 128 + q_hi) exactly; subtracting the bf16 pair (128 + zero) is
-// exact too, and one bf16 multiply by the group's scale gives the same value a dequantised bf16 copy of the weight would hold.
+// 0x43004300` turns two nibbles into the bf16 pair (128 + q_lo, 128 + q_hi) exactly.  The streaming kernel feeds these raw
+// pairs to the MMA and takes zero point and scale out of the sum: per 64-channel step (inside one group) it accumulates
+// sum((128 + q) x) and, with an all-ones A operand, sum(x), and adds scale * (sum((128 + q) x) - (128 + zero) * sum(x)) to the
+// running result in fp32, which is the exact product with (q - zero) * scale.  The dequantise kernel subtracts the bf16 pair
+// (128 + zero) (exact) and multiplies by the bf16 scale (one rounding): the bf16 weight a prompt-sized GEMM then reads.
 // Per (group, feature) one 32-bit word: low half the bf16 scale, high half bf16(128 + zero).
 //
-// ats_gemv_int4: up to 8 tokens, optional residual add, optional SwiGLU over the two halves of the features.
+// ats_gemv_int4: up to 16 tokens (one or two token tiles of eight), optional residual add, optional SwiGLU over the two halves of the features.
 // ats_dequant_int4: the bf16 matrix for prompt-sized products, which then run on the tcgen05 GEMM.
 //
 // Counterparts in the reference: the GPTQ hook of training/trainer.py:681-710 (AutoGPTQ, 4 bits, group 128) and the Triton GPTQ
