@@ -229,6 +229,15 @@ def record(x2: torch.Tensor, w: torch.Tensor) -> None:
     _hessians[key] = (h, xf.shape[0]) if prev is None else (prev[0] + h, prev[1] + xf.shape[0])
 
 
+def hessian_count() -> int:
+    return len(_hessians)
+
+
+def drop_hessians() -> None:
+    """K x K fp32 per projection: not needed once the codes are fixed."""
+    _hessians.clear()
+
+
 def hessian_for(w: torch.Tensor) -> Optional[torch.Tensor]:
     hit = _hessians.get(w.data_ptr())
     return None if hit is None or hit[0].shape[0] != w.shape[1] else hit[0]
@@ -258,6 +267,7 @@ def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01) -> Tuple[t
 
 
 def lookup(w: torch.Tensor):
+    """-> (packed, scale words, group) of the registered 4-bit copy of ``w``, or None (never registered, or changed since)."""
     hit = _weights.get(w.data_ptr())
     if hit is None or hit[0] != w._version or hit[1] != tuple(w.shape):
         return None

@@ -126,8 +126,8 @@ class QuantizationManager:
             finally:
                 int4.observe(False)
                 model.train(was)
-            self.calibrated = len(int4._hessians) > 0
-            return len(int4._hessians)
+            self.calibrated = int4.hessian_count() > 0
+            return int4.hessian_count()
         int8.set_enabled(False)
         int8.observe(True)
         try:
@@ -170,7 +170,7 @@ class QuantizationManager:
                     self.quantized_tensors += 1
                     self.gptq_weights += int(used_gptq)
                     self.quantized_bytes += packed.numel() * 4 + meta.numel() * 4
-            int4._hessians.clear()      # K x K fp32 each: not needed once the codes are fixed
+            int4.drop_hessians()
             int4.set_enabled(True)
             self.applied = True
             return model

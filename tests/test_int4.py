@@ -176,10 +176,10 @@ def test_int4_model_matches_its_dequantised_weights():
         assert gen_q.shape == (2, 16)
         int4.set_enabled(False)
         with torch.no_grad():
+            copies = {name: int4.lookup(p) for name, p in model.named_parameters()}
             for name, p in model.named_parameters():
-                hit = int4._weights.get(p.data_ptr())
-                if hit is not None:
-                    p.copy_(int4.dequantize(hit[2], hit[3], hit[4]))
+                if copies[name] is not None:
+                    p.copy_(int4.dequantize(*copies[name]))
             out_d = model(ids, return_aux_loss=False).float()
             out_d1 = model(ids[:1, :8], return_aux_loss=False).float()
             lg = model(torch.cat([ids, gen_q], 1), return_aux_loss=False).float()[:, 47:63]     # the oracle's logits for every generated token
