@@ -345,6 +345,7 @@ class Config:
     bf16_enabled: bool = True
     quantization_method: Optional[str] = None
     quantization_bits: Optional[int] = None
+    quantization_symmetric: bool = False      # 4-bit: zero point fixed at 8 (AutoGPTQ's sym=True)
     # -- memory -------------------------------------------------------------------
     max_memory_usage: float = 0.9
     memory_cleanup_interval: int = 1000

@@ -531,10 +531,10 @@ def swiglu_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
     from . import int4, int8
     if int8.observing():
         int8.record(x.reshape(-1, x.shape[-1]), w_gate_up)
-    if int4.observing() and reduce_group is None and not torch.is_grad_enabled():
-        return int4.swiglu_mlp_observed(x, w_gate_up, w_down, residual)
     if reduce_group is None and int4.usable(x, w_gate_up) and int4.usable(x, w_down):
         return int4.swiglu_mlp_int4(x, w_gate_up, w_down, residual)
+    if int4.observing() and reduce_group is None and not torch.is_grad_enabled():
+        return int4.swiglu_mlp_observed(x, w_gate_up, w_down, residual)
     if reduce_group is None and int8.usable(x, w_gate_up) and w_gate_up.shape[0] % 32 == 0 and w_down.shape[1] % 16 == 0:
         return int8.swiglu_mlp_int8(x, w_gate_up, w_down, residual)
     if _lib.use_cuda_kernels(x):

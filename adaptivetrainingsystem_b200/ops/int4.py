@@ -30,6 +30,7 @@ _vp, _ci, _cll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 _sig = False
 _enabled = False
 _observing = False
+_observe_only = None                          # storages whose Hessians are wanted (None: all)
 GROUP = 128
 MAX_HESSIAN_DIM = 16384                       # input widths above this are quantised round-to-nearest (the Hessian is K x K fp32)
 GEMV_MAX_ROWS = 16                            # two token tiles of the streaming kernel; beyond that the dequantise + GEMM path
@@ -67,28 +68,29 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.bfloat16).float()
 
 
-def group_params(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """w [N, n] (one group of columns) -> (scale [N] rounded to bf16, zero [N] in 0..15) covering [min(w, 0), max(w, 0)]."""
-    lo = w.amin(1).clamp(max=0.0)
-    hi = w.amax(1).clamp(min=0.0)
+def group_params(w: torch.Tensor, sym: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """w [..., n] (groups of columns in the last dimension) -> (scale [...] rounded to bf16, zero [...] in 0..15) covering
+    [min(w, 0), max(w, 0)]; ``sym``: the range is made symmetric and the zero point is 8 (AutoGPTQ's ``sym=True``)."""
+    lo = w.amin(-1).clamp(max=0.0)
+    hi = w.amax(-1).clamp(min=0.0)
+    if sym:
+        hi = torch.maximum(hi, -lo)
+        lo = -hi
     scale = _bf16(((hi - lo) / 15.0).clamp(min=1e-8))
-    zero = torch.round(-lo / scale).clamp(0, 15)
+    zero = torch.full_like(scale, 8.0) if sym else torch.round(-lo / scale).clamp(0, 15)
     return scale, zero
 
 
-def quantize_rtn(w: torch.Tensor, group: int = GROUP) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def quantize_rtn(w: torch.Tensor, group: int = GROUP, sym: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Round to nearest: -> (codes [N, K] uint8, scale [N, K / group] fp32, zero [N, K / group] fp32)."""
     N, K = w.shape
     wf = w.detach().float().view(N, K // group, group)
-    lo = wf.amin(2).clamp(max=0.0)
-    hi = wf.amax(2).clamp(min=0.0)
-    scale = _bf16(((hi - lo) / 15.0).clamp(min=1e-8))
-    zero = torch.round(-lo / scale).clamp(0, 15)
+    scale, zero = group_params(wf, sym)
     q = (torch.round(wf / scale[:, :, None]) + zero[:, :, None]).clamp(0, 15)
     return q.view(N, K).to(torch.uint8), scale, zero
 
 
-def gptq_quantize(w: torch.Tensor, hessian: torch.Tensor, group: int = GROUP, damp: float = 0.01
+def gptq_quantize(w: torch.Tensor, hessian: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool = False
                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """GPTQ: ``hessian`` = sum over calibration rows of x^T x, [K, K].  Same outputs as :func:`quantize_rtn`."""
     N, K = w.shape
@@ -108,7 +110,7 @@ def gptq_quantize(w: torch.Tensor, hessian: torch.Tensor, group: int = GROUP, da
         W1 = W[:, i1:i2].clone()
         E1 = torch.empty_like(W1)
         H1 = Hinv[i1:i2, i1:i2]
-        sc, z = group_params(W1)           # the group's range after the corrections pushed onto it by the groups before
+        sc, z = group_params(W1, sym)      # the group's range after the corrections pushed onto it by the groups before
         scale[:, b], zero[:, b] = sc, z
         for i in range(group):
             col = W1[:, i]
@@ -208,10 +210,12 @@ def gemv(x2: torch.Tensor, packed: torch.Tensor, meta: torch.Tensor, group: int 
 
 
 # -- calibration (Hessians for GPTQ) -----------------------------------------------------------------------------------------------
-def observe(flag: bool) -> None:
-    """While on, every ``ops.linear`` / MLP product adds x^T x of its input rows to the Hessian of its weight."""
-    global _observing
+def observe(flag: bool, only=None) -> None:
+    """While on, every ``ops.linear`` / MLP product adds x^T x of its input rows to the Hessian of its weight; ``only``: an
+    iterable of weights to restrict the collection to (block-by-block calibration)."""
+    global _observing, _observe_only
     _observing = bool(flag)
+    _observe_only = None if (only is None or not flag) else {w.data_ptr() for w in only}
 
 
 def observing() -> bool:
@@ -220,7 +224,7 @@ def observing() -> bool:
 
 def record(x2: torch.Tensor, w: torch.Tensor) -> None:
     K = x2.shape[-1]
-    if w.dim() != 2 or K > MAX_HESSIAN_DIM:
+    if w.dim() != 2 or K > MAX_HESSIAN_DIM or (_observe_only is not None and w.data_ptr() not in _observe_only):
         return
     xf = x2.detach().reshape(-1, K).float()
     h = xf.t() @ xf
@@ -244,7 +248,7 @@ def hessian_for(w: torch.Tensor) -> Optional[torch.Tensor]:
 
 
 # -- registry ---------------------------------------------------------------------------------------------------------------------
-def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01) -> Tuple[torch.Tensor, torch.Tensor, bool]:
+def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool = False) -> Tuple[torch.Tensor, torch.Tensor, bool]:
     """Quantises ``w`` [N, K] (GPTQ when calibration left a Hessian for it, else round-to-nearest) and routes ``ops.linear`` /
     the SwiGLU MLP with this weight to the 4-bit kernels.  -> (packed, meta, used_gptq)."""
     N, K = w.shape
@@ -255,12 +259,12 @@ def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01) -> Tuple[t
     if H is not None:
         for d in (damp, 10.0 * damp, 100.0 * damp):     # a Hessian of few calibration rows can defeat the fp32 factorisation
             try:
-                done = gptq_quantize(w, H, group, d)
+                done = gptq_quantize(w, H, group, d, sym)
                 break
             except torch.linalg.LinAlgError:
                 continue
     used_gptq = done is not None
-    q, scale, zero = done if used_gptq else quantize_rtn(w, group)
+    q, scale, zero = done if used_gptq else quantize_rtn(w, group, sym)
     packed, meta = pack(q), pack_meta(scale, zero)
     _weights[w.data_ptr()] = (w._version, (N, K), packed, meta, group)
     return packed, meta, used_gptq

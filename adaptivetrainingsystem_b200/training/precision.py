@@ -104,6 +104,7 @@ class QuantizationManager:
         if self.method is None and self.bits == 4:
             self.method = "int4"
         self.gptq_weights = 0
+        self.symmetric = bool(getattr(config, "quantization_symmetric", False))   # AutoGPTQ's ``sym``: zero point fixed at 8
         self.applied = False
         self.calibrated = False
         self.quantized_tensors = 0
@@ -140,6 +141,52 @@ class QuantizationManager:
         self.calibrated = n > 0
         return n
 
+    @staticmethod
+    def _int4_targets(model):
+        """(name, parameter) of every projection the 4-bit path covers, in model order."""
+        from ..ops import int4
+        return [(name, p) for name, p in model.named_parameters()
+                if p.dim() == 2 and int4.shape_ok(p.shape[0], p.shape[1]) and "embed" not in name and "lm_head" not in name
+                and "gate.weight" not in name and "router" not in name and getattr(p, "_ats_z3", None) is None]
+
+    def _register_int4(self, p) -> None:
+        from ..ops import int4
+        packed, meta, used_gptq = int4.register(p, sym=self.symmetric)
+        self.quantized_tensors += 1
+        self.gptq_weights += int(used_gptq)
+        self.quantized_bytes += packed.numel() * 4 + meta.numel() * 4
+
+    @torch.no_grad()
+    def quantize_sequential(self, model, batches):
+        """GPTQ block by block (AutoGPTQ's ``true_sequential``): the Hessians of a block's projections are collected from inputs
+        that already went through the quantised blocks before it, so every block compensates for the error made upstream; only
+        one block's Hessians exist at a time.  Costs one pass over ``batches`` per block."""
+        if self.method not in ("int4", "gptq"):
+            raise RuntimeError("block-by-block quantisation is the 4-bit GPTQ path (quantization_method 'int4' or 'gptq')")
+        from ..ops import int4
+        model.eval()
+        for p in model.parameters():
+            p.requires_grad_(False)
+        blocks: Dict[str, list] = {}
+        for name, p in self._int4_targets(model):
+            parts = name.split(".")
+            key = ".".join(parts[:2]) if parts[0] == "layers" and len(parts) > 2 else parts[0]
+            blocks.setdefault(key, []).append(p)
+        int4.set_enabled(True)              # registered projections run quantised from the moment they exist
+        try:
+            for key, params in blocks.items():
+                int4.observe(True, only=params)
+                for ids in batches:
+                    model(ids, return_aux_loss=False)
+                int4.observe(False)
+                for p in params:
+                    self._register_int4(p)
+                int4.drop_hessians()
+        finally:
+            int4.observe(False)
+        self.calibrated = self.applied = True
+        return model
+
     def available_backends(self) -> Dict[str, bool]:
         out = {"fp8 (native e4m3 GEMM)": torch.cuda.is_available(), "int8 / smoothquant (native s8 GEMM)": True,
                "int4 / gptq (native weight-only 4-bit)": True}
@@ -163,13 +210,8 @@ class QuantizationManager:
         for p in model.parameters():
             p.requires_grad_(False)
         if self.method in ("int4", "gptq"):
-            for name, p in model.named_parameters():
-                if (p.dim() == 2 and int4.shape_ok(p.shape[0], p.shape[1]) and "embed" not in name and "lm_head" not in name
-                        and "gate.weight" not in name and "router" not in name and getattr(p, "_ats_z3", None) is None):
-                    packed, meta, used_gptq = int4.register(p)
-                    self.quantized_tensors += 1
-                    self.gptq_weights += int(used_gptq)
-                    self.quantized_bytes += packed.numel() * 4 + meta.numel() * 4
+            for name, p in self._int4_targets(model):
+                self._register_int4(p)
             int4.drop_hessians()
             int4.set_enabled(True)
             self.applied = True

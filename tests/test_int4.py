@@ -90,6 +90,46 @@ def test_manager_quantises_projections_to_4_bits_cpu():
         int4.clear()
 
 
+def test_symmetric_codes_and_block_by_block_gptq_cpu():
+    """``sym``: zero point 8 everywhere and a range that covers -max |w| .. max |w|.  Block-by-block GPTQ: every projection gets
+    GPTQ codes, only one block's Hessians exist at a time, and the logits stay as close as with one-shot calibration."""
+    from adaptivetrainingsystem_b200.training.precision import QuantizationManager
+    torch.manual_seed(3)
+    w = torch.randn(32, 256) * 0.1
+    q, scale, zero = int4.quantize_rtn(w, 128, sym=True)
+    assert (zero == 8).all()
+    wd = int4.dequantize_reference(int4.pack(q), int4.pack_meta(scale, zero), 128).float()
+    assert ((w - wd).abs() <= 0.5 * scale.repeat_interleave(128, dim=1) * 1.05 + 2.0 ** -8 * w.abs() + 1e-6).all()   # the bf16 scale may fall 0.2 % short of max / 7.5
+    cfg = ModelConfig(vocab_size=256, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=256, seq_length=32,
+                      tie_word_embeddings=False)
+    ids = [torch.randint(0, 256, (4, 32)) for _ in range(2)]
+    errs = {}
+    for mode in ("one_shot", "sequential"):
+        torch.manual_seed(0)
+        model = DeepSeekTransformer(cfg)
+        with torch.no_grad():
+            ref = model(ids[0], return_aux_loss=False)
+        try:
+            qm = QuantizationManager(SimpleNamespace(quantization_method="gptq", quantization_bits=4, quantization_symmetric=True))
+            assert qm.symmetric
+            if mode == "one_shot":
+                qm.calibrate(model, ids)
+                qm.quantize_model(model)
+            else:
+                qm.quantize_sequential(model, ids)
+                assert int4.hessian_count() == 0 and int4.enabled()
+            assert qm.status()["tensors"] == 8 and qm.status()["gptq_weights"] == 8
+            _, zero_l = int4.unpack_meta(int4.lookup(model.layers[1].ffn.down_proj)[1])
+            assert (zero_l == 8).all()
+            with torch.no_grad():
+                out = model(ids[0], return_aux_loss=False)
+            errs[mode] = ((out - ref).norm() / ref.norm()).item()
+        finally:
+            int4.set_enabled(False)
+            int4.clear()
+    assert 0.0 < errs["sequential"] < 0.25 and errs["sequential"] < 1.5 * errs["one_shot"], errs
+
+
 # ------------------------------------------------------------------------------------------------------------------------- GPU
 def _packed(N, K, group, dev, seed):
     g = torch.Generator().manual_seed(seed)
