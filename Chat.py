@@ -53,7 +53,7 @@ def load_checkpoint_smart(path: str):
 
 
 class ChatInterface:
-    def __init__(self, checkpoint: str, device: str = "auto", mode: str = "standard", quantize: str = None):
+    def __init__(self, checkpoint: str, device: str = "auto", mode: str = "standard", quantize: str = None, quantized_file: str = None):
         self.device = torch.device("cuda" if (device == "auto" and torch.cuda.is_available()) else ("cpu" if device == "auto" else device))
         sd, cfg = load_checkpoint_smart(checkpoint)
         cfg.gradient_checkpointing = False
@@ -66,7 +66,14 @@ class ChatInterface:
                 raise SystemExit("--quantize needs a GPU: the fp8 path runs on the tensor-core GEMM")
             from types import SimpleNamespace
             from adaptivetrainingsystem_b200.training import QuantizationManager
-            QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=4 if quantize == "int4" else 8)).quantize_model(self.model)
+            qm = QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=4 if quantize == "int4" else 8))
+            if quantize == "int4" and quantized_file and os.path.exists(quantized_file):
+                # 4-bit copies written earlier (possibly GPTQ-calibrated): attach them and drop the bf16 projections
+                qm.load_quantized(self.model, quantized_file, release_originals=True)
+            else:
+                qm.quantize_model(self.model)
+                if quantize == "int4" and quantized_file:
+                    qm.save_quantized(self.model, quantized_file)
         self.tokenizer = ConversationTokenizer()
         self.engine = GenerationEngine(self.model, self.tokenizer)
         self.params = SamplingParams.from_mode(mode, max_new_tokens=min(256, max(cfg.seq_length // 2, 1)),
@@ -140,10 +147,12 @@ if __name__ == "__main__":
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--device", default="auto")
     ap.add_argument("--quantize", default=None, choices=["fp8", "int8", "int4"], help="post-training quantisation of the projection weights")
+    ap.add_argument("--quantized-file", default=None,
+                    help="with --quantize int4: load the packed 4-bit copies from this file if it exists (the bf16 projections are freed), else write them there")
     ap.add_argument("--prompts-file", default=None, help="one prompt per line, answered together by continuous batching")
     ap.add_argument("--max-batch", type=int, default=16)
     a = ap.parse_args()
-    chat = ChatInterface(a.checkpoint, a.device, a.mode, a.quantize)
+    chat = ChatInterface(a.checkpoint, a.device, a.mode, a.quantize, a.quantized_file)
     if a.prompts_file:
         with open(a.prompts_file) as f:
             lines = [l.strip() for l in f if l.strip()]

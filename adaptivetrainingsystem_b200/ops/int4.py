@@ -270,6 +270,27 @@ def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool 
     return packed, meta, used_gptq
 
 
+def register_packed(w: torch.Tensor, packed: torch.Tensor, meta: torch.Tensor, group: int = GROUP) -> None:
+    """Attaches an existing 4-bit copy (a saved one) to ``w`` without quantising anything."""
+    N, K = w.shape
+    if tuple(packed.shape) != (K // 64, N // 16, 32, 4) or tuple(meta.shape) != (K // group, N) or not shape_ok(N, K, group):
+        raise ValueError(f"packed copy {tuple(packed.shape)} / {tuple(meta.shape)} does not describe a {N} x {K} weight with groups of {group}")
+    _weights[w.data_ptr()] = (w._version, (N, K), packed.to(w.device, torch.int32).contiguous(), meta.to(w.device, torch.int32).contiguous(), group)
+
+
+def release_original(w: torch.Tensor) -> int:
+    """Frees the bf16 storage of a registered weight: ``w`` keeps its shape but points at one element broadcast over it
+    (stride 0), so every read of its VALUES is meaningless from here on; only the 4-bit path may use it.  -> bytes freed."""
+    hit = _weights.pop(w.data_ptr(), None)
+    if hit is None or hit[0] != w._version or hit[1] != tuple(w.shape):
+        raise ValueError("release_original: the weight has no current 4-bit copy")
+    freed = w.numel() * w.element_size()
+    stub = torch.zeros(1, dtype=w.dtype, device=w.device)
+    w.data = stub.expand(*hit[1])
+    _weights[w.data_ptr()] = (w._version, hit[1], hit[2], hit[3], hit[4])
+    return freed
+
+
 def lookup(w: torch.Tensor):
     """-> (packed, scale words, group) of the registered 4-bit copy of ``w``, or None (never registered, or changed since)."""
     hit = _weights.get(w.data_ptr())

@@ -187,6 +187,60 @@ class QuantizationManager:
         self.calibrated = self.applied = True
         return model
 
+    # -- 4-bit copies at rest ----------------------------------------------------------------------------------------------------
+    def save_quantized(self, model, path: str) -> int:
+        """Writes the packed 4-bit copies (codes + scale words per projection, by parameter name) so that a later process can
+        serve them without repeating the calibration (AutoGPTQ's ``save_quantized``).  -> number of tensors written."""
+        from ..ops import int4
+        tensors = {}
+        for name, p in self._int4_targets(model):
+            hit = int4.lookup(p)
+            if hit is not None:
+                tensors[name] = {"packed": hit[0].cpu(), "meta": hit[1].cpu(), "group": int(hit[2])}
+        if not tensors:
+            raise RuntimeError("no projection of this model has a 4-bit copy: run quantize_model / quantize_sequential first")
+        torch.save({"format": "ats-int4-v1", "symmetric": self.symmetric, "tensors": tensors}, path)
+        return len(tensors)
+
+    @torch.no_grad()
+    def load_quantized(self, model, path: str, release_originals: bool = False) -> int:
+        """Attaches saved 4-bit copies to the projections of ``model`` (same architecture) and switches the 4-bit path on.  With
+        ``release_originals`` the bf16 storage of those projections is freed (see :meth:`release_originals`)."""
+        from ..ops import int4
+        blob = torch.load(path, map_location="cpu", weights_only=True)
+        if not isinstance(blob, dict) or blob.get("format") != "ats-int4-v1":
+            raise RuntimeError(f"{path} is not a file written by save_quantized")
+        model.eval()
+        for p in model.parameters():
+            p.requires_grad_(False)
+        params = dict(self._int4_targets(model))
+        missing = [n for n in blob["tensors"] if n not in params]
+        if missing:
+            raise RuntimeError(f"saved 4-bit copies for parameters this model does not have: {missing[:4]}")
+        for name, t in blob["tensors"].items():
+            int4.register_packed(params[name], t["packed"], t["meta"], int(t["group"]))
+            self.quantized_tensors += 1
+            self.quantized_bytes += t["packed"].numel() * 4 + t["meta"].numel() * 4
+        self.method, self.bits, self.symmetric = "int4", 4, bool(blob.get("symmetric", False))
+        int4.set_enabled(True)
+        self.applied = True
+        if release_originals:
+            self.release_originals(model)
+        return len(blob["tensors"])
+
+    @torch.no_grad()
+    def release_originals(self, model) -> int:
+        """Frees the bf16 storage of every projection that has a 4-bit copy: the model then holds a quarter of the projection
+        bytes (head, embeddings, norms and routers stay).  From here on the model serves only through the 4-bit path: its
+        ``state_dict`` no longer holds those weights (use :meth:`save_quantized`), and it cannot be trained.  -> bytes freed."""
+        from ..ops import int4
+        freed = 0
+        for name, p in self._int4_targets(model):
+            if int4.lookup(p) is not None and p.stride() != (0, 0):
+                freed += int4.release_original(p)
+        self.released_bytes = getattr(self, "released_bytes", 0) + freed
+        return freed
+
     def available_backends(self) -> Dict[str, bool]:
         out = {"fp8 (native e4m3 GEMM)": torch.cuda.is_available(), "int8 / smoothquant (native s8 GEMM)": True,
                "int4 / gptq (native weight-only 4-bit)": True}

@@ -130,6 +130,51 @@ def test_symmetric_codes_and_block_by_block_gptq_cpu():
     assert 0.0 < errs["sequential"] < 0.25 and errs["sequential"] < 1.5 * errs["one_shot"], errs
 
 
+def test_saved_4bit_copies_serve_a_fresh_model_without_its_bf16_projections(tmp_path):
+    """save_quantized -> a fresh model of the same architecture (other projection values) -> load_quantized with the bf16
+    storage released: the same logits as the model that was quantised, and the projections hold no storage of their own."""
+    from adaptivetrainingsystem_b200.training.precision import QuantizationManager
+    cfg = ModelConfig(vocab_size=256, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=256, seq_length=32,
+                      tie_word_embeddings=False)
+    ids = torch.randint(0, 256, (2, 32))
+    path = str(tmp_path / "q4.pt")
+    try:
+        torch.manual_seed(0)
+        model = DeepSeekTransformer(cfg)
+        qm = QuantizationManager(SimpleNamespace(quantization_method="int4", quantization_bits=4))
+        with pytest.raises(RuntimeError):
+            qm.save_quantized(model, path)                       # nothing quantised yet
+        qm.quantize_model(model)
+        assert qm.save_quantized(model, path) == 8
+        with torch.no_grad():
+            ref = model(ids, return_aux_loss=False)
+        kept = {n: p.detach().clone() for n, p in model.named_parameters() if p.dim() != 2 or "lm_head" in n or "embed" in n}
+        int4.set_enabled(False)
+        int4.clear()
+        torch.manual_seed(1)
+        fresh = DeepSeekTransformer(cfg)                          # other projections; head, embeddings and norms copied over
+        with torch.no_grad():
+            for n, p in fresh.named_parameters():
+                if n in kept:
+                    p.copy_(kept[n])
+        qm2 = QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=None))
+        assert qm2.load_quantized(fresh, path, release_originals=True) == 8
+        assert qm2.status()["method"] == "int4" and qm2.released_bytes == sum(p.numel() * 4 for n, p in model.named_parameters()
+                                                                              if p.dim() == 2 and "lm_head" not in n and "embed" not in n)
+        proj = fresh.layers[0].ffn.down_proj
+        assert proj.shape == (128, 256) and proj.stride() == (0, 0) and proj.untyped_storage().nbytes() <= 8
+        with torch.no_grad():
+            out = fresh(ids, return_aux_loss=False)
+        assert torch.equal(out, ref)
+        assert qm2.release_originals(fresh) == 0                 # nothing left to free
+        with pytest.raises(RuntimeError):
+            torch.save({"format": "other"}, path)
+            qm2.load_quantized(fresh, path)
+    finally:
+        int4.set_enabled(False)
+        int4.clear()
+
+
 # ------------------------------------------------------------------------------------------------------------------------- GPU
 def _packed(N, K, group, dev, seed):
     g = torch.Generator().manual_seed(seed)
