@@ -120,7 +120,7 @@ class QuantizationManager:
         model.eval()
         if self.method in ("int4", "gptq"):
             int4.set_enabled(False)
-            int4.observe(True)
+            int4.observe(True, only=[p for _, p in self._int4_targets(model)])
             try:
                 for ids in batches:
                     model(ids, return_aux_loss=False)
