@@ -298,6 +298,30 @@ class QuantizationManager:
         self.applied = True
         return model
 
+    # -- names of the reference's manager (``training/trainer.py:681-801``) --------------------------------------------------------
+    @property
+    def is_quantized(self) -> bool:
+        return self.applied
+
+    def quantize_model_gptq(self, model, batches=None):
+        """GPTQ, 4 bits, groups of 128 (the reference's AutoGPTQ configuration: ``sym=True, true_sequential=True`` are
+        ``quantization_symmetric`` and the block-by-block pass taken when ``batches`` are given here)."""
+        self.method, self.bits = "gptq", 4
+        if batches is not None:
+            return self.quantize_sequential(model, batches)
+        return self.quantize_model(model)
+
+    def create_quantized_optimizer(self, model):
+        """The reference returns an optimiser only for bitsandbytes 8-bit modules; post-training quantisation here freezes the
+        model (no parameter requires a gradient), so there is nothing to optimise."""
+        return None
+
+    def get_quantization_info(self) -> Dict[str, Any]:
+        b = self.available_backends()
+        return {"is_quantized": self.applied, "method": self.method, "bits": self.bits,
+                "available_methods": {"bnb": b.get("bitsandbytes", False), "gptq": True, "quanto": b.get("optimum.quanto", False),
+                                      "fp8": b["fp8 (native e4m3 GEMM)"], "int8": True, "smoothquant": True, "int4": True}}
+
     def status(self) -> Dict[str, Any]:
         return {"method": self.method, "bits": self.bits, "applied": self.applied, "tensors": self.quantized_tensors,
                 "quantized_bytes": self.quantized_bytes, "gptq_weights": self.gptq_weights, "backends": self.available_backends()}

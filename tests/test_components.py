@@ -261,6 +261,9 @@ def test_quantization_manager_methods_and_refusals():
         QuantizationManager(SimpleNamespace(quantization_method="gptq", quantization_bits=4)).quantize_model(None)
     with pytest.raises(RuntimeError):
         QuantizationManager(SimpleNamespace(quantization_method="bnb", quantization_bits=4)).quantize_model(None)
+    info = qm.get_quantization_info()                       # the reference manager's names
+    assert info["is_quantized"] is False and info["method"] == "fp8" and info["available_methods"]["gptq"] and not qm.is_quantized
+    assert qm.create_quantized_optimizer(None) is None
 
 
 def test_swiglu_backward_gemm_reference_matches_autograd():
