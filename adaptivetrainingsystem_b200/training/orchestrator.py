@@ -456,6 +456,25 @@ class AdaptiveTrainingOrchestrator:
         return {"current": self.config.precision, "suggested": "mixed_bf16" if nonfinite and "fp8" in self.config.precision else self.config.precision,
                 "reason": f"{nonfinite} divergence events"}
 
+    def suggest_quantization_adjustment(self, serving_memory_gb: Optional[float] = None) -> Dict[str, Any]:
+        """Which post-training quantisation to serve the current model with: the bf16 weights against the memory of the serving
+        GPU (default: this GPU, or 180 GB without one).  fp8 halves the weight bytes of projections and experts; int4 quarters
+        the projections (dense models) and wants a GPTQ calibration pass."""
+        n = self.trainer.model.config.num_parameters() if self.trainer is not None else self.config.num_parameters()
+        if serving_memory_gb is None:
+            serving_memory_gb = torch.cuda.get_device_properties(0).total_memory / 2 ** 30 if torch.cuda.is_available() else 180.0
+        bf16_gb = 2.0 * n / 2 ** 30
+        frac = bf16_gb / serving_memory_gb
+        moe = bool(getattr(self.config, "use_moe", False))
+        if frac < 0.35:
+            pick, why = None, "the bf16 weights leave most of the memory to the KV cache"
+        elif frac < 0.7 or moe:
+            pick, why = "fp8", "e4m3 weights (experts included) halve the bytes a decode step streams"
+        else:
+            pick, why = "int4", "4-bit projections (GPTQ) are what fits next to a KV cache"
+        return {"current": getattr(self.config, "quantization_method", None), "suggested": pick, "bf16_weight_gb": round(bf16_gb, 2),
+                "fraction_of_memory": round(frac, 3), "reason": why}
+
     def enable_memory_optimizations(self) -> None:
         self.trainer.model.config.gradient_checkpointing = True
 

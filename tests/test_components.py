@@ -161,6 +161,10 @@ def test_orchestrator_decisions_drive_the_trainer(tmp_dir):
     batch = next(iter(tr._make_loader(S(512, 32, 4, seed=0), False)))
     tr.train_step(batch); tr.optimizer_step()
     assert tr.engine.get_lr() == pytest.approx(3.3e-6)
+    # documented helper: which post-training quantisation fits the serving memory
+    assert orch.suggest_quantization_adjustment(serving_memory_gb=180.0)["suggested"] is None
+    tight = orch.suggest_quantization_adjustment(serving_memory_gb=1e-4)
+    assert tight["suggested"] == "fp8" and tight["fraction_of_memory"] > 1      # a MoE model: the experts need the e4m3 path
     orch.cleanup()
 
 

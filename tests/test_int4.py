@@ -175,6 +175,46 @@ def test_saved_4bit_copies_serve_a_fresh_model_without_its_bf16_projections(tmp_
         int4.clear()
 
 
+def test_export_for_inference_writes_a_checkpoint_the_chat_loader_reads(tmp_path):
+    """The exported file goes through the chat entry point's loader into an identical model; the int4 export adds the packed
+    copies (GPTQ block by block with calibration batches) and leaves the exporting model unquantised and trainable."""
+    import importlib.util
+    import os
+    from adaptivetrainingsystem_b200.training.precision import QuantizationManager
+    from adaptivetrainingsystem_b200.utils import export_for_inference
+    spec = importlib.util.spec_from_file_location("chat_entry", os.path.join(os.path.dirname(os.path.dirname(__file__)), "Chat.py"))
+    chat = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(chat)
+    torch.manual_seed(0)
+    cfg = ModelConfig(vocab_size=256, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=256, seq_length=32,
+                      tie_word_embeddings=False)
+    model = DeepSeekTransformer(cfg)
+    ids = torch.randint(0, 256, (2, 32))
+    path = str(tmp_path / "serve.pt")
+    try:
+        info = export_for_inference(model, path, dtype=torch.float32, quantize="int4", calibration_batches=[ids])
+        assert info["quantized_tensors"] == 8 and info["gptq_tensors"] == 8 and info["quantized_bytes"] < info["checkpoint_bytes"] / 4
+        assert not int4.enabled() and all(p.requires_grad for p in model.parameters())
+        with torch.no_grad():
+            ref = model(ids, return_aux_loss=False)
+        sd, cfg2 = chat.load_checkpoint_smart(path)
+        served = DeepSeekTransformer(cfg2)
+        served.load_state_dict(sd, strict=False)
+        served.eval()
+        with torch.no_grad():
+            assert torch.equal(served(ids, return_aux_loss=False), ref)
+        qm = QuantizationManager(SimpleNamespace(quantization_method=None, quantization_bits=None))
+        assert qm.load_quantized(served, info["quantized"], release_originals=True) == 8
+        with torch.no_grad():
+            out = served(ids, return_aux_loss=False)
+        assert 0.0 < ((out - ref).norm() / ref.norm()).item() < 0.1
+        with pytest.raises(ValueError):
+            export_for_inference(model, path, quantize="fp8")
+    finally:
+        int4.set_enabled(False)
+        int4.clear()
+
+
 # ------------------------------------------------------------------------------------------------------------------------- GPU
 def _packed(N, K, group, dev, seed):
     g = torch.Generator().manual_seed(seed)
