@@ -346,6 +346,7 @@ class Config:
     quantization_method: Optional[str] = None
     quantization_bits: Optional[int] = None
     quantization_symmetric: bool = False      # 4-bit: zero point fixed at 8 (AutoGPTQ's sym=True)
+    quantization_act_order: bool = False      # 4-bit GPTQ: columns fixed in order of decreasing Hessian diagonal, groups static
     # -- memory -------------------------------------------------------------------
     max_memory_usage: float = 0.9
     memory_cleanup_interval: int = 1000

@@ -90,36 +90,53 @@ def quantize_rtn(w: torch.Tensor, group: int = GROUP, sym: bool = False) -> Tupl
     return q.view(N, K).to(torch.uint8), scale, zero
 
 
-def gptq_quantize(w: torch.Tensor, hessian: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool = False
-                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """GPTQ: ``hessian`` = sum over calibration rows of x^T x, [K, K].  Same outputs as :func:`quantize_rtn`."""
+def gptq_quantize(w: torch.Tensor, hessian: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool = False,
+                  act_order: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """GPTQ: ``hessian`` = sum over calibration rows of x^T x, [K, K].  Same outputs as :func:`quantize_rtn`.
+
+    ``act_order``: the columns are fixed in the order of decreasing Hessian diagonal (the input channels that matter most are
+    rounded first, while every other column can still absorb their error); the groups stay the runs of 128 consecutive ORIGINAL
+    channels with ranges taken up front (AutoGPTQ's ``desc_act`` with ``static_groups``), so the stored layout and the kernels do
+    not change."""
     N, K = w.shape
     W = w.detach().float().clone()
     H = hessian.detach().float().clone().to(W.device)
     dead = torch.diag(H) == 0
     H[dead, dead] = 1.0
     W[:, dead] = 0.0
+    scale = torch.empty(N, K // group, device=W.device)
+    zero = torch.empty(N, K // group, device=W.device)
+    perm = None
+    if act_order:
+        scale, zero = group_params(W.view(N, K // group, group), sym)
+        perm = torch.argsort(torch.diag(H), descending=True)
+        W = W[:, perm]
+        H = H[perm][:, perm]
+        col_group = (perm // group).tolist()
     H += torch.eye(K, device=W.device) * (damp * torch.diag(H).mean())
     # upper Cholesky factor of H^-1: row i holds how the error of column i spreads over the columns after it
     Hinv = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(H)), upper=True)
     Q = torch.empty(N, K, dtype=torch.uint8, device=W.device)
-    scale = torch.empty(N, K // group, device=W.device)
-    zero = torch.empty(N, K // group, device=W.device)
     for b, i1 in enumerate(range(0, K, group)):
         i2 = i1 + group
         W1 = W[:, i1:i2].clone()
         E1 = torch.empty_like(W1)
         H1 = Hinv[i1:i2, i1:i2]
-        sc, z = group_params(W1, sym)      # the group's range after the corrections pushed onto it by the groups before
-        scale[:, b], zero[:, b] = sc, z
+        if perm is None:
+            sc, z = group_params(W1, sym)  # the group's range after the corrections pushed onto it by the groups before
+            scale[:, b], zero[:, b] = sc, z
         for i in range(group):
             col = W1[:, i]
+            if perm is not None:
+                sc, z = scale[:, col_group[i1 + i]], zero[:, col_group[i1 + i]]
             q = (torch.round(col / sc) + z).clamp(0, 15)
             Q[:, i1 + i] = q.to(torch.uint8)
             err = (col - _bf16((q - z) * sc)) / H1[i, i]
             W1[:, i:] -= err[:, None] * H1[i, i:][None, :]
             E1[:, i] = err
         W[:, i2:] -= E1 @ Hinv[i1:i2, i2:]
+    if perm is not None:
+        Q = Q[:, torch.argsort(perm)]
     return Q, scale, zero
 
 
@@ -248,7 +265,8 @@ def hessian_for(w: torch.Tensor) -> Optional[torch.Tensor]:
 
 
 # -- registry ---------------------------------------------------------------------------------------------------------------------
-def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool = False) -> Tuple[torch.Tensor, torch.Tensor, bool]:
+def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool = False, act_order: bool = False
+             ) -> Tuple[torch.Tensor, torch.Tensor, bool]:
     """Quantises ``w`` [N, K] (GPTQ when calibration left a Hessian for it, else round-to-nearest) and routes ``ops.linear`` /
     the SwiGLU MLP with this weight to the 4-bit kernels.  -> (packed, meta, used_gptq)."""
     N, K = w.shape
@@ -259,7 +277,7 @@ def register(w: torch.Tensor, group: int = GROUP, damp: float = 0.01, sym: bool 
     if H is not None:
         for d in (damp, 10.0 * damp, 100.0 * damp):     # a Hessian of few calibration rows can defeat the fp32 factorisation
             try:
-                done = gptq_quantize(w, H, group, d, sym)
+                done = gptq_quantize(w, H, group, d, sym, act_order)
                 break
             except torch.linalg.LinAlgError:
                 continue

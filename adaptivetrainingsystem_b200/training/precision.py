@@ -105,6 +105,7 @@ class QuantizationManager:
             self.method = "int4"
         self.gptq_weights = 0
         self.symmetric = bool(getattr(config, "quantization_symmetric", False))   # AutoGPTQ's ``sym``: zero point fixed at 8
+        self.act_order = bool(getattr(config, "quantization_act_order", False))   # AutoGPTQ's ``desc_act`` with static groups
         self.applied = False
         self.calibrated = False
         self.quantized_tensors = 0
@@ -151,7 +152,7 @@ class QuantizationManager:
 
     def _register_int4(self, p) -> None:
         from ..ops import int4
-        packed, meta, used_gptq = int4.register(p, sym=self.symmetric)
+        packed, meta, used_gptq = int4.register(p, sym=self.symmetric, act_order=self.act_order)
         self.quantized_tensors += 1
         self.gptq_weights += int(used_gptq)
         self.quantized_bytes += packed.numel() * 4 + meta.numel() * 4

@@ -55,6 +55,25 @@ def test_gptq_beats_round_to_nearest_on_correlated_inputs():
     assert e_gptq < 0.5 * e_rtn, (e_gptq, e_rtn)
 
 
+def test_gptq_act_order_helps_when_input_channels_differ_in_scale():
+    """Channels of very different magnitude: fixing the heavy ones first (static groups, stored layout unchanged) lowers the
+    output error again; the codes still unpack to [N, K] with groups of consecutive channels."""
+    torch.manual_seed(2)
+    N, K = 64, 512
+    w = torch.randn(N, K) * 0.05
+    x = (torch.randn(1024, 16) @ torch.randn(16, K) + 0.3 * torch.randn(1024, K)) * torch.exp(torch.randn(K) * 1.5)
+    H = x.t() @ x
+
+    def err(q, s, z):
+        assert q.shape == (N, K) and s.shape == (N, K // 128) and int(q.max()) <= 15
+        wd = int4.dequantize_reference(int4.pack(q), int4.pack_meta(s, z), 128).float()
+        return ((x @ (w - wd).t()) ** 2).sum().item()
+
+    e_plain = err(*int4.gptq_quantize(w, H, 128))
+    e_act = err(*int4.gptq_quantize(w, H, 128, act_order=True))
+    assert e_act < 0.6 * e_plain, (e_act, e_plain)
+
+
 def test_manager_quantises_projections_to_4_bits_cpu():
     """Through the manager on CPU (PyTorch definitions): GPTQ refuses to run uncalibrated; after calibration every projection
     gets a Hessian (the down projection's through the two-step MLP), the head stays in bf16, and the logits stay close."""
