@@ -215,6 +215,8 @@ def gemv(x2: torch.Tensor, packed: torch.Tensor, meta: torch.Tensor, group: int 
     if K != packed.shape[0] * 64 or meta.shape != (K // group, N) or M > GEMV_MAX_ROWS or not packed.is_contiguous() or not meta.is_contiguous():
         raise ValueError(f"gemv: activations {tuple(x2.shape)} do not fit the packed weight {N} x {packed.shape[0] * 64} (group {group})")
     n_out = N // 2 if swiglu else N
+    if M == 0:
+        return torch.empty(0, n_out, dtype=torch.bfloat16, device=x2.device)
     if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
         x2 = x2.contiguous()
     if add is not None and (add.stride(1) != 1 or tuple(add.shape) != (M, n_out)):
