@@ -62,8 +62,8 @@ class ChatInterface:
         self.model.load_state_dict({k: v for k, v in sd.items()}, strict=False)
         self.model = self.model.to(self.device, dtype).eval()
         if quantize:
-            if self.device.type != "cuda":
-                raise SystemExit("--quantize needs a GPU: the fp8 path runs on the tensor-core GEMM")
+            if self.device.type != "cuda" and quantize != "int4":
+                raise SystemExit("--quantize fp8 / int8 needs a GPU: those paths run on the tensor-core GEMM")
             from types import SimpleNamespace
             from adaptivetrainingsystem_b200.training import QuantizationManager
             qm = QuantizationManager(SimpleNamespace(quantization_method=quantize, quantization_bits=4 if quantize == "int4" else 8))

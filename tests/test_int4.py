@@ -234,6 +234,36 @@ def test_export_for_inference_writes_a_checkpoint_the_chat_loader_reads(tmp_path
         int4.clear()
 
 
+def test_chat_serves_saved_4bit_copies_cpu(tmp_path):
+    """The chat entry point with ``--quantize int4 --quantized-file``: the first start writes the packed copies, the second one
+    attaches them, frees the projections and answers with the same tokens (greedy)."""
+    import importlib.util
+    import os
+    from adaptivetrainingsystem_b200.utils import export_for_inference
+    spec = importlib.util.spec_from_file_location("chat_entry2", os.path.join(os.path.dirname(os.path.dirname(__file__)), "Chat.py"))
+    chat = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(chat)
+    torch.manual_seed(0)
+    cfg = ModelConfig(vocab_size=512, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=256, seq_length=128,
+                      tie_word_embeddings=False)
+    ckpt, qfile = str(tmp_path / "m.pt"), str(tmp_path / "m.int4")
+    export_for_inference(DeepSeekTransformer(cfg), ckpt, dtype=torch.float32)
+    answers = []
+    try:
+        for start in range(2):
+            c = chat.ChatInterface(ckpt, device="cpu", mode="greedy", quantize="int4", quantized_file=qfile)
+            c.params.max_new_tokens = 6
+            answers.append(c.engine.generate(c._format_prompt("hello there"), c.params)["tokens"][0].tolist())
+            assert os.path.exists(qfile)
+            assert (c.model.layers[0].ffn.down_proj.stride() == (0, 0)) == (start == 1)
+            int4.set_enabled(False)
+            int4.clear()
+        assert answers[0] == answers[1] and len(answers[0]) == 6
+    finally:
+        int4.set_enabled(False)
+        int4.clear()
+
+
 # ------------------------------------------------------------------------------------------------------------------------- GPU
 def _packed(N, K, group, dev, seed):
     g = torch.Generator().manual_seed(seed)
