@@ -176,6 +176,9 @@ class CheckpointManager:
         self.history_file = os.path.join(directory, "checkpoint_history.json")
         self.history: List[Dict[str, Any]] = []
         self.best_metric = float("inf")
+        # further metadata of the owner, merged into every checkpoint (the trainer adds ``precision_info`` and
+        # ``quantization_info``, the keys of the reference's live format, ``training/trainer.py:3395-3422``)
+        self.extra_meta = None
         if os.path.exists(self.history_file):
             try:
                 with open(self.history_file) as f:
@@ -221,7 +224,9 @@ class CheckpointManager:
         return n * (dist.get_world_size() if getattr(model, "ep_size", 1) > 1 else 1) > 2_000_000_000
 
     def _meta(self, model, scheduler, global_step, epoch, metrics) -> Dict[str, Any]:
+        extra = self.extra_meta() if callable(self.extra_meta) else {}
         return {
+            **extra,
             "scheduler_state_dict": scheduler.state_dict() if scheduler is not None else None,
             "global_step": global_step, "epoch": epoch, "current_epoch": epoch,
             "metrics": {k: list(v)[-1000:] for k, v in (metrics or {}).items()},

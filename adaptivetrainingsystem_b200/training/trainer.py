@@ -147,6 +147,8 @@ class EnhancedConversationTrainer:
         self.checkpoint_history: List[Dict[str, Any]] = []
         exp_dir = os.path.join(getattr(self.config, "output_dir", "experiments"), self.config.experiment_name or "run")
         self.checkpoint_manager = CheckpointManager(self.config, os.path.join(exp_dir, "checkpoints"))
+        self.checkpoint_manager.extra_meta = lambda: {"precision_info": self.precision_manager.get_precision_info(),
+                                                      "quantization_info": self.quantization_manager.get_quantization_info()}
         self.chinchilla_scaler = None
         self.train_dataset = None
         self.eval_dataset = None

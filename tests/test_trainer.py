@@ -113,7 +113,8 @@ def test_train_checkpoint_resume_and_rollback(tmp_dir):
     assert "checkpoint_final.pt" in files and "checkpoint_history.json" in files
     ck = torch.load(os.path.join(tr.checkpoint_manager.directory, "checkpoint_final.pt"), weights_only=False)
     assert {"model_state_dict", "optimizer_state_dict", "scheduler_state_dict", "global_step", "epoch", "config", "model_config",
-            "rng_state"} <= set(ck)
+            "rng_state", "precision_info", "quantization_info"} <= set(ck)
+    assert ck["quantization_info"]["is_quantized"] is False and ck["precision_info"]["name"] == cfg.precision
     assert "layers.0.self_attn.q_proj.weight" in ck["model_state_dict"]
     # resume into a fresh trainer: same parameters and optimiser state
     tr2, _ = make(tmp_dir, num_epochs=2)
