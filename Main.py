@@ -109,8 +109,15 @@ def main(argv=None) -> int:
         logger.info("model %.2f B parameters (%.2f B active); planned epochs %d; estimated %.2f h at %.0f tok/s",
                     cfg.num_parameters() / 1e9, cfg.num_parameters(True) / 1e9, cfg.num_epochs, est["hours"], est["tokens_per_second"])
         save_experiment_metadata(cfg, os.path.join(cfg.output_dir, cfg.experiment_name), get_system_info())
-    if args.resume:
-        info = trainer.load_checkpoint(args.resume)
+    resume = args.resume
+    if not resume and getattr(cfg, "auto_resume", False):
+        # ``auto_resume``: an experiment directory that already holds checkpoints (same experiment name) continues from its latest
+        ck_dir = trainer.checkpoint_manager.directory
+        if os.path.isdir(ck_dir) and any(f.startswith("checkpoint_") and (f.endswith(".pt") or os.path.isdir(os.path.join(ck_dir, f)))
+                                         for f in os.listdir(ck_dir)):
+            resume = "latest"
+    if resume:
+        info = trainer.load_checkpoint(resume)
         logger.info("resumed from %s at step %d", info["path"], info["global_step"])
 
     if args.no_orchestrator:

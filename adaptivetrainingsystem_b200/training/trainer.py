@@ -147,6 +147,7 @@ class EnhancedConversationTrainer:
         self.checkpoint_history: List[Dict[str, Any]] = []
         exp_dir = os.path.join(getattr(self.config, "output_dir", "experiments"), self.config.experiment_name or "run")
         self.checkpoint_manager = CheckpointManager(self.config, os.path.join(exp_dir, "checkpoints"))
+        self._last_backup = time.time()
         self.checkpoint_manager.extra_meta = lambda: {"precision_info": self.precision_manager.get_precision_info(),
                                                       "quantization_info": self.quantization_manager.get_quantization_info()}
         self.chinchilla_scaler = None
@@ -408,6 +409,7 @@ class EnhancedConversationTrainer:
             every = getattr(self.config, "save_every_n_batches", 0)
             if every and self.global_step % every == 0:
                 self.save_checkpoint(epoch, tag=f"step_{self.global_step}")
+            self._maybe_backup(epoch)
         m = self._flush_metrics()
         if m:
             sum_loss += m["loss"]
@@ -467,9 +469,29 @@ class EnhancedConversationTrainer:
         summary["best_eval_loss"] = self.best_eval_loss
         return summary
 
-    def train_with_oom_fallback(self, train_dataset, eval_dataset=None, max_attempts: int = 10) -> Dict[str, Any]:
+    def _maybe_backup(self, epoch: int) -> None:
+        """``backup_every_n_hours``: a rolling ``checkpoint_backup.pt`` on a wall-clock period, independent of the step- and
+        epoch-based saves (the reference reads the flag only in a loop it never imports, ``training_loop.py``).  The clock is
+        rank 0's, broadcast when several ranks train, so that every rank enters the collective save together."""
+        hours = float(getattr(self.config, "backup_every_n_hours", 0) or 0)
+        if hours <= 0:
+            return
+        import torch.distributed as dist
+        due = time.time() - self._last_backup >= hours * 3600.0
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            flag = torch.tensor([int(due)], device=self.device if self.device.type == "cuda" else "cpu")
+            dist.broadcast(flag, 0)
+            due = bool(flag.item())
+        if due:
+            self._last_backup = time.time()
+            self.save_checkpoint(epoch, tag="backup")
+
+    def train_with_oom_fallback(self, train_dataset, eval_dataset=None, max_attempts: Optional[int] = None) -> Dict[str, Any]:
         """Retry with half the micro-batch and twice the accumulation after an out-of-memory error
-        (reference ``trainer.py:1836-1955``); the working pair is written to ``optimal_batch_config.json``."""
+        (reference ``trainer.py:1836-1955``); the working pair is written to ``optimal_batch_config.json``.  ``max_attempts``
+        defaults to the configuration's ``max_retries`` (10 when that is unset)."""
+        if max_attempts is None:
+            max_attempts = int(getattr(self.config, "max_retries", 10) or 10)
         attempts = 0
         while True:
             try:

@@ -1,6 +1,7 @@
 """Trainer API on CPU: loss dictionary, steps, interventions, checkpoints, rollback, OOM recovery."""
 import math
 import os
+import time
 
 import pytest
 import torch
@@ -125,6 +126,27 @@ def test_train_checkpoint_resume_and_rollback(tmp_dir):
     assert torch.allclose(tr.engine.buckets[0].exp_avg, tr2.engine.buckets[0].exp_avg)
     # rollback goes to the checkpoint nearest to step - n
     assert tr.rollback_steps(4) and tr.global_step == 4 and len(tr.metrics["train_losses"]) == 4
+
+
+def test_wall_clock_backup_and_retry_cap_from_config(tmp_dir):
+    """``backup_every_n_hours``: a rolling backup checkpoint once the period has passed; ``max_retries`` caps the OOM retries."""
+    tr, cfg = make(tmp_dir, num_epochs=1)
+    cfg.backup_every_n_hours = 1
+    tr._last_backup -= 2 * 3600.0                       # as if two hours had passed
+    ds = SyntheticTokenDataset(512, 32, 8, seed=1)
+    tr.train(ds)
+    files = os.listdir(tr.checkpoint_manager.directory)
+    assert "checkpoint_backup.pt" in files and time.time() - tr._last_backup < 60
+    cfg.max_retries = 2
+    calls = []
+
+    def boom(*a, **k):
+        calls.append(1)
+        raise RuntimeError("CUDA out of memory (synthetic)")
+    tr.train = boom
+    with pytest.raises(RuntimeError):
+        tr.train_with_oom_fallback(ds)
+    assert len(calls) == 3                              # the first attempt and max_retries retries
 
 
 def test_checkpoint_manager_errors_and_retention(tmp_dir):
