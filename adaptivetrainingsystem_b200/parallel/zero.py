@@ -20,6 +20,7 @@ before its forward and backward (``ZeRO3Hooks``).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple
 
@@ -136,6 +137,7 @@ class ShardedEngine:
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._scratch = torch.zeros(1024, dtype=torch.float32, device=self.device) if self.device.type == "cuda" else None
         self.step_count = 0
+        self.comm_timer = None      # a ``utils.profiler.PhaseTimer`` when the collectives of the step are to be timed
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.buckets: List[Bucket] = []
         self._build_buckets()
@@ -199,32 +201,37 @@ class ShardedEngine:
             for p in b.params:
                 p.grad = None
 
+    def _comm(self, name: str):
+        return self.comm_timer.phase(name) if self.comm_timer is not None else contextlib.nullcontext()
+
     def _reduce(self, b: Bucket) -> torch.Tensor:
         """Returns the (summed over the group) gradient slice this rank updates."""
         lo, hi = b.owned_range()
         if b.W == 1 or b.group is None and not dist.is_initialized():
             return b.flat_grad[lo:hi]
-        if b.shard_states:
-            out = b.flat_grad[lo:hi]
-            if dist.get_backend(b.group) == "gloo":
-                dist.all_reduce(b.flat_grad, group=b.group)
-            else:
-                dist.reduce_scatter_tensor(out, b.flat_grad, group=b.group)
-            return out
-        dist.all_reduce(b.flat_grad, group=b.group)
-        return b.flat_grad
+        with self._comm("grad_reduce"):
+            if b.shard_states:
+                out = b.flat_grad[lo:hi]
+                if dist.get_backend(b.group) == "gloo":
+                    dist.all_reduce(b.flat_grad, group=b.group)
+                else:
+                    dist.reduce_scatter_tensor(out, b.flat_grad, group=b.group)
+                return out
+            dist.all_reduce(b.flat_grad, group=b.group)
+            return b.flat_grad
 
     def _gather(self, b: Bucket) -> None:
         if b.W == 1 or not b.shard_states or not dist.is_initialized():
             return
         lo, hi = b.owned_range()
-        if dist.get_backend(b.group) == "gloo":
-            parts = [torch.empty_like(b.flat_param[lo:hi]) for _ in range(b.W)]
-            dist.all_gather(parts, b.flat_param[lo:hi].clone(), group=b.group)
-            for i, t in enumerate(parts):
-                b.flat_param[i * b.shard:(i + 1) * b.shard].copy_(t)
-        else:
-            dist.all_gather_into_tensor(b.flat_param, b.flat_param[lo:hi], group=b.group)
+        with self._comm("param_gather"):
+            if dist.get_backend(b.group) == "gloo":
+                parts = [torch.empty_like(b.flat_param[lo:hi]) for _ in range(b.W)]
+                dist.all_gather(parts, b.flat_param[lo:hi].clone(), group=b.group)
+                for i, t in enumerate(parts):
+                    b.flat_param[i * b.shard:(i + 1) * b.shard].copy_(t)
+            else:
+                dist.all_gather_into_tensor(b.flat_param, b.flat_param[lo:hi], group=b.group)
 
     def step(self) -> Dict[str, Any]:
         """Reduce gradients, clip by global norm, AdamW on the owned shards, re-assemble parameters.

@@ -27,6 +27,7 @@ import logging
 import math
 import os
 import threading
+import contextlib
 import time
 from collections import deque
 from contextlib import nullcontext
@@ -148,6 +149,12 @@ class EnhancedConversationTrainer:
         exp_dir = os.path.join(getattr(self.config, "output_dir", "experiments"), self.config.experiment_name or "run")
         self.checkpoint_manager = CheckpointManager(self.config, os.path.join(exp_dir, "checkpoints"))
         self._last_backup = time.time()
+        # profiling flags of the configuration (declared by the reference, consumed by none of its live code)
+        from ..utils.profiler import PhaseTimer
+        self.phase_timer = PhaseTimer(self.device) if getattr(self.config, "enable_profiling", False) else None
+        if getattr(self.config, "profile_communication", False) and hasattr(self.engine, "comm_timer"):
+            self.engine.comm_timer = PhaseTimer(self.device)
+        self.peak_memory_gb: List[float] = []
         self.checkpoint_manager.extra_meta = lambda: {"precision_info": self.precision_manager.get_precision_info(),
                                                       "quantization_info": self.quantization_manager.get_quantization_info()}
         self.chinchilla_scaler = None
@@ -218,7 +225,8 @@ class EnhancedConversationTrainer:
         if self.heartbeat is not None:
             self.heartbeat.check()  # a lost peer surfaces here, on the host, before any kernel waits for it
         self.model.train()
-        batch = self._to_device(batch)
+        with self._phase("to_device"):
+            batch = self._to_device(batch)
         if self.mesh.sp_size > 1:
             from ..parallel.strategy import shard_sequence
             batch = shard_sequence(batch, self.mesh)  # this rank's L / W tokens of every sequence
@@ -230,9 +238,10 @@ class EnhancedConversationTrainer:
         mask = batch.get("attention_mask")
         if mask is not None and bool(getattr(self.config, "assume_full_attention_mask", True)):
             mask = None  # packed / synthetic batches are dense; padding is handled by the label mask
-        with self.precision_manager.autocast():
+        with self._phase("forward"), self.precision_manager.autocast():
             out = self.model.forward_loss(batch["input_ids"], labels, batch.get("loss_weights"), mask, self.ignore_index)
-        out["loss"].backward()
+        with self._phase("backward"):
+            out["loss"].backward()
         self.micro_step += 1
         res = self._loss_dict(out["loss"].detach(), out["raw_loss"], out["valid_tokens"], out["accuracy"])
         res["aux_loss"] = out["aux_loss"]
@@ -275,11 +284,29 @@ class EnhancedConversationTrainer:
         tokens = sum(m["input_ids"].numel() for m in mbs)
         self._pending_device.append({"loss": t[0], "raw_loss": t[0], "accuracy": torch.zeros((), device=self.device), "tokens": tokens})
 
+    def _phase(self, name: str):
+        return self.phase_timer.phase(name) if self.phase_timer is not None else contextlib.nullcontext()
+
+    def profiling_summary(self) -> Dict[str, Any]:
+        """What the profiling flags collected: ``enable_profiling`` -> mean device (CUDA events) or host milliseconds per
+        phase of a micro-step; ``profile_communication`` -> the same for the engine's collectives (the fused peer-memory step
+        has no separate collectives to time); ``profile_memory`` -> peak allocated GB per epoch."""
+        out: Dict[str, Any] = {}
+        if self.phase_timer is not None:
+            out["phase_ms"] = self.phase_timer.summary()
+        timer = getattr(self.engine, "comm_timer", None)
+        if timer is not None:
+            out["communication_ms"] = timer.summary()
+        if getattr(self.config, "profile_memory", False):
+            out["peak_memory_gb_per_epoch"] = list(self.peak_memory_gb)
+        return out
+
     def optimizer_step(self) -> Dict[str, Any]:
         if self.pipeline is not None:
             self._pipeline_run()
         with self._lock:
-            stats = self.engine.step()
+            with self._phase("optimizer"):
+                stats = self.engine.step()
             self.global_step += 1
             self._advance_scheduler(stats)
             pending, self._pending = self._pending, []
@@ -423,9 +450,10 @@ class EnhancedConversationTrainer:
         if get_rank() != 0:
             return
         mem = torch.cuda.max_memory_allocated() / 2 ** 30 if self.device.type == "cuda" else 0.0
-        self.logger.info("epoch %d step %d | loss %.4f ppl %.2f acc %.3f | lr %.3e | gnorm %.3f | %.0f tok/s | %s | %.1f GB",
+        rate = "%.0f tok/s | " % m["tokens_per_second"] if getattr(self.config, "log_throughput", True) else ""
+        self.logger.info("epoch %d step %d | loss %.4f ppl %.2f acc %.3f | lr %.3e | gnorm %.3f | %s%s | %.1f GB",
                          epoch, self.global_step, m["loss"], m["perplexity"], m["accuracy"], m["lr"], m["grad_norm"],
-                         m["tokens_per_second"], self.config.precision, mem)
+                         rate, self.config.precision, mem)
 
     def train(self, train_dataset, eval_dataset=None) -> Dict[str, Any]:
         self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
@@ -453,6 +481,13 @@ class EnhancedConversationTrainer:
                     pat = self.config.early_stopping_patience
                     if pat and self.patience_counter >= pat:
                         self.should_stop = True
+                if getattr(self.config, "profile_memory", False):
+                    if self.device.type == "cuda":
+                        self.peak_memory_gb.append(torch.cuda.max_memory_allocated(self.device) / 2 ** 30)
+                        torch.cuda.reset_peak_memory_stats(self.device)
+                    else:
+                        import resource
+                        self.peak_memory_gb.append(resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 2 ** 20)
                 path = self.save_checkpoint(epoch)
                 self.checkpoint_history.append({"epoch": epoch, "global_step": self.global_step, "path": path})
                 self.checkpoint_history = self.checkpoint_history[-10:]
@@ -462,6 +497,11 @@ class EnhancedConversationTrainer:
                 loader = self._make_loader(train_dataset, shuffle=True)
         finally:
             try:
+                prof = self.profiling_summary()
+                if prof:
+                    summary["profiling"] = prof
+                    if get_rank() == 0:
+                        self.logger.info("profiling: %s", prof)
                 summary["final_checkpoint"] = self.save_checkpoint(self.current_epoch, tag="final")
             except Exception as e:  # never mask the original error
                 self.logger.warning("final checkpoint failed: %s", e)

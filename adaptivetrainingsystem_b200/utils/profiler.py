@@ -30,12 +30,16 @@ class PhaseTimer:
                 b.record()
                 torch.cuda.nvtx.range_pop()
                 self._events[name].append((a, b))
+                if len(self._events[name]) > 4096:      # a long run keeps the most recent intervals only
+                    del self._events[name][:2048]
         else:
             t = time.perf_counter()
             try:
                 yield
             finally:
                 self._host[name].append((time.perf_counter() - t) * 1e3)
+                if len(self._host[name]) > 4096:
+                    del self._host[name][:2048]
 
     def summary(self) -> Dict[str, float]:
         out: Dict[str, float] = {}

@@ -149,6 +149,18 @@ def test_wall_clock_backup_and_retry_cap_from_config(tmp_dir):
     assert len(calls) == 3                              # the first attempt and max_retries retries
 
 
+def test_profiling_flags_collect_phases_memory_and_collectives(tmp_dir):
+    """``enable_profiling`` / ``profile_memory`` / ``profile_communication`` / ``log_throughput`` each change what a run reports."""
+    tr, cfg = make(tmp_dir, num_epochs=1, enable_profiling=True, profile_memory=True, profile_communication=True, log_throughput=False)
+    summary = tr.train(SyntheticTokenDataset(512, 32, 8, seed=1))
+    prof = summary["profiling"]
+    assert {"to_device_ms", "forward_ms", "backward_ms", "optimizer_ms"} <= set(prof["phase_ms"]) and prof["phase_ms"]["forward_ms"] > 0
+    assert len(prof["peak_memory_gb_per_epoch"]) == 1 and prof["peak_memory_gb_per_epoch"][0] > 0
+    assert prof["communication_ms"] == {}                 # one rank: no collective ran
+    tr2, _ = make(tmp_dir, num_epochs=1)
+    assert tr2.phase_timer is None and tr2.engine.comm_timer is None and tr2.profiling_summary() == {}
+
+
 def test_checkpoint_manager_errors_and_retention(tmp_dir):
     tr, cfg = make(tmp_dir)
     cm = CheckpointManager(cfg, os.path.join(tmp_dir, "ck"))
