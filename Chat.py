@@ -75,7 +75,7 @@ class ChatInterface:
                 if quantize == "int4" and quantized_file:
                     qm.save_quantized(self.model, quantized_file)
         self.tokenizer = ConversationTokenizer()
-        self.engine = GenerationEngine(self.model, self.tokenizer)
+        self.engine = GenerationEngine(self.model, self.tokenizer, use_kv_cache=bool(getattr(cfg, "use_kv_cache", True)))
         self.params = SamplingParams.from_mode(mode, max_new_tokens=min(256, max(cfg.seq_length // 2, 1)),
                                                stop_token_ids=(self.tokenizer.special_tokens["<|im_end|>"], self.tokenizer.eos_token_id))
         self.history = []

@@ -116,8 +116,15 @@ class KVSlotManager:
 
 class GenerationEngine:
     def __init__(self, model: DeepSeekTransformer, tokenizer=None, max_batch: int = 64, max_len: Optional[int] = None,
-                 pack_experts: bool = False):
+                 pack_experts: bool = False, use_kv_cache: bool = True, kv_cache_dtype: str = "auto"):
+        """``use_kv_cache=False`` is the reference's generation loop (``Chat.py:379-452``: the whole sequence is run again for
+        every token), kept for comparison; ``kv_cache_dtype``: ``"auto"`` / the model's dtype (an 8-bit cache is not built)."""
         self.model = model.eval()
+        self.use_kv_cache = bool(use_kv_cache)
+        own = {torch.bfloat16: ("bf16", "bfloat16"), torch.float32: ("fp32", "float32"), torch.float16: ("fp16", "float16")}
+        dt = next(model.parameters()).dtype
+        if kv_cache_dtype not in ("auto", None) and kv_cache_dtype not in own.get(dt, ()) and not (kv_cache_dtype == "bf16" and dt == torch.float32):
+            raise ValueError(f"kv_cache_dtype {kv_cache_dtype!r}: the cache holds the model's dtype ({dt}); an 8-bit cache is not built")
         self.tokenizer = tokenizer
         self.max_batch = max_batch
         self.max_len = max_len or model.config.seq_length
@@ -175,6 +182,8 @@ class GenerationEngine:
         params = params or SamplingParams()
         dev = input_ids.device
         B, Lp = input_ids.shape
+        if not self.use_kv_cache:
+            return self._generate_without_cache(input_ids, params, on_token)
         total = Lp + params.max_new_tokens
         cache = self.model.make_cache(B, total)
         gen = None
@@ -213,6 +222,34 @@ class GenerationEngine:
         t2 = time.perf_counter()
         self.stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1, "prefill_tokens_per_s": B * Lp / max(t1 - t0, 1e-9),
                       "decode_tokens_per_s": B * max(steps - 1, 1) / max(t2 - t1, 1e-9), "steps": steps}
+        return {"tokens": torch.stack(out, dim=1), **self.stats}
+
+    @torch.no_grad()
+    def _generate_without_cache(self, input_ids: torch.Tensor, params: SamplingParams, on_token=None) -> Dict[str, object]:
+        """Every step runs the whole sequence again (quadratic in the length): the reference's loop, for comparison only."""
+        dev = input_ids.device
+        gen = torch.Generator(device=dev).manual_seed(params.seed) if params.seed is not None else None
+        sync = torch.cuda.synchronize if dev.type == "cuda" else (lambda: None)
+        stop = torch.tensor(list(params.stop_token_ids), device=dev, dtype=torch.long) if params.stop_token_ids else None
+        finished = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=dev)
+        history, out = input_ids, []
+        sync()
+        t0 = time.perf_counter()
+        for step in range(params.max_new_tokens):
+            logits = self.model(history, last_token_only=True, return_aux_loss=False)[:, -1, :]
+            nxt = sample_next(logits, params, history, gen)
+            out.append(nxt)
+            if on_token is not None:
+                on_token(step, nxt)
+            if stop is not None:
+                finished |= (nxt[:, None] == stop[None, :]).any(-1)
+                if bool(finished.all()):
+                    break
+            history = torch.cat([history, nxt[:, None]], dim=1)
+        sync()
+        dt = time.perf_counter() - t0
+        self.stats = {"prefill_s": 0.0, "decode_s": dt, "prefill_tokens_per_s": 0.0,
+                      "decode_tokens_per_s": input_ids.shape[0] * len(out) / max(dt, 1e-9), "steps": len(out), "kv_cache": False}
         return {"tokens": torch.stack(out, dim=1), **self.stats}
 
     # ---------------------------------------------------------------------------------------------------------------

@@ -235,3 +235,21 @@ def test_router_z_loss_adds_to_the_auxiliary_loss_and_trains_the_gate():
     assert float(a0) == 0.0 and abs(float(out["aux_loss"]) - float(want)) < 1e-4 * max(1.0, float(want))
     out["loss"].backward()
     assert layer.gate.weight.grad is not None and float(layer.gate.weight.grad.abs().sum()) > 0
+
+
+def test_generation_without_kv_cache_matches_cached_generation():
+    """``use_kv_cache=False`` (the reference's loop: the whole sequence again for every token) gives the tokens of the cached
+    engine; a cache dtype the engine does not hold is refused."""
+    import pytest
+    from adaptivetrainingsystem_b200.inference import GenerationEngine, SamplingParams
+    torch.manual_seed(0)
+    cfg = ModelConfig(vocab_size=128, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=128, seq_length=64)
+    model = DeepSeekTransformer(cfg).eval()
+    ids = torch.randint(0, 128, (2, 9))
+    params = SamplingParams.from_mode("greedy", max_new_tokens=7)
+    cached = GenerationEngine(model).generate(ids, params)
+    plain = GenerationEngine(model, use_kv_cache=False).generate(ids, params)
+    assert torch.equal(cached["tokens"], plain["tokens"]) and plain["kv_cache"] is False and plain["steps"] == 7
+    with pytest.raises(ValueError):
+        GenerationEngine(model, kv_cache_dtype="fp8")
+    GenerationEngine(model, kv_cache_dtype="fp32")
