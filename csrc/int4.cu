@@ -41,7 +41,8 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
 // (128 + q) pairs -> (q - zero) * scale, in bf16 pairs.  The integer ALU issues a warp instruction every other cycle and is the
 // pipe this kernel fills first (measured: 60 % busy with the plain C++ form, 15 of its instructions per packed word), so the
 // extraction is pinned to one logic operation per pair, (w' & mask) | magic with both constants in registers, and the three
-// shifts of a word are done as multiply-high by a power of two on the FMA pipe, which has room.
+// shifts of a word are done as multiply-high by a power of two on the FMA pipe, which has room (no measurable change by
+// itself: the kernel was waiting for memory then, see the copy ring below).
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t d;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -98,7 +99,7 @@ __host__ __device__ constexpr int int4_ring_bytes(int R, int NT, int DEPTH) { re
 // every warp keeps the copies of DEPTH of its super-steps in flight (a ring in shared memory), so that a CTA's few microseconds
 // are spent streaming and not waiting for one round trip to memory per step.  One tile per CTA and MINB resident CTAs per SM keep
 // the grid fine-grained: with two tiles and 72 registers the 28,672-feature projection ran as 2.02 waves of CTAs, i.e. three.
-// NT: token tiles of eight rows (the dequantised fragments of a step feed NT MMAs).
+// NT: token tiles of eight rows (the code fragments of a step feed NT MMAs).
 template <int R, bool SWIGLU, int NT, int DEPTH, int MINB>
 __global__ void __launch_bounds__(GEMV_WARPS * 32, MINB)
 gemv_int4_kernel(const uint4* __restrict__ wq, const uint32_t* __restrict__ meta, const __nv_bfloat16* __restrict__ x, long long ldx,
