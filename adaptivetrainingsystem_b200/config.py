@@ -42,7 +42,7 @@ PRECISIONS = (
     "fp8", "fp8_e4m3", "fp8_e5m2", "mixed_fp8", "int8", "int4",
 )
 MOE_PATTERNS = ("all", "every_2nd", "every_3rd", "every_4th", "sandwich", "none", "odd")
-SCHEDULERS = ("cosine", "onecycle", "constant", "linear", "warmup_decay")
+SCHEDULERS = ("cosine", "onecycle", "constant", "linear", "warmup_decay", "multistep", "poly", "flat_anneal")
 
 
 def _round_up(x: int, m: int) -> int:
@@ -315,6 +315,10 @@ class Config:
     early_stopping_patience: Optional[int] = None
     min_lr: float = 1e-6
     lr_scheduler: str = "cosine"
+    lr_milestones: Optional[List[float]] = None   # multistep: fractions of the run (or absolute steps when > 1); default 0.5, 0.75
+    lr_gamma: float = 0.1                           # multistep: factor at every milestone
+    lr_power: float = 1.0                           # poly: exponent of the decay
+    lr_flat_fraction: float = 0.72                  # flat_anneal: share of the run at the base rate before the cosine tail
     use_lr_scheduler: bool = True
     # -- monitoring / fault tolerance -----------------------------------------
     health_check_interval: int = 100

@@ -110,6 +110,18 @@ def test_lr_schedules():
     s = LRSchedule("cosine", 1e-3, 100)
     s.scale_base(0.1)
     assert s.lr_at(0) == pytest.approx(1e-4)
+    # the vendored scheduler package's shapes: steps at milestones, polynomial decay, flat then cosine
+    ms = LRSchedule("multistep", 1e-3, 100, milestones=[0.5, 0.75], gamma=0.1)
+    assert [ms.lr_at(t) for t in (0, 49, 50, 74, 75, 99)] == pytest.approx([1e-3, 1e-3, 1e-4, 1e-4, 1e-5, 1e-5])
+    assert LRSchedule("multistep", 1e-3, 100, milestones=[30, 60]).lr_at(45) == pytest.approx(1e-4)      # absolute steps
+    po = LRSchedule("poly", 1e-3, 100, min_lr=1e-5, power=2.0)
+    assert po.lr_at(0) == pytest.approx(1e-3) and po.lr_at(50) == pytest.approx(1e-5 + (1e-3 - 1e-5) * 0.25) and po.lr_at(100) == pytest.approx(1e-5)
+    fa = LRSchedule("flat_anneal", 1e-3, 100, warmup_ratio=0.1, min_lr=0.0, flat_fraction=0.5)
+    assert fa.lr_at(5) < 1e-3 and fa.lr_at(30) == pytest.approx(1e-3) and 0 < fa.lr_at(80) < 1e-3 and fa.lr_at(100) == pytest.approx(0.0, abs=1e-12)
+    restored = LRSchedule("cosine", 1.0, 1)
+    restored.load_state_dict(ms.state_dict())
+    assert restored.lr_at(60) == ms.lr_at(60)
+    assert Config(lr_scheduler="poly", lr_power=2.0).lr_power == 2.0
 
 
 # -- orchestrator ---------------------------------------------------------------------------------------------------
