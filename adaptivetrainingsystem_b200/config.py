@@ -279,7 +279,7 @@ class Config:
     expert_parallel_size: Optional[int] = None
     # -- sharding (DeepSpeed-compatible names) -----------------------------
     use_deepspeed: bool = False
-    optimizer: str = "adamw"  # adamw | lamb | sgd
+    optimizer: str = "adamw"  # adamw | lamb | sgd | lars
     zero_stage: int = 0
     cpu_offload: bool = False
     cpu_offload_optimizer: bool = False

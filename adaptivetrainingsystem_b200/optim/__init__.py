@@ -218,6 +218,49 @@ class LAMBRule(UpdateRule):
         param_out.copy_(master.to(param_out.dtype))
 
 
+class LARSRule(UpdateRule):
+    """LARS (You et al. 2017; the vendored ``colossalai/nn/optimizer/lars.py``): SGD with momentum whose step is scaled per
+    tensor by ``trust * |w| / (|g| + wd |w| + eps)``.  ``segments`` / ``group`` as in :class:`LAMBRule`: a tensor cut by a shard
+    boundary gets its norms completed by an all-reduce.  Tensor operations of the framework, not a kernel of its own: the
+    rule exists for parity of the optimiser list; vector-shaped tensors (norm gains) are better left to a group without decay."""
+    name = "lars"
+
+    def __init__(self, momentum: float = 0.9, trust_coefficient: float = 1e-3, eps: float = 1e-8):
+        self.momentum, self.trust, self.eps = momentum, trust_coefficient, eps
+
+    def init_state(self, master):
+        return {"momentum_buffer": torch.zeros_like(master)}
+
+    def update(self, state, master, grad, param_out, hyper, clip_state, decay, segments=None, group=None, n_segments=None):
+        import torch.distributed as dist
+        segments = [tuple(x) if len(x) == 3 else (x[0], x[1], i) for i, x in enumerate(segments)] if segments else [(0, master.numel(), 0)]
+        n_seg = int(n_segments) if n_segments else max(x[2] for x in segments) + 1
+        multi = group is not None and dist.is_initialized() and dist.get_world_size(group) > 1
+        skip = clip_state[2] != 0.0 if clip_state is not None else None          # non-finite gradients: leave everything as it is
+        gs = clip_state[0] if clip_state is not None else 1.0
+        lr, wd = hyper[0], hyper[4] * (1.0 if decay else 0.0)
+        g = grad.float() * gs
+        sums = torch.zeros(n_seg, 2, dtype=torch.float32, device=master.device)
+        for (s, n, i) in segments:
+            sums[i, 0] += master[s:s + n].pow(2).sum()
+            sums[i, 1] += g[s:s + n].pow(2).sum()
+        if multi:
+            dist.all_reduce(sums, group=group)
+        wn, gn = sums[:, 0].sqrt(), sums[:, 1].sqrt()
+        ratio = torch.where((wn > 0) & (gn > 0), self.trust * wn / (gn + wd * wn + self.eps), torch.ones_like(wn))
+        buf = state["momentum_buffer"]
+        new_buf = buf * self.momentum
+        for (s, n, i) in segments:
+            new_buf[s:s + n] += (lr * ratio[i]) * (g[s:s + n] + wd * master[s:s + n])
+        if skip is not None:
+            new_buf = torch.where(skip, buf, new_buf)
+            master.copy_(torch.where(skip, master, master - new_buf))
+        else:
+            master.sub_(new_buf)
+        buf.copy_(new_buf)
+        param_out.copy_(master.to(param_out.dtype))
+
+
 class HostAdamWRule(UpdateRule):
     """AdamW with master / m / v in pinned host memory (optimiser-state offload).  Each step copies the reduced gradient
     shard device -> host, runs the AVX kernel, and copies the bf16 parameter shard back; the GPU keeps only parameters and
@@ -296,7 +339,7 @@ class HostAdamWRule(UpdateRule):
         master.copy_(state["master_host"], non_blocking=False) if master.device.type == "cpu" else None
 
 
-RULES = {"adamw": AdamWRule, "sgd": SGDRule, "lamb": LAMBRule, "adamw_host": HostAdamWRule}
+RULES = {"adamw": AdamWRule, "sgd": SGDRule, "lamb": LAMBRule, "lars": LARSRule, "adamw_host": HostAdamWRule}
 
 
 def make_rule(name: str, **kw) -> UpdateRule:
@@ -306,4 +349,4 @@ def make_rule(name: str, **kw) -> UpdateRule:
         raise ValueError(f"unknown optimizer {name!r}; choose from {sorted(RULES)}") from None
 
 
-__all__ = ["UpdateRule", "AdamWRule", "SGDRule", "LAMBRule", "HostAdamWRule", "make_rule", "scale_check", "absmax", "RULES"]
+__all__ = ["UpdateRule", "AdamWRule", "SGDRule", "LAMBRule", "LARSRule", "HostAdamWRule", "make_rule", "scale_check", "absmax", "RULES"]

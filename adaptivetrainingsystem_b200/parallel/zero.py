@@ -280,7 +280,7 @@ class ShardedEngine:
                     b.rule_state = self.rule.init_state(b.master)
                     if self.optimizer_name == "adamw_host":  # the device copies of the state are not needed any more
                         b.exp_avg = b.exp_avg_sq = torch.zeros(0, device=self.device)
-                kw = {"n_segments": len(b.params)} if self.optimizer_name == "lamb" else {}
+                kw = {"n_segments": len(b.params)} if self.optimizer_name in ("lamb", "lars") else {}
                 self.rule.update(b.rule_state, b.master, g, b.flat_param[lo:hi], self.hyper, self.clip_state, b.decay,
                                  segments=b.segments_in(lo, hi), group=b.group if b.shard_states and b.W > 1 else None, **kw)
             self._gather(b)

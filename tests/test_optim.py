@@ -52,6 +52,33 @@ def test_lamb_rule_trust_ratio_and_segments():
     assert torch.equal(master, frozen)
 
 
+def test_lars_rule_scales_every_tensor_by_its_own_trust_ratio():
+    torch.manual_seed(3)
+    master = torch.randn(96)
+    segs = [(0, 64, 0), (64, 32, 1)]
+    rule = optim.LARSRule(momentum=0.9, trust_coefficient=0.5)
+    st = rule.init_state(master)
+    out = torch.zeros(96)
+    g = torch.randn(96) * torch.cat([torch.full((64,), 10.0), torch.full((32,), 0.1)])     # very different gradient scales
+    before = master.clone()
+    h = _hyper(step=1.0)
+    lr, wd = float(h[0]), float(h[4])
+    rule.update(st, master, g, out, h, None, True, segments=segs)
+    for s, n, _ in segs:
+        w, gg = before[s:s + n], g[s:s + n]
+        ratio = 0.5 * w.norm() / (gg.norm() + wd * w.norm() + 1e-8)
+        assert torch.allclose(before[s:s + n] - master[s:s + n], lr * ratio * (gg + wd * w), atol=1e-6)
+    assert torch.allclose(out, master)
+    # second step: the momentum buffer carries 0.9 of the first
+    first = (before - master).clone()
+    mid = master.clone()
+    rule.update(st, master, torch.zeros(96), out, h, None, False, segments=segs)
+    assert torch.allclose(mid - master, 0.9 * first, atol=1e-6)
+    frozen = master.clone()
+    rule.update(st, master, g, out, h, torch.tensor([1.0, 0.0, 1.0, 0.0]), True, segments=segs)
+    assert torch.equal(master, frozen)
+
+
 def test_host_adamw_matches_torch_all_isa_levels():
     lib = _lib.host_lib()
     if lib is None:
@@ -79,11 +106,12 @@ def test_engine_with_lamb_and_sgd_trains():
     from adaptivetrainingsystem_b200.config import ConfigPresets
     from adaptivetrainingsystem_b200.models.transformer import DeepSeekTransformer
     from adaptivetrainingsystem_b200.parallel.zero import ShardedEngine
-    for name in ("lamb", "sgd", "adamw_host"):
+    for name in ("lamb", "sgd", "adamw_host", "lars"):
         torch.manual_seed(0)
         cfg = ConfigPresets.tiny_cpu()
         model = DeepSeekTransformer(cfg.to_model_config())
-        eng = ShardedEngine(model, lr=5e-3 if name != "sgd" else 5e-2, optimizer=name)
+        kw = dict(optimizer_kwargs=dict(trust_coefficient=0.02)) if name == "lars" else {}
+        eng = ShardedEngine(model, lr={"sgd": 5e-2, "lars": 1.0}.get(name, 5e-3), optimizer=name, **kw)
         ids = torch.randint(0, cfg.vocab_size, (2, 17))
         losses = []
         for _ in range(6):
