@@ -52,3 +52,29 @@ def test_network_report_finds_ports_and_opens_a_store():
     assert rep["rendezvous"]["ok"] and rep["ready_single_node"]
     assert any(i["name"] == "lo" for i in rep["interfaces"])
     assert R.main(["--network", "--json"]) == 0
+
+
+def test_rank_recorder_merges_ranks_and_tensor_detector_sees_allocations(tmp_path):
+    import time
+    import torch
+    from adaptivetrainingsystem_b200.utils.debug_tools import RankRecorder, TensorDetector, timeline_text
+    d = str(tmp_path / "rec")
+    for rank in (0, 1):
+        r = RankRecorder(rank, d)
+        with r.record("forward"):
+            time.sleep(0.002)
+        with r.record("backward"):
+            time.sleep(0.001)
+        assert r.export().endswith(f"rank_{rank}.json")
+    events = RankRecorder.merge(d)
+    assert len(events) == 4 and events[0]["start"] == 0.0 and {e["rank"] for e in events} == {0, 1}
+    assert all(e["end"] >= e["start"] for e in events)
+    text = timeline_text(events, 40)
+    assert text.count("rank") == 2 and "A=backward" in text and "B=forward" in text
+    det = TensorDetector(include_cpu=True)
+    det.detect()
+    keep = torch.zeros(1000, 3)
+    rep = det.detect()
+    assert any(shape == (1000, 3) for _, shape, _, _ in rep["new"]) and rep["bytes_per_device"]["cpu"] >= 12000
+    del keep
+    assert any(shape == (1000, 3) for _, shape, _, _ in det.detect()["gone"])
